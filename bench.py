@@ -1,0 +1,453 @@
+#!/usr/bin/env python
+"""Benchmark of the 4-bit affine quantized linear on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5]
+                    [--impl ours|reference]
+
+Default (what the headline metric is quoted on): the decode-layer QMV set of an
+8B Qwen3-style decoder at batch 1 -- q, k, v, gate, up, down at M = 1 -- for all
+36 layers with distinct weights (3.57 GB, larger than L2, so every launch
+streams from HBM). One step = one pass over the 36 layers = 216 GEMV launches.
+`value` is algorithmic GB/s with everything resident in HBM; `e2e` is the same
+pass driven through the C ABI with the step's activations copied from pinned
+host memory and the result read back, inside the timed region. The same JSON
+line carries `qmm`: the tensor-core GEMM on the prefill / DiT shapes in
+TFLOP/s (column-split with an NCCL all-gather when N > 1).
+
+With N > 1 (launched under torchrun) the QMV set runs as N independent replicas
+(decode at batch 1 does not shard; weak scaling); the QMM section is the part
+that is partitioned across GPUs.
+
+Inputs are synthetic: weights N(0, 0.02) quantised with the reference recipe on
+the device, activations N(0, 1) bf16; seeded.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+LAYERS = 36
+
+# DRAM traffic per launch measured once with ncu (dram__bytes_read.sum +
+# dram__bytes_write.sum), as a multiple of the algorithmic bytes of that launch;
+# see profiles/. None until a capture exists.
+QMV_TRAFFIC_RATIO = None
+QMM_TRAFFIC_RATIO = None
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                "source": "measured"}
+    return {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": FALLBACK_BF16_TFLOPS,
+            "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-i", str(self.idx), "-lms", "100"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [c.strip() for c in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                    "sw_power_cap"), f[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), samples=len(sm),
+                       reasons=sorted(reasons))
+        return out
+
+
+def dist_env(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        args.gpus = world
+    return rank, world, local
+
+
+# ------------------------------------------------------------------ reference arm
+
+def run_reference(args, rank, world):
+    """The reference's CPU path for this op, timed on the host cores. The reference has no
+    CPU matmul: this is its f32 dequantise routine plus a plain blocked fp32 GEMM (the
+    oracle port), all host threads. Each step is a bounded sample of the workload."""
+    if rank != 0:
+        return
+    import numpy as np
+
+    import oracle
+    from vpipe_b200 import synth
+    oracle.build()
+    cfg = synth.CONFIGS["C2"]
+    layer = []
+    for p in cfg.projs:   # one decoder layer = the sample processed per step
+        codes, s, b = synth.random_qweight(p.N, p.K, synth.seed_for("ref", p.name))
+        x = synth.activations_bf16(1, p.K, synth.seed_for("refx", p.name))
+        layer.append((codes, s, b, x, synth.qmv_bytes(p.K, p.N, 1)))
+    bytes_step = sum(t[4] for t in layer)
+    threads = oracle.max_threads()
+
+    def step():
+        t = 0.0
+        for codes, s, b, x, _ in layer:
+            t += oracle.cpu_linear_seconds(codes, s, b, x, threads)[0]
+        return t
+
+    for _ in range(max(args.warmup, 1)):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    val = bytes_step * args.steps / dt / 1e9
+    line = {
+        "impl": "reference", "metric": "int4_qmv_hbm_gbps", "value": val, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int4*bf16->f32", "data": "synthetic",
+        "config": {"workload": "C2 decode-layer QMV set, 8B Qwen3-style decoder, M=1",
+                   "sample": "1 of 36 layers per step (6 projections, 99.2 MB of weights)"},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": "one decoder layer (q,k,v,gate,up,down at M=1) per step; "
+                                   "f32 dequantise + blocked fp32 GEMM, OpenMP"},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------ our arm
+
+def make_linear(torch, ops, N, K, seed, dev):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    w = (torch.randn((N, K), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    codes, s16, b16 = ops.quantize(w)
+    s, b = ops.scales_to_bf16(s16), ops.scales_to_bf16(b16)
+    del w, s16, b16
+    return codes, s, b
+
+
+def timed(torch, fn, steps, warmup, barrier):
+    """W warm-up + K timed steps between barriers; CUDA events on the current stream."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    return e0.elapsed_time(e1) / 1e3  # seconds
+
+
+def max_over_ranks(torch, dist, world, t, dev):
+    if world == 1:
+        return t
+    v = torch.tensor([t], device=dev, dtype=torch.float64)
+    dist.all_reduce(v, op=dist.ReduceOp.MAX)
+    return float(v.item())
+
+
+def bench_qmv(torch, dist, ops, synth, args, rank, world, dev, pk):
+    cfg = synth.CONFIGS["C2"]
+    layers = []
+    bytes_step = 0
+    xs = {}
+    for K in sorted({p.K for p in cfg.projs}):
+        g = torch.Generator(device=dev).manual_seed(synth.seed_for("x", K, rank))
+        xs[K] = torch.randn((1, K), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    problems = []
+    for layer in range(LAYERS):
+        for p in cfg.projs:
+            codes, s, b = make_linear(torch, ops, p.N, p.K, synth.seed_for("w", layer, p.name, rank), dev)
+            y = torch.empty((1, p.N), dtype=torch.bfloat16, device=dev)
+            problems.append((codes, s, b, xs[p.K], y))
+            bytes_step += synth.qmv_bytes(p.K, p.N, 1)
+        layers.append(problems[-len(cfg.projs):])
+    descs = ops.qmv_set(problems)
+    launches_step = len(problems)
+    torch.cuda.synchronize()
+
+    def direct():
+        ops.qmv_batch(descs)
+
+    # Replay the whole pass as one CUDA graph (launch-bound otherwise: 216 launches of 2-15 us).
+    mode = "cuda-graph"
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            direct()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            direct()
+        step = graph.replay
+        step()
+        torch.cuda.synchronize()
+    except Exception as e:  # fall back to plain launches, and say so
+        mode = f"direct-launches ({type(e).__name__})"
+        step = direct
+
+    barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    t = timed(torch, step, args.steps, args.warmup, barrier)
+    clocks = sampler.stop()
+    t = max_over_ranks(torch, dist, world, t, dev)
+    value = bytes_step * args.steps * world / t / 1e9
+
+    # e2e: the step's activations come from pinned host memory, the last layer's outputs go back
+    host_x = {K: torch.randn((1, K)).to(torch.bfloat16).pin_memory() for K in xs}
+    last = layers[-1]
+    host_y = [torch.empty((1, pr[4].shape[1]), dtype=torch.bfloat16).pin_memory() for pr in last]
+    h2d = sum(v.numel() * 2 for v in host_x.values())
+    d2h = sum(v.numel() * 2 for v in host_y)
+
+    def e2e_step():
+        for K, hx in host_x.items():
+            xs[K].copy_(hx, non_blocking=True)
+        step()
+        for hy, pr in zip(host_y, last):
+            hy.copy_(pr[4], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    te = timed(torch, e2e_step, args.steps, args.warmup, barrier)
+    te = max_over_ranks(torch, dist, world, te, dev)
+    e2e_val = bytes_step * args.steps * world / te / 1e9
+    assert ops.device_status() == 0
+
+    per_gpu = bytes_step * args.steps / t / 1e9
+    roof = {"bound": "hbm", "achieved": per_gpu, "peak": pk["hbm_gbs"], "unit": "GB/s",
+            "frac": per_gpu / pk["hbm_gbs"], "peak_source": pk["source"],
+            "kernel": "affine_qmv_w4g64_kernel", "launches_per_step": launches_step,
+            "bytes_per_launch_avg": bytes_step / launches_step,
+            "traffic": (QMV_TRAFFIC_RATIO * bytes_step / launches_step) if QMV_TRAFFIC_RATIO else None}
+    return {
+        "value": value, "t": t, "bytes_step": bytes_step, "launches_step": launches_step,
+        "clocks": clocks, "roofline": roof, "mode": mode,
+        "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": te / args.steps * 1e3},
+    }
+
+
+def bench_qmm(torch, dist, ops, synth, args, rank, world, dev, pk, key, comm):
+    """QMM on one config's shapes; column-split + all-gather when world > 1."""
+    cfg = synth.CONFIGS[key]
+    M = cfg.M
+    out = {"config": key, "M": M, "shapes": []}
+    barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
+    steps = max(3, min(args.steps, 10))
+    tot_flops, tot_t = 0.0, 0.0
+    for p in cfg.projs:
+        if world > 1 and p.N % (8 * world):
+            continue
+        flops = synth.qmm_flops(p.K, p.N, M)
+        ns = p.N // world
+        codes, s, b = make_linear(torch, ops, ns, p.K, synth.seed_for("w", key, p.name, rank), dev)
+        g = torch.Generator(device=dev).manual_seed(synth.seed_for("x", key, p.name))
+        x = torch.randn((M, p.K), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        if world == 1:
+            y = torch.empty((M, p.N), dtype=torch.bfloat16, device=dev)
+            fn = lambda: ops.qmm(codes, s, b, x, out=y)  # noqa: E731
+        else:
+            y = torch.empty((world, M, ns), dtype=torch.bfloat16, device=dev)
+            fn = lambda: comm.qmm(codes, s, b, x, y, None, args.m_chunks)  # noqa: E731
+        t = timed(torch, fn, steps, 3, barrier)
+        t = max_over_ranks(torch, dist, world, t, dev) / steps
+        rec = {"name": p.name, "K": p.K, "N": p.N, "ms": t * 1e3, "tflops": flops / t / 1e12}
+        if world > 1:   # compute alone, for the split between GEMM and all-gather
+            ymine = y[rank]
+            tc = timed(torch, lambda: ops.qmm(codes, s, b, x, out=ymine), steps, 2, barrier)
+            rec["gemm_only_ms"] = max_over_ranks(torch, dist, world, tc, dev) / steps * 1e3
+            rec["gather_bytes_per_gpu"] = (world - 1) * M * ns * 2
+        out["shapes"].append(rec)
+        tot_flops += flops
+        tot_t += t
+        del codes, s, b, x, y
+        torch.cuda.empty_cache()
+    assert ops.device_status() == 0
+    if tot_t > 0:
+        agg = tot_flops / tot_t / 1e12
+        out.update(metric="int4_qmm_tflops", value=agg, unit="TFLOP/s", n_gpus=world,
+                   scaling="strong" if world > 1 else "weak",
+                   roofline={"bound": "tensor", "achieved": agg / world, "peak": pk["bf16_tflops"],
+                             "unit": "TFLOP/s", "frac": agg / world / pk["bf16_tflops"],
+                             "peak_source": pk["source"] + " (burst, cuBLAS bf16)",
+                             "kernel": "affine_qmm_w4g64_kernel",
+                             "traffic": None})
+    return out
+
+
+def cpu_baseline(synth, seconds_budget=12.0):
+    """The oracle port (f32 dequantise + blocked fp32 GEMM, all host threads) on a bounded
+    sample of the C2 set: whole decoder layers until the time budget is used."""
+    import oracle
+    oracle.build()
+    cfg = synth.CONFIGS["C2"]
+    layer = []
+    for p in cfg.projs:
+        codes, s, b = synth.random_qweight(p.N, p.K, synth.seed_for("cpu", p.name))
+        x = synth.activations_bf16(1, p.K, synth.seed_for("cpux", p.name))
+        layer.append((codes, s, b, x))
+    bytes_layer = sum(synth.qmv_bytes(p.K, p.N, 1) for p in cfg.projs)
+    threads = oracle.max_threads()
+    for codes, s, b, x in layer:   # warm
+        oracle.cpu_linear_seconds(codes, s, b, x, threads)
+    t, n = 0.0, 0
+    while t < seconds_budget and n < LAYERS:
+        for codes, s, b, x in layer:
+            t += oracle.cpu_linear_seconds(codes, s, b, x, threads)[0]
+        n += 1
+    return {"value": bytes_layer * n / t / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"{n} of {LAYERS} decoder layers (6 QMV projections each), "
+                      "f32 dequantise + blocked fp32 GEMM, OpenMP"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5"],
+                    help="c2: the headline line (QMV set + QMM section); c3/c4/c5: QMM only")
+    ap.add_argument("--qmm", default="C4", help="config of the QMM section of the headline line")
+    ap.add_argument("--m-chunks", dest="m_chunks", type=int, default=1)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank, world, local = dist_env(args)
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import vpipe_b200
+    from vpipe_b200 import ops, shard, synth
+    vpipe_b200.lib()  # raises if the CUDA library is missing: there is no fallback
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (vpipe_b200 has no CPU path)")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    comm = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        comm = shard.NsplitComm(rank, world, dev)
+    pk = peaks()
+
+    if args.workload == "c2":
+        q = bench_qmv(torch, dist, ops, synth, args, rank, world, dev, pk)
+        torch.cuda.empty_cache()
+        qmm = bench_qmm(torch, dist, ops, synth, args, rank, world, dev, pk, args.qmm, comm)
+        line = {
+            "metric": "int4_qmv_hbm_gbps", "value": q["value"], "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": q["t"] / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int4*bf16->f32", "data": "synthetic",
+            "config": {"workload": "C2 decode-layer QMV set, 8B Qwen3-style decoder, M=1",
+                       "layers": LAYERS, "projections": "q,k,v,gate,up,down",
+                       "bytes_per_step": q["bytes_step"], "launch_mode": q["mode"],
+                       "l2": "36 layers of distinct weights (3.57 GB) exceed L2; no flush needed",
+                       "parallelism": "replicas only" if world > 1 else "1 GPU"},
+            "roofline": q["roofline"], "e2e": q["e2e"], "clocks": q["clocks"],
+            "gpu_launches": q["launches_step"] * args.steps,
+            "qmm": qmm,
+        }
+        if rank == 0 and world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(synth)
+    else:
+        key = args.workload.upper()
+        sampler = ClockSampler(dev.index)
+        sampler.start()
+        qmm = bench_qmm(torch, dist, ops, synth, args, rank, world, dev, pk, key, comm)
+        clocks = sampler.stop()
+        line = {
+            "metric": "int4_qmm_tflops", "value": qmm.get("value"), "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": sum(s["ms"] for s in qmm["shapes"]),
+            "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+            "dtype": "int4*bf16->f32", "data": "synthetic",
+            "config": {"workload": f"{key} {synth.CONFIGS[key].what}", "M": synth.CONFIGS[key].M,
+                       "l2": "x + y of every shape exceed L2", "m_chunks": args.m_chunks,
+                       "parallelism": f"column-split x{world} + NCCL all-gather" if world > 1 else "1 GPU"},
+            "roofline": qmm.get("roofline"), "clocks": clocks, "shapes": qmm["shapes"],
+            "gpu_launches": len(qmm["shapes"]) * max(3, min(args.steps, 10)),
+        }
+    if comm is not None:
+        comm.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

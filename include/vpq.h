@@ -1,0 +1,194 @@
+/* vpq.h -- C ABI of the B200 (sm_100a) 4-bit affine group-quantized linear.
+ *
+ * Drop-in boundary for the one operator family vpipe (tgo-app-dev/vpipe)
+ * dispatches for every quantized Linear: the weight-only int4, group-64
+ * affine QMV (decode) / QMM (prefill, DiT), its dequantizer and its forward
+ * quantizer. The reference reaches these through its metal-compute kernel
+ * calling convention (bind buffer slots, set int constants, dispatch); each
+ * entry point below takes exactly those slots as plain device pointers and
+ * sizes, and cites the reference interface it replaces.
+ *
+ * Conventions (all entry points)
+ *  - Pointers are CUDA device pointers unless a name ends in _host. The caller
+ *    owns every buffer; nothing here allocates, frees or synchronises unless
+ *    stated. Work is enqueued on `stream` (a cudaStream_t passed as void*; NULL
+ *    is the legacy default stream) and is asynchronous, like an encoded but
+ *    uncommitted Metal dispatch (apple-silicon/metal-compute/compute-encoder.h:188,
+ *    command-stream.h:144).
+ *  - Layout, row-major:  w u32 [N, K/8]  (nibble i of word j of row n is
+ *    k = 8j+i, low nibble first);  scales, biases [N, K/64]  (biases is the
+ *    affine zero point, not a Linear bias);  x [M, K];  y [M, N].
+ *    gpu-kernels/metal/quant/affine_qmv.metal:8-26, affine_dequant.metal:46-47.
+ *  - 16-bit floats are raw bit patterns (bf16 unless stated f16).
+ *  - Return value: VPQ_OK or an error code; nothing is launched on error and
+ *    vpq_last_error() gives a message. There is no CPU fallback: on a machine
+ *    without a usable sm_100 device the compute entry points return
+ *    VPQ_ERR_CUDA. The reference signals the same conditions with
+ *    valid()==false / bool returns (compute-library.h:134, affine-quantizer.cc:57).
+ *  - Alignment: w, scales, biases, x, y must be 16-byte aligned; K % 64 == 0.
+ */
+#ifndef VPQ_H
+#define VPQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VPQ_VERSION 100
+
+typedef enum vpq_status {
+  VPQ_OK = 0,
+  VPQ_ERR_INVALID_ARG = 1, /* null pointer, non-positive size, K % 64 != 0 ...   */
+  VPQ_ERR_ALIGNMENT = 2,   /* a pointer is not 16-byte aligned                    */
+  VPQ_ERR_UNSUPPORTED = 3, /* shape outside what the kernel handles               */
+  VPQ_ERR_CUDA = 4,        /* CUDA runtime / driver error, or no sm_100 device    */
+  VPQ_ERR_NCCL = 5,        /* NCCL missing or returned an error                   */
+  VPQ_ERR_TIMEOUT = 6,     /* a bounded device-side wait gave up                  */
+  VPQ_ERR_NOT_FOUND = 7    /* vpq_function(): unknown (library, entry) pair       */
+} vpq_status;
+
+int vpq_version(void);
+const char* vpq_status_string(int status);
+/* Message for the calling thread's most recent failing call ("" if none). */
+const char* vpq_last_error(void);
+
+/* Byte sizes of the quantizer's three outputs.
+ * Replaces AffineQuantizer::weight_bytes / scale_bytes,
+ * generative-models/quantize/affine-quantizer.h:37-40. */
+size_t vpq_weight_bytes(int N, int K, int bits);
+size_t vpq_scale_bytes(int N, int K, int group);
+
+/* Forward quantizer: dense W[N,K] (f16 or bf16) -> codes u32 [N,K/8],
+ * scales f16 [N,K/64], biases f16 [N,K/64]; clip 1.0 = plain min/max.
+ * Bit-exact with the reference shader.
+ * Replaces kernel affine_quant_w4_g64 (slots 0:x 1:w 2:s 3:b 4:K 5:N 6:clip),
+ * gpu-kernels/metal/quant/affine_dequant.metal:243-301, and the dispatch in
+ * AffineQuantizer::quantize_linear, generative-models/quantize/affine-quantizer.cc:52-84. */
+int vpq_affine_quant_w4_g64(const void* w_elt, int src_is_bf16, uint32_t* codes,
+                            void* scales_f16, void* biases_f16,
+                            int64_t K, int64_t N, float clip, void* stream);
+
+/* FP32 checkpoint tensor -> BF16 (round to nearest even) before quantizing.
+ * Replaces narrow_f32_bf16_, generative-models/quantize/model-quantizer.cc:48-62. */
+int vpq_narrow_f32_bf16(const float* src, void* dst_bf16, int64_t n, void* stream);
+
+/* On-disk F16 scales / biases -> bf16 at load (RNE through f32).
+ * Replaces the F16 branch of to_f16_, generative-models/flux2/metal-flux2-transformer.cc:65-91
+ * (same conversion in generative-models/qwen3/metal-qwen-model.cc:203-213). */
+int vpq_scales_f16_to_bf16(const void* src_f16, void* dst_bf16, int64_t n, void* stream);
+
+/* Dequantize to dense bf16 [N,K]: bf16_rne(float(s)*q + float(b)). Bit-exact.
+ * Replaces kernel affine_dequant_w4g64 (slots 0:w 1:scales 2:biases 3:ydeq 4:K 5:N),
+ * gpu-kernels/metal/quant/affine_dequant.metal:25-58. */
+int vpq_affine_dequant_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
+                                  void* ydeq, int64_t K, int64_t N, void* stream);
+
+/* Decode GEMV: y[m,n] = sum_k x[m,k] * (s*q + b), f32 accumulate, bf16 out.
+ * Every row m streams the whole weight again, as in the reference; meant for
+ * M = 1 (small M works, M >= 16 belongs to vpq_affine_qmm_w4g64_bf16).
+ * K <= 32768. Replaces kernel affine_qmv_w4g64 in library affine_qmv_bf16
+ * (slots 0:w 1:scales 2:biases 3:x 4:y 5:K 6:N; M from the dispatch grid),
+ * gpu-kernels/metal/quant/affine_qmv.metal:286-301, dispatched at
+ * generative-models/qwen3/metal-qwen-model.cc:3033-3048. */
+int vpq_affine_qmv_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
+                              const void* x, void* y, int64_t K, int64_t N, int64_t M,
+                              void* stream);
+
+/* A set of independent GEMVs enqueued back to back (one launch each, in order),
+ * e.g. the q | k | v or gate | up projections of one decoder layer. descs_host
+ * is a host array read during the call. Each launch opts into programmatic
+ * dependent launch, so the weight stream of launch i+1 starts while launch i
+ * drains. Replaces ComputeEncoder::concurrent_scope around the per-projection
+ * dispatches, apple-silicon/metal-compute/compute-encoder.h:156-181, as used in
+ * encode_decode_step_, generative-models/qwen3/metal-qwen-model.cc:3004-3074. */
+typedef struct vpq_linear_desc {
+  const uint32_t* w;
+  const void* scales;
+  const void* biases;
+  const void* x;
+  void* y;
+  int64_t K, N, M;
+} vpq_linear_desc;
+int vpq_affine_qmv_w4g64_bf16_batch(const vpq_linear_desc* descs_host, int count, void* stream);
+
+/* Prefill / DiT GEMM: y[M,N] = x[M,K] @ dequant(W)[N,K]^T. W is dequantised
+ * to bf16 tile by tile in shared memory (bit-identical to
+ * vpq_affine_dequant_w4g64_bf16), multiplied on the tcgen05 tensor cores with
+ * f32 accumulation in tensor memory, rounded once to bf16. M and N tails are
+ * handled; K % 64 == 0. Replaces kernels affine_qmm_steel_w4g64[_bm64|_bm128]
+ * in library affine_qmm_steel_bf16 (slots 0..4 as QMV, 5:K 6:N 7:M),
+ * gpu-kernels/metal/quant/affine_qmm_steel.metal:461-561, and
+ * affine_qmm_mma_w4g64, gpu-kernels/metal/quant/affine_qmm_mma.metal:50-128;
+ * dispatched at generative-models/flux2/metal-flux2-transformer.cc:1291-1330. */
+int vpq_affine_qmm_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
+                              const void* x, void* y, int64_t K, int64_t N, int64_t M,
+                              void* stream);
+
+/* Device-side status of the tensor-core kernels: every wait inside them is
+ * bounded; one that gives up records where and the kernel returns. Reads the
+ * status word of the current device back to the host (synchronises `stream`),
+ * clears it, and returns VPQ_OK or VPQ_ERR_TIMEOUT with *detail set to the
+ * recorded code. The analogue of Fence::wait_ok(&reason),
+ * apple-silicon/metal-compute/command-stream.h:92-99. */
+int vpq_device_status(void* stream, uint32_t* detail);
+
+/* --- calling by the reference's (library, entry) strings ------------------
+ * Replaces MetalCompute::load_library(name).function(entry),
+ * apple-silicon/metal-compute/metal-compute.h:301, compute-library.h:134.
+ * Returns NULL for an unknown pair (the reference returns an invalid handle).
+ * Known libraries: affine_qmv_bf16, affine_qmm_steel_bf16, affine_qmm_mma_bf16,
+ * affine_dequant_bf16, affine_dequant (quantizer, f16 source). */
+typedef struct vpq_function_s vpq_function;
+const vpq_function* vpq_function_lookup(const char* library, const char* entry);
+const char* vpq_function_name(const vpq_function* fn);
+
+/* One dispatch with the reference's slot numbering: buffers[i] is what
+ * set_buffer(i, ...) bound (byte offsets already applied), K / N / M / clip are
+ * what set_constant bound. The grid is derived from the shapes, so the
+ * reference's grid / threadgroup arguments have no counterpart. Slot layouts:
+ *   QMV, QMM : 0:w 1:scales 2:biases 3:x 4:y            affine_qmv.metal:19-26
+ *   dequant  : 0:w 1:scales 2:biases 3:ydeq             affine_dequant.metal:14
+ *   quant    : 0:x 1:w 2:scales_f16 3:biases_f16        affine_dequant.metal:288-296
+ * Replaces ComputeEncoder::set_function/set_buffer/set_constant/dispatch,
+ * apple-silicon/metal-compute/compute-encoder.h:80-83,188. */
+typedef struct vpq_dispatch_args {
+  const void* buffers[8];
+  int64_t K, N, M;
+  float clip;
+} vpq_dispatch_args;
+int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* args, void* stream);
+
+/* --- column-split over the GPUs of one box --------------------------------
+ * No counterpart in the reference (it is single-GPU). Rank r of `world` owns
+ * rows [r*N/world, (r+1)*N/world) of w / scales / biases (contiguous slices of
+ * all three arrays), x is replicated, and the ranks' output column blocks are
+ * all-gathered with NCCL. NCCL is loaded with dlopen at first use. */
+typedef struct vpq_comm_s vpq_comm;
+#define VPQ_UNIQUE_ID_BYTES 128
+/* Rank 0 fills id (host memory) and ships it to the other ranks by any means. */
+int vpq_comm_unique_id(void* id_host);
+int vpq_comm_create(const void* id_host, int rank, int world, vpq_comm** out);
+int vpq_comm_destroy(vpq_comm* comm);
+int vpq_comm_rank(const vpq_comm* comm);
+int vpq_comm_world(const vpq_comm* comm);
+
+/* y_shards: device buffer [world, M, N/world] bf16 (shard-major); each rank
+ * computes its own block in place and receives the others'. If y_rowmajor is
+ * not NULL the gathered blocks are also written as row-major [M, N].
+ * N % world == 0. m_chunks >= 1 splits M so that the gather of one chunk
+ * overlaps the GEMM of the next (uses two internal streams ordered after and
+ * before `stream` with events created at vpq_comm_create). */
+int vpq_affine_qmm_w4g64_bf16_nsplit(vpq_comm* comm,
+                                     const uint32_t* w_shard, const void* scales_shard,
+                                     const void* biases_shard, const void* x,
+                                     void* y_shards, void* y_rowmajor,
+                                     int64_t K, int64_t N, int64_t M, int m_chunks,
+                                     void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VPQ_H */

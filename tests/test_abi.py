@@ -1,0 +1,111 @@
+"""CPU tests of the C-ABI library: it loads, exports every symbol the header
+declares, validates arguments before touching a device, and fails loudly (no
+CPU path) when asked to compute without a GPU."""
+import ctypes as C
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "vpq.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(vpq_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(vpq):
+    from vpipe_b200 import _lib
+    names = _declared_symbols()
+    assert len(names) >= 20
+    L = vpq.lib()
+    for n in names:
+        assert hasattr(L, n), f"libvpq.so lacks {n}"
+    assert set(names) == {s[0] for s in _lib.SYMBOLS}
+
+
+def test_version_and_status_strings(vpq):
+    L = vpq.lib()
+    assert L.vpq_version() == 100
+    assert vpq.status_string(0) == "ok"
+    for code in range(1, 8):
+        assert vpq.status_string(code) not in ("ok", "unknown status")
+
+
+def test_byte_sizes_mirror_the_quantizer(vpq):
+    # AffineQuantizer::weight_bytes / scale_bytes, affine-quantizer.h:37-40
+    L = vpq.lib()
+    assert L.vpq_weight_bytes(12288, 4096, 4) == 12288 * (4096 * 4 // 32) * 4
+    assert L.vpq_scale_bytes(12288, 4096, 64) == 12288 * 64 * 2
+    assert L.vpq_weight_bytes(16, 128, 8) == 16 * 32 * 4
+
+
+def test_function_table_uses_reference_names(vpq):
+    ops = vpq.ops
+    for libname, entry in [("affine_qmv_bf16", "affine_qmv_w4g64"),
+                           ("affine_qmm_steel_bf16", "affine_qmm_steel_w4g64"),
+                           ("affine_qmm_steel_bf16", "affine_qmm_steel_w4g64_bm64"),
+                           ("affine_qmm_steel_bf16", "affine_qmm_steel_w4g64_bm128"),
+                           ("affine_qmm_mma_bf16", "affine_qmm_mma_w4g64"),
+                           ("affine_dequant_bf16", "affine_dequant_w4g64"),
+                           ("affine_dequant_bf16", "affine_quant_w4_g64"),
+                           ("affine_dequant", "affine_quant_w4_g64")]:
+        fn = ops.function(libname, entry)
+        assert fn, (libname, entry)
+        assert vpq.lib().vpq_function_name(fn).decode() == entry
+    # unknown names give an invalid handle, as the reference's .valid()==false
+    assert not ops.function("affine_qmv_bf16", "no_such_entry")
+    assert not ops.function("no_such_library", "affine_qmv_w4g64")
+    assert "no entry" in vpq.lib().vpq_last_error().decode()
+
+
+def test_argument_validation_happens_before_any_device_work(vpq):
+    L = vpq.lib()
+    buf = (C.c_ubyte * 4096)()
+    p = C.addressof(buf)
+    p16 = (p + 15) & ~15
+    INVALID, ALIGN, UNSUP = 1, 2, 3
+    # null pointers
+    assert L.vpq_affine_qmv_w4g64_bf16(None, p16, p16, p16, p16, 64, 8, 1, None) == INVALID
+    assert L.vpq_affine_qmm_w4g64_bf16(p16, p16, p16, None, p16, 64, 8, 1, None) == INVALID
+    assert L.vpq_affine_dequant_w4g64_bf16(p16, None, p16, p16, 64, 8, None) == INVALID
+    assert L.vpq_affine_quant_w4_g64(p16, 1, p16, p16, None, 64, 8, 1.0, None) == INVALID
+    # K must be a positive multiple of the group size (affine-quantizer.cc:57)
+    assert L.vpq_affine_quant_w4_g64(p16, 1, p16, p16, p16, 96, 8, 1.0, None) == INVALID
+    assert L.vpq_affine_qmv_w4g64_bf16(p16, p16, p16, p16, p16, 100, 8, 1, None) == INVALID
+    assert L.vpq_affine_qmm_w4g64_bf16(p16, p16, p16, p16, p16, 64, 0, 1, None) == INVALID
+    assert L.vpq_affine_dequant_w4g64_bf16(p16, p16, p16, p16, -64, 8, None) == INVALID
+    assert "K%64" in L.vpq_last_error().decode()
+    # alignment
+    assert L.vpq_affine_qmv_w4g64_bf16(p16 + 4, p16, p16, p16, p16, 64, 8, 1, None) == ALIGN
+    assert L.vpq_affine_qmm_w4g64_bf16(p16, p16, p16, p16 + 8, p16, 64, 8, 1, None) == ALIGN
+    # outside the supported range
+    assert L.vpq_affine_qmv_w4g64_bf16(p16, p16, p16, p16, p16, 65536, 8, 1, None) == UNSUP
+    # nsplit argument checks need no communicator
+    assert L.vpq_affine_qmm_w4g64_bf16_nsplit(None, p16, p16, p16, p16, p16, None, 64, 8, 1, 1, None) == INVALID
+    assert L.vpq_dispatch(None, None, None) == INVALID
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="only meaningful without a GPU")
+def test_no_cpu_fallback_without_a_gpu(vpq):
+    """Valid arguments but no device: a loud VPQ_ERR_CUDA, never a silent CPU result."""
+    L = vpq.lib()
+    buf = (C.c_ubyte * 65536)()
+    p16 = (C.addressof(buf) + 15) & ~15
+    CUDA = 4
+    assert L.vpq_affine_qmv_w4g64_bf16(p16, p16, p16, p16, p16, 64, 8, 1, None) == CUDA
+    assert "no CPU path" in L.vpq_last_error().decode() or "CUDA" in L.vpq_last_error().decode()
+    assert L.vpq_affine_qmm_w4g64_bf16(p16, p16, p16, p16, p16, 64, 8, 1, None) == CUDA
+    assert L.vpq_affine_dequant_w4g64_bf16(p16, p16, p16, p16, 64, 8, None) == CUDA
+    assert L.vpq_affine_quant_w4_g64(p16, 1, p16, p16, p16, 64, 8, 1.0, None) == CUDA
+    with pytest.raises(Exception):
+        vpq.ops.qmv(torch.zeros(8, 8, dtype=torch.int32), torch.zeros(8, 1), torch.zeros(8, 1),
+                    torch.zeros(1, 64))
+
+
+def test_python_front_end_refuses_cpu_tensors(vpq):
+    with pytest.raises(Exception):
+        vpq.ops.dequantize(torch.zeros(8, 8, dtype=torch.int32), torch.zeros(8, 1), torch.zeros(8, 1))

@@ -1,0 +1,161 @@
+// api.cu -- status strings, per-thread error message, device checks, byte-size
+// helpers and the (library, entry) function table of the C ABI.
+#include "vpq_common.cuh"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+namespace vpq {
+
+static thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+void clear_error() { g_err[0] = '\0'; }
+
+struct DevInfo {
+  int checked = 0;  // 0 = not yet, 1 = ok, -1 = not sm_100
+  int major = 0, minor = 0, sms = 0;
+};
+static DevInfo g_dev[64];
+static std::mutex g_dev_mu;
+
+static int probe(int* dev_out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return fail(VPQ_ERR_CUDA, "no usable CUDA device (%s); this library has no CPU path",
+                cudaGetErrorString(e));
+  }
+  std::lock_guard<std::mutex> lk(g_dev_mu);
+  DevInfo& d = g_dev[dev];
+  if (d.checked == 0) {
+    if (cudaDeviceGetAttribute(&d.major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&d.minor, cudaDevAttrComputeCapabilityMinor, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(VPQ_ERR_CUDA, "cannot query device %d", dev);
+    }
+    d.checked = (d.major == 10) ? 1 : -1;
+  }
+  *dev_out = dev;
+  return VPQ_OK;
+}
+
+int require_sm100() {
+  int dev = 0;
+  if (int rc = probe(&dev)) { return rc; }
+  if (g_dev[dev].checked != 1) {
+    return fail(VPQ_ERR_CUDA, "device %d is sm_%d%d; the kernels are built for sm_100a only", dev,
+                g_dev[dev].major, g_dev[dev].minor);
+  }
+  return VPQ_OK;
+}
+
+int num_sms() {
+  int dev = 0;
+  if (probe(&dev) != VPQ_OK) { return 148; }
+  return g_dev[dev].sms > 0 ? g_dev[dev].sms : 148;
+}
+
+}  // namespace vpq
+
+using namespace vpq;
+
+extern "C" int vpq_version(void) { return VPQ_VERSION; }
+
+extern "C" const char* vpq_status_string(int status) {
+  switch (status) {
+    case VPQ_OK: return "ok";
+    case VPQ_ERR_INVALID_ARG: return "invalid argument";
+    case VPQ_ERR_ALIGNMENT: return "pointer not 16-byte aligned";
+    case VPQ_ERR_UNSUPPORTED: return "unsupported shape";
+    case VPQ_ERR_CUDA: return "CUDA error or no sm_100 device";
+    case VPQ_ERR_NCCL: return "NCCL error";
+    case VPQ_ERR_TIMEOUT: return "device-side wait timed out";
+    case VPQ_ERR_NOT_FOUND: return "unknown library or entry";
+    default: return "unknown status";
+  }
+}
+
+extern "C" const char* vpq_last_error(void) { return g_err; }
+
+// generative-models/quantize/affine-quantizer.h:37-40
+extern "C" size_t vpq_weight_bytes(int N, int K, int bits) {
+  return (size_t)N * (size_t)(K * bits / 32) * 4u;
+}
+extern "C" size_t vpq_scale_bytes(int N, int K, int group) {
+  return (size_t)N * (size_t)(K / group) * 2u;
+}
+
+// ------------------------------------------------------- function registry
+struct vpq_function_s {
+  const char* library;
+  const char* entry;
+  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src)
+};
+
+// The reference selects the element type with the library-name suffix and
+// keeps entry names unchanged (apple-silicon/metal-compute/CMakeLists.txt:69-72,156-177).
+// The three QMM tile variants share one kernel here (the tile is chosen from
+// the shape), so their names all resolve to it.
+static const vpq_function_s g_functions[] = {
+    {"affine_qmv_bf16", "affine_qmv_w4g64", 0},
+    {"affine_qmm_steel_bf16", "affine_qmm_steel_w4g64", 1},
+    {"affine_qmm_steel_bf16", "affine_qmm_steel_w4g64_bm64", 1},
+    {"affine_qmm_steel_bf16", "affine_qmm_steel_w4g64_bm128", 1},
+    {"affine_qmm_mma_bf16", "affine_qmm_mma_w4g64", 1},
+    {"affine_dequant_bf16", "affine_dequant_w4g64", 2},
+    {"affine_dequant_bf16", "affine_quant_w4_g64", 3},
+    {"affine_dequant", "affine_quant_w4_g64", 4},
+};
+
+extern "C" const vpq_function* vpq_function_lookup(const char* library, const char* entry) {
+  clear_error();
+  if (!library || !entry) {
+    fail(VPQ_ERR_NOT_FOUND, "function_lookup: null name");
+    return nullptr;
+  }
+  for (const vpq_function_s& f : g_functions) {
+    if (std::strcmp(f.library, library) == 0 && std::strcmp(f.entry, entry) == 0) { return &f; }
+  }
+  fail(VPQ_ERR_NOT_FOUND, "function_lookup: no entry '%s' in library '%s'", entry, library);
+  return nullptr;
+}
+
+extern "C" const char* vpq_function_name(const vpq_function* fn) { return fn ? fn->entry : ""; }
+
+extern "C" int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* a, void* stream) {
+  clear_error();
+  if (!fn || !a) { return fail(VPQ_ERR_INVALID_ARG, "dispatch: null function or arguments"); }
+  const void* const* b = a->buffers;
+  switch (fn->kind) {
+    case 0:
+      return vpq_affine_qmv_w4g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
+                                       const_cast<void*>(b[4]), a->K, a->N, a->M < 1 ? 1 : a->M,
+                                       stream);
+    case 1:
+      return vpq_affine_qmm_w4g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
+                                       const_cast<void*>(b[4]), a->K, a->N, a->M, stream);
+    case 2:
+      return vpq_affine_dequant_w4g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2],
+                                           const_cast<void*>(b[3]), a->K, a->N, stream);
+    case 3:
+    case 4:
+      return vpq_affine_quant_w4_g64(b[0], fn->kind == 3 ? 1 : 0,
+                                     static_cast<uint32_t*>(const_cast<void*>(b[1])),
+                                     const_cast<void*>(b[2]), const_cast<void*>(b[3]), a->K, a->N,
+                                     a->clip, stream);
+    default:
+      return fail(VPQ_ERR_NOT_FOUND, "dispatch: corrupt function handle");
+  }
+}

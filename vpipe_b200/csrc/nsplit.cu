@@ -1,0 +1,236 @@
+// nsplit.cu -- column-split QMM over the GPUs of one box.
+//
+// The reference is single-GPU, so this part has no counterpart there. Output
+// columns are independent: rank r owns rows [r*N/G, (r+1)*N/G) of the packed
+// weight, scales and biases (contiguous slices of all three arrays, the same
+// property the reference uses to row-concatenate q|k|v,
+// generative-models/qwen3/metal-qwen-model.cc:214-250), x is replicated, and
+// the only exchange is an all-gather of the output column blocks over
+// NVLink / NVSwitch. NCCL is loaded with dlopen so the library itself has no
+// link-time dependency on it.
+//
+// Each rank's GEMM writes its [M, N/G] block contiguously into a shard-major
+// buffer [G, M, N/G]. With m_chunks > 1 the rows are cut into chunks and the
+// exchange of chunk i (grouped ncclSend / ncclRecv, which may place every
+// peer's rows anywhere) runs on a second stream while chunk i+1 is computed.
+#include "vpq_common.cuh"
+
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <cstring>
+
+struct vpq_comm_s {
+  ncclComm_t comm = nullptr;
+  int rank = 0, world = 1, device = 0;
+  cudaStream_t comm_stream = nullptr;
+  cudaEvent_t ev_start = nullptr, ev_done = nullptr;
+  cudaEvent_t ev_chunk[16] = {};
+};
+
+namespace vpq {
+namespace {
+
+struct Nccl {
+  void* handle = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*GroupStart)() = nullptr;
+  ncclResult_t (*GroupEnd)() = nullptr;
+  const char* (*GetErrorString)(ncclResult_t) = nullptr;
+  bool ok = false;
+};
+
+Nccl& nccl() {
+  static Nccl n;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    const char* names[] = {"libnccl.so.2", "libnccl.so"};
+    for (const char* nm : names) {
+      n.handle = dlopen(nm, RTLD_NOW | RTLD_GLOBAL);
+      if (n.handle) { break; }
+    }
+    if (n.handle) {
+#define VPQ_SYM(field, sym) n.field = reinterpret_cast<decltype(n.field)>(dlsym(n.handle, sym))
+      VPQ_SYM(GetUniqueId, "ncclGetUniqueId");
+      VPQ_SYM(CommInitRank, "ncclCommInitRank");
+      VPQ_SYM(CommDestroy, "ncclCommDestroy");
+      VPQ_SYM(AllGather, "ncclAllGather");
+      VPQ_SYM(Send, "ncclSend");
+      VPQ_SYM(Recv, "ncclRecv");
+      VPQ_SYM(GroupStart, "ncclGroupStart");
+      VPQ_SYM(GroupEnd, "ncclGroupEnd");
+      VPQ_SYM(GetErrorString, "ncclGetErrorString");
+#undef VPQ_SYM
+      n.ok = n.GetUniqueId && n.CommInitRank && n.CommDestroy && n.AllGather && n.Send && n.Recv &&
+             n.GroupStart && n.GroupEnd && n.GetErrorString;
+    }
+  }
+  return n;
+}
+
+#define VPQ_NCCL_OK(expr)                                                              \
+  do {                                                                                 \
+    ncclResult_t _r = (expr);                                                          \
+    if (_r != ncclSuccess) {                                                           \
+      return ::vpq::fail(VPQ_ERR_NCCL, "%s: %s", #expr, nccl().GetErrorString(_r));    \
+    }                                                                                  \
+  } while (0)
+
+// shard-major [G, M, Ns] -> row-major [M, G*Ns] for rows [m0, m1)
+__global__ void __launch_bounds__(256)
+shards_to_rowmajor_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int64_t M,
+                          int ns_vec, int world, int64_t m0, int64_t m1) {
+  const int64_t per_row = (int64_t)ns_vec * world;
+  const int64_t total = (m1 - m0) * per_row;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t m = m0 + i / per_row;
+    const int64_t c = i % per_row;
+    const int r = (int)(c / ns_vec);
+    const int j = (int)(c % ns_vec);
+    out[m * per_row + c] = in[((int64_t)r * M + m) * ns_vec + j];
+  }
+}
+
+}  // namespace
+}  // namespace vpq
+
+using namespace vpq;
+
+extern "C" int vpq_comm_unique_id(void* id_host) {
+  clear_error();
+  if (!id_host) { return fail(VPQ_ERR_INVALID_ARG, "comm_unique_id: null pointer"); }
+  if (!nccl().ok) { return fail(VPQ_ERR_NCCL, "libnccl.so.2 could not be loaded"); }
+  static_assert(sizeof(ncclUniqueId) == VPQ_UNIQUE_ID_BYTES, "unique id size");
+  ncclUniqueId id;
+  VPQ_NCCL_OK(nccl().GetUniqueId(&id));
+  std::memcpy(id_host, &id, sizeof(id));
+  return VPQ_OK;
+}
+
+extern "C" int vpq_comm_create(const void* id_host, int rank, int world, vpq_comm** out) {
+  clear_error();
+  if (!id_host || !out || world < 1 || rank < 0 || rank >= world) {
+    return fail(VPQ_ERR_INVALID_ARG, "comm_create: bad arguments (rank=%d world=%d)", rank, world);
+  }
+  if (!nccl().ok) { return fail(VPQ_ERR_NCCL, "libnccl.so.2 could not be loaded"); }
+  if (int rc = require_sm100()) { return rc; }
+  vpq_comm* c = new vpq_comm_s();
+  c->rank = rank;
+  c->world = world;
+  VPQ_CUDA_OK(cudaGetDevice(&c->device));
+  ncclUniqueId id;
+  std::memcpy(&id, id_host, sizeof(id));
+  ncclResult_t r = nccl().CommInitRank(&c->comm, world, id, rank);
+  if (r != ncclSuccess) {
+    delete c;
+    return fail(VPQ_ERR_NCCL, "ncclCommInitRank: %s", nccl().GetErrorString(r));
+  }
+  VPQ_CUDA_OK(cudaStreamCreateWithFlags(&c->comm_stream, cudaStreamNonBlocking));
+  VPQ_CUDA_OK(cudaEventCreateWithFlags(&c->ev_start, cudaEventDisableTiming));
+  VPQ_CUDA_OK(cudaEventCreateWithFlags(&c->ev_done, cudaEventDisableTiming));
+  for (auto& e : c->ev_chunk) { VPQ_CUDA_OK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming)); }
+  *out = c;
+  return VPQ_OK;
+}
+
+extern "C" int vpq_comm_destroy(vpq_comm* c) {
+  clear_error();
+  if (!c) { return VPQ_OK; }
+  if (c->comm_stream) { cudaStreamSynchronize(c->comm_stream); }
+  if (c->comm) { nccl().CommDestroy(c->comm); }
+  for (auto& e : c->ev_chunk) {
+    if (e) { cudaEventDestroy(e); }
+  }
+  if (c->ev_start) { cudaEventDestroy(c->ev_start); }
+  if (c->ev_done) { cudaEventDestroy(c->ev_done); }
+  if (c->comm_stream) { cudaStreamDestroy(c->comm_stream); }
+  delete c;
+  return VPQ_OK;
+}
+
+extern "C" int vpq_comm_rank(const vpq_comm* c) { return c ? c->rank : -1; }
+extern "C" int vpq_comm_world(const vpq_comm* c) { return c ? c->world : 0; }
+
+extern "C" int vpq_affine_qmm_w4g64_bf16_nsplit(vpq_comm* c, const uint32_t* w_shard,
+                                                const void* scales_shard, const void* biases_shard,
+                                                const void* x, void* y_shards, void* y_rowmajor,
+                                                int64_t K, int64_t N, int64_t M, int m_chunks,
+                                                void* stream) {
+  clear_error();
+  if (!c || !y_shards) { return fail(VPQ_ERR_INVALID_ARG, "qmm_nsplit: null communicator or output"); }
+  const int G = c->world;
+  if (N <= 0 || (N % G) != 0) {
+    return fail(VPQ_ERR_INVALID_ARG, "qmm_nsplit: N=%lld is not a multiple of the %d ranks",
+                (long long)N, G);
+  }
+  if (m_chunks < 1 || m_chunks > 16) {
+    return fail(VPQ_ERR_INVALID_ARG, "qmm_nsplit: m_chunks must be 1..16 (got %d)", m_chunks);
+  }
+  const int64_t Ns = N / G;
+  if (y_rowmajor && (Ns % 8) != 0) {
+    return fail(VPQ_ERR_UNSUPPORTED, "qmm_nsplit: row-major output needs N/world %% 8 == 0");
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  __nv_bfloat16* ys = static_cast<__nv_bfloat16*>(y_shards);
+  __nv_bfloat16* mine = ys + (int64_t)c->rank * M * Ns;
+
+  if (G == 1) {
+    if (int rc = vpq_affine_qmm_w4g64_bf16(w_shard, scales_shard, biases_shard, x, mine, K, Ns, M, stream)) {
+      return rc;
+    }
+    if (y_rowmajor && y_rowmajor != y_shards) {
+      VPQ_CUDA_OK(cudaMemcpyAsync(y_rowmajor, y_shards, (size_t)M * N * 2, cudaMemcpyDeviceToDevice, st));
+    }
+    return VPQ_OK;
+  }
+
+  // chunk boundaries on multiples of 128 rows (the GEMM's row tile)
+  const int64_t row_tiles = (M + 127) / 128;
+  if (m_chunks > row_tiles) { m_chunks = (int)row_tiles; }
+  const uint16_t* xb = static_cast<const uint16_t*>(x);
+  for (int ch = 0; ch < m_chunks; ++ch) {
+    const int64_t m0 = (row_tiles * ch / m_chunks) * 128;
+    int64_t m1 = (row_tiles * (ch + 1) / m_chunks) * 128;
+    if (m1 > M) { m1 = M; }
+    const int64_t rows = m1 - m0;
+    if (rows <= 0) { continue; }
+    if (int rc = vpq_affine_qmm_w4g64_bf16(w_shard, scales_shard, biases_shard, xb + m0 * K,
+                                           mine + m0 * Ns, K, Ns, rows, stream)) {
+      return rc;
+    }
+    VPQ_CUDA_OK(cudaEventRecord(c->ev_chunk[ch], st));
+    VPQ_CUDA_OK(cudaStreamWaitEvent(c->comm_stream, c->ev_chunk[ch], 0));
+    if (m_chunks == 1) {
+      VPQ_NCCL_OK(nccl().AllGather(mine, ys, (size_t)(M * Ns), ncclBfloat16, c->comm, c->comm_stream));
+    } else {
+      VPQ_NCCL_OK(nccl().GroupStart());
+      for (int r = 0; r < G; ++r) {
+        if (r == c->rank) { continue; }
+        VPQ_NCCL_OK(nccl().Send(mine + m0 * Ns, (size_t)(rows * Ns), ncclBfloat16, r, c->comm, c->comm_stream));
+        VPQ_NCCL_OK(nccl().Recv(ys + ((int64_t)r * M + m0) * Ns, (size_t)(rows * Ns), ncclBfloat16, r,
+                                c->comm, c->comm_stream));
+      }
+      VPQ_NCCL_OK(nccl().GroupEnd());
+    }
+    if (y_rowmajor) {
+      const int64_t vecs = rows * (N / 8);
+      int64_t blocks = (vecs + 255) / 256;
+      const int64_t cap = (int64_t)num_sms() * 8;
+      if (blocks > cap) { blocks = cap; }
+      shards_to_rowmajor_kernel<<<(unsigned)blocks, 256, 0, c->comm_stream>>>(
+          reinterpret_cast<const uint4*>(ys), reinterpret_cast<uint4*>(y_rowmajor), M, (int)(Ns / 8), G,
+          m0, m1);
+      VPQ_LAUNCH_OK("shards_to_rowmajor");
+    }
+  }
+  VPQ_CUDA_OK(cudaEventRecord(c->ev_done, c->comm_stream));
+  VPQ_CUDA_OK(cudaStreamWaitEvent(st, c->ev_done, 0));
+  return VPQ_OK;
+}

@@ -1,0 +1,571 @@
+// qmm.cu -- prefill / DiT GEMM over 4-bit affine group-64 weights on the
+// sm_100a tensor cores:  y[M,N] = x[M,K] @ dequant(W)[N,K]^T.
+//
+// Replaces affine_qmm_steel_w4g64[_bm64|_bm128] (qmm_t_impl,
+// gpu-kernels/metal/quant/affine_qmm_steel.metal:318-561) and
+// affine_qmm_mma_w4g64 (gpu-kernels/metal/quant/affine_qmm_mma.metal:50-128).
+// Same numerics as those kernels: the weight tile is dequantised to bf16
+// (f32 multiply-add, one rounding to bf16; bit-identical to
+// affine_dequant_w4g64) before the multiply, f32 accumulation, one rounding
+// of the result to bf16.
+//
+// One persistent CTA per SM, 448 threads in four roles:
+//   warps 0-3   epilogue: tcgen05.ld the finished 128 x BN f32 accumulator out
+//               of tensor memory, round to bf16, store to y
+//   warp  4     TMA producer: per 64-wide k block, one bf16 x tile [128 x 64]
+//               (128-byte swizzle) and one packed-nibble W tile [BN x 32 B]
+//   warp  5     MMA issuer: one thread issues 4 tcgen05.mma (128 x BN x 16)
+//               per k block; allocates / frees tensor memory
+//   warps 6-13  dequantisers: thread t owns W-tile row t; per k block it turns
+//               that row's 32 bytes of nibbles (exactly one quantization
+//               group) into 64 bf16 and writes them into the K-major,
+//               128-byte-swizzled operand tile the MMA descriptor expects
+// linked by mbarrier rings (x+codes stages, dequantised-B stages, two
+// accumulator buffers in tensor memory so the epilogue of tile i overlaps the
+// main loop of tile i+1). Every wait is bounded: a wait that gives up records
+// a code in a device status word and the kernel drains and returns.
+//
+// No TMA multicast is used anywhere; each CTA issues plain TMA loads and tile
+// reuse between CTAs comes from L2.
+#include "vpq_common.cuh"
+
+#include <cuda.h>
+
+namespace vpq {
+
+// Status word of the tensor-core kernels: 0, or (site << 8) | role of the
+// first bounded wait that gave up.
+__device__ uint32_t g_qmm_status;
+
+namespace {
+
+constexpr int BM = 128;       // x rows per tile  (MMA M)
+constexpr int BK = 64;        // k per stage = one quantization group
+constexpr int kStages = 4;    // x + codes ring
+constexpr int kBStages = 3;   // dequantised B ring
+constexpr int kEpiWarps = 4;
+constexpr int kDqWarpsMax = 8;
+constexpr uint32_t kSpinLimit = 1u << 22;  // polls (with back-off) before a wait gives up
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int kXBytes = BM * BK * 2;       // 16 KB, 128B-swizzled
+  static constexpr int kCodeBytes = BN * (BK / 2);  // BN rows x 32 B
+  static constexpr int kBBytes = BN * BK * 2;       // 128B-swizzled K-major
+  static constexpr int kOffX = 0;
+  static constexpr int kOffB = kOffX + kStages * kXBytes;
+  static constexpr int kOffCode = kOffB + kBStages * kBBytes;
+  static constexpr int kOffBar = kOffCode + kStages * kCodeBytes;
+  static constexpr int kNumBars = 2 * kStages + 2 * kBStages + 4;
+  static constexpr int kOffTmem = kOffBar + kNumBars * 8;
+  static constexpr int kTotal = kOffTmem + 16;
+  static constexpr int kAlloc = kTotal + 1024;  // slack to align the base to 1024 B
+};
+
+// ------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait. On giving up, records (site << 8 | role) once and returns false.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t code,
+                                          volatile uint32_t* abort_flag) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) { return true; }
+    if (i > 64) {
+      __nanosleep(i > 4096 ? 256 : 32);
+      if (*abort_flag) { return false; }
+    }
+  }
+  *abort_flag = 1;
+  atomicCAS(&g_qmm_status, 0u, code);
+  return false;
+}
+
+// The same wait for a whole warp: every lane polls, then the lanes agree, so a
+// warp never splits around the __syncwarp / .sync.aligned operations that follow.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, uint32_t code,
+                                          volatile uint32_t* abort_flag) {
+  const bool mine = mbar_wait(bar, parity, code, abort_flag);
+  return __all_sync(0xffffffffu, mine);
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Arrives on `bar` once every tcgen05.mma issued so far by this thread is done.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               ::"r"(bar)
+               : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of
+// 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_sw128_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3fffu);  // start address
+  d |= (uint64_t)1 << 16;                       // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                       // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor: D f32, A/B bf16, both K-major, M = 128, N = BN.
+template <int BN>
+__device__ __forceinline__ constexpr uint32_t make_idesc() {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// 8 nibbles of one packed word -> 8 bf16 (4 packed registers), bit-identical
+// to bf16_rne(fmaf(s, q, b)). The nibble is dropped into mantissa bits 16..19
+// of 0x43000000 (the float 128 + q); with b128 = b - 128 s formed exactly,
+// fmaf(s, 128 + q, b128) rounds the same real number s q + b once.
+__device__ __forceinline__ void dequant_word_fast(uint32_t word, float s, float b128, uint32_t* out) {
+  const uint32_t e = word & 0x0f0f0f0fu;
+  const uint32_t o = (word >> 4) & 0x0f0f0f0fu;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t fe, fo;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(fe) : "r"(e), "r"(0x43000000u), "r"(0x7054u + (j << 8)));
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(fo) : "r"(o), "r"(0x43000000u), "r"(0x7054u + (j << 8)));
+    const float ve = __fmaf_rn(s, __uint_as_float(fe), b128);
+    const float vo = __fmaf_rn(s, __uint_as_float(fo), b128);
+    out[j] = pack_bf16x2(ve, vo);
+  }
+}
+
+__device__ __forceinline__ void dequant_word_exact(uint32_t word, float s, float b, uint32_t* out) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float ve = dequant_f32(s, (word >> (8 * j)) & 0xfu, b);
+    const float vo = dequant_f32(s, (word >> (8 * j + 4)) & 0xfu, b);
+    out[j] = pack_bf16x2(ve, vo);
+  }
+}
+
+enum Role : uint32_t { kRoleEpi = 1, kRoleTma = 2, kRoleMma = 3, kRoleDq = 4 };
+
+template <int BN>
+__global__ void __launch_bounds__(32 * (kEpiWarps + 2 + BN / 32), 1)
+affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                        const __grid_constant__ CUtensorMap tmap_w,
+                        const uint16_t* __restrict__ scales, const uint16_t* __restrict__ biases,
+                        __nv_bfloat16* __restrict__ y, int M, int N, int K) {
+  using L = SmemLayout<BN>;
+  constexpr int kDqWarps = BN / 32;
+  static_assert(kDqWarps <= kDqWarpsMax, "tile too wide");
+  constexpr uint32_t kTmemCols = 2 * BN;  // two accumulator buffers (power of two >= 32)
+  static_assert(kTmemCols == 512 || kTmemCols == 256 || kTmemCols == 128, "tensor memory columns");
+
+  extern __shared__ unsigned char smem_dyn[];
+  const uint32_t raw = smem_u32(smem_dyn);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
+  unsigned char* base_ptr = smem_dyn + (base - raw);
+
+  const uint32_t bar0 = base + L::kOffBar;
+  auto bar_full = [&](int s) { return bar0 + 8u * s; };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (kStages + s); };
+  auto bar_bfull = [&](int t) { return bar0 + 8u * (2 * kStages + t); };
+  auto bar_bempty = [&](int t) { return bar0 + 8u * (2 * kStages + kBStages + t); };
+  auto bar_accfull = [&](int a) { return bar0 + 8u * (2 * kStages + 2 * kBStages + a); };
+  auto bar_accempty = [&](int a) { return bar0 + 8u * (2 * kStages + 2 * kBStages + 2 + a); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L::kOffTmem);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int tiles_m = (M + BM - 1) / BM;
+  const int tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = K / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full(s), 1);
+      mbar_init(bar_empty(s), 1 + kDqWarps);
+    }
+    for (int t = 0; t < kBStages; ++t) {
+      mbar_init(bar_bfull(t), kDqWarps);
+      mbar_init(bar_bempty(t), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_accfull(a), 1);
+      mbar_init(bar_accempty(a), kEpiWarps);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) {  // tensor memory: whole warp allocates, address lands in shared memory
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32((const void*)tmem_slot)), "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    // ------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / tiles_n) * BM;
+        const int n0 = (tile % tiles_n) * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          if (!mbar_wait(bar_empty(s), ph ^ 1u, (1u << 8) | kRoleTma, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(bar_full(s), L::kXBytes + L::kCodeBytes);
+          tma_load_2d(base + L::kOffX + s * L::kXBytes, &tmap_x, bar_full(s), kb * BK, m0);
+          tma_load_2d(base + L::kOffCode + s * L::kCodeBytes, &tmap_w, bar_full(s), kb * (BK / 8), n0);
+        }
+      }
+      // Never leave with a copy still in flight: wait for the last load of every stage.
+      const uint32_t issued = it;
+      for (int s = 0; s < kStages; ++s) {
+        // index of the last iteration that used stage s, if any
+        if (issued > (uint32_t)s) {
+          const uint32_t last = ((issued - 1 - s) / kStages) * kStages + s;
+          mbar_wait(bar_full(s), (last / kStages) & 1u, (2u << 8) | kRoleTma, abort_flag);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // --------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc<BN>();
+      uint32_t it = 0, ti = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++ti) {
+        const int a = ti & 1;
+        const uint32_t aph = (ti >> 1) & 1u;
+        if (!mbar_wait(bar_accempty(a), aph ^ 1u, (1u << 8) | kRoleMma, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          const int t = it % kBStages;
+          const uint32_t bph = (it / kBStages) & 1u;
+          if (!mbar_wait(bar_full(s), ph, (2u << 8) | kRoleMma, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(bar_bfull(t), bph, (3u << 8) | kRoleMma, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t a_desc = make_sw128_desc(base + L::kOffX + s * L::kXBytes);
+          const uint64_t b_desc = make_sw128_desc(base + L::kOffB + t * L::kBBytes);
+#pragma unroll
+          for (int k16 = 0; k16 < BK / 16; ++k16) {
+            // 16 bf16 = 32 bytes further along K inside the swizzle atom: +2 in the address field
+            umma_bf16(d_tmem, a_desc + 2u * k16, b_desc + 2u * k16, idesc, (kb | k16) ? 1u : 0u);
+          }
+          umma_commit(bar_empty(s));   // x stage free once these MMAs have read it
+          umma_commit(bar_bempty(t));  // dequantised tile free likewise
+        }
+        if (ok) { umma_commit(bar_accfull(a)); }
+      }
+    }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------- dequantisers
+    const int t_row = threadIdx.x - 6 * 32;  // 0 .. BN-1 : row of the W tile
+    const uint32_t row_off = (uint32_t)(t_row >> 3) * 1024u + (uint32_t)(t_row & 7) * 128u;
+    const uint32_t sw = (uint32_t)(t_row & 7);
+    const int groups = K >> 6;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int n0 = (tile % tiles_n) * BN;
+      int row = n0 + t_row;
+      row = row < N ? row : N - 1;  // tail rows: any valid scale; their columns are never stored
+      const uint16_t* srow = scales + (int64_t)row * groups;
+      const uint16_t* brow = biases + (int64_t)row * groups;
+      uint32_t s_next = ldg_nc_u16(srow), b_next = ldg_nc_u16(brow);
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1u;
+        const int t = it % kBStages;
+        const uint32_t bph = (it / kBStages) & 1u;
+        const float sc = bf16_bits_to_f32(s_next);
+        const float bi = bf16_bits_to_f32(b_next);
+        if (kb + 1 < num_kb) {
+          s_next = ldg_nc_u16(srow + kb + 1);
+          b_next = ldg_nc_u16(brow + kb + 1);
+        }
+        if (!warp_wait(bar_full(s), ph, (1u << 8) | kRoleDq, abort_flag)) { ok = false; break; }
+        const uint4* cp = reinterpret_cast<const uint4*>(base_ptr + L::kOffCode + s * L::kCodeBytes +
+                                                         t_row * (BK / 2));
+        const uint4 c0 = cp[0], c1 = cp[1];
+        __syncwarp();
+        if (lane == 0) { mbar_arrive(bar_empty(s)); }  // codes are in registers
+
+        // b - 128 s, and whether that subtraction was exact (two-sum residual)
+        const float t128 = 128.0f * sc;
+        const float b128 = bi - t128;
+        const float bb = b128 - bi;
+        const float resid = (bi - (b128 - bb)) + (-t128 - bb);
+        uint32_t o[32];
+        const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        if (resid == 0.0f) {
+#pragma unroll
+          for (int wd = 0; wd < 8; ++wd) { dequant_word_fast(cw[wd], sc, b128, o + 4 * wd); }
+        } else {
+#pragma unroll
+          for (int wd = 0; wd < 8; ++wd) { dequant_word_exact(cw[wd], sc, bi, o + 4 * wd); }
+        }
+
+        if (!warp_wait(bar_bempty(t), bph ^ 1u, (2u << 8) | kRoleDq, abort_flag)) { ok = false; break; }
+        unsigned char* bt = base_ptr + L::kOffB + t * L::kBBytes + row_off;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {  // 16-byte chunk c of the row lands at chunk (c ^ row%8)
+          *reinterpret_cast<uint4*>(bt + ((c ^ sw) << 4)) =
+              make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+        }
+        fence_proxy_async();  // make the generic-proxy writes visible to the tensor core
+        __syncwarp();
+        if (lane == 0) { mbar_arrive(bar_bfull(t)); }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    uint32_t ti = 0;
+    bool ok = true;
+    const bool vec_ok = (N % 8) == 0;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++ti) {
+      const int m0 = (tile / tiles_n) * BM;
+      const int n0 = (tile % tiles_n) * BN;
+      const int a = ti & 1;
+      const uint32_t aph = (ti >> 1) & 1u;
+      if (!warp_wait(bar_accfull(a), aph, (1u << 8) | kRoleEpi, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int m = m0 + warp * 32 + lane;  // warp w reads tensor-memory lanes 32w .. 32w+31
+      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(a * BN);
+      __nv_bfloat16* yrow = y + (int64_t)m * N + n0;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + (uint32_t)(c * 32), r);
+        tmem_ld_wait();
+        const int nc = n0 + c * 32;
+        if (m < M && nc < N) {
+          if (vec_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (nc + v * 8 < N) {
+                uint4 pk;
+                pk.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                pk.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                pk.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                pk.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                *reinterpret_cast<uint4*>(yrow + c * 32 + v * 8) = pk;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (nc + j < N) { yrow[c * 32 + j] = __float2bfloat16_rn(__uint_as_float(r[j])); }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(bar_accempty(a)); }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    } else {
+      cudaGetLastError();
+    }
+  }
+  return fn;
+}
+
+int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elt_bytes, const void* ptr,
+                uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer,
+                CUtensorMapSwizzle swz, const char* what) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) { return fail(VPQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver"); }
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {inner * (uint64_t)elt_bytes};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    return fail(VPQ_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
+  }
+  return VPQ_OK;
+}
+
+template <int BN>
+int launch_qmm(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const void* x,
+               __nv_bfloat16* y, int K, int N, int M, cudaStream_t st) {
+  using L = SmemLayout<BN>;
+  CUtensorMap map_x, map_w;
+  if (int rc = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)K, (uint64_t)M,
+                           BK, BM, CU_TENSOR_MAP_SWIZZLE_128B, "x")) {
+    return rc;
+  }
+  if (int rc = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w, (uint64_t)(K / 8),
+                           (uint64_t)N, BK / 8, BN, CU_TENSOR_MAP_SWIZZLE_NONE, "w")) {
+    return rc;
+  }
+  auto kern = affine_qmm_w4g64_kernel<BN>;
+  VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int sms = num_sms();
+  const int grid = tiles < sms ? tiles : sms;
+  constexpr int threads = 32 * (kEpiWarps + 2 + BN / 32);
+  kern<<<grid, threads, L::kAlloc, st>>>(map_x, map_w, scales, biases, y, M, N, K);
+  VPQ_LAUNCH_OK("affine_qmm_w4g64");
+  return VPQ_OK;
+}
+
+}  // namespace
+}  // namespace vpq
+
+using namespace vpq;
+
+extern "C" int vpq_affine_qmm_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
+                                         const void* x, void* y, int64_t K, int64_t N, int64_t M,
+                                         void* stream) {
+  clear_error();
+  if (!w || !scales || !biases || !x || !y) {
+    return fail(VPQ_ERR_INVALID_ARG, "affine_qmm_w4g64: null pointer");
+  }
+  if (K <= 0 || N <= 0 || M <= 0 || (K % 64) != 0) {
+    return fail(VPQ_ERR_INVALID_ARG, "affine_qmm_w4g64: need K>0, N>0, M>0, K%%64==0 (K=%lld N=%lld M=%lld)",
+                (long long)K, (long long)N, (long long)M);
+  }
+  if (K > (1 << 20) || N > (1 << 24) || M > (1 << 24)) {
+    return fail(VPQ_ERR_UNSUPPORTED, "affine_qmm_w4g64: shape too large (K=%lld N=%lld M=%lld)",
+                (long long)K, (long long)N, (long long)M);
+  }
+  if (!aligned16(w) || !aligned16(x) || !aligned16(y) ||
+      (reinterpret_cast<uintptr_t>(scales) & 1) || (reinterpret_cast<uintptr_t>(biases) & 1)) {
+    return fail(VPQ_ERR_ALIGNMENT, "affine_qmm_w4g64: w, x and y must be 16-byte aligned");
+  }
+  if (int rc = require_sm100()) { return rc; }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return launch_qmm<256>(w, static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases),
+                         x, static_cast<__nv_bfloat16*>(y), (int)K, (int)N, (int)M, st);
+}
+
+extern "C" int vpq_device_status(void* stream, uint32_t* detail) {
+  clear_error();
+  if (int rc = require_sm100()) { return rc; }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint32_t v = 0;
+  VPQ_CUDA_OK(cudaMemcpyFromSymbolAsync(&v, g_qmm_status, sizeof(v), 0, cudaMemcpyDeviceToHost, st));
+  VPQ_CUDA_OK(cudaStreamSynchronize(st));
+  if (detail) { *detail = v; }
+  if (v != 0) {
+    const uint32_t zero = 0;
+    VPQ_CUDA_OK(cudaMemcpyToSymbolAsync(g_qmm_status, &zero, sizeof(zero), 0, cudaMemcpyHostToDevice, st));
+    VPQ_CUDA_OK(cudaStreamSynchronize(st));
+    return fail(VPQ_ERR_TIMEOUT, "a bounded device-side wait gave up (site %u, role %u)", v >> 8, v & 0xffu);
+  }
+  return VPQ_OK;
+}

@@ -1,0 +1,86 @@
+// vpq_common.cuh -- shared host/device helpers for the sm_100a kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "../../include/vpq.h"
+
+namespace vpq {
+
+// ----------------------------------------------------------------- host side
+// Records a message for vpq_last_error() and returns `code`.
+int fail(int code, const char* fmt, ...);
+void clear_error();
+
+// Makes sure the current device can run sm_100a code (cached per device).
+int require_sm100();
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+#define VPQ_CUDA_OK(expr)                                                          \
+  do {                                                                             \
+    cudaError_t _e = (expr);                                                       \
+    if (_e != cudaSuccess) {                                                       \
+      return ::vpq::fail(VPQ_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(_e));   \
+    }                                                                              \
+  } while (0)
+
+#define VPQ_LAUNCH_OK(what)                                                        \
+  do {                                                                             \
+    cudaError_t _e = cudaGetLastError();                                           \
+    if (_e != cudaSuccess) {                                                       \
+      return ::vpq::fail(VPQ_ERR_CUDA, "%s launch: %s", what, cudaGetErrorString(_e)); \
+    }                                                                              \
+  } while (0)
+
+int num_sms();
+
+// --------------------------------------------------------------- device side
+#ifdef __CUDACC__
+
+// f32 -> bf16 bits, the reference's integer round-to-nearest-even form
+// (generative-models/quantize/model-quantizer.cc:56-60). Equal to
+// cvt.rn.bf16.f32 for every finite input.
+__device__ __forceinline__ uint32_t f32_to_bf16_bits(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u + 0x7fffu + ((u >> 16) & 1u)) >> 16;
+}
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t b) {
+  return __uint_as_float(b << 16);
+}
+
+// Two f32 -> packed bf16x2 (lo = a, hi = b), round to nearest even.
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  return r;
+}
+
+// The dequantised weight, exactly as the reference computes it: s*q is exact
+// in f32 (8-bit x 4-bit significands), one f32 rounding on the add, then RNE
+// to bf16 (gpu-kernels/metal/quant/affine_dequant.metal:49-52).
+__device__ __forceinline__ float dequant_f32(float s, uint32_t q, float b) {
+  return __fmaf_rn(s, (float)q, b);
+}
+
+__device__ __forceinline__ uint4 ldg_stream_v4(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+
+__device__ __forceinline__ uint32_t ldg_nc_u16(const void* p) {
+  uint16_t r;
+  asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(r) : "l"(p));
+  return r;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace vpq

@@ -1,0 +1,125 @@
+"""Torch-tensor front end to the C ABI (device pointers pass straight through).
+
+16-bit float tensors may be torch.bfloat16 / torch.float16 or raw int16/uint16
+bit patterns; packed weights are int32 / uint32 [N, K/8].
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import check, lib
+
+
+def _ptr(t: torch.Tensor) -> int:
+    if not t.is_cuda:
+        raise ValueError("vpipe_b200.ops: tensors must live on a CUDA device (no CPU path)")
+    if not t.is_contiguous():
+        raise ValueError("vpipe_b200.ops: tensors must be contiguous")
+    return t.data_ptr()
+
+
+def _stream(stream=None) -> int:
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return s.cuda_stream
+
+
+def quantize(w: torch.Tensor, clip: float = 1.0, stream=None):
+    """Dense [N,K] f16/bf16 -> (codes int32 [N,K/8], scales f16, biases f16)."""
+    if w.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("quantize: w must be float16 or bfloat16")
+    N, K = w.shape
+    dev = w.device
+    with torch.cuda.device(dev):
+        codes = torch.empty((N, max(K // 8, 1)), dtype=torch.int32, device=dev)
+        s = torch.empty((N, max(K // 64, 1)), dtype=torch.float16, device=dev)
+        b = torch.empty_like(s)
+        check(lib().vpq_affine_quant_w4_g64(_ptr(w), int(w.dtype == torch.bfloat16), _ptr(codes),
+                                            _ptr(s), _ptr(b), K, N, clip, _stream(stream)))
+    return codes, s, b
+
+
+def narrow_f32_bf16(w: torch.Tensor, stream=None) -> torch.Tensor:
+    out = torch.empty(w.shape, dtype=torch.bfloat16, device=w.device)
+    with torch.cuda.device(w.device):
+        check(lib().vpq_narrow_f32_bf16(_ptr(w), _ptr(out), w.numel(), _stream(stream)))
+    return out
+
+
+def scales_to_bf16(s_f16: torch.Tensor, stream=None) -> torch.Tensor:
+    out = torch.empty(s_f16.shape, dtype=torch.bfloat16, device=s_f16.device)
+    with torch.cuda.device(s_f16.device):
+        check(lib().vpq_scales_f16_to_bf16(_ptr(s_f16), _ptr(out), s_f16.numel(), _stream(stream)))
+    return out
+
+
+def dequantize(codes, scales, biases, out=None, stream=None) -> torch.Tensor:
+    N, Kw = codes.shape
+    K = Kw * 8
+    if out is None:
+        out = torch.empty((N, K), dtype=torch.bfloat16, device=codes.device)
+    with torch.cuda.device(codes.device):
+        check(lib().vpq_affine_dequant_w4g64_bf16(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(out),
+                                                  K, N, _stream(stream)))
+    return out
+
+
+def qmv(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
+    N, Kw = codes.shape
+    K = Kw * 8
+    M = x.numel() // K
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().vpq_affine_qmv_w4g64_bf16(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x),
+                                              _ptr(out), K, N, M, _stream(stream)))
+    return out
+
+
+def qmv_set(problems):
+    """Builds the host descriptor array for qmv_batch from (codes, scales, biases, x, y) tuples."""
+    arr = (_lib.LinearDesc * len(problems))()
+    for d, (codes, scales, biases, x, y) in zip(arr, problems):
+        N, Kw = codes.shape
+        d.w, d.scales, d.biases, d.x, d.y = _ptr(codes), _ptr(scales), _ptr(biases), _ptr(x), _ptr(y)
+        d.K, d.N, d.M = Kw * 8, N, x.numel() // (Kw * 8)
+    return arr
+
+
+def qmv_batch(descs, stream=None) -> None:
+    check(lib().vpq_affine_qmv_w4g64_bf16_batch(descs, len(descs), _stream(stream)))
+
+
+def qmm(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
+    N, Kw = codes.shape
+    K = Kw * 8
+    M = x.numel() // K
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().vpq_affine_qmm_w4g64_bf16(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x),
+                                              _ptr(out), K, N, M, _stream(stream)))
+    return out
+
+
+def device_status(stream=None) -> int:
+    """Raises VpqError(TIMEOUT) if a bounded device-side wait gave up; else 0."""
+    detail = C.c_uint32(0)
+    check(lib().vpq_device_status(_stream(stream), C.byref(detail)))
+    return int(detail.value)
+
+
+def function(library: str, entry: str):
+    """The reference's load_library(name).function(entry); None if unknown."""
+    return lib().vpq_function_lookup(library.encode(), entry.encode())
+
+
+def dispatch(fn, buffers, K=0, N=0, M=0, clip=1.0, stream=None) -> None:
+    """One dispatch with the reference's slot numbering (see include/vpq.h)."""
+    a = _lib.DispatchArgs()
+    for i, t in enumerate(buffers):
+        a.buffers[i] = _ptr(t) if t is not None else None
+    a.K, a.N, a.M, a.clip = K, N, M, clip
+    check(lib().vpq_dispatch(fn, C.byref(a), _stream(stream)))
