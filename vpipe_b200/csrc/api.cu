@@ -1,6 +1,6 @@
 // api.cu -- status strings, per-thread error message, device checks, byte-size
 // helpers and the (library, entry) function table of the C ABI.
-#include "vpq_common.cuh"
+#include "vpq_sm100.cuh"
 
 #include <cstdarg>
 #include <cstdio>
@@ -65,6 +65,47 @@ int num_sms() {
   int dev = 0;
   if (probe(&dev) != VPQ_OK) { return 148; }
   return g_dev[dev].sms > 0 ? g_dev[dev].sms : 148;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up at run time, so the library does not link libcuda.
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    } else {
+      cudaGetLastError();
+    }
+  }
+  return fn;
+}
+
+int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elt_bytes, const void* ptr,
+                uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer,
+                CUtensorMapSwizzle swz, const char* what) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) { return fail(VPQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver"); }
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {inner * (uint64_t)elt_bytes};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    return fail(VPQ_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
+  }
+  return VPQ_OK;
 }
 
 }  // namespace vpq

@@ -27,9 +27,7 @@
 //
 // No TMA multicast is used anywhere; each CTA issues plain TMA loads and tile
 // reuse between CTAs comes from L2.
-#include "vpq_common.cuh"
-
-#include <cuda.h>
+#include "vpq_sm100.cuh"
 
 namespace vpq {
 
@@ -45,7 +43,6 @@ constexpr int kStages = 4;    // x + codes ring
 constexpr int kBStages = 3;   // dequantised B ring
 constexpr int kEpiWarps = 4;
 constexpr int kDqWarpsMax = 8;
-constexpr uint32_t kSpinLimit = 1u << 22;  // polls (with back-off) before a wait gives up
 
 template <int BN>
 struct SmemLayout {
@@ -63,72 +60,6 @@ struct SmemLayout {
 };
 
 // ------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
-// Bounded wait. On giving up, records (site << 8 | role) once and returns false.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t code,
-                                          volatile uint32_t* abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) { return true; }
-    if (i > 64) {
-      __nanosleep(i > 4096 ? 256 : 32);
-      if (*abort_flag) { return false; }
-    }
-  }
-  *abort_flag = 1;
-  atomicCAS(&g_qmm_status, 0u, code);
-  return false;
-}
-
-// The same wait for a whole warp: every lane polls, then the lanes agree, so a
-// warp never splits around the __syncwarp / .sync.aligned operations that follow.
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, uint32_t code,
-                                          volatile uint32_t* abort_flag) {
-  const bool mine = mbar_wait(bar, parity, code, abort_flag);
-  return __all_sync(0xffffffffu, mine);
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                            int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
-      : "memory");
-}
-
-__device__ __forceinline__ void fence_proxy_async() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -268,7 +199,7 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
       mbar_init(bar_accempty(a), kEpiWarps);
     }
     *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_mbar_init();
   }
   if (warp == 5) {  // tensor memory: whole warp allocates, address lands in shared memory
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -292,7 +223,7 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
-          if (!mbar_wait(bar_empty(s), ph ^ 1u, (1u << 8) | kRoleTma, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(bar_empty(s), ph ^ 1u, (1u << 8) | kRoleTma, abort_flag, &g_qmm_status)) { ok = false; break; }
           mbar_expect_tx(bar_full(s), L::kXBytes + L::kCodeBytes);
           tma_load_2d(base + L::kOffX + s * L::kXBytes, &tmap_x, bar_full(s), kb * BK, m0);
           tma_load_2d(base + L::kOffCode + s * L::kCodeBytes, &tmap_w, bar_full(s), kb * (BK / 8), n0);
@@ -304,7 +235,7 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
         // index of the last iteration that used stage s, if any
         if (issued > (uint32_t)s) {
           const uint32_t last = ((issued - 1 - s) / kStages) * kStages + s;
-          mbar_wait(bar_full(s), (last / kStages) & 1u, (2u << 8) | kRoleTma, abort_flag);
+          mbar_wait(bar_full(s), (last / kStages) & 1u, (2u << 8) | kRoleTma, abort_flag, &g_qmm_status);
         }
       }
     }
@@ -317,7 +248,7 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++ti) {
         const int a = ti & 1;
         const uint32_t aph = (ti >> 1) & 1u;
-        if (!mbar_wait(bar_accempty(a), aph ^ 1u, (1u << 8) | kRoleMma, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(bar_accempty(a), aph ^ 1u, (1u << 8) | kRoleMma, abort_flag, &g_qmm_status)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
@@ -325,8 +256,8 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
           const uint32_t ph = (it / kStages) & 1u;
           const int t = it % kBStages;
           const uint32_t bph = (it / kBStages) & 1u;
-          if (!mbar_wait(bar_full(s), ph, (2u << 8) | kRoleMma, abort_flag)) { ok = false; break; }
-          if (!mbar_wait(bar_bfull(t), bph, (3u << 8) | kRoleMma, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(bar_full(s), ph, (2u << 8) | kRoleMma, abort_flag, &g_qmm_status)) { ok = false; break; }
+          if (!mbar_wait(bar_bfull(t), bph, (3u << 8) | kRoleMma, abort_flag, &g_qmm_status)) { ok = false; break; }
           tc_fence_after();
           const uint64_t a_desc = make_sw128_desc(base + L::kOffX + s * L::kXBytes);
           const uint64_t b_desc = make_sw128_desc(base + L::kOffB + t * L::kBBytes);
@@ -367,7 +298,7 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
           s_next = ldg_nc_u16(srow + kb + 1);
           b_next = ldg_nc_u16(brow + kb + 1);
         }
-        if (!warp_wait(bar_full(s), ph, (1u << 8) | kRoleDq, abort_flag)) { ok = false; break; }
+        if (!warp_wait(bar_full(s), ph, (1u << 8) | kRoleDq, abort_flag, &g_qmm_status)) { ok = false; break; }
         const uint4* cp = reinterpret_cast<const uint4*>(base_ptr + L::kOffCode + s * L::kCodeBytes +
                                                          t_row * (BK / 2));
         const uint4 c0 = cp[0], c1 = cp[1];
@@ -389,7 +320,7 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
           for (int wd = 0; wd < 8; ++wd) { dequant_word_exact(cw[wd], sc, bi, o + 4 * wd); }
         }
 
-        if (!warp_wait(bar_bempty(t), bph ^ 1u, (2u << 8) | kRoleDq, abort_flag)) { ok = false; break; }
+        if (!warp_wait(bar_bempty(t), bph ^ 1u, (2u << 8) | kRoleDq, abort_flag, &g_qmm_status)) { ok = false; break; }
         unsigned char* bt = base_ptr + L::kOffB + t * L::kBBytes + row_off;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {  // 16-byte chunk c of the row lands at chunk (c ^ row%8)
@@ -411,7 +342,7 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const int n0 = (tile % tiles_n) * BN;
       const int a = ti & 1;
       const uint32_t aph = (ti >> 1) & 1u;
-      if (!warp_wait(bar_accfull(a), aph, (1u << 8) | kRoleEpi, abort_flag)) { ok = false; break; }
+      if (!warp_wait(bar_accfull(a), aph, (1u << 8) | kRoleEpi, abort_flag, &g_qmm_status)) { ok = false; break; }
       tc_fence_after();
       const int m = m0 + warp * 32 + lane;  // warp w reads tensor-memory lanes 32w .. 32w+31
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(a * BN);
@@ -459,46 +390,6 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
 }
 
 // ------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess) {
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-    } else {
-      cudaGetLastError();
-    }
-  }
-  return fn;
-}
-
-int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elt_bytes, const void* ptr,
-                uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer,
-                CUtensorMapSwizzle swz, const char* what) {
-  EncodeTiledFn enc = encode_tiled_fn();
-  if (!enc) { return fail(VPQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver"); }
-  const cuuint64_t dims[2] = {inner, outer};
-  const cuuint64_t strides[1] = {inner * (uint64_t)elt_bytes};
-  const cuuint32_t box[2] = {box_inner, box_outer};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    return fail(VPQ_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
-  }
-  return VPQ_OK;
-}
-
 template <int BN>
 int launch_qmm(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const void* x,
                __nv_bfloat16* y, int K, int N, int M, cudaStream_t st) {

@@ -4,25 +4,30 @@
 // Replaces affine_qmv_w4g64 (qmv_fast_impl<T,64,4,false,4,2,2>,
 // gpu-kernels/metal/quant/affine_qmv.metal:186-301).
 //
-// The kernel is a pure HBM stream of the packed weights:
-//  * each lane reads 16 bytes (32 nibbles, half a quantization group) per row
-//    per step with a 128-bit non-allocating load, so a warp covers 1024
-//    consecutive k of one row (512 contiguous bytes) per load instruction;
-//  * a warp keeps R rows in flight and prefetches the next step's words while
-//    it works on the current ones;
-//  * nibbles become f32 without a convert instruction: PRMT drops the nibble
-//    into mantissa bits 16..19 of 0x43000000, which is the float 128 + q;
-//    packed f32x2 FMAs accumulate x*(128+q), and the 128*sum(x) surplus is
-//    removed per 32-value chunk with the chunk sums of x that the CTA computes
-//    once. Everything is f32: products are exact and the surplus is at most
-//    2^7 times a 32-term partial sum, so the result carries f32 rounding noise
-//    only (no bf16 / fp16 intermediate anywhere);
-//  * x lives in shared memory as f32, transposed so that lane l's 32 values
-//    of a step are eight conflict-free 128-bit reads, shared by the R rows;
-//  * one shuffle butterfly per row at the end.
-// The grid is persistent (2 CTAs per SM); the launch opts into programmatic
-// dependent launch so the next GEMV's first weight words are already in
-// flight while this one drains.
+// The kernel is a stream of the packed weights out of HBM; everything else is
+// arranged so that the SM keeps up with 23 bytes (46 nibbles) per clock:
+//  * a CTA owns tiles of 16 output rows and its 8 warps split K (warp w takes
+//    a contiguous run of 128-wide k tiles), so even a 4096 x 4096 matrix gives
+//    every warp work and all loads of a warp are independent;
+//  * lane (g, t) of a warp reads 16 bytes of row g and 16 bytes of row g+8 per
+//    k tile (a quad covers 64 contiguous bytes of a row) with 128-bit
+//    non-allocating loads; four k tiles (8 loads per lane) are kept in flight;
+//  * nibbles are widened in registers to bf16 128+q with one LOP3 per two
+//    nibbles (0x4300 | q is exactly 128 + q) and fed, unscaled, to
+//    mma.sync.m16n8k16 against x; products are exact and the accumulation is
+//    f32. A first SIMT version of this kernel (one PRMT and half an f32x2 FMA
+//    per nibble) was bound by the integer pipe at under a quarter of the HBM
+//    rate; the tensor-core form needs about a third of the instructions;
+//  * the two quantization groups of a k tile go to different accumulator
+//    columns (even columns see only the first 64 k of x, odd columns the last
+//    64), so each group's sum comes out separately and is scaled once:
+//    res += s * (acc - 128 * sum(x_group)) + b * sum(x_group), in f32;
+//  * x is staged once per CTA in shared memory, already permuted into the
+//    B-fragment order that matches the nibble pairing (k, k+4);
+//  * per row tile: one shuffle, one shared-memory reduction over the 8 warps.
+// The launch opts into programmatic dependent launch: the first weight loads
+// are issued before griddepcontrol.wait, so the next GEMV's stream starts
+// while this one drains.
 #include "vpq_common.cuh"
 
 namespace vpq {
@@ -31,195 +36,212 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr int kStepK = 1024;  // k covered by one warp-wide 16-byte load
+constexpr int kSlots = 6;     // k tiles in flight per warp
+constexpr int kTileK = 128;   // k per tile: 64 bytes of a row, two quantization groups
 
-__device__ __forceinline__ void fma2(float& acc_lo, float& acc_hi, float a_lo, float a_hi,
-                                     float b_lo, float b_hi) {
-  asm("{\n\t"
-      ".reg .b64 ra, rb, rc;\n\t"
-      "mov.b64 ra, {%2, %3};\n\t"
-      "mov.b64 rb, {%4, %5};\n\t"
-      "mov.b64 rc, {%0, %1};\n\t"
-      "fma.rn.f32x2 rc, ra, rb, rc;\n\t"
-      "mov.b64 {%0, %1}, rc;\n\t"
-      "}"
-      : "+f"(acc_lo), "+f"(acc_hi)
-      : "f"(a_lo), "f"(a_hi), "f"(b_lo), "f"(b_hi));
-}
-
-__device__ __forceinline__ float nibble_f32(uint32_t bytes, uint32_t selector) {
-  uint32_t r;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(bytes), "r"(0x43000000u), "r"(selector));
-  return __uint_as_float(r);  // 128 + q
-}
-
-// sum over the 8 nibbles of `word` of x[k] * (128 + q[k]); x0 = k 0..3, x1 = k 4..7
-__device__ __forceinline__ void word_fma(uint32_t word, const float4& x0, const float4& x1,
-                                         float& acc_lo, float& acc_hi) {
-  const uint32_t e = word & 0x0f0f0f0fu;         // nibbles 0,2,4,6 as bytes
-  const uint32_t o = (word >> 4) & 0x0f0f0f0fu;  // nibbles 1,3,5,7 as bytes
-  fma2(acc_lo, acc_hi, nibble_f32(e, 0x7054u), nibble_f32(o, 0x7054u), x0.x, x0.y);
-  fma2(acc_lo, acc_hi, nibble_f32(e, 0x7154u), nibble_f32(o, 0x7154u), x0.z, x0.w);
-  fma2(acc_lo, acc_hi, nibble_f32(e, 0x7254u), nibble_f32(o, 0x7254u), x1.x, x1.y);
-  fma2(acc_lo, acc_hi, nibble_f32(e, 0x7354u), nibble_f32(o, 0x7354u), x1.z, x1.w);
-}
-
-template <int R>
-struct Fetch {
-  uint4 w[R];
-  uint32_t s[R], b[R];
+struct Slot {
+  uint4 ra, rb;     // 32 nibbles of row g and of row g+8
+  uint32_t s, z;    // scale and bias (bf16 bits) of this lane's (row, group) item
 };
 
-template <int R>
-__device__ __forceinline__ void fetch(Fetch<R>& f, const uint32_t* __restrict__ w,
-                                      const uint16_t* __restrict__ scales,
-                                      const uint16_t* __restrict__ biases, int64_t row0, int N,
-                                      int K, int step, int lane) {
-  const int kk = step * kStepK + lane * 32;
-  const bool live = kk < K;
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                               uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+      "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// (v & 0x000f000f) | 0x43004300 in one LOP3: the bf16 pair (128 + lo nibble, 128 + hi nibble)
+__device__ __forceinline__ uint32_t and_or_magic(uint32_t v) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, 0x000f000f, 0x43004300, 0xEA;" : "=r"(r) : "r"(v));
+  return r;
+}
+
+// 8 MMAs of one k tile: rows g / g+8 words wa / wb against the staged x fragments
+__device__ __forceinline__ void unit_mma(float (&c)[4], float (&d)[4], const uint4& ra, const uint4& rb,
+                                         const uint4* __restrict__ xb, int xb_q) {
+  const uint32_t wa[4] = {ra.x, ra.y, ra.z, ra.w};
+  const uint32_t wb[4] = {rb.x, rb.y, rb.z, rb.w};
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    int64_t row = row0 + r;
-    row = row < N ? row : N - 1;  // tail rows re-read the last row; never stored
-    if (live) {
-      f.w[r] = ldg_stream_v4(w + row * (K >> 3) + (kk >> 3));
-      f.s[r] = ldg_nc_u16(scales + row * (K >> 6) + (kk >> 6));
-      f.b[r] = ldg_nc_u16(biases + row * (K >> 6) + (kk >> 6));
-    } else {
-      f.w[r] = make_uint4(0, 0, 0, 0);
-      f.s[r] = 0;
-      f.b[r] = 0;
-    }
+  for (int wd = 0; wd < 4; ++wd) {
+    const uint4 xv = xb[wd * xb_q];
+    const uint32_t a = wa[wd], b = wb[wd];
+    // nibble pairs (n0,n4) (n1,n5) (n2,n6) (n3,n7) of each word
+    mma_bf16_16816(c, and_or_magic(a), and_or_magic(b), and_or_magic(a >> 4), and_or_magic(b >> 4),
+                   xv.x, xv.y);
+    mma_bf16_16816(d, and_or_magic(a >> 8), and_or_magic(b >> 8), and_or_magic(a >> 12),
+                   and_or_magic(b >> 12), xv.z, xv.w);  // second accumulator: two shorter dependency chains
   }
 }
 
-template <int R>
 __global__ void __launch_bounds__(kThreads, 2)
 affine_qmv_w4g64_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ scales,
                         const uint16_t* __restrict__ biases, const uint16_t* __restrict__ x,
-                        __nv_bfloat16* __restrict__ y, int K, int N, int steps) {
+                        __nv_bfloat16* __restrict__ y, int K, int N) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  float4* xs = reinterpret_cast<float4*>(smem_raw);                // [steps][8][32] float4
-  float* xsum = reinterpret_cast<float*>(xs + (size_t)steps * 256);  // [steps][32]
+  const int KT = (K + kTileK - 1) / kTileK;  // k tiles (the last may hold one group only)
+  const int G = K >> 6;                      // groups per row
+  const int KW = K >> 3;                     // packed words per row
+  uint4* xperm = reinterpret_cast<uint4*>(smem_raw);            // [KT][4 quarters][4 t] x 16 B
+  uint4* zero16 = xperm + (size_t)KT * 16;                      // 16 bytes of zeros
+  float* xg = reinterpret_cast<float*>(zero16 + 1);             // [2*KT] group sums of x
+  float* red = xg + 2 * KT;                                     // [2][kWarps][16]
 
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
   const int m = blockIdx.y;
-  const int num_row_blocks = (N + R - 1) / R;
-  const int total_warps = gridDim.x * kWarps;
-  const int gw = blockIdx.x * kWarps + warp;
+  const int row_tiles = (N + 15) >> 4;
+  // this warp's contiguous run of k tiles: [kt0, kt0 + n_kt)
+  const int n_kt = KT / kWarps + (warp < KT % kWarps ? 1 : 0);
+  const int kt0 = warp * (KT / kWarps) + min(warp, KT % kWarps);
+  const int item_row = g + ((t >> 1) << 3);  // the row whose (group t&1) sum this lane scales
+  const int my_tiles = blockIdx.x < row_tiles ? (row_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const int total_units = my_tiles * n_kt;
 
   // Let the next kernel in the stream start its own weight prefetch now.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
+  // ---- fetch side: walks the units (row tile, k tile) in the order they are consumed.
+  // Offsets past the end of a row (K % 128 == 64) or of the matrix (N % 16 != 0) are clamped
+  // onto valid data; what they fetch meets x == 0 or is never stored.
+  const uint32_t* f_pa = w;
+  const uint32_t* f_pb = w;
+  const uint16_t* f_ps = scales;
+  const uint16_t* f_pz = biases;
+  int f_tile = blockIdx.x, f_i = 0, f_units = 0;
+  auto fetch_tile_setup = [&]() {
+    const int r0 = f_tile << 4;
+    f_pa = w + (int64_t)min(r0 + g, N - 1) * KW;
+    f_pb = w + (int64_t)min(r0 + g + 8, N - 1) * KW;
+    const int64_t ri = min(r0 + item_row, N - 1);
+    f_ps = scales + ri * G;
+    f_pz = biases + ri * G;
+  };
+  auto fetch = [&](Slot& sl) {
+    if (f_units < total_units) {
+      const int kt = kt0 + f_i;
+      const int woff = min(kt * 16 + t * 4, KW - 4);
+      const int goff = min(2 * kt + (t & 1), G - 1);
+      sl.ra = ldg_stream_v4(f_pa + woff);
+      sl.rb = ldg_stream_v4(f_pb + woff);
+      sl.s = ldg_nc_u16(f_ps + goff);
+      sl.z = ldg_nc_u16(f_pz + goff);
+      ++f_units;
+      if (++f_i == n_kt) {
+        f_i = 0;
+        f_tile += gridDim.x;
+        fetch_tile_setup();
+      }
+    }
+  };
+
   // First weight words: they do not depend on the previous kernel.
-  Fetch<R> cur;
-  int rb = gw, step = 0;
-  const bool have_work = rb < num_row_blocks;
-  if (have_work) { fetch<R>(cur, w, scales, biases, (int64_t)rb * R, N, K, 0, lane); }
+  Slot slot[kSlots];
+  fetch_tile_setup();
+#pragma unroll
+  for (int j = 0; j < kSlots; ++j) { fetch(slot[j]); }
 
   // x (and y) may be produced / consumed by the previous kernel.
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  // Stage x as f32, transposed: element k = 1024 j + 32 l + 4 i + e lives in
-  // xs[(j*8 + i)*32 + l].e ; xsum[j*32 + l] = sum of lane l's 32 values.
+  // ---- stage x: 8 consecutive values (x0..x7) become the four B-fragment
+  // registers (x0,x4) (x1,x5) (x2,x6) (x3,x7); group sums in f32.
   {
     const uint16_t* xr = x + (int64_t)m * K;
-    const int chunks = steps * (kStepK / 8);
-    for (int t = threadIdx.x; t < chunks; t += kThreads) {
-      const int k0 = t * 8;
-      uint4 raw = make_uint4(0, 0, 0, 0);
-      if (k0 < K) { raw = *reinterpret_cast<const uint4*>(xr + k0); }
-      const float4 lo = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
-                                    __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
-      const float4 hi = make_float4(__uint_as_float(raw.z << 16), __uint_as_float(raw.z & 0xffff0000u),
-                                    __uint_as_float(raw.w << 16), __uint_as_float(raw.w & 0xffff0000u));
-      const int j = k0 / kStepK, l = (k0 % kStepK) / 32, i0 = (k0 % 32) / 4;
-      xs[(j * 8 + i0) * 32 + l] = lo;
-      xs[(j * 8 + i0 + 1) * 32 + l] = hi;
-      float part = ((lo.x + lo.y) + (lo.z + lo.w)) + ((hi.x + hi.y) + (hi.z + hi.w));
+    const int chunks = KT * 16;  // 16-byte chunks of the padded x
+    // warp-uniform bound: every lane takes part in the shuffles below
+    for (int i = threadIdx.x; i - lane < chunks; i += kThreads) {
+      const bool live = i < chunks;
+      const int k0 = i * 8;
+      uint4 in = make_uint4(0, 0, 0, 0);
+      if (live && k0 < K) { in = *reinterpret_cast<const uint4*>(xr + k0); }
+      uint4 out;
+      asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(out.x) : "r"(in.x), "r"(in.z));
+      asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(out.y) : "r"(in.x), "r"(in.z));
+      asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(out.z) : "r"(in.y), "r"(in.w));
+      asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(out.w) : "r"(in.y), "r"(in.w));
+      const int kt = i >> 4, tt = (i >> 2) & 3, q = i & 3;
+      if (live) { xperm[(kt * 4 + q) * 4 + tt] = out; }
+      float part = ((bf16_bits_to_f32(in.x & 0xffffu) + __uint_as_float(in.x & 0xffff0000u)) +
+                    (bf16_bits_to_f32(in.y & 0xffffu) + __uint_as_float(in.y & 0xffff0000u))) +
+                   ((bf16_bits_to_f32(in.z & 0xffffu) + __uint_as_float(in.z & 0xffff0000u)) +
+                    (bf16_bits_to_f32(in.w & 0xffffu) + __uint_as_float(in.w & 0xffff0000u)));
       part += __shfl_xor_sync(0xffffffffu, part, 1);
       part += __shfl_xor_sync(0xffffffffu, part, 2);
-      if ((t & 3) == 0) { xsum[j * 32 + l] = part; }
+      part += __shfl_xor_sync(0xffffffffu, part, 4);
+      if (live && (i & 7) == 0) { xg[i >> 3] = part; }
     }
+    if (threadIdx.x == 0) { *zero16 = make_uint4(0, 0, 0, 0); }
   }
   __syncthreads();
 
-  if (!have_work) { return; }
+  // Even accumulator columns see the first group of a k tile (chunks t = 0, 1),
+  // odd columns the second (t = 2, 3); column c is supplied by the lanes with g == c.
+  const bool real = ((g & 1) == 0) ? (t < 2) : (t >= 2);
+  const uint4* xb_base = real ? xperm + t : zero16;
+  const int xb_kt = real ? 16 : 0, xb_q = real ? 4 : 0;
 
-  float res[R];
+  // ---- consume side
+  int buf = 0, c_i = 0, tile = blockIdx.x;
+  float res = 0.0f;
+  auto finish_tile = [&]() {  // both groups of a row, then the 8 warps' K slices
+    res += __shfl_xor_sync(0xffffffffu, res, 1);
+    if ((t & 1) == 0) { red[(buf * kWarps + warp) * 16 + item_row] = res; }
+    __syncthreads();
+    if (warp == 0 && lane < 16) {
+      float v = 0.0f;
 #pragma unroll
-  for (int r = 0; r < R; ++r) { res[r] = 0.0f; }
-
-  while (true) {
-    // prefetch the next (row block, step)
-    int nrb = rb, nstep = step + 1;
-    if (nstep == steps) {
-      nstep = 0;
-      nrb = rb + total_warps;
+      for (int ww = 0; ww < kWarps; ++ww) { v += red[(buf * kWarps + ww) * 16 + lane]; }
+      const int row = (tile << 4) + lane;
+      if (row < N) { y[(int64_t)m * N + row] = __float2bfloat16_rn(v); }
     }
-    const bool more = nrb < num_row_blocks;
-    Fetch<R> nxt;
-    if (more) { fetch<R>(nxt, w, scales, biases, (int64_t)nrb * R, N, K, nstep, lane); }
+    buf ^= 1;
+    res = 0.0f;
+    tile += gridDim.x;
+  };
 
-    // consume the current step
-    {
-      float acc_lo[R], acc_hi[R];
+  if (n_kt == 0) {  // K < 1024: this warp holds no k tile but still joins every reduction
+    for (int i = 0; i < my_tiles; ++i) { finish_tile(); }
+    return;
+  }
+
+  for (int u = 0; u < total_units; u += kSlots) {
 #pragma unroll
-      for (int r = 0; r < R; ++r) { acc_lo[r] = 0.0f, acc_hi[r] = 0.0f; }
-      const float4* xp = xs + step * 256 + lane;
-#pragma unroll
-      for (int wd = 0; wd < 4; ++wd) {
-        const float4 x0 = xp[(2 * wd) * 32];
-        const float4 x1 = xp[(2 * wd + 1) * 32];
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-          const uint32_t word = wd == 0 ? cur.w[r].x : wd == 1 ? cur.w[r].y : wd == 2 ? cur.w[r].z : cur.w[r].w;
-          word_fma(word, x0, x1, acc_lo[r], acc_hi[r]);
+    for (int j = 0; j < kSlots; ++j) {
+      if (u + j < total_units) {
+        const int kt = kt0 + c_i;
+        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f}, d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        unit_mma(c, d, slot[j].ra, slot[j].rb, xb_base + kt * xb_kt, xb_q);
+        // c0 = (row g, first group) c1 = (row g, second) c2 = (row g+8, first) c3 = (row g+8, second)
+        const float val = t == 0 ? c[0] + d[0] : t == 1 ? c[1] + d[1] : t == 2 ? c[2] + d[2] : c[3] + d[3];
+        const float xs = xg[2 * kt + (t & 1)];
+        res = __fmaf_rn(bf16_bits_to_f32(slot[j].s), __fmaf_rn(-128.0f, xs, val), res);
+        res = __fmaf_rn(bf16_bits_to_f32(slot[j].z), xs, res);
+        fetch(slot[j]);  // refill with the unit four ahead
+        if (++c_i == n_kt) {
+          c_i = 0;
+          finish_tile();
         }
       }
-      const float xsc = xsum[step * 32 + lane];
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        const float s = bf16_bits_to_f32(cur.s[r]);
-        const float b = bf16_bits_to_f32(cur.b[r]);
-        const float t = __fmaf_rn(-128.0f, xsc, acc_lo[r] + acc_hi[r]);  // sum x*q over the chunk
-        res[r] = __fmaf_rn(s, t, res[r]);
-        res[r] = __fmaf_rn(b, xsc, res[r]);
-      }
     }
-
-    if (nstep == 0) {  // the row block is complete: reduce over lanes and store
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        float v = res[r];
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) { v += __shfl_xor_sync(0xffffffffu, v, off); }
-        const int64_t row = (int64_t)rb * R + r;
-        if (lane == 0 && row < N) { y[(int64_t)m * N + row] = __float2bfloat16_rn(v); }
-        res[r] = 0.0f;
-      }
-    }
-    if (!more) { break; }
-    cur = nxt;
-    rb = nrb;
-    step = nstep;
   }
 }
 
-template <int R>
 int launch_qmv(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const uint16_t* x,
                __nv_bfloat16* y, int K, int N, int M, cudaStream_t st) {
-  const int steps = (K + kStepK - 1) / kStepK;
-  const size_t smem = (size_t)steps * (256 * sizeof(float4) + 32 * sizeof(float));
-  auto kern = affine_qmv_w4g64_kernel<R>;
+  const int KT = (K + kTileK - 1) / kTileK;
+  const size_t smem = (size_t)KT * 256 + 16 + (size_t)2 * KT * sizeof(float) + 2 * kWarps * 16 * sizeof(float);
+  auto kern = affine_qmv_w4g64_kernel;
   if (smem > 48 * 1024) {
     VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   }
-  const int row_blocks = (N + R - 1) / R;
-  int ctas = (row_blocks + kWarps - 1) / kWarps;
+  const int row_tiles = (N + 15) / 16;
   const int cap = 2 * num_sms();
-  if (ctas > cap) { ctas = cap; }
+  const int ctas = row_tiles < cap ? row_tiles : cap;
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)ctas, (unsigned)M, 1);
@@ -231,7 +253,7 @@ int launch_qmv(const uint32_t* w, const uint16_t* scales, const uint16_t* biases
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  VPQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, w, scales, biases, x, y, K, N, steps));
+  VPQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, w, scales, biases, x, y, K, N));
   return VPQ_OK;
 }
 
@@ -265,11 +287,7 @@ extern "C" int vpq_affine_qmv_w4g64_bf16(const uint32_t* w, const void* scales, 
   const uint16_t* bi = static_cast<const uint16_t*>(biases);
   const uint16_t* xx = static_cast<const uint16_t*>(x);
   __nv_bfloat16* yy = static_cast<__nv_bfloat16*>(y);
-  // Rows per warp: more rows share each x read; fewer rows spread a small
-  // matrix over more warps.
-  if (N >= 8192) { return launch_qmv<4>(w, sc, bi, xx, yy, (int)K, (int)N, (int)M, st); }
-  if (N >= 2048) { return launch_qmv<2>(w, sc, bi, xx, yy, (int)K, (int)N, (int)M, st); }
-  return launch_qmv<1>(w, sc, bi, xx, yy, (int)K, (int)N, (int)M, st);
+  return launch_qmv(w, sc, bi, xx, yy, (int)K, (int)N, (int)M, st);
 }
 
 extern "C" int vpq_affine_qmv_w4g64_bf16_batch(const vpq_linear_desc* d, int count, void* stream) {
