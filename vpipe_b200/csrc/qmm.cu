@@ -451,7 +451,13 @@ extern "C" int vpq_device_status(void* stream, uint32_t* detail) {
   uint32_t v = 0;
   VPQ_CUDA_OK(cudaMemcpyFromSymbolAsync(&v, g_qmm_status, sizeof(v), 0, cudaMemcpyDeviceToHost, st));
   VPQ_CUDA_OK(cudaStreamSynchronize(st));
-  if (detail) { *detail = v; }
+  uint32_t vq = 0;
+  if (int rc = qmv_status_read(st, &vq)) { return rc; }
+  if (detail) { *detail = v ? v : (vq ? (vq | 0x10000u) : 0u); }
+  if (vq != 0 && v == 0) {
+    return fail(VPQ_ERR_TIMEOUT, "a bounded device-side wait gave up in the GEMV kernel (site %u, role %u)",
+                vq >> 8, vq & 0xffu);
+  }
   if (v != 0) {
     const uint32_t zero = 0;
     VPQ_CUDA_OK(cudaMemcpyToSymbolAsync(g_qmm_status, &zero, sizeof(zero), 0, cudaMemcpyHostToDevice, st));

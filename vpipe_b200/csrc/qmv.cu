@@ -5,19 +5,21 @@
 // gpu-kernels/metal/quant/affine_qmv.metal:186-301).
 //
 // The kernel is a stream of the packed weights out of HBM; everything else is
-// arranged so that the SM keeps up with 23 bytes (46 nibbles) per clock:
-//  * a CTA owns tiles of 16 output rows and its 8 warps split K (warp w takes
-//    a contiguous run of 128-wide k tiles), so even a 4096 x 4096 matrix gives
-//    every warp work and all loads of a warp are independent;
-//  * lane (g, t) of a warp reads 16 bytes of row g and 16 bytes of row g+8 per
-//    k tile (a quad covers 64 contiguous bytes of a row) with 128-bit
-//    non-allocating loads; four k tiles (8 loads per lane) are kept in flight;
-//  * nibbles are widened in registers to bf16 128+q with one LOP3 per two
-//    nibbles (0x4300 | q is exactly 128 + q) and fed, unscaled, to
-//    mma.sync.m16n8k16 against x; products are exact and the accumulation is
-//    f32. A first SIMT version of this kernel (one PRMT and half an f32x2 FMA
-//    per nibble) was bound by the integer pipe at under a quarter of the HBM
-//    rate; the tensor-core form needs about a third of the instructions;
+// arranged so that an SM keeps up with 23 bytes (46 nibbles) per clock:
+//  * the weights never pass through the load/store unit: a producer warp
+//    streams them with TMA, as [16 rows x 128 bytes] boxes (128-byte swizzle),
+//    into a ring of 16 KB stages (16 rows x 2048 k, plus that span's scales and
+//    biases), so up to ~190 KB per SM are in flight with no register cost.
+//    Two earlier versions that loaded nibbles with per-lane 128-bit loads
+//    saturated near 2.5 TB/s, stalled on outstanding L1 requests;
+//  * a CTA owns tiles of 16 output rows; consumer warp w of 8 takes box w of
+//    every stage (two 128-wide k tiles), so K is split across the warps;
+//  * lane (g, t) reads 16 bytes of two rows per k tile from the stage
+//    (conflict-free through the swizzle), widens the nibbles in registers to
+//    bf16 128+q with one LOP3 per two nibbles (0x4300 | q is exactly 128 + q)
+//    and feeds them, unscaled, to mma.sync.m16n8k16 against x; products are
+//    exact and the accumulation is f32. A first SIMT version (one PRMT and half
+//    an f32x2 FMA per nibble) was bound by the integer pipe;
 //  * the two quantization groups of a k tile go to different accumulator
 //    columns (even columns see only the first 64 k of x, odd columns the last
 //    64), so each group's sum comes out separately and is scaled once:
@@ -25,220 +27,405 @@
 //  * x is staged once per CTA in shared memory, already permuted into the
 //    B-fragment order that matches the nibble pairing (k, k+4);
 //  * per row tile: one shuffle, one shared-memory reduction over the 8 warps.
-// The launch opts into programmatic dependent launch: the first weight loads
-// are issued before griddepcontrol.wait, so the next GEMV's stream starts
-// while this one drains.
-#include "vpq_common.cuh"
+// The launch opts into programmatic dependent launch: the producer starts
+// streaming weights before griddepcontrol.wait, so the next GEMV's stream is
+// already running while this one drains. Every barrier wait is bounded.
+#include "vpq_sm100.cuh"
 
 namespace vpq {
 
+// 0, or (site << 8) | role of the first bounded wait that gave up in this kernel.
+__device__ uint32_t g_qmv_status;
+
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kWarps = kThreads / 32;
-constexpr int kSlots = 6;     // k tiles in flight per warp
-constexpr int kTileK = 128;   // k per tile: 64 bytes of a row, two quantization groups
+constexpr int kConsWarps = 8;
+constexpr int kConsThreads = kConsWarps * 32;
+constexpr int kThreads = kConsThreads + 32;  // + producer warp
+constexpr int kTileK = 128;                  // k per MMA unit: 64 bytes of a row, two groups
+constexpr int kBoxBytes = 16 * 128;          // one TMA box: 16 rows x 128 bytes (256 k)
+constexpr int kBoxesPerStage = 8;            // a stage spans 2048 k
+constexpr int kStageW = kBoxesPerStage * kBoxBytes;  // 16 KB of nibbles
+constexpr int kStageSZ = 2 * 16 * 64;        // scales + biases of the span: 2 x [16 rows x 32 groups]
+constexpr int kMaxStages = 6;
+constexpr int kRedSlots = 8;                 // row tiles whose cross-warp sums may be pending
 
-struct Slot {
-  uint4 ra, rb;     // 32 nibbles of row g and of row g+8
-  uint32_t s, z;    // scale and bias (bf16 bits) of this lane's (row, group) item
-};
-
-__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                               uint32_t a3, uint32_t b0, uint32_t b1) {
+// D = A * B + C on fp16 operands, f32 accumulate.
+__device__ __forceinline__ void mma_f16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                              uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
       "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// (v & 0x000f000f) | 0x43004300 in one LOP3: the bf16 pair (128 + lo nibble, 128 + hi nibble)
-__device__ __forceinline__ uint32_t and_or_magic(uint32_t v) {
+// D = A * B: starts an accumulator chain without first clearing four registers.
+__device__ __forceinline__ void mma_f16_16816_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                    uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+      "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
+// fp16 pairs straight out of a packed word, one LOP3 each:
+//   lo_magic(v) = (v & 0x000f000f) | 0x64006400 -> (1024 + nibble 0, 1024 + nibble 4) of v
+//   hi_magic(v) = (v & 0x00f000f0) | 0x54005400 -> (  64 + nibble 1,   64 + nibble 5) of v
+__device__ __forceinline__ uint32_t lo_magic(uint32_t v) {
   uint32_t r;
-  asm("lop3.b32 %0, %1, 0x000f000f, 0x43004300, 0xEA;" : "=r"(r) : "r"(v));
+  asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xEA;" : "=r"(r) : "r"(v));
+  return r;
+}
+__device__ __forceinline__ uint32_t hi_magic(uint32_t v) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, 0x00f000f0, 0x54005400, 0xEA;" : "=r"(r) : "r"(v));
   return r;
 }
 
-// 8 MMAs of one k tile: rows g / g+8 words wa / wb against the staged x fragments
-__device__ __forceinline__ void unit_mma(float (&c)[4], float (&d)[4], const uint4& ra, const uint4& rb,
-                                         const uint4* __restrict__ xb, int xb_q) {
-  const uint32_t wa[4] = {ra.x, ra.y, ra.z, ra.w};
-  const uint32_t wb[4] = {rb.x, rb.y, rb.z, rb.w};
-#pragma unroll
-  for (int wd = 0; wd < 4; ++wd) {
-    const uint4 xv = xb[wd * xb_q];
-    const uint32_t a = wa[wd], b = wb[wd];
-    // nibble pairs (n0,n4) (n1,n5) (n2,n6) (n3,n7) of each word
-    mma_bf16_16816(c, and_or_magic(a), and_or_magic(b), and_or_magic(a >> 4), and_or_magic(b >> 4),
-                   xv.x, xv.y);
-    mma_bf16_16816(d, and_or_magic(a >> 8), and_or_magic(b >> 8), and_or_magic(a >> 12),
-                   and_or_magic(b >> 12), xv.z, xv.w);  // second accumulator: two shorter dependency chains
-  }
-}
+enum : uint32_t { kRoleProducer = 1, kRoleConsumer = 2 };
 
+template <bool SCALES_TMA>
 __global__ void __launch_bounds__(kThreads, 2)
-affine_qmv_w4g64_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ scales,
-                        const uint16_t* __restrict__ biases, const uint16_t* __restrict__ x,
-                        __nv_bfloat16* __restrict__ y, int K, int N) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int KT = (K + kTileK - 1) / kTileK;  // k tiles (the last may hold one group only)
-  const int G = K >> 6;                      // groups per row
-  const int KW = K >> 3;                     // packed words per row
-  uint4* xperm = reinterpret_cast<uint4*>(smem_raw);            // [KT][4 quarters][4 t] x 16 B
-  uint4* zero16 = xperm + (size_t)KT * 16;                      // 16 bytes of zeros
-  float* xg = reinterpret_cast<float*>(zero16 + 1);             // [2*KT] group sums of x
-  float* red = xg + 2 * KT;                                     // [2][kWarps][16]
+affine_qmv_w4g64_kernel(const __grid_constant__ CUtensorMap map_w,
+                        const __grid_constant__ CUtensorMap map_s,
+                        const __grid_constant__ CUtensorMap map_z,
+                        const uint16_t* __restrict__ scales, const uint16_t* __restrict__ biases,
+                        const uint16_t* __restrict__ x, __nv_bfloat16* __restrict__ y, int K, int N,
+                        int stages) {
+  extern __shared__ unsigned char smem_dyn[];
+  const uint32_t raw = smem_u32(smem_dyn);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled boxes need 1024-byte alignment
+  unsigned char* base_ptr = smem_dyn + (base - raw);
+  constexpr int kStageBytes = kStageW + (SCALES_TMA ? kStageSZ : 0);
+
+  const int KT = ((K + 255) >> 8) * 2;        // k tiles per row, padded to whole 256-k boxes (x is zero there)
+  const int G = K >> 6;                       // groups per row
+  const int NB = (K + 255) >> 8;              // 128-byte boxes per row
+  const int SPT = (NB + kBoxesPerStage - 1) / kBoxesPerStage;  // stages per row tile
+
+  unsigned char* p = base_ptr + (size_t)stages * kStageBytes;
+  uint4* xperm = reinterpret_cast<uint4*>(p);                    // [KT][4 quarters][4 t] x 16 B
+  uint4* zero256 = xperm + (size_t)KT * 16;                      // 320 bytes of zeros
+  float2* xg = reinterpret_cast<float2*>(zero256 + 20);          // [2*KT] per group: surplus, sum of x
+  float* red = reinterpret_cast<float*>(xg + 2 * KT);            // [kRedSlots][kConsWarps][16]
+  uint32_t* red_cnt = reinterpret_cast<uint32_t*>(red + kRedSlots * kConsWarps * 16);  // [kRedSlots]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(red_cnt + kRedSlots);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * kMaxStages);
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar_full = [&](int s) { return bar0 + 8u * s; };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (kMaxStages + s); };
 
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  const int g = lane >> 2, t = lane & 3;
   const int m = blockIdx.y;
   const int row_tiles = (N + 15) >> 4;
-  // this warp's contiguous run of k tiles: [kt0, kt0 + n_kt)
-  const int n_kt = KT / kWarps + (warp < KT % kWarps ? 1 : 0);
-  const int kt0 = warp * (KT / kWarps) + min(warp, KT % kWarps);
-  const int item_row = g + ((t >> 1) << 3);  // the row whose (group t&1) sum this lane scales
-  const int my_tiles = blockIdx.x < row_tiles ? (row_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-  const int total_units = my_tiles * n_kt;
 
-  // Let the next kernel in the stream start its own weight prefetch now.
+  // Let the next kernel in the stream start its own weight stream now.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-  // ---- fetch side: walks the units (row tile, k tile) in the order they are consumed.
-  // Offsets past the end of a row (K % 128 == 64) or of the matrix (N % 16 != 0) are clamped
-  // onto valid data; what they fetch meets x == 0 or is never stored.
-  const uint32_t* f_pa = w;
-  const uint32_t* f_pb = w;
-  const uint16_t* f_ps = scales;
-  const uint16_t* f_pz = biases;
-  int f_tile = blockIdx.x, f_i = 0, f_units = 0;
-  auto fetch_tile_setup = [&]() {
-    const int r0 = f_tile << 4;
-    f_pa = w + (int64_t)min(r0 + g, N - 1) * KW;
-    f_pb = w + (int64_t)min(r0 + g + 8, N - 1) * KW;
-    const int64_t ri = min(r0 + item_row, N - 1);
-    f_ps = scales + ri * G;
-    f_pz = biases + ri * G;
-  };
-  auto fetch = [&](Slot& sl) {
-    if (f_units < total_units) {
-      const int kt = kt0 + f_i;
-      const int woff = min(kt * 16 + t * 4, KW - 4);
-      const int goff = min(2 * kt + (t & 1), G - 1);
-      sl.ra = ldg_stream_v4(f_pa + woff);
-      sl.rb = ldg_stream_v4(f_pb + woff);
-      sl.s = ldg_nc_u16(f_ps + goff);
-      sl.z = ldg_nc_u16(f_pz + goff);
-      ++f_units;
-      if (++f_i == n_kt) {
-        f_i = 0;
-        f_tile += gridDim.x;
-        fetch_tile_setup();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(bar_full(s), 1);
+      mbar_init(bar_empty(s), kConsWarps);
+    }
+    *abort_flag = 0;
+    for (int i = 0; i < kRedSlots; ++i) { red_cnt[i] = 0; }
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  if (warp == kConsWarps) {
+    // ------------------------------------------------------------ producer
+    // Weights, scales and biases are constants of the model: streaming them
+    // does not wait for the previous kernel.
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < row_tiles && ok; tile += gridDim.x) {
+        for (int st = 0; st < SPT; ++st, ++it) {
+          const int s = it % stages;
+          const uint32_t ph = (it / stages) & 1u;
+          if (!mbar_wait(bar_empty(s), ph ^ 1u, (1u << 8) | kRoleProducer, abort_flag, &g_qmv_status)) {
+            ok = false;
+            break;
+          }
+          const int nb = min(kBoxesPerStage, NB - st * kBoxesPerStage);
+          const uint32_t dst = base + (uint32_t)s * kStageBytes;
+          mbar_expect_tx(bar_full(s), (uint32_t)nb * kBoxBytes + (SCALES_TMA ? kStageSZ : 0));
+          for (int b = 0; b < nb; ++b) {
+            tma_load_2d(dst + b * kBoxBytes, &map_w, bar_full(s), (st * kBoxesPerStage + b) * 32, tile * 16);
+          }
+          if (SCALES_TMA) {
+            tma_load_2d(dst + kStageW, &map_s, bar_full(s), st * 32, tile * 16);
+            tma_load_2d(dst + kStageW + kStageSZ / 2, &map_z, bar_full(s), st * 32, tile * 16);
+          }
+        }
+      }
+      // Never leave with a copy still in flight: wait for the last load of every stage.
+      for (int s = 0; s < stages; ++s) {
+        if (it > (uint32_t)s) {
+          const uint32_t last = ((it - 1 - s) / stages) * stages + s;
+          mbar_wait(bar_full(s), (last / stages) & 1u, (2u << 8) | kRoleProducer, abort_flag, &g_qmv_status);
+        }
       }
     }
-  };
+    return;
+  }
 
-  // First weight words: they do not depend on the previous kernel.
-  Slot slot[kSlots];
-  fetch_tile_setup();
-#pragma unroll
-  for (int j = 0; j < kSlots; ++j) { fetch(slot[j]); }
+  // ---------------------------------------------------------------- consumers
+  const int g = lane >> 2, t = lane & 3;
+  const int rho = (g >> 1) | ((g & 1) << 2);  // stage row of MMA row g (g+8 -> rho+8): bank-conflict-free
+  const int item_row = rho + ((t >> 1) << 3); // the row whose (group t&1) sum this lane scales
+  const int par = t & 1;
 
   // x (and y) may be produced / consumed by the previous kernel.
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  // ---- stage x: 8 consecutive values (x0..x7) become the four B-fragment
-  // registers (x0,x4) (x1,x5) (x2,x6) (x3,x7); group sums in f32.
+  // ---- stage x as fp16. The tensor-core operands are fp16: a nibble sits in the low mantissa bits
+  // of 0x6400 (1024 + q) or, one nibble higher, of 0x5400 (64 + q), so no shift is needed for half
+  // of them. x is scaled by a power of two so that its largest magnitude lands in [2^14, 2^15):
+  // every bf16 value within 2^-28 of the maximum is then exact in fp16, and the scale is undone
+  // exactly at the end.
+  const uint16_t* xr = x + (int64_t)m * K;
+  const int chunks = KT * 16;  // 16-byte chunks of the padded x
+  // Each thread keeps up to kXRegs chunks of x in registers between the two passes (find the
+  // maximum, then convert), so x is read once and all of a thread's loads are in flight together.
+  // Longer rows (K > 8 * 256 * kXRegs) re-read the remainder in the second pass.
+  constexpr int kXRegs = 8;
+  uint4 xin[kXRegs];
   {
-    const uint16_t* xr = x + (int64_t)m * K;
-    const int chunks = KT * 16;  // 16-byte chunks of the padded x
-    // warp-uniform bound: every lane takes part in the shuffles below
-    for (int i = threadIdx.x; i - lane < chunks; i += kThreads) {
-      const bool live = i < chunks;
-      const int k0 = i * 8;
-      uint4 in = make_uint4(0, 0, 0, 0);
-      if (live && k0 < K) { in = *reinterpret_cast<const uint4*>(xr + k0); }
-      uint4 out;
-      asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(out.x) : "r"(in.x), "r"(in.z));
-      asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(out.y) : "r"(in.x), "r"(in.z));
-      asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(out.z) : "r"(in.y), "r"(in.w));
-      asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(out.w) : "r"(in.y), "r"(in.w));
-      const int kt = i >> 4, tt = (i >> 2) & 3, q = i & 3;
-      if (live) { xperm[(kt * 4 + q) * 4 + tt] = out; }
-      float part = ((bf16_bits_to_f32(in.x & 0xffffu) + __uint_as_float(in.x & 0xffff0000u)) +
-                    (bf16_bits_to_f32(in.y & 0xffffu) + __uint_as_float(in.y & 0xffff0000u))) +
-                   ((bf16_bits_to_f32(in.z & 0xffffu) + __uint_as_float(in.z & 0xffff0000u)) +
-                    (bf16_bits_to_f32(in.w & 0xffffu) + __uint_as_float(in.w & 0xffff0000u)));
-      part += __shfl_xor_sync(0xffffffffu, part, 1);
-      part += __shfl_xor_sync(0xffffffffu, part, 2);
-      part += __shfl_xor_sync(0xffffffffu, part, 4);
-      if (live && (i & 7) == 0) { xg[i >> 3] = part; }
+    uint32_t amax = 0;  // largest |x| as bf16 bits (ordering of magnitudes == ordering of bit patterns)
+#pragma unroll
+    for (int r = 0; r < kXRegs; ++r) {
+      const int i = threadIdx.x + r * kConsThreads;
+      xin[r] = make_uint4(0, 0, 0, 0);
+      if (i * 8 < K) { xin[r] = *reinterpret_cast<const uint4*>(xr + i * 8); }
     }
-    if (threadIdx.x == 0) { *zero16 = make_uint4(0, 0, 0, 0); }
+#pragma unroll
+    for (int r = 0; r < kXRegs; ++r) {
+      const uint32_t v[4] = {xin[r].x, xin[r].y, xin[r].z, xin[r].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        amax = max(amax, v[j] & 0x7fffu);
+        amax = max(amax, (v[j] >> 16) & 0x7fffu);
+      }
+    }
+    for (int i = threadIdx.x + kXRegs * kConsThreads; i * 8 < K; i += kConsThreads) {
+      const uint4 in = *reinterpret_cast<const uint4*>(xr + i * 8);
+      const uint32_t v[4] = {in.x, in.y, in.z, in.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        amax = max(amax, v[j] & 0x7fffu);
+        amax = max(amax, (v[j] >> 16) & 0x7fffu);
+      }
+    }
+    amax = __reduce_max_sync(0xffffffffu, amax);
+    if (lane == 0) { red_cnt[warp] = amax; }  // borrowed until the barriers below; cleared after
   }
-  __syncthreads();
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsThreads) : "memory");  // consumers only
+  float x_scale, x_unscale;
+  {
+    uint32_t amax = 0;
+#pragma unroll
+    for (int ww = 0; ww < kConsWarps; ++ww) { amax = max(amax, red_cnt[ww]); }
+    int e = (int)(amax >> 7);            // biased exponent of the largest magnitude
+    e = min(max(e, 16), 240);            // all-zero / denormal / huge x: keep both factors normal
+    x_scale = __uint_as_float((uint32_t)(268 - e) << 23);    // 2^(141 - e): max |x| -> [2^14, 2^15)
+    x_unscale = __uint_as_float((uint32_t)(e - 14) << 23);   // its exact inverse
+  }
+  // 8 consecutive values (x0..x7) become the four B-fragment registers (x0,x4) (x1,x5) (x2,x6)
+  // (x3,x7). Per group of 64: xg[].x = 1024 * sum(even k) + 64 * sum(odd k), the surplus the
+  // magic constants add to the accumulator; xg[].y = sum of all 64, for the bias term.
+  auto convert_chunk = [&](int i, const uint4& in) {  // called by whole warps: shuffles inside
+    const bool live = i < chunks;
+    const uint32_t v[4] = {in.x, in.y, in.z, in.w};
+    uint32_t hb[4];
+    float se = 0.0f, so = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __half2 h = __floats2half2_rn(__uint_as_float(v[j] << 16) * x_scale,
+                                          __uint_as_float(v[j] & 0xffff0000u) * x_scale);
+      const float2 f = __half22float2(h);  // what the tensor core will see
+      se += f.x;
+      so += f.y;
+      hb[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    uint4 out;
+    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(out.x) : "r"(hb[0]), "r"(hb[2]));
+    asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(out.y) : "r"(hb[0]), "r"(hb[2]));
+    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(out.z) : "r"(hb[1]), "r"(hb[3]));
+    asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(out.w) : "r"(hb[1]), "r"(hb[3]));
+    const int kt = i >> 4, tt = (i >> 2) & 3, q = i & 3;
+    if (live) { xperm[(kt * 4 + q) * 4 + tt] = out; }
+#pragma unroll
+    for (int off = 1; off < 8; off <<= 1) {
+      se += __shfl_xor_sync(0xffffffffu, se, off);
+      so += __shfl_xor_sync(0xffffffffu, so, off);
+    }
+    if (live && (i & 7) == 0) { xg[i >> 3] = make_float2(__fmaf_rn(1024.0f, se, 64.0f * so), se + so); }
+  };
+#pragma unroll
+  for (int r = 0; r < kXRegs; ++r) {
+    const int i = threadIdx.x + r * kConsThreads;
+    if (i - lane < chunks) { convert_chunk(i, xin[r]); }  // warp-uniform
+  }
+  for (int i = threadIdx.x + kXRegs * kConsThreads; i - lane < chunks; i += kConsThreads) {
+    uint4 in = make_uint4(0, 0, 0, 0);
+    if (i * 8 < K) { in = *reinterpret_cast<const uint4*>(xr + i * 8); }
+    convert_chunk(i, in);
+  }
+  if (threadIdx.x < 20) { zero256[threadIdx.x] = make_uint4(0, 0, 0, 0); }
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsThreads) : "memory");
+  if (threadIdx.x < kRedSlots) { red_cnt[threadIdx.x] = 0; }  // ordered before its first use by the tile loop's waits
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsThreads) : "memory");
 
   // Even accumulator columns see the first group of a k tile (chunks t = 0, 1),
   // odd columns the second (t = 2, 3); column c is supplied by the lanes with g == c.
+  // The other lanes read zeros from a block laid out like one k tile of xperm.
   const bool real = ((g & 1) == 0) ? (t < 2) : (t >= 2);
-  const uint4* xb_base = real ? xperm + t : zero16;
-  const int xb_kt = real ? 16 : 0, xb_q = real ? 4 : 0;
+  // (+4: quarter q of the zero block sits in the banks quarter q+1 of the data uses, so the two
+  // halves of a warp never collide)
+  const uint4* xb_base = real ? xperm + t : zero256 + 4;
+  const int xb_kt = real ? 16 : 0;
 
-  // ---- consume side
-  int buf = 0, c_i = 0, tile = blockIdx.x;
-  float res = 0.0f;
-  auto finish_tile = [&]() {  // both groups of a row, then the 8 warps' K slices
-    res += __shfl_xor_sync(0xffffffffu, res, 1);
-    if ((t & 1) == 0) { red[(buf * kWarps + warp) * 16 + item_row] = res; }
-    __syncthreads();
-    if (warp == 0 && lane < 16) {
-      float v = 0.0f;
-#pragma unroll
-      for (int ww = 0; ww < kWarps; ++ww) { v += red[(buf * kWarps + ww) * 16 + lane]; }
-      const int row = (tile << 4) + lane;
-      if (row < N) { y[(int64_t)m * N + row] = __float2bfloat16_rn(v); }
-    }
-    buf ^= 1;
-    res = 0.0f;
-    tile += gridDim.x;
-  };
+  // byte offsets of this lane's two 16-byte reads inside its box, per half (k tile) of the box
+  const uint32_t off_h0 = (uint32_t)rho * 128u + (uint32_t)(((0 + t) ^ rho) << 4);
+  const uint32_t off_h1 = (uint32_t)rho * 128u + (uint32_t)(((4 + t) ^ rho) << 4);
+  const uint32_t sz_off = (uint32_t)kStageW + (uint32_t)item_row * 64u + (uint32_t)warp * 8u;
+  const uint32_t sel = par ? 0x3244u : 0x1044u;  // PRMT: this lane's bf16 of a pair -> f32 bits
 
-  if (n_kt == 0) {  // K < 1024: this warp holds no k tile but still joins every reduction
-    for (int i = 0; i < my_tiles; ++i) { finish_tile(); }
-    return;
-  }
-
-  for (int u = 0; u < total_units; u += kSlots) {
-#pragma unroll
-    for (int j = 0; j < kSlots; ++j) {
-      if (u + j < total_units) {
-        const int kt = kt0 + c_i;
-        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f}, d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        unit_mma(c, d, slot[j].ra, slot[j].rb, xb_base + kt * xb_kt, xb_q);
-        // c0 = (row g, first group) c1 = (row g, second) c2 = (row g+8, first) c3 = (row g+8, second)
-        const float val = t == 0 ? c[0] + d[0] : t == 1 ? c[1] + d[1] : t == 2 ? c[2] + d[2] : c[3] + d[3];
-        const float xs = xg[2 * kt + (t & 1)];
-        res = __fmaf_rn(bf16_bits_to_f32(slot[j].s), __fmaf_rn(-128.0f, xs, val), res);
-        res = __fmaf_rn(bf16_bits_to_f32(slot[j].z), xs, res);
-        fetch(slot[j]);  // refill with the unit four ahead
-        if (++c_i == n_kt) {
-          c_i = 0;
-          finish_tile();
-        }
+  uint32_t tile_seq = 0, ph = 0;
+  int s = 0;
+  bool ok = true;
+  for (int tile = blockIdx.x; tile < row_tiles && ok; tile += gridDim.x, ++tile_seq) {
+    float res = 0.0f;
+    for (int st = 0; st < SPT; ++st) {
+      if (!warp_wait(bar_full(s), ph, (1u << 8) | kRoleConsumer, abort_flag, &g_qmv_status)) {
+        ok = false;
+        break;
       }
+      const unsigned char* sb = base_ptr + (size_t)s * kStageBytes;
+      const int kt0 = st * 16 + warp * 2;  // this warp's box holds k tiles kt0 and kt0 + 1
+      if (kt0 < KT) {
+        const unsigned char* box = sb + warp * kBoxBytes;
+        // both k tiles of the box at once: four independent accumulator chains
+        const uint4 ra0 = *reinterpret_cast<const uint4*>(box + off_h0);
+        const uint4 rb0 = *reinterpret_cast<const uint4*>(box + off_h0 + 1024);
+        const uint4 ra1 = *reinterpret_cast<const uint4*>(box + off_h1);
+        const uint4 rb1 = *reinterpret_cast<const uint4*>(box + off_h1 + 1024);
+        uint2 sw = make_uint2(0, 0), zw = make_uint2(0, 0);
+        if (SCALES_TMA) {
+          sw = *reinterpret_cast<const uint2*>(sb + sz_off);
+          zw = *reinterpret_cast<const uint2*>(sb + sz_off + kStageSZ / 2);
+        }
+        const int kt1 = kt0 + 1;
+        float c0[4], d0[4], c1[4], d1[4];
+        const uint4* xb0 = xb_base + kt0 * xb_kt;
+        const uint4* xb1 = xb_base + kt1 * xb_kt;
+        const uint32_t a0[4] = {ra0.x, ra0.y, ra0.z, ra0.w}, b0[4] = {rb0.x, rb0.y, rb0.z, rb0.w};
+        const uint32_t a1[4] = {ra1.x, ra1.y, ra1.z, ra1.w}, b1[4] = {rb1.x, rb1.y, rb1.z, rb1.w};
+#pragma unroll
+        for (int wd = 0; wd < 4; ++wd) {
+          const uint4 x0 = xb0[wd * 4];
+          const uint4 x1 = xb1[wd * 4];
+          const uint32_t a0h = a0[wd] >> 8, b0h = b0[wd] >> 8, a1h = a1[wd] >> 8, b1h = b1[wd] >> 8;
+          // nibble pairs (n0,n4) (n1,n5) of each word, then (n2,n6) (n3,n7) from the word >> 8
+          if (wd == 0) {
+            mma_f16_16816_first(c0, lo_magic(a0[wd]), lo_magic(b0[wd]), hi_magic(a0[wd]), hi_magic(b0[wd]), x0.x, x0.y);
+            mma_f16_16816_first(c1, lo_magic(a1[wd]), lo_magic(b1[wd]), hi_magic(a1[wd]), hi_magic(b1[wd]), x1.x, x1.y);
+            mma_f16_16816_first(d0, lo_magic(a0h), lo_magic(b0h), hi_magic(a0h), hi_magic(b0h), x0.z, x0.w);
+            mma_f16_16816_first(d1, lo_magic(a1h), lo_magic(b1h), hi_magic(a1h), hi_magic(b1h), x1.z, x1.w);
+          } else {
+            mma_f16_16816(c0, lo_magic(a0[wd]), lo_magic(b0[wd]), hi_magic(a0[wd]), hi_magic(b0[wd]), x0.x, x0.y);
+            mma_f16_16816(c1, lo_magic(a1[wd]), lo_magic(b1[wd]), hi_magic(a1[wd]), hi_magic(b1[wd]), x1.x, x1.y);
+            mma_f16_16816(d0, lo_magic(a0h), lo_magic(b0h), hi_magic(a0h), hi_magic(b0h), x0.z, x0.w);
+            mma_f16_16816(d1, lo_magic(a1h), lo_magic(b1h), hi_magic(a1h), hi_magic(b1h), x1.z, x1.w);
+          }
+        }
+        // per unit: [0] = (row g, first group) [1] = (row g, second) [2] = (row g+8, first) [3] = (row g+8, second)
+        const float v0 = (t == 0 ? c0[0] : t == 1 ? c0[1] : t == 2 ? c0[2] : c0[3]) +
+                         (t == 0 ? d0[0] : t == 1 ? d0[1] : t == 2 ? d0[2] : d0[3]);
+        const float v1 = (t == 0 ? c1[0] : t == 1 ? c1[1] : t == 2 ? c1[2] : c1[3]) +
+                         (t == 0 ? d1[0] : t == 1 ? d1[1] : t == 2 ? d1[2] : d1[3]);
+        const float2 xs0 = xg[2 * kt0 + par];
+        const float2 xs1 = xg[2 * kt1 + par];
+        uint32_t s0, z0, s1, z1;
+        if (SCALES_TMA) {
+          asm("prmt.b32 %0, %1, %2, %3;" : "=r"(s0) : "r"(sw.x), "r"(0u), "r"(sel));
+          asm("prmt.b32 %0, %1, %2, %3;" : "=r"(z0) : "r"(zw.x), "r"(0u), "r"(sel));
+          asm("prmt.b32 %0, %1, %2, %3;" : "=r"(s1) : "r"(sw.y), "r"(0u), "r"(sel));
+          asm("prmt.b32 %0, %1, %2, %3;" : "=r"(z1) : "r"(zw.y), "r"(0u), "r"(sel));
+        } else {
+          // clamped onto valid data: a clamped group meets x == 0, a clamped row is never stored
+          const int64_t ri = min(tile * 16 + item_row, N - 1);
+          const int g0 = min(2 * kt0 + par, G - 1), g1 = min(2 * kt1 + par, G - 1);
+          s0 = ldg_nc_u16(scales + ri * G + g0) << 16;
+          z0 = ldg_nc_u16(biases + ri * G + g0) << 16;
+          s1 = ldg_nc_u16(scales + ri * G + g1) << 16;
+          z1 = ldg_nc_u16(biases + ri * G + g1) << 16;
+        }
+        res = __fmaf_rn(__uint_as_float(s0), v0 - xs0.x, res);
+        res = __fmaf_rn(__uint_as_float(z0), xs0.y, res);
+        res = __fmaf_rn(__uint_as_float(s1), v1 - xs1.x, res);
+        res = __fmaf_rn(__uint_as_float(z1), xs1.y, res);
+      }
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(bar_empty(s)); }  // this warp's part of the stage is in registers
+      if (++s == stages) {
+        s = 0;
+        ph ^= 1u;
+      }
+    }
+    if (!ok) { break; }
+    // Both groups of a row, then the 8 warps' K slices: every warp posts its 16 partial sums and
+    // moves on; the warp that posts last adds them in warp order (so the result does not depend
+    // on arrival order) and stores. The ring of kRedSlots tiles is deeper than a warp can run ahead.
+    res += __shfl_xor_sync(0xffffffffu, res, 1);
+    const int slot = tile_seq % kRedSlots;
+    if (par == 0) { red[(slot * kConsWarps + warp) * 16 + item_row] = res; }
+    __syncwarp();
+    uint32_t last = 0;
+    if (lane == 0) {
+      __threadfence_block();
+      last = atomicAdd(&red_cnt[slot], 1u) == (uint32_t)(kConsWarps - 1);
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last) {
+      __threadfence_block();
+      if (lane < 16) {
+        float v = 0.0f;
+#pragma unroll
+        for (int ww = 0; ww < kConsWarps; ++ww) {
+          v += *reinterpret_cast<volatile float*>(&red[(slot * kConsWarps + ww) * 16 + lane]);
+        }
+        const int row = (tile << 4) + lane;
+        if (row < N) { y[(int64_t)m * N + row] = __float2bfloat16_rn(v * x_unscale); }
+      }
+      __syncwarp();
+      if (lane == 0) { red_cnt[slot] = 0; }
     }
   }
 }
 
-int launch_qmv(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const uint16_t* x,
-               __nv_bfloat16* y, int K, int N, int M, cudaStream_t st) {
-  const int KT = (K + kTileK - 1) / kTileK;
-  const size_t smem = (size_t)KT * 256 + 16 + (size_t)2 * KT * sizeof(float) + 2 * kWarps * 16 * sizeof(float);
-  auto kern = affine_qmv_w4g64_kernel;
-  if (smem > 48 * 1024) {
-    VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  }
+template <bool SCALES_TMA>
+int launch_qmv_t(const CUtensorMap& mw, const CUtensorMap& ms, const CUtensorMap& mz,
+                 const uint16_t* scales, const uint16_t* biases, const uint16_t* x, __nv_bfloat16* y,
+                 int K, int N, int M, cudaStream_t st) {
+  const int KT = ((K + 255) / 256) * 2;  // as in the kernel: k tiles padded to whole 256-k boxes
+  const size_t stage_bytes = kStageW + (SCALES_TMA ? kStageSZ : 0);
+  const size_t fixed = 1024 /*alignment slack*/ + (size_t)KT * 256 + 320 + (size_t)2 * KT * 8 +
+                       kRedSlots * kConsWarps * 16 * 4 + kRedSlots * 4 + 2 * kMaxStages * 8 + 16;
+  const size_t budget = 112 * 1024;  // two CTAs per SM
+  int stages = fixed + 2 * stage_bytes <= budget ? (int)((budget - fixed) / stage_bytes) : 2;
+  if (stages > kMaxStages) { stages = kMaxStages; }
+  const int NB = (K + 255) / 256;
+  const int SPT = (NB + kBoxesPerStage - 1) / kBoxesPerStage;
+  (void)SPT;
+  const size_t smem = fixed + (size_t)stages * stage_bytes;
+  auto kern = affine_qmv_w4g64_kernel<SCALES_TMA>;
+  VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int row_tiles = (N + 15) / 16;
   const int cap = 2 * num_sms();
   const int ctas = row_tiles < cap ? row_tiles : cap;
@@ -253,11 +440,52 @@ int launch_qmv(const uint32_t* w, const uint16_t* scales, const uint16_t* biases
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  VPQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, w, scales, biases, x, y, K, N));
+  VPQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, mw, ms, mz, scales, biases, x, y, K, N, stages));
   return VPQ_OK;
 }
 
+int launch_qmv(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const uint16_t* x,
+               __nv_bfloat16* y, int K, int N, int M, cudaStream_t st) {
+  CUtensorMap mw, ms, mz;
+  if (int rc = make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w, (uint64_t)(K / 8), (uint64_t)N, 32,
+                           16, CU_TENSOR_MAP_SWIZZLE_128B, "w")) {
+    return rc;
+  }
+  // The scale / bias rows can be TMA boxes only if their pitch is a multiple of 16 bytes.
+  const bool scales_tma = (K % 512) == 0 && aligned16(scales) && aligned16(biases);
+  if (scales_tma) {
+    const int G = K / 64;
+    if (int rc = make_map_2d(&ms, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, (uint64_t)G, (uint64_t)N, 32,
+                             16, CU_TENSOR_MAP_SWIZZLE_NONE, "scales")) {
+      return rc;
+    }
+    if (int rc = make_map_2d(&mz, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, biases, (uint64_t)G, (uint64_t)N, 32,
+                             16, CU_TENSOR_MAP_SWIZZLE_NONE, "biases")) {
+      return rc;
+    }
+    return launch_qmv_t<true>(mw, ms, mz, scales, biases, x, y, K, N, M, st);
+  }
+  ms = mw;
+  mz = mw;
+  return launch_qmv_t<false>(mw, ms, mz, scales, biases, x, y, K, N, M, st);
+}
+
 }  // namespace
+}  // namespace vpq
+
+namespace vpq {
+int qmv_status_read(cudaStream_t st, uint32_t* out) {
+  uint32_t v = 0;
+  VPQ_CUDA_OK(cudaMemcpyFromSymbolAsync(&v, g_qmv_status, sizeof(v), 0, cudaMemcpyDeviceToHost, st));
+  VPQ_CUDA_OK(cudaStreamSynchronize(st));
+  if (v != 0) {
+    const uint32_t zero = 0;
+    VPQ_CUDA_OK(cudaMemcpyToSymbolAsync(g_qmv_status, &zero, sizeof(zero), 0, cudaMemcpyHostToDevice, st));
+    VPQ_CUDA_OK(cudaStreamSynchronize(st));
+  }
+  *out = v;
+  return VPQ_OK;
+}
 }  // namespace vpq
 
 using namespace vpq;

@@ -38,6 +38,9 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 int num_sms();
 
+// Reads and clears the GEMV kernel's device status word (qmv.cu).
+int qmv_status_read(cudaStream_t st, uint32_t* out);
+
 // --------------------------------------------------------------- device side
 #ifdef __CUDACC__
 
