@@ -124,19 +124,34 @@ __device__ __forceinline__ void tmem_ld_wait() {
 // 8 nibbles of one packed word -> 8 bf16 (4 packed registers), bit-identical
 // to bf16_rne(fmaf(s, q, b)). The nibble is dropped into mantissa bits 16..19
 // of 0x43000000 (the float 128 + q); with b128 = b - 128 s formed exactly,
-// fmaf(s, 128 + q, b128) rounds the same real number s q + b once.
-__device__ __forceinline__ void dequant_word_fast(uint32_t word, float s, float b128, uint32_t* out) {
-  const uint32_t e = word & 0x0f0f0f0fu;
-  const uint32_t o = (word >> 4) & 0x0f0f0f0fu;
+// fmaf(s, 128 + q, b128) rounds the same real number s q + b once. The two
+// multiply-adds of a nibble pair share one packed f32x2 instruction; s2 / b2
+// hold (s, s) and (b128, b128).
+__device__ __forceinline__ void dequant_word_fast(uint32_t word, uint64_t s2, uint64_t b2, uint32_t* out) {
+  const uint32_t e = word & 0x0f0f0f0fu;         // nibbles 0,2,4,6 as bytes
+  const uint32_t o = (word >> 4) & 0x0f0f0f0fu;  // nibbles 1,3,5,7 as bytes
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     uint32_t fe, fo;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(fe) : "r"(e), "r"(0x43000000u), "r"(0x7054u + (j << 8)));
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(fo) : "r"(o), "r"(0x43000000u), "r"(0x7054u + (j << 8)));
-    const float ve = __fmaf_rn(s, __uint_as_float(fe), b128);
-    const float vo = __fmaf_rn(s, __uint_as_float(fo), b128);
-    out[j] = pack_bf16x2(ve, vo);
+    asm("{\n\t"
+        ".reg .b64 q2, v2;\n\t"
+        ".reg .b32 ve, vo;\n\t"
+        "mov.b64 q2, {%1, %2};\n\t"
+        "fma.rn.f32x2 v2, %3, q2, %4;\n\t"
+        "mov.b64 {ve, vo}, v2;\n\t"
+        "cvt.rn.bf16x2.f32 %0, vo, ve;\n\t"
+        "}"
+        : "=r"(out[j])
+        : "r"(fe), "r"(fo), "l"(s2), "l"(b2));
   }
+}
+
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
 }
 
 __device__ __forceinline__ void dequant_word_exact(uint32_t word, float s, float b, uint32_t* out) {
@@ -313,8 +328,9 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
         uint32_t o[32];
         const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
         if (resid == 0.0f) {
+          const uint64_t s2 = pack_f32x2(sc, sc), b2 = pack_f32x2(b128, b128);
 #pragma unroll
-          for (int wd = 0; wd < 8; ++wd) { dequant_word_fast(cw[wd], sc, b128, o + 4 * wd); }
+          for (int wd = 0; wd < 8; ++wd) { dequant_word_fast(cw[wd], s2, b2, o + 4 * wd); }
         } else {
 #pragma unroll
           for (int wd = 0; wd < 8; ++wd) { dequant_word_exact(cw[wd], sc, bi, o + 4 * wd); }
