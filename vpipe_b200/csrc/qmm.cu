@@ -29,6 +29,8 @@
 // reuse between CTAs comes from L2.
 #include "vpq_sm100.cuh"
 
+#include <cstdlib>
+
 namespace vpq {
 
 // Status word of the tensor-core kernels: 0, or (site << 8) | role of the
@@ -162,6 +164,57 @@ __device__ __forceinline__ void dequant_word_exact(uint32_t word, float s, float
     out[j] = pack_bf16x2(ve, vo);
   }
 }
+
+// One row's scales and biases along K: eight groups (16 bytes) per load, fetched one block of
+// eight k blocks ahead, so the latency of these small loads never sits in the dequant loop.
+// Rows whose pitch or base is not 16-byte aligned fall back to one 2-byte load per k block.
+struct ScaleStream {
+  const uint16_t* s;
+  const uint16_t* b;
+  int groups;
+  bool vec;
+  uint4 s_cur, b_cur, s_nxt, b_nxt;
+  uint32_t s1, b1;
+  __device__ __forceinline__ ScaleStream(const uint16_t* srow, const uint16_t* brow, int g)
+      : s(srow), b(brow), groups(g) {
+    vec = ((g & 7) == 0) && ((reinterpret_cast<uintptr_t>(srow) | reinterpret_cast<uintptr_t>(brow)) & 15u) == 0;
+    s_cur = b_cur = s_nxt = b_nxt = make_uint4(0, 0, 0, 0);
+    s1 = b1 = 0;
+    if (vec) {
+      s_nxt = __ldg(reinterpret_cast<const uint4*>(s));
+      b_nxt = __ldg(reinterpret_cast<const uint4*>(b));
+    } else {
+      s1 = ldg_nc_u16(s);
+      b1 = ldg_nc_u16(b);
+    }
+  }
+  __device__ __forceinline__ static float pick(const uint4& v, int i) {
+    const uint32_t w = i < 4 ? (i < 2 ? v.x : v.y) : (i < 6 ? v.z : v.w);
+    return __uint_as_float((i & 1) ? (w & 0xffff0000u) : (w << 16));
+  }
+  __device__ __forceinline__ void get(int kb, float& sc, float& bi) {
+    if (vec) {
+      const int i = kb & 7;
+      if (i == 0) {
+        s_cur = s_nxt;
+        b_cur = b_nxt;
+        if (kb + 8 < groups) {
+          s_nxt = __ldg(reinterpret_cast<const uint4*>(s + kb + 8));
+          b_nxt = __ldg(reinterpret_cast<const uint4*>(b + kb + 8));
+        }
+      }
+      sc = pick(s_cur, i);
+      bi = pick(b_cur, i);
+    } else {
+      sc = bf16_bits_to_f32(s1);
+      bi = bf16_bits_to_f32(b1);
+      if (kb + 1 < groups) {
+        s1 = ldg_nc_u16(s + kb + 1);
+        b1 = ldg_nc_u16(b + kb + 1);
+      }
+    }
+  }
+};
 
 enum Role : uint32_t { kRoleEpi = 1, kRoleTma = 2, kRoleMma = 3, kRoleDq = 4 };
 
@@ -301,18 +354,14 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
       row = row < N ? row : N - 1;  // tail rows: any valid scale; their columns are never stored
       const uint16_t* srow = scales + (int64_t)row * groups;
       const uint16_t* brow = biases + (int64_t)row * groups;
-      uint32_t s_next = ldg_nc_u16(srow), b_next = ldg_nc_u16(brow);
+      ScaleStream sst(srow, brow, groups);
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int s = it % kStages;
         const uint32_t ph = (it / kStages) & 1u;
         const int t = it % kBStages;
         const uint32_t bph = (it / kBStages) & 1u;
-        const float sc = bf16_bits_to_f32(s_next);
-        const float bi = bf16_bits_to_f32(b_next);
-        if (kb + 1 < num_kb) {
-          s_next = ldg_nc_u16(srow + kb + 1);
-          b_next = ldg_nc_u16(brow + kb + 1);
-        }
+        float sc, bi;
+        sst.get(kb, sc, bi);
         if (!warp_wait(bar_full(s), ph, (1u << 8) | kRoleDq, abort_flag, &g_qmm_status)) { ok = false; break; }
         const uint4* cp = reinterpret_cast<const uint4*>(base_ptr + L::kOffCode + s * L::kCodeBytes +
                                                          t_row * (BK / 2));
@@ -405,6 +454,8 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
   }
 }
 
+#include "qmm_2cta.cuh"
+
 // ------------------------------------------------------------- host side
 template <int BN>
 int launch_qmm(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const void* x,
@@ -427,6 +478,28 @@ int launch_qmm(const uint32_t* w, const uint16_t* scales, const uint16_t* biases
   constexpr int threads = 32 * (kEpiWarps + 2 + BN / 32);
   kern<<<grid, threads, L::kAlloc, st>>>(map_x, map_w, scales, biases, y, M, N, K);
   VPQ_LAUNCH_OK("affine_qmm_w4g64");
+  return VPQ_OK;
+}
+
+int launch_qmm_2cta(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const void* x,
+                    __nv_bfloat16* y, int K, int N, int M, cudaStream_t st) {
+  using L = two_cta::Smem;
+  CUtensorMap map_x, map_w;
+  if (int rc = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)K, (uint64_t)M,
+                           BK, 128, CU_TENSOR_MAP_SWIZZLE_128B, "x")) {
+    return rc;
+  }
+  if (int rc = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w, (uint64_t)(K / 8),
+                           (uint64_t)N, BK / 8, 128, CU_TENSOR_MAP_SWIZZLE_NONE, "w")) {
+    return rc;
+  }
+  auto kern = two_cta::affine_qmm_w4g64_2cta_kernel;
+  VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
+  const int tiles = ((M + two_cta::TM - 1) / two_cta::TM) * ((N + two_cta::TN - 1) / two_cta::TN);
+  const int pairs = num_sms() / 2;
+  const int grid = 2 * (tiles < pairs ? tiles : pairs);
+  kern<<<grid, two_cta::kThreads2, L::kAlloc, st>>>(map_x, map_w, scales, biases, y, M, N, K);
+  VPQ_LAUNCH_OK("affine_qmm_w4g64 (2-CTA)");
   return VPQ_OK;
 }
 
@@ -456,6 +529,13 @@ extern "C" int vpq_affine_qmm_w4g64_bf16(const uint32_t* w, const void* scales, 
   }
   if (int rc = require_sm100()) { return rc; }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // 256 x 256 tiles on CTA pairs when there are at least two row tiles' worth of rows; the
+  // single-CTA 128 x 256 kernel otherwise.
+  static const bool force_1cta = std::getenv("VPQ_QMM_1CTA") != nullptr;
+  if (M > 128 && !force_1cta) {
+    return launch_qmm_2cta(w, static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases),
+                           x, static_cast<__nv_bfloat16*>(y), (int)K, (int)N, (int)M, st);
+  }
   return launch_qmm<256>(w, static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases),
                          x, static_cast<__nv_bfloat16*>(y), (int)K, (int)N, (int)M, st);
 }

@@ -1,0 +1,385 @@
+// qmm_2cta.cuh -- the QMM as a 2-CTA (cta_group::2) kernel: a cluster of two CTAs on one TPC
+// computes a 256 x 256 output tile. Included by qmm.cu (uses its helpers).
+//
+// Why two CTAs: with a 128-row tile, every 64-wide k block costs one SM the dequantisation of
+// 256 W rows and the shared-memory traffic of a full B operand. In a CTA pair each SM keeps its
+// own 128 x rows (A operand) but only HALF of the W tile (128 rows of B); the tensor cores of
+// both SMs read both halves. Dequant work and shared-memory bytes per flop halve.
+//
+// Per CTA, 448 threads as in the 1-CTA kernel: warps 0-3 epilogue (tensor-memory lanes = this
+// CTA's 128 output rows), warp 4 TMA producer, warp 5 tensor-memory allocation (+ MMA issue in the
+// leader CTA only), warps 6-13 dequantisers (two threads per W row, 32 values each).
+//
+// Barriers. Local to each CTA: cfull[s] (packed W landed here), empty[s] (x + codes slot free:
+// one multicast tcgen05.commit + the local dequant warps), bempty[t] (dequantised tile free:
+// multicast commit), accfull[a] (accumulator done: multicast commit). In the leader CTA only:
+// xfull[s] (x tiles of BOTH CTAs landed: the peer's TMA signals it through cta_group::2),
+// bfull[t] (both halves dequantised: local + remote arrivals), accempty[a] (both CTAs' epilogues
+// drained). No TMA load is a multicast load. Every wait is bounded.
+#pragma once
+
+namespace two_cta {
+
+constexpr int TM = 256;        // tile rows (128 per CTA)
+constexpr int TN = 256;        // tile columns (128 W rows dequantised per CTA)
+constexpr int kXStages = 6;    // x + codes ring
+constexpr int kBTiles = 4;     // dequantised-B ring
+constexpr int kDqWarps = 8;
+constexpr int kThreads2 = 32 * (kEpiWarps + 2 + kDqWarps);
+
+struct Smem {
+  static constexpr int kXBytes = 128 * BK * 2;        // 16 KB, 128B-swizzled
+  static constexpr int kCodeBytes = 128 * (BK / 2);   // 128 rows x 32 B
+  static constexpr int kBBytes = 128 * BK * 2;        // 16 KB, 128B-swizzled K-major
+  static constexpr int kOffX = 0;
+  static constexpr int kOffB = kOffX + kXStages * kXBytes;
+  static constexpr int kOffCode = kOffB + kBTiles * kBBytes;
+  static constexpr int kOffBar = kOffCode + kXStages * kCodeBytes;
+  static constexpr int kNumBars = 3 * kXStages + 2 * kBTiles + 4;
+  static constexpr int kOffTmem = kOffBar + kNumBars * 8;
+  static constexpr int kTotal = kOffTmem + 16;
+  static constexpr int kAlloc = kTotal + 1024;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// shared::cluster address of `local_addr` (a shared::cta address) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// Bounded wait used by the leader's MMA thread on barriers the partner CTA also arrives on. The
+// partner's shared-memory writes are published to the async proxy by its fence.proxy.async before
+// its remote arrive; the tensor core reads them only after this wait returns.
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, uint32_t code,
+                                                  volatile uint32_t* abort_flag, uint32_t* status_word) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) { return true; }
+    if (i > 64) {
+      __nanosleep(i > 4096 ? 256 : 32);
+      if (*abort_flag) { return false; }
+    }
+  }
+  *abort_flag = 1;
+  atomicCAS(status_word, 0u, code);
+  return false;
+}
+
+// x tile of a CTA pair: lands in this CTA's shared memory, completes bytes on the LEADER's barrier.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map,
+                                                 uint32_t leader_bar_cluster_addr, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(leader_bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Arrives on the barrier at this shared-memory offset in BOTH CTAs once the MMAs issued so far are done.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"((uint16_t)3)
+      : "memory");
+}
+
+// Instruction descriptor: D f32, A/B bf16, both K-major, M = 256 (pair), N = 256.
+__device__ __forceinline__ constexpr uint32_t make_idesc_pair() {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
+}
+
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
+affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                             const __grid_constant__ CUtensorMap tmap_w,
+                             const uint16_t* __restrict__ scales, const uint16_t* __restrict__ biases,
+                             __nv_bfloat16* __restrict__ y, int M, int N, int K) {
+  using L = Smem;
+  constexpr uint32_t kTmemCols = 512;  // two 256-column accumulator buffers
+
+  extern __shared__ unsigned char smem_dyn[];
+  const uint32_t raw = smem_u32(smem_dyn);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_dyn + (base - raw);
+
+  const uint32_t bar0 = base + L::kOffBar;
+  auto bar_xfull = [&](int s) { return bar0 + 8u * s; };
+  auto bar_cfull = [&](int s) { return bar0 + 8u * (kXStages + s); };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (2 * kXStages + s); };
+  auto bar_bfull = [&](int t) { return bar0 + 8u * (3 * kXStages + t); };
+  auto bar_bempty = [&](int t) { return bar0 + 8u * (3 * kXStages + kBTiles + t); };
+  auto bar_accfull = [&](int a) { return bar0 + 8u * (3 * kXStages + 2 * kBTiles + a); };
+  auto bar_accempty = [&](int a) { return bar0 + 8u * (3 * kXStages + 2 * kBTiles + 2 + a); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L::kOffTmem);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader (issues the MMAs)
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+
+  const int tiles_m = (M + TM - 1) / TM;
+  const int tiles_n = (N + TN - 1) / TN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = K / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kXStages; ++s) {
+      mbar_init(bar_xfull(s), 1);
+      mbar_init(bar_cfull(s), 1);
+      mbar_init(bar_empty(s), 1 + kDqWarps);
+    }
+    for (int t = 0; t < kBTiles; ++t) {
+      mbar_init(bar_bfull(t), 2 * kDqWarps);
+      mbar_init(bar_bempty(t), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_accfull(a), 1);
+      mbar_init(bar_accempty(a), 2 * kEpiWarps);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 5) {  // the same warp of both CTAs allocates the pair's tensor memory
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32((const void*)tmem_slot)), "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anybody signals across
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    // ------------------------------------------------------- TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        const int m0 = (tile / tiles_n) * TM + (int)rank * 128;
+        const int n0 = (tile % tiles_n) * TN + (int)rank * 128;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kXStages;
+          const uint32_t ph = (it / kXStages) & 1u;
+          if (!mbar_wait(bar_empty(s), ph ^ 1u, (1u << 8) | kRoleTma, abort_flag, &g_qmm_status)) { ok = false; break; }
+          // the leader expects the x bytes of both CTAs; each CTA expects its own codes
+          if (rank == 0) { mbar_expect_tx(bar_xfull(s), 2 * L::kXBytes); }
+          mbar_expect_tx(bar_cfull(s), L::kCodeBytes);
+          tma_load_2d_pair(base + L::kOffX + s * L::kXBytes, &tmap_x, map_to_cta(bar_xfull(s), 0), kb * BK, m0);
+          tma_load_2d(base + L::kOffCode + s * L::kCodeBytes, &tmap_w, bar_cfull(s), kb * (BK / 8), n0);
+        }
+      }
+      // Never leave with a copy still in flight: the codes barriers are local; the x copies of
+      // the last uses of each stage are covered by the final cluster barrier below, which the
+      // leader reaches only after its MMAs (hence these loads) completed or its waits gave up.
+      for (int s = 0; s < kXStages; ++s) {
+        if (it > (uint32_t)s) {
+          const uint32_t last = ((it - 1 - s) / kXStages) * kXStages + s;
+          mbar_wait(bar_cfull(s), (last / kXStages) & 1u, (2u << 8) | kRoleTma, abort_flag, &g_qmm_status);
+          if (rank == 0) {
+            mbar_wait(bar_xfull(s), (last / kXStages) & 1u, (3u << 8) | kRoleTma, abort_flag, &g_qmm_status);
+          }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // --------------------------------------------------------- MMA issuer (leader only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_pair();
+      uint32_t it = 0, ti = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++ti) {
+        const int a = ti & 1;
+        const uint32_t aph = (ti >> 1) & 1u;
+        if (!mbar_wait_cluster(bar_accempty(a), aph ^ 1u, (1u << 8) | kRoleMma, abort_flag, &g_qmm_status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(a * TN);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kXStages;
+          const uint32_t ph = (it / kXStages) & 1u;
+          const int t = it % kBTiles;
+          const uint32_t bph = (it / kBTiles) & 1u;
+          if (!mbar_wait_cluster(bar_xfull(s), ph, (2u << 8) | kRoleMma, abort_flag, &g_qmm_status)) { ok = false; break; }
+          if (!mbar_wait_cluster(bar_bfull(t), bph, (3u << 8) | kRoleMma, abort_flag, &g_qmm_status)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t a_desc = make_sw128_desc(base + L::kOffX + s * L::kXBytes);
+          const uint64_t b_desc = make_sw128_desc(base + L::kOffB + t * L::kBBytes);
+#pragma unroll
+          for (int k16 = 0; k16 < BK / 16; ++k16) {
+            umma_bf16_pair(d_tmem, a_desc + 2u * k16, b_desc + 2u * k16, idesc, (kb | k16) ? 1u : 0u);
+          }
+          umma_commit_pair(bar_empty(s));   // x stage free in both CTAs
+          umma_commit_pair(bar_bempty(t));  // dequantised tiles free in both CTAs
+        }
+        if (ok) { umma_commit_pair(bar_accfull(a)); }
+      }
+    }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------- dequantisers (both CTAs)
+    const int tq = threadIdx.x - 6 * 32;   // 0 .. 255
+    const int t_row = tq >> 1;             // row of this CTA's half of the W tile
+    const int half = tq & 1;               // which 32 of the group's 64 values
+    const uint32_t row_off = (uint32_t)(t_row >> 3) * 1024u + (uint32_t)(t_row & 7) * 128u;
+    const uint32_t sw = (uint32_t)(t_row & 7);
+    const int groups = K >> 6;
+    const uint32_t bfull_leader = map_to_cta(bar0, 0);  // cluster address of the leader's barrier block
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      const int n0 = (tile % tiles_n) * TN + (int)rank * 128;
+      int row = n0 + t_row;
+      row = row < N ? row : N - 1;  // tail rows: any valid scale; their columns are never stored
+      const uint16_t* srow = scales + (int64_t)row * groups;
+      const uint16_t* brow = biases + (int64_t)row * groups;
+      ScaleStream sst(srow, brow, groups);
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % kXStages;
+        const uint32_t ph = (it / kXStages) & 1u;
+        const int t = it % kBTiles;
+        const uint32_t bph = (it / kBTiles) & 1u;
+        float sc, bi;
+        sst.get(kb, sc, bi);
+        if (!warp_wait(bar_cfull(s), ph, (1u << 8) | kRoleDq, abort_flag, &g_qmm_status)) { ok = false; break; }
+        const uint4 c0 = *reinterpret_cast<const uint4*>(base_ptr + L::kOffCode + s * L::kCodeBytes +
+                                                         t_row * (BK / 2) + half * 16);
+        __syncwarp();
+        if (lane == 0) { mbar_arrive(bar_empty(s)); }  // codes are in registers
+
+        const float t128 = 128.0f * sc;
+        const float b128 = bi - t128;
+        const float bb = b128 - bi;
+        const float resid = (bi - (b128 - bb)) + (-t128 - bb);  // two-sum residual of b - 128 s
+        uint32_t o[16];
+        const uint32_t cw[4] = {c0.x, c0.y, c0.z, c0.w};
+        if (resid == 0.0f) {
+          const uint64_t s2 = pack_f32x2(sc, sc), b2 = pack_f32x2(b128, b128);
+#pragma unroll
+          for (int wd = 0; wd < 4; ++wd) { dequant_word_fast(cw[wd], s2, b2, o + 4 * wd); }
+        } else {
+#pragma unroll
+          for (int wd = 0; wd < 4; ++wd) { dequant_word_exact(cw[wd], sc, bi, o + 4 * wd); }
+        }
+
+        if (!warp_wait(bar_bempty(t), bph ^ 1u, (2u << 8) | kRoleDq, abort_flag, &g_qmm_status)) { ok = false; break; }
+        unsigned char* bt = base_ptr + L::kOffB + t * L::kBBytes + row_off;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {  // 16-byte chunk (4*half + c) of the row lands at chunk ^ row%8
+          *reinterpret_cast<uint4*>(bt + ((((uint32_t)(half * 4 + c)) ^ sw) << 4)) =
+              make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+        }
+        fence_proxy_async();  // generic-proxy writes -> visible to the tensor cores' async reads
+        __syncwarp();
+        if (lane == 0) {
+          if (rank == 0) {
+            mbar_arrive(bar_bfull(t));
+          } else {
+            mbar_arrive_cluster(bfull_leader + 8u * (3 * kXStages + t));
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (both CTAs)
+    uint32_t ti = 0;
+    bool ok = true;
+    const bool vec_ok = (N % 8) == 0;
+    const uint32_t accempty_leader = map_to_cta(bar0, 0) + 8u * (3 * kXStages + 2 * kBTiles + 2);
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++ti) {
+      const int m0 = (tile / tiles_n) * TM + (int)rank * 128;
+      const int n0 = (tile % tiles_n) * TN;
+      const int a = ti & 1;
+      const uint32_t aph = (ti >> 1) & 1u;
+      if (!warp_wait(bar_accfull(a), aph, (1u << 8) | kRoleEpi, abort_flag, &g_qmm_status)) { ok = false; break; }
+      tc_fence_after();
+      const int m = m0 + warp * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(a * TN);
+      __nv_bfloat16* yrow = y + (int64_t)m * N + n0;
+#pragma unroll 1
+      for (int c = 0; c < TN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + (uint32_t)(c * 32), r);
+        tmem_ld_wait();
+        const int nc = n0 + c * 32;
+        if (m < M && nc < N) {
+          if (vec_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (nc + v * 8 < N) {
+                uint4 pk;
+                pk.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                pk.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                pk.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                pk.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                *reinterpret_cast<uint4*>(yrow + c * 32 + v * 8) = pk;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (nc + j < N) { yrow[c * 32 + j] = __float2bfloat16_rn(__uint_as_float(r[j])); }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0) {
+          mbar_arrive(bar_accempty(a));
+        } else {
+          mbar_arrive_cluster(accempty_leader + 8u * a);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // nobody leaves while its partner may still read its shared memory or signal it
+  if (warp == 5) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
+}  // namespace two_cta
