@@ -129,26 +129,31 @@ __device__ __forceinline__ void tmem_ld_wait() {
 // fmaf(s, 128 + q, b128) rounds the same real number s q + b once. The two
 // multiply-adds of a nibble pair share one packed f32x2 instruction; s2 / b2
 // hold (s, s) and (b128, b128).
+// One nibble pair (byte J of the even / odd nibble words) -> one packed bf16x2. The PRMT selector
+// and the magic constant are immediates of the instruction, not registers.
+#define VPQ_DEQUANT_PAIR(J, SEL)                                                     \
+  asm("{\n\t"                                                                        \
+      ".reg .b32 fe, fo, ve, vo;\n\t"                                                \
+      ".reg .b64 q2, v2;\n\t"                                                        \
+      "prmt.b32 fe, %1, 0x43000000, " SEL ";\n\t"                                    \
+      "prmt.b32 fo, %2, 0x43000000, " SEL ";\n\t"                                    \
+      "mov.b64 q2, {fe, fo};\n\t"                                                    \
+      "fma.rn.f32x2 v2, %3, q2, %4;\n\t"                                             \
+      "mov.b64 {ve, vo}, v2;\n\t"                                                    \
+      "cvt.rn.bf16x2.f32 %0, vo, ve;\n\t"                                            \
+      "}"                                                                            \
+      : "=r"(out[J])                                                                 \
+      : "r"(e), "r"(o), "l"(s2), "l"(b2))
+
 __device__ __forceinline__ void dequant_word_fast(uint32_t word, uint64_t s2, uint64_t b2, uint32_t* out) {
   const uint32_t e = word & 0x0f0f0f0fu;         // nibbles 0,2,4,6 as bytes
   const uint32_t o = (word >> 4) & 0x0f0f0f0fu;  // nibbles 1,3,5,7 as bytes
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    uint32_t fe, fo;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(fe) : "r"(e), "r"(0x43000000u), "r"(0x7054u + (j << 8)));
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(fo) : "r"(o), "r"(0x43000000u), "r"(0x7054u + (j << 8)));
-    asm("{\n\t"
-        ".reg .b64 q2, v2;\n\t"
-        ".reg .b32 ve, vo;\n\t"
-        "mov.b64 q2, {%1, %2};\n\t"
-        "fma.rn.f32x2 v2, %3, q2, %4;\n\t"
-        "mov.b64 {ve, vo}, v2;\n\t"
-        "cvt.rn.bf16x2.f32 %0, vo, ve;\n\t"
-        "}"
-        : "=r"(out[j])
-        : "r"(fe), "r"(fo), "l"(s2), "l"(b2));
-  }
+  VPQ_DEQUANT_PAIR(0, "0x7054");
+  VPQ_DEQUANT_PAIR(1, "0x7154");
+  VPQ_DEQUANT_PAIR(2, "0x7254");
+  VPQ_DEQUANT_PAIR(3, "0x7354");
 }
+#undef VPQ_DEQUANT_PAIR
 
 __device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
   uint64_t r;

@@ -22,8 +22,8 @@ namespace two_cta {
 
 constexpr int TM = 256;        // tile rows (128 per CTA)
 constexpr int TN = 256;        // tile columns (128 W rows dequantised per CTA)
-constexpr int kXStages = 6;    // x + codes ring
-constexpr int kBTiles = 4;     // dequantised-B ring
+constexpr int kXStages = 5;    // x + codes ring
+constexpr int kBTiles = 6;     // dequantised-B ring
 constexpr int kDqWarps = 8;
 constexpr int kThreads2 = 32 * (kEpiWarps + 2 + kDqWarps);
 
@@ -290,11 +290,12 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const float resid = (bi - (b128 - bb)) + (-t128 - bb);  // two-sum residual of b - 128 s
         uint32_t o[16];
         const uint32_t cw[4] = {c0.x, c0.y, c0.z, c0.w};
-        if (resid == 0.0f) {
+        {
           const uint64_t s2 = pack_f32x2(sc, sc), b2 = pack_f32x2(b128, b128);
 #pragma unroll
           for (int wd = 0; wd < 4; ++wd) { dequant_word_fast(cw[wd], s2, b2, o + 4 * wd); }
-        } else {
+        }
+        if (resid != 0.0f) {  // b - 128 s was not exact for this group: redo it the plain way
 #pragma unroll
           for (int wd = 0; wd < 4; ++wd) { dequant_word_exact(cw[wd], sc, bi, o + 4 * wd); }
         }
