@@ -114,6 +114,22 @@ typedef struct vpq_linear_desc {
 } vpq_linear_desc;
 int vpq_affine_qmv_w4g64_bf16_batch(const vpq_linear_desc* descs_host, int count, void* stream);
 
+/* A list of independent GEMVs run as ONE launch: the kernel walks the row tiles of all problems
+ * back to back, so there is no launch gap and no per-problem ramp-up, and problems that read the
+ * same x (q | k | v, gate | up) stage it once. "Encode once, commit many": the analogue of
+ * encoding a decode step's dispatches into one command buffer and re-committing it,
+ * apple-silicon/metal-compute/command-stream.h:144, generative-models/qwen3/metal-qwen-model.cc:3004-3074.
+ * The GEMVs must be independent of each other (none reads another's y); pointers are captured
+ * at creation, their contents may change between runs. `workspace` is caller-owned device memory
+ * of vpq_qmv_plan_bytes() bytes holding the per-problem descriptors; it must outlive the plan.
+ * vpq_qmv_plan_create copies into it and synchronises `stream`; vpq_qmv_plan_run only launches. */
+typedef struct vpq_qmv_plan_s vpq_qmv_plan;
+size_t vpq_qmv_plan_bytes(const vpq_linear_desc* descs_host, int count);
+int vpq_qmv_plan_create(const vpq_linear_desc* descs_host, int count, void* workspace, size_t bytes,
+                        void* stream, vpq_qmv_plan** out);
+int vpq_qmv_plan_run(const vpq_qmv_plan* plan, void* stream);
+int vpq_qmv_plan_destroy(vpq_qmv_plan* plan);
+
 /* Prefill / DiT GEMM: y[M,N] = x[M,K] @ dequant(W)[N,K]^T. W is dequantised
  * to bf16 tile by tile in shared memory (bit-identical to
  * vpq_affine_dequant_w4g64_bf16), multiplied on the tcgen05 tensor cores with

@@ -298,3 +298,31 @@ def test_qmv_and_qmm_agree_on_small_m(vpq, oracle_mod):
     args = (to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16), to_dev(x, torch.bfloat16))
     yv, ym = vpq.ops.qmv(*args), vpq.ops.qmm(*args)
     assert oracle_mod.err_metrics(f32(ym), f32(yv))["max_rel_rms"] < TOL
+
+
+def test_qmv_plan_equals_single_launches(vpq, oracle_mod):
+    """A plan (all GEMVs in one launch) must give the bytes of the per-GEMV launches: shared x
+    (q|k|v), a different K (down), a K whose scales cannot be TMA boxes (3840), ragged N, M = 2."""
+    shapes = [(4096, 512, 1), (4096, 128, 1), (4096, 136, 1), (12288, 256, 1), (3840, 40, 1),
+              (1024, 33, 2), (4096, 4096, 1)]
+    xs = {}
+    problems, singles = [], []
+    for i, (K, N, M) in enumerate(shapes):
+        codes, s, b = quantized_linear(oracle_mod, N, K, 900 + i)
+        if (K, M) not in xs:
+            xs[(K, M)] = to_dev(synth.activations_bf16(M, K, 950 + K + M), torch.bfloat16)
+        x = xs[(K, M)]
+        dc, ds, db = to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16)
+        y = torch.zeros((M, N), dtype=torch.bfloat16, device=dev())
+        problems.append((dc, ds, db, x, y))
+        singles.append(vpq.ops.qmv(dc, ds, db, x))
+    plan = vpq.ops.QmvPlan(problems)
+    for _ in range(2):          # a plan is re-runnable
+        for p in problems:
+            p[4].zero_()
+        plan.run()
+        torch.cuda.synchronize()
+        for p, want in zip(problems, singles):
+            assert torch.equal(p[4], want)
+    plan.close()
+    assert vpq.ops.device_status() == 0

@@ -25,6 +25,10 @@ SYMBOLS = [
     ("vpq_affine_dequant_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _i64, _i64, _vp]),
     ("vpq_affine_qmv_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     ("vpq_affine_qmv_w4g64_bf16_batch", _i, [_vp, _i, _vp]),
+    ("vpq_qmv_plan_bytes", C.c_size_t, [_vp, _i]),
+    ("vpq_qmv_plan_create", _i, [_vp, _i, _vp, C.c_size_t, _vp, C.POINTER(_vp)]),
+    ("vpq_qmv_plan_run", _i, [_vp, _vp]),
+    ("vpq_qmv_plan_destroy", _i, [_vp]),
     ("vpq_affine_qmm_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     ("vpq_device_status", _i, [_vp, C.POINTER(C.c_uint32)]),
     ("vpq_function_lookup", _vp, [C.c_char_p, C.c_char_p]),

@@ -27,10 +27,17 @@
 //  * x is staged once per CTA in shared memory, already permuted into the
 //    B-fragment order that matches the nibble pairing (k, k+4);
 //  * per row tile: one shuffle, one shared-memory reduction over the 8 warps.
+// One launch can run a whole list of GEMVs (a "plan"): the CTAs walk the concatenated row tiles
+// of all problems, the producer keeps streaming across problem boundaries, and the consumers
+// re-stage x only when the next problem reads a different x. A single GEMV is a one-problem list
+// passed in the kernel parameters.
 // The launch opts into programmatic dependent launch: the producer starts
-// streaming weights before griddepcontrol.wait, so the next GEMV's stream is
+// streaming weights before griddepcontrol.wait, so the next launch's stream is
 // already running while this one drains. Every barrier wait is bounded.
 #include "vpq_sm100.cuh"
+
+#include <cstdlib>
+#include <cstring>
 
 namespace vpq {
 
@@ -86,32 +93,39 @@ __device__ __forceinline__ uint32_t hi_magic(uint32_t v) {
 
 enum : uint32_t { kRoleProducer = 1, kRoleConsumer = 2 };
 
-template <bool SCALES_TMA>
+// One GEMV of a launch. Lives in the kernel parameters (single GEMV) or in caller-provided
+// device memory (plan). Tensor maps need 64-byte alignment.
+struct alignas(64) QmvProblem {
+  CUtensorMap mw, ms, mz;      // packed weights [N, K/8] u32; scales, biases [N, K/64] (valid if scales_tma)
+  const uint16_t* scales;
+  const uint16_t* biases;
+  const uint16_t* x;           // one row of K bf16
+  __nv_bfloat16* y;            // N outputs
+  int K, N;
+  int tile_begin, row_tiles;   // this problem's range in the launch's global list of 16-row tiles
+  int scales_tma;              // scale / bias rows are TMA boxes (pitch and base 16-byte aligned)
+  int pad[3];
+};
+static_assert(sizeof(QmvProblem) % 64 == 0, "problem records are laid out back to back");
+
 __global__ void __launch_bounds__(kThreads, 2)
-affine_qmv_w4g64_kernel(const __grid_constant__ CUtensorMap map_w,
-                        const __grid_constant__ CUtensorMap map_s,
-                        const __grid_constant__ CUtensorMap map_z,
-                        const uint16_t* __restrict__ scales, const uint16_t* __restrict__ biases,
-                        const uint16_t* __restrict__ x, __nv_bfloat16* __restrict__ y, int K, int N,
-                        int stages) {
+affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProblem* __restrict__ list,
+                        int total_tiles, int stages, int cap_kt) {
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t raw = smem_u32(smem_dyn);
   const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled boxes need 1024-byte alignment
   unsigned char* base_ptr = smem_dyn + (base - raw);
-  constexpr int kStageBytes = kStageW + (SCALES_TMA ? kStageSZ : 0);
+  constexpr int kStageBytes = kStageW + kStageSZ;
+  const QmvProblem* probs = list ? list : &single;
 
-  const int KT = ((K + 255) >> 8) * 2;        // k tiles per row, padded to whole 256-k boxes (x is zero there)
-  const int G = K >> 6;                       // groups per row
-  const int NB = (K + 255) >> 8;              // 128-byte boxes per row
-  const int SPT = (NB + kBoxesPerStage - 1) / kBoxesPerStage;  // stages per row tile
-
-  unsigned char* p = base_ptr + (size_t)stages * kStageBytes;
-  uint4* xperm = reinterpret_cast<uint4*>(p);                    // [KT][4 quarters][4 t] x 16 B
-  uint4* zero256 = xperm + (size_t)KT * 16;                      // 320 bytes of zeros
-  float2* xg = reinterpret_cast<float2*>(zero256 + 20);          // [2*KT] per group: surplus, sum of x
-  float* red = reinterpret_cast<float*>(xg + 2 * KT);            // [kRedSlots][kConsWarps][16]
+  unsigned char* p0 = base_ptr + (size_t)stages * kStageBytes;
+  uint4* xperm = reinterpret_cast<uint4*>(p0);                   // [cap_kt][4 quarters][4 t] x 16 B
+  uint4* zero256 = xperm + (size_t)cap_kt * 16;                  // 320 bytes of zeros
+  float2* xg = reinterpret_cast<float2*>(zero256 + 20);          // [2*cap_kt] per group: surplus, sum of x
+  float* red = reinterpret_cast<float*>(xg + 2 * cap_kt);        // [kRedSlots][kConsWarps][16]
   uint32_t* red_cnt = reinterpret_cast<uint32_t*>(red + kRedSlots * kConsWarps * 16);  // [kRedSlots]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(red_cnt + kRedSlots);
+  uint32_t* amax_buf = red_cnt + kRedSlots;                      // [kConsWarps]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(amax_buf + kConsWarps);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * kMaxStages);
   const uint32_t bar0 = smem_u32(bars);
   auto bar_full = [&](int s) { return bar0 + 8u * s; };
@@ -119,8 +133,6 @@ affine_qmv_w4g64_kernel(const __grid_constant__ CUtensorMap map_w,
 
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  const int m = blockIdx.y;
-  const int row_tiles = (N + 15) >> 4;
 
   // Let the next kernel in the stream start its own weight stream now.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -134,6 +146,7 @@ affine_qmv_w4g64_kernel(const __grid_constant__ CUtensorMap map_w,
     for (int i = 0; i < kRedSlots; ++i) { red_cnt[i] = 0; }
     fence_mbar_init();
   }
+  if (threadIdx.x < 20) { zero256[threadIdx.x] = make_uint4(0, 0, 0, 0); }
   __syncthreads();
 
   if (warp == kConsWarps) {
@@ -143,7 +156,19 @@ affine_qmv_w4g64_kernel(const __grid_constant__ CUtensorMap map_w,
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < row_tiles && ok; tile += gridDim.x) {
+      int pi = 0;
+      const QmvProblem* P = probs;
+      int tb = P->tile_begin, rt = P->row_tiles;
+      for (int gt = blockIdx.x; gt < total_tiles && ok; gt += gridDim.x) {
+        while (gt >= tb + rt) {
+          P = probs + (++pi);
+          tb = P->tile_begin;
+          rt = P->row_tiles;
+        }
+        const int tile = gt - tb;
+        const int NB = (P->K + 255) >> 8;                              // 128-byte boxes per row
+        const int SPT = (NB + kBoxesPerStage - 1) / kBoxesPerStage;    // stages per row tile
+        const bool sz_tma = P->scales_tma != 0;
         for (int st = 0; st < SPT; ++st, ++it) {
           const int s = it % stages;
           const uint32_t ph = (it / stages) & 1u;
@@ -153,13 +178,13 @@ affine_qmv_w4g64_kernel(const __grid_constant__ CUtensorMap map_w,
           }
           const int nb = min(kBoxesPerStage, NB - st * kBoxesPerStage);
           const uint32_t dst = base + (uint32_t)s * kStageBytes;
-          mbar_expect_tx(bar_full(s), (uint32_t)nb * kBoxBytes + (SCALES_TMA ? kStageSZ : 0));
+          mbar_expect_tx(bar_full(s), (uint32_t)nb * kBoxBytes + (sz_tma ? kStageSZ : 0));
           for (int b = 0; b < nb; ++b) {
-            tma_load_2d(dst + b * kBoxBytes, &map_w, bar_full(s), (st * kBoxesPerStage + b) * 32, tile * 16);
+            tma_load_2d(dst + b * kBoxBytes, &P->mw, bar_full(s), (st * kBoxesPerStage + b) * 32, tile * 16);
           }
-          if (SCALES_TMA) {
-            tma_load_2d(dst + kStageW, &map_s, bar_full(s), st * 32, tile * 16);
-            tma_load_2d(dst + kStageW + kStageSZ / 2, &map_z, bar_full(s), st * 32, tile * 16);
+          if (sz_tma) {
+            tma_load_2d(dst + kStageW, &P->ms, bar_full(s), st * 32, tile * 16);
+            tma_load_2d(dst + kStageW + kStageSZ / 2, &P->mz, bar_full(s), st * 32, tile * 16);
           }
         }
       }
@@ -183,19 +208,18 @@ affine_qmv_w4g64_kernel(const __grid_constant__ CUtensorMap map_w,
   // x (and y) may be produced / consumed by the previous kernel.
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  // ---- stage x as fp16. The tensor-core operands are fp16: a nibble sits in the low mantissa bits
-  // of 0x6400 (1024 + q) or, one nibble higher, of 0x5400 (64 + q), so no shift is needed for half
-  // of them. x is scaled by a power of two so that its largest magnitude lands in [2^14, 2^15):
-  // every bf16 value within 2^-28 of the maximum is then exact in fp16, and the scale is undone
-  // exactly at the end.
-  const uint16_t* xr = x + (int64_t)m * K;
-  const int chunks = KT * 16;  // 16-byte chunks of the padded x
-  // Each thread keeps up to kXRegs chunks of x in registers between the two passes (find the
-  // maximum, then convert), so x is read once and all of a thread's loads are in flight together.
-  // Longer rows (K > 8 * 256 * kXRegs) re-read the remainder in the second pass.
-  constexpr int kXRegs = 8;
-  uint4 xin[kXRegs];
-  {
+  // ---- staging of one x vector as fp16 (called by all consumer warps together).
+  // The tensor-core operands are fp16: a nibble sits in the low mantissa bits of 0x6400 (1024 + q)
+  // or, one nibble higher, of 0x5400 (64 + q), so no shift is needed for half of them. x is scaled
+  // by a power of two so that its largest magnitude lands in [2^14, 2^15): every bf16 value within
+  // 2^-28 of the maximum is then exact in fp16, and the scale is undone exactly at the end.
+  // 8 consecutive values (x0..x7) become the four B-fragment registers (x0,x4) (x1,x5) (x2,x6)
+  // (x3,x7). Per group of 64: xg[].x = 1024 * sum(even k) + 64 * sum(odd k), the surplus the
+  // magic constants add to the accumulator; xg[].y = sum of all 64, for the bias term.
+  constexpr int kXRegs = 8;  // chunks a thread keeps in registers between the two passes
+  auto stage_x = [&](const uint16_t* xr, int K, int KT) -> float {
+    const int chunks = KT * 16;  // 16-byte chunks of the padded x
+    uint4 xin[kXRegs];
     uint32_t amax = 0;  // largest |x| as bf16 bits (ordering of magnitudes == ordering of bit patterns)
 #pragma unroll
     for (int r = 0; r < kXRegs; ++r) {
@@ -222,71 +246,64 @@ affine_qmv_w4g64_kernel(const __grid_constant__ CUtensorMap map_w,
       }
     }
     amax = __reduce_max_sync(0xffffffffu, amax);
-    if (lane == 0) { red_cnt[warp] = amax; }  // borrowed until the barriers below; cleared after
-  }
-  asm volatile("bar.sync 1, %0;" ::"n"(kConsThreads) : "memory");  // consumers only
-  float x_scale, x_unscale;
-  {
-    uint32_t amax = 0;
+    // the barrier also orders the previous problem's last reads of xperm / xg before the writes below
+    if (lane == 0) { amax_buf[warp] = amax; }
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsThreads) : "memory");  // consumers only
+    amax = 0;
 #pragma unroll
-    for (int ww = 0; ww < kConsWarps; ++ww) { amax = max(amax, red_cnt[ww]); }
+    for (int ww = 0; ww < kConsWarps; ++ww) { amax = max(amax, amax_buf[ww]); }
     int e = (int)(amax >> 7);            // biased exponent of the largest magnitude
     e = min(max(e, 16), 240);            // all-zero / denormal / huge x: keep both factors normal
-    x_scale = __uint_as_float((uint32_t)(268 - e) << 23);    // 2^(141 - e): max |x| -> [2^14, 2^15)
-    x_unscale = __uint_as_float((uint32_t)(e - 14) << 23);   // its exact inverse
-  }
-  // 8 consecutive values (x0..x7) become the four B-fragment registers (x0,x4) (x1,x5) (x2,x6)
-  // (x3,x7). Per group of 64: xg[].x = 1024 * sum(even k) + 64 * sum(odd k), the surplus the
-  // magic constants add to the accumulator; xg[].y = sum of all 64, for the bias term.
-  auto convert_chunk = [&](int i, const uint4& in) {  // called by whole warps: shuffles inside
-    const bool live = i < chunks;
-    const uint32_t v[4] = {in.x, in.y, in.z, in.w};
-    uint32_t hb[4];
-    float se = 0.0f, so = 0.0f;
+    const float x_scale = __uint_as_float((uint32_t)(268 - e) << 23);  // 2^(141 - e): max |x| -> [2^14, 2^15)
+    const float x_unscale = __uint_as_float((uint32_t)(e - 14) << 23); // its exact inverse
+    auto convert_chunk = [&](int i, const uint4& in) {  // called by whole warps: shuffles inside
+      const bool live = i < chunks;
+      const uint32_t v[4] = {in.x, in.y, in.z, in.w};
+      uint32_t hb[4];
+      float se = 0.0f, so = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const __half2 h = __floats2half2_rn(__uint_as_float(v[j] << 16) * x_scale,
-                                          __uint_as_float(v[j] & 0xffff0000u) * x_scale);
-      const float2 f = __half22float2(h);  // what the tensor core will see
-      se += f.x;
-      so += f.y;
-      hb[j] = *reinterpret_cast<const uint32_t*>(&h);
-    }
-    uint4 out;
-    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(out.x) : "r"(hb[0]), "r"(hb[2]));
-    asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(out.y) : "r"(hb[0]), "r"(hb[2]));
-    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(out.z) : "r"(hb[1]), "r"(hb[3]));
-    asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(out.w) : "r"(hb[1]), "r"(hb[3]));
-    const int kt = i >> 4, tt = (i >> 2) & 3, q = i & 3;
-    if (live) { xperm[(kt * 4 + q) * 4 + tt] = out; }
+      for (int j = 0; j < 4; ++j) {
+        const __half2 h = __floats2half2_rn(__uint_as_float(v[j] << 16) * x_scale,
+                                            __uint_as_float(v[j] & 0xffff0000u) * x_scale);
+        const float2 f = __half22float2(h);  // what the tensor core will see
+        se += f.x;
+        so += f.y;
+        hb[j] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      uint4 out;
+      asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(out.x) : "r"(hb[0]), "r"(hb[2]));
+      asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(out.y) : "r"(hb[0]), "r"(hb[2]));
+      asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(out.z) : "r"(hb[1]), "r"(hb[3]));
+      asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(out.w) : "r"(hb[1]), "r"(hb[3]));
+      const int kt = i >> 4, tt = (i >> 2) & 3, q = i & 3;
+      if (live) { xperm[(kt * 4 + q) * 4 + tt] = out; }
 #pragma unroll
-    for (int off = 1; off < 8; off <<= 1) {
-      se += __shfl_xor_sync(0xffffffffu, se, off);
-      so += __shfl_xor_sync(0xffffffffu, so, off);
+      for (int off = 1; off < 8; off <<= 1) {
+        se += __shfl_xor_sync(0xffffffffu, se, off);
+        so += __shfl_xor_sync(0xffffffffu, so, off);
+      }
+      if (live && (i & 7) == 0) { xg[i >> 3] = make_float2(__fmaf_rn(1024.0f, se, 64.0f * so), se + so); }
+    };
+#pragma unroll
+    for (int r = 0; r < kXRegs; ++r) {
+      const int i = threadIdx.x + r * kConsThreads;
+      if (i - lane < chunks) { convert_chunk(i, xin[r]); }  // warp-uniform
     }
-    if (live && (i & 7) == 0) { xg[i >> 3] = make_float2(__fmaf_rn(1024.0f, se, 64.0f * so), se + so); }
+    for (int i = threadIdx.x + kXRegs * kConsThreads; i - lane < chunks; i += kConsThreads) {
+      uint4 in = make_uint4(0, 0, 0, 0);
+      if (i * 8 < K) { in = *reinterpret_cast<const uint4*>(xr + i * 8); }
+      convert_chunk(i, in);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsThreads) : "memory");
+    return x_unscale;
   };
-#pragma unroll
-  for (int r = 0; r < kXRegs; ++r) {
-    const int i = threadIdx.x + r * kConsThreads;
-    if (i - lane < chunks) { convert_chunk(i, xin[r]); }  // warp-uniform
-  }
-  for (int i = threadIdx.x + kXRegs * kConsThreads; i - lane < chunks; i += kConsThreads) {
-    uint4 in = make_uint4(0, 0, 0, 0);
-    if (i * 8 < K) { in = *reinterpret_cast<const uint4*>(xr + i * 8); }
-    convert_chunk(i, in);
-  }
-  if (threadIdx.x < 20) { zero256[threadIdx.x] = make_uint4(0, 0, 0, 0); }
-  asm volatile("bar.sync 1, %0;" ::"n"(kConsThreads) : "memory");
-  if (threadIdx.x < kRedSlots) { red_cnt[threadIdx.x] = 0; }  // ordered before its first use by the tile loop's waits
-  asm volatile("bar.sync 1, %0;" ::"n"(kConsThreads) : "memory");
 
   // Even accumulator columns see the first group of a k tile (chunks t = 0, 1),
   // odd columns the second (t = 2, 3); column c is supplied by the lanes with g == c.
-  // The other lanes read zeros from a block laid out like one k tile of xperm.
-  const bool real = ((g & 1) == 0) ? (t < 2) : (t >= 2);
+  // The other lanes read zeros from a block laid out like one k tile of xperm
   // (+4: quarter q of the zero block sits in the banks quarter q+1 of the data uses, so the two
-  // halves of a warp never collide)
+  // halves of a warp never collide).
+  const bool real = ((g & 1) == 0) ? (t < 2) : (t >= 2);
   const uint4* xb_base = real ? xperm + t : zero256 + 4;
   const int xb_kt = real ? 16 : 0;
 
@@ -299,7 +316,45 @@ affine_qmv_w4g64_kernel(const __grid_constant__ CUtensorMap map_w,
   uint32_t tile_seq = 0, ph = 0;
   int s = 0;
   bool ok = true;
-  for (int tile = blockIdx.x; tile < row_tiles && ok; tile += gridDim.x, ++tile_seq) {
+  int pi = 0;
+  const QmvProblem* P = probs;
+  int tb = P->tile_begin, rt = P->row_tiles;
+  const uint16_t* staged_x = nullptr;
+  int staged_K = -1;
+  float x_unscale = 1.0f;
+  // per-problem values, refreshed when the walk enters a new problem
+  int K = 0, N = 0, G = 0, KT = 0, SPT = 0;
+  bool sz_tma = false;
+  const uint16_t* scales = nullptr;
+  const uint16_t* biases = nullptr;
+  __nv_bfloat16* y = nullptr;
+  bool fresh = true;
+  for (int gt = blockIdx.x; gt < total_tiles && ok; gt += gridDim.x, ++tile_seq) {
+    while (gt >= tb + rt) {
+      P = probs + (++pi);
+      tb = P->tile_begin;
+      rt = P->row_tiles;
+      fresh = true;
+    }
+    if (fresh) {
+      fresh = false;
+      K = P->K;
+      N = P->N;
+      G = K >> 6;
+      KT = ((K + 255) >> 8) * 2;  // k tiles per row, padded to whole 256-k boxes (x is zero there)
+      SPT = (((K + 255) >> 8) + kBoxesPerStage - 1) / kBoxesPerStage;
+      sz_tma = P->scales_tma != 0;
+      scales = P->scales;
+      biases = P->biases;
+      y = P->y;
+      const uint16_t* xr = P->x;
+      if (xr != staged_x || K != staged_K) {  // q|k|v or gate|up of a layer share one staging
+        x_unscale = stage_x(xr, K, KT);
+        staged_x = xr;
+        staged_K = K;
+      }
+    }
+    const int tile = gt - tb;
     float res = 0.0f;
     for (int st = 0; st < SPT; ++st) {
       if (!warp_wait(bar_full(s), ph, (1u << 8) | kRoleConsumer, abort_flag, &g_qmv_status)) {
@@ -316,7 +371,7 @@ affine_qmv_w4g64_kernel(const __grid_constant__ CUtensorMap map_w,
         const uint4 ra1 = *reinterpret_cast<const uint4*>(box + off_h1);
         const uint4 rb1 = *reinterpret_cast<const uint4*>(box + off_h1 + 1024);
         uint2 sw = make_uint2(0, 0), zw = make_uint2(0, 0);
-        if (SCALES_TMA) {
+        if (sz_tma) {
           sw = *reinterpret_cast<const uint2*>(sb + sz_off);
           zw = *reinterpret_cast<const uint2*>(sb + sz_off + kStageSZ / 2);
         }
@@ -352,7 +407,7 @@ affine_qmv_w4g64_kernel(const __grid_constant__ CUtensorMap map_w,
         const float2 xs0 = xg[2 * kt0 + par];
         const float2 xs1 = xg[2 * kt1 + par];
         uint32_t s0, z0, s1, z1;
-        if (SCALES_TMA) {
+        if (sz_tma) {
           asm("prmt.b32 %0, %1, %2, %3;" : "=r"(s0) : "r"(sw.x), "r"(0u), "r"(sel));
           asm("prmt.b32 %0, %1, %2, %3;" : "=r"(z0) : "r"(zw.x), "r"(0u), "r"(sel));
           asm("prmt.b32 %0, %1, %2, %3;" : "=r"(s1) : "r"(sw.y), "r"(0u), "r"(sel));
@@ -401,7 +456,7 @@ affine_qmv_w4g64_kernel(const __grid_constant__ CUtensorMap map_w,
           v += *reinterpret_cast<volatile float*>(&red[(slot * kConsWarps + ww) * 16 + lane]);
         }
         const int row = (tile << 4) + lane;
-        if (row < N) { y[(int64_t)m * N + row] = __float2bfloat16_rn(v * x_unscale); }
+        if (row < N) { y[row] = __float2bfloat16_rn(v * x_unscale); }
       }
       __syncwarp();
       if (lane == 0) { red_cnt[slot] = 0; }
@@ -409,71 +464,95 @@ affine_qmv_w4g64_kernel(const __grid_constant__ CUtensorMap map_w,
   }
 }
 
-template <bool SCALES_TMA>
-int launch_qmv_t(const CUtensorMap& mw, const CUtensorMap& ms, const CUtensorMap& mz,
-                 const uint16_t* scales, const uint16_t* biases, const uint16_t* x, __nv_bfloat16* y,
-                 int K, int N, int M, cudaStream_t st) {
-  const int KT = ((K + 255) / 256) * 2;  // as in the kernel: k tiles padded to whole 256-k boxes
-  const size_t stage_bytes = kStageW + (SCALES_TMA ? kStageSZ : 0);
-  const size_t fixed = 1024 /*alignment slack*/ + (size_t)KT * 256 + 320 + (size_t)2 * KT * 8 +
-                       kRedSlots * kConsWarps * 16 * 4 + kRedSlots * 4 + 2 * kMaxStages * 8 + 16;
+// ------------------------------------------------------------------ host side
+struct LaunchShape {
+  int stages;
+  size_t smem;
+};
+
+LaunchShape shape_for(int cap_kt) {
+  const size_t stage_bytes = kStageW + kStageSZ;
+  const size_t fixed = 1024 /*alignment slack*/ + (size_t)cap_kt * 256 + 320 + (size_t)2 * cap_kt * 8 +
+                       kRedSlots * kConsWarps * 16 * 4 + kRedSlots * 4 + kConsWarps * 4 +
+                       2 * kMaxStages * 8 + 16;
   const size_t budget = 112 * 1024;  // two CTAs per SM
   int stages = fixed + 2 * stage_bytes <= budget ? (int)((budget - fixed) / stage_bytes) : 2;
   if (stages > kMaxStages) { stages = kMaxStages; }
-  const int NB = (K + 255) / 256;
-  const int SPT = (NB + kBoxesPerStage - 1) / kBoxesPerStage;
-  (void)SPT;
-  const size_t smem = fixed + (size_t)stages * stage_bytes;
-  auto kern = affine_qmv_w4g64_kernel<SCALES_TMA>;
-  VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  const int row_tiles = (N + 15) / 16;
-  const int cap = 2 * num_sms();
-  const int ctas = row_tiles < cap ? row_tiles : cap;
+  return {stages, fixed + (size_t)stages * stage_bytes};
+}
 
+int fill_problem(QmvProblem* p, const uint32_t* w, const uint16_t* scales, const uint16_t* biases,
+                 const uint16_t* x, __nv_bfloat16* y, int K, int N, int tile_begin) {
+  std::memset(p, 0, sizeof(*p));
+  if (int rc = make_map_2d(&p->mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w, (uint64_t)(K / 8), (uint64_t)N, 32,
+                           16, CU_TENSOR_MAP_SWIZZLE_128B, "w")) {
+    return rc;
+  }
+  // The scale / bias rows can be TMA boxes only if their pitch and base are multiples of 16 bytes.
+  p->scales_tma = ((K % 512) == 0 && aligned16(scales) && aligned16(biases)) ? 1 : 0;
+  if (p->scales_tma) {
+    const int G = K / 64;
+    if (int rc = make_map_2d(&p->ms, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, (uint64_t)G, (uint64_t)N, 32,
+                             16, CU_TENSOR_MAP_SWIZZLE_NONE, "scales")) {
+      return rc;
+    }
+    if (int rc = make_map_2d(&p->mz, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, biases, (uint64_t)G, (uint64_t)N, 32,
+                             16, CU_TENSOR_MAP_SWIZZLE_NONE, "biases")) {
+      return rc;
+    }
+  }
+  p->scales = scales;
+  p->biases = biases;
+  p->x = x;
+  p->y = y;
+  p->K = K;
+  p->N = N;
+  p->tile_begin = tile_begin;
+  p->row_tiles = (N + 15) / 16;
+  return VPQ_OK;
+}
+
+int launch_list(const QmvProblem& single, const QmvProblem* list, int total_tiles, int cap_kt,
+                cudaStream_t st) {
+  const LaunchShape ls = shape_for(cap_kt);
+  auto kern = affine_qmv_w4g64_kernel;
+  VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ls.smem));
+  const int cap = 2 * num_sms();
+  const int ctas = total_tiles < cap ? total_tiles : cap;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)ctas, (unsigned)M, 1);
+  cfg.gridDim = dim3((unsigned)ctas, 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = smem;
+  cfg.dynamicSmemBytes = ls.smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  VPQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, mw, ms, mz, scales, biases, x, y, K, N, stages));
+  VPQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, single, list, total_tiles, ls.stages, cap_kt));
   return VPQ_OK;
 }
 
-int launch_qmv(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const uint16_t* x,
-               __nv_bfloat16* y, int K, int N, int M, cudaStream_t st) {
-  CUtensorMap mw, ms, mz;
-  if (int rc = make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w, (uint64_t)(K / 8), (uint64_t)N, 32,
-                           16, CU_TENSOR_MAP_SWIZZLE_128B, "w")) {
-    return rc;
+int check_qmv_args(const char* who, const void* w, const void* scales, const void* biases, const void* x,
+                   const void* y, int64_t K, int64_t N, int64_t M) {
+  if (!w || !scales || !biases || !x || !y) { return fail(VPQ_ERR_INVALID_ARG, "%s: null pointer", who); }
+  if (K <= 0 || N <= 0 || M <= 0 || (K % 64) != 0) {
+    return fail(VPQ_ERR_INVALID_ARG, "%s: need K>0, N>0, M>0, K%%64==0 (K=%lld N=%lld M=%lld)", who,
+                (long long)K, (long long)N, (long long)M);
   }
-  // The scale / bias rows can be TMA boxes only if their pitch is a multiple of 16 bytes.
-  const bool scales_tma = (K % 512) == 0 && aligned16(scales) && aligned16(biases);
-  if (scales_tma) {
-    const int G = K / 64;
-    if (int rc = make_map_2d(&ms, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, (uint64_t)G, (uint64_t)N, 32,
-                             16, CU_TENSOR_MAP_SWIZZLE_NONE, "scales")) {
-      return rc;
-    }
-    if (int rc = make_map_2d(&mz, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, biases, (uint64_t)G, (uint64_t)N, 32,
-                             16, CU_TENSOR_MAP_SWIZZLE_NONE, "biases")) {
-      return rc;
-    }
-    return launch_qmv_t<true>(mw, ms, mz, scales, biases, x, y, K, N, M, st);
+  if (K > 32768 || N > (1 << 30) || M > 65535) {
+    return fail(VPQ_ERR_UNSUPPORTED, "%s: K<=32768, M<=65535 supported (K=%lld M=%lld)", who, (long long)K,
+                (long long)M);
   }
-  ms = mw;
-  mz = mw;
-  return launch_qmv_t<false>(mw, ms, mz, scales, biases, x, y, K, N, M, st);
+  if (!aligned16(w) || !aligned16(x) || (reinterpret_cast<uintptr_t>(scales) & 1) ||
+      (reinterpret_cast<uintptr_t>(biases) & 1) || (reinterpret_cast<uintptr_t>(y) & 1)) {
+    return fail(VPQ_ERR_ALIGNMENT, "%s: w and x must be 16-byte aligned", who);
+  }
+  return VPQ_OK;
 }
 
 }  // namespace
-}  // namespace vpq
 
-namespace vpq {
 int qmv_status_read(cudaStream_t st, uint32_t* out) {
   uint32_t v = 0;
   VPQ_CUDA_OK(cudaMemcpyFromSymbolAsync(&v, g_qmv_status, sizeof(v), 0, cudaMemcpyDeviceToHost, st));
@@ -490,32 +569,31 @@ int qmv_status_read(cudaStream_t st, uint32_t* out) {
 
 using namespace vpq;
 
+struct vpq_qmv_plan_s {
+  const QmvProblem* list_dev;
+  int count;        // problems (one per GEMV row)
+  int total_tiles;
+  int cap_kt;
+};
+
 extern "C" int vpq_affine_qmv_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
                                          const void* x, void* y, int64_t K, int64_t N, int64_t M,
                                          void* stream) {
   clear_error();
-  if (!w || !scales || !biases || !x || !y) {
-    return fail(VPQ_ERR_INVALID_ARG, "affine_qmv_w4g64: null pointer");
-  }
-  if (K <= 0 || N <= 0 || M <= 0 || (K % 64) != 0) {
-    return fail(VPQ_ERR_INVALID_ARG, "affine_qmv_w4g64: need K>0, N>0, M>0, K%%64==0 (K=%lld N=%lld M=%lld)",
-                (long long)K, (long long)N, (long long)M);
-  }
-  if (K > 32768 || N > (1 << 30) || M > 65535) {
-    return fail(VPQ_ERR_UNSUPPORTED, "affine_qmv_w4g64: K<=32768, M<=65535 supported (K=%lld M=%lld)",
-                (long long)K, (long long)M);
-  }
-  if (!aligned16(w) || !aligned16(x) || (reinterpret_cast<uintptr_t>(scales) & 1) ||
-      (reinterpret_cast<uintptr_t>(biases) & 1) || (reinterpret_cast<uintptr_t>(y) & 1)) {
-    return fail(VPQ_ERR_ALIGNMENT, "affine_qmv_w4g64: w and x must be 16-byte aligned");
-  }
+  if (int rc = check_qmv_args("affine_qmv_w4g64", w, scales, biases, x, y, K, N, M)) { return rc; }
   if (int rc = require_sm100()) { return rc; }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const uint16_t* sc = static_cast<const uint16_t*>(scales);
-  const uint16_t* bi = static_cast<const uint16_t*>(biases);
-  const uint16_t* xx = static_cast<const uint16_t*>(x);
-  __nv_bfloat16* yy = static_cast<__nv_bfloat16*>(y);
-  return launch_qmv(w, sc, bi, xx, yy, (int)K, (int)N, (int)M, st);
+  const int cap_kt = (int)((K + 255) / 256) * 2;
+  for (int64_t m = 0; m < M; ++m) {  // every row streams the weight again, as in the reference
+    QmvProblem p;
+    if (int rc = fill_problem(&p, w, static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases),
+                              static_cast<const uint16_t*>(x) + m * K, static_cast<__nv_bfloat16*>(y) + m * N,
+                              (int)K, (int)N, 0)) {
+      return rc;
+    }
+    if (int rc = launch_list(p, nullptr, p.row_tiles, cap_kt, st)) { return rc; }
+  }
+  return VPQ_OK;
 }
 
 extern "C" int vpq_affine_qmv_w4g64_bf16_batch(const vpq_linear_desc* d, int count, void* stream) {
@@ -527,5 +605,81 @@ extern "C" int vpq_affine_qmv_w4g64_bf16_batch(const vpq_linear_desc* d, int cou
       return rc;
     }
   }
+  return VPQ_OK;
+}
+
+extern "C" size_t vpq_qmv_plan_bytes(const vpq_linear_desc* d, int count) {
+  if (!d || count <= 0) { return 0; }
+  size_t rows = 0;
+  for (int i = 0; i < count; ++i) { rows += d[i].M > 0 ? (size_t)d[i].M : 0; }
+  return rows * sizeof(QmvProblem) + 64;
+}
+
+extern "C" int vpq_qmv_plan_create(const vpq_linear_desc* d, int count, void* workspace, size_t bytes,
+                                   void* stream, vpq_qmv_plan** out) {
+  clear_error();
+  if (!d || count <= 0 || !workspace || !out) {
+    return fail(VPQ_ERR_INVALID_ARG, "qmv_plan_create: null or empty arguments");
+  }
+  if (bytes < vpq_qmv_plan_bytes(d, count)) {
+    return fail(VPQ_ERR_INVALID_ARG, "qmv_plan_create: workspace of %zu bytes, %zu needed", bytes,
+                vpq_qmv_plan_bytes(d, count));
+  }
+  for (int i = 0; i < count; ++i) {
+    if (int rc = check_qmv_args("qmv_plan_create", d[i].w, d[i].scales, d[i].biases, d[i].x, d[i].y,
+                                d[i].K, d[i].N, d[i].M)) {
+      return rc;
+    }
+  }
+  if (int rc = require_sm100()) { return rc; }
+  size_t rows = 0;
+  for (int i = 0; i < count; ++i) { rows += (size_t)d[i].M; }
+  QmvProblem* host = static_cast<QmvProblem*>(std::aligned_alloc(64, rows * sizeof(QmvProblem)));
+  if (!host) { return fail(VPQ_ERR_INVALID_ARG, "qmv_plan_create: out of host memory"); }
+  int tiles = 0, cap_kt = 0;
+  size_t r = 0;
+  for (int i = 0; i < count; ++i) {
+    for (int64_t m = 0; m < d[i].M; ++m, ++r) {
+      const int rc = fill_problem(&host[r], d[i].w, static_cast<const uint16_t*>(d[i].scales),
+                                  static_cast<const uint16_t*>(d[i].biases),
+                                  static_cast<const uint16_t*>(d[i].x) + m * d[i].K,
+                                  static_cast<__nv_bfloat16*>(d[i].y) + m * d[i].N, (int)d[i].K, (int)d[i].N,
+                                  tiles);
+      if (rc) {
+        std::free(host);
+        return rc;
+      }
+      tiles += host[r].row_tiles;
+      const int kt = (int)((d[i].K + 255) / 256) * 2;
+      cap_kt = kt > cap_kt ? kt : cap_kt;
+    }
+  }
+  const uintptr_t dev = (reinterpret_cast<uintptr_t>(workspace) + 63) & ~(uintptr_t)63;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(reinterpret_cast<void*>(dev), host, rows * sizeof(QmvProblem),
+                                  cudaMemcpyHostToDevice, st);
+  if (e == cudaSuccess) { e = cudaStreamSynchronize(st); }
+  std::free(host);
+  if (e != cudaSuccess) { return fail(VPQ_ERR_CUDA, "qmv_plan_create: copy failed: %s", cudaGetErrorString(e)); }
+  vpq_qmv_plan* plan = new vpq_qmv_plan_s();
+  plan->list_dev = reinterpret_cast<const QmvProblem*>(dev);
+  plan->count = (int)rows;
+  plan->total_tiles = tiles;
+  plan->cap_kt = cap_kt;
+  *out = plan;
+  return VPQ_OK;
+}
+
+extern "C" int vpq_qmv_plan_run(const vpq_qmv_plan* plan, void* stream) {
+  clear_error();
+  if (!plan) { return fail(VPQ_ERR_INVALID_ARG, "qmv_plan_run: null plan"); }
+  if (int rc = require_sm100()) { return rc; }
+  QmvProblem unused;
+  std::memset(&unused, 0, sizeof(unused));
+  return launch_list(unused, plan->list_dev, plan->total_tiles, plan->cap_kt, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int vpq_qmv_plan_destroy(vpq_qmv_plan* plan) {
+  delete plan;
   return VPQ_OK;
 }

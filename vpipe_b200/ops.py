@@ -92,6 +92,29 @@ def qmv_batch(descs, stream=None) -> None:
     check(lib().vpq_affine_qmv_w4g64_bf16_batch(descs, len(descs), _stream(stream)))
 
 
+class QmvPlan:
+    """A list of independent GEMVs run as one launch (vpq_qmv_plan_*). Holds the device workspace."""
+
+    def __init__(self, problems, stream=None):
+        self.descs = qmv_set(problems)
+        self._keep = problems            # the plan captures pointers: keep the tensors alive
+        dev = problems[0][0].device
+        n = lib().vpq_qmv_plan_bytes(self.descs, len(self.descs))
+        self.workspace = torch.empty(n, dtype=torch.uint8, device=dev)
+        self.handle = C.c_void_p()
+        with torch.cuda.device(dev):
+            check(lib().vpq_qmv_plan_create(self.descs, len(self.descs), self.workspace.data_ptr(), n,
+                                            _stream(stream), C.byref(self.handle)))
+
+    def run(self, stream=None) -> None:
+        check(lib().vpq_qmv_plan_run(self.handle, _stream(stream)))
+
+    def close(self) -> None:
+        if self.handle:
+            lib().vpq_qmv_plan_destroy(self.handle)
+            self.handle = None
+
+
 def qmm(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
     N, Kw = codes.shape
     K = Kw * 8
