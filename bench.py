@@ -6,8 +6,9 @@
 
 Default (what the headline metric is quoted on): the decode-layer QMV set of an
 8B Qwen3-style decoder at batch 1 -- q, k, v, gate, up, down at M = 1 -- for all
-36 layers with distinct weights (3.57 GB, larger than L2, so every launch
-streams from HBM). One step = one pass over the 36 layers = 216 GEMV launches.
+36 layers with distinct weights (3.57 GB, larger than L2, so everything
+streams from HBM). One step = one pass over the 36 layers = 216 GEMVs, run as one
+plan launch (vpq_qmv_plan_run); --no-plan replays 216 separate launches as a graph.
 `value` is algorithmic GB/s with everything resident in HBM; `e2e` is the same
 pass driven through the C ABI with the step's activations copied from pinned
 host memory and the result read back, inside the timed region. The same JSON
