@@ -331,14 +331,17 @@ def bench_qmm(torch, dist, ops, synth, args, rank, world, dev, pk, key, comm):
         if world == 1:
             y = torch.empty((M, p.N), dtype=torch.bfloat16, device=dev)
             fn = lambda: ops.qmm(codes, s, b, x, out=y)  # noqa: E731
-        else:
+        elif args.nccl_gather or M <= 128:
             y = torch.empty((world, M, ns), dtype=torch.bfloat16, device=dev)
             fn = lambda: comm.qmm(codes, s, b, x, y, None, args.m_chunks)  # noqa: E731
+        else:   # fused: the epilogue stores into every rank's row-major y; no collective
+            y, y_ptr = comm.alloc_symmetric((M, p.N), torch.bfloat16)
+            fn = lambda: comm.qmm_fused(codes, s, b, x, y_ptr)  # noqa: E731
         t = timed(torch, fn, steps, 3, barrier)
         t = max_over_ranks(torch, dist, world, t, dev) / steps
         rec = {"name": p.name, "K": p.K, "N": p.N, "ms": t * 1e3, "tflops": flops / t / 1e12}
-        if world > 1:   # compute alone, for the split between GEMM and all-gather
-            ymine = y[rank]
+        if world > 1:   # compute alone, for the split between GEMM and the exchange
+            ymine = torch.empty((M, ns), dtype=torch.bfloat16, device=dev)
             tc = timed(torch, lambda: ops.qmm(codes, s, b, x, out=ymine), steps, 2, barrier)
             rec["gemm_only_ms"] = max_over_ranks(torch, dist, world, tc, dev) / steps * 1e3
             rec["gather_bytes_per_gpu"] = (world - 1) * M * ns * 2
@@ -397,6 +400,8 @@ def main():
     ap.add_argument("--m-chunks", dest="m_chunks", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-plan", action="store_true", help="QMV set as 216 graph-replayed launches")
+    ap.add_argument("--nccl-gather", action="store_true",
+                    help="N > 1: GEMM then NCCL all-gather instead of the fused peer-store epilogue")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, world, local = dist_env(args)
@@ -456,7 +461,8 @@ def main():
             "dtype": "int4*bf16->f32", "data": "synthetic",
             "config": {"workload": f"{key} {synth.CONFIGS[key].what}", "M": synth.CONFIGS[key].M,
                        "l2": "x + y of every shape exceed L2", "m_chunks": args.m_chunks,
-                       "parallelism": f"column-split x{world} + NCCL all-gather" if world > 1 else "1 GPU"},
+                       "parallelism": (f"column-split x{world}, " + ("GEMM + NCCL all-gather" if args.nccl_gather else
+                                        "fused peer-store epilogue over NVLink")) if world > 1 else "1 GPU"},
             "roofline": qmm.get("roofline"), "clocks": clocks, "shapes": qmm["shapes"],
             "gpu_launches": len(qmm["shapes"]) * max(3, min(args.steps, 10)),
         }

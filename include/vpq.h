@@ -204,6 +204,19 @@ int vpq_affine_qmm_w4g64_bf16_nsplit(vpq_comm* comm,
                                      int64_t K, int64_t N, int64_t M, int m_chunks,
                                      void* stream);
 
+/* Fused form: no separate collective. y lives in a symmetric buffer that every rank has mapped
+ * (CUDA IPC, one process per GPU); each rank's GEMM epilogue stores its column block straight
+ * into row-major y[M, N] of EVERY rank with ordinary stores over NVLink, and a small flag
+ * barrier over the same mapping follows on the stream. vpq_comm_alloc_symmetric is collective
+ * (all ranks, same order) and is the one place this library allocates device memory; it owns
+ * the buffer until vpq_comm_free_symmetric / vpq_comm_destroy. Needs M > 128, N % (8*world) == 0. */
+int vpq_comm_alloc_symmetric(vpq_comm* comm, size_t bytes, void** local_ptr);
+int vpq_comm_free_symmetric(vpq_comm* comm, void* local_ptr);
+int vpq_affine_qmm_w4g64_bf16_nsplit_fused(vpq_comm* comm, const uint32_t* w_shard,
+                                           const void* scales_shard, const void* biases_shard,
+                                           const void* x, void* y_sym, int64_t K, int64_t N, int64_t M,
+                                           void* stream);
+
 #ifdef __cplusplus
 }
 #endif

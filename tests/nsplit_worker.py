@@ -40,6 +40,28 @@ def main():
         ok = ok and good
         if rank == 0:
             print(f"nsplit world={world} M={M} K={K} N={N} chunks={chunks}: {'ok' if good else 'MISMATCH'}", flush=True)
+    # fused form: no collective; every rank's epilogue stores into every rank's row-major y
+    for (M, K, N) in [(512, 1024, 1024), (1000, 2048, 2048), (4096, 4096, 12288)]:
+        g = torch.Generator(device=dev).manual_seed(4321 + N)
+        w = (torch.randn((N, K), generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        x = torch.randn((M, K), generator=g, device=dev).to(torch.bfloat16)
+        codes, s16, b16 = ops.quantize(w)
+        s, b = ops.scales_to_bf16(s16), ops.scales_to_bf16(b16)
+        full = ops.qmm(codes, s, b, x)
+        lo, hi = shard.shard_rows(N, world, rank)
+        cs, ss, bs = codes[lo:hi].contiguous(), s[lo:hi].contiguous(), b[lo:hi].contiguous()
+        y_sym, y_ptr = comm.alloc_symmetric((M, N), torch.bfloat16)
+        good = True
+        for _ in range(2):      # twice: the barrier epoch advances
+            y_sym.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            comm.qmm_fused(cs, ss, bs, x, y_ptr)
+            torch.cuda.synchronize()
+            good = good and torch.equal(y_sym, full)
+        ok = ok and good
+        if rank == 0:
+            print(f"nsplit-fused world={world} M={M} K={K} N={N}: {'ok' if good else 'MISMATCH'}", flush=True)
     assert ops.device_status() == 0
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)

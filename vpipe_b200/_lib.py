@@ -39,6 +39,9 @@ SYMBOLS = [
     ("vpq_comm_destroy", _i, [_vp]),
     ("vpq_comm_rank", _i, [_vp]),
     ("vpq_comm_world", _i, [_vp]),
+    ("vpq_comm_alloc_symmetric", _i, [_vp, C.c_size_t, C.POINTER(_vp)]),
+    ("vpq_comm_free_symmetric", _i, [_vp, _vp]),
+    ("vpq_affine_qmm_w4g64_bf16_nsplit_fused", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     ("vpq_affine_qmm_w4g64_bf16_nsplit", _i,
      [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i, _vp]),
 ]

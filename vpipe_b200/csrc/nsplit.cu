@@ -20,9 +20,21 @@
 
 #include <cstring>
 
+struct vpq_sym_buf {
+  void* local = nullptr;
+  void* peer[8] = {};   // peer[r]: rank r's buffer mapped here (peer[rank] == local)
+  size_t bytes = 0;
+};
+
 struct vpq_comm_s {
   ncclComm_t comm = nullptr;
   int rank = 0, world = 1, device = 0;
+  // fused column-split: symmetric buffers, and a flag array per rank for the cross-GPU barrier
+  vpq_sym_buf bufs[8];
+  int nbufs = 0;
+  vpq_sym_buf flags;       // uint32 [8] per rank
+  uint32_t epoch = 0;
+  void* handle_stage = nullptr;  // device staging for the IPC-handle exchange
   cudaStream_t comm_stream = nullptr;
   cudaEvent_t ev_start = nullptr, ev_done = nullptr;
   cudaEvent_t ev_chunk[16] = {};
@@ -30,6 +42,8 @@ struct vpq_comm_s {
 
 namespace vpq {
 namespace {
+
+constexpr int kCollectiveSms = 16;  // SMs the GEMM leaves to NCCL when the exchange overlaps it
 
 struct Nccl {
   void* handle = nullptr;
@@ -82,6 +96,27 @@ Nccl& nccl() {
     }                                                                                  \
   } while (0)
 
+// Cross-GPU barrier over peer-mapped flags: thread r publishes this rank's epoch into rank r's
+// flag array, then waits (bounded) until rank r's epoch has arrived here. Launched after the
+// GEMM on the same stream, so this GPU's peer stores are complete before its flag is raised.
+__global__ void peer_barrier_kernel(uint32_t* const* peer_flags, uint32_t* my_flags, int rank, int world,
+                                    uint32_t epoch, uint32_t* status) {
+  const int r = threadIdx.x;
+  if (r >= world) { return; }
+  __threadfence_system();
+  volatile uint32_t* remote = peer_flags[r] + rank;
+  *remote = epoch;
+  __threadfence_system();
+  volatile uint32_t* mine = my_flags + r;
+  for (uint32_t i = 0; i < (1u << 24); ++i) {
+    if ((int32_t)(*mine - epoch) >= 0) { return; }
+    __nanosleep(100);
+  }
+  atomicCAS(status, 0u, 0x7700u | (uint32_t)r);  // rank r never arrived
+}
+
+__device__ uint32_t g_nsplit_status;
+
 // shard-major [G, M, Ns] -> row-major [M, G*Ns] for rows [m0, m1)
 __global__ void __launch_bounds__(256)
 shards_to_rowmajor_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int64_t M,
@@ -102,6 +137,10 @@ shards_to_rowmajor_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
 }  // namespace vpq
 
 using namespace vpq;
+
+namespace {
+void unmap_peers(vpq_comm* c, vpq_sym_buf* b);
+}
 
 extern "C" int vpq_comm_unique_id(void* id_host) {
   clear_error();
@@ -144,6 +183,10 @@ extern "C" int vpq_comm_destroy(vpq_comm* c) {
   clear_error();
   if (!c) { return VPQ_OK; }
   if (c->comm_stream) { cudaStreamSynchronize(c->comm_stream); }
+  cudaDeviceSynchronize();
+  for (int i = 0; i < c->nbufs; ++i) { unmap_peers(c, &c->bufs[i]); }
+  if (c->flags.local) { unmap_peers(c, &c->flags); }
+  if (c->handle_stage) { cudaFree(c->handle_stage); }
   if (c->comm) { nccl().CommDestroy(c->comm); }
   for (auto& e : c->ev_chunk) {
     if (e) { cudaEventDestroy(e); }
@@ -191,18 +234,20 @@ extern "C" int vpq_affine_qmm_w4g64_bf16_nsplit(vpq_comm* c, const uint32_t* w_s
     return VPQ_OK;
   }
 
-  // chunk boundaries on multiples of 128 rows (the GEMM's row tile)
-  const int64_t row_tiles = (M + 127) / 128;
+  // chunk boundaries on multiples of 256 rows (the GEMM's row tile)
+  const int64_t row_tiles = (M + 255) / 256;
   if (m_chunks > row_tiles) { m_chunks = (int)row_tiles; }
   const uint16_t* xb = static_cast<const uint16_t*>(x);
   for (int ch = 0; ch < m_chunks; ++ch) {
-    const int64_t m0 = (row_tiles * ch / m_chunks) * 128;
-    int64_t m1 = (row_tiles * (ch + 1) / m_chunks) * 128;
+    const int64_t m0 = (row_tiles * ch / m_chunks) * 256;
+    int64_t m1 = (row_tiles * (ch + 1) / m_chunks) * 256;
     if (m1 > M) { m1 = M; }
     const int64_t rows = m1 - m0;
     if (rows <= 0) { continue; }
-    if (int rc = vpq_affine_qmm_w4g64_bf16(w_shard, scales_shard, biases_shard, xb + m0 * K,
-                                           mine + m0 * Ns, K, Ns, rows, stream)) {
+    // chunked: leave a few SMs idle so the exchange of the previous chunk runs beside this GEMM
+    const int reserve = m_chunks > 1 ? kCollectiveSms : 0;
+    if (int rc = qmm_launch_reserved(w_shard, scales_shard, biases_shard, xb + m0 * K, mine + m0 * Ns, K, Ns,
+                                     rows, stream, reserve)) {
       return rc;
     }
     VPQ_CUDA_OK(cudaEventRecord(c->ev_chunk[ch], st));
@@ -234,3 +279,135 @@ extern "C" int vpq_affine_qmm_w4g64_bf16_nsplit(vpq_comm* c, const uint32_t* w_s
   VPQ_CUDA_OK(cudaStreamWaitEvent(st, c->ev_done, 0));
   return VPQ_OK;
 }
+
+// ------------------------------------------------------------ fused column-split
+namespace {
+
+// Collective: every rank maps every other rank's `local` allocation (CUDA IPC; one process per GPU).
+int map_peers(vpq_comm* c, vpq_sym_buf* b) {
+  const int G = c->world;
+  cudaIpcMemHandle_t mine;
+  VPQ_CUDA_OK(cudaIpcGetMemHandle(&mine, b->local));
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  if (!c->handle_stage) { VPQ_CUDA_OK(cudaMalloc(&c->handle_stage, 64 * 10)); }  // 8 + 1 handles, pointer table
+  char* stage = static_cast<char*>(c->handle_stage);
+  VPQ_CUDA_OK(cudaMemcpyAsync(stage + 64 * 8, &mine, 64, cudaMemcpyHostToDevice, c->comm_stream));
+  VPQ_NCCL_OK(nccl().AllGather(stage + 64 * 8, stage, 64, ncclUint8, c->comm, c->comm_stream));
+  cudaIpcMemHandle_t all[8];
+  VPQ_CUDA_OK(cudaMemcpyAsync(all, stage, 64 * (size_t)G, cudaMemcpyDeviceToHost, c->comm_stream));
+  VPQ_CUDA_OK(cudaStreamSynchronize(c->comm_stream));
+  for (int r = 0; r < G; ++r) {
+    if (r == c->rank) {
+      b->peer[r] = b->local;
+    } else {
+      VPQ_CUDA_OK(cudaIpcOpenMemHandle(&b->peer[r], all[r], cudaIpcMemLazyEnablePeerAccess));
+    }
+  }
+  return VPQ_OK;
+}
+
+void unmap_peers(vpq_comm* c, vpq_sym_buf* b) {
+  for (int r = 0; r < c->world; ++r) {
+    if (r != c->rank && b->peer[r]) { cudaIpcCloseMemHandle(b->peer[r]); }
+    b->peer[r] = nullptr;
+  }
+  if (b->local) { cudaFree(b->local); }
+  b->local = nullptr;
+}
+
+}  // namespace
+
+extern "C" int vpq_comm_alloc_symmetric(vpq_comm* c, size_t bytes, void** local_ptr) {
+  clear_error();
+  if (!c || !local_ptr || bytes == 0) { return fail(VPQ_ERR_INVALID_ARG, "comm_alloc_symmetric: bad arguments"); }
+  if (c->world > 8) { return fail(VPQ_ERR_UNSUPPORTED, "comm_alloc_symmetric: at most 8 ranks"); }
+  if (c->nbufs >= 8) { return fail(VPQ_ERR_UNSUPPORTED, "comm_alloc_symmetric: at most 8 live buffers"); }
+  if (!c->flags.local) {  // first use: the barrier flags
+    VPQ_CUDA_OK(cudaMalloc(&c->flags.local, 8 * sizeof(uint32_t)));
+    VPQ_CUDA_OK(cudaMemset(c->flags.local, 0, 8 * sizeof(uint32_t)));
+    VPQ_CUDA_OK(cudaDeviceSynchronize());
+    c->flags.bytes = 8 * sizeof(uint32_t);
+    if (int rc = map_peers(c, &c->flags)) { return rc; }
+    // the peers' flag arrays as a device table for the barrier kernel
+    uint32_t* hp[8] = {};
+    for (int r = 0; r < c->world; ++r) { hp[r] = static_cast<uint32_t*>(c->flags.peer[r]); }
+    VPQ_CUDA_OK(cudaMemcpy(static_cast<char*>(c->handle_stage) + 64 * 9, hp, sizeof(hp), cudaMemcpyHostToDevice));
+  }
+  vpq_sym_buf* b = &c->bufs[c->nbufs];
+  VPQ_CUDA_OK(cudaMalloc(&b->local, bytes));
+  b->bytes = bytes;
+  if (int rc = map_peers(c, b)) { return rc; }
+  ++c->nbufs;
+  *local_ptr = b->local;
+  return VPQ_OK;
+}
+
+extern "C" int vpq_comm_free_symmetric(vpq_comm* c, void* local_ptr) {
+  clear_error();
+  if (!c || !local_ptr) { return fail(VPQ_ERR_INVALID_ARG, "comm_free_symmetric: bad arguments"); }
+  for (int i = 0; i < c->nbufs; ++i) {
+    if (c->bufs[i].local == local_ptr) {
+      cudaDeviceSynchronize();
+      unmap_peers(c, &c->bufs[i]);
+      c->bufs[i] = c->bufs[c->nbufs - 1];
+      c->bufs[c->nbufs - 1] = vpq_sym_buf();
+      --c->nbufs;
+      return VPQ_OK;
+    }
+  }
+  return fail(VPQ_ERR_INVALID_ARG, "comm_free_symmetric: not a buffer of this communicator");
+}
+
+extern "C" int vpq_affine_qmm_w4g64_bf16_nsplit_fused(vpq_comm* c, const uint32_t* w_shard,
+                                                      const void* scales_shard, const void* biases_shard,
+                                                      const void* x, void* y_sym, int64_t K, int64_t N,
+                                                      int64_t M, void* stream) {
+  clear_error();
+  if (!c || !y_sym) { return fail(VPQ_ERR_INVALID_ARG, "qmm_nsplit_fused: null communicator or output"); }
+  const int G = c->world;
+  if (N <= 0 || (N % (8 * G)) != 0) {
+    return fail(VPQ_ERR_INVALID_ARG, "qmm_nsplit_fused: N=%lld must be a multiple of 8 x %d ranks", (long long)N, G);
+  }
+  const vpq_sym_buf* b = nullptr;
+  for (int i = 0; i < c->nbufs; ++i) {
+    if (c->bufs[i].local == y_sym) { b = &c->bufs[i]; }
+  }
+  if (!b) { return fail(VPQ_ERR_INVALID_ARG, "qmm_nsplit_fused: y must come from vpq_comm_alloc_symmetric"); }
+  if (b->bytes < (size_t)M * (size_t)N * 2) { return fail(VPQ_ERR_INVALID_ARG, "qmm_nsplit_fused: y too small"); }
+  const int64_t Ns = N / G;
+  // this GPU's copy first, then the peers', so the local stores lead
+  void* dests[8];
+  int n = 0;
+  dests[n++] = b->local;
+  for (int r = 1; r < G; ++r) { dests[n++] = b->peer[(c->rank + r) % G]; }
+  if (int rc = qmm_launch_multi_dest(w_shard, scales_shard, biases_shard, x, dests, n, N, (int64_t)c->rank * Ns,
+                                     K, Ns, M, stream)) {
+    return rc;
+  }
+  if (G > 1) {
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    char* stage = static_cast<char*>(c->handle_stage) + 64 * 9;  // the peers' flag pointers
+    uint32_t* status = nullptr;
+    VPQ_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_nsplit_status));
+    ++c->epoch;
+    peer_barrier_kernel<<<1, 32, 0, st>>>(reinterpret_cast<uint32_t* const*>(stage),
+                                          static_cast<uint32_t*>(c->flags.local), c->rank, G, c->epoch, status);
+    VPQ_LAUNCH_OK("peer_barrier");
+  }
+  return VPQ_OK;
+}
+
+namespace vpq {
+int nsplit_status_read(cudaStream_t st, uint32_t* out) {
+  uint32_t v = 0;
+  VPQ_CUDA_OK(cudaMemcpyFromSymbolAsync(&v, g_nsplit_status, sizeof(v), 0, cudaMemcpyDeviceToHost, st));
+  VPQ_CUDA_OK(cudaStreamSynchronize(st));
+  if (v != 0) {
+    const uint32_t zero = 0;
+    VPQ_CUDA_OK(cudaMemcpyToSymbolAsync(g_nsplit_status, &zero, sizeof(zero), 0, cudaMemcpyHostToDevice, st));
+    VPQ_CUDA_OK(cudaStreamSynchronize(st));
+  }
+  *out = v;
+  return VPQ_OK;
+}
+}  // namespace vpq

@@ -487,7 +487,7 @@ int launch_qmm(const uint32_t* w, const uint16_t* scales, const uint16_t* biases
 }
 
 int launch_qmm_2cta(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const void* x,
-                    __nv_bfloat16* y, int K, int N, int M, cudaStream_t st) {
+                    const two_cta::OutSpec& out, int K, int N, int M, cudaStream_t st, int reserve_sms) {
   using L = two_cta::Smem;
   CUtensorMap map_x, map_w;
   if (int rc = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)K, (uint64_t)M,
@@ -501,9 +501,10 @@ int launch_qmm_2cta(const uint32_t* w, const uint16_t* scales, const uint16_t* b
   auto kern = two_cta::affine_qmm_w4g64_2cta_kernel;
   VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
   const int tiles = ((M + two_cta::TM - 1) / two_cta::TM) * ((N + two_cta::TN - 1) / two_cta::TN);
-  const int pairs = num_sms() / 2;
+  int pairs = (num_sms() - reserve_sms) / 2;  // SMs left free run a concurrent collective
+  if (pairs < 1) { pairs = 1; }
   const int grid = 2 * (tiles < pairs ? tiles : pairs);
-  kern<<<grid, two_cta::kThreads2, L::kAlloc, st>>>(map_x, map_w, scales, biases, y, M, N, K);
+  kern<<<grid, two_cta::kThreads2, L::kAlloc, st>>>(map_x, map_w, scales, biases, out, M, N, K);
   VPQ_LAUNCH_OK("affine_qmm_w4g64 (2-CTA)");
   return VPQ_OK;
 }
@@ -513,9 +514,9 @@ int launch_qmm_2cta(const uint32_t* w, const uint16_t* scales, const uint16_t* b
 
 using namespace vpq;
 
-extern "C" int vpq_affine_qmm_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
-                                         const void* x, void* y, int64_t K, int64_t N, int64_t M,
-                                         void* stream) {
+namespace vpq {
+int qmm_launch_reserved(const uint32_t* w, const void* scales, const void* biases, const void* x, void* y,
+                        int64_t K, int64_t N, int64_t M, void* stream, int reserve_sms) {
   clear_error();
   if (!w || !scales || !biases || !x || !y) {
     return fail(VPQ_ERR_INVALID_ARG, "affine_qmm_w4g64: null pointer");
@@ -538,11 +539,48 @@ extern "C" int vpq_affine_qmm_w4g64_bf16(const uint32_t* w, const void* scales, 
   // single-CTA 128 x 256 kernel otherwise.
   static const bool force_1cta = std::getenv("VPQ_QMM_1CTA") != nullptr;
   if (M > 128 && !force_1cta) {
+    two_cta::OutSpec out = {};
+    out.base[0] = static_cast<__nv_bfloat16*>(y);
+    out.count = 1;
+    out.col0 = 0;
+    out.ld = N;
     return launch_qmm_2cta(w, static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases),
-                           x, static_cast<__nv_bfloat16*>(y), (int)K, (int)N, (int)M, st);
+                           x, out, (int)K, (int)N, (int)M, st, reserve_sms);
   }
   return launch_qmm<256>(w, static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases),
                          x, static_cast<__nv_bfloat16*>(y), (int)K, (int)N, (int)M, st);
+}
+
+// Column block [M, N] of a wider row-major output, stored into `count` destinations (this GPU's
+// and its peers' copies of y): the fused epilogue of the column-split. Needs M > 128.
+int qmm_launch_multi_dest(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                          void* const* dests, int count, int64_t ld, int64_t col0, int64_t K, int64_t N,
+                          int64_t M, void* stream) {
+  if (!w || !scales || !biases || !x || !dests || count < 1 || count > 8) {
+    return fail(VPQ_ERR_INVALID_ARG, "qmm (fused split): null pointer or more than 8 destinations");
+  }
+  if (K <= 0 || N <= 0 || M <= 128 || (K % 64) != 0 || (ld % 8) != 0 || (col0 % 8) != 0) {
+    return fail(VPQ_ERR_UNSUPPORTED, "qmm (fused split): needs M > 128, K %% 64 == 0, ld and col0 %% 8 == 0");
+  }
+  if (!aligned16(w) || !aligned16(x)) { return fail(VPQ_ERR_ALIGNMENT, "qmm (fused split): w, x alignment"); }
+  if (int rc = require_sm100()) { return rc; }
+  two_cta::OutSpec out = {};
+  for (int d = 0; d < count; ++d) {
+    if (!dests[d] || !aligned16(dests[d])) { return fail(VPQ_ERR_ALIGNMENT, "qmm (fused split): destination %d", d); }
+    out.base[d] = static_cast<__nv_bfloat16*>(dests[d]);
+  }
+  out.count = count;
+  out.col0 = (int)col0;
+  out.ld = ld;
+  return launch_qmm_2cta(w, static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases), x, out,
+                         (int)K, (int)N, (int)M, static_cast<cudaStream_t>(stream), 0);
+}
+}  // namespace vpq
+
+extern "C" int vpq_affine_qmm_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
+                                         const void* x, void* y, int64_t K, int64_t N, int64_t M,
+                                         void* stream) {
+  return qmm_launch_reserved(w, scales, biases, x, y, K, N, M, stream, 0);
 }
 
 extern "C" int vpq_device_status(void* stream, uint32_t* detail) {
@@ -555,6 +593,12 @@ extern "C" int vpq_device_status(void* stream, uint32_t* detail) {
   uint32_t vq = 0;
   if (int rc = qmv_status_read(st, &vq)) { return rc; }
   if (detail) { *detail = v ? v : (vq ? (vq | 0x10000u) : 0u); }
+  uint32_t vn = 0;
+  if (int rc = nsplit_status_read(st, &vn)) { return rc; }
+  if (vn != 0 && v == 0 && vq == 0) {
+    if (detail) { *detail = vn | 0x20000u; }
+    return fail(VPQ_ERR_TIMEOUT, "the cross-GPU barrier gave up waiting for rank %u", vn & 0xffu);
+  }
   if (vq != 0 && v == 0) {
     return fail(VPQ_ERR_TIMEOUT, "a bounded device-side wait gave up in the GEMV kernel (site %u, role %u)",
                 vq >> 8, vq & 0xffu);

@@ -23,9 +23,20 @@ namespace two_cta {
 constexpr int TM = 256;        // tile rows (128 per CTA)
 constexpr int TN = 256;        // tile columns (128 W rows dequantised per CTA)
 constexpr int kXStages = 5;    // x + codes ring
-constexpr int kBTiles = 6;     // dequantised-B ring
+constexpr int kBTiles = 5;     // dequantised-B ring
 constexpr int kDqWarps = 8;
 constexpr int kThreads2 = 32 * (kEpiWarps + 2 + kDqWarps);
+
+// Where a CTA pair's output tile goes: `count` row-major destinations (this GPU's y and, in the
+// fused column-split, every peer's y mapped into this address space), leading dimension `ld`,
+// and the column at which this GPU's block starts. Peer destinations are written with ordinary
+// stores over NVLink.
+struct OutSpec {
+  __nv_bfloat16* base[8];
+  int count;
+  int col0;
+  int64_t ld;
+};
 
 struct Smem {
   static constexpr int kXBytes = 128 * BK * 2;        // 16 KB, 128B-swizzled
@@ -34,7 +45,9 @@ struct Smem {
   static constexpr int kOffX = 0;
   static constexpr int kOffB = kOffX + kXStages * kXBytes;
   static constexpr int kOffCode = kOffB + kBTiles * kBBytes;
-  static constexpr int kOffBar = kOffCode + kXStages * kCodeBytes;
+  static constexpr int kEpiBytes = 32 * 256;          // per epilogue warp: 32 rows x 128 bf16
+  static constexpr int kOffEpi = kOffCode + kXStages * kCodeBytes;
+  static constexpr int kOffBar = kOffEpi + kEpiWarps * kEpiBytes;
   static constexpr int kNumBars = 3 * kXStages + 2 * kBTiles + 4;
   static constexpr int kOffTmem = kOffBar + kNumBars * 8;
   static constexpr int kTotal = kOffTmem + 16;
@@ -129,7 +142,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
 affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
                              const __grid_constant__ CUtensorMap tmap_w,
                              const uint16_t* __restrict__ scales, const uint16_t* __restrict__ biases,
-                             __nv_bfloat16* __restrict__ y, int M, int N, int K) {
+                             const OutSpec out, int M, int N, int K) {
   using L = Smem;
   constexpr uint32_t kTmemCols = 512;  // two 256-column accumulator buffers
 
@@ -322,7 +335,7 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // ------------------------------------------------------------ epilogue (both CTAs)
     uint32_t ti = 0;
     bool ok = true;
-    const bool vec_ok = (N % 8) == 0;
+    const bool vec_ok = (N % 8) == 0 && (out.ld % 8) == 0 && (out.col0 % 8) == 0;
     const uint32_t accempty_leader = map_to_cta(bar0, 0) + 8u * (3 * kXStages + 2 * kBTiles + 2);
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++ti) {
       const int m0 = (tile / tiles_n) * TM + (int)rank * 128;
@@ -331,35 +344,64 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const uint32_t aph = (ti >> 1) & 1u;
       if (!warp_wait(bar_accfull(a), aph, (1u << 8) | kRoleEpi, abort_flag, &g_qmm_status)) { ok = false; break; }
       tc_fence_after();
-      const int m = m0 + warp * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(a * TN);
-      __nv_bfloat16* yrow = y + (int64_t)m * N + n0;
+      // The accumulator comes out of tensor memory one row per lane; it is transposed through a
+      // warp-private, XOR-swizzled staging block so that 16 lanes store 256 contiguous bytes of
+      // one output row (what remote stores over NVLink, and local ones, want).
+      unsigned char* stg = base_ptr + L::kOffEpi + warp * L::kEpiBytes;
+      const int mrow0 = m0 + warp * 32;
 #pragma unroll 1
-      for (int c = 0; c < TN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(taddr + (uint32_t)(c * 32), r);
-        tmem_ld_wait();
-        const int nc = n0 + c * 32;
-        if (m < M && nc < N) {
-          if (vec_ok) {
+      for (int h = 0; h < TN / 128; ++h) {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld32(taddr + (uint32_t)(h * 128 + c * 32), r);
+          tmem_ld_wait();
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              if (nc + v * 8 < N) {
-                uint4 pk;
-                pk.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-                pk.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-                pk.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-                pk.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-                *reinterpret_cast<uint4*>(yrow + c * 32 + v * 8) = pk;
+          for (int v = 0; v < 4; ++v) {
+            uint4 pk;
+            pk.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+            pk.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+            pk.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+            pk.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+            const int j = c * 4 + v;  // 16-byte chunk of the 256-byte row
+            *reinterpret_cast<uint4*>(stg + lane * 256 + ((j ^ (lane & 15)) << 4)) = pk;
+          }
+        }
+        __syncwarp();
+        const int nc0 = n0 + h * 128;          // first column of this 128-column half (within the block)
+        const int j = lane & 15;               // this lane's 16-byte chunk = 8 columns
+        const bool col_ok = nc0 + j * 8 < N;
+        if (vec_ok) {
+#pragma unroll 4
+          for (int i = 0; i < 16; ++i) {
+            const int row = 2 * i + (lane >> 4);
+            const uint4 pk = *reinterpret_cast<const uint4*>(stg + row * 256 + ((j ^ (row & 15)) << 4));
+            const int mm = mrow0 + row;
+            if (mm < M && col_ok) {
+              const int64_t off = (int64_t)mm * out.ld + out.col0 + nc0 + j * 8;
+              for (int d = 0; d < out.count; ++d) {  // this GPU first, then every peer
+                *reinterpret_cast<uint4*>(out.base[d] + off) = pk;
               }
             }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (nc + j < N) { yrow[c * 32 + j] = __float2bfloat16_rn(__uint_as_float(r[j])); }
+          }
+        } else {  // ragged widths: element-wise
+          for (int i = 0; i < 16; ++i) {
+            const int row = 2 * i + (lane >> 4);
+            const uint4 pk = *reinterpret_cast<const uint4*>(stg + row * 256 + ((j ^ (row & 15)) << 4));
+            const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&pk);
+            const int mm = mrow0 + row;
+            if (mm < M) {
+              for (int d = 0; d < out.count; ++d) {
+                __nv_bfloat16* yrow = out.base[d] + (int64_t)mm * out.ld + out.col0 + nc0 + j * 8;
+                for (int q = 0; q < 8; ++q) {
+                  if (nc0 + j * 8 + q < N) { yrow[q] = e[q]; }
+                }
+              }
             }
           }
         }
+        __syncwarp();
       }
       tc_fence_before();
       __syncwarp();

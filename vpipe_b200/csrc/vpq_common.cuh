@@ -38,8 +38,20 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 int num_sms();
 
+// The QMM with `reserve_sms` SMs left idle for a collective running beside it (qmm.cu).
+int qmm_launch_reserved(const uint32_t* w, const void* scales, const void* biases, const void* x, void* y,
+                        int64_t K, int64_t N, int64_t M, void* stream, int reserve_sms);
+
+// The QMM whose epilogue stores its [M, N] column block into several row-major outputs of leading
+// dimension ld at column col0 (this GPU's y and its peers' y); qmm.cu.
+int qmm_launch_multi_dest(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                          void* const* dests, int count, int64_t ld, int64_t col0, int64_t K, int64_t N,
+                          int64_t M, void* stream);
+
 // Reads and clears the GEMV kernel's device status word (qmv.cu).
 int qmv_status_read(cudaStream_t st, uint32_t* out);
+// Same for the cross-GPU barrier of the fused column-split (nsplit.cu).
+int nsplit_status_read(cudaStream_t st, uint32_t* out);
 
 // --------------------------------------------------------------- device side
 #ifdef __CUDACC__

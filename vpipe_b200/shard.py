@@ -87,6 +87,41 @@ class NsplitComm:
             x.data_ptr(), y_shards.data_ptr(),
             y_rowmajor.data_ptr() if y_rowmajor is not None else None, K, N, M, m_chunks, st))
 
+    def alloc_symmetric(self, shape, dtype):
+        """A tensor in a buffer every rank has mapped (collective call). Keep the returned tensor's
+        owner (this communicator) alive while it is in use."""
+        import torch
+
+        from ._lib import check, lib
+        n = 1
+        for d in shape:
+            n *= int(d)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        ptr = C.c_void_p()
+        check(lib().vpq_comm_alloc_symmetric(self.handle, nbytes, C.byref(ptr)))
+
+        class _Raw:  # exposes the device allocation through the CUDA array interface
+            pass
+        raw = _Raw()
+        raw.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr.value, False),
+                                        "version": 2}
+        t = torch.as_tensor(raw, device=torch.device("cuda", torch.cuda.current_device()))
+        return t.view(dtype).view(*shape), ptr.value
+
+    def qmm_fused(self, codes_shard, scales_shard, biases_shard, x, y_sym_ptr, stream=None):
+        """Column-split QMM whose epilogue writes every rank's row-major y directly (no collective)."""
+        import torch
+
+        from ._lib import check, lib
+        ns, kw = codes_shard.shape
+        K = kw * 8
+        N = ns * self.world
+        M = x.numel() // K
+        st = (stream if stream is not None else torch.cuda.current_stream()).cuda_stream
+        check(lib().vpq_affine_qmm_w4g64_bf16_nsplit_fused(
+            self.handle, codes_shard.data_ptr(), scales_shard.data_ptr(), biases_shard.data_ptr(),
+            x.data_ptr(), y_sym_ptr, K, N, M, st))
+
     def close(self):
         from ._lib import lib
         if self.handle:
