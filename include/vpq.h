@@ -130,6 +130,21 @@ int vpq_qmv_plan_create(const vpq_linear_desc* descs_host, int count, void* work
 int vpq_qmv_plan_run(const vpq_qmv_plan* plan, void* stream);
 int vpq_qmv_plan_destroy(vpq_qmv_plan* plan);
 
+/* The same one-launch set of independent GEMVs for callers that must not allocate device memory
+ * and have no workspace to lend: code running inside someone else's memory budget (a host
+ * application whose allocator owns every byte of HBM, a plugin entry point that is handed
+ * buffers and nothing else) or on a latency path where a cudaMalloc, which can synchronise the
+ * whole device, is not acceptable. No counterpart in the reference. The descriptor list the
+ * kernel needs lives in a fixed 28 KB array inside the library image (held by every GPU that
+ * loads the library until exit), so at most 64 GEMV rows (sum of M over the set) fit in one call;
+ * larger sets are rejected with VPQ_ERR_UNSUPPORTED. The call performs no cudaMalloc / cudaFree
+ * and uses no allocating library routine. The first call on each device looks up the array's
+ * device address; make that first call outside any stream capture. All calls share the one
+ * array: a call rewrites every descriptor it uses (nothing is read from a previous call), but
+ * two calls that overlap on the GPU (different streams, or graphs replayed concurrently) race on
+ * it -- keep calls to this entry point ordered on one stream per device. */
+int vpq_affine_qmv_w4g64_bf16_set_noalloc(const vpq_linear_desc* descs_host, int count, void* stream);
+
 /* Prefill / DiT GEMM: y[M,N] = x[M,K] @ dequant(W)[N,K]^T. W is dequantised
  * to bf16 tile by tile in shared memory (bit-identical to
  * vpq_affine_dequant_w4g64_bf16), multiplied on the tcgen05 tensor cores with

@@ -679,6 +679,67 @@ extern "C" int vpq_qmv_plan_run(const vpq_qmv_plan* plan, void* stream) {
   return launch_list(unused, plan->list_dev, plan->total_tiles, plan->cap_kt, static_cast<cudaStream_t>(stream));
 }
 
+// ---------------------------------------------------------------- no-allocation variant
+// The plan kernel needs its list of problem descriptors in device memory. This variant keeps that
+// list in a fixed array that is part of the library image, so the call neither allocates nor needs
+// a caller workspace. Every GPU that loads the library carries the array (28 KB) until exit.
+constexpr int kNoAllocMaxRows = 64;  // GEMV rows (sum of M over the set) one call can take
+static __device__ __align__(256) unsigned char g_noalloc_descs[kNoAllocMaxRows * sizeof(QmvProblem)];
+
+extern "C" int vpq_affine_qmv_w4g64_bf16_set_noalloc(const vpq_linear_desc* d, int count, void* stream) {
+  clear_error();
+  if (!d || count <= 0) { return fail(VPQ_ERR_INVALID_ARG, "qmv_set_noalloc: null or empty set"); }
+  int64_t rows = 0;
+  for (int i = 0; i < count; ++i) {
+    if (int rc = check_qmv_args("qmv_set_noalloc", d[i].w, d[i].scales, d[i].biases, d[i].x, d[i].y, d[i].K,
+                                d[i].N, d[i].M)) {
+      return rc;
+    }
+    rows += d[i].M;
+  }
+  if (rows > kNoAllocMaxRows) {
+    return fail(VPQ_ERR_UNSUPPORTED,
+                "qmv_set_noalloc: %lld GEMV rows in the set, the built-in descriptor array holds %d; "
+                "split the set or use vpq_qmv_plan_create with a workspace",
+                (long long)rows, kNoAllocMaxRows);
+  }
+  if (int rc = require_sm100()) { return rc; }
+  // Device address of the array, looked up once per device with that device current. In host code
+  // the array's name is only a handle for this lookup, never a pointer a kernel could use.
+  static void* dev_addr[64] = {};
+  int dev = 0;
+  VPQ_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) { return fail(VPQ_ERR_CUDA, "qmv_set_noalloc: device index %d", dev); }
+  if (!dev_addr[dev]) {
+    void* ptr = nullptr;
+    VPQ_CUDA_OK(cudaGetSymbolAddress(&ptr, g_noalloc_descs));
+    dev_addr[dev] = ptr;
+  }
+  QmvProblem host[kNoAllocMaxRows];
+  int tiles = 0, cap_kt = 0, r = 0;
+  for (int i = 0; i < count; ++i) {
+    for (int64_t m = 0; m < d[i].M; ++m, ++r) {
+      if (int rc = fill_problem(&host[r], d[i].w, static_cast<const uint16_t*>(d[i].scales),
+                                static_cast<const uint16_t*>(d[i].biases),
+                                static_cast<const uint16_t*>(d[i].x) + m * d[i].K,
+                                static_cast<__nv_bfloat16*>(d[i].y) + m * d[i].N, (int)d[i].K, (int)d[i].N,
+                                tiles)) {
+        return rc;
+      }
+      tiles += host[r].row_tiles;
+      const int kt = (int)((d[i].K + 255) / 256) * 2;
+      cap_kt = kt > cap_kt ? kt : cap_kt;
+    }
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // every descriptor the kernel will read is rewritten here, so nothing stale from the previous
+  // call is ever used; the copy is ordered before the launch on the same stream
+  VPQ_CUDA_OK(cudaMemcpyAsync(dev_addr[dev], host, (size_t)r * sizeof(QmvProblem), cudaMemcpyHostToDevice, st));
+  QmvProblem unused;
+  std::memset(&unused, 0, sizeof(unused));
+  return launch_list(unused, static_cast<const QmvProblem*>(dev_addr[dev]), tiles, cap_kt, st);
+}
+
 extern "C" int vpq_qmv_plan_destroy(vpq_qmv_plan* plan) {
   delete plan;
   return VPQ_OK;

@@ -92,6 +92,12 @@ def qmv_batch(descs, stream=None) -> None:
     check(lib().vpq_affine_qmv_w4g64_bf16_batch(descs, len(descs), _stream(stream)))
 
 
+def qmv_set_noalloc(descs, stream=None) -> None:
+    """One launch for a set of at most 64 independent GEMV rows, with no device allocation and no
+    workspace (vpq_affine_qmv_w4g64_bf16_set_noalloc). Calls must not overlap on the GPU."""
+    check(lib().vpq_affine_qmv_w4g64_bf16_set_noalloc(descs, len(descs), _stream(stream)))
+
+
 class QmvPlan:
     """A list of independent GEMVs run as one launch (vpq_qmv_plan_*). Holds the device workspace."""
 
