@@ -75,31 +75,12 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
-// Bounded wait used by the leader's MMA thread on barriers the partner CTA also arrives on. The
-// partner's shared-memory writes are published to the async proxy by its fence.proxy.async before
-// its remote arrive; the tensor core reads them only after this wait returns.
+// The leader's MMA thread waits on barriers the partner CTA also arrives on with the ordinary
+// bounded wait: the partner's shared-memory writes are published to the async proxy by its
+// fence.proxy.async before its remote arrive, and the tensor core reads them only afterwards.
 __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, uint32_t code,
                                                   volatile uint32_t* abort_flag, uint32_t* status_word) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (ok) { return true; }
-    if (i > 64) {
-      __nanosleep(i > 4096 ? 256 : 32);
-      if (*abort_flag) { return false; }
-    }
-  }
-  *abort_flag = 1;
-  atomicCAS(status_word, 0u, code);
-  return false;
+  return mbar_wait(bar, parity, code, abort_flag, status_word);
 }
 
 // x tile of a CTA pair: lands in this CTA's shared memory, completes bytes on the LEADER's barrier.

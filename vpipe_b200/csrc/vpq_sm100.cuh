@@ -15,7 +15,6 @@ int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elt_bytes, const v
 
 #ifdef __CUDACC__
 
-constexpr uint32_t kSpinLimit = 1u << 22;  // polls (with back-off) before a wait gives up
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -48,17 +47,36 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait. On giving up it raises the CTA's abort flag, records `code`
-// in the kernel's device status word (first failure wins) and returns false.
+// Bounded wait. The poll loop is four instructions of PTX around mbarrier.try_wait with a
+// suspend-time hint (the thread sleeps in hardware instead of taking issue slots from the warps
+// that are working; a profile of the first QMM showed most issued instructions were polls).
+// On giving up it raises the CTA's abort flag, records `code` in the kernel's device status word
+// (first failure wins) and returns false.
+constexpr uint32_t kWaitHintNs = 1000;     // how long one try_wait may sleep
+constexpr uint32_t kWaitPolls = 1u << 21;  // polls before a wait gives up (about 2 s of sleeping)
+
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t code,
                                           volatile uint32_t* abort_flag, uint32_t* status_word) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) { return true; }
-    if (i > 64) {
-      __nanosleep(i > 4096 ? 256 : 32);
-      if (*abort_flag) { return false; }
-    }
-  }
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      ".reg .u32 n;\n\t"
+      "mov.u32 n, 0;\n\t"
+      "mov.u32 %0, 1;\n"
+      "VPQ_WAIT_LOOP:\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "@p bra VPQ_WAIT_DONE;\n\t"
+      "add.u32 n, n, 1;\n\t"
+      "setp.lt.u32 q, n, %4;\n\t"
+      "@q bra VPQ_WAIT_LOOP;\n\t"
+      "mov.u32 %0, 0;\n"
+      "VPQ_WAIT_DONE:\n\t"
+      "}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity), "r"(kWaitHintNs), "r"(kWaitPolls)
+      : "memory");
+  if (done) { return true; }
   *abort_flag = 1;
   atomicCAS(status_word, 0u, code);
   return false;
