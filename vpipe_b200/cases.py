@@ -1,0 +1,86 @@
+"""Small, self-contained invocations of the kernels for profiling and quick timing.
+
+    python -m vpipe_b200.cases qmv  K N [launches]     # single GEMVs on distinct weight copies
+    python -m vpipe_b200.cases plan LAYERS             # the C2 decode set as one plan launch
+    python -m vpipe_b200.cases qmm  M K N [reps]       # the GEMM
+
+Weights are random packed nibbles with bf16 scales / biases (the distribution of the reference's
+kernel tests); each command prints one JSON line with the CUDA-event time. Meant to be wrapped by
+`ncu -k regex:affine_q… -c 1` on a size that ends in seconds.
+"""
+from __future__ import annotations
+
+import json
+import sys
+
+import torch
+
+from . import ops, synth
+
+
+def _weight(N, K, dev):
+    codes = torch.randint(-2**31, 2**31 - 1, (N, K // 8), dtype=torch.int32, device=dev)
+    s = (torch.rand((N, K // 64), device=dev) * 0.015 + 0.005).to(torch.bfloat16)
+    b = (torch.rand((N, K // 64), device=dev) * 0.2 - 0.1).to(torch.bfloat16)
+    return codes, s, b
+
+
+def _time(fn, reps):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / 1e3 / reps
+
+
+def main(argv):
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    kind = argv[0]
+    if kind == "qmv":
+        K, N = int(argv[1]), int(argv[2])
+        n = int(argv[3]) if len(argv) > 3 else 6
+        x = torch.randn((1, K), device=dev).to(torch.bfloat16)
+        sets = [_weight(N, K, dev) + (x, torch.empty((1, N), dtype=torch.bfloat16, device=dev)) for _ in range(n)]
+        it = iter(sets * 2)
+        for p in sets:
+            ops.qmv(*p[:4], out=p[4])
+        torch.cuda.synchronize()
+        t = _time(lambda: (lambda p: ops.qmv(*p[:4], out=p[4]))(next(it)), n)
+        print(json.dumps({"case": "qmv", "K": K, "N": N, "us": t * 1e6,
+                          "GBs": synth.qmv_bytes(K, N) / t / 1e9}))
+    elif kind == "plan":
+        layers = int(argv[1])
+        xs = {K: torch.randn((1, K), device=dev).to(torch.bfloat16) for K in (4096, 12288)}
+        probs = []
+        for _ in range(layers):
+            for p in synth.CONFIGS["C2"].projs:
+                probs.append(_weight(p.N, p.K, dev) + (xs[p.K], torch.empty((1, p.N), dtype=torch.bfloat16, device=dev)))
+        plan = ops.QmvPlan(probs)
+        for _ in range(3):
+            plan.run()
+        torch.cuda.synchronize()
+        t = _time(plan.run, 1)
+        nbytes = sum(synth.qmv_bytes(p.K, p.N) for p in synth.CONFIGS["C2"].projs) * layers
+        print(json.dumps({"case": "plan", "layers": layers, "us": t * 1e6, "GBs": nbytes / t / 1e9}))
+    elif kind == "qmm":
+        M, K, N = int(argv[1]), int(argv[2]), int(argv[3])
+        reps = int(argv[4]) if len(argv) > 4 else 3
+        x = torch.randn((M, K), device=dev).to(torch.bfloat16)
+        codes, s, b = _weight(N, K, dev)
+        y = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        for _ in range(2):
+            ops.qmm(codes, s, b, x, out=y)
+        torch.cuda.synchronize()
+        t = _time(lambda: ops.qmm(codes, s, b, x, out=y), reps)
+        print(json.dumps({"case": "qmm", "M": M, "K": K, "N": N, "ms": t * 1e3,
+                          "tflops": synth.qmm_flops(K, N, M) / t / 1e12}))
+    else:
+        raise SystemExit(__doc__)
+    assert ops.device_status() == 0
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])
