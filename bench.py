@@ -42,9 +42,11 @@ FALLBACK_BF16_TFLOPS = 1590.0
 LAYERS = 36
 
 # DRAM traffic per launch measured once with ncu (dram__bytes_read.sum +
-# dram__bytes_write.sum), as a multiple of the algorithmic bytes of that launch;
-# see profiles/. None until a capture exists.
-QMV_TRAFFIC_RATIO = None
+# dram__bytes_write.sum) as a multiple of the algorithmic bytes of that launch, from a 4-layer
+# plan (profiles/qmv_plan_c2_4layers.md: 401.4 MB moved for 396.9 MB algorithmic); traffic grows
+# in proportion to the layers, so the 36-layer launch is scaled by it. The QMM is tensor-bound
+# and its y stays in L2 during a capture, so no DRAM figure is reported for it.
+QMV_TRAFFIC_RATIO = 1.011
 QMM_TRAFFIC_RATIO = None
 
 
