@@ -179,44 +179,39 @@ struct ScaleStream {
   int groups;
   bool vec;
   uint4 s_cur, b_cur, s_nxt, b_nxt;
-  uint32_t s1, b1;
+  int blk;
   __device__ __forceinline__ ScaleStream(const uint16_t* srow, const uint16_t* brow, int g)
       : s(srow), b(brow), groups(g) {
     vec = ((g & 7) == 0) && ((reinterpret_cast<uintptr_t>(srow) | reinterpret_cast<uintptr_t>(brow)) & 15u) == 0;
     s_cur = b_cur = s_nxt = b_nxt = make_uint4(0, 0, 0, 0);
-    s1 = b1 = 0;
+    blk = -1;
     if (vec) {
       s_nxt = __ldg(reinterpret_cast<const uint4*>(s));
       b_nxt = __ldg(reinterpret_cast<const uint4*>(b));
-    } else {
-      s1 = ldg_nc_u16(s);
-      b1 = ldg_nc_u16(b);
     }
   }
   __device__ __forceinline__ static float pick(const uint4& v, int i) {
     const uint32_t w = i < 4 ? (i < 2 ? v.x : v.y) : (i < 6 ? v.z : v.w);
     return __uint_as_float((i & 1) ? (w & 0xffff0000u) : (w << 16));
   }
+  // Works for any increasing sequence of kb (a warp group may take every other k block).
   __device__ __forceinline__ void get(int kb, float& sc, float& bi) {
     if (vec) {
       const int i = kb & 7;
-      if (i == 0) {
+      if ((kb >> 3) != blk) {
+        blk = kb >> 3;
         s_cur = s_nxt;
         b_cur = b_nxt;
-        if (kb + 8 < groups) {
-          s_nxt = __ldg(reinterpret_cast<const uint4*>(s + kb + 8));
-          b_nxt = __ldg(reinterpret_cast<const uint4*>(b + kb + 8));
+        if (blk * 8 + 8 < groups) {
+          s_nxt = __ldg(reinterpret_cast<const uint4*>(s + blk * 8 + 8));
+          b_nxt = __ldg(reinterpret_cast<const uint4*>(b + blk * 8 + 8));
         }
       }
       sc = pick(s_cur, i);
       bi = pick(b_cur, i);
     } else {
-      sc = bf16_bits_to_f32(s1);
-      bi = bf16_bits_to_f32(b1);
-      if (kb + 1 < groups) {
-        s1 = ldg_nc_u16(s + kb + 1);
-        b1 = ldg_nc_u16(b + kb + 1);
-      }
+      sc = bf16_bits_to_f32(ldg_nc_u16(s + kb));
+      bi = bf16_bits_to_f32(ldg_nc_u16(b + kb));
     }
   }
 };

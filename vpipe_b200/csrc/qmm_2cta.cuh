@@ -25,6 +25,8 @@ constexpr int TN = 256;        // tile columns (128 W rows dequantised per CTA)
 constexpr int kXStages = 5;    // x + codes ring
 constexpr int kBTiles = 5;     // dequantised-B ring
 constexpr int kDqWarps = 8;
+constexpr int kDqGroups = 2;   // warp groups that take alternate k blocks (a group = 4 warps = 128 rows)
+constexpr int kDqGroupWarps = kDqWarps / kDqGroups;
 constexpr int kThreads2 = 32 * (kEpiWarps + 2 + kDqWarps);
 
 // Where a CTA pair's output tile goes: `count` row-major destinations (this GPU's y and, in the
@@ -158,10 +160,10 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
     for (int s = 0; s < kXStages; ++s) {
       mbar_init(bar_xfull(s), 1);
       mbar_init(bar_cfull(s), 1);
-      mbar_init(bar_empty(s), 1 + kDqWarps);
+      mbar_init(bar_empty(s), 1 + kDqGroupWarps);
     }
     for (int t = 0; t < kBTiles; ++t) {
-      mbar_init(bar_bfull(t), 2 * kDqWarps);
+      mbar_init(bar_bfull(t), 2 * kDqGroupWarps);
       mbar_init(bar_bempty(t), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -249,9 +251,10 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
     }
   } else if (warp >= 6) {
     // ------------------------------------------------------- dequantisers (both CTAs)
-    const int tq = threadIdx.x - 6 * 32;   // 0 .. 255
-    const int t_row = tq >> 1;             // row of this CTA's half of the W tile
-    const int half = tq & 1;               // which 32 of the group's 64 values
+    // Two groups of four warps take alternate k blocks, one W row (a whole group of 64 values)
+    // per thread: a group has two MMA periods to turn a tile around instead of one.
+    const int grp = (warp - 6) / kDqGroupWarps;
+    const int t_row = threadIdx.x - 6 * 32 - grp * (kDqGroupWarps * 32);  // 0 .. 127
     const uint32_t row_off = (uint32_t)(t_row >> 3) * 1024u + (uint32_t)(t_row & 7) * 128u;
     const uint32_t sw = (uint32_t)(t_row & 7);
     const int groups = K >> 6;
@@ -270,11 +273,13 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const uint32_t ph = (it / kXStages) & 1u;
         const int t = it % kBTiles;
         const uint32_t bph = (it / kBTiles) & 1u;
+        if ((kb & (kDqGroups - 1)) != grp) { continue; }  // the other group's k block
         float sc, bi;
         sst.get(kb, sc, bi);
         if (!warp_wait(bar_cfull(s), ph, (1u << 8) | kRoleDq, abort_flag, &g_qmm_status)) { ok = false; break; }
-        const uint4 c0 = *reinterpret_cast<const uint4*>(base_ptr + L::kOffCode + s * L::kCodeBytes +
-                                                         t_row * (BK / 2) + half * 16);
+        const uint4* cp = reinterpret_cast<const uint4*>(base_ptr + L::kOffCode + s * L::kCodeBytes +
+                                                         t_row * (BK / 2));
+        const uint4 c0 = cp[0], c1 = cp[1];
         __syncwarp();
         if (lane == 0) { mbar_arrive(bar_empty(s)); }  // codes are in registers
 
@@ -282,23 +287,23 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const float b128 = bi - t128;
         const float bb = b128 - bi;
         const float resid = (bi - (b128 - bb)) + (-t128 - bb);  // two-sum residual of b - 128 s
-        uint32_t o[16];
-        const uint32_t cw[4] = {c0.x, c0.y, c0.z, c0.w};
+        uint32_t o[32];
+        const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
         {
           const uint64_t s2 = pack_f32x2(sc, sc), b2 = pack_f32x2(b128, b128);
 #pragma unroll
-          for (int wd = 0; wd < 4; ++wd) { dequant_word_fast(cw[wd], s2, b2, o + 4 * wd); }
+          for (int wd = 0; wd < 8; ++wd) { dequant_word_fast(cw[wd], s2, b2, o + 4 * wd); }
         }
         if (resid != 0.0f) {  // b - 128 s was not exact for this group: redo it the plain way
 #pragma unroll
-          for (int wd = 0; wd < 4; ++wd) { dequant_word_exact(cw[wd], sc, bi, o + 4 * wd); }
+          for (int wd = 0; wd < 8; ++wd) { dequant_word_exact(cw[wd], sc, bi, o + 4 * wd); }
         }
 
         if (!warp_wait(bar_bempty(t), bph ^ 1u, (2u << 8) | kRoleDq, abort_flag, &g_qmm_status)) { ok = false; break; }
         unsigned char* bt = base_ptr + L::kOffB + t * L::kBBytes + row_off;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {  // 16-byte chunk (4*half + c) of the row lands at chunk ^ row%8
-          *reinterpret_cast<uint4*>(bt + ((((uint32_t)(half * 4 + c)) ^ sw) << 4)) =
+        for (int c = 0; c < 8; ++c) {  // 16-byte chunk c of the row lands at chunk (c ^ row%8)
+          *reinterpret_cast<uint4*>(bt + ((((uint32_t)c) ^ sw) << 4)) =
               make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
         }
         fence_proxy_async();  // generic-proxy writes -> visible to the tensor cores' async reads
