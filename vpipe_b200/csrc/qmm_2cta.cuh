@@ -8,7 +8,8 @@
 //
 // Per CTA, 448 threads as in the 1-CTA kernel: warps 0-3 epilogue (tensor-memory lanes = this
 // CTA's 128 output rows), warp 4 TMA producer, warp 5 tensor-memory allocation (+ MMA issue in the
-// leader CTA only), warps 6-13 dequantisers (two threads per W row, 32 values each).
+// leader CTA only), warps 6-13 dequantisers: two groups of four warps, one W row (64 values) per
+// thread, the groups taking alternate k blocks so one block's latency hides behind the other's.
 //
 // Barriers. Local to each CTA: cfull[s] (packed W landed here), empty[s] (x + codes slot free:
 // one multicast tcgen05.commit + the local dequant warps), bempty[t] (dequantised tile free:
