@@ -14,19 +14,20 @@
 //    saturated near 2.5 TB/s, stalled on outstanding L1 requests;
 //  * a CTA owns tiles of 16 output rows; consumer warp w of 8 takes box w of
 //    every stage (two 128-wide k tiles), so K is split across the warps;
-//  * lane (g, t) reads 16 bytes of two rows per k tile from the stage
-//    (conflict-free through the swizzle), widens the nibbles in registers to
-//    bf16 128+q with one LOP3 per two nibbles (0x4300 | q is exactly 128 + q)
-//    and feeds them, unscaled, to mma.sync.m16n8k16 against x; products are
-//    exact and the accumulation is f32. A first SIMT version (one PRMT and half
-//    an f32x2 FMA per nibble) was bound by the integer pipe;
-//  * the two quantization groups of a k tile go to different accumulator
-//    columns (even columns see only the first 64 k of x, odd columns the last
-//    64), so each group's sum comes out separately and is scaled once:
-//    res += s * (acc - 128 * sum(x_group)) + b * sum(x_group), in f32;
-//  * x is staged once per CTA in shared memory, already permuted into the
-//    B-fragment order that matches the nibble pairing (k, k+4);
-//  * per row tile: one shuffle, one shared-memory reduction over the 8 warps.
+//  * the arithmetic is integer and exact. x is scaled by a power of two, rounded to a 23-bit
+//    integer and split into three signed base-256 digits; a packed word becomes tensor-core
+//    operands with two LOP3 and no shift: (w & 0x0f0f0f0f) holds its even nibbles as bytes,
+//    (w & 0xf0f0f0f0) its odd nibbles times 16, and the two kinds go to separate
+//    mma.sync.m16n8k32.u8.s8 accumulators (the second is divided by 16 afterwards). Earlier
+//    versions were bound by the integer pipe: a SIMT one (one PRMT and half an f32x2 FMA per
+//    nibble), then an fp16 mma.sync one (four LOP3 and a shift per word);
+//  * the eight accumulator columns are (digit, group parity): lane t of a quad ends up with the
+//    sums of digit t for both quantization groups of a k tile and both of its rows, so every
+//    lane folds four (row, group) sums per k tile with that group's scale -- and lane 3, whose
+//    digit does not exist, folds the bias term b * sum(x) instead. Accumulators start from the
+//    bit pattern of 12582912.0f, so the integer sum reads back as a float with no conversion;
+//  * x is staged once per CTA in shared memory, already as digit bytes in B-fragment order;
+//  * per row tile: two shuffles, one shared-memory reduction over the 8 warps.
 // One launch can run a whole list of GEMVs (a "plan"): the CTAs walk the concatenated row tiles
 // of all problems, the producer keeps streaming across problem boundaries, and the consumers
 // re-stage x only when the next problem reads a different x. A single GEMV is a one-problem list
@@ -57,39 +58,36 @@ constexpr int kStageSZ = 2 * 16 * 64;        // scales + biases of the span: 2 x
 constexpr int kMaxStages = 6;
 constexpr int kRedSlots = 8;                 // row tiles whose cross-warp sums may be pending
 
-// D = A * B + C on fp16 operands, f32 accumulate.
-__device__ __forceinline__ void mma_f16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                              uint32_t a3, uint32_t b0, uint32_t b1) {
+// D = A * B + C: A unsigned bytes [16 x 32], B signed bytes [32 x 8], s32 accumulate.
+__device__ __forceinline__ void mma_u8s8_16832(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
   asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 "
       "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// D = A * B: starts an accumulator chain without first clearing four registers.
-__device__ __forceinline__ void mma_f16_16816_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                                    uint32_t a3, uint32_t b0, uint32_t b1) {
+// D = A * B + init: starts an accumulator chain from a constant held in one register.
+__device__ __forceinline__ void mma_u8s8_16832_first(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                     uint32_t a3, uint32_t b0, uint32_t b1, int init) {
   asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 "
       "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-      : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+      : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(init));
 }
 
-// fp16 pairs straight out of a packed word, one LOP3 each:
-//   lo_magic(v) = (v & 0x000f000f) | 0x64006400 -> (1024 + nibble 0, 1024 + nibble 4) of v
-//   hi_magic(v) = (v & 0x00f000f0) | 0x54005400 -> (  64 + nibble 1,   64 + nibble 5) of v
-__device__ __forceinline__ uint32_t lo_magic(uint32_t v) {
-  uint32_t r;
-  asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xEA;" : "=r"(r) : "r"(v));
-  return r;
-}
-__device__ __forceinline__ uint32_t hi_magic(uint32_t v) {
-  uint32_t r;
-  asm("lop3.b32 %0, %1, 0x00f000f0, 0x54005400, 0xEA;" : "=r"(r) : "r"(v));
-  return r;
-}
+// Accumulators start at the bits of 12582912.0f (1.5 * 2^23): while |sum| < 2^22 the integer
+// result, read as a float, is exactly 12582912 + sum.
+constexpr int kAccInit = 0x4B400000;
+constexpr float kAccInitF = 12582912.0f;
+// Odd nibbles enter the tensor core as 16 * q: their accumulator, read as a float and divided by
+// 16, carries kAccInitF / 16; that and the even accumulator's kAccInitF are removed together.
+constexpr float kAccSurplus = kAccInitF / 16.0f + kAccInitF;  // 13369344, exact
+constexpr uint32_t kEvenNibbles = 0x0f0f0f0fu;
+constexpr uint32_t kOddNibbles = 0xf0f0f0f0u;
+constexpr int kXBytesPerKt = 3 * 128;  // staged x per k tile: 3 digits x [4 chunks x 32 bytes]
 
 enum : uint32_t { kRoleProducer = 1, kRoleConsumer = 2 };
 
@@ -119,10 +117,11 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
   const QmvProblem* probs = list ? list : &single;
 
   unsigned char* p0 = base_ptr + (size_t)stages * kStageBytes;
-  uint4* xperm = reinterpret_cast<uint4*>(p0);                   // [cap_kt][4 quarters][4 t] x 16 B
-  uint4* zero256 = xperm + (size_t)cap_kt * 16;                  // 320 bytes of zeros
-  float2* xg = reinterpret_cast<float2*>(zero256 + 20);          // [2*cap_kt] per group: surplus, sum of x
-  float* red = reinterpret_cast<float*>(xg + 2 * cap_kt);        // [kRedSlots][kConsWarps][16]
+  uint4* zero128 = reinterpret_cast<uint4*>(p0);                 // 128 bytes of zeros, 128-byte aligned
+  unsigned char* xq = p0 + 128;                                  // [cap_kt][3 digits][4 chunks][32 B]
+  float* xg = reinterpret_cast<float*>(xq + (size_t)cap_kt * kXBytesPerKt);  // [2*cap_kt] sum of x per group
+  float* zero16 = xg + 2 * cap_kt;                               // 16 bytes of zeros (cap_kt is even)
+  float* red = zero16 + 4;                                       // [kRedSlots][kConsWarps][16]
   uint32_t* red_cnt = reinterpret_cast<uint32_t*>(red + kRedSlots * kConsWarps * 16);  // [kRedSlots]
   uint32_t* amax_buf = red_cnt + kRedSlots;                      // [kConsWarps]
   uint64_t* bars = reinterpret_cast<uint64_t*>(amax_buf + kConsWarps);
@@ -146,7 +145,8 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
     for (int i = 0; i < kRedSlots; ++i) { red_cnt[i] = 0; }
     fence_mbar_init();
   }
-  if (threadIdx.x < 20) { zero256[threadIdx.x] = make_uint4(0, 0, 0, 0); }
+  if (threadIdx.x < 8) { zero128[threadIdx.x] = make_uint4(0, 0, 0, 0); }
+  if (threadIdx.x == 8) { *reinterpret_cast<uint4*>(zero16) = make_uint4(0, 0, 0, 0); }
   __syncthreads();
 
   if (warp == kConsWarps) {
@@ -202,116 +202,138 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
   // ---------------------------------------------------------------- consumers
   const int g = lane >> 2, t = lane & 3;
   const int rho = (g >> 1) | ((g & 1) << 2);  // stage row of MMA row g (g+8 -> rho+8): bank-conflict-free
-  const int item_row = rho + ((t >> 1) << 3); // the row whose (group t&1) sum this lane scales
-  const int par = t & 1;
 
   // x (and y) may be produced / consumed by the previous kernel.
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  // ---- staging of one x vector as fp16 (called by all consumer warps together).
-  // The tensor-core operands are fp16: a nibble sits in the low mantissa bits of 0x6400 (1024 + q)
-  // or, one nibble higher, of 0x5400 (64 + q), so no shift is needed for half of them. x is scaled
-  // by a power of two so that its largest magnitude lands in [2^14, 2^15): every bf16 value within
-  // 2^-28 of the maximum is then exact in fp16, and the scale is undone exactly at the end.
-  // 8 consecutive values (x0..x7) become the four B-fragment registers (x0,x4) (x1,x5) (x2,x6)
-  // (x3,x7). Per group of 64: xg[].x = 1024 * sum(even k) + 64 * sum(odd k), the surplus the
-  // magic constants add to the accumulator; xg[].y = sum of all 64, for the bias term.
-  constexpr int kXRegs = 8;  // chunks a thread keeps in registers between the two passes
+  // ---- staging of one x vector as signed digit bytes (called by all consumer warps together).
+  // x is scaled by a power of two so that its largest magnitude lands in [2^21, 2^22) and rounded
+  // to an integer X: every bf16 value within 2^-14 of the maximum is exact, smaller ones are off
+  // by at most 2^-22 of the maximum. X = d0 + 256 d1 + 65536 d2 with digits in [-128, 127]
+  // (adding 0x808080 turns the balanced digits into plain bytes; the xor takes the offset off
+  // again in two's complement). A thread converts 16 consecutive values (two packed words' worth,
+  // w0 and w1) and stores, per digit, the 16 bytes one lane feeds to an even-nibble MMA
+  // (x0,x2,x4,x6 of w0 | of w1) and an odd-nibble MMA (x1,x3,x5,x7 of w0 | of w1).
+  // xg[group] = sum of the 64 X of the group, for the bias term. Returns 1 / scale.
+  constexpr int kXRegs = 3;  // 16-value pieces a thread keeps in registers between the two passes
   auto stage_x = [&](const uint16_t* xr, int K, int KT) -> float {
-    const int chunks = KT * 16;  // 16-byte chunks of the padded x
-    uint4 xin[kXRegs];
+    const int pieces = KT * 8;  // 32-byte pieces of the padded x
+    uint4 xin[kXRegs][2];
     uint32_t amax = 0;  // largest |x| as bf16 bits (ordering of magnitudes == ordering of bit patterns)
-#pragma unroll
-    for (int r = 0; r < kXRegs; ++r) {
-      const int i = threadIdx.x + r * kConsThreads;
-      xin[r] = make_uint4(0, 0, 0, 0);
-      if (i * 8 < K) { xin[r] = *reinterpret_cast<const uint4*>(xr + i * 8); }
-    }
-#pragma unroll
-    for (int r = 0; r < kXRegs; ++r) {
-      const uint32_t v[4] = {xin[r].x, xin[r].y, xin[r].z, xin[r].w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        amax = max(amax, v[j] & 0x7fffu);
-        amax = max(amax, (v[j] >> 16) & 0x7fffu);
-      }
-    }
-    for (int i = threadIdx.x + kXRegs * kConsThreads; i * 8 < K; i += kConsThreads) {
-      const uint4 in = *reinterpret_cast<const uint4*>(xr + i * 8);
+    auto fold_amax = [&](const uint4& in) {
       const uint32_t v[4] = {in.x, in.y, in.z, in.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         amax = max(amax, v[j] & 0x7fffu);
         amax = max(amax, (v[j] >> 16) & 0x7fffu);
       }
+    };
+#pragma unroll
+    for (int r = 0; r < kXRegs; ++r) {
+      const int i = threadIdx.x + r * kConsThreads;
+      xin[r][0] = xin[r][1] = make_uint4(0, 0, 0, 0);
+      if (i * 16 < K) {
+        xin[r][0] = *reinterpret_cast<const uint4*>(xr + i * 16);
+        xin[r][1] = *reinterpret_cast<const uint4*>(xr + i * 16 + 8);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kXRegs; ++r) {
+      fold_amax(xin[r][0]);
+      fold_amax(xin[r][1]);
+    }
+    for (int i = threadIdx.x + kXRegs * kConsThreads; i * 16 < K; i += kConsThreads) {
+      fold_amax(*reinterpret_cast<const uint4*>(xr + i * 16));
+      fold_amax(*reinterpret_cast<const uint4*>(xr + i * 16 + 8));
     }
     amax = __reduce_max_sync(0xffffffffu, amax);
-    // the barrier also orders the previous problem's last reads of xperm / xg before the writes below
+    // the barrier also orders the previous problem's last reads of xq / xg before the writes below
     if (lane == 0) { amax_buf[warp] = amax; }
     asm volatile("bar.sync 1, %0;" ::"n"(kConsThreads) : "memory");  // consumers only
     amax = 0;
 #pragma unroll
     for (int ww = 0; ww < kConsWarps; ++ww) { amax = max(amax, amax_buf[ww]); }
     int e = (int)(amax >> 7);            // biased exponent of the largest magnitude
-    e = min(max(e, 16), 240);            // all-zero / denormal / huge x: keep both factors normal
-    const float x_scale = __uint_as_float((uint32_t)(268 - e) << 23);  // 2^(141 - e): max |x| -> [2^14, 2^15)
-    const float x_unscale = __uint_as_float((uint32_t)(e - 14) << 23); // its exact inverse
-    auto convert_chunk = [&](int i, const uint4& in) {  // called by whole warps: shuffles inside
-      const bool live = i < chunks;
-      const uint32_t v[4] = {in.x, in.y, in.z, in.w};
-      uint32_t hb[4];
-      float se = 0.0f, so = 0.0f;
+    e = min(max(e, 22), 254);            // all-zero / denormal x: keep both factors normal
+    const float x_scale = __uint_as_float((uint32_t)(275 - e) << 23);   // 2^(148 - e): max |x| -> [2^21, 2^22)
+    const float x_unscale = __uint_as_float((uint32_t)(e - 21) << 23);  // its exact inverse
+    auto convert_piece = [&](int i, const uint4& in0, const uint4& in1) {  // whole warps: shuffles inside
+      const bool live = i < pieces;
+      const uint32_t v[8] = {in0.x, in0.y, in0.z, in0.w, in1.x, in1.y, in1.z, in1.w};
+      uint32_t z[16];
+      int sum = 0;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const __half2 h = __floats2half2_rn(__uint_as_float(v[j] << 16) * x_scale,
-                                            __uint_as_float(v[j] & 0xffff0000u) * x_scale);
-        const float2 f = __half22float2(h);  // what the tensor core will see
-        se += f.x;
-        so += f.y;
-        hb[j] = *reinterpret_cast<const uint32_t*>(&h);
+      for (int j = 0; j < 8; ++j) {
+        const int lo = __float2int_rn(__uint_as_float(v[j] << 16) * x_scale);
+        const int hi = __float2int_rn(__uint_as_float(v[j] & 0xffff0000u) * x_scale);
+        sum += lo + hi;
+        z[2 * j] = ((uint32_t)lo + 0x808080u) ^ 0x808080u;
+        z[2 * j + 1] = ((uint32_t)hi + 0x808080u) ^ 0x808080u;
       }
-      uint4 out;
-      asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(out.x) : "r"(hb[0]), "r"(hb[2]));
-      asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(out.y) : "r"(hb[0]), "r"(hb[2]));
-      asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(out.z) : "r"(hb[1]), "r"(hb[3]));
-      asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(out.w) : "r"(hb[1]), "r"(hb[3]));
-      const int kt = i >> 4, tt = (i >> 2) & 3, q = i & 3;
-      if (live) { xperm[(kt * 4 + q) * 4 + tt] = out; }
+      // byte d of za, zb, zc, zd -> one word per digit d
+      auto digits_of4 = [](uint32_t za, uint32_t zb, uint32_t zc, uint32_t zd, uint32_t (&out)[3]) {
+        const uint32_t t0 = __byte_perm(za, zb, 0x5140), t1 = __byte_perm(zc, zd, 0x5140);
+        const uint32_t t2 = __byte_perm(za, zb, 0x0062), t3 = __byte_perm(zc, zd, 0x0062);
+        out[0] = __byte_perm(t0, t1, 0x5410);
+        out[1] = __byte_perm(t0, t1, 0x7632);
+        out[2] = __byte_perm(t2, t3, 0x5410);
+      };
+      uint32_t e0[3], o0[3], e1[3], o1[3];
+      digits_of4(z[0], z[2], z[4], z[6], e0);
+      digits_of4(z[1], z[3], z[5], z[7], o0);
+      digits_of4(z[8], z[10], z[12], z[14], e1);
+      digits_of4(z[9], z[11], z[13], z[15], o1);
+      if (live) {
+        unsigned char* dst = xq + (size_t)(i >> 3) * kXBytesPerKt + (i & 7) * 16;
 #pragma unroll
-      for (int off = 1; off < 8; off <<= 1) {
-        se += __shfl_xor_sync(0xffffffffu, se, off);
-        so += __shfl_xor_sync(0xffffffffu, so, off);
+        for (int d = 0; d < 3; ++d) {
+          *reinterpret_cast<uint4*>(dst + d * 128) = make_uint4(e0[d], e1[d], o0[d], o1[d]);
+        }
       }
-      if (live && (i & 7) == 0) { xg[i >> 3] = make_float2(__fmaf_rn(1024.0f, se, 64.0f * so), se + so); }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      if (live && (i & 3) == 0) { xg[i >> 2] = (float)sum; }
     };
 #pragma unroll
     for (int r = 0; r < kXRegs; ++r) {
       const int i = threadIdx.x + r * kConsThreads;
-      if (i - lane < chunks) { convert_chunk(i, xin[r]); }  // warp-uniform
+      if (i - lane < pieces) { convert_piece(i, xin[r][0], xin[r][1]); }  // warp-uniform
     }
-    for (int i = threadIdx.x + kXRegs * kConsThreads; i - lane < chunks; i += kConsThreads) {
-      uint4 in = make_uint4(0, 0, 0, 0);
-      if (i * 8 < K) { in = *reinterpret_cast<const uint4*>(xr + i * 8); }
-      convert_chunk(i, in);
+    for (int i = threadIdx.x + kXRegs * kConsThreads; i - lane < pieces; i += kConsThreads) {
+      uint4 in0 = make_uint4(0, 0, 0, 0), in1 = in0;
+      if (i * 16 < K) {
+        in0 = *reinterpret_cast<const uint4*>(xr + i * 16);
+        in1 = *reinterpret_cast<const uint4*>(xr + i * 16 + 8);
+      }
+      convert_piece(i, in0, in1);
     }
     asm volatile("bar.sync 1, %0;" ::"n"(kConsThreads) : "memory");
     return x_unscale;
   };
 
-  // Even accumulator columns see the first group of a k tile (chunks t = 0, 1),
-  // odd columns the second (t = 2, 3); column c is supplied by the lanes with g == c.
-  // The other lanes read zeros from a block laid out like one k tile of xperm
-  // (+4: quarter q of the zero block sits in the banks quarter q+1 of the data uses, so the two
-  // halves of a warp never collide).
-  const bool real = ((g & 1) == 0) ? (t < 2) : (t >= 2);
-  const uint4* xb_base = real ? xperm + t : zero256 + 4;
-  const int xb_kt = real ? 16 : 0;
+  // Accumulator column c of an MMA is supplied by the lanes with g == c and stands for
+  // (digit c >> 1, group parity c & 1): those lanes feed the digit's bytes if their chunk t lies
+  // in that group (t >> 1 == parity) and zeros otherwise (digit 3 does not exist: always zeros).
+  // Zeros come from a block laid out like one digit of one k tile, read at the other 16-byte half
+  // of the lane's 32-byte slot, so real and zero lanes of a quarter warp never share a bank.
+  const bool real = (g < 6) && ((t >> 1) == (g & 1));
+  const unsigned char* xop_base =
+      real ? xq + (g >> 1) * 128 + t * 32 : reinterpret_cast<const unsigned char*>(zero128) + t * 32 + 16;
+  const int xop_kt = real ? kXBytesPerKt : 0;
+  const int xop_second = real ? 16 : -16;
+  // Lane 3 of a quad folds the bias term: it reads biases where the others read scales, and the
+  // group sums of x where the others read zeros.
+  const bool bias_lane = t == 3;
+  const float* xs_base = bias_lane ? xg : zero16;
+  const int xs_box = bias_lane ? 4 : 0;
+  const float digit_weight = t == 1 ? 256.0f : t == 2 ? 65536.0f : 1.0f;
 
   // byte offsets of this lane's two 16-byte reads inside its box, per half (k tile) of the box
   const uint32_t off_h0 = (uint32_t)rho * 128u + (uint32_t)(((0 + t) ^ rho) << 4);
   const uint32_t off_h1 = (uint32_t)rho * 128u + (uint32_t)(((4 + t) ^ rho) << 4);
-  const uint32_t sz_off = (uint32_t)kStageW + (uint32_t)item_row * 64u + (uint32_t)warp * 8u;
-  const uint32_t sel = par ? 0x3244u : 0x1044u;  // PRMT: this lane's bf16 of a pair -> f32 bits
+  // this lane's 8 bytes (4 groups of the warp's box) of row rho in the stage's scales or biases
+  const uint32_t sz_off = (uint32_t)kStageW + (bias_lane ? (uint32_t)kStageSZ / 2 : 0u) + (uint32_t)rho * 64u +
+                          (uint32_t)warp * 8u;
 
   uint32_t tile_seq = 0, ph = 0;
   int s = 0;
@@ -355,7 +377,7 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
       }
     }
     const int tile = gt - tb;
-    float res = 0.0f;
+    float res_a = 0.0f, res_b = 0.0f;  // rows rho and rho + 8 of the tile: this lane's digit (or bias) share
     for (int st = 0; st < SPT; ++st) {
       if (!warp_wait(bar_full(s), ph, (1u << 8) | kRoleConsumer, abort_flag, &g_qmv_status)) {
         ok = false;
@@ -365,66 +387,65 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
       const int kt0 = st * 16 + warp * 2;  // this warp's box holds k tiles kt0 and kt0 + 1
       if (kt0 < KT) {
         const unsigned char* box = sb + warp * kBoxBytes;
-        // both k tiles of the box at once: four independent accumulator chains
-        const uint4 ra0 = *reinterpret_cast<const uint4*>(box + off_h0);
-        const uint4 rb0 = *reinterpret_cast<const uint4*>(box + off_h0 + 1024);
-        const uint4 ra1 = *reinterpret_cast<const uint4*>(box + off_h1);
+        const uint4 ra0 = *reinterpret_cast<const uint4*>(box + off_h0);         // row rho,     k tile kt0
+        const uint4 rb0 = *reinterpret_cast<const uint4*>(box + off_h0 + 1024);  // row rho + 8
+        const uint4 ra1 = *reinterpret_cast<const uint4*>(box + off_h1);         // row rho,     k tile kt0 + 1
         const uint4 rb1 = *reinterpret_cast<const uint4*>(box + off_h1 + 1024);
-        uint2 sw = make_uint2(0, 0), zw = make_uint2(0, 0);
+        const unsigned char* xop = xop_base + kt0 * xop_kt;
+        const uint4 x00 = *reinterpret_cast<const uint4*>(xop);                  // kt0, words 0 1
+        const uint4 x01 = *reinterpret_cast<const uint4*>(xop + xop_second);     // kt0, words 2 3
+        const uint4 x10 = *reinterpret_cast<const uint4*>(xop + xop_kt);
+        const uint4 x11 = *reinterpret_cast<const uint4*>(xop + xop_kt + xop_second);
+        uint2 sa, sb2;  // 4 consecutive groups' scales (or biases) of rows rho, rho + 8
         if (sz_tma) {
-          sw = *reinterpret_cast<const uint2*>(sb + sz_off);
-          zw = *reinterpret_cast<const uint2*>(sb + sz_off + kStageSZ / 2);
-        }
-        const int kt1 = kt0 + 1;
-        float c0[4], d0[4], c1[4], d1[4];
-        const uint4* xb0 = xb_base + kt0 * xb_kt;
-        const uint4* xb1 = xb_base + kt1 * xb_kt;
-        const uint32_t a0[4] = {ra0.x, ra0.y, ra0.z, ra0.w}, b0[4] = {rb0.x, rb0.y, rb0.z, rb0.w};
-        const uint32_t a1[4] = {ra1.x, ra1.y, ra1.z, ra1.w}, b1[4] = {rb1.x, rb1.y, rb1.z, rb1.w};
-#pragma unroll
-        for (int wd = 0; wd < 4; ++wd) {
-          const uint4 x0 = xb0[wd * 4];
-          const uint4 x1 = xb1[wd * 4];
-          const uint32_t a0h = a0[wd] >> 8, b0h = b0[wd] >> 8, a1h = a1[wd] >> 8, b1h = b1[wd] >> 8;
-          // nibble pairs (n0,n4) (n1,n5) of each word, then (n2,n6) (n3,n7) from the word >> 8
-          if (wd == 0) {
-            mma_f16_16816_first(c0, lo_magic(a0[wd]), lo_magic(b0[wd]), hi_magic(a0[wd]), hi_magic(b0[wd]), x0.x, x0.y);
-            mma_f16_16816_first(c1, lo_magic(a1[wd]), lo_magic(b1[wd]), hi_magic(a1[wd]), hi_magic(b1[wd]), x1.x, x1.y);
-            mma_f16_16816_first(d0, lo_magic(a0h), lo_magic(b0h), hi_magic(a0h), hi_magic(b0h), x0.z, x0.w);
-            mma_f16_16816_first(d1, lo_magic(a1h), lo_magic(b1h), hi_magic(a1h), hi_magic(b1h), x1.z, x1.w);
-          } else {
-            mma_f16_16816(c0, lo_magic(a0[wd]), lo_magic(b0[wd]), hi_magic(a0[wd]), hi_magic(b0[wd]), x0.x, x0.y);
-            mma_f16_16816(c1, lo_magic(a1[wd]), lo_magic(b1[wd]), hi_magic(a1[wd]), hi_magic(b1[wd]), x1.x, x1.y);
-            mma_f16_16816(d0, lo_magic(a0h), lo_magic(b0h), hi_magic(a0h), hi_magic(b0h), x0.z, x0.w);
-            mma_f16_16816(d1, lo_magic(a1h), lo_magic(b1h), hi_magic(a1h), hi_magic(b1h), x1.z, x1.w);
-          }
-        }
-        // per unit: [0] = (row g, first group) [1] = (row g, second) [2] = (row g+8, first) [3] = (row g+8, second)
-        const float v0 = (t == 0 ? c0[0] : t == 1 ? c0[1] : t == 2 ? c0[2] : c0[3]) +
-                         (t == 0 ? d0[0] : t == 1 ? d0[1] : t == 2 ? d0[2] : d0[3]);
-        const float v1 = (t == 0 ? c1[0] : t == 1 ? c1[1] : t == 2 ? c1[2] : c1[3]) +
-                         (t == 0 ? d1[0] : t == 1 ? d1[1] : t == 2 ? d1[2] : d1[3]);
-        const float2 xs0 = xg[2 * kt0 + par];
-        const float2 xs1 = xg[2 * kt1 + par];
-        uint32_t s0, z0, s1, z1;
-        if (sz_tma) {
-          asm("prmt.b32 %0, %1, %2, %3;" : "=r"(s0) : "r"(sw.x), "r"(0u), "r"(sel));
-          asm("prmt.b32 %0, %1, %2, %3;" : "=r"(z0) : "r"(zw.x), "r"(0u), "r"(sel));
-          asm("prmt.b32 %0, %1, %2, %3;" : "=r"(s1) : "r"(sw.y), "r"(0u), "r"(sel));
-          asm("prmt.b32 %0, %1, %2, %3;" : "=r"(z1) : "r"(zw.y), "r"(0u), "r"(sel));
+          sa = *reinterpret_cast<const uint2*>(sb + sz_off);
+          sb2 = *reinterpret_cast<const uint2*>(sb + sz_off + 512);
         } else {
           // clamped onto valid data: a clamped group meets x == 0, a clamped row is never stored
-          const int64_t ri = min(tile * 16 + item_row, N - 1);
-          const int g0 = min(2 * kt0 + par, G - 1), g1 = min(2 * kt1 + par, G - 1);
-          s0 = ldg_nc_u16(scales + ri * G + g0) << 16;
-          z0 = ldg_nc_u16(biases + ri * G + g0) << 16;
-          s1 = ldg_nc_u16(scales + ri * G + g1) << 16;
-          z1 = ldg_nc_u16(biases + ri * G + g1) << 16;
+          const uint16_t* src = bias_lane ? biases : scales;
+          const int64_t r_a = min(tile * 16 + rho, N - 1), r_b = min(tile * 16 + rho + 8, N - 1);
+          const int g0 = min(2 * kt0, G - 1), g1 = min(2 * kt0 + 1, G - 1);
+          const int g2 = min(2 * kt0 + 2, G - 1), g3 = min(2 * kt0 + 3, G - 1);
+          sa.x = ldg_nc_u16(src + r_a * G + g0) | (ldg_nc_u16(src + r_a * G + g1) << 16);
+          sa.y = ldg_nc_u16(src + r_a * G + g2) | (ldg_nc_u16(src + r_a * G + g3) << 16);
+          sb2.x = ldg_nc_u16(src + r_b * G + g0) | (ldg_nc_u16(src + r_b * G + g1) << 16);
+          sb2.y = ldg_nc_u16(src + r_b * G + g2) | (ldg_nc_u16(src + r_b * G + g3) << 16);
         }
-        res = __fmaf_rn(__uint_as_float(s0), v0 - xs0.x, res);
-        res = __fmaf_rn(__uint_as_float(z0), xs0.y, res);
-        res = __fmaf_rn(__uint_as_float(s1), v1 - xs1.x, res);
-        res = __fmaf_rn(__uint_as_float(z1), xs1.y, res);
+        const float4 xs = *reinterpret_cast<const float4*>(xs_base + (kt0 >> 1) * xs_box);
+        // four independent chains: even / odd nibbles of each k tile
+        int ce0[4], co0[4], ce1[4], co1[4];
+        mma_u8s8_16832_first(ce0, ra0.x & kEvenNibbles, rb0.x & kEvenNibbles, ra0.y & kEvenNibbles,
+                             rb0.y & kEvenNibbles, x00.x, x00.y, kAccInit);
+        mma_u8s8_16832_first(ce1, ra1.x & kEvenNibbles, rb1.x & kEvenNibbles, ra1.y & kEvenNibbles,
+                             rb1.y & kEvenNibbles, x10.x, x10.y, kAccInit);
+        mma_u8s8_16832_first(co0, ra0.x & kOddNibbles, rb0.x & kOddNibbles, ra0.y & kOddNibbles,
+                             rb0.y & kOddNibbles, x00.z, x00.w, kAccInit);
+        mma_u8s8_16832_first(co1, ra1.x & kOddNibbles, rb1.x & kOddNibbles, ra1.y & kOddNibbles,
+                             rb1.y & kOddNibbles, x10.z, x10.w, kAccInit);
+        mma_u8s8_16832(ce0, ra0.z & kEvenNibbles, rb0.z & kEvenNibbles, ra0.w & kEvenNibbles,
+                       rb0.w & kEvenNibbles, x01.x, x01.y);
+        mma_u8s8_16832(ce1, ra1.z & kEvenNibbles, rb1.z & kEvenNibbles, ra1.w & kEvenNibbles,
+                       rb1.w & kEvenNibbles, x11.x, x11.y);
+        mma_u8s8_16832(co0, ra0.z & kOddNibbles, rb0.z & kOddNibbles, ra0.w & kOddNibbles,
+                       rb0.w & kOddNibbles, x01.z, x01.w);
+        mma_u8s8_16832(co1, ra1.z & kOddNibbles, rb1.z & kOddNibbles, ra1.w & kOddNibbles,
+                       rb1.w & kOddNibbles, x11.z, x11.w);
+        // c[0] = (row rho, first group of the k tile) c[1] = (rho, second) c[2] = (rho + 8, first)
+        // c[3] = (rho + 8, second); value = even + odd / 16 - surplus (+ sum of x in a bias lane,
+        // whose accumulators hold the bare initial value)
+        const float k0 = xs.x - kAccSurplus, k1 = xs.y - kAccSurplus;
+        const float k2 = xs.z - kAccSurplus, k3 = xs.w - kAccSurplus;
+        auto val = [](int even, int odd, float k) {
+          return __int_as_float(even) + __fmaf_rn(__int_as_float(odd), 0.0625f, k);
+        };
+        res_a = __fmaf_rn(__uint_as_float(sa.x << 16), val(ce0[0], co0[0], k0), res_a);
+        res_a = __fmaf_rn(__uint_as_float(sa.x & 0xffff0000u), val(ce0[1], co0[1], k1), res_a);
+        res_a = __fmaf_rn(__uint_as_float(sa.y << 16), val(ce1[0], co1[0], k2), res_a);
+        res_a = __fmaf_rn(__uint_as_float(sa.y & 0xffff0000u), val(ce1[1], co1[1], k3), res_a);
+        res_b = __fmaf_rn(__uint_as_float(sb2.x << 16), val(ce0[2], co0[2], k0), res_b);
+        res_b = __fmaf_rn(__uint_as_float(sb2.x & 0xffff0000u), val(ce0[3], co0[3], k1), res_b);
+        res_b = __fmaf_rn(__uint_as_float(sb2.y << 16), val(ce1[2], co1[2], k2), res_b);
+        res_b = __fmaf_rn(__uint_as_float(sb2.y & 0xffff0000u), val(ce1[3], co1[3], k3), res_b);
       }
       __syncwarp();
       if (lane == 0) { mbar_arrive(bar_empty(s)); }  // this warp's part of the stage is in registers
@@ -434,12 +455,18 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
       }
     }
     if (!ok) { break; }
-    // Both groups of a row, then the 8 warps' K slices: every warp posts its 16 partial sums and
-    // moves on; the warp that posts last adds them in warp order (so the result does not depend
-    // on arrival order) and stores. The ring of kRedSlots tiles is deeper than a warp can run ahead.
-    res += __shfl_xor_sync(0xffffffffu, res, 1);
+    // The four lanes of a quad (three digits + bias) are summed so that even lanes end with row
+    // rho and odd lanes with row rho + 8; then the 8 warps' K slices: every warp posts its 16
+    // partial sums and moves on; the warp that posts last adds them in warp order (so the result
+    // does not depend on arrival order) and stores. The ring of kRedSlots tiles is deeper than a
+    // warp can run ahead.
+    res_a *= digit_weight;
+    res_b *= digit_weight;
+    float keep = (t & 1) ? res_b : res_a;
+    keep += __shfl_xor_sync(0xffffffffu, (t & 1) ? res_a : res_b, 1);
+    keep += __shfl_xor_sync(0xffffffffu, keep, 2);
     const int slot = tile_seq % kRedSlots;
-    if (par == 0) { red[(slot * kConsWarps + warp) * 16 + item_row] = res; }
+    if (t < 2) { red[(slot * kConsWarps + warp) * 16 + rho + 8 * t] = keep; }
     __syncwarp();
     uint32_t last = 0;
     if (lane == 0) {
@@ -472,7 +499,7 @@ struct LaunchShape {
 
 LaunchShape shape_for(int cap_kt) {
   const size_t stage_bytes = kStageW + kStageSZ;
-  const size_t fixed = 1024 /*alignment slack*/ + (size_t)cap_kt * 256 + 320 + (size_t)2 * cap_kt * 8 +
+  const size_t fixed = 1024 /*alignment slack*/ + 128 + (size_t)cap_kt * kXBytesPerKt + (size_t)2 * cap_kt * 4 + 16 +
                        kRedSlots * kConsWarps * 16 * 4 + kRedSlots * 4 + kConsWarps * 4 +
                        2 * kMaxStages * 8 + 16;
   const size_t budget = 112 * 1024;  // two CTAs per SM
