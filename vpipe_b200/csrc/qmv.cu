@@ -108,13 +108,25 @@ static_assert(sizeof(QmvProblem) % 64 == 0, "problem records are laid out back t
 
 __global__ void __launch_bounds__(kThreads, 2)
 affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProblem* __restrict__ list,
-                        int total_tiles, int stages, int cap_kt) {
+                        const int2* __restrict__ ranges, int total_tiles, int stages, int cap_kt) {
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t raw = smem_u32(smem_dyn);
   const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled boxes need 1024-byte alignment
   unsigned char* base_ptr = smem_dyn + (base - raw);
   constexpr int kStageBytes = kStageW + kStageSZ;
   const QmvProblem* probs = list ? list : &single;
+  // Every CTA takes one contiguous run of the launch's row tiles (and so meets few different x):
+  // from the host's table {first tile, its problem} for a list, evenly split for a single GEMV.
+  int gt_begin, gt_end;
+  if (ranges) {
+    const int2 a = ranges[blockIdx.x], b = ranges[blockIdx.x + 1];
+    gt_begin = a.x;
+    gt_end = b.x;
+    probs += a.y;
+  } else {
+    gt_begin = (int)(((int64_t)total_tiles * blockIdx.x) / gridDim.x);
+    gt_end = (int)(((int64_t)total_tiles * (blockIdx.x + 1)) / gridDim.x);
+  }
 
   unsigned char* p0 = base_ptr + (size_t)stages * kStageBytes;
   uint4* zero128 = reinterpret_cast<uint4*>(p0);                 // 128 bytes of zeros, 128-byte aligned
@@ -159,7 +171,7 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
       int pi = 0;
       const QmvProblem* P = probs;
       int tb = P->tile_begin, rt = P->row_tiles;
-      for (int gt = blockIdx.x; gt < total_tiles && ok; gt += gridDim.x) {
+      for (int gt = gt_begin; gt < gt_end && ok; ++gt) {
         while (gt >= tb + rt) {
           P = probs + (++pi);
           tb = P->tile_begin;
@@ -210,7 +222,7 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
   // x is scaled by a power of two so that its largest magnitude lands in [2^21, 2^22) and rounded
   // to an integer X: every bf16 value within 2^-14 of the maximum is exact, smaller ones are off
   // by at most 2^-22 of the maximum. X = d0 + 256 d1 + 65536 d2 with digits in [-128, 127]
-  // (adding 0x808080 turns the balanced digits into plain bytes; the xor takes the offset off
+  // (adding 0x808080 turns the balanced digits into plain bytes; an xor takes the offset off
   // again in two's complement). A thread converts 16 consecutive values (two packed words' worth,
   // w0 and w1) and stores, per digit, the 16 bytes one lane feeds to an even-nibble MMA
   // (x0,x2,x4,x6 of w0 | of w1) and an odd-nibble MMA (x1,x3,x5,x7 of w0 | of w1).
@@ -260,23 +272,27 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
     auto convert_piece = [&](int i, const uint4& in0, const uint4& in1) {  // whole warps: shuffles inside
       const bool live = i < pieces;
       const uint32_t v[8] = {in0.x, in0.y, in0.z, in0.w, in1.x, in1.y, in1.z, in1.w};
+      // round(x * scale) without the conversion unit: the low bits of fma(x, scale, 1.5 * 2^23)
+      // are 0x4B400000 + X. One add moves that to X + 0x808080 (bytes 0..2: digits + 128; byte 3
+      // is never used); the + 128 is taken off the transposed words below.
       uint32_t z[16];
-      int sum = 0;
+      uint32_t sum = 0;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const int lo = __float2int_rn(__uint_as_float(v[j] << 16) * x_scale);
-        const int hi = __float2int_rn(__uint_as_float(v[j] & 0xffff0000u) * x_scale);
+        const uint32_t lo = __float_as_uint(__fmaf_rn(__uint_as_float(v[j] << 16), x_scale, kAccInitF));
+        const uint32_t hi = __float_as_uint(__fmaf_rn(__uint_as_float(v[j] & 0xffff0000u), x_scale, kAccInitF));
         sum += lo + hi;
-        z[2 * j] = ((uint32_t)lo + 0x808080u) ^ 0x808080u;
-        z[2 * j + 1] = ((uint32_t)hi + 0x808080u) ^ 0x808080u;
+        z[2 * j] = lo + (0x808080u - (uint32_t)kAccInit);
+        z[2 * j + 1] = hi + (0x808080u - (uint32_t)kAccInit);
       }
+      sum -= 16u * (uint32_t)kAccInit;  // = sum of the 16 X, modulo 2^32
       // byte d of za, zb, zc, zd -> one word per digit d
       auto digits_of4 = [](uint32_t za, uint32_t zb, uint32_t zc, uint32_t zd, uint32_t (&out)[3]) {
         const uint32_t t0 = __byte_perm(za, zb, 0x5140), t1 = __byte_perm(zc, zd, 0x5140);
         const uint32_t t2 = __byte_perm(za, zb, 0x0062), t3 = __byte_perm(zc, zd, 0x0062);
-        out[0] = __byte_perm(t0, t1, 0x5410);
-        out[1] = __byte_perm(t0, t1, 0x7632);
-        out[2] = __byte_perm(t2, t3, 0x5410);
+        out[0] = __byte_perm(t0, t1, 0x5410) ^ 0x80808080u;
+        out[1] = __byte_perm(t0, t1, 0x7632) ^ 0x80808080u;
+        out[2] = __byte_perm(t2, t3, 0x5410) ^ 0x80808080u;
       };
       uint32_t e0[3], o0[3], e1[3], o1[3];
       digits_of4(z[0], z[2], z[4], z[6], e0);
@@ -292,7 +308,7 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
       }
       sum += __shfl_xor_sync(0xffffffffu, sum, 1);
       sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      if (live && (i & 3) == 0) { xg[i >> 2] = (float)sum; }
+      if (live && (i & 3) == 0) { xg[i >> 2] = (float)(int)sum; }
     };
 #pragma unroll
     for (int r = 0; r < kXRegs; ++r) {
@@ -351,7 +367,7 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
   const uint16_t* biases = nullptr;
   __nv_bfloat16* y = nullptr;
   bool fresh = true;
-  for (int gt = blockIdx.x; gt < total_tiles && ok; gt += gridDim.x, ++tile_seq) {
+  for (int gt = gt_begin; gt < gt_end && ok; ++gt, ++tile_seq) {
     while (gt >= tb + rt) {
       P = probs + (++pi);
       tb = P->tile_begin;
@@ -539,13 +555,46 @@ int fill_problem(QmvProblem* p, const uint32_t* w, const uint16_t* scales, const
   return VPQ_OK;
 }
 
-int launch_list(const QmvProblem& single, const QmvProblem* list, int total_tiles, int cap_kt,
+constexpr int kMaxGrid = 1023;  // CTAs a range table has room for
+
+int grid_for(int total_tiles) {
+  int cap = 2 * num_sms();
+  if (cap > kMaxGrid) { cap = kMaxGrid; }
+  return total_tiles < cap ? total_tiles : cap;
+}
+
+// Splits the concatenated row tiles of `count` problems into `grid` contiguous runs of about equal
+// cost (a tile costs its stages plus a fixed share for the reduction and the store).
+// out[b] = {first tile of CTA b, index of the problem it belongs to}, out[grid] closes the list.
+void build_ranges(const QmvProblem* p, size_t count, int grid, int2* out) {
+  auto tile_cost = [](const QmvProblem& q) {
+    const int nb = (q.K + 255) >> 8;
+    return (int64_t)(4 * ((nb + kBoxesPerStage - 1) / kBoxesPerStage) + 3);
+  };
+  int64_t total = 0;
+  for (size_t r = 0; r < count; ++r) { total += tile_cost(p[r]) * p[r].row_tiles; }
+  size_t r = 0;
+  int64_t before = 0;  // cost of the problems before r
+  for (int b = 0; b < grid; ++b) {
+    const int64_t target = total * b / grid;
+    while (r + 1 < count && before + tile_cost(p[r]) * p[r].row_tiles <= target) {
+      before += tile_cost(p[r]) * p[r].row_tiles;
+      ++r;
+    }
+    int t = (int)((target - before) / tile_cost(p[r]));
+    if (t > p[r].row_tiles) { t = p[r].row_tiles; }
+    out[b] = make_int2(p[r].tile_begin + t, (int)r);
+  }
+  const QmvProblem& last = p[count - 1];
+  out[grid] = make_int2(last.tile_begin + last.row_tiles, (int)(count - 1));
+}
+
+int launch_list(const QmvProblem& single, const QmvProblem* list, const int2* ranges, int total_tiles, int cap_kt,
                 cudaStream_t st) {
   const LaunchShape ls = shape_for(cap_kt);
   auto kern = affine_qmv_w4g64_kernel;
   VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ls.smem));
-  const int cap = 2 * num_sms();
-  const int ctas = total_tiles < cap ? total_tiles : cap;
+  const int ctas = grid_for(total_tiles);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)ctas, 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
@@ -556,7 +605,7 @@ int launch_list(const QmvProblem& single, const QmvProblem* list, int total_tile
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  VPQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, single, list, total_tiles, ls.stages, cap_kt));
+  VPQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, single, list, ranges, total_tiles, ls.stages, cap_kt));
   return VPQ_OK;
 }
 
@@ -598,6 +647,7 @@ using namespace vpq;
 
 struct vpq_qmv_plan_s {
   const QmvProblem* list_dev;
+  const int2* ranges_dev;
   int count;        // problems (one per GEMV row)
   int total_tiles;
   int cap_kt;
@@ -618,7 +668,7 @@ extern "C" int vpq_affine_qmv_w4g64_bf16(const uint32_t* w, const void* scales, 
                               (int)K, (int)N, 0)) {
       return rc;
     }
-    if (int rc = launch_list(p, nullptr, p.row_tiles, cap_kt, st)) { return rc; }
+    if (int rc = launch_list(p, nullptr, nullptr, p.row_tiles, cap_kt, st)) { return rc; }
   }
   return VPQ_OK;
 }
@@ -639,7 +689,7 @@ extern "C" size_t vpq_qmv_plan_bytes(const vpq_linear_desc* d, int count) {
   if (!d || count <= 0) { return 0; }
   size_t rows = 0;
   for (int i = 0; i < count; ++i) { rows += d[i].M > 0 ? (size_t)d[i].M : 0; }
-  return rows * sizeof(QmvProblem) + 64;
+  return rows * sizeof(QmvProblem) + 64 + (kMaxGrid + 1) * sizeof(int2);
 }
 
 extern "C" int vpq_qmv_plan_create(const vpq_linear_desc* d, int count, void* workspace, size_t bytes,
@@ -682,14 +732,23 @@ extern "C" int vpq_qmv_plan_create(const vpq_linear_desc* d, int count, void* wo
     }
   }
   const uintptr_t dev = (reinterpret_cast<uintptr_t>(workspace) + 63) & ~(uintptr_t)63;
+  const uintptr_t dev_ranges = dev + rows * sizeof(QmvProblem);
+  const int grid = grid_for(tiles);
+  int2 host_ranges[kMaxGrid + 1];
+  build_ranges(host, rows, grid, host_ranges);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e = cudaMemcpyAsync(reinterpret_cast<void*>(dev), host, rows * sizeof(QmvProblem),
                                   cudaMemcpyHostToDevice, st);
+  if (e == cudaSuccess) {
+    e = cudaMemcpyAsync(reinterpret_cast<void*>(dev_ranges), host_ranges, (size_t)(grid + 1) * sizeof(int2),
+                        cudaMemcpyHostToDevice, st);
+  }
   if (e == cudaSuccess) { e = cudaStreamSynchronize(st); }
   std::free(host);
   if (e != cudaSuccess) { return fail(VPQ_ERR_CUDA, "qmv_plan_create: copy failed: %s", cudaGetErrorString(e)); }
   vpq_qmv_plan* plan = new vpq_qmv_plan_s();
   plan->list_dev = reinterpret_cast<const QmvProblem*>(dev);
+  plan->ranges_dev = reinterpret_cast<const int2*>(dev_ranges);
   plan->count = (int)rows;
   plan->total_tiles = tiles;
   plan->cap_kt = cap_kt;
@@ -703,7 +762,8 @@ extern "C" int vpq_qmv_plan_run(const vpq_qmv_plan* plan, void* stream) {
   if (int rc = require_sm100()) { return rc; }
   QmvProblem unused;
   std::memset(&unused, 0, sizeof(unused));
-  return launch_list(unused, plan->list_dev, plan->total_tiles, plan->cap_kt, static_cast<cudaStream_t>(stream));
+  return launch_list(unused, plan->list_dev, plan->ranges_dev, plan->total_tiles, plan->cap_kt,
+                     static_cast<cudaStream_t>(stream));
 }
 
 // ---------------------------------------------------------------- no-allocation variant
@@ -711,7 +771,8 @@ extern "C" int vpq_qmv_plan_run(const vpq_qmv_plan* plan, void* stream) {
 // list in a fixed array that is part of the library image, so the call neither allocates nor needs
 // a caller workspace. Every GPU that loads the library carries the array (28 KB) until exit.
 constexpr int kNoAllocMaxRows = 64;  // GEMV rows (sum of M over the set) one call can take
-static __device__ __align__(256) unsigned char g_noalloc_descs[kNoAllocMaxRows * sizeof(QmvProblem)];
+static __device__ __align__(256) unsigned char
+    g_noalloc_descs[kNoAllocMaxRows * sizeof(QmvProblem) + (kMaxGrid + 1) * sizeof(int2)];  // records, then the CTA ranges
 
 extern "C" int vpq_affine_qmv_w4g64_bf16_set_noalloc(const vpq_linear_desc* d, int count, void* stream) {
   clear_error();
@@ -762,9 +823,15 @@ extern "C" int vpq_affine_qmv_w4g64_bf16_set_noalloc(const vpq_linear_desc* d, i
   // every descriptor the kernel will read is rewritten here, so nothing stale from the previous
   // call is ever used; the copy is ordered before the launch on the same stream
   VPQ_CUDA_OK(cudaMemcpyAsync(dev_addr[dev], host, (size_t)r * sizeof(QmvProblem), cudaMemcpyHostToDevice, st));
+  const int grid = grid_for(tiles);
+  int2 host_ranges[kMaxGrid + 1];
+  build_ranges(host, (size_t)r, grid, host_ranges);
+  void* dev_ranges = static_cast<unsigned char*>(dev_addr[dev]) + kNoAllocMaxRows * sizeof(QmvProblem);
+  VPQ_CUDA_OK(cudaMemcpyAsync(dev_ranges, host_ranges, (size_t)(grid + 1) * sizeof(int2), cudaMemcpyHostToDevice, st));
   QmvProblem unused;
   std::memset(&unused, 0, sizeof(unused));
-  return launch_list(unused, static_cast<const QmvProblem*>(dev_addr[dev]), tiles, cap_kt, st);
+  return launch_list(unused, static_cast<const QmvProblem*>(dev_addr[dev]), static_cast<const int2*>(dev_ranges), tiles,
+                     cap_kt, st);
 }
 
 extern "C" int vpq_qmv_plan_destroy(vpq_qmv_plan* plan) {
