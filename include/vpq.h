@@ -97,6 +97,18 @@ int vpq_affine_qmv_w4g64_bf16(const uint32_t* w, const void* scales, const void*
                               const void* x, void* y, int64_t K, int64_t N, int64_t M,
                               void* stream);
 
+/* The fused decode GEMVs as single calls (see VPQ_EPILOGUE_* below for the arithmetic).
+ * _add: slot 7 of the reference kernel is `residual` [M, N]. _swiglu: N = 2 * ffn, y is [M, N/2].
+ * _qkv: slots 4..6 of the reference kernel are the three outputs, 8..10 the row counts. */
+int vpq_affine_qmv_w4g64_bf16_add(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                                  void* y, int64_t K, int64_t N, int64_t M, const void* residual,
+                                  void* stream);
+int vpq_affine_qmv_swiglu_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                                     void* y, int64_t K, int64_t N, int64_t M, void* stream);
+int vpq_affine_qmv_qkv_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                                  void* q_out, void* k_out, void* v_out, int64_t K, int64_t q_rows,
+                                  int64_t k_rows, int64_t v_rows, int64_t M, void* stream);
+
 /* A set of independent GEMVs enqueued back to back (one launch each, in order),
  * e.g. the q | k | v or gate | up projections of one decoder layer. descs_host
  * is a host array read during the call. Each launch opts into programmatic
@@ -111,7 +123,23 @@ typedef struct vpq_linear_desc {
   const void* x;
   void* y;
   int64_t K, N, M;
+  /* Fused store, VPQ_EPILOGUE_*; zero-initialised descriptors store y = x W^T as is. */
+  int32_t epilogue;
+  int32_t reserved;
+  const void* aux;      /* ADD: residual [M, N]; QKV: the k output [M, k_rows] (written) */
+  void* y3;             /* QKV: the v output [M, N - q_rows - k_rows] */
+  int64_t q_rows, k_rows;
 } vpq_linear_desc;
+
+/* What the GEMV does with each row's f32 sum (the reference's fused decode kernels):
+ * ADD     y[n] = bf16(bf16(sum) + residual[n])                  affine_qmv_w4g64_add,
+ *         gpu-kernels/metal/quant/affine_qmv.metal:265-270,347-363 (o_proj / down_proj + residual)
+ * SWIGLU  W rows interleaved (2j = gate j, 2j+1 = up j), N = 2 ffn, y is [M, N/2]:
+ *         y[j] = bf16(silu(sum[2j]) * sum[2j+1]), from the unrounded sums    affine_qmv_swiglu_w4g64,
+ *         affine_qmv.metal:806-906
+ * QKV     W is q | k | v row-concatenated; rows land in three buffers: y (q), aux (k), y3 (v)
+ *         affine_qmv_qkv_w4g64, affine_qmv.metal:405-516 */
+enum { VPQ_EPILOGUE_NONE = 0, VPQ_EPILOGUE_ADD = 1, VPQ_EPILOGUE_SWIGLU = 2, VPQ_EPILOGUE_QKV = 3 };
 int vpq_affine_qmv_w4g64_bf16_batch(const vpq_linear_desc* descs_host, int count, void* stream);
 
 /* A list of independent GEMVs run as ONE launch: the kernel walks the row tiles of all problems
@@ -170,7 +198,8 @@ int vpq_device_status(void* stream, uint32_t* detail);
  * Replaces MetalCompute::load_library(name).function(entry),
  * apple-silicon/metal-compute/metal-compute.h:301, compute-library.h:134.
  * Returns NULL for an unknown pair (the reference returns an invalid handle).
- * Known libraries: affine_qmv_bf16, affine_qmm_steel_bf16, affine_qmm_mma_bf16,
+ * Known libraries: affine_qmv_bf16 (entries affine_qmv_w4g64, affine_qmv_w4g64_add,
+ * affine_qmv_swiglu_w4g64, affine_qmv_qkv_w4g64), affine_qmm_steel_bf16, affine_qmm_mma_bf16,
  * affine_dequant_bf16, affine_dequant (quantizer, f16 source). */
 typedef struct vpq_function_s vpq_function;
 const vpq_function* vpq_function_lookup(const char* library, const char* entry);
@@ -181,6 +210,9 @@ const char* vpq_function_name(const vpq_function* fn);
  * what set_constant bound. The grid is derived from the shapes, so the
  * reference's grid / threadgroup arguments have no counterpart. Slot layouts:
  *   QMV, QMM : 0:w 1:scales 2:biases 3:x 4:y            affine_qmv.metal:19-26
+ *   QMV add  : as QMV, 7:residual                       affine_qmv.metal:347-363
+ *   QMV swiglu: as QMV (N = 2 ffn, y is [M, N/2])       affine_qmv.metal:891-906
+ *   QMV qkv  : 0:w 1:scales 2:biases 3:x 4:q 5:k 6:v; K, q_rows, k_rows, v_rows   affine_qmv.metal:492-511
  *   dequant  : 0:w 1:scales 2:biases 3:ydeq             affine_dequant.metal:14
  *   quant    : 0:x 1:w 2:scales_f16 3:biases_f16        affine_dequant.metal:288-296
  * Replaces ComputeEncoder::set_function/set_buffer/set_constant/dispatch,
@@ -189,6 +221,7 @@ typedef struct vpq_dispatch_args {
   const void* buffers[8];
   int64_t K, N, M;
   float clip;
+  int64_t q_rows, k_rows, v_rows; /* QMV qkv only */
 } vpq_dispatch_args;
 int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* args, void* stream);
 

@@ -204,6 +204,24 @@ def linear_f32(codes, s_bf16, b_bf16, x_bf16, mode: str = "fast") -> np.ndarray:
     return matmul_f32(x_bf16, dequant_f32(codes, s_bf16, b_bf16), mode)
 
 
+def fused_add(y_f32: np.ndarray, residual_bf16: np.ndarray) -> np.ndarray:
+    """Residual store of the fused GEMV: the sum is rounded to bf16, the add happens in bf16
+    (`T v = static_cast<T>(result[row]); if (ADD) v += residual[row];`,
+    gpu-kernels/metal/quant/affine_qmv.metal:268-270). Returns bf16 bits."""
+    y = bf16_to_f32(narrow_f32_bf16(np.asarray(y_f32, np.float32)))
+    return narrow_f32_bf16((y + bf16_to_f32(residual_bf16)).astype(np.float32))
+
+
+def fused_swiglu(y_f32: np.ndarray) -> np.ndarray:
+    """SwiGLU store over row-interleaved gate | up (column 2j = gate j, 2j+1 = up j of y[M, N]):
+    `(g / (1 + exp(-g))) * u` in f32 from the unrounded sums, rounded once
+    (gpu-kernels/metal/quant/affine_qmv.metal:881-887). Returns bf16 bits [M, N/2]."""
+    y = np.asarray(y_f32, np.float32)
+    g, u = y[:, 0::2], y[:, 1::2]
+    one = np.float32(1.0)
+    return narrow_f32_bf16(((g / (one + np.exp(-g))) * u).astype(np.float32))
+
+
 def qmv_kernel_order(codes, s_bf16, b_bf16, x_bf16) -> np.ndarray:
     codes = _c(codes, np.uint32)
     x = _c(x_bf16, np.uint16)

@@ -46,6 +46,9 @@ def test_byte_sizes_mirror_the_quantizer(vpq):
 def test_function_table_uses_reference_names(vpq):
     ops = vpq.ops
     for libname, entry in [("affine_qmv_bf16", "affine_qmv_w4g64"),
+                           ("affine_qmv_bf16", "affine_qmv_w4g64_add"),
+                           ("affine_qmv_bf16", "affine_qmv_swiglu_w4g64"),
+                           ("affine_qmv_bf16", "affine_qmv_qkv_w4g64"),
                            ("affine_qmm_steel_bf16", "affine_qmm_steel_w4g64"),
                            ("affine_qmm_steel_bf16", "affine_qmm_steel_w4g64_bm64"),
                            ("affine_qmm_steel_bf16", "affine_qmm_steel_w4g64_bm128"),
@@ -84,6 +87,11 @@ def test_argument_validation_happens_before_any_device_work(vpq):
     assert L.vpq_affine_qmm_w4g64_bf16(p16, p16, p16, p16 + 8, p16, 64, 8, 1, None) == ALIGN
     # outside the supported range
     assert L.vpq_affine_qmv_w4g64_bf16(p16, p16, p16, p16, p16, 65536, 8, 1, None) == UNSUP
+    # fused stores: residual missing, odd N for swiglu, row counts beyond N
+    assert L.vpq_affine_qmv_w4g64_bf16_add(p16, p16, p16, p16, p16, 64, 8, 1, None, None) == INVALID
+    assert L.vpq_affine_qmv_swiglu_w4g64_bf16(p16, p16, p16, p16, p16, 64, 7, 1, None) == INVALID
+    assert L.vpq_affine_qmv_qkv_w4g64_bf16(p16, p16, p16, p16, p16, p16, p16, 64, 0, 8, 8, 1, None) == INVALID
+    assert L.vpq_affine_qmv_qkv_w4g64_bf16(p16, p16, p16, p16, p16, None, p16, 64, 8, 8, 8, 1, None) == INVALID
     # nsplit argument checks need no communicator
     assert L.vpq_affine_qmm_w4g64_bf16_nsplit(None, p16, p16, p16, p16, p16, None, 64, 8, 1, 1, None) == INVALID
     assert L.vpq_dispatch(None, None, None) == INVALID

@@ -1,0 +1,133 @@
+"""GPU parity of the fused decode GEMVs (residual add, SwiGLU over interleaved gate | up, q | k | v
+with three outputs) against the oracle's restatement of the reference's fused stores
+(gpu-kernels/metal/quant/affine_qmv.metal:265-270, 806-906, 405-516), through the C ABI.
+
+Two kinds of check: against the fp32 oracle within the 1e-2 tolerance of the plain GEMV, and
+bit-exact consistency with the plain GEMV where the fused store is a function of its bf16 output
+(add, qkv)."""
+import numpy as np
+import pytest
+import torch
+
+from vpipe_b200 import synth
+
+from test_gpu_parity import TOL, bits16, dev, f32, quantized_linear, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _need_gpu(vpq):
+    assert torch.cuda.is_available(), "the -m gpu tests need a CUDA device"
+    torch.cuda.set_device(0)
+    yield
+    torch.cuda.synchronize()
+    assert vpq.ops.device_status() == 0
+
+
+def _linear(oracle_mod, N, K, M, seed):
+    codes, s, b = quantized_linear(oracle_mod, N, K, seed)
+    x = synth.activations_bf16(M, K, seed + 1)
+    ref = oracle_mod.linear_f32(codes, s, b, x, "fast")
+    d = (to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16), to_dev(x, torch.bfloat16))
+    return d, ref
+
+
+@pytest.mark.parametrize("K,N,M", [(4096, 4096, 1), (12288, 4096, 1), (320, 33, 2), (3840, 16, 1)])
+def test_qmv_add(vpq, oracle_mod, K, N, M):
+    d, ref = _linear(oracle_mod, N, K, M, 7000 + N + K)
+    res = synth.activations_bf16(M, N, 7100 + N)
+    dres = to_dev(res, torch.bfloat16)
+    y = vpq.ops.qmv_add(*d, dres)
+    want = synth.bf16_bits_to_f32(oracle_mod.fused_add(ref, res))
+    e = oracle_mod.err_metrics(f32(y), want)
+    assert e["rel_l2"] < TOL and e["max_rel_rms"] < TOL, e
+    # the same sums as the plain GEMV, rounded to bf16, then one bf16 add
+    plain = vpq.ops.qmv(*d)
+    assert torch.equal(y, (plain.float() + dres.float()).to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("K,N,M", [(4096, 2 * 1024, 1), (4096, 2 * 12288, 1), (1088, 18, 2), (64, 2, 1)])
+def test_qmv_swiglu(vpq, oracle_mod, K, N, M):
+    d, ref = _linear(oracle_mod, N, K, M, 7200 + N + K)
+    y = vpq.ops.qmv_swiglu(*d)
+    assert y.shape == (M, N // 2)
+    want = synth.bf16_bits_to_f32(oracle_mod.fused_swiglu(ref))
+    e = oracle_mod.err_metrics(f32(y), want)
+    assert e["rel_l2"] < TOL and e["max_rel_rms"] < TOL, e
+    # against silu(gate) * up formed from the plain GEMV's bf16 outputs: equal up to their rounding
+    plain = vpq.ops.qmv(*d).float()
+    g, u = plain[:, 0::2], plain[:, 1::2]
+    approx = (g / (1.0 + torch.exp(-g)) * u).cpu().numpy()
+    assert oracle_mod.err_metrics(f32(y), approx)["max_rel_rms"] < 2e-2
+
+
+def test_qmv_swiglu_does_not_write_past_the_halved_output(vpq, oracle_mod):
+    K, N = 1024, 70
+    d, _ = _linear(oracle_mod, N, K, 1, 7300)
+    pad = 64
+    buf = torch.full((pad + N // 2 + pad,), -3.0, dtype=torch.bfloat16, device=dev())
+    y = buf[pad:pad + N // 2].view(1, N // 2)
+    vpq.ops.qmv_swiglu(*d, out=y)
+    assert torch.all(buf[:pad] == -3.0) and torch.all(buf[pad + N // 2:] == -3.0)
+    assert torch.all(y != -3.0)
+
+
+@pytest.mark.parametrize("K,q,k,v,M", [(4096, 4096, 1024, 1024, 1), (1024, 40, 24, 8, 2), (512, 16, 16, 0, 1),
+                                         (512, 19, 5, 11, 1)])
+def test_qmv_qkv_lands_rows_in_three_buffers(vpq, oracle_mod, K, q, k, v, M):
+    N = q + k + v
+    d, ref = _linear(oracle_mod, N, K, M, 7400 + N + K)
+    yq, yk, yv = vpq.ops.qmv_qkv(*d, q, k, v)
+    plain = vpq.ops.qmv(*d)
+    assert torch.equal(yq, plain[:, :q])
+    assert torch.equal(yk, plain[:, q:q + k])
+    assert torch.equal(yv, plain[:, q + k:])
+    e = oracle_mod.err_metrics(f32(torch.cat([yq, yk, yv], dim=1)), ref)
+    assert e["rel_l2"] < TOL, e
+
+
+def test_fused_stores_inside_a_plan(vpq, oracle_mod):
+    """One launch holding a q|k|v GEMV, a SwiGLU gate|up GEMV and a down GEMV with residual: the
+    bytes of the three single calls."""
+    K, F = 1024, 1536
+    dq, _ = _linear(oracle_mod, 1024 + 256 + 256, K, 1, 7500)
+    dg, _ = _linear(oracle_mod, 2 * F, K, 1, 7510)
+    dd, _ = _linear(oracle_mod, K, F, 1, 7520)
+    res = to_dev(synth.activations_bf16(1, K, 7530), torch.bfloat16)
+    want_qkv = vpq.ops.qmv_qkv(*dq, 1024, 256, 256)
+    want_act = vpq.ops.qmv_swiglu(*dg)
+    want_out = vpq.ops.qmv_add(*dd, res)
+    z = lambda n: torch.zeros((1, n), dtype=torch.bfloat16, device=dev())
+    yq, yk, yv, act, out = z(1024), z(256), z(256), z(F), z(K)
+    plan = vpq.ops.QmvPlan([
+        dq + (yq, {"epilogue": "qkv", "aux": yk, "y3": yv, "q_rows": 1024, "k_rows": 256}),
+        dg + (act, {"epilogue": "swiglu"}),
+        dd + (out, {"epilogue": "add", "aux": res}),
+    ])
+    plan.run()
+    torch.cuda.synchronize()
+    assert torch.equal(yq, want_qkv[0]) and torch.equal(yk, want_qkv[1]) and torch.equal(yv, want_qkv[2])
+    assert torch.equal(act, want_act)
+    assert torch.equal(out, want_out)
+    plan.close()
+
+
+def test_fused_entries_by_reference_names(vpq, oracle_mod):
+    ops = vpq.ops
+    K, N = 512, 48
+    d, _ = _linear(oracle_mod, N, K, 1, 7600)
+    res = to_dev(synth.activations_bf16(1, N, 7610), torch.bfloat16)
+    y = torch.empty((1, N), dtype=torch.bfloat16, device=dev())
+    ops.dispatch(ops.function("affine_qmv_bf16", "affine_qmv_w4g64_add"),
+                 {0: d[0], 1: d[1], 2: d[2], 3: d[3], 4: y, 7: res}, K=K, N=N)
+    assert torch.equal(y, ops.qmv_add(*d, res))
+    y2 = torch.empty((1, N // 2), dtype=torch.bfloat16, device=dev())
+    ops.dispatch(ops.function("affine_qmv_bf16", "affine_qmv_swiglu_w4g64"),
+                 {0: d[0], 1: d[1], 2: d[2], 3: d[3], 4: y2}, K=K, N=N)
+    assert torch.equal(y2, ops.qmv_swiglu(*d))
+    yq, yk, yv = (torch.empty((1, n), dtype=torch.bfloat16, device=dev()) for n in (16, 16, 16))
+    ops.dispatch(ops.function("affine_qmv_bf16", "affine_qmv_qkv_w4g64"),
+                 {0: d[0], 1: d[1], 2: d[2], 3: d[3], 4: yq, 5: yk, 6: yv}, K=K, q_rows=16, k_rows=16, v_rows=16)
+    want = ops.qmv_qkv(*d, 16, 16, 16)
+    assert torch.equal(yq, want[0]) and torch.equal(yk, want[1]) and torch.equal(yv, want[2])

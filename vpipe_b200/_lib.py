@@ -24,6 +24,9 @@ SYMBOLS = [
     ("vpq_scales_f16_to_bf16", _i, [_vp, _vp, _i64, _vp]),
     ("vpq_affine_dequant_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _i64, _i64, _vp]),
     ("vpq_affine_qmv_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    ("vpq_affine_qmv_w4g64_bf16_add", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp]),
+    ("vpq_affine_qmv_swiglu_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    ("vpq_affine_qmv_qkv_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
     ("vpq_affine_qmv_w4g64_bf16_batch", _i, [_vp, _i, _vp]),
     ("vpq_affine_qmv_w4g64_bf16_set_noalloc", _i, [_vp, _i, _vp]),
     ("vpq_qmv_plan_bytes", C.c_size_t, [_vp, _i]),
@@ -51,14 +54,17 @@ SYMBOLS = [
 class DispatchArgs(C.Structure):
     """struct vpq_dispatch_args"""
     _fields_ = [("buffers", C.c_void_p * 8), ("K", C.c_int64), ("N", C.c_int64),
-                ("M", C.c_int64), ("clip", C.c_float)]
+                ("M", C.c_int64), ("clip", C.c_float), ("q_rows", C.c_int64),
+                ("k_rows", C.c_int64), ("v_rows", C.c_int64)]
 
 
 class LinearDesc(C.Structure):
     """struct vpq_linear_desc"""
     _fields_ = [("w", C.c_void_p), ("scales", C.c_void_p), ("biases", C.c_void_p),
                 ("x", C.c_void_p), ("y", C.c_void_p), ("K", C.c_int64), ("N", C.c_int64),
-                ("M", C.c_int64)]
+                ("M", C.c_int64), ("epilogue", C.c_int32), ("reserved", C.c_int32),
+                ("aux", C.c_void_p), ("y3", C.c_void_p), ("q_rows", C.c_int64),
+                ("k_rows", C.c_int64)]
 
 
 class VpqError(RuntimeError):

@@ -142,7 +142,7 @@ extern "C" size_t vpq_scale_bytes(int N, int K, int group) {
 struct vpq_function_s {
   const char* library;
   const char* entry;
-  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src)
+  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv
 };
 
 // The reference selects the element type with the library-name suffix and
@@ -151,6 +151,9 @@ struct vpq_function_s {
 // the shape), so their names all resolve to it.
 static const vpq_function_s g_functions[] = {
     {"affine_qmv_bf16", "affine_qmv_w4g64", 0},
+    {"affine_qmv_bf16", "affine_qmv_w4g64_add", 5},
+    {"affine_qmv_bf16", "affine_qmv_swiglu_w4g64", 6},
+    {"affine_qmv_bf16", "affine_qmv_qkv_w4g64", 7},
     {"affine_qmm_steel_bf16", "affine_qmm_steel_w4g64", 1},
     {"affine_qmm_steel_bf16", "affine_qmm_steel_w4g64_bm64", 1},
     {"affine_qmm_steel_bf16", "affine_qmm_steel_w4g64_bm128", 1},
@@ -196,6 +199,18 @@ extern "C" int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* a, 
                                      static_cast<uint32_t*>(const_cast<void*>(b[1])),
                                      const_cast<void*>(b[2]), const_cast<void*>(b[3]), a->K, a->N,
                                      a->clip, stream);
+    case 5:
+      return vpq_affine_qmv_w4g64_bf16_add(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
+                                           const_cast<void*>(b[4]), a->K, a->N, a->M < 1 ? 1 : a->M, b[7],
+                                           stream);
+    case 6:
+      return vpq_affine_qmv_swiglu_w4g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
+                                              const_cast<void*>(b[4]), a->K, a->N, a->M < 1 ? 1 : a->M, stream);
+    case 7:
+      return vpq_affine_qmv_qkv_w4g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
+                                           const_cast<void*>(b[4]), const_cast<void*>(b[5]),
+                                           const_cast<void*>(b[6]), a->K, a->q_rows, a->k_rows, a->v_rows,
+                                           a->M < 1 ? 1 : a->M, stream);
     default:
       return fail(VPQ_ERR_NOT_FOUND, "dispatch: corrupt function handle");
   }

@@ -91,6 +91,10 @@ constexpr int kXBytesPerKt = 3 * 128;  // staged x per k tile: 3 digits x [4 chu
 
 enum : uint32_t { kRoleProducer = 1, kRoleConsumer = 2 };
 
+// Fused stores (the reference's affine_qmv_w4g64_add, affine_qmv_swiglu_w4g64 and
+// affine_qmv_qkv_w4g64, gpu-kernels/metal/quant/affine_qmv.metal:347-363, 806-906, 405-516).
+enum : int { kEpiNone = 0, kEpiAdd = 1, kEpiSwiglu = 2, kEpiQkv = 3 };
+
 // One GEMV of a launch. Lives in the kernel parameters (single GEMV) or in caller-provided
 // device memory (plan). Tensor maps need 64-byte alignment.
 struct alignas(64) QmvProblem {
@@ -102,7 +106,11 @@ struct alignas(64) QmvProblem {
   int K, N;
   int tile_begin, row_tiles;   // this problem's range in the launch's global list of 16-row tiles
   int scales_tma;              // scale / bias rows are TMA boxes (pitch and base 16-byte aligned)
-  int pad[3];
+  int epilogue;                // kEpi*: what the store does with a row's sum
+  int q_rows, k_rows;          // kEpiQkv: rows [0, q_rows) -> y, [q_rows, q_rows + k_rows) -> aux, the rest -> y3
+  const uint16_t* aux;         // kEpiAdd: residual, N values; kEpiQkv: the second output
+  __nv_bfloat16* y3;           // kEpiQkv: the third output
+  int pad[12];
 };
 static_assert(sizeof(QmvProblem) % 64 == 0, "problem records are laid out back to back");
 
@@ -498,8 +506,31 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
         for (int ww = 0; ww < kConsWarps; ++ww) {
           v += *reinterpret_cast<volatile float*>(&red[(slot * kConsWarps + ww) * 16 + lane]);
         }
+        v *= x_unscale;
         const int row = (tile << 4) + lane;
-        if (row < N) { y[row] = __float2bfloat16_rn(v * x_unscale); }
+        const int epi = P->epilogue;
+        if (epi == kEpiNone) {
+          if (row < N) { y[row] = __float2bfloat16_rn(v); }
+        } else if (epi == kEpiAdd) {
+          // the sum is rounded to bf16 first, then added to the residual in bf16, as the reference does
+          if (row < N) {
+            const float r = __uint_as_float((uint32_t)P->aux[row] << 16);
+            y[row] = __float2bfloat16_rn(__bfloat162float(__float2bfloat16_rn(v)) + r);
+          }
+        } else if (epi == kEpiSwiglu) {
+          // rows 2j, 2j+1 are gate j, up j: one output silu(gate) * up from the unrounded sums
+          const float up = __shfl_down_sync(0x0000ffffu, v, 1);
+          if ((lane & 1) == 0 && row + 1 < N) { y[row >> 1] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * up); }
+        } else {
+          const int q_rows = P->q_rows, qk = q_rows + P->k_rows;
+          if (row < q_rows) {
+            y[row] = __float2bfloat16_rn(v);
+          } else if (row < qk) {
+            reinterpret_cast<__nv_bfloat16*>(const_cast<uint16_t*>(P->aux))[row - q_rows] = __float2bfloat16_rn(v);
+          } else if (row < N) {
+            P->y3[row - qk] = __float2bfloat16_rn(v);
+          }
+        }
       }
       __syncwarp();
       if (lane == 0) { red_cnt[slot] = 0; }
@@ -628,6 +659,70 @@ int check_qmv_args(const char* who, const void* w, const void* scales, const voi
   return VPQ_OK;
 }
 
+// Validation of one descriptor, fused store included.
+int check_desc(const char* who, const vpq_linear_desc& d) {
+  if (int rc = check_qmv_args(who, d.w, d.scales, d.biases, d.x, d.y, d.K, d.N, d.M)) { return rc; }
+  switch (d.epilogue) {
+    case VPQ_EPILOGUE_NONE:
+      return VPQ_OK;
+    case VPQ_EPILOGUE_ADD:
+      if (!d.aux || (reinterpret_cast<uintptr_t>(d.aux) & 1)) {
+        return fail(VPQ_ERR_INVALID_ARG, "%s: the residual is null or not 2-byte aligned", who);
+      }
+      return VPQ_OK;
+    case VPQ_EPILOGUE_SWIGLU:
+      if (d.N % 2) { return fail(VPQ_ERR_INVALID_ARG, "%s: swiglu needs an even N (gate / up interleaved)", who); }
+      return VPQ_OK;
+    case VPQ_EPILOGUE_QKV:
+      if (d.q_rows < 0 || d.k_rows < 0 || d.q_rows + d.k_rows > d.N) {
+        return fail(VPQ_ERR_INVALID_ARG, "%s: q_rows %lld + k_rows %lld exceed N %lld", who, (long long)d.q_rows,
+                    (long long)d.k_rows, (long long)d.N);
+      }
+      if ((d.k_rows > 0 && !d.aux) || (d.q_rows + d.k_rows < d.N && !d.y3) ||
+          (reinterpret_cast<uintptr_t>(d.aux) & 1) || (reinterpret_cast<uintptr_t>(d.y3) & 1)) {
+        return fail(VPQ_ERR_INVALID_ARG, "%s: k / v output null or not 2-byte aligned", who);
+      }
+      return VPQ_OK;
+    default:
+      return fail(VPQ_ERR_INVALID_ARG, "%s: unknown epilogue %d", who, (int)d.epilogue);
+  }
+}
+
+// Row m of a descriptor as a kernel problem.
+int fill_from_desc(QmvProblem* p, const vpq_linear_desc& d, int64_t m, int tile_begin) {
+  const int64_t y_pitch = d.epilogue == VPQ_EPILOGUE_SWIGLU ? d.N / 2
+                          : d.epilogue == VPQ_EPILOGUE_QKV  ? d.q_rows
+                                                            : d.N;
+  if (int rc = fill_problem(p, d.w, static_cast<const uint16_t*>(d.scales), static_cast<const uint16_t*>(d.biases),
+                            static_cast<const uint16_t*>(d.x) + m * d.K,
+                            static_cast<__nv_bfloat16*>(d.y) + m * y_pitch, (int)d.K, (int)d.N, tile_begin)) {
+    return rc;
+  }
+  p->epilogue = d.epilogue;
+  if (d.epilogue == VPQ_EPILOGUE_ADD) {
+    p->aux = static_cast<const uint16_t*>(d.aux) + m * d.N;
+  } else if (d.epilogue == VPQ_EPILOGUE_QKV) {
+    p->q_rows = (int)d.q_rows;
+    p->k_rows = (int)d.k_rows;
+    p->aux = static_cast<const uint16_t*>(d.aux) + m * d.k_rows;
+    p->y3 = static_cast<__nv_bfloat16*>(d.y3) + m * (d.N - d.q_rows - d.k_rows);
+  }
+  return VPQ_OK;
+}
+
+// One launch per row of one descriptor (every row streams the weight again, as in the reference).
+int launch_desc_rows(const char* who, const vpq_linear_desc& d, cudaStream_t st) {
+  if (int rc = check_desc(who, d)) { return rc; }
+  if (int rc = require_sm100()) { return rc; }
+  const int cap_kt = (int)((d.K + 255) / 256) * 2;
+  for (int64_t m = 0; m < d.M; ++m) {
+    QmvProblem p;
+    if (int rc = fill_from_desc(&p, d, m, 0)) { return rc; }
+    if (int rc = launch_list(p, nullptr, nullptr, p.row_tiles, cap_kt, st)) { return rc; }
+  }
+  return VPQ_OK;
+}
+
 }  // namespace
 
 int qmv_status_read(cudaStream_t st, uint32_t* out) {
@@ -654,34 +749,72 @@ struct vpq_qmv_plan_s {
   int cap_kt;
 };
 
+namespace {
+vpq_linear_desc make_desc(const uint32_t* w, const void* scales, const void* biases, const void* x, void* y,
+                          int64_t K, int64_t N, int64_t M) {
+  vpq_linear_desc d;
+  std::memset(&d, 0, sizeof(d));
+  d.w = w;
+  d.scales = scales;
+  d.biases = biases;
+  d.x = x;
+  d.y = y;
+  d.K = K;
+  d.N = N;
+  d.M = M;
+  return d;
+}
+}  // namespace
+
 extern "C" int vpq_affine_qmv_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
                                          const void* x, void* y, int64_t K, int64_t N, int64_t M,
                                          void* stream) {
   clear_error();
-  if (int rc = check_qmv_args("affine_qmv_w4g64", w, scales, biases, x, y, K, N, M)) { return rc; }
-  if (int rc = require_sm100()) { return rc; }
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int cap_kt = (int)((K + 255) / 256) * 2;
-  for (int64_t m = 0; m < M; ++m) {  // every row streams the weight again, as in the reference
-    QmvProblem p;
-    if (int rc = fill_problem(&p, w, static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases),
-                              static_cast<const uint16_t*>(x) + m * K, static_cast<__nv_bfloat16*>(y) + m * N,
-                              (int)K, (int)N, 0)) {
-      return rc;
-    }
-    if (int rc = launch_list(p, nullptr, nullptr, p.row_tiles, cap_kt, st)) { return rc; }
+  return launch_desc_rows("affine_qmv_w4g64", make_desc(w, scales, biases, x, y, K, N, M),
+                          static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int vpq_affine_qmv_w4g64_bf16_add(const uint32_t* w, const void* scales, const void* biases,
+                                             const void* x, void* y, int64_t K, int64_t N, int64_t M,
+                                             const void* residual, void* stream) {
+  clear_error();
+  vpq_linear_desc d = make_desc(w, scales, biases, x, y, K, N, M);
+  d.epilogue = VPQ_EPILOGUE_ADD;
+  d.aux = residual;
+  return launch_desc_rows("affine_qmv_w4g64_add", d, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int vpq_affine_qmv_swiglu_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
+                                                const void* x, void* y, int64_t K, int64_t N, int64_t M,
+                                                void* stream) {
+  clear_error();
+  vpq_linear_desc d = make_desc(w, scales, biases, x, y, K, N, M);
+  d.epilogue = VPQ_EPILOGUE_SWIGLU;
+  return launch_desc_rows("affine_qmv_swiglu_w4g64", d, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int vpq_affine_qmv_qkv_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
+                                             const void* x, void* q_out, void* k_out, void* v_out, int64_t K,
+                                             int64_t q_rows, int64_t k_rows, int64_t v_rows, int64_t M,
+                                             void* stream) {
+  clear_error();
+  if (q_rows <= 0 || k_rows < 0 || v_rows < 0) {
+    return fail(VPQ_ERR_INVALID_ARG, "affine_qmv_qkv_w4g64: need q_rows > 0, k_rows >= 0, v_rows >= 0");
   }
-  return VPQ_OK;
+  vpq_linear_desc d = make_desc(w, scales, biases, x, q_out, K, q_rows + k_rows + v_rows, M);
+  d.epilogue = VPQ_EPILOGUE_QKV;
+  d.aux = k_out;
+  d.y3 = v_out;
+  d.q_rows = q_rows;
+  d.k_rows = k_rows;
+  return launch_desc_rows("affine_qmv_qkv_w4g64", d, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int vpq_affine_qmv_w4g64_bf16_batch(const vpq_linear_desc* d, int count, void* stream) {
   clear_error();
   if (!d || count <= 0) { return fail(VPQ_ERR_INVALID_ARG, "affine_qmv_w4g64_batch: null or empty set"); }
   for (int i = 0; i < count; ++i) {
-    if (int rc = vpq_affine_qmv_w4g64_bf16(d[i].w, d[i].scales, d[i].biases, d[i].x, d[i].y, d[i].K,
-                                           d[i].N, d[i].M, stream)) {
-      return rc;
-    }
+    if (int rc = launch_desc_rows("affine_qmv_w4g64_batch", d[i], static_cast<cudaStream_t>(stream))) { return rc; }
   }
   return VPQ_OK;
 }
@@ -704,10 +837,7 @@ extern "C" int vpq_qmv_plan_create(const vpq_linear_desc* d, int count, void* wo
                 vpq_qmv_plan_bytes(d, count));
   }
   for (int i = 0; i < count; ++i) {
-    if (int rc = check_qmv_args("qmv_plan_create", d[i].w, d[i].scales, d[i].biases, d[i].x, d[i].y,
-                                d[i].K, d[i].N, d[i].M)) {
-      return rc;
-    }
+    if (int rc = check_desc("qmv_plan_create", d[i])) { return rc; }
   }
   if (int rc = require_sm100()) { return rc; }
   size_t rows = 0;
@@ -718,11 +848,7 @@ extern "C" int vpq_qmv_plan_create(const vpq_linear_desc* d, int count, void* wo
   size_t r = 0;
   for (int i = 0; i < count; ++i) {
     for (int64_t m = 0; m < d[i].M; ++m, ++r) {
-      const int rc = fill_problem(&host[r], d[i].w, static_cast<const uint16_t*>(d[i].scales),
-                                  static_cast<const uint16_t*>(d[i].biases),
-                                  static_cast<const uint16_t*>(d[i].x) + m * d[i].K,
-                                  static_cast<__nv_bfloat16*>(d[i].y) + m * d[i].N, (int)d[i].K, (int)d[i].N,
-                                  tiles);
+      const int rc = fill_from_desc(&host[r], d[i], m, tiles);
       if (rc) {
         std::free(host);
         return rc;
@@ -780,10 +906,7 @@ extern "C" int vpq_affine_qmv_w4g64_bf16_set_noalloc(const vpq_linear_desc* d, i
   if (!d || count <= 0) { return fail(VPQ_ERR_INVALID_ARG, "qmv_set_noalloc: null or empty set"); }
   int64_t rows = 0;
   for (int i = 0; i < count; ++i) {
-    if (int rc = check_qmv_args("qmv_set_noalloc", d[i].w, d[i].scales, d[i].biases, d[i].x, d[i].y, d[i].K,
-                                d[i].N, d[i].M)) {
-      return rc;
-    }
+    if (int rc = check_desc("qmv_set_noalloc", d[i])) { return rc; }
     rows += d[i].M;
   }
   if (rows > kNoAllocMaxRows) {
@@ -808,13 +931,7 @@ extern "C" int vpq_affine_qmv_w4g64_bf16_set_noalloc(const vpq_linear_desc* d, i
   int tiles = 0, cap_kt = 0, r = 0;
   for (int i = 0; i < count; ++i) {
     for (int64_t m = 0; m < d[i].M; ++m, ++r) {
-      if (int rc = fill_problem(&host[r], d[i].w, static_cast<const uint16_t*>(d[i].scales),
-                                static_cast<const uint16_t*>(d[i].biases),
-                                static_cast<const uint16_t*>(d[i].x) + m * d[i].K,
-                                static_cast<__nv_bfloat16*>(d[i].y) + m * d[i].N, (int)d[i].K, (int)d[i].N,
-                                tiles)) {
-        return rc;
-      }
+      if (int rc = fill_from_desc(&host[r], d[i], m, tiles)) { return rc; }
       tiles += host[r].row_tiles;
       const int kt = (int)((d[i].K + 255) / 256) * 2;
       cap_kt = kt > cap_kt ? kt : cap_kt;

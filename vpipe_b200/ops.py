@@ -78,13 +78,69 @@ def qmv(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
     return out
 
 
+def qmv_add(codes, scales, biases, x, residual, out=None, stream=None) -> torch.Tensor:
+    """y = bf16(bf16(x W^T) + residual) (vpq_affine_qmv_w4g64_bf16_add)."""
+    N, Kw = codes.shape
+    K = Kw * 8
+    M = x.numel() // K
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().vpq_affine_qmv_w4g64_bf16_add(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x), _ptr(out),
+                                                  K, N, M, _ptr(residual), _stream(stream)))
+    return out
+
+
+def qmv_swiglu(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
+    """Rows of W interleaved gate / up: y[M, N/2] = silu(gate) * up (vpq_affine_qmv_swiglu_w4g64_bf16)."""
+    N, Kw = codes.shape
+    K = Kw * 8
+    M = x.numel() // K
+    if out is None:
+        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().vpq_affine_qmv_swiglu_w4g64_bf16(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x), _ptr(out),
+                                                     K, N, M, _stream(stream)))
+    return out
+
+
+def qmv_qkv(codes, scales, biases, x, q_rows, k_rows, v_rows, stream=None):
+    """W = q | k | v row-concatenated; returns (q, k, v) (vpq_affine_qmv_qkv_w4g64_bf16)."""
+    N, Kw = codes.shape
+    K = Kw * 8
+    M = x.numel() // K
+    assert q_rows + k_rows + v_rows == N
+    outs = [torch.empty((M, r), dtype=torch.bfloat16, device=x.device) for r in (q_rows, k_rows, v_rows)]
+    with torch.cuda.device(x.device):
+        check(lib().vpq_affine_qmv_qkv_w4g64_bf16(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x),
+                                                  _ptr(outs[0]), _ptr(outs[1]) if k_rows else None,
+                                                  _ptr(outs[2]) if v_rows else None, K, q_rows, k_rows, v_rows,
+                                                  M, _stream(stream)))
+    return tuple(outs)
+
+
+EPILOGUES = {"none": 0, "add": 1, "swiglu": 2, "qkv": 3}
+
+
 def qmv_set(problems):
-    """Builds the host descriptor array for qmv_batch from (codes, scales, biases, x, y) tuples."""
+    """Builds the host descriptor array for qmv_batch / QmvPlan from (codes, scales, biases, x, y)
+    tuples; an optional sixth element is a dict describing a fused store:
+    {"epilogue": "add", "aux": residual} | {"epilogue": "swiglu"} |
+    {"epilogue": "qkv", "aux": k_out, "y3": v_out, "q_rows": .., "k_rows": ..}."""
     arr = (_lib.LinearDesc * len(problems))()
-    for d, (codes, scales, biases, x, y) in zip(arr, problems):
+    for d, prob in zip(arr, problems):
+        codes, scales, biases, x, y = prob[:5]
         N, Kw = codes.shape
         d.w, d.scales, d.biases, d.x, d.y = _ptr(codes), _ptr(scales), _ptr(biases), _ptr(x), _ptr(y)
         d.K, d.N, d.M = Kw * 8, N, x.numel() // (Kw * 8)
+        if len(prob) > 5 and prob[5]:
+            e = prob[5]
+            d.epilogue = EPILOGUES[e["epilogue"]]
+            if e.get("aux") is not None:
+                d.aux = _ptr(e["aux"])
+            if e.get("y3") is not None:
+                d.y3 = _ptr(e["y3"])
+            d.q_rows, d.k_rows = e.get("q_rows", 0), e.get("k_rows", 0)
     return arr
 
 
@@ -145,10 +201,13 @@ def function(library: str, entry: str):
     return lib().vpq_function_lookup(library.encode(), entry.encode())
 
 
-def dispatch(fn, buffers, K=0, N=0, M=0, clip=1.0, stream=None) -> None:
-    """One dispatch with the reference's slot numbering (see include/vpq.h)."""
+def dispatch(fn, buffers, K=0, N=0, M=0, clip=1.0, q_rows=0, k_rows=0, v_rows=0, stream=None) -> None:
+    """One dispatch with the reference's slot numbering (see include/vpq.h). `buffers` is a list
+    indexed by slot, or a dict {slot: tensor}."""
     a = _lib.DispatchArgs()
-    for i, t in enumerate(buffers):
+    items = buffers.items() if isinstance(buffers, dict) else enumerate(buffers)
+    for i, t in items:
         a.buffers[i] = _ptr(t) if t is not None else None
     a.K, a.N, a.M, a.clip = K, N, M, clip
+    a.q_rows, a.k_rows, a.v_rows = q_rows, k_rows, v_rows
     check(lib().vpq_dispatch(fn, C.byref(a), _stream(stream)))
