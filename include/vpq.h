@@ -163,7 +163,7 @@ int vpq_qmv_plan_destroy(vpq_qmv_plan* plan);
  * application whose allocator owns every byte of HBM, a plugin entry point that is handed
  * buffers and nothing else) or on a latency path where a cudaMalloc, which can synchronise the
  * whole device, is not acceptable. No counterpart in the reference. The descriptor list the
- * kernel needs lives in a fixed 28 KB array inside the library image (held by every GPU that
+ * kernel needs lives in a fixed 40 KB array inside the library image (held by every GPU that
  * loads the library until exit), so at most 64 GEMV rows (sum of M over the set) fit in one call;
  * larger sets are rejected with VPQ_ERR_UNSUPPORTED. The call performs no cudaMalloc / cudaFree
  * and uses no allocating library routine. The first call on each device looks up the array's
