@@ -186,6 +186,15 @@ int vpq_affine_qmm_w4g64_bf16(const uint32_t* w, const void* scales, const void*
                               const void* x, void* y, int64_t K, int64_t N, int64_t M,
                               void* stream);
 
+/* Fused SwiGLU GEMM: W rows interleaved by output feature (row 2j = gate j, row 2j+1 = up j),
+ * N = 2 * ffn; y[M, N/2] = bf16(silu(x.gate_j) * (x.up_j)) computed in f32 from the accumulators,
+ * so the [M, N] intermediate is never written. Replaces affine_qmm_swiglu_w4g64[_bm64|_bm128]
+ * (same slots as the GEMM, y half as wide), gpu-kernels/metal/quant/affine_qmm_steel.metal:641-850;
+ * unlike those, any even N is accepted (tails are masked). */
+int vpq_affine_qmm_swiglu_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
+                                     const void* x, void* y, int64_t K, int64_t N, int64_t M,
+                                     void* stream);
+
 /* Device-side status of the tensor-core kernels: every wait inside them is
  * bounded; one that gives up records where and the kernel returns. Reads the
  * status word of the current device back to the host (synchronises `stream`),
@@ -211,7 +220,7 @@ const char* vpq_function_name(const vpq_function* fn);
  * reference's grid / threadgroup arguments have no counterpart. Slot layouts:
  *   QMV, QMM : 0:w 1:scales 2:biases 3:x 4:y            affine_qmv.metal:19-26
  *   QMV add  : as QMV, 7:residual                       affine_qmv.metal:347-363
- *   QMV swiglu: as QMV (N = 2 ffn, y is [M, N/2])       affine_qmv.metal:891-906
+ *   QMV / QMM swiglu: as QMV / QMM (N = 2 ffn, y is [M, N/2])   affine_qmv.metal:891-906, affine_qmm_steel.metal:801-827
  *   QMV qkv  : 0:w 1:scales 2:biases 3:x 4:q 5:k 6:v; K, q_rows, k_rows, v_rows   affine_qmv.metal:492-511
  *   dequant  : 0:w 1:scales 2:biases 3:ydeq             affine_dequant.metal:14
  *   quant    : 0:x 1:w 2:scales_f16 3:biases_f16        affine_dequant.metal:288-296

@@ -131,3 +131,57 @@ def test_fused_entries_by_reference_names(vpq, oracle_mod):
                  {0: d[0], 1: d[1], 2: d[2], 3: d[3], 4: yq, 5: yk, 6: yv}, K=K, q_rows=16, k_rows=16, v_rows=16)
     want = ops.qmv_qkv(*d, 16, 16, 16)
     assert torch.equal(yq, want[0]) and torch.equal(yk, want[1]) and torch.equal(yv, want[2])
+
+
+# ------------------------------------------------------------------------ GEMM
+
+@pytest.mark.parametrize("M,K,N", [(256, 512, 512), (300, 1024, 154), (129, 64, 2), (2048, 4096, 2 * 1024),
+                                   (64, 256, 96)])
+def test_qmm_swiglu(vpq, oracle_mod, M, K, N):
+    """Fused SwiGLU GEMM (affine_qmm_swiglu_w4g64, affine_qmm_steel.metal:641-827) against the
+    oracle's silu(gate) * up over the fp32 dequantise-then-matmul reference; ragged M and N."""
+    codes, s, b = quantized_linear(oracle_mod, N, K, 7700 + M + N + K)
+    x = synth.activations_bf16(M, K, 7701 + M + N + K)
+    d = (to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16), to_dev(x, torch.bfloat16))
+    y = vpq.ops.qmm_swiglu(*d)
+    assert y.shape == (M, N // 2)
+    assert vpq.ops.device_status() == 0
+    # the GEMM multiplies W rounded to bf16, as the reference's does (affine_qmm_steel.metal:86-95):
+    # with the same W the only difference left is the f32 summation order
+    w_bf16 = oracle_mod.bf16_to_f32(oracle_mod.dequant_bf16(codes, s, b))
+    want = synth.bf16_bits_to_f32(oracle_mod.fused_swiglu(oracle_mod.matmul_f32(x, w_bf16, "fast")))
+    e = oracle_mod.err_metrics(f32(y), want)
+    assert e["rel_l2"] < TOL and e["max_rel_rms"] < TOL, e
+    # against the fp32 dequantise-then-matmul oracle the bf16 rounding of W (~1e-3 per product
+    # sum) is amplified by |up| and |silu'(gate)|: the reference's own GEMM bound, rel-L2 < 3e-2
+    ref = oracle_mod.linear_f32(codes, s, b, x, "fast")
+    e32 = oracle_mod.err_metrics(f32(y), synth.bf16_bits_to_f32(oracle_mod.fused_swiglu(ref)))
+    assert e32["rel_l2"] < 5e-3 and e32["max_rel_rms"] < 3e-2, e32
+    # and against silu(gate) * up formed from the plain GEMM's bf16 output
+    plain = vpq.ops.qmm(*d).float()
+    g, u = plain[:, 0::2], plain[:, 1::2]
+    approx = (g / (1.0 + torch.exp(-g)) * u).cpu().numpy()
+    assert oracle_mod.err_metrics(f32(y), approx)["max_rel_rms"] < 2e-2
+
+
+def test_qmm_swiglu_stays_inside_its_output(vpq, oracle_mod):
+    M, K, N = 130, 128, 66
+    d, _ = _linear(oracle_mod, N, K, M, 7800)
+    pad = 128
+    buf = torch.full((pad + M * (N // 2) + pad,), -3.0, dtype=torch.bfloat16, device=dev())
+    y = buf[pad:pad + M * (N // 2)].view(M, N // 2)
+    vpq.ops.qmm_swiglu(*d, out=y)
+    assert torch.all(buf[:pad] == -3.0) and torch.all(buf[pad + M * (N // 2):] == -3.0)
+    assert torch.all(y != -3.0)
+
+
+def test_qmm_swiglu_by_reference_names(vpq, oracle_mod):
+    ops = vpq.ops
+    M, K, N = 256, 256, 256
+    d, _ = _linear(oracle_mod, N, K, M, 7900)
+    want = ops.qmm_swiglu(*d)
+    for entry in ("affine_qmm_swiglu_w4g64", "affine_qmm_swiglu_w4g64_bm64", "affine_qmm_swiglu_w4g64_bm128"):
+        y = torch.empty((M, N // 2), dtype=torch.bfloat16, device=dev())
+        ops.dispatch(ops.function("affine_qmm_steel_bf16", entry), {0: d[0], 1: d[1], 2: d[2], 3: d[3], 4: y},
+                     K=K, N=N, M=M)
+        assert torch.equal(y, want)

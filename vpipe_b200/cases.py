@@ -3,6 +3,7 @@
     python -m vpipe_b200.cases qmv  K N [launches]     # single GEMVs on distinct weight copies
     python -m vpipe_b200.cases plan LAYERS             # the C2 decode set as one plan launch
     python -m vpipe_b200.cases qmm  M K N [reps]       # the GEMM
+    python -m vpipe_b200.cases qmm_swiglu M K N [reps] # the GEMM with the fused SwiGLU store (N = 2 ffn)
 
 Weights are random packed nibbles with bf16 scales / biases (the distribution of the reference's
 kernel tests); each command prints one JSON line with the CUDA-event time. Meant to be wrapped by
@@ -65,17 +66,18 @@ def main(argv):
         t = _time(plan.run, 1)
         nbytes = sum(synth.qmv_bytes(p.K, p.N) for p in synth.CONFIGS["C2"].projs) * layers
         print(json.dumps({"case": "plan", "layers": layers, "us": t * 1e6, "GBs": nbytes / t / 1e9}))
-    elif kind == "qmm":
+    elif kind in ("qmm", "qmm_swiglu"):
         M, K, N = int(argv[1]), int(argv[2]), int(argv[3])
         reps = int(argv[4]) if len(argv) > 4 else 3
         x = torch.randn((M, K), device=dev).to(torch.bfloat16)
         codes, s, b = _weight(N, K, dev)
-        y = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        fn = ops.qmm if kind == "qmm" else ops.qmm_swiglu
+        y = torch.empty((M, N if kind == "qmm" else N // 2), dtype=torch.bfloat16, device=dev)
         for _ in range(2):
-            ops.qmm(codes, s, b, x, out=y)
+            fn(codes, s, b, x, out=y)
         torch.cuda.synchronize()
-        t = _time(lambda: ops.qmm(codes, s, b, x, out=y), reps)
-        print(json.dumps({"case": "qmm", "M": M, "K": K, "N": N, "ms": t * 1e3,
+        t = _time(lambda: fn(codes, s, b, x, out=y), reps)
+        print(json.dumps({"case": kind, "M": M, "K": K, "N": N, "ms": t * 1e3,
                           "tflops": synth.qmm_flops(K, N, M) / t / 1e12}))
     else:
         raise SystemExit(__doc__)

@@ -493,7 +493,7 @@ int launch_qmm_2cta(const uint32_t* w, const uint16_t* scales, const uint16_t* b
                            (uint64_t)N, BK / 8, 128, CU_TENSOR_MAP_SWIZZLE_NONE, "w")) {
     return rc;
   }
-  auto kern = two_cta::affine_qmm_w4g64_2cta_kernel;
+  auto kern = out.swiglu ? two_cta::affine_qmm_w4g64_2cta_kernel<true> : two_cta::affine_qmm_w4g64_2cta_kernel<false>;
   VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
   const int tiles = ((M + two_cta::TM - 1) / two_cta::TM) * ((N + two_cta::TN - 1) / two_cta::TN);
   int pairs = (num_sms() - reserve_sms) / 2;  // SMs left free run a concurrent collective
@@ -576,6 +576,35 @@ extern "C" int vpq_affine_qmm_w4g64_bf16(const uint32_t* w, const void* scales, 
                                          const void* x, void* y, int64_t K, int64_t N, int64_t M,
                                          void* stream) {
   return qmm_launch_reserved(w, scales, biases, x, y, K, N, M, stream, 0);
+}
+
+extern "C" int vpq_affine_qmm_swiglu_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
+                                                const void* x, void* y, int64_t K, int64_t N, int64_t M,
+                                                void* stream) {
+  clear_error();
+  if (!w || !scales || !biases || !x || !y) { return fail(VPQ_ERR_INVALID_ARG, "affine_qmm_swiglu_w4g64: null pointer"); }
+  if (K <= 0 || N <= 0 || M <= 0 || (K % 64) != 0 || (N % 2) != 0) {
+    return fail(VPQ_ERR_INVALID_ARG,
+                "affine_qmm_swiglu_w4g64: need K>0, M>0, K%%64==0 and an even N>0 (K=%lld N=%lld M=%lld)",
+                (long long)K, (long long)N, (long long)M);
+  }
+  if (K > (1 << 20) || N > (1 << 24) || M > (1 << 24)) {
+    return fail(VPQ_ERR_UNSUPPORTED, "affine_qmm_swiglu_w4g64: shape too large (K=%lld N=%lld M=%lld)",
+                (long long)K, (long long)N, (long long)M);
+  }
+  if (!aligned16(w) || !aligned16(x) || !aligned16(y) || (reinterpret_cast<uintptr_t>(scales) & 1) ||
+      (reinterpret_cast<uintptr_t>(biases) & 1)) {
+    return fail(VPQ_ERR_ALIGNMENT, "affine_qmm_swiglu_w4g64: w, x and y must be 16-byte aligned");
+  }
+  if (int rc = require_sm100()) { return rc; }
+  two_cta::OutSpec out = {};
+  out.base[0] = static_cast<__nv_bfloat16*>(y);
+  out.count = 1;
+  out.col0 = 0;
+  out.ld = N / 2;
+  out.swiglu = 1;
+  return launch_qmm_2cta(w, static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases), x, out,
+                         (int)K, (int)N, (int)M, static_cast<cudaStream_t>(stream), 0);
 }
 
 extern "C" int vpq_device_status(void* stream, uint32_t* detail) {

@@ -39,6 +39,8 @@ struct OutSpec {
   int count;
   int col0;
   int64_t ld;
+  int swiglu;  // columns 2j, 2j+1 of the product are gate j, up j: store silu(gate) * up, half as wide
+               // (selects the kernel instantiation)
 };
 
 struct Smem {
@@ -122,6 +124,7 @@ __device__ __forceinline__ constexpr uint32_t make_idesc_pair() {
 }
 
 
+template <bool kSwiglu>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
 affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
                              const __grid_constant__ CUtensorMap tmap_w,
@@ -322,7 +325,13 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // ------------------------------------------------------------ epilogue (both CTAs)
     uint32_t ti = 0;
     bool ok = true;
-    const bool vec_ok = (N % 8) == 0 && (out.ld % 8) == 0 && (out.col0 % 8) == 0;
+    // Fused SwiGLU (the reference's affine_qmm_swiglu_w4g64, affine_qmm_steel.metal:641-800): the
+    // 256 columns of a tile become 128 outputs, one pass of the same store path.
+    constexpr bool swiglu = kSwiglu;
+    const int n_out = swiglu ? N / 2 : N;                 // width of the stored block
+    constexpr int passes = swiglu ? 1 : TN / 128;
+    constexpr int loads = swiglu ? 8 : 4;                 // 32-column accumulator reads per pass
+    const bool vec_ok = (n_out % 8) == 0 && (out.ld % 8) == 0 && (out.col0 % 8) == 0;
     const uint32_t accempty_leader = map_to_cta(bar0, 0) + 8u * (3 * kXStages + 2 * kBTiles + 2);
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++ti) {
       const int m0 = (tile / tiles_n) * TM + (int)rank * 128;
@@ -338,27 +347,46 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
       unsigned char* stg = base_ptr + L::kOffEpi + warp * L::kEpiBytes;
       const int mrow0 = m0 + warp * 32;
 #pragma unroll 1
-      for (int h = 0; h < TN / 128; ++h) {
+      for (int h = 0; h < passes; ++h) {
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < loads; ++c) {
           uint32_t r[32];
           tmem_ld32(taddr + (uint32_t)(h * 128 + c * 32), r);
           tmem_ld_wait();
+          if (swiglu) {
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 pk;
-            pk.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-            pk.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-            pk.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-            pk.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-            const int j = c * 4 + v;  // 16-byte chunk of the 256-byte row
-            *reinterpret_cast<uint4*>(stg + lane * 256 + ((j ^ (lane & 15)) << 4)) = pk;
+            for (int v = 0; v < 2; ++v) {
+              float o[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float g = __uint_as_float(r[16 * v + 2 * i]), u = __uint_as_float(r[16 * v + 2 * i + 1]);
+                o[i] = __fdividef(g, 1.0f + __expf(-g)) * u;
+              }
+              uint4 pk;
+              pk.x = pack_bf16x2(o[0], o[1]);
+              pk.y = pack_bf16x2(o[2], o[3]);
+              pk.z = pack_bf16x2(o[4], o[5]);
+              pk.w = pack_bf16x2(o[6], o[7]);
+              const int j = c * 2 + v;
+              *reinterpret_cast<uint4*>(stg + lane * 256 + ((j ^ (lane & 15)) << 4)) = pk;
+            }
+          } else {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 pk;
+              pk.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+              pk.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+              pk.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+              pk.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+              const int j = c * 4 + v;  // 16-byte chunk of the 256-byte row
+              *reinterpret_cast<uint4*>(stg + lane * 256 + ((j ^ (lane & 15)) << 4)) = pk;
+            }
           }
         }
         __syncwarp();
-        const int nc0 = n0 + h * 128;          // first column of this 128-column half (within the block)
+        const int nc0 = swiglu ? n0 / 2 : n0 + h * 128;  // first stored column of this pass (within the block)
         const int j = lane & 15;               // this lane's 16-byte chunk = 8 columns
-        const bool col_ok = nc0 + j * 8 < N;
+        const bool col_ok = nc0 + j * 8 < n_out;
         if (vec_ok) {
 #pragma unroll 4
           for (int i = 0; i < 16; ++i) {
@@ -382,7 +410,7 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
               for (int d = 0; d < out.count; ++d) {
                 __nv_bfloat16* yrow = out.base[d] + (int64_t)mm * out.ld + out.col0 + nc0 + j * 8;
                 for (int q = 0; q < 8; ++q) {
-                  if (nc0 + j * 8 + q < N) { yrow[q] = e[q]; }
+                  if (nc0 + j * 8 + q < n_out) { yrow[q] = e[q]; }
                 }
               }
             }
