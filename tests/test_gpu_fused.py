@@ -11,7 +11,7 @@ import torch
 
 from vpipe_b200 import synth
 
-from test_gpu_parity import TOL, bits16, dev, f32, quantized_linear, to_dev
+from test_gpu_parity import TOL, bits16, bits32, dev, f32, quantized_linear, to_dev
 
 pytestmark = pytest.mark.gpu
 
@@ -185,3 +185,22 @@ def test_qmm_swiglu_by_reference_names(vpq, oracle_mod):
         ops.dispatch(ops.function("affine_qmm_steel_bf16", entry), {0: d[0], 1: d[1], 2: d[2], 3: d[3], 4: y},
                      K=K, N=N, M=M)
         assert torch.equal(y, want)
+
+
+def test_checkpoint_on_disk_loads_and_computes(vpq, oracle_mod, tmp_path):
+    """quantize (GPU) -> write the reference's on-disk triple -> load -> dequantize / GEMV: the
+    bytes survive the file format and the result equals the oracle's."""
+    from vpipe_b200 import checkpoint
+    N, K = 96, 512
+    w = to_dev(synth.f32_to_bf16_bits(synth.weight_f32(N, K, 8100)), torch.bfloat16)
+    codes, s16, b16 = vpq.ops.quantize(w)
+    checkpoint.write_model(str(tmp_path), {
+        "layers.0.proj.weight": bits32(codes),
+        "layers.0.proj.scales": bits16(s16).view(np.float16),
+        "layers.0.proj.biases": bits16(b16).view(np.float16),
+    }, 64, 4)
+    m = checkpoint.Model(str(tmp_path))
+    c2, s2, b2 = checkpoint.load_quant_linear(m, "layers.0.proj", dev())
+    assert torch.equal(c2, codes)
+    want = oracle_mod.dequant_bf16(bits32(codes), oracle_mod.f16_to_bf16(bits16(s16)), oracle_mod.f16_to_bf16(bits16(b16)))
+    assert np.array_equal(bits16(vpq.ops.dequantize(c2, s2, b2)), want)
