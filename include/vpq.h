@@ -109,6 +109,15 @@ int vpq_affine_qmv_qkv_w4g64_bf16(const uint32_t* w, const void* scales, const v
                                   void* q_out, void* k_out, void* v_out, int64_t K, int64_t q_rows,
                                   int64_t k_rows, int64_t v_rows, int64_t M, void* stream);
 
+/* Small-batch decode GEMV: the M rows of x (M = 2..8: decode of several branches, MTP verify)
+ * share ONE stream of the weights, up to 4 rows per pass (4 up to K = 5120, 2 up to K = 8192: the
+ * rows live in shared memory; longer rows, and a single left-over row, run on the M = 1 kernel). fp16 tensor-core arithmetic with exact products and f32 accumulation; the rows agree
+ * with vpq_affine_qmv_w4g64_bf16 to f32 rounding, not bit for bit (the reference's batched rows
+ * are bit-identical to its M = 1 kernel). Replaces affine_qmv_batch_w4g64 / affine_qmv_batch4_w4g64
+ * (slots as QMV, 7: total rows), gpu-kernels/metal/quant/affine_qmv.metal:1553-1705. */
+int vpq_affine_qmv_batch_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                                    void* y, int64_t K, int64_t N, int64_t M, void* stream);
+
 /* A set of independent GEMVs enqueued back to back (one launch each, in order),
  * e.g. the q | k | v or gate | up projections of one decoder layer. descs_host
  * is a host array read during the call. Each launch opts into programmatic

@@ -49,6 +49,8 @@ def test_function_table_uses_reference_names(vpq):
                            ("affine_qmv_bf16", "affine_qmv_w4g64_add"),
                            ("affine_qmv_bf16", "affine_qmv_swiglu_w4g64"),
                            ("affine_qmv_bf16", "affine_qmv_qkv_w4g64"),
+                           ("affine_qmv_bf16", "affine_qmv_batch_w4g64"),
+                           ("affine_qmv_bf16", "affine_qmv_batch4_w4g64"),
                            ("affine_qmm_steel_bf16", "affine_qmm_steel_w4g64"),
                            ("affine_qmm_steel_bf16", "affine_qmm_steel_w4g64_bm64"),
                            ("affine_qmm_steel_bf16", "affine_qmm_steel_w4g64_bm128"),
@@ -95,6 +97,8 @@ def test_argument_validation_happens_before_any_device_work(vpq):
     assert L.vpq_affine_qmv_qkv_w4g64_bf16(p16, p16, p16, p16, p16, p16, p16, 64, 0, 8, 8, 1, None) == INVALID
     assert L.vpq_affine_qmv_qkv_w4g64_bf16(p16, p16, p16, p16, p16, None, p16, 64, 8, 8, 8, 1, None) == INVALID
     assert L.vpq_affine_qmm_swiglu_w4g64_bf16(p16, p16, p16, p16, p16, 64, 9, 4, None) == INVALID
+    assert L.vpq_affine_qmv_batch_w4g64_bf16(p16, p16, p16, p16, None, 64, 8, 4, None) == INVALID
+    assert L.vpq_affine_qmv_batch_w4g64_bf16(p16, p16, p16, p16 + 2, p16, 64, 8, 4, None) == ALIGN
     # nsplit argument checks need no communicator
     assert L.vpq_affine_qmm_w4g64_bf16_nsplit(None, p16, p16, p16, p16, p16, None, 64, 8, 1, 1, None) == INVALID
     assert L.vpq_dispatch(None, None, None) == INVALID

@@ -204,3 +204,51 @@ def test_checkpoint_on_disk_loads_and_computes(vpq, oracle_mod, tmp_path):
     assert torch.equal(c2, codes)
     want = oracle_mod.dequant_bf16(bits32(codes), oracle_mod.f16_to_bf16(bits16(s16)), oracle_mod.f16_to_bf16(bits16(b16)))
     assert np.array_equal(bits16(vpq.ops.dequantize(c2, s2, b2)), want)
+
+
+# ------------------------------------------------------------------------ small-batch GEMV
+
+@pytest.mark.parametrize("K,N,M", [(4096, 4096, 4), (4096, 1024, 2), (12288, 4096, 3), (4096, 12288, 8),
+                                   (3840, 40, 3), (64, 8, 2), (320, 33, 5), (1088, 8193, 1)])
+def test_qmv_batch_rows_share_one_weight_stream(vpq, oracle_mod, K, N, M):
+    """affine_qmv_batch(4)_w4g64 (affine_qmv.metal:1553-1705): every row within the GEMV's tolerance
+    of the fp32 oracle and equal, up to f32 rounding before the bf16 store, to the M = 1 kernel's."""
+    d, ref = _linear(oracle_mod, N, K, M, 8200 + N + K + M)
+    y = vpq.ops.qmv_batch_rows(*d)
+    assert y.shape == (M, N)
+    e = oracle_mod.err_metrics(f32(y), ref)
+    assert e["rel_l2"] < TOL and e["max_rel_rms"] < TOL and e["max_rel_1e2"] < TOL, e
+    serial = vpq.ops.qmv(*d)
+    a, b = f32(y), f32(serial)
+    # one bf16 ulp of the larger magnitude (2^-7 relative), or f32 noise next to a zero crossing
+    assert np.all(np.abs(a - b) <= np.maximum(np.abs(a), np.abs(b)) * 2.0 ** -7 + 1e-5 * np.abs(b).max())
+    assert (bits16(y) == bits16(serial)).mean() > (0.97 if y.numel() >= 1000 else 0.85)
+
+
+def test_qmv_batch_rows_with_very_different_magnitudes(vpq, oracle_mod):
+    """Each row of x has its own power-of-two scale: a row 2^40 times larger than its neighbour
+    must not cost the small one its accuracy."""
+    K, N = 2048, 64
+    codes, s, b = quantized_linear(oracle_mod, N, K, 8300)
+    x = synth.bf16_bits_to_f32(synth.activations_bf16(3, K, 8301))
+    x[1] *= 2.0 ** 40
+    x[2] *= 2.0 ** -30
+    xb = synth.f32_to_bf16_bits(x)
+    y = vpq.ops.qmv_batch_rows(to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16),
+                               to_dev(xb, torch.bfloat16))
+    ref = oracle_mod.linear_f32(codes, s, b, xb, "f64")
+    for m in range(3):
+        e = oracle_mod.err_metrics(f32(y)[m:m + 1], ref[m:m + 1])
+        assert e["rel_l2"] < TOL and e["max_rel_rms"] < TOL, (m, e)
+
+
+def test_qmv_batch_by_reference_names(vpq, oracle_mod):
+    ops = vpq.ops
+    K, N, M = 512, 48, 4
+    d, _ = _linear(oracle_mod, N, K, M, 8400)
+    want = ops.qmv_batch_rows(*d)
+    for entry in ("affine_qmv_batch_w4g64", "affine_qmv_batch4_w4g64"):
+        y = torch.empty((M, N), dtype=torch.bfloat16, device=dev())
+        ops.dispatch(ops.function("affine_qmv_bf16", entry), {0: d[0], 1: d[1], 2: d[2], 3: d[3], 4: y},
+                     K=K, N=N, M=M)
+        assert torch.equal(y, want)

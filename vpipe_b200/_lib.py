@@ -25,6 +25,7 @@ SYMBOLS = [
     ("vpq_affine_dequant_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _i64, _i64, _vp]),
     ("vpq_affine_qmv_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     ("vpq_affine_qmm_swiglu_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    ("vpq_affine_qmv_batch_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     ("vpq_affine_qmv_w4g64_bf16_add", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp]),
     ("vpq_affine_qmv_swiglu_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     ("vpq_affine_qmv_qkv_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp]),

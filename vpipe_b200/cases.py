@@ -2,6 +2,7 @@
 
     python -m vpipe_b200.cases qmv  K N [launches]     # single GEMVs on distinct weight copies
     python -m vpipe_b200.cases plan LAYERS             # the C2 decode set as one plan launch
+    python -m vpipe_b200.cases qmv_batch K N M [launches]  # small-batch GEMV vs M serial GEMVs
     python -m vpipe_b200.cases qmm  M K N [reps]       # the GEMM
     python -m vpipe_b200.cases qmm_swiglu M K N [reps] # the GEMM with the fused SwiGLU store (N = 2 ffn)
 
@@ -52,6 +53,27 @@ def main(argv):
         t = _time(lambda: (lambda p: ops.qmv(*p[:4], out=p[4]))(next(it)), n)
         print(json.dumps({"case": "qmv", "K": K, "N": N, "us": t * 1e6,
                           "GBs": synth.qmv_bytes(K, N) / t / 1e9}))
+    elif kind == "qmv_batch":
+        K, N, M = int(argv[1]), int(argv[2]), int(argv[3])
+        n = int(argv[4]) if len(argv) > 4 else 8
+        x = torch.randn((M, K), device=dev).to(torch.bfloat16)
+        sets = [_weight(N, K, dev) + (x, torch.empty((M, N), dtype=torch.bfloat16, device=dev)) for _ in range(n)]
+        out = {"case": "qmv_batch", "K": K, "N": N, "M": M}
+        for name, fn in (("batch", ops.qmv_batch_rows), ("serial", ops.qmv)):
+            for p in sets:
+                fn(*p[:4], out=p[4])
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()          # graph replay: launch overhead out of the picture
+            with torch.cuda.graph(g):
+                for p in sets:
+                    fn(*p[:4], out=p[4])
+            g.replay()
+            torch.cuda.synchronize()
+            t = _time(g.replay, 3) / n
+            out[name + "_us"] = t * 1e6
+            out[name + "_weight_GBs"] = synth.qmv_bytes(K, N) / t / 1e9
+        out["speedup"] = out["serial_us"] / out["batch_us"]
+        print(json.dumps(out))
     elif kind == "plan":
         layers = int(argv[1])
         xs = {K: torch.randn((1, K), device=dev).to(torch.bfloat16) for K in (4096, 12288)}

@@ -142,7 +142,7 @@ extern "C" size_t vpq_scale_bytes(int N, int K, int group) {
 struct vpq_function_s {
   const char* library;
   const char* entry;
-  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu
+  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch
 };
 
 // The reference selects the element type with the library-name suffix and
@@ -154,6 +154,8 @@ static const vpq_function_s g_functions[] = {
     {"affine_qmv_bf16", "affine_qmv_w4g64_add", 5},
     {"affine_qmv_bf16", "affine_qmv_swiglu_w4g64", 6},
     {"affine_qmv_bf16", "affine_qmv_qkv_w4g64", 7},
+    {"affine_qmv_bf16", "affine_qmv_batch_w4g64", 9},
+    {"affine_qmv_bf16", "affine_qmv_batch4_w4g64", 9},
     {"affine_qmm_steel_bf16", "affine_qmm_steel_w4g64", 1},
     {"affine_qmm_steel_bf16", "affine_qmm_steel_w4g64_bm64", 1},
     {"affine_qmm_steel_bf16", "affine_qmm_steel_w4g64_bm128", 1},
@@ -217,6 +219,9 @@ extern "C" int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* a, 
     case 8:
       return vpq_affine_qmm_swiglu_w4g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
                                               const_cast<void*>(b[4]), a->K, a->N, a->M, stream);
+    case 9:
+      return vpq_affine_qmv_batch_w4g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
+                                             const_cast<void*>(b[4]), a->K, a->N, a->M < 1 ? 1 : a->M, stream);
     default:
       return fail(VPQ_ERR_NOT_FOUND, "dispatch: corrupt function handle");
   }

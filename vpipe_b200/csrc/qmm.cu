@@ -616,6 +616,9 @@ extern "C" int vpq_device_status(void* stream, uint32_t* detail) {
   VPQ_CUDA_OK(cudaStreamSynchronize(st));
   uint32_t vq = 0;
   if (int rc = qmv_status_read(st, &vq)) { return rc; }
+  if (vq == 0) {
+    if (int rc = qmvb_status_read(st, &vq)) { return rc; }  // the small-batch GEMV reports like the GEMV
+  }
   if (detail) { *detail = v ? v : (vq ? (vq | 0x10000u) : 0u); }
   uint32_t vn = 0;
   if (int rc = nsplit_status_read(st, &vn)) { return rc; }
