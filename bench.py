@@ -216,15 +216,27 @@ def bench_qmv(torch, dist, ops, synth, args, rank, world, dev, pk):
     cfg = synth.CONFIGS["C2"]
     layers = []
     bytes_step = 0
-    xs = {}
-    for K in sorted({p.K for p in cfg.projs}):
+    # the step's activations live in ONE device buffer (one host->device copy per step), the last
+    # layer's outputs in another (one device->host copy per step)
+    Ks = sorted({p.K for p in cfg.projs})
+    x_all = torch.empty((sum(Ks),), dtype=torch.bfloat16, device=dev)
+    xs, off = {}, 0
+    for K in Ks:
         g = torch.Generator(device=dev).manual_seed(synth.seed_for("x", K, rank))
-        xs[K] = torch.randn((1, K), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        xs[K] = x_all[off:off + K].view(1, K)     # offsets are multiples of 4096 elements: 16-byte aligned
+        xs[K].copy_(torch.randn((1, K), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16))
+        off += K
+    y_last = torch.empty((sum(p.N for p in cfg.projs),), dtype=torch.bfloat16, device=dev)
     problems = []
     for layer in range(LAYERS):
+        off = 0
         for p in cfg.projs:
             codes, s, b = make_linear(torch, ops, p.N, p.K, synth.seed_for("w", layer, p.name, rank), dev)
-            y = torch.empty((1, p.N), dtype=torch.bfloat16, device=dev)
+            if layer == LAYERS - 1:
+                y = y_last[off:off + p.N].view(1, p.N)
+                off += p.N
+            else:
+                y = torch.empty((1, p.N), dtype=torch.bfloat16, device=dev)
             problems.append((codes, s, b, xs[p.K], y))
             bytes_step += synth.qmv_bytes(p.K, p.N, 1)
         layers.append(problems[-len(cfg.projs):])
@@ -281,18 +293,15 @@ def bench_qmv(torch, dist, ops, synth, args, rank, world, dev, pk):
     value = bytes_step * args.steps * world / t / 1e9
 
     # e2e: the step's activations come from pinned host memory, the last layer's outputs go back
-    host_x = {K: torch.randn((1, K)).to(torch.bfloat16).pin_memory() for K in xs}
-    last = layers[-1]
-    host_y = [torch.empty((1, pr[4].shape[1]), dtype=torch.bfloat16).pin_memory() for pr in last]
-    h2d = sum(v.numel() * 2 for v in host_x.values())
-    d2h = sum(v.numel() * 2 for v in host_y)
+    host_x = torch.randn((x_all.numel(),)).to(torch.bfloat16).pin_memory()
+    host_y = torch.empty((y_last.numel(),), dtype=torch.bfloat16).pin_memory()
+    h2d = host_x.numel() * 2
+    d2h = host_y.numel() * 2
 
     def e2e_step():
-        for K, hx in host_x.items():
-            xs[K].copy_(hx, non_blocking=True)
+        x_all.copy_(host_x, non_blocking=True)
         step()
-        for hy, pr in zip(host_y, last):
-            hy.copy_(pr[4], non_blocking=True)
+        host_y.copy_(y_last, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     te = timed(torch, e2e_step, args.steps, args.warmup, barrier)

@@ -137,12 +137,19 @@ class ComputeEncoder {
   void set_buffer(int index, const void* device_ptr) {
     if (index >= 0 && index < 8) { _args.buffers[index] = device_ptr; }
   }
-  // The reference numbers the int constants after the buffers: QMV 5:K 6:N, QMM 5:K 6:N 7:M,
-  // dequant 4:K 5:N, quant 4:K 5:N 6:clip. set_k / set_n / set_m / set_clip say which is which.
+  // The reference numbers the int constants after the buffers: QMV 5:K 6:N (7: residual buffer of
+  // _add, total rows of _batch), QMM 5:K 6:N 7:M, dequant 4:K 5:N, quant 4:K 5:N 6:clip.
+  // set_k / set_n / set_m / set_clip say which is which.
   void set_k(int64_t K) { _args.K = K; }
   void set_n(int64_t N) { _args.N = N; }
   void set_m(int64_t M) { _args.M = M; }
   void set_clip(float clip) { _args.clip = clip; }
+  // affine_qmv_qkv_w4g64 numbers its constants 7:K 8:q_rows 9:k_rows 10:v_rows (outputs in slots 4..6)
+  void set_qkv_rows(int64_t q_rows, int64_t k_rows, int64_t v_rows) {
+    _args.q_rows = q_rows;
+    _args.k_rows = k_rows;
+    _args.v_rows = v_rows;
+  }
   void dispatch();
 
  private:
