@@ -80,6 +80,20 @@ int vpq_narrow_f32_bf16(const float* src, void* dst_bf16, int64_t n, void* strea
  * (same conversion in generative-models/qwen3/metal-qwen-model.cc:203-213). */
 int vpq_scales_f16_to_bf16(const void* src_f16, void* dst_bf16, int64_t n, void* stream);
 
+/* The quantizer and dequantizer for the format twins the reference's mixed-precision and
+ * GGUF-repacked checkpoints use: bits 4 or 8, group 64 or 32 (codes u32 [N, K*bits/32], 8-bit
+ * codes one byte per value, little-endian in the word; scales / biases [N, K/group]). Bit-exact
+ * with kernels affine_quant_w8_g64 / _w4_g64 / _w8_g32 / _w4_g32 and affine_dequant_w4g64 / _w8g64
+ * / _w8g32, gpu-kernels/metal/quant/affine_dequant.metal:25-135,243-301; validated as
+ * AffineQuantizer::quantize_linear does, generative-models/quantize/affine-quantizer.cc:55-57.
+ * The GEMV / GEMM kernels of this library compute w4 g64 only: other formats are dequantised once
+ * and multiplied densely, as the reference itself does for its codec weights
+ * (affine_dequant.metal:100-106). */
+int vpq_affine_quant(const void* w_elt, int src_is_bf16, uint32_t* codes, void* scales_f16, void* biases_f16,
+                     int64_t K, int64_t N, int bits, int group, float clip, void* stream);
+int vpq_affine_dequant_bf16(const uint32_t* w, const void* scales, const void* biases, void* ydeq, int64_t K,
+                            int64_t N, int bits, int group, void* stream);
+
 /* Dequantize to dense bf16 [N,K]: bf16_rne(float(s)*q + float(b)). Bit-exact.
  * Replaces kernel affine_dequant_w4g64 (slots 0:w 1:scales 2:biases 3:ydeq 4:K 5:N),
  * gpu-kernels/metal/quant/affine_dequant.metal:25-58. */

@@ -51,6 +51,11 @@ def lib():
         L.vpq_o_quant_w4_g64.restype = C.c_int
         L.vpq_o_quant_w4_g64.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
                                          C.c_void_p, C.c_int, C.c_int, C.c_float]
+        L.vpq_o_quant.restype = C.c_int
+        L.vpq_o_quant.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                                  C.c_int, C.c_int, C.c_int, C.c_int, C.c_float]
+        L.vpq_o_dequant_bf16.restype = C.c_int
+        L.vpq_o_dequant_bf16.argtypes = [C.c_void_p] * 4 + [C.c_int] * 4
         for name in ("vpq_o_dequant_w4g64_bf16", "vpq_o_dequant_w4g64_f32"):
             f = getattr(L, name)
             f.restype = None
@@ -100,6 +105,12 @@ def ref():
             d = getattr(R, f"ref_affine_dequant_w4g64_{sfx}")
             d.restype = C.c_int
             d.argtypes = [C.c_void_p] * 4 + [C.c_int, C.c_int]
+            q = getattr(R, f"ref_affine_quant_{sfx}")
+            q.restype = C.c_int
+            q.argtypes = [C.c_void_p] * 4 + [C.c_int] * 4 + [C.c_float]
+            d = getattr(R, f"ref_affine_dequant_{sfx}")
+            d.restype = C.c_int
+            d.argtypes = [C.c_void_p] * 4 + [C.c_int] * 4
         _ref = R
     return _ref
 
@@ -158,6 +169,38 @@ def dequant_bf16(codes, s_bf16, b_bf16, use_ref: bool = False) -> np.ndarray:
         ref().ref_affine_dequant_w4g64_bf16(_p(codes), _p(s), _p(b), _p(out), K, N)
     else:
         lib().vpq_o_dequant_w4g64_bf16(_p(codes), _p(s), _p(b), _p(out), K, N)
+    return out
+
+
+def quant(w_elt: np.ndarray, bits: int, group: int, src_is_bf16: bool = True, clip: float = 1.0,
+          use_ref: bool = False):
+    """Any (bits, group) of the reference's quantizer template (4|8, 64|32):
+    [N,K] f16/bf16 bit patterns -> (codes u32 [N,K*bits/32], scales f16, biases f16 [N,K/group])."""
+    w = _c(w_elt, np.uint16)
+    N, K = w.shape
+    codes = np.zeros((N, K * bits // 32), np.uint32)
+    s = np.zeros((N, K // group), np.uint16)
+    b = np.zeros((N, K // group), np.uint16)
+    if use_ref:
+        fn = getattr(ref(), "ref_affine_quant_" + ("bf16" if src_is_bf16 else "f16"))
+        rc = fn(_p(w), _p(codes), _p(s), _p(b), K, N, bits, group, clip)
+    else:
+        rc = lib().vpq_o_quant(_p(w), int(src_is_bf16), _p(codes), _p(s), _p(b), K, N, bits, group, clip)
+    if rc != 0:
+        raise ValueError("quant: bad arguments")
+    return codes, s, b
+
+
+def dequant_bf16_any(codes, s_bf16, b_bf16, bits: int, group: int, use_ref: bool = False) -> np.ndarray:
+    """Dequantizer for any (bits, group); the reference ships w4g64, w8g64 and w8g32 kernels."""
+    codes = _c(codes, np.uint32)
+    N, Kw = codes.shape
+    K = Kw * 32 // bits
+    out = np.empty((N, K), np.uint16)
+    args = (_p(codes), _p(_c(s_bf16, np.uint16)), _p(_c(b_bf16, np.uint16)), _p(out), K, N, bits, group)
+    rc = ref().ref_affine_dequant_bf16(*args) if use_ref else lib().vpq_o_dequant_bf16(*args)
+    if rc != 0:
+        raise ValueError("dequant_bf16_any: bad arguments")
     return out
 
 

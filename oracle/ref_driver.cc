@@ -59,4 +59,56 @@ int REF_FN(ref_affine_dequant_w4g64)(const uint32_t* w, const void* s, const voi
   return 0;
 }
 
+// The other instantiations of the same template (w8_g64, w8_g32, w4_g32) and the 8-bit
+// dequantizers: selected by (bits, group).
+int REF_FN(ref_affine_quant)(const void* x, uint32_t* w, void* s, void* b, int K, int N, int bits, int group,
+                             float clip) {
+  if (N <= 0 || K <= 0 || (K % group) != 0) { return -1; }
+  for (unsigned n = 0; n < (unsigned)N; ++n) {
+    for (unsigned g = 0; g < (unsigned)(K / group); ++g) {
+      const VPIPE_ELT* xp = static_cast<const VPIPE_ELT*>(x);
+      half* sp = static_cast<half*>(s);
+      half* bp = static_cast<half*>(b);
+      const metal::uint2 gid(g, n);
+      if (bits == 8 && group == 64) {
+        affine_quant_w8_g64(xp, w, sp, bp, K, N, clip, gid);
+      } else if (bits == 4 && group == 64) {
+        affine_quant_w4_g64(xp, w, sp, bp, K, N, clip, gid);
+      } else if (bits == 8 && group == 32) {
+        affine_quant_w8_g32(xp, w, sp, bp, K, N, clip, gid);
+      } else if (bits == 4 && group == 32) {
+        affine_quant_w4_g32(xp, w, sp, bp, K, N, clip, gid);
+      } else {
+        return -1;
+      }
+    }
+  }
+  return 0;
+}
+
+// The reference ships dequantizers for w4g64, w8g64 and w8g32 (no w4g32 one).
+int REF_FN(ref_affine_dequant)(const uint32_t* w, const void* s, const void* b, void* out, int K, int N,
+                               int bits, int group) {
+  if (N <= 0 || K <= 0 || (K % group) != 0) { return -1; }
+  const unsigned words = (unsigned)(K * bits / 32);
+  for (unsigned n = 0; n < (unsigned)N; ++n) {
+    for (unsigned word = 0; word < words; ++word) {
+      const VPIPE_ELT* sp = static_cast<const VPIPE_ELT*>(s);
+      const VPIPE_ELT* bp = static_cast<const VPIPE_ELT*>(b);
+      VPIPE_ELT* op = static_cast<VPIPE_ELT*>(out);
+      const metal::uint2 gid(word, n);
+      if (bits == 4 && group == 64) {
+        affine_dequant_w4g64(w, sp, bp, op, K, N, gid);
+      } else if (bits == 8 && group == 64) {
+        affine_dequant_w8g64(w, sp, bp, op, K, N, gid);
+      } else if (bits == 8 && group == 32) {
+        affine_dequant_w8g32(w, sp, bp, op, K, N, gid);
+      } else {
+        return -1;
+      }
+    }
+  }
+  return 0;
+}
+
 }  // extern "C"

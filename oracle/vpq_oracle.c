@@ -156,7 +156,79 @@ int vpq_o_quant_w4_g64(const uint16_t* w_elt, int src_is_bf16, uint32_t* codes,
   return 0;
 }
 
+/* The template the reference instantiates for w8_g64, w4_g64, w8_g32 and w4_g32
+ * (affine_quant_impl<BITS, GROUP>, affine_dequant.metal:243-301). */
+int vpq_o_quant(const uint16_t* w_elt, int src_is_bf16, uint32_t* codes, uint16_t* scales_f16,
+                uint16_t* biases_f16, int K, int N, int bits, int group, float clip) {
+  if (N <= 0 || K <= 0 || (bits != 4 && bits != 8) || (group != 32 && group != 64) || (K % group) != 0) {
+    return -1;
+  }
+  const int KG = K / group;
+  const int VPW = 32 / bits;          /* values per word, :255 */
+  const int WPG = group / VPW;        /* words per group, :256 */
+  const int QMAX = (1 << bits) - 1;
+  const int WPR = K * bits / 32;      /* words per row, :258 */
+  for (int n = 0; n < N; ++n) {
+    for (int grp = 0; grp < KG; ++grp) {
+      const uint16_t* xp = w_elt + (size_t)n * K + (size_t)grp * group;
+      float v[64];
+      float mn = INFINITY, mx = -INFINITY;
+      for (int i = 0; i < group; ++i) {
+        v[i] = src_is_bf16 ? vpq_o_bf16_to_f32(xp[i]) : vpq_o_f16_to_f32(xp[i]);
+        mn = msl_min(mn, v[i]);
+        mx = msl_max(mx, v[i]);
+      }
+      if (clip < 1.0f) {
+        const float mid = 0.5f * (mn + mx);
+        mn = mid + (mn - mid) * clip;
+        mx = mid + (mx - mid) * clip;
+      }
+      const float scale = (mx - mn) / (float)QMAX;
+      const float inv = (scale > 0.0f) ? 1.0f / scale : 0.0f;
+      scales_f16[(size_t)n * KG + grp] = vpq_o_f32_to_f16(scale);
+      biases_f16[(size_t)n * KG + grp] = vpq_o_f32_to_f16(mn);
+      uint32_t* wp = codes + (size_t)n * WPR + (size_t)grp * WPG;
+      for (int wi = 0; wi < WPG; ++wi) {
+        uint32_t packed = 0;
+        for (int i = 0; i < VPW; ++i) {
+          int q = (int)roundf((v[wi * VPW + i] - mn) * inv);
+          q = q < 0 ? 0 : (q > QMAX ? QMAX : q);
+          packed |= ((uint32_t)q) << (bits * i);
+        }
+        wp[wi] = packed;
+      }
+    }
+  }
+  return 0;
+}
+
 /* ------------------------------------------------------------- dequantize */
+
+/* affine_dequant_w4g64 / w8g64 / w8g32 (affine_dequant.metal:25-58, 69-98, 107-135) and the
+ * group-32 form of the 4-bit one: y = (ELT)(s * q + b), one rounding in f32, one to bf16. */
+int vpq_o_dequant_bf16(const uint32_t* codes, const uint16_t* s_bf16, const uint16_t* b_bf16,
+                       uint16_t* out_bf16, int K, int N, int bits, int group) {
+  if (N <= 0 || K <= 0 || (bits != 4 && bits != 8) || (group != 32 && group != 64) || (K % group) != 0) {
+    return -1;
+  }
+  const int VPW = 32 / bits, Kw = K / VPW, Kg = K / group;
+  const uint32_t mask = (1u << bits) - 1u;
+  for (int n = 0; n < N; ++n) {
+    for (int word = 0; word < Kw; ++word) {
+      const int k0 = word * VPW;
+      const size_t g = (size_t)n * Kg + (size_t)(k0 / group);
+      const float s = vpq_o_bf16_to_f32(s_bf16[g]);
+      const float b = vpq_o_bf16_to_f32(b_bf16[g]);
+      const uint32_t packed = codes[(size_t)n * Kw + word];
+      for (int i = 0; i < VPW; ++i) {
+        const uint32_t q = (packed >> (bits * i)) & mask;
+        out_bf16[(size_t)n * K + k0 + i] = vpq_o_f32_to_bf16(s * (float)q + b);  /* s*q exact in f32 */
+      }
+    }
+  }
+  return 0;
+}
+
 
 void vpq_o_dequant_w4g64_bf16(const uint32_t* codes, const uint16_t* s_bf16,
                               const uint16_t* b_bf16, uint16_t* out_bf16,

@@ -53,6 +53,11 @@ int vpq_o_quant_w4_g64(const uint16_t* w_elt, int src_is_bf16, uint32_t* codes,
 
 /* Dequantize to bf16: bf16_rne(float(s)*float(q) + float(b)).
  * gpu-kernels/metal/quant/affine_dequant.metal:25-58 */
+/* Any of the reference's (bits, group) pairs: (4|8, 64|32). */
+int vpq_o_quant(const uint16_t* w_elt, int src_is_bf16, uint32_t* codes, uint16_t* scales_f16,
+                uint16_t* biases_f16, int K, int N, int bits, int group, float clip);
+int vpq_o_dequant_bf16(const uint32_t* codes, const uint16_t* s_bf16, const uint16_t* b_bf16,
+                       uint16_t* out_bf16, int K, int N, int bits, int group);
 void vpq_o_dequant_w4g64_bf16(const uint32_t* codes, const uint16_t* s_bf16,
                               const uint16_t* b_bf16, uint16_t* out_bf16,
                               int K, int N);

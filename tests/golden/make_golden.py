@@ -67,6 +67,25 @@ def dequant_case(name, N, K, seed):
     print(name, {k: v.shape for k, v in out.items()})
 
 
+def twin_case(name, N, K, bits, group, bf16, clip, seed):
+    """The other (bits, group) instantiations of the quantizer template and their dequantizers
+    (affine_dequant.metal:60-135, 303-306); the reference has no w4g32 dequant kernel."""
+    w = synth.weight_f32(N, K, seed)
+    wb = synth.f32_to_bf16_bits(w) if bf16 else w.astype(np.float16).view(np.uint16)
+    wb[0, :group] = 0x8000                     # all -0
+    wb[1, :group] = wb[1, 0]                   # constant group
+    wb[2, 0:group:2], wb[2, 1:group:2] = 0x8000, 0x0000
+    codes, s, b = oracle.quant(wb, bits, group, bf16, clip, use_ref=True)
+    out = {"w_bits": wb, "src_is_bf16": np.array(int(bf16)), "clip": np.array(clip, np.float32),
+           "bits": np.array(bits), "group": np.array(group), "codes": codes, "scales_f16": s, "biases_f16": b}
+    if bf16 and (bits, group) != (4, 32):
+        sb, bb = oracle.f16_to_bf16(s), oracle.f16_to_bf16(b)
+        out["scales_bf16"], out["biases_bf16"] = sb, bb
+        out["deq_bf16"] = oracle.dequant_bf16_any(codes, sb, bb, bits, group, use_ref=True)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **out)
+    print(name, {k: v.shape for k, v in out.items()})
+
+
 if __name__ == "__main__":
     oracle.build()
     if not oracle.have_ref():
@@ -76,3 +95,7 @@ if __name__ == "__main__":
     quant_case("quant_f16_n16_k192", 16, 192, False, 1.0, 13, special=True)
     quant_case("quant_bf16_clip09_n16_k128", 16, 128, True, 0.9, 14, special=True)
     dequant_case("dequant_bf16_n33_k320", 33, 320, 15)
+    twin_case("twin_w8g64_bf16_n12_k256", 12, 256, 8, 64, True, 1.0, 16)
+    twin_case("twin_w8g32_bf16_n12_k160", 12, 160, 8, 32, True, 0.9, 17)
+    twin_case("twin_w4g32_bf16_n12_k160", 12, 160, 4, 32, True, 1.0, 18)
+    twin_case("twin_w8g64_f16_n12_k128", 12, 128, 8, 64, False, 1.0, 19)

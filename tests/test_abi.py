@@ -59,7 +59,11 @@ def test_function_table_uses_reference_names(vpq):
                            ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64_bm128"),
                            ("affine_dequant_bf16", "affine_dequant_w4g64"),
                            ("affine_dequant_bf16", "affine_quant_w4_g64"),
-                           ("affine_dequant", "affine_quant_w4_g64")]:
+                           ("affine_dequant", "affine_quant_w4_g64"),
+                           ("affine_dequant_bf16", "affine_dequant_w8g64"),
+                           ("affine_dequant_bf16", "affine_dequant_w8g32"),
+                           ("affine_dequant_bf16", "affine_quant_w8_g64"),
+                           ("affine_dequant", "affine_quant_w4_g32")]:
         fn = ops.function(libname, entry)
         assert fn, (libname, entry)
         assert vpq.lib().vpq_function_name(fn).decode() == entry
@@ -99,6 +103,10 @@ def test_argument_validation_happens_before_any_device_work(vpq):
     assert L.vpq_affine_qmm_swiglu_w4g64_bf16(p16, p16, p16, p16, p16, 64, 9, 4, None) == INVALID
     assert L.vpq_affine_qmv_batch_w4g64_bf16(p16, p16, p16, p16, None, 64, 8, 4, None) == INVALID
     assert L.vpq_affine_qmv_batch_w4g64_bf16(p16, p16, p16, p16 + 2, p16, 64, 8, 4, None) == ALIGN
+    # format twins: width and group are validated as AffineQuantizer::quantize_linear does
+    assert L.vpq_affine_quant(p16, 1, p16, p16, p16, 64, 8, 3, 64, 1.0, None) == UNSUP
+    assert L.vpq_affine_quant(p16, 1, p16, p16, p16, 48, 8, 8, 32, 1.0, None) == INVALID
+    assert L.vpq_affine_dequant_bf16(p16, p16, p16, p16, 64, 8, 8, 16, None) == UNSUP
     # nsplit argument checks need no communicator
     assert L.vpq_affine_qmm_w4g64_bf16_nsplit(None, p16, p16, p16, p16, p16, None, 64, 8, 1, 1, None) == INVALID
     assert L.vpq_dispatch(None, None, None) == INVALID

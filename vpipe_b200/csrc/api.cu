@@ -142,7 +142,7 @@ extern "C" size_t vpq_scale_bytes(int N, int K, int group) {
 struct vpq_function_s {
   const char* library;
   const char* entry;
-  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch
+  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch; 10 + code: quant / dequant twins (see fmt_*)
 };
 
 // The reference selects the element type with the library-name suffix and
@@ -166,6 +166,15 @@ static const vpq_function_s g_functions[] = {
     {"affine_dequant_bf16", "affine_dequant_w4g64", 2},
     {"affine_dequant_bf16", "affine_quant_w4_g64", 3},
     {"affine_dequant", "affine_quant_w4_g64", 4},
+    // the format twins: kind = 10 + 16 * (quant ? 1 + bf16 source : 0) + 4 * (bits == 8) + (group == 32)
+    {"affine_dequant_bf16", "affine_dequant_w8g64", 10 + 4},
+    {"affine_dequant_bf16", "affine_dequant_w8g32", 10 + 4 + 1},
+    {"affine_dequant_bf16", "affine_quant_w8_g64", 10 + 32 + 4},
+    {"affine_dequant_bf16", "affine_quant_w8_g32", 10 + 32 + 4 + 1},
+    {"affine_dequant_bf16", "affine_quant_w4_g32", 10 + 32 + 1},
+    {"affine_dequant", "affine_quant_w8_g64", 10 + 16 + 4},
+    {"affine_dequant", "affine_quant_w8_g32", 10 + 16 + 4 + 1},
+    {"affine_dequant", "affine_quant_w4_g32", 10 + 16 + 1},
 };
 
 extern "C" const vpq_function* vpq_function_lookup(const char* library, const char* entry) {
@@ -222,7 +231,16 @@ extern "C" int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* a, 
     case 9:
       return vpq_affine_qmv_batch_w4g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
                                              const_cast<void*>(b[4]), a->K, a->N, a->M < 1 ? 1 : a->M, stream);
-    default:
-      return fail(VPQ_ERR_NOT_FOUND, "dispatch: corrupt function handle");
+    default: {
+      if (fn->kind < 10 || fn->kind >= 10 + 48) { return fail(VPQ_ERR_NOT_FOUND, "dispatch: corrupt function handle"); }
+      const int code = fn->kind - 10, quant = code >> 4, bits = (code & 4) ? 8 : 4, group = (code & 1) ? 32 : 64;
+      if (quant) {
+        return vpq_affine_quant(b[0], quant == 2 ? 1 : 0, static_cast<uint32_t*>(const_cast<void*>(b[1])),
+                                const_cast<void*>(b[2]), const_cast<void*>(b[3]), a->K, a->N, bits, group, a->clip,
+                                stream);
+      }
+      return vpq_affine_dequant_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], const_cast<void*>(b[3]), a->K,
+                                     a->N, bits, group, stream);
+    }
   }
 }

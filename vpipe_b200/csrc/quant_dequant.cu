@@ -1,29 +1,33 @@
 // quant_dequant.cu -- forward quantizer, dequantizer and the load-time dtype
-// conversions of the 4-bit affine group-64 format. All bit-exact with the
+// conversions of the affine group-quantized formats: 4-bit group-64 (the hot
+// path's format) and its twins w8g64, w8g32, w4g32. All bit-exact with the
 // reference shaders; all pure HBM streams.
 #include "vpq_common.cuh"
 
 namespace vpq {
 
 // ---------------------------------------------------------------- quantize
-// One thread owns 8 consecutive values (one packed word); the 8 threads of a
-// group reduce min / max with shuffles. Replaces affine_quant_impl<4,64>
-// (gpu-kernels/metal/quant/affine_dequant.metal:243-301), which uses one
-// thread per group with strided reads.
+// One thread owns 8 consecutive values (one packed word at 4 bits, two at 8);
+// the GROUP / 8 threads of a group reduce min / max with shuffles. Replaces
+// affine_quant_impl<BITS,GROUP> (gpu-kernels/metal/quant/affine_dequant.metal:243-301,
+// instantiated as affine_quant_w4_g64, _w8_g64, _w8_g32, _w4_g32), which uses
+// one thread per group with strided reads.
 //
 // The reference scans the group in index order with min(a,b) = (b<a)?b:a, so
 // among equal values (+0 / -0) the FIRST one is kept; that decides the sign
 // bit of a zero bias. The butterfly keeps that rule: on a tie the lower lane
 // (lower indices) wins.
-template <bool SRC_BF16>
+template <bool SRC_BF16, int BITS, int GROUP>
 __global__ void __launch_bounds__(256)
-affine_quant_w4_g64_kernel(const uint16_t* __restrict__ x, uint32_t* __restrict__ w,
-                           __half* __restrict__ s, __half* __restrict__ b,
-                           int64_t total_words, float clip) {
+affine_quant_kernel(const uint16_t* __restrict__ x, uint32_t* __restrict__ w,
+                    __half* __restrict__ s, __half* __restrict__ b,
+                    int64_t total_words, float clip) {  // total_words: octets of values (N * K / 8)
+  constexpr int TPG = GROUP / 8;             // threads per group
+  constexpr float QMAX = (float)((1 << BITS) - 1);
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const unsigned lane = threadIdx.x & 31u;
   // The loop bound is warp-uniform (all 32 lanes take part in every shuffle);
-  // total_words is a multiple of 8, so the 8 lanes of a group are valid together.
+  // total_words is a multiple of TPG, so the lanes of a group are valid together.
   for (int64_t word = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; word - lane < total_words;
        word += stride) {
     const bool valid = word < total_words;
@@ -47,7 +51,7 @@ affine_quant_w4_g64_kernel(const uint16_t* __restrict__ x, uint32_t* __restrict_
       mx = (mx < v[i]) ? v[i] : mx;
     }
 #pragma unroll
-    for (int d = 1; d < 8; d <<= 1) {
+    for (int d = 1; d < TPG; d <<= 1) {
       const float omn = __shfl_xor_sync(0xffffffffu, mn, d);
       const float omx = __shfl_xor_sync(0xffffffffu, mx, d);
       if (lane & d) {  // partner holds lower indices: it wins ties
@@ -63,46 +67,69 @@ affine_quant_w4_g64_kernel(const uint16_t* __restrict__ x, uint32_t* __restrict_
       mn = __fadd_rn(mid, __fmul_rn(__fsub_rn(mn, mid), clip));
       mx = __fadd_rn(mid, __fmul_rn(__fsub_rn(mx, mid), clip));
     }
-    const float scale = __fdiv_rn(__fsub_rn(mx, mn), 15.0f);
+    const float scale = __fdiv_rn(__fsub_rn(mx, mn), QMAX);
     const float inv = (scale > 0.0f) ? __fdiv_rn(1.0f, scale) : 0.0f;
-    uint32_t packed = 0;
+    uint32_t packed[2] = {0, 0};
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       int q = (int)roundf(__fmul_rn(__fsub_rn(v[i], mn), inv));  // half away from zero
-      q = min(max(q, 0), 15);
-      packed |= (uint32_t)q << (4 * i);
+      q = min(max(q, 0), (int)QMAX);
+      if (BITS == 4) {
+        packed[0] |= (uint32_t)q << (4 * i);
+      } else {
+        packed[i >> 2] |= (uint32_t)q << (8 * (i & 3));
+      }
     }
     if (!valid) { continue; }
-    w[word] = packed;
-    if ((word & 7) == 0) {
-      s[word >> 3] = __float2half_rn(scale);
-      b[word >> 3] = __float2half_rn(mn);
+    if (BITS == 4) {
+      w[word] = packed[0];
+    } else {
+      *reinterpret_cast<uint2*>(w + 2 * word) = make_uint2(packed[0], packed[1]);
+    }
+    if ((word % TPG) == 0) {
+      s[word / TPG] = __float2half_rn(scale);
+      b[word / TPG] = __float2half_rn(mn);
     }
   }
 }
 
 // -------------------------------------------------------------- dequantize
-// One thread expands one packed word into 8 bf16 (one 16-byte store), so a
-// warp reads 128 B and writes 512 B, both fully coalesced.
-// Replaces affine_dequant_w4g64 (gpu-kernels/metal/quant/affine_dequant.metal:25-58).
+// One thread expands 8 values (one packed word at 4 bits, two at 8) into 8 bf16 (one 16-byte
+// store): fully coalesced reads and writes. Replaces affine_dequant_w4g64, _w8g64 and _w8g32
+// (gpu-kernels/metal/quant/affine_dequant.metal:25-58, 69-98, 107-135); the w4g32 form has no
+// kernel in the reference (its group-32 models dequantise inside the GEMV) but follows from the
+// same expression.
+template <int BITS, int GROUP>
 __global__ void __launch_bounds__(256)
-affine_dequant_w4g64_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ scales,
-                            const uint16_t* __restrict__ biases, uint4* __restrict__ ydeq,
-                            int64_t total_words) {
+affine_dequant_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ scales,
+                      const uint16_t* __restrict__ biases, uint4* __restrict__ ydeq,
+                      int64_t total_octets) {
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t word = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; word < total_words;
-       word += stride) {
-    const uint32_t packed = __ldg(w + word);
-    const float s = bf16_bits_to_f32(__ldg(scales + (word >> 3)));
-    const float b = bf16_bits_to_f32(__ldg(biases + (word >> 3)));
+  for (int64_t oct = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; oct < total_octets; oct += stride) {
+    const int64_t g = oct / (GROUP / 8);
+    const float s = bf16_bits_to_f32(__ldg(scales + g));
+    const float b = bf16_bits_to_f32(__ldg(biases + g));
+    uint32_t q[8];
+    if (BITS == 4) {
+      const uint32_t packed = __ldg(w + oct);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { q[i] = (packed >> (4 * i)) & 0xfu; }
+    } else {
+      const uint2 packed = __ldg(reinterpret_cast<const uint2*>(w) + oct);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        q[i] = (packed.x >> (8 * i)) & 0xffu;
+        q[4 + i] = (packed.y >> (8 * i)) & 0xffu;
+      }
+    }
     uint32_t o[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint32_t lo = f32_to_bf16_bits(dequant_f32(s, (packed >> (8 * i)) & 0xfu, b));
-      const uint32_t hi = f32_to_bf16_bits(dequant_f32(s, (packed >> (8 * i + 4)) & 0xfu, b));
+      const uint32_t lo = f32_to_bf16_bits(dequant_f32(s, q[2 * i], b));
+      const uint32_t hi = f32_to_bf16_bits(dequant_f32(s, q[2 * i + 1], b));
       o[i] = lo | (hi << 16);
     }
-    ydeq[word] = make_uint4(o[0], o[1], o[2], o[3]);
+    ydeq[oct] = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
 
@@ -133,57 +160,103 @@ static int stream_grid(int64_t items, int threads) {
 
 using namespace vpq;
 
+namespace {
+template <int BITS, int GROUP>
+void launch_quant(bool bf16, const void* w_elt, uint32_t* codes, void* s16, void* b16, int64_t octets, float clip,
+                  cudaStream_t st) {
+  const int grid = stream_grid(octets, 256);
+  if (bf16) {
+    affine_quant_kernel<true, BITS, GROUP><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(w_elt), codes,
+                                                                 static_cast<__half*>(s16),
+                                                                 static_cast<__half*>(b16), octets, clip);
+  } else {
+    affine_quant_kernel<false, BITS, GROUP><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(w_elt), codes,
+                                                                  static_cast<__half*>(s16),
+                                                                  static_cast<__half*>(b16), octets, clip);
+  }
+}
+bool known_format(int bits, int group) { return (bits == 4 || bits == 8) && (group == 64 || group == 32); }
+}  // namespace
+
+extern "C" int vpq_affine_quant(const void* w_elt, int src_is_bf16, uint32_t* codes, void* scales_f16,
+                                void* biases_f16, int64_t K, int64_t N, int bits, int group, float clip,
+                                void* stream) {
+  clear_error();
+  if (!w_elt || !codes || !scales_f16 || !biases_f16) {
+    return fail(VPQ_ERR_INVALID_ARG, "affine_quant: null pointer");
+  }
+  if (!known_format(bits, group)) {  // affine-quantizer.cc:55-56
+    return fail(VPQ_ERR_UNSUPPORTED, "affine_quant: bits must be 4 or 8 and group 64 or 32 (bits=%d group=%d)", bits,
+                group);
+  }
+  if (N <= 0 || K <= 0 || (K % group) != 0) {  // affine-quantizer.cc:57
+    return fail(VPQ_ERR_INVALID_ARG, "affine_quant: need N>0, K>0, K%%%d==0 (K=%lld N=%lld)", group, (long long)K,
+                (long long)N);
+  }
+  if (!aligned16(w_elt) || !aligned16(codes)) {
+    return fail(VPQ_ERR_ALIGNMENT, "affine_quant: w_elt and codes must be 16-byte aligned");
+  }
+  if (int rc = require_sm100()) { return rc; }
+  const int64_t octets = N * (K / 8);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool bf = src_is_bf16 != 0;
+  if (bits == 4 && group == 64) {
+    launch_quant<4, 64>(bf, w_elt, codes, scales_f16, biases_f16, octets, clip, st);
+  } else if (bits == 8 && group == 64) {
+    launch_quant<8, 64>(bf, w_elt, codes, scales_f16, biases_f16, octets, clip, st);
+  } else if (bits == 8 && group == 32) {
+    launch_quant<8, 32>(bf, w_elt, codes, scales_f16, biases_f16, octets, clip, st);
+  } else {
+    launch_quant<4, 32>(bf, w_elt, codes, scales_f16, biases_f16, octets, clip, st);
+  }
+  VPQ_LAUNCH_OK("affine_quant");
+  return VPQ_OK;
+}
+
 extern "C" int vpq_affine_quant_w4_g64(const void* w_elt, int src_is_bf16, uint32_t* codes,
                                        void* scales_f16, void* biases_f16, int64_t K, int64_t N,
                                        float clip, void* stream) {
+  return vpq_affine_quant(w_elt, src_is_bf16, codes, scales_f16, biases_f16, K, N, 4, 64, clip, stream);
+}
+
+extern "C" int vpq_affine_dequant_bf16(const uint32_t* w, const void* scales, const void* biases, void* ydeq,
+                                       int64_t K, int64_t N, int bits, int group, void* stream) {
   clear_error();
-  if (!w_elt || !codes || !scales_f16 || !biases_f16) {
-    return fail(VPQ_ERR_INVALID_ARG, "affine_quant_w4_g64: null pointer");
+  if (!w || !scales || !biases || !ydeq) { return fail(VPQ_ERR_INVALID_ARG, "affine_dequant: null pointer"); }
+  if (!known_format(bits, group)) {
+    return fail(VPQ_ERR_UNSUPPORTED, "affine_dequant: bits must be 4 or 8 and group 64 or 32 (bits=%d group=%d)", bits,
+                group);
   }
-  if (N <= 0 || K <= 0 || (K % 64) != 0) {  // affine-quantizer.cc:57
-    return fail(VPQ_ERR_INVALID_ARG, "affine_quant_w4_g64: need N>0, K>0, K%%64==0 (K=%lld N=%lld)",
-                (long long)K, (long long)N);
+  if (N <= 0 || K <= 0 || (K % group) != 0) {
+    return fail(VPQ_ERR_INVALID_ARG, "affine_dequant: need N>0, K>0, K%%%d==0", group);
   }
-  if (!aligned16(w_elt) || !aligned16(codes)) {
-    return fail(VPQ_ERR_ALIGNMENT, "affine_quant_w4_g64: w_elt and codes must be 16-byte aligned");
+  if (!aligned16(ydeq) || !aligned16(w)) {
+    return fail(VPQ_ERR_ALIGNMENT, "affine_dequant: w and ydeq must be 16-byte aligned");
   }
   if (int rc = require_sm100()) { return rc; }
-  const int64_t words = N * (K / 8);
-  const int grid = stream_grid(words, 256);
+  const int64_t octets = N * (K / 8);
+  const int grid = stream_grid(octets, 256);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (src_is_bf16) {
-    affine_quant_w4_g64_kernel<true><<<grid, 256, 0, st>>>(
-        static_cast<const uint16_t*>(w_elt), codes, static_cast<__half*>(scales_f16),
-        static_cast<__half*>(biases_f16), words, clip);
+  const uint16_t* sp = static_cast<const uint16_t*>(scales);
+  const uint16_t* bp = static_cast<const uint16_t*>(biases);
+  uint4* out = static_cast<uint4*>(ydeq);
+  if (bits == 4 && group == 64) {
+    affine_dequant_kernel<4, 64><<<grid, 256, 0, st>>>(w, sp, bp, out, octets);
+  } else if (bits == 8 && group == 64) {
+    affine_dequant_kernel<8, 64><<<grid, 256, 0, st>>>(w, sp, bp, out, octets);
+  } else if (bits == 8 && group == 32) {
+    affine_dequant_kernel<8, 32><<<grid, 256, 0, st>>>(w, sp, bp, out, octets);
   } else {
-    affine_quant_w4_g64_kernel<false><<<grid, 256, 0, st>>>(
-        static_cast<const uint16_t*>(w_elt), codes, static_cast<__half*>(scales_f16),
-        static_cast<__half*>(biases_f16), words, clip);
+    affine_dequant_kernel<4, 32><<<grid, 256, 0, st>>>(w, sp, bp, out, octets);
   }
-  VPQ_LAUNCH_OK("affine_quant_w4_g64");
+  VPQ_LAUNCH_OK("affine_dequant");
   return VPQ_OK;
 }
 
 extern "C" int vpq_affine_dequant_w4g64_bf16(const uint32_t* w, const void* scales,
                                              const void* biases, void* ydeq, int64_t K, int64_t N,
                                              void* stream) {
-  clear_error();
-  if (!w || !scales || !biases || !ydeq) {
-    return fail(VPQ_ERR_INVALID_ARG, "affine_dequant_w4g64: null pointer");
-  }
-  if (N <= 0 || K <= 0 || (K % 64) != 0) {
-    return fail(VPQ_ERR_INVALID_ARG, "affine_dequant_w4g64: need N>0, K>0, K%%64==0");
-  }
-  if (!aligned16(ydeq) || !aligned16(w)) {
-    return fail(VPQ_ERR_ALIGNMENT, "affine_dequant_w4g64: w and ydeq must be 16-byte aligned");
-  }
-  if (int rc = require_sm100()) { return rc; }
-  const int64_t words = N * (K / 8);
-  affine_dequant_w4g64_kernel<<<stream_grid(words, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      w, static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases),
-      static_cast<uint4*>(ydeq), words);
-  VPQ_LAUNCH_OK("affine_dequant_w4g64");
-  return VPQ_OK;
+  return vpq_affine_dequant_bf16(w, scales, biases, ydeq, K, N, 4, 64, stream);
 }
 
 extern "C" int vpq_scales_f16_to_bf16(const void* src_f16, void* dst_bf16, int64_t n, void* stream) {

@@ -26,19 +26,35 @@ def _stream(stream=None) -> int:
     return s.cuda_stream
 
 
-def quantize(w: torch.Tensor, clip: float = 1.0, stream=None):
-    """Dense [N,K] f16/bf16 -> (codes int32 [N,K/8], scales f16, biases f16)."""
+def quantize(w: torch.Tensor, clip: float = 1.0, stream=None, bits: int = 4, group: int = 64):
+    """Dense [N,K] f16/bf16 -> (codes int32 [N,K*bits/32], scales f16, biases f16 [N,K/group])."""
     if w.dtype not in (torch.float16, torch.bfloat16):
         raise ValueError("quantize: w must be float16 or bfloat16")
     N, K = w.shape
     dev = w.device
     with torch.cuda.device(dev):
-        codes = torch.empty((N, max(K // 8, 1)), dtype=torch.int32, device=dev)
-        s = torch.empty((N, max(K // 64, 1)), dtype=torch.float16, device=dev)
+        codes = torch.empty((N, max(K * bits // 32, 1)), dtype=torch.int32, device=dev)
+        s = torch.empty((N, max(K // group, 1)), dtype=torch.float16, device=dev)
         b = torch.empty_like(s)
-        check(lib().vpq_affine_quant_w4_g64(_ptr(w), int(w.dtype == torch.bfloat16), _ptr(codes),
-                                            _ptr(s), _ptr(b), K, N, clip, _stream(stream)))
+        if (bits, group) == (4, 64):
+            check(lib().vpq_affine_quant_w4_g64(_ptr(w), int(w.dtype == torch.bfloat16), _ptr(codes),
+                                                _ptr(s), _ptr(b), K, N, clip, _stream(stream)))
+        else:
+            check(lib().vpq_affine_quant(_ptr(w), int(w.dtype == torch.bfloat16), _ptr(codes), _ptr(s), _ptr(b),
+                                         K, N, bits, group, clip, _stream(stream)))
     return codes, s, b
+
+
+def dequantize_any(codes, scales, biases, bits: int, group: int, out=None, stream=None) -> torch.Tensor:
+    """Any of the format twins (bits 4 | 8, group 64 | 32) -> dense bf16 [N, K]."""
+    N, Kw = codes.shape
+    K = Kw * 32 // bits
+    if out is None:
+        out = torch.empty((N, K), dtype=torch.bfloat16, device=codes.device)
+    with torch.cuda.device(codes.device):
+        check(lib().vpq_affine_dequant_bf16(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(out), K, N, bits, group,
+                                            _stream(stream)))
+    return out
 
 
 def narrow_f32_bf16(w: torch.Tensor, stream=None) -> torch.Tensor:
