@@ -31,6 +31,7 @@ import statistics
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -62,17 +63,53 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
+    """SM clock and throttle reasons sampled while the timed region runs: NVML polled every ~2 ms
+    from a thread (reading only), nvidia-smi every 100 ms if NVML is not importable."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+                   0x4: "sw_power_cap"}
 
     def __init__(self, gpu_index: int):
         self.idx = gpu_index
         self.proc = None
         self.path = None
+        self.thread = None
+        self.rows = []
+        self.max_mhz = None
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:  # the CUDA index is relative to CUDA_VISIBLE_DEVICES: find the same GPU by its UUID
+            import torch
+            uuid = str(torch.cuda.get_device_properties(self.idx).uuid)
+            uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+            return pynvml, pynvml.nvmlDeviceGetHandleByUUID(uuid)
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.idx)
 
     def start(self):
+        try:
+            nv, h = self._nvml_handle()
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            self.halt = threading.Event()
+
+            def loop():
+                while not self.halt.is_set():
+                    try:
+                        self.rows.append((float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)),
+                                          int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))))
+                    except Exception:
+                        pass
+                    time.sleep(0.002)
+
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
@@ -85,6 +122,16 @@ class ClockSampler:
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.thread is not None:
+            self.halt.set()
+            self.thread.join(timeout=2)
+            if self.rows:
+                reasons = set()
+                for _, mask in self.rows:
+                    reasons.update(name for bit, name in self.REASON_BITS.items() if mask & bit)
+                out.update(sm_mhz=statistics.median(r[0] for r in self.rows), sm_max_mhz=self.max_mhz,
+                           samples=len(self.rows), reasons=sorted(reasons), source="nvml")
+            return out
         if self.proc is None:
             return out
         time.sleep(0.15)
@@ -113,7 +160,7 @@ class ClockSampler:
             pass
         if sm:
             out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), samples=len(sm),
-                       reasons=sorted(reasons))
+                       reasons=sorted(reasons), source="nvidia-smi")
         return out
 
 
