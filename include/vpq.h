@@ -86,8 +86,8 @@ int vpq_scales_f16_to_bf16(const void* src_f16, void* dst_bf16, int64_t n, void*
  * with kernels affine_quant_w8_g64 / _w4_g64 / _w8_g32 / _w4_g32 and affine_dequant_w4g64 / _w8g64
  * / _w8g32, gpu-kernels/metal/quant/affine_dequant.metal:25-135,243-301; validated as
  * AffineQuantizer::quantize_linear does, generative-models/quantize/affine-quantizer.cc:55-57.
- * The GEMV / GEMM kernels of this library compute w4 g64 only: other formats are dequantised once
- * and multiplied densely, as the reference itself does for its codec weights
+ * Besides w4 g64 the library has a fused GEMV for w8 g64 (vpq_affine_qmv_w8g64_bf16); the other
+ * combinations are dequantised once and multiplied densely, as the reference itself does for its codec weights
  * (affine_dequant.metal:100-106). */
 int vpq_affine_quant(const void* w_elt, int src_is_bf16, uint32_t* codes, void* scales_f16, void* biases_f16,
                      int64_t K, int64_t N, int bits, int group, float clip, void* stream);
@@ -122,6 +122,13 @@ int vpq_affine_qmv_swiglu_w4g64_bf16(const uint32_t* w, const void* scales, cons
 int vpq_affine_qmv_qkv_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
                                   void* q_out, void* k_out, void* v_out, int64_t K, int64_t q_rows,
                                   int64_t k_rows, int64_t v_rows, int64_t M, void* stream);
+
+/* Decode GEMV over 8-bit group-64 weights (w u32 [N, K/4], one byte per value): the 8-bit linears
+ * of mixed-precision checkpoints. Exact integer tensor-core arithmetic as the 4-bit kernel, with
+ * no unpacking at all. K <= 16384. Replaces affine_qmv_w8g64 (slots as affine_qmv_w4g64),
+ * gpu-kernels/metal/quant/affine_qmv.metal:186-301,3027-3070. */
+int vpq_affine_qmv_w8g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                              void* y, int64_t K, int64_t N, int64_t M, void* stream);
 
 /* Small-batch decode GEMV: the M rows of x (M = 2..8: decode of several branches, MTP verify)
  * share ONE stream of the weights, up to 4 rows per pass (4 up to K = 5120, 2 up to K = 8192: the

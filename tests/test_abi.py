@@ -49,6 +49,7 @@ def test_function_table_uses_reference_names(vpq):
                            ("affine_qmv_bf16", "affine_qmv_w4g64_add"),
                            ("affine_qmv_bf16", "affine_qmv_swiglu_w4g64"),
                            ("affine_qmv_bf16", "affine_qmv_qkv_w4g64"),
+                           ("affine_qmv_bf16", "affine_qmv_w8g64"),
                            ("affine_qmv_bf16", "affine_qmv_batch_w4g64"),
                            ("affine_qmv_bf16", "affine_qmv_batch4_w4g64"),
                            ("affine_qmm_steel_bf16", "affine_qmm_steel_w4g64"),
@@ -103,6 +104,7 @@ def test_argument_validation_happens_before_any_device_work(vpq):
     assert L.vpq_affine_qmm_swiglu_w4g64_bf16(p16, p16, p16, p16, p16, 64, 9, 4, None) == INVALID
     assert L.vpq_affine_qmv_batch_w4g64_bf16(p16, p16, p16, p16, None, 64, 8, 4, None) == INVALID
     assert L.vpq_affine_qmv_batch_w4g64_bf16(p16, p16, p16, p16 + 2, p16, 64, 8, 4, None) == ALIGN
+    assert L.vpq_affine_qmv_w8g64_bf16(p16, p16, p16, p16, p16, 32768, 8, 1, None) == UNSUP
     # format twins: width and group are validated as AffineQuantizer::quantize_linear does
     assert L.vpq_affine_quant(p16, 1, p16, p16, p16, 64, 8, 3, 64, 1.0, None) == UNSUP
     assert L.vpq_affine_quant(p16, 1, p16, p16, p16, 48, 8, 8, 32, 1.0, None) == INVALID

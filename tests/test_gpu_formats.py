@@ -73,3 +73,47 @@ def test_twins_by_reference_names_and_dense_route(vpq, oracle_mod):
     # unknown width / group: refused, not guessed
     with pytest.raises(vpq.VpqError):
         ops.quantize(w, bits=2, group=64)
+
+
+def _w8_reference(oracle_mod, codes, s_bf16, b_bf16, x_bits, mode="fast"):
+    """fp32 dequantise-then-matmul oracle for w8 g64: deq = s * byte + b in f32 (affine_dequant.metal:88-92
+    without the final rounding), then the oracle's matmul."""
+    N, Kw = codes.shape
+    q = codes.view(np.uint8).reshape(N, Kw * 4).astype(np.float32)
+    s = np.repeat(synth.bf16_bits_to_f32(s_bf16), 64, axis=1)
+    b = np.repeat(synth.bf16_bits_to_f32(b_bf16), 64, axis=1)
+    return oracle_mod.matmul_f32(x_bits, (s * q + b).astype(np.float32), mode)
+
+
+@pytest.mark.parametrize("K,N,M", [(4096, 4096, 1), (12288, 512, 1), (1024, 1024, 2), (3840, 40, 1), (64, 8, 1),
+                                   (320, 33, 2), (1152, 8193, 1)])
+def test_qmv_w8g64_matches_fp32_oracle(vpq, oracle_mod, K, N, M):
+    wb = synth.f32_to_bf16_bits(synth.weight_f32(N, K, synth.seed_for("w8", K, N)))
+    codes, s16, b16 = oracle_mod.quant(wb, 8, 64)
+    s, b = oracle_mod.f16_to_bf16(s16), oracle_mod.f16_to_bf16(b16)
+    x = synth.activations_bf16(M, K, synth.seed_for("w8x", K, N))
+    y = vpq.ops.qmv_w8(to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16), to_dev(x, torch.bfloat16))
+    assert y.shape == (M, N)
+    assert vpq.ops.device_status() == 0
+    e = oracle_mod.err_metrics(y.float().cpu().numpy(), _w8_reference(oracle_mod, codes, s, b, x))
+    assert e["rel_l2"] < 1e-2 and e["max_rel_rms"] < 1e-2 and e["max_rel_1e2"] < 1e-2, e
+
+
+def test_qmv_w8g64_f32_accuracy_and_name(vpq, oracle_mod):
+    """Random bytes with large biases (cancellation): the result is the bf16 rounding of the f64
+    reference up to one ulp nearly everywhere; and the entry is reachable by the reference's name."""
+    N, K = 256, 2048
+    rng = np.random.default_rng(9)
+    codes = rng.integers(0, 2**32, (N, K // 4), dtype=np.uint32)
+    s = synth.f32_to_bf16_bits((rng.random((N, K // 64)) * 0.001 + 0.0003).astype(np.float32))
+    b = synth.f32_to_bf16_bits((rng.random((N, K // 64)) * 0.2 - 0.1).astype(np.float32))
+    x = synth.activations_bf16(1, K, 91)
+    d = (to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16), to_dev(x, torch.bfloat16))
+    y = vpq.ops.qmv_w8(*d)
+    ref = _w8_reference(oracle_mod, codes, s, b, x, "f64")
+    want = synth.f32_to_bf16_bits(ref.astype(np.float32))
+    ulps = np.abs(bits16(y).astype(np.int64) - want.astype(np.int64))
+    assert (ulps <= 1).mean() > 0.999
+    y2 = torch.empty_like(y)
+    vpq.ops.dispatch(vpq.ops.function("affine_qmv_bf16", "affine_qmv_w8g64"), list(d) + [y2], K=K, N=N)
+    assert torch.equal(y, y2)

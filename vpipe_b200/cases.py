@@ -3,6 +3,7 @@
     python -m vpipe_b200.cases qmv  K N [launches]     # single GEMVs on distinct weight copies
     python -m vpipe_b200.cases plan LAYERS             # the C2 decode set as one plan launch
     python -m vpipe_b200.cases qmv_batch K N M [launches]  # small-batch GEMV vs M serial GEMVs
+    python -m vpipe_b200.cases qmv_w8 K N [launches]   # 8-bit GEMV on distinct weight copies (graph replay)
     python -m vpipe_b200.cases qmm  M K N [reps]       # the GEMM
     python -m vpipe_b200.cases qmm_swiglu M K N [reps] # the GEMM with the fused SwiGLU store (N = 2 ffn)
 
@@ -53,6 +54,28 @@ def main(argv):
         t = _time(lambda: (lambda p: ops.qmv(*p[:4], out=p[4]))(next(it)), n)
         print(json.dumps({"case": "qmv", "K": K, "N": N, "us": t * 1e6,
                           "GBs": synth.qmv_bytes(K, N) / t / 1e9}))
+    elif kind == "qmv_w8":
+        K, N = int(argv[1]), int(argv[2])
+        n = int(argv[3]) if len(argv) > 3 else 8
+        x = torch.randn((1, K), device=dev).to(torch.bfloat16)
+        sets = []
+        for _ in range(n):
+            codes = torch.randint(-2**31, 2**31 - 1, (N, K // 4), dtype=torch.int32, device=dev)
+            s = (torch.rand((N, K // 64), device=dev) * 0.001 + 0.0003).to(torch.bfloat16)
+            b = (torch.rand((N, K // 64), device=dev) * 0.2 - 0.1).to(torch.bfloat16)
+            sets.append((codes, s, b, x, torch.empty((1, N), dtype=torch.bfloat16, device=dev)))
+        for p in sets:
+            ops.qmv_w8(*p[:4], out=p[4])
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for p in sets:
+                ops.qmv_w8(*p[:4], out=p[4])
+        g.replay()
+        torch.cuda.synchronize()
+        t = _time(g.replay, 3) / n
+        nbytes = N * K + 2 * N * (K // 64) * 2 + 2 * K + 2 * N
+        print(json.dumps({"case": "qmv_w8", "K": K, "N": N, "us": t * 1e6, "GBs": nbytes / t / 1e9}))
     elif kind == "qmv_batch":
         K, N, M = int(argv[1]), int(argv[2]), int(argv[3])
         n = int(argv[4]) if len(argv) > 4 else 8

@@ -619,6 +619,9 @@ extern "C" int vpq_device_status(void* stream, uint32_t* detail) {
   if (vq == 0) {
     if (int rc = qmvb_status_read(st, &vq)) { return rc; }  // the small-batch GEMV reports like the GEMV
   }
+  if (vq == 0) {
+    if (int rc = qmv8_status_read(st, &vq)) { return rc; }  // and the 8-bit one
+  }
   if (detail) { *detail = v ? v : (vq ? (vq | 0x10000u) : 0u); }
   uint32_t vn = 0;
   if (int rc = nsplit_status_read(st, &vn)) { return rc; }

@@ -1,0 +1,434 @@
+// qmv_w8.cu -- decode GEMV over 8-bit affine group-64 weights (M = 1 per launch).
+//
+// y[n] = sum_k x[k] * (s[n,k/64] * q[n,k] + b[n,k/64]),  q one byte per value, f32 accumulate.
+// Replaces affine_qmv_w8g64 (qmv_fast_impl<T,64,8,...>, gpu-kernels/metal/quant/affine_qmv.metal:186-301
+// instantiated at :3027-3070): the 8-bit linears of mixed-precision checkpoints.
+//
+// The skeleton of the 4-bit kernel (qmv.cu): a producer warp streams [16 rows x 128 bytes] TMA
+// boxes (here 128 k each) plus the span's scales and biases into a ring of stages (8 boxes =
+// 1024 k); eight consumer warps split K, warp w takes box w of every stage; exact integer
+// arithmetic on mma.sync.m16n8k32.u8.s8 with x as three signed base-256 digits. With one byte per
+// weight no unpacking is left: the bytes a lane loads ARE its A fragments. One MMA takes 16 k
+// of the k tile's first group (k columns 0..15) and 16 k of its second (16..31); accumulator
+// column (digit, parity) gets the digit's bytes in the half of B that belongs to its group and
+// zeros in the other, so a lane ends up with digit t's sums for both groups and both of its rows
+// and folds them with the groups' scales (lane 3 of a quad folds the bias term b * sum(x)).
+// x is staged per CTA as digit bytes in natural k order. Every barrier wait is bounded.
+#include "vpq_sm100.cuh"
+
+#include <cstring>
+
+namespace vpq {
+
+__device__ uint32_t g_qmv8_status;  // 0, or (site << 8) | role of the first bounded wait that gave up
+
+namespace {
+
+constexpr int kConsWarps = 8;
+constexpr int kConsThreads = kConsWarps * 32;
+constexpr int kThreads = kConsThreads + 32;  // + producer warp
+constexpr int kBoxBytes = 16 * 128;          // one TMA box: 16 rows x 128 bytes (128 k, two groups)
+constexpr int kBoxesPerStage = 8;            // a stage spans 1024 k
+constexpr int kStageW = kBoxesPerStage * kBoxBytes;
+constexpr int kStageSZ = 2 * 16 * 32;        // scales + biases of the span: 2 x [16 rows x 16 groups]
+constexpr int kStageBytes = kStageW + kStageSZ;
+constexpr int kMaxStages = 6;
+constexpr int kRedSlots = 8;
+constexpr int kXBytesPerKt = 3 * 128;        // staged x per 128-k tile: 3 digit planes of 128 bytes
+
+constexpr int kAccInit = 0x4B400000;         // bits of 12582912.0f: an s32 sum |v| < 2^22 added to it reads as a float
+constexpr float kAccInitF = 12582912.0f;
+
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 "
+      "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_u8s8_first(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1, int init) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 "
+      "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(init));
+}
+
+enum : uint32_t { kRoleProducer = 1, kRoleConsumer = 2 };
+
+struct alignas(64) Problem8 {
+  CUtensorMap mw, ms, mz;      // weights [N, K/4] u32; scales, biases [N, K/64] (valid if scales_tma)
+  const uint16_t* scales;
+  const uint16_t* biases;
+  const uint16_t* x;           // K bf16
+  __nv_bfloat16* y;            // N outputs
+  int K, N;
+  int row_tiles;
+  int scales_tma;
+};
+
+__global__ void __launch_bounds__(kThreads, 2)
+affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_kt) {
+  extern __shared__ unsigned char smem_dyn[];
+  const uint32_t raw = smem_u32(smem_dyn);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled boxes need 1024-byte alignment
+  unsigned char* base_ptr = smem_dyn + (base - raw);
+  const int K = P.K, N = P.N;
+
+  unsigned char* p0 = base_ptr + (size_t)stages * kStageBytes;
+  uint4* zero128 = reinterpret_cast<uint4*>(p0);                 // 128 bytes of zeros, 128-byte aligned
+  unsigned char* xq = p0 + 128;                                  // [cap_kt][3 digits][128 B]: digit bytes in k order
+  float* xg = reinterpret_cast<float*>(xq + (size_t)cap_kt * kXBytesPerKt);  // [2*cap_kt] sum of X per group
+  float* zero16 = xg + ((2 * cap_kt + 3) & ~3);                  // 16 bytes of zeros, 16-byte aligned (cap_kt may be odd)
+  float* red = zero16 + 4;                                       // [kRedSlots][kConsWarps][16]
+  uint32_t* red_cnt = reinterpret_cast<uint32_t*>(red + kRedSlots * kConsWarps * 16);
+  uint32_t* amax_buf = red_cnt + kRedSlots;                      // [kConsWarps]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(amax_buf + kConsWarps);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * kMaxStages);
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar_full = [&](int s) { return bar0 + 8u * s; };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (kMaxStages + s); };
+
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int NB = (K + 127) >> 7;                               // boxes (128-k tiles) per row
+  const int SPT = (NB + kBoxesPerStage - 1) / kBoxesPerStage;  // stages per row tile
+  const int gt_begin = (int)(((int64_t)P.row_tiles * blockIdx.x) / gridDim.x);
+  const int gt_end = (int)(((int64_t)P.row_tiles * (blockIdx.x + 1)) / gridDim.x);
+
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(bar_full(s), 1);
+      mbar_init(bar_empty(s), kConsWarps);
+    }
+    *abort_flag = 0;
+    for (int i = 0; i < kRedSlots; ++i) { red_cnt[i] = 0; }
+    fence_mbar_init();
+  }
+  if (threadIdx.x < 8) { zero128[threadIdx.x] = make_uint4(0, 0, 0, 0); }
+  if (threadIdx.x == 8) { *reinterpret_cast<uint4*>(zero16) = make_uint4(0, 0, 0, 0); }
+  __syncthreads();
+
+  if (warp == kConsWarps) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      const bool sz_tma = P.scales_tma != 0;
+      for (int tile = gt_begin; tile < gt_end && ok; ++tile) {
+        for (int st = 0; st < SPT; ++st, ++it) {
+          const int s = it % stages;
+          const uint32_t ph = (it / stages) & 1u;
+          if (!mbar_wait(bar_empty(s), ph ^ 1u, (1u << 8) | kRoleProducer, abort_flag, &g_qmv8_status)) {
+            ok = false;
+            break;
+          }
+          const int nb = min(kBoxesPerStage, NB - st * kBoxesPerStage);
+          const uint32_t dst = base + (uint32_t)s * kStageBytes;
+          mbar_expect_tx(bar_full(s), (uint32_t)nb * kBoxBytes + (sz_tma ? kStageSZ : 0));
+          for (int b = 0; b < nb; ++b) {
+            tma_load_2d(dst + b * kBoxBytes, &P.mw, bar_full(s), (st * kBoxesPerStage + b) * 32, tile * 16);
+          }
+          if (sz_tma) {
+            tma_load_2d(dst + kStageW, &P.ms, bar_full(s), st * 16, tile * 16);
+            tma_load_2d(dst + kStageW + kStageSZ / 2, &P.mz, bar_full(s), st * 16, tile * 16);
+          }
+        }
+      }
+      // Never leave with a copy still in flight: wait for the last load of every stage.
+      for (int s = 0; s < stages; ++s) {
+        if (it > (uint32_t)s) {
+          const uint32_t last = ((it - 1 - s) / stages) * stages + s;
+          mbar_wait(bar_full(s), (last / stages) & 1u, (2u << 8) | kRoleProducer, abort_flag, &g_qmv8_status);
+        }
+      }
+    }
+    return;
+  }
+
+  // ---------------------------------------------------------------- consumers
+  const int g = lane >> 2, t = lane & 3;
+  const int rho = (g >> 1) | ((g & 1) << 2);  // stage row of MMA row g (g+8 -> rho+8): bank-conflict-free
+
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // x may come from the previous kernel
+
+  // ---- staging of x as signed digit bytes (all consumer warps together): scaled by a power of two
+  // so that max |x| lands in [2^21, 2^22), rounded to an integer X (exact for every bf16 value
+  // within 2^-14 of the maximum), X = d0 + 256 d1 + 65536 d2 with digits in [-128, 127]; digit
+  // plane d of k tile kt holds the 128 bytes d(X[128 kt .. 128 kt + 127]) in order.
+  float x_unscale;
+  {
+    const int pieces = NB * 8;  // 16-value pieces of the padded x
+    uint32_t amax = 0;
+    for (int i = threadIdx.x; i * 16 < K; i += kConsThreads) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint4 in = *reinterpret_cast<const uint4*>(P.x + i * 16 + 8 * h);
+        const uint32_t v[4] = {in.x, in.y, in.z, in.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { amax = max(amax, max(v[j] & 0x7fffu, (v[j] >> 16) & 0x7fffu)); }
+      }
+    }
+    amax = __reduce_max_sync(0xffffffffu, amax);
+    if (lane == 0) { amax_buf[warp] = amax; }
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsThreads) : "memory");  // consumers only
+    amax = 0;
+#pragma unroll
+    for (int ww = 0; ww < kConsWarps; ++ww) { amax = max(amax, amax_buf[ww]); }
+    int e = (int)(amax >> 7);            // biased exponent of the largest magnitude
+    e = min(max(e, 22), 254);            // all-zero / denormal x: keep both factors normal
+    const float x_scale = __uint_as_float((uint32_t)(275 - e) << 23);  // 2^(148 - e)
+    x_unscale = __uint_as_float((uint32_t)(e - 21) << 23);             // its exact inverse
+    for (int i = threadIdx.x; i - lane < pieces; i += kConsThreads) {  // warp-uniform trip count: shuffles inside
+      const bool live = i < pieces;
+      uint4 in0 = make_uint4(0, 0, 0, 0), in1 = in0;
+      if (live && i * 16 < K) {
+        in0 = *reinterpret_cast<const uint4*>(P.x + i * 16);
+        in1 = *reinterpret_cast<const uint4*>(P.x + i * 16 + 8);
+      }
+      const uint32_t v[8] = {in0.x, in0.y, in0.z, in0.w, in1.x, in1.y, in1.z, in1.w};
+      // round(x * scale) on the FMA pipe: the low bits of fma(x, scale, 1.5 * 2^23) are
+      // 0x4B400000 + X; one add turns that into X + 0x808080 (bytes 0..2 = digits + 128).
+      uint32_t z[16];
+      uint32_t sum = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t lo = __float_as_uint(__fmaf_rn(__uint_as_float(v[j] << 16), x_scale, kAccInitF));
+        const uint32_t hi = __float_as_uint(__fmaf_rn(__uint_as_float(v[j] & 0xffff0000u), x_scale, kAccInitF));
+        sum += lo + hi;
+        z[2 * j] = lo + (0x808080u - (uint32_t)kAccInit);
+        z[2 * j + 1] = hi + (0x808080u - (uint32_t)kAccInit);
+      }
+      sum -= 16u * (uint32_t)kAccInit;  // = sum of the 16 X, modulo 2^32
+      uint32_t plane[3][4];             // digit d of values 4 q .. 4 q + 3 -> plane[d][q]
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t za = z[4 * q], zb = z[4 * q + 1], zc = z[4 * q + 2], zd = z[4 * q + 3];
+        const uint32_t t0 = __byte_perm(za, zb, 0x5140), t1 = __byte_perm(zc, zd, 0x5140);
+        const uint32_t t2 = __byte_perm(za, zb, 0x0062), t3 = __byte_perm(zc, zd, 0x0062);
+        plane[0][q] = __byte_perm(t0, t1, 0x5410) ^ 0x80808080u;
+        plane[1][q] = __byte_perm(t0, t1, 0x7632) ^ 0x80808080u;
+        plane[2][q] = __byte_perm(t2, t3, 0x5410) ^ 0x80808080u;
+      }
+      if (live) {
+        unsigned char* dst = xq + (size_t)(i >> 3) * kXBytesPerKt + (i & 7) * 16;
+#pragma unroll
+        for (int d = 0; d < 3; ++d) {
+          *reinterpret_cast<uint4*>(dst + d * 128) = make_uint4(plane[d][0], plane[d][1], plane[d][2], plane[d][3]);
+        }
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      if (live && (i & 3) == 0) { xg[i >> 2] = (float)(int)sum; }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsThreads) : "memory");
+  }
+
+  // Accumulator column c (fed by the lanes with g == c) = (digit c >> 1, group parity c & 1).
+  // An MMA's first 16 k columns come from the k tile's first group, the last 16 from its second:
+  // B register 0 of a lane carries its digit's bytes if the column's parity is 0, register 1 if
+  // it is 1; the other register reads zeros (from a zero line, at the chunks the real reads of
+  // the same quarter warp do not use).
+  const int digit = g >> 1, parity = g & 1;
+  const bool has_digit = digit < 3;
+  const unsigned char* zline = reinterpret_cast<const unsigned char*>(zero128);
+  const unsigned char* real_ptr = xq + digit * 128 + parity * 64 + t * 16;
+  const unsigned char* b0_ptr = (has_digit && parity == 0) ? real_ptr : zline + (4 + t) * 16;
+  const unsigned char* b1_ptr = (has_digit && parity == 1) ? real_ptr : zline + t * 16;
+  const int b0_kt = (has_digit && parity == 0) ? kXBytesPerKt : 0;
+  const int b1_kt = (has_digit && parity == 1) ? kXBytesPerKt : 0;
+  const bool bias_lane = t == 3;  // folds b * sum(x) where the others fold s * (digit sum)
+  const float* xs_base = bias_lane ? xg : zero16;
+  const int xs_kt = bias_lane ? 2 : 0;
+  const float digit_weight = t == 1 ? 256.0f : t == 2 ? 65536.0f : 1.0f;
+
+  const uint32_t off_lo = (uint32_t)rho * 128u + (uint32_t)(((0 + t) ^ rho) << 4);  // k 16 t .. of the first group
+  const uint32_t off_hi = (uint32_t)rho * 128u + (uint32_t)(((4 + t) ^ rho) << 4);  // k 64 + 16 t .. of the second
+  // 4 bytes = the 2 groups of this warp's box, row rho, in the stage's scales or biases
+  const uint32_t sz_off = (uint32_t)kStageW + (bias_lane ? (uint32_t)kStageSZ / 2 : 0u) + (uint32_t)rho * 32u +
+                          (uint32_t)warp * 4u;
+  const bool sz_tma = P.scales_tma != 0;
+  const int G = K >> 6;
+
+  uint32_t tile_seq = 0, ph = 0;
+  int s = 0;
+  bool ok = true;
+  for (int tile = gt_begin; tile < gt_end && ok; ++tile, ++tile_seq) {
+    float res_a = 0.0f, res_b = 0.0f;  // W rows rho and rho + 8: this lane's digit (or bias) share
+    for (int st = 0; st < SPT; ++st) {
+      if (!warp_wait(bar_full(s), ph, (1u << 8) | kRoleConsumer, abort_flag, &g_qmv8_status)) {
+        ok = false;
+        break;
+      }
+      const unsigned char* sb = base_ptr + (size_t)s * kStageBytes;
+      const int kt = st * kBoxesPerStage + warp;  // this warp's box = k tile kt
+      if (kt < NB) {
+        const unsigned char* box = sb + warp * kBoxBytes;
+        const uint4 ra_lo = *reinterpret_cast<const uint4*>(box + off_lo);
+        const uint4 ra_hi = *reinterpret_cast<const uint4*>(box + off_hi);
+        const uint4 rb_lo = *reinterpret_cast<const uint4*>(box + off_lo + 1024);
+        const uint4 rb_hi = *reinterpret_cast<const uint4*>(box + off_hi + 1024);
+        const uint4 x0 = *reinterpret_cast<const uint4*>(b0_ptr + (size_t)kt * b0_kt);
+        const uint4 x1 = *reinterpret_cast<const uint4*>(b1_ptr + (size_t)kt * b1_kt);
+        uint32_t sa, sb2;  // the two groups' scales (or biases) of rows rho, rho + 8
+        if (sz_tma) {
+          sa = *reinterpret_cast<const uint32_t*>(sb + sz_off);
+          sb2 = *reinterpret_cast<const uint32_t*>(sb + sz_off + 256);
+        } else {
+          // clamped onto valid data: a clamped group meets x == 0, a clamped row is never stored
+          const uint16_t* src = bias_lane ? P.biases : P.scales;
+          const int64_t r_a = min(tile * 16 + rho, N - 1), r_b = min(tile * 16 + rho + 8, N - 1);
+          const int g0 = min(2 * kt, G - 1), g1 = min(2 * kt + 1, G - 1);
+          sa = ldg_nc_u16(src + r_a * G + g0) | (ldg_nc_u16(src + r_a * G + g1) << 16);
+          sb2 = ldg_nc_u16(src + r_b * G + g0) | (ldg_nc_u16(src + r_b * G + g1) << 16);
+        }
+        const float2 xs = *reinterpret_cast<const float2*>(xs_base + kt * xs_kt);
+        int ca[4], cb[4];  // two independent chains
+        mma_u8s8_first(ca, ra_lo.x, rb_lo.x, ra_hi.x, rb_hi.x, x0.x, x1.x, kAccInit);
+        mma_u8s8_first(cb, ra_lo.y, rb_lo.y, ra_hi.y, rb_hi.y, x0.y, x1.y, kAccInit);
+        mma_u8s8(ca, ra_lo.z, rb_lo.z, ra_hi.z, rb_hi.z, x0.z, x1.z);
+        mma_u8s8(cb, ra_lo.w, rb_lo.w, ra_hi.w, rb_hi.w, x0.w, x1.w);
+        // c[0] = (row rho, first group) c[1] = (rho, second) c[2] = (rho + 8, first) c[3] = (rho + 8, second);
+        // value = chain a + chain b without the two initial values (+ sum of x in a bias lane,
+        // whose accumulators hold the bare initial value)
+        const float k0 = kAccInitF - xs.x, k1 = kAccInitF - xs.y;
+        auto val = [](int a, int b, float k) { return (__int_as_float(a) - kAccInitF) + (__int_as_float(b) - k); };
+        res_a = __fmaf_rn(__uint_as_float(sa << 16), val(ca[0], cb[0], k0), res_a);
+        res_a = __fmaf_rn(__uint_as_float(sa & 0xffff0000u), val(ca[1], cb[1], k1), res_a);
+        res_b = __fmaf_rn(__uint_as_float(sb2 << 16), val(ca[2], cb[2], k0), res_b);
+        res_b = __fmaf_rn(__uint_as_float(sb2 & 0xffff0000u), val(ca[3], cb[3], k1), res_b);
+      }
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(bar_empty(s)); }
+      if (++s == stages) {
+        s = 0;
+        ph ^= 1u;
+      }
+    }
+    if (!ok) { break; }
+    // quad: digits + bias -> even lanes end with row rho, odd lanes with row rho + 8; then the 8
+    // warps' K slices: the warp that posts last adds them in warp order and stores.
+    res_a *= digit_weight;
+    res_b *= digit_weight;
+    float keep = (t & 1) ? res_b : res_a;
+    keep += __shfl_xor_sync(0xffffffffu, (t & 1) ? res_a : res_b, 1);
+    keep += __shfl_xor_sync(0xffffffffu, keep, 2);
+    const int slot = tile_seq % kRedSlots;
+    if (t < 2) { red[(slot * kConsWarps + warp) * 16 + rho + 8 * t] = keep; }
+    __syncwarp();
+    uint32_t last = 0;
+    if (lane == 0) {
+      __threadfence_block();
+      last = atomicAdd(&red_cnt[slot], 1u) == (uint32_t)(kConsWarps - 1);
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last) {
+      __threadfence_block();
+      if (lane < 16) {
+        float v = 0.0f;
+#pragma unroll
+        for (int ww = 0; ww < kConsWarps; ++ww) {
+          v += *reinterpret_cast<volatile float*>(&red[(slot * kConsWarps + ww) * 16 + lane]);
+        }
+        const int row = (tile << 4) + lane;
+        if (row < N) { P.y[row] = __float2bfloat16_rn(v * x_unscale); }
+      }
+      __syncwarp();
+      if (lane == 0) { red_cnt[slot] = 0; }
+    }
+  }
+}
+
+size_t fixed_smem(int cap_kt) {
+  return 1024 /*alignment slack*/ + 128 + (size_t)cap_kt * kXBytesPerKt + (size_t)((2 * cap_kt + 3) & ~3) * 4 + 16 +
+         (size_t)kRedSlots * kConsWarps * 16 * 4 + kRedSlots * 4 + kConsWarps * 4 + 2 * kMaxStages * 8 + 16;
+}
+
+}  // namespace
+
+int qmv8_status_read(cudaStream_t st, uint32_t* out) {
+  uint32_t v = 0;
+  VPQ_CUDA_OK(cudaMemcpyFromSymbolAsync(&v, g_qmv8_status, sizeof(v), 0, cudaMemcpyDeviceToHost, st));
+  VPQ_CUDA_OK(cudaStreamSynchronize(st));
+  if (v != 0) {
+    const uint32_t zero = 0;
+    VPQ_CUDA_OK(cudaMemcpyToSymbolAsync(g_qmv8_status, &zero, sizeof(zero), 0, cudaMemcpyHostToDevice, st));
+    VPQ_CUDA_OK(cudaStreamSynchronize(st));
+  }
+  *out = v;
+  return VPQ_OK;
+}
+}  // namespace vpq
+
+using namespace vpq;
+
+extern "C" int vpq_affine_qmv_w8g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                                         void* y, int64_t K, int64_t N, int64_t M, void* stream) {
+  clear_error();
+  if (!w || !scales || !biases || !x || !y) { return fail(VPQ_ERR_INVALID_ARG, "affine_qmv_w8g64: null pointer"); }
+  if (K <= 0 || N <= 0 || M <= 0 || (K % 64) != 0) {
+    return fail(VPQ_ERR_INVALID_ARG, "affine_qmv_w8g64: need K>0, N>0, M>0, K%%64==0 (K=%lld N=%lld M=%lld)",
+                (long long)K, (long long)N, (long long)M);
+  }
+  if (K > 16384 || N > (1 << 30) || M > 65535) {
+    return fail(VPQ_ERR_UNSUPPORTED, "affine_qmv_w8g64: K<=16384, M<=65535 supported (K=%lld M=%lld)", (long long)K,
+                (long long)M);
+  }
+  if (!aligned16(w) || !aligned16(x) || (reinterpret_cast<uintptr_t>(scales) & 1) ||
+      (reinterpret_cast<uintptr_t>(biases) & 1) || (reinterpret_cast<uintptr_t>(y) & 1)) {
+    return fail(VPQ_ERR_ALIGNMENT, "affine_qmv_w8g64: w and x must be 16-byte aligned");
+  }
+  if (int rc = require_sm100()) { return rc; }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Problem8 p;
+  std::memset(&p, 0, sizeof(p));
+  if (int rc = make_map_2d(&p.mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w, (uint64_t)(K / 4), (uint64_t)N, 32, 16,
+                           CU_TENSOR_MAP_SWIZZLE_128B, "w")) {
+    return rc;
+  }
+  p.scales_tma = ((K % 512) == 0 && aligned16(scales) && aligned16(biases)) ? 1 : 0;
+  if (p.scales_tma) {
+    if (int rc = make_map_2d(&p.ms, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, (uint64_t)(K / 64), (uint64_t)N, 16, 16,
+                             CU_TENSOR_MAP_SWIZZLE_NONE, "scales")) {
+      return rc;
+    }
+    if (int rc = make_map_2d(&p.mz, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, biases, (uint64_t)(K / 64), (uint64_t)N, 16, 16,
+                             CU_TENSOR_MAP_SWIZZLE_NONE, "biases")) {
+      return rc;
+    }
+  }
+  p.scales = static_cast<const uint16_t*>(scales);
+  p.biases = static_cast<const uint16_t*>(biases);
+  p.K = (int)K;
+  p.N = (int)N;
+  p.row_tiles = (int)((N + 15) / 16);
+  const int cap_kt = (int)((K + 127) / 128);
+  const size_t fixed = fixed_smem(cap_kt);
+  const size_t budget = 112 * 1024;  // two CTAs per SM
+  int stages = fixed + 2 * (size_t)kStageBytes <= budget ? (int)((budget - fixed) / kStageBytes) : 2;
+  if (stages > kMaxStages) { stages = kMaxStages; }
+  const size_t smem = fixed + (size_t)stages * kStageBytes;
+  auto kern = affine_qmv_w8g64_kernel;
+  VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int cap = 2 * num_sms();
+  for (int64_t m = 0; m < M; ++m) {  // every row streams the weight again, as in the reference
+    p.x = static_cast<const uint16_t*>(x) + m * K;
+    p.y = static_cast<__nv_bfloat16*>(y) + m * N;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(p.row_tiles < cap ? p.row_tiles : cap), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    VPQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p, stages, cap_kt));
+  }
+  return VPQ_OK;
+}

@@ -51,6 +51,7 @@ int qmm_launch_multi_dest(const uint32_t* w, const void* scales, const void* bia
 // Reads and clears the GEMV kernel's device status word (qmv.cu).
 int qmv_status_read(cudaStream_t st, uint32_t* out);
 int qmvb_status_read(cudaStream_t st, uint32_t* out);
+int qmv8_status_read(cudaStream_t st, uint32_t* out);
 // Same for the cross-GPU barrier of the fused column-split (nsplit.cu).
 int nsplit_status_read(cudaStream_t st, uint32_t* out);
 
