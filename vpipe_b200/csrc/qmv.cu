@@ -552,7 +552,6 @@ LaunchShape shape_for(int cap_kt) {
   const size_t budget = 112 * 1024;  // two CTAs per SM
   int stages = fixed + 2 * stage_bytes <= budget ? (int)((budget - fixed) / stage_bytes) : 2;
   if (stages > kMaxStages) { stages = kMaxStages; }
-  if (const char* e = std::getenv("VPQ_EXP_STAGES")) { const int v = std::atoi(e); if (v >= 2 && v < stages) { stages = v; } }
   return {stages, fixed + (size_t)stages * stage_bytes};
 }
 
