@@ -95,6 +95,72 @@ static double run_linear(Compute& mc, const char* lib, const char* entry, int M,
   return den > 0 ? std::sqrt(num / den) : std::sqrt(num);
 }
 
+// The fused decode stores through the encoder, against the plain GEMV of the same weights:
+// affine_qmv_qkv_w4g64 (outputs in slots 4..6, row counts as constants), affine_qmv_w4g64_add
+// (slot 7 = residual) and affine_qmv_swiglu_w4g64 (rows interleaved gate | up, halved output).
+static void test_fused_decode_stores(Compute& mc) {
+  const int K = 512, Q = 64, KR = 32, V = 32, N = Q + KR + V;
+  QWeight q = make_qweight(N, K, 4242);
+  std::vector<uint16_t> x(K), res(N);
+  std::mt19937 rng(77);
+  std::normal_distribution<float> nd(0.0f, 1.0f);
+  for (auto& v : x) { v = f32_to_bf16(nd(rng)); }
+  for (auto& v : res) { v = f32_to_bf16(nd(rng)); }
+  SharedBuffer wb = mc.make_shared_buffer(q.packed.size()), sb = mc.make_shared_buffer(q.scales.size() * 2),
+               bb = mc.make_shared_buffer(q.biases.size() * 2), xb = mc.make_shared_buffer(K * 2),
+               rb = mc.make_shared_buffer(N * 2), plain = mc.make_shared_buffer(N * 2),
+               fused = mc.make_shared_buffer(N * 2), added = mc.make_shared_buffer(N * 2),
+               act = mc.make_shared_buffer(N);
+  std::memcpy(wb.contents(), q.packed.data(), q.packed.size());
+  std::memcpy(sb.contents(), q.scales.data(), q.scales.size() * 2);
+  std::memcpy(bb.contents(), q.biases.data(), q.biases.size() * 2);
+  std::memcpy(xb.contents(), x.data(), K * 2);
+  std::memcpy(rb.contents(), res.data(), N * 2);
+  ComputeLibrary lib = mc.load_library("affine_qmv_bf16");
+  CommandStream st;
+  auto bind = [&](ComputeEncoder& enc, const char* entry) {
+    ComputeFunction fn = lib.function(entry);
+    EXPECT_TRUE(fn.valid());
+    enc.set_function(fn);
+    enc.set_buffer(0, wb); enc.set_buffer(1, sb); enc.set_buffer(2, bb); enc.set_buffer(3, xb);
+    enc.set_k(K); enc.set_n(N);
+  };
+  {
+    ComputeEncoder enc = st.begin_compute();
+    bind(enc, "affine_qmv_w4g64");
+    enc.set_buffer(4, plain);
+    enc.dispatch();
+    bind(enc, "affine_qmv_qkv_w4g64");
+    enc.set_buffer(4, fused); enc.set_buffer(5, fused, Q * 2); enc.set_buffer(6, fused, (Q + KR) * 2);
+    enc.set_qkv_rows(Q, KR, V);
+    enc.dispatch();
+    bind(enc, "affine_qmv_w4g64_add");
+    enc.set_buffer(4, added); enc.set_buffer(7, rb);
+    enc.dispatch();
+    bind(enc, "affine_qmv_swiglu_w4g64");
+    enc.set_buffer(4, act);
+    enc.dispatch();
+  }
+  std::string why;
+  EXPECT_TRUE(st.commit().wait_ok(&why));
+  const uint16_t* p = static_cast<const uint16_t*>(plain.contents());
+  const uint16_t* f = static_cast<const uint16_t*>(fused.contents());
+  const uint16_t* a = static_cast<const uint16_t*>(added.contents());
+  const uint16_t* g = static_cast<const uint16_t*>(act.contents());
+  int bad = 0;
+  for (int n = 0; n < N; ++n) {
+    if (f[n] != p[n]) { ++bad; }                                             // q | k | v land where the rows say
+    if (a[n] != f32_to_bf16(bf16_to_f32(p[n]) + bf16_to_f32(res[n]))) { ++bad; }  // bf16(bf16(sum) + residual)
+  }
+  for (int j = 0; j < N / 2; ++j) {  // silu(gate) * up, from unrounded sums: equal to the bf16 route within 2 %
+    const float gt = bf16_to_f32(p[2 * j]), up = bf16_to_f32(p[2 * j + 1]);
+    const float want = gt / (1.0f + std::exp(-gt)) * up;
+    if (std::fabs(bf16_to_f32(g[j]) - want) > 0.02f * std::fabs(want) + 0.02f) { ++bad; }
+  }
+  std::printf("[fused] qkv / add / swiglu through the encoder: %d mismatches\n", bad);
+  EXPECT_TRUE(bad == 0);
+}
+
 int main() {
   Compute mc;
   if (!mc.valid()) { std::printf("no CUDA device: nothing to test\n"); return 2; }
@@ -113,6 +179,7 @@ int main() {
     std::printf("[qmv] N=512 K=3840 rel-L2=%.3e\n", e);
     EXPECT_TRUE(e < 1e-2);
   }
+  test_fused_decode_stores(mc);
   // unknown entry -> invalid function, as ComputeLibrary::function does
   EXPECT_TRUE(!mc.load_library("affine_qmv_bf16").function("nope").valid());
   // quantize -> dequant round trip (model-quantize-roundtrip.cc:84-164): rel-L2 < 0.20 for w4
