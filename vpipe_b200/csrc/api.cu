@@ -90,9 +90,43 @@ static EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// Encoding a tensor map costs about a microsecond of host time and a GEMV needs three; a model
+// calls the same weights every step, so the maps are kept in a small direct-mapped cache. A map
+// is a pure function of the key below, so an entry can never be stale.
+namespace {
+struct MapKey {
+  const void* ptr;
+  uint64_t inner, outer;
+  uint32_t box_inner, box_outer;
+  int dt, elt_bytes, swz;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && inner == o.inner && outer == o.outer && box_inner == o.box_inner &&
+           box_outer == o.box_outer && dt == o.dt && elt_bytes == o.elt_bytes && swz == o.swz;
+  }
+};
+struct MapSlot {
+  MapKey key;
+  CUtensorMap map;
+  bool used;
+};
+constexpr int kMapSlots = 1024;
+MapSlot g_maps[kMapSlots];
+std::mutex g_maps_mutex;
+}  // namespace
+
 int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elt_bytes, const void* ptr,
                 uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer,
                 CUtensorMapSwizzle swz, const char* what) {
+  const MapKey key = {ptr, inner, outer, box_inner, box_outer, (int)dt, elt_bytes, (int)swz};
+  const uint64_t h = (reinterpret_cast<uintptr_t>(ptr) >> 4) * 0x9E3779B97F4A7C15ull + box_outer * 31u + (uint64_t)dt;
+  MapSlot& slot = g_maps[(h >> 32) % kMapSlots];
+  {
+    std::lock_guard<std::mutex> lock(g_maps_mutex);
+    if (slot.used && slot.key == key) {
+      *map = slot.map;
+      return VPQ_OK;
+    }
+  }
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) { return fail(VPQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver"); }
   const cuuint64_t dims[2] = {inner, outer};
@@ -105,6 +139,21 @@ int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elt_bytes, const v
   if (r != CUDA_SUCCESS) {
     return fail(VPQ_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
   }
+  std::lock_guard<std::mutex> lock(g_maps_mutex);
+  slot.key = key;
+  slot.map = *map;
+  slot.used = true;
+  return VPQ_OK;
+}
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) only when a launch needs more than any before
+// it on this device (the attribute is per function and device; it costs a driver call).
+int ensure_dynamic_smem(const void* func, int* granted /* [64], zero-initialised, one per function */, size_t bytes) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { return fail(VPQ_ERR_CUDA, "no current device"); }
+  if ((int)bytes <= granted[dev]) { return VPQ_OK; }
+  VPQ_CUDA_OK(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+  granted[dev] = (int)bytes;
   return VPQ_OK;
 }
 

@@ -625,7 +625,8 @@ int launch_list(const QmvProblem& single, const QmvProblem* list, const int2* ra
                 cudaStream_t st) {
   const LaunchShape ls = shape_for(cap_kt);
   auto kern = affine_qmv_w4g64_kernel;
-  VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ls.smem));
+  static int granted[64] = {};
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), granted, ls.smem)) { return rc; }
   const int ctas = grid_for(total_tiles);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)ctas, 1, 1);

@@ -506,7 +506,8 @@ extern "C" int vpq_affine_qmv_batch_w4g64_bf16(const uint32_t* w, const void* sc
       continue;
     }
     const size_t smem = fixed + (size_t)stages * kStageBytes;
-    VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static int granted[64] = {};
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), granted, smem)) { return rc; }
     const int cap = 2 * num_sms();
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(p.row_tiles < cap ? p.row_tiles : cap), 1, 1);

@@ -413,7 +413,8 @@ extern "C" int vpq_affine_qmv_w8g64_bf16(const uint32_t* w, const void* scales, 
   if (stages > kMaxStages) { stages = kMaxStages; }
   const size_t smem = fixed + (size_t)stages * kStageBytes;
   auto kern = affine_qmv_w8g64_kernel;
-  VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  static int granted[64] = {};
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), granted, smem)) { return rc; }
   const int cap = 2 * num_sms();
   for (int64_t m = 0; m < M; ++m) {  // every row streams the weight again, as in the reference
     p.x = static_cast<const uint16_t*>(x) + m * K;

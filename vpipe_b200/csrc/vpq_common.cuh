@@ -49,6 +49,7 @@ int qmm_launch_multi_dest(const uint32_t* w, const void* scales, const void* bia
                           int64_t M, void* stream);
 
 // Reads and clears the GEMV kernel's device status word (qmv.cu).
+int ensure_dynamic_smem(const void* func, int* granted, size_t bytes);
 int qmv_status_read(cudaStream_t st, uint32_t* out);
 int qmvb_status_read(cudaStream_t st, uint32_t* out);
 int qmv8_status_read(cudaStream_t st, uint32_t* out);
