@@ -86,8 +86,8 @@ int vpq_scales_f16_to_bf16(const void* src_f16, void* dst_bf16, int64_t n, void*
  * with kernels affine_quant_w8_g64 / _w4_g64 / _w8_g32 / _w4_g32 and affine_dequant_w4g64 / _w8g64
  * / _w8g32, gpu-kernels/metal/quant/affine_dequant.metal:25-135,243-301; validated as
  * AffineQuantizer::quantize_linear does, generative-models/quantize/affine-quantizer.cc:55-57.
- * Besides w4 g64 the library has a fused GEMV for w8 g64 (vpq_affine_qmv_w8g64_bf16); the other
- * combinations are dequantised once and multiplied densely, as the reference itself does for its codec weights
+ * Besides w4 g64 the library has a fused GEMV and GEMM for w8 g64 (vpq_affine_qmv_w8g64_bf16,
+ * vpq_affine_qmm_w8g64_bf16); group-32 layers are dequantised once and multiplied densely, as the reference itself does for its codec weights
  * (affine_dequant.metal:100-106). */
 int vpq_affine_quant(const void* w_elt, int src_is_bf16, uint32_t* codes, void* scales_f16, void* biases_f16,
                      int64_t K, int64_t N, int bits, int group, float clip, void* stream);
@@ -224,6 +224,12 @@ int vpq_affine_qmm_w4g64_bf16(const uint32_t* w, const void* scales, const void*
 int vpq_affine_qmm_swiglu_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
                                      const void* x, void* y, int64_t K, int64_t N, int64_t M,
                                      void* stream);
+
+/* GEMM over 8-bit group-64 weights (w u32 [N, K/4]): the same CTA-pair tcgen05 kernel, the W tile
+ * dequantised from bytes (bit-identical to vpq_affine_dequant_bf16 at bits 8). Replaces
+ * affine_qmm_steel_w8g64[_bm64|_bm128], gpu-kernels/metal/quant/affine_qmm_steel.metal:1595-1675. */
+int vpq_affine_qmm_w8g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                              void* y, int64_t K, int64_t N, int64_t M, void* stream);
 
 /* Device-side status of the tensor-core kernels: every wait inside them is
  * bounded; one that gives up records where and the kernel returns. Reads the

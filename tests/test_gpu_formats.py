@@ -117,3 +117,43 @@ def test_qmv_w8g64_f32_accuracy_and_name(vpq, oracle_mod):
     y2 = torch.empty_like(y)
     vpq.ops.dispatch(vpq.ops.function("affine_qmv_bf16", "affine_qmv_w8g64"), list(d) + [y2], K=K, N=N)
     assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("M,K,N", [(256, 512, 512), (130, 320, 95), (33, 128, 33), (2048, 4096, 1024), (512, 2560, 256)])
+def test_qmm_w8g64(vpq, oracle_mod, M, K, N):
+    """affine_qmm_steel_w8g64 (affine_qmm_steel.metal:1595-1675): against the fp32 oracle within the
+    reference's GEMM bound, and against a dense f32 product of the bit-exact dequantised W."""
+    wb = synth.f32_to_bf16_bits(synth.weight_f32(N, K, synth.seed_for("qmm8", M, K, N)))
+    codes, s16, b16 = oracle_mod.quant(wb, 8, 64)
+    s, b = oracle_mod.f16_to_bf16(s16), oracle_mod.f16_to_bf16(b16)
+    x = synth.activations_bf16(M, K, synth.seed_for("qmm8x", M, K, N))
+    d = (to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16), to_dev(x, torch.bfloat16))
+    y = vpq.ops.qmm_w8(*d)
+    assert y.shape == (M, N)
+    assert vpq.ops.device_status() == 0
+    e = oracle_mod.err_metrics(y.float().cpu().numpy(), _w8_reference(oracle_mod, codes, s, b, x))
+    assert e["rel_l2"] < 3e-3 and e["max_rel_rms"] < 1e-2, e
+    wd = vpq.ops.dequantize_any(d[0], d[1], d[2], 8, 64)
+    assert np.array_equal(bits16(wd), oracle_mod.dequant_bf16_any(codes, s, b, 8, 64))
+    ref = d[3].float() @ wd.float().t()
+    assert float((y.float() - ref).abs().max()) <= 1e-2 * float(ref.abs().max())
+    assert float((y.float() - ref).norm() / ref.norm()) < 3e-3
+
+
+def test_qmm_w8g64_large_scales_take_the_exact_route(vpq, oracle_mod):
+    """Scales at or above 2^-5 (and zero scales) cannot use the scaled-subnormal multiply: same result."""
+    M, K, N = 256, 256, 128
+    rng = np.random.default_rng(12)
+    codes = rng.integers(0, 2**32, (N, K // 4), dtype=np.uint32)
+    s = synth.f32_to_bf16_bits((rng.random((N, K // 64)) * 0.2).astype(np.float32))   # many above 2^-5
+    s[0, :] = 0                                                                    # zero scale
+    b = synth.f32_to_bf16_bits((rng.random((N, K // 64)) * 2 - 1).astype(np.float32))
+    x = synth.activations_bf16(M, K, 13)
+    d = (to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16), to_dev(x, torch.bfloat16))
+    y = vpq.ops.qmm_w8(*d)
+    wd = vpq.ops.dequantize_any(d[0], d[1], d[2], 8, 64)
+    ref = d[3].float() @ wd.float().t()
+    assert float((y.float() - ref).norm() / ref.norm()) < 3e-3
+    y2 = torch.empty_like(y)
+    vpq.ops.dispatch(vpq.ops.function("affine_qmm_steel_bf16", "affine_qmm_steel_w8g64"), list(d) + [y2], K=K, N=N, M=M)
+    assert torch.equal(y, y2)

@@ -6,6 +6,7 @@
     python -m vpipe_b200.cases qmv_w8 K N [launches]   # 8-bit GEMV on distinct weight copies (graph replay)
     python -m vpipe_b200.cases qmm  M K N [reps]       # the GEMM
     python -m vpipe_b200.cases qmm_swiglu M K N [reps] # the GEMM with the fused SwiGLU store (N = 2 ffn)
+    python -m vpipe_b200.cases qmm_w8 M K N [reps]     # the GEMM over 8-bit weights
 
 Weights are random packed nibbles with bf16 scales / biases (the distribution of the reference's
 kernel tests); each command prints one JSON line with the CUDA-event time. Meant to be wrapped by
@@ -111,6 +112,20 @@ def main(argv):
         t = _time(plan.run, 1)
         nbytes = sum(synth.qmv_bytes(p.K, p.N) for p in synth.CONFIGS["C2"].projs) * layers
         print(json.dumps({"case": "plan", "layers": layers, "us": t * 1e6, "GBs": nbytes / t / 1e9}))
+    elif kind == "qmm_w8":
+        M, K, N = int(argv[1]), int(argv[2]), int(argv[3])
+        reps = int(argv[4]) if len(argv) > 4 else 3
+        x = torch.randn((M, K), device=dev).to(torch.bfloat16)
+        codes = torch.randint(-2**31, 2**31 - 1, (N, K // 4), dtype=torch.int32, device=dev)
+        s = (torch.rand((N, K // 64), device=dev) * 0.001 + 0.0003).to(torch.bfloat16)
+        b = (torch.rand((N, K // 64), device=dev) * 0.2 - 0.1).to(torch.bfloat16)
+        y = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        for _ in range(2):
+            ops.qmm_w8(codes, s, b, x, out=y)
+        torch.cuda.synchronize()
+        t = _time(lambda: ops.qmm_w8(codes, s, b, x, out=y), reps)
+        print(json.dumps({"case": kind, "M": M, "K": K, "N": N, "ms": t * 1e3,
+                          "tflops": synth.qmm_flops(K, N, M) / t / 1e12}))
     elif kind in ("qmm", "qmm_swiglu"):
         M, K, N = int(argv[1]), int(argv[2]), int(argv[3])
         reps = int(argv[4]) if len(argv) > 4 else 3

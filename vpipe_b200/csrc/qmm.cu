@@ -155,6 +155,37 @@ __device__ __forceinline__ void dequant_word_fast(uint32_t word, uint64_t s2, ui
 }
 #undef VPQ_DEQUANT_PAIR
 
+// 8-bit codes: the two byte pairs of a word -> two packed bf16x2. The byte goes to bits 16..23
+// of a zero word (PRMT), which as a float is q * 2^-133; s2 holds (s * 2^133, s * 2^133).
+#define VPQ_DEQUANT_PAIR8(J, SEL_LO, SEL_HI)                                         \
+  asm("{\n\t"                                                                        \
+      ".reg .b32 fe, fo, ve, vo;\n\t"                                                \
+      ".reg .b64 q2, v2;\n\t"                                                        \
+      "prmt.b32 fe, %1, 0, " SEL_LO ";\n\t"                                          \
+      "prmt.b32 fo, %1, 0, " SEL_HI ";\n\t"                                          \
+      "mov.b64 q2, {fe, fo};\n\t"                                                    \
+      "fma.rn.f32x2 v2, %2, q2, %3;\n\t"                                             \
+      "mov.b64 {ve, vo}, v2;\n\t"                                                    \
+      "cvt.rn.bf16x2.f32 %0, vo, ve;\n\t"                                            \
+      "}"                                                                            \
+      : "=r"(out[J])                                                                 \
+      : "r"(word), "l"(s2), "l"(b2))
+
+__device__ __forceinline__ void dequant_word8_fast(uint32_t word, uint64_t s2, uint64_t b2, uint32_t* out) {
+  VPQ_DEQUANT_PAIR8(0, "0x4044", "0x4144");  // bytes 0, 1
+  VPQ_DEQUANT_PAIR8(1, "0x4244", "0x4344");  // bytes 2, 3
+}
+#undef VPQ_DEQUANT_PAIR8
+
+__device__ __forceinline__ void dequant_word8_exact(uint32_t word, float s, float b, uint32_t* out) {
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const float ve = dequant_f32(s, (word >> (16 * j)) & 0xffu, b);
+    const float vo = dequant_f32(s, (word >> (16 * j + 8)) & 0xffu, b);
+    out[j] = pack_bf16x2(ve, vo);
+  }
+}
+
 __device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
   uint64_t r;
   asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
@@ -481,27 +512,34 @@ int launch_qmm(const uint32_t* w, const uint16_t* scales, const uint16_t* biases
   return VPQ_OK;
 }
 
-int launch_qmm_2cta(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const void* x,
-                    const two_cta::OutSpec& out, int K, int N, int M, cudaStream_t st, int reserve_sms) {
-  using L = two_cta::Smem;
+template <int BITS>
+int launch_qmm_2cta_bits(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const void* x,
+                         const two_cta::OutSpec& out, int K, int N, int M, cudaStream_t st, int reserve_sms) {
+  using L = two_cta::SmemT<BITS>;
   CUtensorMap map_x, map_w;
   if (int rc = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)K, (uint64_t)M,
                            BK, 128, CU_TENSOR_MAP_SWIZZLE_128B, "x")) {
     return rc;
   }
-  if (int rc = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w, (uint64_t)(K / 8),
-                           (uint64_t)N, BK / 8, 128, CU_TENSOR_MAP_SWIZZLE_NONE, "w")) {
+  if (int rc = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w, (uint64_t)(K * BITS / 32),
+                           (uint64_t)N, BK * BITS / 32, 128, CU_TENSOR_MAP_SWIZZLE_NONE, "w")) {
     return rc;
   }
-  auto kern = out.swiglu ? two_cta::affine_qmm_w4g64_2cta_kernel<true> : two_cta::affine_qmm_w4g64_2cta_kernel<false>;
+  auto kern = out.swiglu ? two_cta::affine_qmm_w4g64_2cta_kernel<true, BITS>
+                         : two_cta::affine_qmm_w4g64_2cta_kernel<false, BITS>;
   VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
   const int tiles = ((M + two_cta::TM - 1) / two_cta::TM) * ((N + two_cta::TN - 1) / two_cta::TN);
   int pairs = (num_sms() - reserve_sms) / 2;  // SMs left free run a concurrent collective
   if (pairs < 1) { pairs = 1; }
   const int grid = 2 * (tiles < pairs ? tiles : pairs);
   kern<<<grid, two_cta::kThreads2, L::kAlloc, st>>>(map_x, map_w, scales, biases, out, M, N, K);
-  VPQ_LAUNCH_OK("affine_qmm_w4g64 (2-CTA)");
+  VPQ_LAUNCH_OK("affine_qmm (2-CTA)");
   return VPQ_OK;
+}
+
+int launch_qmm_2cta(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const void* x,
+                    const two_cta::OutSpec& out, int K, int N, int M, cudaStream_t st, int reserve_sms) {
+  return launch_qmm_2cta_bits<4>(w, scales, biases, x, out, K, N, M, st, reserve_sms);
 }
 
 }  // namespace
@@ -605,6 +643,32 @@ extern "C" int vpq_affine_qmm_swiglu_w4g64_bf16(const uint32_t* w, const void* s
   out.swiglu = 1;
   return launch_qmm_2cta(w, static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases), x, out,
                          (int)K, (int)N, (int)M, static_cast<cudaStream_t>(stream), 0);
+}
+
+extern "C" int vpq_affine_qmm_w8g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                                         void* y, int64_t K, int64_t N, int64_t M, void* stream) {
+  clear_error();
+  if (!w || !scales || !biases || !x || !y) { return fail(VPQ_ERR_INVALID_ARG, "affine_qmm_w8g64: null pointer"); }
+  if (K <= 0 || N <= 0 || M <= 0 || (K % 64) != 0) {
+    return fail(VPQ_ERR_INVALID_ARG, "affine_qmm_w8g64: need K>0, N>0, M>0, K%%64==0 (K=%lld N=%lld M=%lld)",
+                (long long)K, (long long)N, (long long)M);
+  }
+  if (K > (1 << 20) || N > (1 << 24) || M > (1 << 24)) {
+    return fail(VPQ_ERR_UNSUPPORTED, "affine_qmm_w8g64: shape too large (K=%lld N=%lld M=%lld)", (long long)K,
+                (long long)N, (long long)M);
+  }
+  if (!aligned16(w) || !aligned16(x) || !aligned16(y) || (reinterpret_cast<uintptr_t>(scales) & 1) ||
+      (reinterpret_cast<uintptr_t>(biases) & 1)) {
+    return fail(VPQ_ERR_ALIGNMENT, "affine_qmm_w8g64: w, x and y must be 16-byte aligned");
+  }
+  if (int rc = require_sm100()) { return rc; }
+  two_cta::OutSpec out = {};
+  out.base[0] = static_cast<__nv_bfloat16*>(y);
+  out.count = 1;
+  out.col0 = 0;
+  out.ld = N;
+  return launch_qmm_2cta_bits<8>(w, static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases), x, out,
+                                 (int)K, (int)N, (int)M, static_cast<cudaStream_t>(stream), 0);
 }
 
 extern "C" int vpq_device_status(void* stream, uint32_t* detail) {

@@ -23,7 +23,8 @@ namespace two_cta {
 
 constexpr int TM = 256;        // tile rows (128 per CTA)
 constexpr int TN = 256;        // tile columns (128 W rows dequantised per CTA)
-constexpr int kXStages = 5;    // x + codes ring
+constexpr int kXStages4 = 5;   // x + codes ring, 4-bit weights
+constexpr int kXStages8 = 4;   // ... 8-bit weights (the codes of a stage are twice as large)
 constexpr int kBTiles = 5;     // dequantised-B ring
 constexpr int kDqWarps = 8;
 constexpr int kDqGroups = 2;   // warp groups that take alternate k blocks (a group = 4 warps = 128 rows)
@@ -43,9 +44,11 @@ struct OutSpec {
                // (selects the kernel instantiation)
 };
 
-struct Smem {
+template <int BITS>
+struct SmemT {
+  static constexpr int kXStages = BITS == 8 ? kXStages8 : kXStages4;
   static constexpr int kXBytes = 128 * BK * 2;        // 16 KB, 128B-swizzled
-  static constexpr int kCodeBytes = 128 * (BK / 2);   // 128 rows x 32 B
+  static constexpr int kCodeBytes = 128 * (BK * BITS / 8);  // 128 rows x 32 B (64 B at 8 bits)
   static constexpr int kBBytes = 128 * BK * 2;        // 16 KB, 128B-swizzled K-major
   static constexpr int kOffX = 0;
   static constexpr int kOffB = kOffX + kXStages * kXBytes;
@@ -58,6 +61,8 @@ struct Smem {
   static constexpr int kTotal = kOffTmem + 16;
   static constexpr int kAlloc = kTotal + 1024;
 };
+using Smem = SmemT<4>;
+static_assert(SmemT<4>::kAlloc <= 227 * 1024 && SmemT<8>::kAlloc <= 227 * 1024, "shared memory of the pair kernel");
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -124,13 +129,14 @@ __device__ __forceinline__ constexpr uint32_t make_idesc_pair() {
 }
 
 
-template <bool kSwiglu>
+template <bool kSwiglu, int BITS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
 affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
                              const __grid_constant__ CUtensorMap tmap_w,
                              const uint16_t* __restrict__ scales, const uint16_t* __restrict__ biases,
                              const OutSpec out, int M, int N, int K) {
-  using L = Smem;
+  using L = SmemT<BITS>;
+  constexpr int kXStages = L::kXStages;
   constexpr uint32_t kTmemCols = 512;  // two 256-column accumulator buffers
 
   extern __shared__ unsigned char smem_dyn[];
@@ -205,7 +211,7 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
           if (rank == 0) { mbar_expect_tx(bar_xfull(s), 2 * L::kXBytes); }
           mbar_expect_tx(bar_cfull(s), L::kCodeBytes);
           tma_load_2d_pair(base + L::kOffX + s * L::kXBytes, &tmap_x, map_to_cta(bar_xfull(s), 0), kb * BK, m0);
-          tma_load_2d(base + L::kOffCode + s * L::kCodeBytes, &tmap_w, bar_cfull(s), kb * (BK / 8), n0);
+          tma_load_2d(base + L::kOffCode + s * L::kCodeBytes, &tmap_w, bar_cfull(s), kb * (BK * BITS / 32), n0);
         }
       }
       // Never leave with a copy still in flight: the codes barriers are local; the x copies of
@@ -282,25 +288,48 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
         sst.get(kb, sc, bi);
         if (!warp_wait(bar_cfull(s), ph, (1u << 8) | kRoleDq, abort_flag, &g_qmm_status)) { ok = false; break; }
         const uint4* cp = reinterpret_cast<const uint4*>(base_ptr + L::kOffCode + s * L::kCodeBytes +
-                                                         t_row * (BK / 2));
-        const uint4 c0 = cp[0], c1 = cp[1];
-        __syncwarp();
-        if (lane == 0) { mbar_arrive(bar_empty(s)); }  // codes are in registers
-
-        const float t128 = 128.0f * sc;
-        const float b128 = bi - t128;
-        const float bb = b128 - bi;
-        const float resid = (bi - (b128 - bb)) + (-t128 - bb);  // two-sum residual of b - 128 s
+                                                         t_row * (BK * BITS / 8));
         uint32_t o[32];
-        const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-        {
-          const uint64_t s2 = pack_f32x2(sc, sc), b2 = pack_f32x2(b128, b128);
+        if (BITS == 4) {
+          const uint4 c0 = cp[0], c1 = cp[1];
+          __syncwarp();
+          if (lane == 0) { mbar_arrive(bar_empty(s)); }  // codes are in registers
+
+          const float t128 = 128.0f * sc;
+          const float b128 = bi - t128;
+          const float bb = b128 - bi;
+          const float resid = (bi - (b128 - bb)) + (-t128 - bb);  // two-sum residual of b - 128 s
+          const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+          {
+            const uint64_t s2 = pack_f32x2(sc, sc), b2 = pack_f32x2(b128, b128);
 #pragma unroll
-          for (int wd = 0; wd < 8; ++wd) { dequant_word_fast(cw[wd], s2, b2, o + 4 * wd); }
-        }
-        if (resid != 0.0f) {  // b - 128 s was not exact for this group: redo it the plain way
+            for (int wd = 0; wd < 8; ++wd) { dequant_word_fast(cw[wd], s2, b2, o + 4 * wd); }
+          }
+          if (resid != 0.0f) {  // b - 128 s was not exact for this group: redo it the plain way
 #pragma unroll
-          for (int wd = 0; wd < 8; ++wd) { dequant_word_exact(cw[wd], sc, bi, o + 4 * wd); }
+            for (int wd = 0; wd < 8; ++wd) { dequant_word_exact(cw[wd], sc, bi, o + 4 * wd); }
+          }
+        } else {
+          const uint4 c0 = cp[0], c1 = cp[1], c2 = cp[2], c3 = cp[3];
+          __syncwarp();
+          if (lane == 0) { mbar_arrive(bar_empty(s)); }  // codes are in registers
+          const uint32_t cw[16] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w,
+                                   c2.x, c2.y, c2.z, c2.w, c3.x, c3.y, c3.z, c3.w};
+          // A byte placed in bits 16..23 of an otherwise zero word is the float q * 2^-133
+          // (subnormals and the first binade are linear in their bit pattern), so
+          // fma(that, s * 2^133, b) rounds the same real number as fma(s, q, b): bit-exact,
+          // as long as s * 2^133 is a normal float (2^-126 <= |s| < 2^-5; else the plain way).
+          const uint32_t sbits = __float_as_uint(sc);
+          const uint32_t sexp = (sbits >> 23) & 0xffu;
+          if (sexp >= 1u && sexp <= 121u) {  // a normal s below 2^-5: s * 2^133 by exponent arithmetic
+            const float s_up = __uint_as_float(sbits + (133u << 23));
+            const uint64_t s2 = pack_f32x2(s_up, s_up), b2 = pack_f32x2(bi, bi);
+#pragma unroll
+            for (int wd = 0; wd < 16; ++wd) { dequant_word8_fast(cw[wd], s2, b2, o + 2 * wd); }
+          } else {
+#pragma unroll
+            for (int wd = 0; wd < 16; ++wd) { dequant_word8_exact(cw[wd], sc, bi, o + 2 * wd); }
+          }
         }
 
         if (!warp_wait(bar_bempty(t), bph ^ 1u, (2u << 8) | kRoleDq, abort_flag, &g_qmm_status)) { ok = false; break; }

@@ -231,6 +231,19 @@ def qmm(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
     return out
 
 
+def qmm_w8(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
+    """GEMM over 8-bit group-64 weights, codes int32 [N, K/4] (vpq_affine_qmm_w8g64_bf16)."""
+    N, Kw = codes.shape
+    K = Kw * 4
+    M = x.numel() // K
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().vpq_affine_qmm_w8g64_bf16(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x), _ptr(out),
+                                              K, N, M, _stream(stream)))
+    return out
+
+
 def qmm_swiglu(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
     """Rows of W interleaved gate / up: y[M, N/2] = silu(gate) * up (vpq_affine_qmm_swiglu_w4g64_bf16)."""
     N, Kw = codes.shape
