@@ -157,3 +157,21 @@ def test_qmm_w8g64_large_scales_take_the_exact_route(vpq, oracle_mod):
     y2 = torch.empty_like(y)
     vpq.ops.dispatch(vpq.ops.function("affine_qmm_steel_bf16", "affine_qmm_steel_w8g64"), list(d) + [y2], K=K, N=N, M=M)
     assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_gemm_tile_dequant_is_bit_identical_to_the_dequantizer(vpq, oracle_mod, bits):
+    """x = identity: y[m, n] = W_deq[n, m] with nothing to round, so the GEMM output IS the tile the
+    kernel dequantised. Includes zero scales, scales >= 2^-5 (the plain route) and extreme pairs."""
+    K, N = 256, 320
+    rng = np.random.default_rng(20 + bits)
+    codes = rng.integers(0, 2**32, (N, K * bits // 32), dtype=np.uint32)
+    s = synth.f32_to_bf16_bits((rng.random((N, K // 64)) * (0.02 if bits == 4 else 0.002) + 0.0001).astype(np.float32))
+    b = synth.f32_to_bf16_bits((rng.random((N, K // 64)) * 0.4 - 0.2).astype(np.float32))
+    s[0, :], s[1, :], s[2, 0], s[3, 0] = 0, 0x3E00, 0x0080, 0x3D00      # zero, 0.125, smallest normal, 2^-5
+    b[2, 0], b[4, 0] = 0x3F80, 0x8000
+    x = synth.f32_to_bf16_bits(np.eye(K, dtype=np.float32))
+    d = (to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16), to_dev(x, torch.bfloat16))
+    y = (vpq.ops.qmm if bits == 4 else vpq.ops.qmm_w8)(*d)
+    want = oracle_mod.dequant_bf16_any(codes, s, b, bits, 64)
+    assert np.array_equal(bits16(y), want.T)

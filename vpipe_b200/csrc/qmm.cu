@@ -123,20 +123,21 @@ __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// 8 nibbles of one packed word -> 8 bf16 (4 packed registers), bit-identical
-// to bf16_rne(fmaf(s, q, b)). The nibble is dropped into mantissa bits 16..19
-// of 0x43000000 (the float 128 + q); with b128 = b - 128 s formed exactly,
-// fmaf(s, 128 + q, b128) rounds the same real number s q + b once. The two
-// multiply-adds of a nibble pair share one packed f32x2 instruction; s2 / b2
-// hold (s, s) and (b128, b128).
-// One nibble pair (byte J of the even / odd nibble words) -> one packed bf16x2. The PRMT selector
-// and the magic constant are immediates of the instruction, not registers.
+// 8 nibbles of one packed word -> 8 bf16 (4 packed registers), bit-identical to
+// bf16_rne(fmaf(s, q, b)). A nibble moved into bits 16..23 of a zero word is, read as a float,
+// the subnormal (or first-binade) number n * 2^-133, n the integer in those bits: the even
+// nibbles arrive as q, the odd ones (left in the high half of their byte) as 16 q. Then
+// fmaf(n * 2^-133, s * 2^133 (or s * 2^129 for the odd ones), b) rounds the same real number
+// s q + b once. The two multiply-adds of a nibble pair share one packed f32x2 instruction;
+// s2 holds (s * 2^133, s * 2^129), b2 holds (b, b). Valid while s * 2^133 is a normal float
+// (2^-126 <= |s| < 2^-5); dequant_scale_up() says so, other scales take dequant_word_exact.
+// One nibble pair (byte J of the even / odd nibble words) -> one packed bf16x2.
 #define VPQ_DEQUANT_PAIR(J, SEL)                                                     \
   asm("{\n\t"                                                                        \
       ".reg .b32 fe, fo, ve, vo;\n\t"                                                \
       ".reg .b64 q2, v2;\n\t"                                                        \
-      "prmt.b32 fe, %1, 0x43000000, " SEL ";\n\t"                                    \
-      "prmt.b32 fo, %2, 0x43000000, " SEL ";\n\t"                                    \
+      "prmt.b32 fe, %1, 0, " SEL ";\n\t"                                             \
+      "prmt.b32 fo, %2, 0, " SEL ";\n\t"                                             \
       "mov.b64 q2, {fe, fo};\n\t"                                                    \
       "fma.rn.f32x2 v2, %3, q2, %4;\n\t"                                             \
       "mov.b64 {ve, vo}, v2;\n\t"                                                    \
@@ -146,14 +147,23 @@ __device__ __forceinline__ void tmem_ld_wait() {
       : "r"(e), "r"(o), "l"(s2), "l"(b2))
 
 __device__ __forceinline__ void dequant_word_fast(uint32_t word, uint64_t s2, uint64_t b2, uint32_t* out) {
-  const uint32_t e = word & 0x0f0f0f0fu;         // nibbles 0,2,4,6 as bytes
-  const uint32_t o = (word >> 4) & 0x0f0f0f0fu;  // nibbles 1,3,5,7 as bytes
-  VPQ_DEQUANT_PAIR(0, "0x7054");
-  VPQ_DEQUANT_PAIR(1, "0x7154");
-  VPQ_DEQUANT_PAIR(2, "0x7254");
-  VPQ_DEQUANT_PAIR(3, "0x7354");
+  const uint32_t e = word & 0x0f0f0f0fu;  // nibbles 0,2,4,6 in the low halves of the bytes
+  const uint32_t o = word & 0xf0f0f0f0u;  // nibbles 1,3,5,7 times 16
+  VPQ_DEQUANT_PAIR(0, "0x4044");
+  VPQ_DEQUANT_PAIR(1, "0x4144");
+  VPQ_DEQUANT_PAIR(2, "0x4244");
+  VPQ_DEQUANT_PAIR(3, "0x4344");
 }
 #undef VPQ_DEQUANT_PAIR
+
+// s * 2^shift by exponent arithmetic; false if s is zero / subnormal or s * 2^133 would overflow.
+__device__ __forceinline__ bool dequant_scale_up(float s, float& s_133, float& s_129) {
+  const uint32_t bits = __float_as_uint(s);
+  const uint32_t e = (bits >> 23) & 0xffu;
+  s_133 = __uint_as_float(bits + (133u << 23));
+  s_129 = __uint_as_float(bits + (129u << 23));
+  return e >= 1u && e <= 121u;
+}
 
 // 8-bit codes: the two byte pairs of a word -> two packed bf16x2. The byte goes to bits 16..23
 // of a zero word (PRMT), which as a float is q * 2^-133; s2 holds (s * 2^133, s * 2^133).
@@ -400,15 +410,11 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
         __syncwarp();
         if (lane == 0) { mbar_arrive(bar_empty(s)); }  // codes are in registers
 
-        // b - 128 s, and whether that subtraction was exact (two-sum residual)
-        const float t128 = 128.0f * sc;
-        const float b128 = bi - t128;
-        const float bb = b128 - bi;
-        const float resid = (bi - (b128 - bb)) + (-t128 - bb);
         uint32_t o[32];
         const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-        if (resid == 0.0f) {
-          const uint64_t s2 = pack_f32x2(sc, sc), b2 = pack_f32x2(b128, b128);
+        float s_133, s_129;
+        if (dequant_scale_up(sc, s_133, s_129)) {
+          const uint64_t s2 = pack_f32x2(s_133, s_129), b2 = pack_f32x2(bi, bi);
 #pragma unroll
           for (int wd = 0; wd < 8; ++wd) { dequant_word_fast(cw[wd], s2, b2, o + 4 * wd); }
         } else {

@@ -295,17 +295,13 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
           __syncwarp();
           if (lane == 0) { mbar_arrive(bar_empty(s)); }  // codes are in registers
 
-          const float t128 = 128.0f * sc;
-          const float b128 = bi - t128;
-          const float bb = b128 - bi;
-          const float resid = (bi - (b128 - bb)) + (-t128 - bb);  // two-sum residual of b - 128 s
           const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-          {
-            const uint64_t s2 = pack_f32x2(sc, sc), b2 = pack_f32x2(b128, b128);
+          float s_133, s_129;
+          if (dequant_scale_up(sc, s_133, s_129)) {
+            const uint64_t s2 = pack_f32x2(s_133, s_129), b2 = pack_f32x2(bi, bi);
 #pragma unroll
             for (int wd = 0; wd < 8; ++wd) { dequant_word_fast(cw[wd], s2, b2, o + 4 * wd); }
-          }
-          if (resid != 0.0f) {  // b - 128 s was not exact for this group: redo it the plain way
+          } else {  // a zero, subnormal or large scale: the plain way
 #pragma unroll
             for (int wd = 0; wd < 8; ++wd) { dequant_word_exact(cw[wd], sc, bi, o + 4 * wd); }
           }
@@ -319,11 +315,9 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
           // (subnormals and the first binade are linear in their bit pattern), so
           // fma(that, s * 2^133, b) rounds the same real number as fma(s, q, b): bit-exact,
           // as long as s * 2^133 is a normal float (2^-126 <= |s| < 2^-5; else the plain way).
-          const uint32_t sbits = __float_as_uint(sc);
-          const uint32_t sexp = (sbits >> 23) & 0xffu;
-          if (sexp >= 1u && sexp <= 121u) {  // a normal s below 2^-5: s * 2^133 by exponent arithmetic
-            const float s_up = __uint_as_float(sbits + (133u << 23));
-            const uint64_t s2 = pack_f32x2(s_up, s_up), b2 = pack_f32x2(bi, bi);
+          float s_133, s_129;
+          if (dequant_scale_up(sc, s_133, s_129)) {
+            const uint64_t s2 = pack_f32x2(s_133, s_133), b2 = pack_f32x2(bi, bi);
 #pragma unroll
             for (int wd = 0; wd < 16; ++wd) { dequant_word8_fast(cw[wd], s2, b2, o + 2 * wd); }
           } else {
