@@ -378,6 +378,7 @@ def bench_qmm(torch, dist, ops, synth, args, rank, world, dev, pk, key, comm):
     barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
     steps = max(3, min(args.steps, 10))
     tot_flops, tot_t = 0.0, 0.0
+    e2e_t, e2e_flops, h2d, d2h = 0.0, 0.0, 0, 0
     for p in cfg.projs:
         if world > 1 and p.N % (8 * world):
             continue
@@ -403,6 +404,30 @@ def bench_qmm(torch, dist, ops, synth, args, rank, world, dev, pk, key, comm):
             tc = timed(torch, lambda: ops.qmm(codes, s, b, x, out=ymine), steps, 2, barrier)
             rec["gemm_only_ms"] = max_over_ranks(torch, dist, world, tc, dev) / steps * 1e3
             rec["gather_bytes_per_gpu"] = (world - 1) * M * ns * 2
+        if world == 1:
+            # end to end: the activations come from pinned host memory and the product goes back,
+            # inside the timed region (PCIe-bound for the large shapes, and reported as such)
+            try:
+                hx = torch.empty((M, p.K), dtype=torch.bfloat16).pin_memory()
+                hx.copy_(x)
+                hy = torch.empty((M, p.N), dtype=torch.bfloat16).pin_memory()
+
+                def e2e_step():
+                    x.copy_(hx, non_blocking=True)
+                    ops.qmm(codes, s, b, x, out=y)
+                    hy.copy_(y, non_blocking=True)
+                    torch.cuda.current_stream().synchronize()
+
+                te = timed(torch, e2e_step, 3, 3, barrier) / 3
+                rec["e2e_ms"] = te * 1e3
+                e2e_t += te
+                e2e_flops += flops
+                h2d += hx.numel() * 2
+                d2h += hy.numel() * 2
+                del hx, hy
+            except Exception as e:   # not enough pinned memory for this shape: say so
+                rec["e2e_ms"] = None
+                rec["e2e_error"] = type(e).__name__
         out["shapes"].append(rec)
         tot_flops += flops
         tot_t += t
@@ -418,6 +443,9 @@ def bench_qmm(torch, dist, ops, synth, args, rank, world, dev, pk, key, comm):
                              "peak_source": pk["source"] + " (burst, cuBLAS bf16)",
                              "kernel": "affine_qmm_w4g64_kernel",
                              "traffic": None})
+        if e2e_t > 0:
+            out["e2e"] = {"value": e2e_flops / e2e_t / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                          "d2h_bytes_per_step": d2h, "note": "one step = every shape once, x from and y to pinned host memory"}
     return out
 
 
@@ -521,7 +549,7 @@ def main():
                        "l2": "x + y of every shape exceed L2", "m_chunks": args.m_chunks,
                        "parallelism": (f"column-split x{world}, " + ("GEMM + NCCL all-gather" if args.nccl_gather else
                                         "fused peer-store epilogue over NVLink")) if world > 1 else "1 GPU"},
-            "roofline": qmm.get("roofline"), "clocks": clocks, "shapes": qmm["shapes"],
+            "roofline": qmm.get("roofline"), "e2e": qmm.get("e2e"), "clocks": clocks, "shapes": qmm["shapes"],
             "gpu_launches": len(qmm["shapes"]) * max(3, min(args.steps, 10)),
         }
     if comm is not None:
