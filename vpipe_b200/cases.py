@@ -4,6 +4,7 @@
     python -m vpipe_b200.cases plan LAYERS             # the C2 decode set as one plan launch
     python -m vpipe_b200.cases qmv_batch K N M [launches]  # small-batch GEMV vs M serial GEMVs
     python -m vpipe_b200.cases qmv_w8 K N [launches]   # 8-bit GEMV on distinct weight copies (graph replay)
+    python -m vpipe_b200.cases decode_layers LAYERS    # 8B-decoder layers as dependent fused launches (graph replay)
     python -m vpipe_b200.cases qmm  M K N [reps]       # the GEMM
     python -m vpipe_b200.cases qmm_swiglu M K N [reps] # the GEMM with the fused SwiGLU store (N = 2 ffn)
     python -m vpipe_b200.cases qmm_w8 M K N [reps]     # the GEMM over 8-bit weights
@@ -55,6 +56,46 @@ def main(argv):
         t = _time(lambda: (lambda p: ops.qmv(*p[:4], out=p[4]))(next(it)), n)
         print(json.dumps({"case": "qmv", "K": K, "N": N, "us": t * 1e6,
                           "GBs": synth.qmv_bytes(K, N) / t / 1e9}))
+    elif kind == "decode_layers":
+        # What a decode step of an 8B decoder issues per layer when it uses the fused entries:
+        # q|k|v (one GEMV, three outputs), o_proj + residual, gate|up with SwiGLU, down + residual;
+        # each launch reads what the one before wrote (attention itself is not modelled: o_proj
+        # reads the q output). 4 launches per layer instead of 7 plain GEMVs + 3 elementwise passes.
+        layers = int(argv[1])
+        H, KV, F = 4096, 1024, 12288
+        h = torch.randn((1, H), device=dev).to(torch.bfloat16)
+        L, nbytes = [], 0
+        for _ in range(layers):
+            qkv, o, gu, dn = _weight(H + 2 * KV, H, dev), _weight(H, H, dev), _weight(2 * F, H, dev), _weight(H, F, dev)
+            bufs = [torch.empty((1, n), dtype=torch.bfloat16, device=dev) for n in (H, KV, KV, H, F, H)]
+            L.append((qkv, o, gu, dn, bufs))
+            nbytes += (synth.qmv_bytes(H, H + 2 * KV) + synth.qmv_bytes(H, H) + synth.qmv_bytes(H, 2 * F) +
+                       synth.qmv_bytes(F, H))
+
+        def step():
+            x = h
+            for qkv, o, gu, dn, (q, k, v, h1, act, h2) in L:
+                check = ops.check
+                lib = ops.lib()
+                st = torch.cuda.current_stream().cuda_stream
+                check(lib.vpq_affine_qmv_qkv_w4g64_bf16(qkv[0].data_ptr(), qkv[1].data_ptr(), qkv[2].data_ptr(),
+                                                        x.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                                        H, H, KV, KV, 1, st))
+                ops.qmv_add(o[0], o[1], o[2], q, x, out=h1)
+                ops.qmv_swiglu(gu[0], gu[1], gu[2], h1, out=act)
+                ops.qmv_add(dn[0], dn[1], dn[2], act, h1, out=h2)
+                x = h2
+
+        step()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            step()
+        g.replay()
+        torch.cuda.synchronize()
+        t = _time(g.replay, 5)
+        print(json.dumps({"case": "decode_layers", "layers": layers, "launches": 4 * layers, "us": t * 1e6,
+                          "us_per_launch": t * 1e6 / (4 * layers), "GBs": nbytes / t / 1e9}))
     elif kind == "qmv_w8":
         K, N = int(argv[1]), int(argv[2])
         n = int(argv[3]) if len(argv) > 3 else 8
