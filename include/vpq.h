@@ -87,7 +87,8 @@ int vpq_scales_f16_to_bf16(const void* src_f16, void* dst_bf16, int64_t n, void*
  * / _w8g32, gpu-kernels/metal/quant/affine_dequant.metal:25-135,243-301; validated as
  * AffineQuantizer::quantize_linear does, generative-models/quantize/affine-quantizer.cc:55-57.
  * Besides w4 g64 the library has a fused GEMV and GEMM for w8 g64 (vpq_affine_qmv_w8g64_bf16,
- * vpq_affine_qmm_w8g64_bf16); group-32 layers are dequantised once and multiplied densely, as the reference itself does for its codec weights
+ * vpq_affine_qmm_w8g64_bf16) and a fused GEMV for w4 g32 (vpq_affine_qmv_w4g32_bf16); the remaining
+ * combinations are dequantised once and multiplied densely, as the reference itself does for its codec weights
  * (affine_dequant.metal:100-106). */
 int vpq_affine_quant(const void* w_elt, int src_is_bf16, uint32_t* codes, void* scales_f16, void* biases_f16,
                      int64_t K, int64_t N, int bits, int group, float clip, void* stream);
@@ -128,6 +129,13 @@ int vpq_affine_qmv_qkv_w4g64_bf16(const uint32_t* w, const void* scales, const v
  * no unpacking at all. K <= 16384. Replaces affine_qmv_w8g64 (slots as affine_qmv_w4g64),
  * gpu-kernels/metal/quant/affine_qmv.metal:186-301,3027-3070. */
 int vpq_affine_qmv_w8g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                              void* y, int64_t K, int64_t N, int64_t M, void* stream);
+
+/* Decode GEMV over 4-bit group-32 weights (scales / biases [N, K/32]): GGUF Q4_0 repacks. The
+ * small-batch kernel with the accumulator columns = (row of x, group 0..3 of a 128-k tile): up to
+ * two rows of x share one stream of the weights. K % 32 == 0, K <= 32768. Replaces affine_qmv_w4g32
+ * (slots as affine_qmv_w4g64), gpu-kernels/metal/quant/affine_qmv.metal:303-320. */
+int vpq_affine_qmv_w4g32_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
                               void* y, int64_t K, int64_t N, int64_t M, void* stream);
 
 /* Small-batch decode GEMV: the M rows of x (M = 2..8: decode of several branches, MTP verify)

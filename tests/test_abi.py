@@ -50,6 +50,7 @@ def test_function_table_uses_reference_names(vpq):
                            ("affine_qmv_bf16", "affine_qmv_swiglu_w4g64"),
                            ("affine_qmv_bf16", "affine_qmv_qkv_w4g64"),
                            ("affine_qmv_bf16", "affine_qmv_w8g64"),
+                           ("affine_qmv_bf16", "affine_qmv_w4g32"),
                            ("affine_qmm_steel_bf16", "affine_qmm_steel_w8g64"),
                            ("affine_qmv_bf16", "affine_qmv_batch_w4g64"),
                            ("affine_qmv_bf16", "affine_qmv_batch4_w4g64"),

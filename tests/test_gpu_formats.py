@@ -175,3 +175,50 @@ def test_gemm_tile_dequant_is_bit_identical_to_the_dequantizer(vpq, oracle_mod, 
     y = (vpq.ops.qmm if bits == 4 else vpq.ops.qmm_w8)(*d)
     want = oracle_mod.dequant_bf16_any(codes, s, b, bits, 64)
     assert np.array_equal(bits16(y), want.T)
+
+
+def _g32_reference(oracle_mod, codes, s_bf16, b_bf16, x_bits, mode="fast"):
+    """fp32 dequantise-then-matmul oracle for w4 g32: deq = s * nibble + b in f32, group 32."""
+    N, Kw = codes.shape
+    K = Kw * 8
+    q = np.zeros((N, K), np.float32)
+    for i in range(8):
+        q[:, i::8] = ((codes >> np.uint32(4 * i)) & np.uint32(0xF)).astype(np.float32)
+    s = np.repeat(synth.bf16_bits_to_f32(s_bf16), 32, axis=1)
+    b = np.repeat(synth.bf16_bits_to_f32(b_bf16), 32, axis=1)
+    return oracle_mod.matmul_f32(x_bits, (s * q + b).astype(np.float32), mode)
+
+
+@pytest.mark.parametrize("K,N,M", [(4096, 4096, 1), (4096, 1024, 2), (8192, 512, 3), (12288, 256, 2), (3840, 40, 1),
+                                   (32, 8, 1), (96, 33, 2), (1152, 4099, 1)])
+def test_qmv_w4g32_matches_fp32_oracle(vpq, oracle_mod, K, N, M):
+    """affine_qmv_w4g32 (affine_qmv.metal:303-320): the quantizer's group-32 output through the GEMV,
+    against the fp32 dequantise-then-matmul oracle and the bit-exact group-32 dequantizer."""
+    wb = synth.f32_to_bf16_bits(synth.weight_f32(N, K, synth.seed_for("g32", K, N)))
+    codes, s16, b16 = oracle_mod.quant(wb, 4, 32)
+    s, b = oracle_mod.f16_to_bf16(s16), oracle_mod.f16_to_bf16(b16)
+    x = synth.activations_bf16(M, K, synth.seed_for("g32x", K, N))
+    d = (to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16), to_dev(x, torch.bfloat16))
+    y = vpq.ops.qmv_g32(*d)
+    assert y.shape == (M, N)
+    assert vpq.ops.device_status() == 0
+    e = oracle_mod.err_metrics(y.float().cpu().numpy(), _g32_reference(oracle_mod, codes, s, b, x))
+    assert e["rel_l2"] < 1e-2 and e["max_rel_rms"] < 1e-2 and e["max_rel_1e2"] < 1e-2, e
+
+
+def test_qmv_w4g32_f32_accuracy_and_name(vpq, oracle_mod):
+    N, K = 256, 2048
+    rng = np.random.default_rng(31)
+    codes = rng.integers(0, 2**32, (N, K // 8), dtype=np.uint32)
+    s = synth.f32_to_bf16_bits((rng.random((N, K // 32)) * 0.015 + 0.005).astype(np.float32))
+    b = synth.f32_to_bf16_bits((rng.random((N, K // 32)) * 0.2 - 0.1).astype(np.float32))
+    x = synth.activations_bf16(2, K, 32)
+    d = (to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16), to_dev(x, torch.bfloat16))
+    y = vpq.ops.qmv_g32(*d)
+    ref = _g32_reference(oracle_mod, codes, s, b, x, "f64")
+    want = synth.f32_to_bf16_bits(ref.astype(np.float32))
+    ulps = np.abs(bits16(y).astype(np.int64) - want.astype(np.int64))
+    assert (ulps <= 1).mean() > 0.999
+    y2 = torch.empty_like(y)
+    vpq.ops.dispatch(vpq.ops.function("affine_qmv_bf16", "affine_qmv_w4g32"), list(d) + [y2], K=K, N=N, M=2)
+    assert torch.equal(y, y2)

@@ -28,6 +28,7 @@ SYMBOLS = [
     ("vpq_affine_dequant_bf16", _i, [_vp, _vp, _vp, _vp, _i64, _i64, _i, _i, _vp]),
     ("vpq_affine_qmm_swiglu_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     ("vpq_affine_qmm_w8g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    ("vpq_affine_qmv_w4g32_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     ("vpq_affine_qmv_w8g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     ("vpq_affine_qmv_batch_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     ("vpq_affine_qmv_w4g64_bf16_add", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp]),

@@ -40,8 +40,9 @@ constexpr int kThreads = kConsThreads + 32;  // + producer warp
 constexpr int kBoxBytes = 16 * 128;          // one TMA box: 16 rows x 128 bytes (256 k)
 constexpr int kBoxesPerStage = 8;            // a stage spans 2048 k
 constexpr int kStageW = kBoxesPerStage * kBoxBytes;
-constexpr int kStageSZ = 2 * 16 * 64;        // scales + biases of the span: 2 x [16 rows x 32 groups]
-constexpr int kStageBytes = kStageW + kStageSZ;
+// scales + biases of a stage's span: 2 x [16 rows x 2048 / GROUP groups] bf16
+template <int GROUP> constexpr int stage_sz() { return 2 * 16 * (2048 / GROUP) * 2; }
+template <int GROUP> constexpr int stage_bytes() { return kStageW + stage_sz<GROUP>(); }
 constexpr int kMaxStages = 6;
 constexpr int kRedSlots = 8;                 // row tiles whose cross-warp sums may be pending
 constexpr int kMaxRows = 4;                  // rows of x per pass
@@ -89,8 +90,17 @@ struct alignas(64) BatchProblem {
   int scales_tma;
 };
 
+// GROUP = 64: columns = (row of x 0..3, group parity). GROUP = 32 (the reference's affine_qmv_w4g32,
+// gpu-kernels/metal/quant/affine_qmv.metal:303-320: GGUF Q4_0 repacks): a k tile of 128 has four
+// groups and a lane's 32-nibble chunk is exactly one of them, so columns = (row of x 0..1, group
+// 0..3); lanes t and t ^ 1 of a quad then hold the two halves of a row's sum.
+template <int GROUP>
 __global__ void __launch_bounds__(kThreads, 2)
-affine_qmv_batch_w4g64_kernel(const __grid_constant__ BatchProblem P, int stages, int cap_kt) {
+affine_qmv_batch_w4_kernel(const __grid_constant__ BatchProblem P, int stages, int cap_kt) {
+  constexpr int GPT = 128 / GROUP;            // groups per k tile
+  constexpr int GPS = 2048 / GROUP;           // groups per stage
+  constexpr int kStageSZ = stage_sz<GROUP>();
+  constexpr int kStageBytes = stage_bytes<GROUP>();
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t raw = smem_u32(smem_dyn);
   const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled boxes need 1024-byte alignment
@@ -101,7 +111,7 @@ affine_qmv_batch_w4g64_kernel(const __grid_constant__ BatchProblem P, int stages
   uint4* xperm = reinterpret_cast<uint4*>(p0);                   // [M][cap_kt][4 quarters][4 t] x 16 B
   uint4* zero256 = xperm + (size_t)M * cap_kt * 16;              // 320 bytes of zeros (also read as float2 zeros)
   float2* xg = reinterpret_cast<float2*>(zero256 + 20);          // [M][2*cap_kt] per group: surplus, sum of x
-  float* unscale = reinterpret_cast<float*>(xg + (size_t)M * 2 * cap_kt);  // [kMaxRows]
+  float* unscale = reinterpret_cast<float*>(xg + (size_t)M * GPT * cap_kt);  // [kMaxRows]
   float* red = unscale + kMaxRows;                               // [kRedSlots][kConsWarps][kMaxRows][16]
   uint32_t* red_cnt = reinterpret_cast<uint32_t*>(red + kRedSlots * kConsWarps * kMaxRows * 16);
   uint32_t* amax_buf = red_cnt + kRedSlots;                      // [kConsWarps][kMaxRows]
@@ -155,8 +165,8 @@ affine_qmv_batch_w4g64_kernel(const __grid_constant__ BatchProblem P, int stages
             tma_load_2d(dst + b * kBoxBytes, &P.mw, bar_full(s), (st * kBoxesPerStage + b) * 32, tile * 16);
           }
           if (sz_tma) {
-            tma_load_2d(dst + kStageW, &P.ms, bar_full(s), st * 32, tile * 16);
-            tma_load_2d(dst + kStageW + kStageSZ / 2, &P.mz, bar_full(s), st * 32, tile * 16);
+            tma_load_2d(dst + kStageW, &P.ms, bar_full(s), st * GPS, tile * 16);
+            tma_load_2d(dst + kStageW + kStageSZ / 2, &P.mz, bar_full(s), st * GPS, tile * 16);
           }
         }
       }
@@ -248,12 +258,12 @@ affine_qmv_batch_w4g64_kernel(const __grid_constant__ BatchProblem P, int stages
       const int kt = ci >> 4, tt = (ci >> 2) & 3, q = ci & 3;
       if (live) { xperm[(size_t)m * cap_kt * 16 + (kt * 4 + q) * 4 + tt] = out; }
 #pragma unroll
-      for (int off = 1; off < 8; off <<= 1) {
+      for (int off = 1; off < GROUP / 8; off <<= 1) {
         se += __shfl_xor_sync(0xffffffffu, se, off);
         so += __shfl_xor_sync(0xffffffffu, so, off);
       }
-      if (live && (ci & 7) == 0) {
-        xg[(size_t)m * 2 * cap_kt + (ci >> 3)] = make_float2(__fmaf_rn(1024.0f, se, 64.0f * so), se + so);
+      if (live && (ci % (GROUP / 8)) == 0) {
+        xg[(size_t)m * GPT * cap_kt + ci / (GROUP / 8)] = make_float2(__fmaf_rn(1024.0f, se, 64.0f * so), se + so);
       }
     };
 #pragma unroll
@@ -271,22 +281,28 @@ affine_qmv_batch_w4g64_kernel(const __grid_constant__ BatchProblem P, int stages
   // the k tile): those lanes read that row's fragments where their chunk t lies in that group
   // (chunks 0, 1 -> first group, 2, 3 -> second) and zeros otherwise, from a block laid out like
   // one k tile of xperm (+4: its quarter q sits in the banks quarter q+1 of the data uses).
-  const int col_row = g >> 1;
-  const bool real = col_row < M && ((g & 1) == (t >> 1));
+  const int col_row = g / GPT;                        // row of x this lane's column stands for
+  const int chunk_group = GPT == 2 ? (t >> 1) : t;    // group of the k tile this lane's chunk lies in
+  const bool real = col_row < M && ((g % GPT) == chunk_group);
   const uint4* xb_base = real ? xperm + (size_t)col_row * cap_kt * 16 + t : zero256 + 4;
   const int xb_kt = real ? 16 : 0;
-  // Lane t of a quad folds row t of x: its accumulator registers are columns 2t, 2t+1.
-  const bool row_live = t < M;
-  const float2* xg_row = row_live ? xg + (size_t)t * 2 * cap_kt : reinterpret_cast<const float2*>(zero256);
+  // Lane t of a quad folds its accumulator columns 2t, 2t+1: row t of x, both groups (GROUP 64);
+  // row t >> 1 of x, groups 2 (t & 1) and 2 (t & 1) + 1 of the k tile (GROUP 32).
+  const int m_lane = GPT == 2 ? t : (t >> 1);
+  const int gbase = GPT == 2 ? 0 : 2 * (t & 1);
+  const bool row_live = m_lane < M;
+  const float2* xg_row = row_live ? xg + (size_t)m_lane * GPT * cap_kt : reinterpret_cast<const float2*>(zero256);
   const int xg_step = row_live ? 1 : 0;
 
   // byte offsets of this lane's two 16-byte reads inside its box, per half (k tile) of the box
   const uint32_t off_h0 = (uint32_t)rho * 128u + (uint32_t)(((0 + t) ^ rho) << 4);
   const uint32_t off_h1 = (uint32_t)rho * 128u + (uint32_t)(((4 + t) ^ rho) << 4);
-  // 8 bytes = the 4 groups of this warp's box, row rho, in the stage's scales (biases: + kStageSZ / 2)
-  const uint32_t sz_off = (uint32_t)kStageW + (uint32_t)rho * 64u + (uint32_t)warp * 8u;
+  // this lane's two groups of the box's first k tile, row rho, in the stage's scales (the second
+  // k tile: + 2 GPT bytes; row rho + 8: + 8 rows; biases: + kStageSZ / 2)
+  const uint32_t sz_off = (uint32_t)kStageW + (uint32_t)rho * (GPS * 2) + (uint32_t)(warp * 2 * GPT + gbase) * 2u;
+  constexpr uint32_t kRow8 = 8u * GPS * 2u;
   const bool sz_tma = P.scales_tma != 0;
-  const int G = K >> 6;
+  const int G = K / GROUP;
 
   uint32_t tile_seq = 0, ph = 0;
   int s = 0;
@@ -306,22 +322,28 @@ affine_qmv_batch_w4g64_kernel(const __grid_constant__ BatchProblem P, int stages
         const uint4 rb0 = *reinterpret_cast<const uint4*>(box + off_h0 + 1024);
         const uint4 ra1 = *reinterpret_cast<const uint4*>(box + off_h1);
         const uint4 rb1 = *reinterpret_cast<const uint4*>(box + off_h1 + 1024);
-        uint2 sa, sb2, za, zb;  // scales / biases of the box's 4 groups, rows rho and rho + 8
+        uint32_t sa[2], sb2[2], za[2], zb[2];  // per k tile: this lane's two groups' scales / biases, rows rho, rho + 8
         if (sz_tma) {
-          sa = *reinterpret_cast<const uint2*>(sb + sz_off);
-          sb2 = *reinterpret_cast<const uint2*>(sb + sz_off + 512);
-          za = *reinterpret_cast<const uint2*>(sb + sz_off + kStageSZ / 2);
-          zb = *reinterpret_cast<const uint2*>(sb + sz_off + kStageSZ / 2 + 512);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const unsigned char* q = sb + sz_off + h * (2 * GPT);
+            sa[h] = *reinterpret_cast<const uint32_t*>(q);
+            sb2[h] = *reinterpret_cast<const uint32_t*>(q + kRow8);
+            za[h] = *reinterpret_cast<const uint32_t*>(q + kStageSZ / 2);
+            zb[h] = *reinterpret_cast<const uint32_t*>(q + kStageSZ / 2 + kRow8);
+          }
         } else {
           // clamped onto valid data: a clamped group meets x == 0, a clamped row is never stored
           const int64_t r_a = min(tile * 16 + rho, N - 1), r_b = min(tile * 16 + rho + 8, N - 1);
-          const int g0 = min(2 * kt0, G - 1), g1 = min(2 * kt0 + 1, G - 1);
-          const int g2 = min(2 * kt0 + 2, G - 1), g3 = min(2 * kt0 + 3, G - 1);
           auto pair = [](const uint16_t* p, int64_t i, int64_t j) { return ldg_nc_u16(p + i) | (ldg_nc_u16(p + j) << 16); };
-          sa = make_uint2(pair(P.scales, r_a * G + g0, r_a * G + g1), pair(P.scales, r_a * G + g2, r_a * G + g3));
-          sb2 = make_uint2(pair(P.scales, r_b * G + g0, r_b * G + g1), pair(P.scales, r_b * G + g2, r_b * G + g3));
-          za = make_uint2(pair(P.biases, r_a * G + g0, r_a * G + g1), pair(P.biases, r_a * G + g2, r_a * G + g3));
-          zb = make_uint2(pair(P.biases, r_b * G + g0, r_b * G + g1), pair(P.biases, r_b * G + g2, r_b * G + g3));
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int g0 = min((kt0 + h) * GPT + gbase, G - 1), g1 = min((kt0 + h) * GPT + gbase + 1, G - 1);
+            sa[h] = pair(P.scales, r_a * G + g0, r_a * G + g1);
+            sb2[h] = pair(P.scales, r_b * G + g0, r_b * G + g1);
+            za[h] = pair(P.biases, r_a * G + g0, r_a * G + g1);
+            zb[h] = pair(P.biases, r_b * G + g0, r_b * G + g1);
+          }
         }
         const int kt1 = kt0 + 1;
         float c0[4], d0[4], c1[4], d1[4];  // four independent accumulator chains
@@ -348,26 +370,26 @@ affine_qmv_batch_w4g64_kernel(const __grid_constant__ BatchProblem P, int stages
           }
         }
         // [0] = (W row rho, first group) [1] = (rho, second) [2] = (rho + 8, first) [3] = (rho + 8, second)
-        const float4 xs0 = *reinterpret_cast<const float4*>(xg_row + 2 * kt0 * xg_step);  // groups 2 kt0, 2 kt0 + 1
-        const float4 xs1 = *reinterpret_cast<const float4*>(xg_row + 2 * kt1 * xg_step);
+        const float4 xs0 = *reinterpret_cast<const float4*>(xg_row + (kt0 * GPT + gbase) * xg_step);  // this lane's two groups
+        const float4 xs1 = *reinterpret_cast<const float4*>(xg_row + (kt1 * GPT + gbase) * xg_step);
         auto lo = [](uint32_t v) { return __uint_as_float(v << 16); };
         auto hi = [](uint32_t v) { return __uint_as_float(v & 0xffff0000u); };
-        res_a = __fmaf_rn(lo(sa.x), (c0[0] + d0[0]) - xs0.x, res_a);
-        res_a = __fmaf_rn(lo(za.x), xs0.y, res_a);
-        res_a = __fmaf_rn(hi(sa.x), (c0[1] + d0[1]) - xs0.z, res_a);
-        res_a = __fmaf_rn(hi(za.x), xs0.w, res_a);
-        res_a = __fmaf_rn(lo(sa.y), (c1[0] + d1[0]) - xs1.x, res_a);
-        res_a = __fmaf_rn(lo(za.y), xs1.y, res_a);
-        res_a = __fmaf_rn(hi(sa.y), (c1[1] + d1[1]) - xs1.z, res_a);
-        res_a = __fmaf_rn(hi(za.y), xs1.w, res_a);
-        res_b = __fmaf_rn(lo(sb2.x), (c0[2] + d0[2]) - xs0.x, res_b);
-        res_b = __fmaf_rn(lo(zb.x), xs0.y, res_b);
-        res_b = __fmaf_rn(hi(sb2.x), (c0[3] + d0[3]) - xs0.z, res_b);
-        res_b = __fmaf_rn(hi(zb.x), xs0.w, res_b);
-        res_b = __fmaf_rn(lo(sb2.y), (c1[2] + d1[2]) - xs1.x, res_b);
-        res_b = __fmaf_rn(lo(zb.y), xs1.y, res_b);
-        res_b = __fmaf_rn(hi(sb2.y), (c1[3] + d1[3]) - xs1.z, res_b);
-        res_b = __fmaf_rn(hi(zb.y), xs1.w, res_b);
+        res_a = __fmaf_rn(lo(sa[0]), (c0[0] + d0[0]) - xs0.x, res_a);
+        res_a = __fmaf_rn(lo(za[0]), xs0.y, res_a);
+        res_a = __fmaf_rn(hi(sa[0]), (c0[1] + d0[1]) - xs0.z, res_a);
+        res_a = __fmaf_rn(hi(za[0]), xs0.w, res_a);
+        res_a = __fmaf_rn(lo(sa[1]), (c1[0] + d1[0]) - xs1.x, res_a);
+        res_a = __fmaf_rn(lo(za[1]), xs1.y, res_a);
+        res_a = __fmaf_rn(hi(sa[1]), (c1[1] + d1[1]) - xs1.z, res_a);
+        res_a = __fmaf_rn(hi(za[1]), xs1.w, res_a);
+        res_b = __fmaf_rn(lo(sb2[0]), (c0[2] + d0[2]) - xs0.x, res_b);
+        res_b = __fmaf_rn(lo(zb[0]), xs0.y, res_b);
+        res_b = __fmaf_rn(hi(sb2[0]), (c0[3] + d0[3]) - xs0.z, res_b);
+        res_b = __fmaf_rn(hi(zb[0]), xs0.w, res_b);
+        res_b = __fmaf_rn(lo(sb2[1]), (c1[2] + d1[2]) - xs1.x, res_b);
+        res_b = __fmaf_rn(lo(zb[1]), xs1.y, res_b);
+        res_b = __fmaf_rn(hi(sb2[1]), (c1[3] + d1[3]) - xs1.z, res_b);
+        res_b = __fmaf_rn(hi(zb[1]), xs1.w, res_b);
       }
       __syncwarp();
       if (lane == 0) { mbar_arrive(bar_empty(s)); }  // this warp's part of the stage is in registers
@@ -381,10 +403,16 @@ affine_qmv_batch_w4g64_kernel(const __grid_constant__ BatchProblem P, int stages
     // warp that posts last adds them in warp order (the result does not depend on arrival order)
     // and stores. The ring of kRedSlots tiles is deeper than a warp can run ahead.
     const int slot = tile_seq % kRedSlots;
-    float* mine = red + ((size_t)(slot * kConsWarps + warp) * kMaxRows + t) * 16;
-    const float us = unscale[t];
-    mine[rho] = res_a * us;
-    mine[rho + 8] = res_b * us;
+    if (GPT == 4) {  // lanes t and t ^ 1 hold the two halves (groups 0 1 / 2 3 of every k tile) of one row of x
+      res_a += __shfl_xor_sync(0xffffffffu, res_a, 1);
+      res_b += __shfl_xor_sync(0xffffffffu, res_b, 1);
+    }
+    if (GPT == 2 || (t & 1) == 0) {
+      float* mine = red + ((size_t)(slot * kConsWarps + warp) * kMaxRows + m_lane) * 16;
+      const float us = unscale[m_lane];
+      mine[rho] = res_a * us;
+      mine[rho + 8] = res_b * us;
+    }
     __syncwarp();
     uint32_t last = 0;
     if (lane == 0) {
@@ -412,19 +440,105 @@ affine_qmv_batch_w4g64_kernel(const __grid_constant__ BatchProblem P, int stages
 }
 
 // ------------------------------------------------------------------ host side
+template <int GROUP>
 size_t fixed_smem(int rows, int cap_kt) {
-  return 1024 /*alignment slack*/ + (size_t)rows * cap_kt * 256 + 320 + (size_t)rows * 2 * cap_kt * 8 + kMaxRows * 4 +
-         (size_t)kRedSlots * kConsWarps * kMaxRows * 16 * 4 + kRedSlots * 4 + kConsWarps * kMaxRows * 4 +
-         2 * kMaxStages * 8 + 16;
+  return 1024 /*alignment slack*/ + (size_t)rows * cap_kt * 256 + 320 + (size_t)rows * (128 / GROUP) * cap_kt * 8 +
+         kMaxRows * 4 + (size_t)kRedSlots * kConsWarps * kMaxRows * 16 * 4 + kRedSlots * 4 +
+         kConsWarps * kMaxRows * 4 + 2 * kMaxStages * 8 + 16;
 }
 constexpr size_t kSmemBudget = 112 * 1024;  // two CTAs per SM
 
 // Rows of x one pass can hold next to at least three ring stages (with fewer the stream stalls
-// and M serial GEMVs are faster); 1 = use the M = 1 kernel.
+// and M serial GEMVs are faster); at most 4 (group 64) or 2 (group 32: four groups per k tile
+// take the accumulator columns of two rows).
+template <int GROUP>
 int rows_per_pass(int cap_kt) {
-  int rows = kMaxRows;
-  while (rows > 1 && fixed_smem(rows, cap_kt) + 3 * (size_t)kStageBytes > kSmemBudget) { --rows; }
+  int rows = GROUP == 64 ? kMaxRows : 2;
+  while (rows > 1 && fixed_smem<GROUP>(rows, cap_kt) + 3 * (size_t)stage_bytes<GROUP>() > kSmemBudget) { --rows; }
   return rows;
+}
+
+// Passes of `per_pass` rows over one weight stream each. min_rows: the fewest rows this kernel
+// takes itself (group 64 hands single rows to the exact M = 1 kernel through `single`).
+template <int GROUP>
+int launch_batch(const char* who, const uint32_t* w, const void* scales, const void* biases, const void* x, void* y,
+                 int64_t K, int64_t N, int64_t M, int per_pass, cudaStream_t st,
+                 int (*single)(const uint32_t*, const void*, const void*, const void*, void*, int64_t, int64_t, int64_t,
+                               void*)) {
+  const int cap_kt = (int)((K + 255) / 256) * 2;
+  BatchProblem p;
+  std::memset(&p, 0, sizeof(p));
+  if (int rc = make_map_2d(&p.mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w, (uint64_t)(K / 8), (uint64_t)N, 32, 16,
+                           CU_TENSOR_MAP_SWIZZLE_128B, "w")) {
+    return rc;
+  }
+  constexpr int GPS = 2048 / GROUP;
+  // scale / bias rows as TMA boxes: pitch and base multiples of 16 bytes
+  p.scales_tma = ((K / GROUP) % 8 == 0 && aligned16(scales) && aligned16(biases)) ? 1 : 0;
+  if (p.scales_tma) {
+    if (int rc = make_map_2d(&p.ms, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, (uint64_t)(K / GROUP), (uint64_t)N, GPS,
+                             16, CU_TENSOR_MAP_SWIZZLE_NONE, "scales")) {
+      return rc;
+    }
+    if (int rc = make_map_2d(&p.mz, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, biases, (uint64_t)(K / GROUP), (uint64_t)N, GPS,
+                             16, CU_TENSOR_MAP_SWIZZLE_NONE, "biases")) {
+      return rc;
+    }
+  }
+  p.scales = static_cast<const uint16_t*>(scales);
+  p.biases = static_cast<const uint16_t*>(biases);
+  p.K = (int)K;
+  p.N = (int)N;
+  p.row_tiles = (int)((N + 15) / 16);
+  auto kern = affine_qmv_batch_w4_kernel<GROUP>;
+  for (int64_t m0 = 0; m0 < M; m0 += per_pass) {
+    const int rows = (int)((M - m0) < per_pass ? (M - m0) : per_pass);
+    p.x = static_cast<const uint16_t*>(x) + m0 * K;
+    p.y = static_cast<__nv_bfloat16*>(y) + m0 * N;
+    p.M = rows;
+    if (rows == 1 && single) {  // a single row left over: the exact M = 1 kernel
+      if (int rc = single(w, scales, biases, p.x, p.y, K, N, 1, st)) { return rc; }
+      continue;
+    }
+    const size_t fixed = fixed_smem<GROUP>(rows, cap_kt);
+    int stages = fixed < kSmemBudget ? (int)((kSmemBudget - fixed) / stage_bytes<GROUP>()) : 0;
+    if (stages > kMaxStages) { stages = kMaxStages; }
+    if (stages < 2) { return fail(VPQ_ERR_UNSUPPORTED, "%s: K=%lld does not fit in shared memory", who, (long long)K); }
+    const size_t smem = fixed + (size_t)stages * stage_bytes<GROUP>();
+    static int granted[64] = {};
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), granted, smem)) { return rc; }
+    const int cap = 2 * num_sms();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(p.row_tiles < cap ? p.row_tiles : cap), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    VPQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p, stages, cap_kt));
+  }
+  return VPQ_OK;
+}
+
+int check_batch_args(const char* who, const void* w, const void* scales, const void* biases, const void* x,
+                     const void* y, int64_t K, int64_t N, int64_t M, int group) {
+  if (!w || !scales || !biases || !x || !y) { return fail(VPQ_ERR_INVALID_ARG, "%s: null pointer", who); }
+  if (K <= 0 || N <= 0 || M <= 0 || (K % group) != 0 || (K % 8) != 0) {
+    return fail(VPQ_ERR_INVALID_ARG, "%s: need K>0, N>0, M>0, K%%%d==0 (K=%lld N=%lld M=%lld)", who, group,
+                (long long)K, (long long)N, (long long)M);
+  }
+  if (K > 32768 || N > (1 << 30) || M > 65535) {
+    return fail(VPQ_ERR_UNSUPPORTED, "%s: K<=32768, M<=65535 supported (K=%lld M=%lld)", who, (long long)K,
+                (long long)M);
+  }
+  if (!aligned16(w) || !aligned16(x) || (reinterpret_cast<uintptr_t>(scales) & 1) ||
+      (reinterpret_cast<uintptr_t>(biases) & 1) || (reinterpret_cast<uintptr_t>(y) & 1)) {
+    return fail(VPQ_ERR_ALIGNMENT, "%s: w and x must be 16-byte aligned", who);
+  }
+  return VPQ_OK;
 }
 
 }  // namespace
@@ -449,77 +563,22 @@ extern "C" int vpq_affine_qmv_batch_w4g64_bf16(const uint32_t* w, const void* sc
                                                const void* x, void* y, int64_t K, int64_t N, int64_t M,
                                                void* stream) {
   clear_error();
-  if (!w || !scales || !biases || !x || !y) { return fail(VPQ_ERR_INVALID_ARG, "affine_qmv_batch_w4g64: null pointer"); }
-  if (K <= 0 || N <= 0 || M <= 0 || (K % 64) != 0) {
-    return fail(VPQ_ERR_INVALID_ARG, "affine_qmv_batch_w4g64: need K>0, N>0, M>0, K%%64==0 (K=%lld N=%lld M=%lld)",
-                (long long)K, (long long)N, (long long)M);
-  }
-  if (K > 32768 || N > (1 << 30) || M > 65535) {
-    return fail(VPQ_ERR_UNSUPPORTED, "affine_qmv_batch_w4g64: K<=32768, M<=65535 supported (K=%lld M=%lld)",
-                (long long)K, (long long)M);
-  }
-  if (!aligned16(w) || !aligned16(x) || (reinterpret_cast<uintptr_t>(scales) & 1) ||
-      (reinterpret_cast<uintptr_t>(biases) & 1) || (reinterpret_cast<uintptr_t>(y) & 1) || (K % 8) != 0) {
-    return fail(VPQ_ERR_ALIGNMENT, "affine_qmv_batch_w4g64: w and x must be 16-byte aligned");
-  }
+  if (int rc = check_batch_args("affine_qmv_batch_w4g64", w, scales, biases, x, y, K, N, M, 64)) { return rc; }
   if (int rc = require_sm100()) { return rc; }
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int cap_kt = (int)((K + 255) / 256) * 2;
-  const int per_pass = rows_per_pass(cap_kt);
+  const int per_pass = rows_per_pass<64>((int)((K + 255) / 256) * 2);
   if (per_pass < 2 || M == 1) {  // long rows (K > 8192) do not fit twice in shared memory: one row at a time
     return vpq_affine_qmv_w4g64_bf16(w, scales, biases, x, y, K, N, M, stream);
   }
-  BatchProblem p;
-  std::memset(&p, 0, sizeof(p));
-  if (int rc = make_map_2d(&p.mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w, (uint64_t)(K / 8), (uint64_t)N, 32, 16,
-                           CU_TENSOR_MAP_SWIZZLE_128B, "w")) {
-    return rc;
-  }
-  p.scales_tma = ((K % 512) == 0 && aligned16(scales) && aligned16(biases)) ? 1 : 0;
-  if (p.scales_tma) {
-    if (int rc = make_map_2d(&p.ms, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, (uint64_t)(K / 64), (uint64_t)N, 32, 16,
-                             CU_TENSOR_MAP_SWIZZLE_NONE, "scales")) {
-      return rc;
-    }
-    if (int rc = make_map_2d(&p.mz, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, biases, (uint64_t)(K / 64), (uint64_t)N, 32, 16,
-                             CU_TENSOR_MAP_SWIZZLE_NONE, "biases")) {
-      return rc;
-    }
-  }
-  p.scales = static_cast<const uint16_t*>(scales);
-  p.biases = static_cast<const uint16_t*>(biases);
-  p.K = (int)K;
-  p.N = (int)N;
-  p.row_tiles = (int)((N + 15) / 16);
-  auto kern = affine_qmv_batch_w4g64_kernel;
-  for (int64_t m0 = 0; m0 < M; m0 += per_pass) {
-    const int rows = (int)((M - m0) < per_pass ? (M - m0) : per_pass);
-    p.x = static_cast<const uint16_t*>(x) + m0 * K;
-    p.y = static_cast<__nv_bfloat16*>(y) + m0 * N;
-    p.M = rows;
-    const size_t fixed = fixed_smem(rows, cap_kt);
-    int stages = (int)((kSmemBudget - fixed) / kStageBytes);
-    if (stages > kMaxStages) { stages = kMaxStages; }
-    if (stages < 2) { return fail(VPQ_ERR_UNSUPPORTED, "affine_qmv_batch_w4g64: K=%lld does not fit", (long long)K); }
-    if (rows == 1) {  // a single row left over: the exact M = 1 kernel
-      if (int rc = vpq_affine_qmv_w4g64_bf16(w, scales, biases, p.x, p.y, K, N, 1, stream)) { return rc; }
-      continue;
-    }
-    const size_t smem = fixed + (size_t)stages * kStageBytes;
-    static int granted[64] = {};
-    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), granted, smem)) { return rc; }
-    const int cap = 2 * num_sms();
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(p.row_tiles < cap ? p.row_tiles : cap), 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    VPQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p, stages, cap_kt));
-  }
-  return VPQ_OK;
+  return launch_batch<64>("affine_qmv_batch_w4g64", w, scales, biases, x, y, K, N, M, per_pass,
+                          static_cast<cudaStream_t>(stream), vpq_affine_qmv_w4g64_bf16);
+}
+
+extern "C" int vpq_affine_qmv_w4g32_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                                         void* y, int64_t K, int64_t N, int64_t M, void* stream) {
+  clear_error();
+  if (int rc = check_batch_args("affine_qmv_w4g32", w, scales, biases, x, y, K, N, M, 32)) { return rc; }
+  if (int rc = require_sm100()) { return rc; }
+  const int per_pass = rows_per_pass<32>((int)((K + 255) / 256) * 2);  // 2 rows per weight stream where they fit
+  return launch_batch<32>("affine_qmv_w4g32", w, scales, biases, x, y, K, N, M, per_pass,
+                          static_cast<cudaStream_t>(stream), nullptr);
 }

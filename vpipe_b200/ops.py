@@ -94,6 +94,19 @@ def qmv(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
     return out
 
 
+def qmv_g32(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
+    """GEMV over 4-bit group-32 weights, scales / biases [N, K/32] (vpq_affine_qmv_w4g32_bf16)."""
+    N, Kw = codes.shape
+    K = Kw * 8
+    M = x.numel() // K
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().vpq_affine_qmv_w4g32_bf16(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x), _ptr(out),
+                                              K, N, M, _stream(stream)))
+    return out
+
+
 def qmv_w8(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
     """GEMV over 8-bit group-64 weights, codes int32 [N, K/4] (vpq_affine_qmv_w8g64_bf16)."""
     N, Kw = codes.shape
