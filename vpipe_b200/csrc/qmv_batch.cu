@@ -1,4 +1,5 @@
-// qmv_batch.cu -- small-batch decode GEMV: M = 2..4 rows of x against one stream of the weights.
+// qmv_batch.cu -- small-batch decode GEMV: M = 2..4 rows of x against one stream of the weights
+// (group 64), and the group-32 GEMV (1..2 rows per stream), one kernel templated over the group size.
 //
 // y[m,n] = sum_k x[m,k] * (s[n,k/64] * q[n,k] + b[n,k/64]),  f32 accumulate, weights read once.
 // Replaces affine_qmv_batch_w4g64 / affine_qmv_batch4_w4g64 (qmv_batch_impl<T,64,4,MAXM>,
