@@ -123,6 +123,14 @@ int vpq_affine_qmv_swiglu_w4g64_bf16(const uint32_t* w, const void* scales, cons
 int vpq_affine_qmv_qkv_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
                                   void* q_out, void* k_out, void* v_out, int64_t K, int64_t q_rows,
                                   int64_t k_rows, int64_t v_rows, int64_t M, void* stream);
+/* _geglu: as _swiglu with gelu_pytorch_tanh on the gate (affine_qmv_geglu_w4g64,
+ * gpu-kernels/metal/quant/affine_qmv.metal:1352-1448). _gelu_mul: slot 7 of the reference kernel is
+ * `mul` [M, N]; y = gelu(bf16(sum)) * mul (affine_qmv_gelu_mul_w4g64, affine_qmv.metal:265-283,745-765). */
+int vpq_affine_qmv_geglu_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                                    void* y, int64_t K, int64_t N, int64_t M, void* stream);
+int vpq_affine_qmv_gelu_mul_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                                       void* y, int64_t K, int64_t N, int64_t M, const void* mul,
+                                       void* stream);
 
 /* Decode GEMV over 8-bit group-64 weights (w u32 [N, K/4], one byte per value): the 8-bit linears
  * of mixed-precision checkpoints. Exact integer tensor-core arithmetic as the 4-bit kernel, with
@@ -164,7 +172,7 @@ typedef struct vpq_linear_desc {
   /* Fused store, VPQ_EPILOGUE_*; zero-initialised descriptors store y = x W^T as is. */
   int32_t epilogue;
   int32_t reserved;
-  const void* aux;      /* ADD: residual [M, N]; QKV: the k output [M, k_rows] (written) */
+  const void* aux;      /* ADD: residual [M, N]; GELU_MUL: multiplier [M, N]; QKV: the k output [M, k_rows] (written) */
   void* y3;             /* QKV: the v output [M, N - q_rows - k_rows] */
   int64_t q_rows, k_rows;
 } vpq_linear_desc;
@@ -176,8 +184,19 @@ typedef struct vpq_linear_desc {
  *         y[j] = bf16(silu(sum[2j]) * sum[2j+1]), from the unrounded sums    affine_qmv_swiglu_w4g64,
  *         affine_qmv.metal:806-906
  * QKV     W is q | k | v row-concatenated; rows land in three buffers: y (q), aux (k), y3 (v)
- *         affine_qmv_qkv_w4g64, affine_qmv.metal:405-516 */
-enum { VPQ_EPILOGUE_NONE = 0, VPQ_EPILOGUE_ADD = 1, VPQ_EPILOGUE_SWIGLU = 2, VPQ_EPILOGUE_QKV = 3 };
+ *         affine_qmv_qkv_w4g64, affine_qmv.metal:405-516
+ * GEGLU   as SWIGLU with gelu(g) = 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) on the gate
+ *         affine_qmv_geglu_w4g64, affine_qmv.metal:1352-1448
+ * GELU_MUL y[n] = bf16(gelu(bf16(sum)) * mul[n])                 affine_qmv_gelu_mul_w4g64,
+ *         affine_qmv.metal:265-283,745-765 (Gemma per-layer-input gate) */
+enum {
+  VPQ_EPILOGUE_NONE = 0,
+  VPQ_EPILOGUE_ADD = 1,
+  VPQ_EPILOGUE_SWIGLU = 2,
+  VPQ_EPILOGUE_QKV = 3,
+  VPQ_EPILOGUE_GEGLU = 4,
+  VPQ_EPILOGUE_GELU_MUL = 5
+};
 int vpq_affine_qmv_w4g64_bf16_batch(const vpq_linear_desc* descs_host, int count, void* stream);
 
 /* A list of independent GEMVs run as ONE launch: the kernel walks the row tiles of all problems
@@ -238,6 +257,17 @@ int vpq_affine_qmm_swiglu_w4g64_bf16(const uint32_t* w, const void* scales, cons
  * affine_qmm_steel_w8g64[_bm64|_bm128], gpu-kernels/metal/quant/affine_qmm_steel.metal:1595-1675. */
 int vpq_affine_qmm_w8g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
                               void* y, int64_t K, int64_t N, int64_t M, void* stream);
+
+/* The other gated GEMMs, same slots and layout as the SwiGLU one: gelu_pytorch_tanh on the gate
+ * (affine_qmm_geglu_w4g64, gpu-kernels/metal/quant/affine_qmm_steel.metal:1451-1569), and both
+ * activations over 8-bit weights (affine_qmm_swiglu_w8g64, :1700-1790; affine_qmm_geglu_w8g64,
+ * :1864-1885). */
+int vpq_affine_qmm_geglu_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                                    void* y, int64_t K, int64_t N, int64_t M, void* stream);
+int vpq_affine_qmm_swiglu_w8g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                                     void* y, int64_t K, int64_t N, int64_t M, void* stream);
+int vpq_affine_qmm_geglu_w8g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                                    void* y, int64_t K, int64_t N, int64_t M, void* stream);
 
 /* Device-side status of the tensor-core kernels: every wait inside them is
  * bounded; one that gives up records where and the kernel returns. Reads the

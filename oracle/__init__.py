@@ -265,6 +265,30 @@ def fused_swiglu(y_f32: np.ndarray) -> np.ndarray:
     return narrow_f32_bf16(((g / (one + np.exp(-g))) * u).astype(np.float32))
 
 
+def gelu_tanh_f32(x: np.ndarray) -> np.ndarray:
+    """gelu_pytorch_tanh in f32: `0.5 x (1 + tanh(k0 (x + 0.044715 x^3)))`, k0 = sqrt(2 / pi)
+    (gpu-kernels/metal/ops/llm_elementwise.metal:388-407)."""
+    x = np.asarray(x, np.float32)
+    k0, c = np.float32(0.7978845608028654), np.float32(0.044715)
+    t = np.tanh((k0 * (x + c * x * x * x)).astype(np.float32)).astype(np.float32)
+    return (np.float32(0.5) * x * (np.float32(1.0) + t)).astype(np.float32)
+
+
+def fused_geglu(y_f32: np.ndarray) -> np.ndarray:
+    """GeGLU store over row-interleaved gate | up: gelu_tanh(g) * u in f32 from the unrounded sums,
+    rounded once (gpu-kernels/metal/quant/affine_qmv.metal:1421-1429,
+    quant/affine_qmm_steel.metal:1535-1545). Returns bf16 bits [M, N/2]."""
+    y = np.asarray(y_f32, np.float32)
+    return narrow_f32_bf16((gelu_tanh_f32(y[:, 0::2]) * y[:, 1::2]).astype(np.float32))
+
+
+def fused_gelu_mul(y_f32: np.ndarray, mul_bf16: np.ndarray) -> np.ndarray:
+    """Per-layer-input gate store: gelu_tanh of the bf16-rounded sum, times `mul`, rounded once
+    (gpu-kernels/metal/quant/affine_qmv.metal:271-282). Returns bf16 bits."""
+    y = bf16_to_f32(narrow_f32_bf16(np.asarray(y_f32, np.float32)))
+    return narrow_f32_bf16((gelu_tanh_f32(y) * bf16_to_f32(mul_bf16)).astype(np.float32))
+
+
 def qmv_kernel_order(codes, s_bf16, b_bf16, x_bf16) -> np.ndarray:
     codes = _c(codes, np.uint32)
     x = _c(x_bf16, np.uint16)

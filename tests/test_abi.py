@@ -59,6 +59,11 @@ def test_function_table_uses_reference_names(vpq):
                            ("affine_qmm_steel_bf16", "affine_qmm_steel_w4g64_bm128"),
                            ("affine_qmm_mma_bf16", "affine_qmm_mma_w4g64"),
                            ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64"),
+                           ("affine_qmm_steel_bf16", "affine_qmm_geglu_w4g64"),
+                           ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w8g64"),
+                           ("affine_qmm_steel_bf16", "affine_qmm_geglu_w8g64"),
+                           ("affine_qmv_bf16", "affine_qmv_geglu_w4g64"),
+                           ("affine_qmv_bf16", "affine_qmv_gelu_mul_w4g64"),
                            ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64_bm128"),
                            ("affine_dequant_bf16", "affine_dequant_w4g64"),
                            ("affine_dequant_bf16", "affine_quant_w4_g64"),
@@ -104,6 +109,11 @@ def test_argument_validation_happens_before_any_device_work(vpq):
     assert L.vpq_affine_qmv_qkv_w4g64_bf16(p16, p16, p16, p16, p16, p16, p16, 64, 0, 8, 8, 1, None) == INVALID
     assert L.vpq_affine_qmv_qkv_w4g64_bf16(p16, p16, p16, p16, p16, None, p16, 64, 8, 8, 8, 1, None) == INVALID
     assert L.vpq_affine_qmm_swiglu_w4g64_bf16(p16, p16, p16, p16, p16, 64, 9, 4, None) == INVALID
+    assert L.vpq_affine_qmm_geglu_w4g64_bf16(p16, p16, p16, p16, p16, 64, 9, 4, None) == INVALID
+    assert L.vpq_affine_qmm_swiglu_w8g64_bf16(p16, p16, p16, p16, p16, 96, 8, 4, None) == INVALID
+    assert L.vpq_affine_qmm_geglu_w8g64_bf16(None, p16, p16, p16, p16, 64, 8, 4, None) == INVALID
+    assert L.vpq_affine_qmv_geglu_w4g64_bf16(p16, p16, p16, p16, p16, 64, 7, 1, None) == INVALID
+    assert L.vpq_affine_qmv_gelu_mul_w4g64_bf16(p16, p16, p16, p16, p16, 64, 8, 1, None, None) == INVALID
     assert L.vpq_affine_qmv_batch_w4g64_bf16(p16, p16, p16, p16, None, 64, 8, 4, None) == INVALID
     assert L.vpq_affine_qmv_batch_w4g64_bf16(p16, p16, p16, p16 + 2, p16, 64, 8, 4, None) == ALIGN
     assert L.vpq_affine_qmv_w8g64_bf16(p16, p16, p16, p16, p16, 32768, 8, 1, None) == UNSUP

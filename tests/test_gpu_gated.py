@@ -1,0 +1,137 @@
+"""The other gated stores of the reference's quantized linears: GeGLU on the GEMV and the GEMM
+(affine_qmv_geglu_w4g64, affine_qmm_geglu_w4g64), the per-layer-input gate (affine_qmv_gelu_mul_w4g64)
+and both activations over 8-bit weights (affine_qmm_swiglu_w8g64, affine_qmm_geglu_w8g64). The
+activation is gelu_pytorch_tanh, restated in the oracle from ops/llm_elementwise.metal:388-407."""
+import numpy as np
+import pytest
+import torch
+
+from vpipe_b200 import synth
+
+from test_gpu_parity import TOL, dev, f32, quantized_linear, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _need_gpu(vpq):
+    assert torch.cuda.is_available(), "the -m gpu tests need a CUDA device"
+    torch.cuda.set_device(0)
+    yield
+    torch.cuda.synchronize()
+    assert vpq.ops.device_status() == 0
+
+
+def _linear(oracle_mod, N, K, M, seed):
+    codes, s, b = quantized_linear(oracle_mod, N, K, seed)
+    x = synth.activations_bf16(M, K, seed + 1)
+    ref = oracle_mod.linear_f32(codes, s, b, x, "fast")
+    d = (to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16), to_dev(x, torch.bfloat16))
+    return d, ref
+
+
+def _gelu_t(x):
+    return torch.nn.functional.gelu(x, approximate="tanh")
+
+
+@pytest.mark.parametrize("K,N,M", [(4096, 2 * 1024, 1), (2560, 2 * 10240, 1), (1088, 18, 2), (64, 2, 1)])
+def test_qmv_geglu(vpq, oracle_mod, K, N, M):
+    d, ref = _linear(oracle_mod, N, K, M, 8200 + N + K)
+    y = vpq.ops.qmv_geglu(*d)
+    assert y.shape == (M, N // 2)
+    want = synth.bf16_bits_to_f32(oracle_mod.fused_geglu(ref))
+    e = oracle_mod.err_metrics(f32(y), want)
+    assert e["rel_l2"] < TOL and e["max_rel_rms"] < TOL, e
+    plain = vpq.ops.qmv(*d).float()
+    approx = (_gelu_t(plain[:, 0::2]) * plain[:, 1::2]).cpu().numpy()
+    assert oracle_mod.err_metrics(f32(y), approx)["max_rel_rms"] < 2e-2
+
+
+@pytest.mark.parametrize("K,N,M", [(2560, 256, 1), (4096, 4096, 1), (320, 33, 2)])
+def test_qmv_gelu_mul(vpq, oracle_mod, K, N, M):
+    d, ref = _linear(oracle_mod, N, K, M, 8300 + N + K)
+    mul = synth.activations_bf16(M, N, 8301 + N)
+    dmul = to_dev(mul, torch.bfloat16)
+    y = vpq.ops.qmv_gelu_mul(*d, dmul)
+    want = synth.bf16_bits_to_f32(oracle_mod.fused_gelu_mul(ref, mul))
+    e = oracle_mod.err_metrics(f32(y), want)
+    assert e["rel_l2"] < TOL and e["max_rel_rms"] < TOL, e
+    # the activation reads the bf16-rounded GEMV result: a separate pass over y gives the same values
+    # up to the accuracy of tanh
+    plain = vpq.ops.qmv(*d).float()
+    sep = (_gelu_t(plain) * dmul.float()).to(torch.bfloat16)
+    diff = (y.float() - sep.float()).abs()
+    assert float((diff <= 2 ** -7 * sep.float().abs() + 1e-30).float().mean()) == 1.0
+    assert float((y == sep).float().mean()) > 0.99
+
+
+def test_gated_gemvs_inside_a_plan_and_by_name(vpq, oracle_mod):
+    ops = vpq.ops
+    K, N = 1024, 512
+    d, _ = _linear(oracle_mod, N, K, 1, 8400)
+    mul = to_dev(synth.activations_bf16(1, N, 8401), torch.bfloat16)
+    want_g = ops.qmv_geglu(*d)
+    want_m = ops.qmv_gelu_mul(*d, mul)
+    y_g = torch.zeros((1, N // 2), dtype=torch.bfloat16, device=dev())
+    y_m = torch.zeros((1, N), dtype=torch.bfloat16, device=dev())
+    ops.qmv_batch(ops.qmv_set([d + (y_g, {"epilogue": "geglu"}),
+                               d + (y_m, {"epilogue": "gelu_mul", "aux": mul})]))
+    assert torch.equal(y_g, want_g) and torch.equal(y_m, want_m)
+    y2 = torch.zeros_like(y_g)
+    ops.dispatch(ops.function("affine_qmv_bf16", "affine_qmv_geglu_w4g64"), list(d) + [y2], K=K, N=N)
+    assert torch.equal(y2, want_g)
+    y3 = torch.zeros_like(y_m)
+    ops.dispatch(ops.function("affine_qmv_bf16", "affine_qmv_gelu_mul_w4g64"),
+                 {0: d[0], 1: d[1], 2: d[2], 3: d[3], 4: y3, 7: mul}, K=K, N=N)
+    assert torch.equal(y3, want_m)
+
+
+def _w8_linear(oracle_mod, N, K, M, seed):
+    wb = synth.f32_to_bf16_bits(synth.weight_f32(N, K, seed))
+    codes, s16, b16 = oracle_mod.quant(wb, 8, 64)
+    s, b = oracle_mod.f16_to_bf16(s16), oracle_mod.f16_to_bf16(b16)
+    x = synth.activations_bf16(M, K, seed + 1)
+    d = (to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16), to_dev(x, torch.bfloat16))
+    return (codes, s, b, x), d
+
+
+@pytest.mark.parametrize("bits,act", [(4, "geglu"), (8, "swiglu"), (8, "geglu")])
+@pytest.mark.parametrize("M,K,N", [(256, 512, 512), (300, 1024, 154), (129, 64, 2), (2048, 2560, 2 * 1024)])
+def test_qmm_gated(vpq, oracle_mod, bits, act, M, K, N):
+    """With the same bf16 W the only difference from the oracle is the f32 summation order; the
+    store applies the activation to the unrounded accumulators (affine_qmm_steel.metal:1535-1545)."""
+    seed = 8500 + M + N + K + bits
+    if bits == 4:
+        codes, s, b = quantized_linear(oracle_mod, N, K, seed)
+        x = synth.activations_bf16(M, K, seed + 1)
+        d = (to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16), to_dev(x, torch.bfloat16))
+    else:
+        (codes, s, b, x), d = _w8_linear(oracle_mod, N, K, M, seed)
+    y = vpq.ops.qmm_swiglu(*d, act=act, bits=bits)
+    assert y.shape == (M, N // 2)
+    assert vpq.ops.device_status() == 0
+    w_bf16 = oracle_mod.bf16_to_f32(oracle_mod.dequant_bf16_any(codes, s, b, bits, 64))
+    fuse = oracle_mod.fused_geglu if act == "geglu" else oracle_mod.fused_swiglu
+    want = synth.bf16_bits_to_f32(fuse(oracle_mod.matmul_f32(x, w_bf16, "fast")))
+    e = oracle_mod.err_metrics(f32(y), want)
+    assert e["rel_l2"] < TOL and e["max_rel_rms"] < TOL, e
+    plain = (vpq.ops.qmm(*d) if bits == 4 else vpq.ops.qmm_w8(*d)).float()
+    g, u = plain[:, 0::2], plain[:, 1::2]
+    approx = ((_gelu_t(g) if act == "geglu" else g / (1.0 + torch.exp(-g))) * u).cpu().numpy()
+    assert oracle_mod.err_metrics(f32(y), approx)["max_rel_rms"] < 2e-2
+
+
+def test_qmm_gated_by_reference_names(vpq, oracle_mod):
+    ops = vpq.ops
+    M, K, N = 256, 256, 256
+    d4, _ = _linear(oracle_mod, N, K, M, 8600)
+    _, d8 = _w8_linear(oracle_mod, N, K, M, 8601)
+    for entry, d, act, bits in (("affine_qmm_geglu_w4g64", d4, "geglu", 4),
+                                ("affine_qmm_swiglu_w8g64", d8, "swiglu", 8),
+                                ("affine_qmm_swiglu_w8g64_bm64", d8, "swiglu", 8),
+                                ("affine_qmm_geglu_w8g64", d8, "geglu", 8)):
+        want = ops.qmm_swiglu(*d, act=act, bits=bits)
+        y = torch.empty((M, N // 2), dtype=torch.bfloat16, device=dev())
+        ops.dispatch(ops.function("affine_qmm_steel_bf16", entry), {0: d[0], 1: d[1], 2: d[2], 3: d[3], 4: y},
+                     K=K, N=N, M=M)
+        assert torch.equal(y, want), entry

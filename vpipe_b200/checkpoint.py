@@ -74,9 +74,9 @@ def load_quant_linear(model: Model, pfx: str, device, group: int | None = None):
     N, K, bits, group = model.quant_shape(pfx, group)
     if bits != 4 or group != 64:
         raise ValueError(f"{pfx}: w{bits} g{group}; this library computes w4 g64")
-    codes = torch.from_numpy(np.ascontiguousarray(model.numpy(pfx + ".weight")).view(np.int32)).to(device)
-    s16 = torch.from_numpy(np.ascontiguousarray(model.numpy(pfx + ".scales"))).to(device)
-    b16 = torch.from_numpy(np.ascontiguousarray(model.numpy(pfx + ".biases"))).to(device)
+    codes = torch.from_numpy(np.array(model.numpy(pfx + ".weight")).view(np.int32)).to(device)
+    s16 = torch.from_numpy(np.array(model.numpy(pfx + ".scales"))).to(device)
+    b16 = torch.from_numpy(np.array(model.numpy(pfx + ".biases"))).to(device)
     return codes, ops.scales_to_bf16(s16), ops.scales_to_bf16(b16)
 
 

@@ -191,7 +191,7 @@ extern "C" size_t vpq_scale_bytes(int N, int K, int group) {
 struct vpq_function_s {
   const char* library;
   const char* entry;
-  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32; 10 + code: quant / dequant twins (see fmt_*)
+  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64; 10 + code: quant / dequant twins (see fmt_*)
 };
 
 // The reference selects the element type with the library-name suffix and
@@ -203,6 +203,8 @@ static const vpq_function_s g_functions[] = {
     {"affine_qmv_bf16", "affine_qmv_w4g64_add", 5},
     {"affine_qmv_bf16", "affine_qmv_swiglu_w4g64", 6},
     {"affine_qmv_bf16", "affine_qmv_qkv_w4g64", 7},
+    {"affine_qmv_bf16", "affine_qmv_geglu_w4g64", 61},
+    {"affine_qmv_bf16", "affine_qmv_gelu_mul_w4g64", 62},
     {"affine_qmv_bf16", "affine_qmv_w8g64", 58},
     {"affine_qmv_bf16", "affine_qmv_w4g32", 60},
     {"affine_qmv_bf16", "affine_qmv_batch_w4g64", 9},
@@ -217,6 +219,11 @@ static const vpq_function_s g_functions[] = {
     {"affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64", 8},
     {"affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64_bm64", 8},
     {"affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64_bm128", 8},
+    {"affine_qmm_steel_bf16", "affine_qmm_geglu_w4g64", 63},
+    {"affine_qmm_steel_bf16", "affine_qmm_swiglu_w8g64", 64},
+    {"affine_qmm_steel_bf16", "affine_qmm_swiglu_w8g64_bm64", 64},
+    {"affine_qmm_steel_bf16", "affine_qmm_swiglu_w8g64_bm128", 64},
+    {"affine_qmm_steel_bf16", "affine_qmm_geglu_w8g64", 65},
     {"affine_dequant_bf16", "affine_dequant_w4g64", 2},
     {"affine_dequant_bf16", "affine_quant_w4_g64", 3},
     {"affine_dequant", "affine_quant_w4_g64", 4},
@@ -285,6 +292,22 @@ extern "C" int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* a, 
     case 9:
       return vpq_affine_qmv_batch_w4g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
                                              const_cast<void*>(b[4]), a->K, a->N, a->M < 1 ? 1 : a->M, stream);
+    case 61:
+      return vpq_affine_qmv_geglu_w4g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
+                                             const_cast<void*>(b[4]), a->K, a->N, a->M < 1 ? 1 : a->M, stream);
+    case 62:
+      return vpq_affine_qmv_gelu_mul_w4g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
+                                                const_cast<void*>(b[4]), a->K, a->N, a->M < 1 ? 1 : a->M, b[7],
+                                                stream);
+    case 63:
+      return vpq_affine_qmm_geglu_w4g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
+                                             const_cast<void*>(b[4]), a->K, a->N, a->M, stream);
+    case 64:
+      return vpq_affine_qmm_swiglu_w8g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
+                                              const_cast<void*>(b[4]), a->K, a->N, a->M, stream);
+    case 65:
+      return vpq_affine_qmm_geglu_w8g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
+                                             const_cast<void*>(b[4]), a->K, a->N, a->M, stream);
     case 60:
       return vpq_affine_qmv_w4g32_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3], const_cast<void*>(b[4]),
                                        a->K, a->N, a->M < 1 ? 1 : a->M, stream);

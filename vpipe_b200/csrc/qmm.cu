@@ -531,8 +531,9 @@ int launch_qmm_2cta_bits(const uint32_t* w, const uint16_t* scales, const uint16
                            (uint64_t)N, BK * BITS / 32, 128, CU_TENSOR_MAP_SWIZZLE_NONE, "w")) {
     return rc;
   }
-  auto kern = out.swiglu ? two_cta::affine_qmm_w4g64_2cta_kernel<true, BITS>
-                         : two_cta::affine_qmm_w4g64_2cta_kernel<false, BITS>;
+  auto kern = out.swiglu == 2   ? two_cta::affine_qmm_w4g64_2cta_kernel<2, BITS>
+              : out.swiglu == 1 ? two_cta::affine_qmm_w4g64_2cta_kernel<1, BITS>
+                                : two_cta::affine_qmm_w4g64_2cta_kernel<0, BITS>;
   VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
   const int tiles = ((M + two_cta::TM - 1) / two_cta::TM) * ((N + two_cta::TN - 1) / two_cta::TN);
   int pairs = (num_sms() - reserve_sms) / 2;  // SMs left free run a concurrent collective
@@ -622,23 +623,23 @@ extern "C" int vpq_affine_qmm_w4g64_bf16(const uint32_t* w, const void* scales, 
   return qmm_launch_reserved(w, scales, biases, x, y, K, N, M, stream, 0);
 }
 
-extern "C" int vpq_affine_qmm_swiglu_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
-                                                const void* x, void* y, int64_t K, int64_t N, int64_t M,
-                                                void* stream) {
+namespace {
+// Gated GEMMs: gate / up rows interleaved in w, y = act(gate) * up, [M, N / 2].
+int qmm_gated(const char* who, int bits, int act, const uint32_t* w, const void* scales, const void* biases,
+              const void* x, void* y, int64_t K, int64_t N, int64_t M, void* stream) {
   clear_error();
-  if (!w || !scales || !biases || !x || !y) { return fail(VPQ_ERR_INVALID_ARG, "affine_qmm_swiglu_w4g64: null pointer"); }
+  if (!w || !scales || !biases || !x || !y) { return fail(VPQ_ERR_INVALID_ARG, "%s: null pointer", who); }
   if (K <= 0 || N <= 0 || M <= 0 || (K % 64) != 0 || (N % 2) != 0) {
-    return fail(VPQ_ERR_INVALID_ARG,
-                "affine_qmm_swiglu_w4g64: need K>0, M>0, K%%64==0 and an even N>0 (K=%lld N=%lld M=%lld)",
+    return fail(VPQ_ERR_INVALID_ARG, "%s: need K>0, M>0, K%%64==0 and an even N>0 (K=%lld N=%lld M=%lld)", who,
                 (long long)K, (long long)N, (long long)M);
   }
   if (K > (1 << 20) || N > (1 << 24) || M > (1 << 24)) {
-    return fail(VPQ_ERR_UNSUPPORTED, "affine_qmm_swiglu_w4g64: shape too large (K=%lld N=%lld M=%lld)",
-                (long long)K, (long long)N, (long long)M);
+    return fail(VPQ_ERR_UNSUPPORTED, "%s: shape too large (K=%lld N=%lld M=%lld)", who, (long long)K, (long long)N,
+                (long long)M);
   }
   if (!aligned16(w) || !aligned16(x) || !aligned16(y) || (reinterpret_cast<uintptr_t>(scales) & 1) ||
       (reinterpret_cast<uintptr_t>(biases) & 1)) {
-    return fail(VPQ_ERR_ALIGNMENT, "affine_qmm_swiglu_w4g64: w, x and y must be 16-byte aligned");
+    return fail(VPQ_ERR_ALIGNMENT, "%s: w, x and y must be 16-byte aligned", who);
   }
   if (int rc = require_sm100()) { return rc; }
   two_cta::OutSpec out = {};
@@ -646,9 +647,37 @@ extern "C" int vpq_affine_qmm_swiglu_w4g64_bf16(const uint32_t* w, const void* s
   out.count = 1;
   out.col0 = 0;
   out.ld = N / 2;
-  out.swiglu = 1;
-  return launch_qmm_2cta(w, static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases), x, out,
-                         (int)K, (int)N, (int)M, static_cast<cudaStream_t>(stream), 0);
+  out.swiglu = act;
+  const uint16_t* s16 = static_cast<const uint16_t*>(scales);
+  const uint16_t* b16 = static_cast<const uint16_t*>(biases);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (bits == 8) { return launch_qmm_2cta_bits<8>(w, s16, b16, x, out, (int)K, (int)N, (int)M, st, 0); }
+  return launch_qmm_2cta_bits<4>(w, s16, b16, x, out, (int)K, (int)N, (int)M, st, 0);
+}
+}  // namespace
+
+extern "C" int vpq_affine_qmm_swiglu_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
+                                                const void* x, void* y, int64_t K, int64_t N, int64_t M,
+                                                void* stream) {
+  return qmm_gated("affine_qmm_swiglu_w4g64", 4, 1, w, scales, biases, x, y, K, N, M, stream);
+}
+
+extern "C" int vpq_affine_qmm_geglu_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
+                                               const void* x, void* y, int64_t K, int64_t N, int64_t M,
+                                               void* stream) {
+  return qmm_gated("affine_qmm_geglu_w4g64", 4, 2, w, scales, biases, x, y, K, N, M, stream);
+}
+
+extern "C" int vpq_affine_qmm_swiglu_w8g64_bf16(const uint32_t* w, const void* scales, const void* biases,
+                                                const void* x, void* y, int64_t K, int64_t N, int64_t M,
+                                                void* stream) {
+  return qmm_gated("affine_qmm_swiglu_w8g64", 8, 1, w, scales, biases, x, y, K, N, M, stream);
+}
+
+extern "C" int vpq_affine_qmm_geglu_w8g64_bf16(const uint32_t* w, const void* scales, const void* biases,
+                                               const void* x, void* y, int64_t K, int64_t N, int64_t M,
+                                               void* stream) {
+  return qmm_gated("affine_qmm_geglu_w8g64", 8, 2, w, scales, biases, x, y, K, N, M, stream);
 }
 
 extern "C" int vpq_affine_qmm_w8g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,

@@ -40,8 +40,8 @@ struct OutSpec {
   int count;
   int col0;
   int64_t ld;
-  int swiglu;  // columns 2j, 2j+1 of the product are gate j, up j: store silu(gate) * up, half as wide
-               // (selects the kernel instantiation)
+  int swiglu;  // 1, 2: columns 2j, 2j+1 of the product are gate j, up j: store act(gate) * up, half as
+               // wide; act = silu (1) or the tanh form of gelu (2). Selects the kernel instantiation.
 };
 
 template <int BITS>
@@ -129,7 +129,7 @@ __device__ __forceinline__ constexpr uint32_t make_idesc_pair() {
 }
 
 
-template <bool kSwiglu, int BITS>
+template <int kAct, int BITS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
 affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
                              const __grid_constant__ CUtensorMap tmap_w,
@@ -348,9 +348,10 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // ------------------------------------------------------------ epilogue (both CTAs)
     uint32_t ti = 0;
     bool ok = true;
-    // Fused SwiGLU (the reference's affine_qmm_swiglu_w4g64, affine_qmm_steel.metal:641-800): the
-    // 256 columns of a tile become 128 outputs, one pass of the same store path.
-    constexpr bool swiglu = kSwiglu;
+    // Fused SwiGLU / GeGLU (the reference's affine_qmm_swiglu_w4g64, affine_qmm_steel.metal:641-800,
+    // and affine_qmm_geglu_w4g64, :1451-1547): the 256 columns of a tile become 128 outputs, one
+    // pass of the same store path.
+    constexpr bool swiglu = kAct != 0;
     const int n_out = swiglu ? N / 2 : N;                 // width of the stored block
     constexpr int passes = swiglu ? 1 : TN / 128;
     constexpr int loads = swiglu ? 8 : 4;                 // 32-column accumulator reads per pass
@@ -383,7 +384,12 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 const float g = __uint_as_float(r[16 * v + 2 * i]), u = __uint_as_float(r[16 * v + 2 * i + 1]);
-                o[i] = __fdividef(g, 1.0f + __expf(-g)) * u;
+                if (kAct == 2) {  // gelu_pytorch_tanh(g) * u
+                  const float th = tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g));
+                  o[i] = 0.5f * g * (1.0f + th) * u;
+                } else {
+                  o[i] = __fdividef(g, 1.0f + __expf(-g)) * u;
+                }
               }
               uint4 pk;
               pk.x = pack_bf16x2(o[0], o[1]);

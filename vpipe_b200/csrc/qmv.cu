@@ -93,7 +93,7 @@ enum : uint32_t { kRoleProducer = 1, kRoleConsumer = 2 };
 
 // Fused stores (the reference's affine_qmv_w4g64_add, affine_qmv_swiglu_w4g64 and
 // affine_qmv_qkv_w4g64, gpu-kernels/metal/quant/affine_qmv.metal:347-363, 806-906, 405-516).
-enum : int { kEpiNone = 0, kEpiAdd = 1, kEpiSwiglu = 2, kEpiQkv = 3 };
+enum : int { kEpiNone = 0, kEpiAdd = 1, kEpiSwiglu = 2, kEpiQkv = 3, kEpiGeglu = 4, kEpiGeluMul = 5 };
 
 // One GEMV of a launch. Lives in the kernel parameters (single GEMV) or in caller-provided
 // device memory (plan). Tensor maps need 64-byte alignment.
@@ -108,11 +108,18 @@ struct alignas(64) QmvProblem {
   int scales_tma;              // scale / bias rows are TMA boxes (pitch and base 16-byte aligned)
   int epilogue;                // kEpi*: what the store does with a row's sum
   int q_rows, k_rows;          // kEpiQkv: rows [0, q_rows) -> y, [q_rows, q_rows + k_rows) -> aux, the rest -> y3
-  const uint16_t* aux;         // kEpiAdd: residual, N values; kEpiQkv: the second output
+  const uint16_t* aux;         // kEpiAdd: residual, N values; kEpiGeluMul: the multiplier; kEpiQkv: the second output
   __nv_bfloat16* y3;           // kEpiQkv: the third output
   int pad[12];
 };
 static_assert(sizeof(QmvProblem) % 64 == 0, "problem records are laid out back to back");
+
+// gelu_pytorch_tanh: 0.5 x (1 + tanh(sqrt(2 / pi) (x + 0.044715 x^3))), the activation of the
+// reference's geglu stores (affine_qmv.metal:1421-1429, ops/llm_elementwise.metal:388-407).
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float t = tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x));
+  return 0.5f * x * (1.0f + t);
+}
 
 __global__ void __launch_bounds__(kThreads, 2)
 affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProblem* __restrict__ list,
@@ -521,6 +528,16 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
           // rows 2j, 2j+1 are gate j, up j: one output silu(gate) * up from the unrounded sums
           const float up = __shfl_down_sync(0x0000ffffu, v, 1);
           if ((lane & 1) == 0 && row + 1 < N) { y[row >> 1] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * up); }
+        } else if (epi == kEpiGeglu) {
+          // as above with the tanh form of gelu on the gate
+          const float up = __shfl_down_sync(0x0000ffffu, v, 1);
+          if ((lane & 1) == 0 && row + 1 < N) { y[row >> 1] = __float2bfloat16_rn(gelu_tanh(v) * up); }
+        } else if (epi == kEpiGeluMul) {
+          // gelu of the bf16-rounded sum, times the multiplier: what a separate pass over y would compute
+          if (row < N) {
+            const float m = __uint_as_float((uint32_t)P->aux[row] << 16);
+            y[row] = __float2bfloat16_rn(gelu_tanh(__bfloat162float(__float2bfloat16_rn(v))) * m);
+          }
         } else {
           const int q_rows = P->q_rows, qk = q_rows + P->k_rows;
           if (row < q_rows) {
@@ -676,8 +693,14 @@ int check_desc(const char* who, const vpq_linear_desc& d) {
         return fail(VPQ_ERR_INVALID_ARG, "%s: the residual is null or not 2-byte aligned", who);
       }
       return VPQ_OK;
+    case VPQ_EPILOGUE_GELU_MUL:
+      if (!d.aux || (reinterpret_cast<uintptr_t>(d.aux) & 1)) {
+        return fail(VPQ_ERR_INVALID_ARG, "%s: the multiplier is null or not 2-byte aligned", who);
+      }
+      return VPQ_OK;
     case VPQ_EPILOGUE_SWIGLU:
-      if (d.N % 2) { return fail(VPQ_ERR_INVALID_ARG, "%s: swiglu needs an even N (gate / up interleaved)", who); }
+    case VPQ_EPILOGUE_GEGLU:
+      if (d.N % 2) { return fail(VPQ_ERR_INVALID_ARG, "%s: a gated store needs an even N (gate / up interleaved)", who); }
       return VPQ_OK;
     case VPQ_EPILOGUE_QKV:
       if (d.q_rows < 0 || d.k_rows < 0 || d.q_rows + d.k_rows > d.N) {
@@ -696,7 +719,8 @@ int check_desc(const char* who, const vpq_linear_desc& d) {
 
 // Row m of a descriptor as a kernel problem.
 int fill_from_desc(QmvProblem* p, const vpq_linear_desc& d, int64_t m, int tile_begin) {
-  const int64_t y_pitch = d.epilogue == VPQ_EPILOGUE_SWIGLU ? d.N / 2
+  const bool gated = d.epilogue == VPQ_EPILOGUE_SWIGLU || d.epilogue == VPQ_EPILOGUE_GEGLU;
+  const int64_t y_pitch = gated ? d.N / 2
                           : d.epilogue == VPQ_EPILOGUE_QKV  ? d.q_rows
                                                             : d.N;
   if (int rc = fill_problem(p, d.w, static_cast<const uint16_t*>(d.scales), static_cast<const uint16_t*>(d.biases),
@@ -705,7 +729,7 @@ int fill_from_desc(QmvProblem* p, const vpq_linear_desc& d, int64_t m, int tile_
     return rc;
   }
   p->epilogue = d.epilogue;
-  if (d.epilogue == VPQ_EPILOGUE_ADD) {
+  if (d.epilogue == VPQ_EPILOGUE_ADD || d.epilogue == VPQ_EPILOGUE_GELU_MUL) {
     p->aux = static_cast<const uint16_t*>(d.aux) + m * d.N;
   } else if (d.epilogue == VPQ_EPILOGUE_QKV) {
     p->q_rows = (int)d.q_rows;
@@ -797,6 +821,25 @@ extern "C" int vpq_affine_qmv_swiglu_w4g64_bf16(const uint32_t* w, const void* s
   vpq_linear_desc d = make_desc(w, scales, biases, x, y, K, N, M);
   d.epilogue = VPQ_EPILOGUE_SWIGLU;
   return launch_desc_rows("affine_qmv_swiglu_w4g64", d, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int vpq_affine_qmv_geglu_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
+                                               const void* x, void* y, int64_t K, int64_t N, int64_t M,
+                                               void* stream) {
+  clear_error();
+  vpq_linear_desc d = make_desc(w, scales, biases, x, y, K, N, M);
+  d.epilogue = VPQ_EPILOGUE_GEGLU;
+  return launch_desc_rows("affine_qmv_geglu_w4g64", d, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int vpq_affine_qmv_gelu_mul_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
+                                                  const void* x, void* y, int64_t K, int64_t N, int64_t M,
+                                                  const void* mul, void* stream) {
+  clear_error();
+  vpq_linear_desc d = make_desc(w, scales, biases, x, y, K, N, M);
+  d.epilogue = VPQ_EPILOGUE_GELU_MUL;
+  d.aux = mul;
+  return launch_desc_rows("affine_qmv_gelu_mul_w4g64", d, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int vpq_affine_qmv_qkv_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,

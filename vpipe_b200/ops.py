@@ -146,16 +146,34 @@ def qmv_add(codes, scales, biases, x, residual, out=None, stream=None) -> torch.
     return out
 
 
-def qmv_swiglu(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
-    """Rows of W interleaved gate / up: y[M, N/2] = silu(gate) * up (vpq_affine_qmv_swiglu_w4g64_bf16)."""
+def qmv_swiglu(codes, scales, biases, x, out=None, stream=None, act="swiglu") -> torch.Tensor:
+    """Rows of W interleaved gate / up: y[M, N/2] = silu(gate) * up (vpq_affine_qmv_swiglu_w4g64_bf16),
+    or gelu_tanh(gate) * up with act="geglu" (vpq_affine_qmv_geglu_w4g64_bf16)."""
     N, Kw = codes.shape
     K = Kw * 8
     M = x.numel() // K
     if out is None:
         out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+    fn = {"swiglu": lib().vpq_affine_qmv_swiglu_w4g64_bf16, "geglu": lib().vpq_affine_qmv_geglu_w4g64_bf16}[act]
     with torch.cuda.device(x.device):
-        check(lib().vpq_affine_qmv_swiglu_w4g64_bf16(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x), _ptr(out),
-                                                     K, N, M, _stream(stream)))
+        check(fn(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x), _ptr(out), K, N, M, _stream(stream)))
+    return out
+
+
+def qmv_geglu(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
+    return qmv_swiglu(codes, scales, biases, x, out, stream, act="geglu")
+
+
+def qmv_gelu_mul(codes, scales, biases, x, mul, out=None, stream=None) -> torch.Tensor:
+    """y = bf16(gelu_tanh(bf16(x W^T)) * mul) (vpq_affine_qmv_gelu_mul_w4g64_bf16)."""
+    N, Kw = codes.shape
+    K = Kw * 8
+    M = x.numel() // K
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().vpq_affine_qmv_gelu_mul_w4g64_bf16(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x),
+                                                       _ptr(out), K, N, M, _ptr(mul), _stream(stream)))
     return out
 
 
@@ -174,13 +192,14 @@ def qmv_qkv(codes, scales, biases, x, q_rows, k_rows, v_rows, stream=None):
     return tuple(outs)
 
 
-EPILOGUES = {"none": 0, "add": 1, "swiglu": 2, "qkv": 3}
+EPILOGUES = {"none": 0, "add": 1, "swiglu": 2, "qkv": 3, "geglu": 4, "gelu_mul": 5}
 
 
 def qmv_set(problems):
     """Builds the host descriptor array for qmv_batch / QmvPlan from (codes, scales, biases, x, y)
     tuples; an optional sixth element is a dict describing a fused store:
-    {"epilogue": "add", "aux": residual} | {"epilogue": "swiglu"} |
+    {"epilogue": "add", "aux": residual} | {"epilogue": "swiglu"} | {"epilogue": "geglu"} |
+    {"epilogue": "gelu_mul", "aux": mul} |
     {"epilogue": "qkv", "aux": k_out, "y3": v_out, "q_rows": .., "k_rows": ..}."""
     arr = (_lib.LinearDesc * len(problems))()
     for d, prob in zip(arr, problems):
@@ -257,16 +276,17 @@ def qmm_w8(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
     return out
 
 
-def qmm_swiglu(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
-    """Rows of W interleaved gate / up: y[M, N/2] = silu(gate) * up (vpq_affine_qmm_swiglu_w4g64_bf16)."""
+def qmm_swiglu(codes, scales, biases, x, out=None, stream=None, act="swiglu", bits=4) -> torch.Tensor:
+    """Rows of W interleaved gate / up: y[M, N/2] = act(gate) * up, act silu ("swiglu") or gelu_tanh
+    ("geglu"), over 4- or 8-bit weights (vpq_affine_qmm_{swiglu,geglu}_w{4,8}g64_bf16)."""
     N, Kw = codes.shape
-    K = Kw * 8
+    K = Kw * (32 // bits)
     M = x.numel() // K
     if out is None:
         out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+    fn = getattr(lib(), f"vpq_affine_qmm_{act}_w{bits}g64_bf16")
     with torch.cuda.device(x.device):
-        check(lib().vpq_affine_qmm_swiglu_w4g64_bf16(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x), _ptr(out),
-                                                     K, N, M, _stream(stream)))
+        check(fn(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x), _ptr(out), K, N, M, _stream(stream)))
     return out
 
 
