@@ -269,6 +269,35 @@ int vpq_affine_qmm_swiglu_w8g64_bf16(const uint32_t* w, const void* scales, cons
 int vpq_affine_qmm_geglu_w8g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
                                     void* y, int64_t K, int64_t N, int64_t M, void* stream);
 
+/* Grouped (mixture-of-experts) GEMMs for prefill. The (token, expert) pairs are sorted by expert
+ * and each expert's block is padded to whole row tiles of vpq_qmm_grouped_tile_rows() rows (128;
+ * the reference pads to its BM of 32 / 64): M is the padded row count, tile2e [ceil(M / tile)] the
+ * expert of each row tile (negative: an all-padding tile, skipped). w is [experts, N, K/8], scales /
+ * biases [experts, N, K/64].
+ * _grouped_: the down GEMM. x_sorted [M, K]; row m of the product is stored to row sdst[m] of
+ *   y [y_rows, N] (negative: a padding row, not stored; sdst null: y is [M, N] in sorted order).
+ *   Replaces affine_qmm_grouped_w4g64 (slots 0:w 1:scales 2:biases 3:x 4:y 5:K 6:N 7:M 8:tile2e
+ *   9:sdst), gpu-kernels/metal/quant/affine_qmm_steel.metal:1042-1064,1371-1440.
+ * _grouped_swiglu_ / _grouped_geglu_: the gate|up GEMM, rows of w interleaved gate / up, y [M, N/2]
+ *   in sorted order. With srow, x is the hidden [x_rows, K] and sorted row m reads row srow[m] of it
+ *   (negative: zeros); the reference fuses that gather into its x loader, here it is one pass into
+ *   the caller's scratch x_sorted [M, K] ahead of the GEMM, which reads x through TMA. With srow
+ *   null, x is already sorted and x_sorted is unused. Replaces affine_qmm_grouped_swiglu_w4g64 /
+ *   affine_qmm_grouped_geglu_w4g64 (slot 9 = srow), affine_qmm_steel.metal:1098-1176,1186-1288,1314-1336. */
+int vpq_qmm_grouped_tile_rows(void);
+int vpq_affine_qmm_grouped_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
+                                      const void* x_sorted, void* y, int64_t K, int64_t N, int64_t M,
+                                      const int* tile2e, const int* sdst, int64_t experts, int64_t y_rows,
+                                      void* stream);
+int vpq_affine_qmm_grouped_swiglu_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
+                                             const void* x, void* y, int64_t K, int64_t N, int64_t M,
+                                             const int* tile2e, const int* srow, int64_t experts,
+                                             int64_t x_rows, void* x_sorted, void* stream);
+int vpq_affine_qmm_grouped_geglu_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
+                                            const void* x, void* y, int64_t K, int64_t N, int64_t M,
+                                            const int* tile2e, const int* srow, int64_t experts,
+                                            int64_t x_rows, void* x_sorted, void* stream);
+
 /* Device-side status of the tensor-core kernels: every wait inside them is
  * bounded; one that gives up records where and the kernel returns. Reads the
  * status word of the current device back to the host (synchronises `stream`),

@@ -1,0 +1,129 @@
+"""Grouped (mixture-of-experts) GEMMs: affine_qmm_grouped_swiglu_w4g64 (gate|up, rows gathered from
+the hidden through srow), affine_qmm_grouped_geglu_w4g64, affine_qmm_grouped_w4g64 (down, rows
+scattered through sdst), affine_qmm_steel.metal:1026-1176,1186-1288,1371-1440. Checked pair by pair
+against the ungrouped entry points run on each expert's own rows, and against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from vpipe_b200 import moe, synth
+
+from test_gpu_parity import TOL, dev, f32, quantized_linear, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _need_gpu(vpq):
+    assert torch.cuda.is_available(), "the -m gpu tests need a CUDA device"
+    torch.cuda.set_device(0)
+    yield
+    torch.cuda.synchronize()
+    assert vpq.ops.device_status() == 0
+
+
+def _experts(oracle_mod, E, N, K, seed):
+    per = [quantized_linear(oracle_mod, N, K, seed + 17 * e) for e in range(E)]
+    codes = np.stack([p[0] for p in per])
+    s = np.stack([p[1] for p in per])
+    b = np.stack([p[2] for p in per])
+    return per, (to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16))
+
+
+def _routing(T, E, top_k, seed, idle=()):
+    """top_k distinct experts per token, skewed so that block sizes differ; `idle` experts get none."""
+    rng = np.random.default_rng(seed)
+    live = [e for e in range(E) if e not in idle]
+    p = rng.random(len(live)) ** 2 + 0.05
+    p /= p.sum()
+    eid = np.stack([rng.choice(live, size=top_k, replace=False, p=p) for _ in range(T)]).reshape(-1)
+    return eid.astype(np.int32)
+
+
+@pytest.mark.parametrize("act", ["swiglu", "geglu"])
+@pytest.mark.parametrize("T,E,top_k,K,N", [(96, 4, 2, 512, 512), (300, 8, 2, 1024, 2 * 384), (33, 3, 1, 64, 34)])
+def test_grouped_gate_up_gathers_rows_and_matches_per_expert_calls(vpq, oracle_mod, act, T, E, top_k, K, N):
+    ops = vpq.ops
+    tile = ops.qmm_grouped_tile_rows()
+    per, d = _experts(oracle_mod, E, N, K, 9100 + T + K)
+    x = synth.activations_bf16(T, K, 9101 + T)
+    dx = to_dev(x, torch.bfloat16)
+    eid = _routing(T, E, top_k, 9102 + T, idle=(1,) if E > 3 else ())
+    tile2e, srow, sdst, npad = moe.sort_pairs(eid, E, top_k, tile)
+    y = torch.full((npad, N // 2), -3.0, dtype=torch.bfloat16, device=dev())
+    ops.qmm_grouped_gated(*d, dx, to_dev(tile2e), to_dev(srow), act=act, out=y)
+    assert ops.device_status() == 0
+    yh = f32(y)
+    fuse = oracle_mod.fused_geglu if act == "geglu" else oracle_mod.fused_swiglu
+    for e in range(E):
+        slots = np.nonzero((np.repeat(tile2e, tile) == e) & (srow >= 0))[0]
+        if slots.size == 0:
+            continue
+        xe = np.ascontiguousarray(x[srow[slots]])
+        codes, s, b = per[e]
+        w_bf16 = oracle_mod.bf16_to_f32(oracle_mod.dequant_bf16(codes, s, b))
+        want = synth.bf16_bits_to_f32(fuse(oracle_mod.matmul_f32(xe, w_bf16, "fast")))
+        err = oracle_mod.err_metrics(yh[slots], want)
+        assert err["rel_l2"] < TOL and err["max_rel_rms"] < TOL, (e, err)
+    # padding slots of a live tile multiply zero rows: act(0) * 0 = 0; whole padding tiles do not exist
+    pad = np.nonzero(srow < 0)[0]
+    assert np.all(yh[pad] == 0.0)
+
+
+@pytest.mark.parametrize("T,E,top_k,K,N", [(96, 4, 2, 512, 512), (300, 8, 2, 768, 1000), (40, 3, 1, 64, 33)])
+def test_grouped_down_scatters_rows_to_pair_order(vpq, oracle_mod, T, E, top_k, K, N):
+    ops = vpq.ops
+    tile = ops.qmm_grouped_tile_rows()
+    per, d = _experts(oracle_mod, E, N, K, 9200 + T + K)
+    eid = _routing(T, E, top_k, 9201 + T)
+    tile2e, srow, sdst, npad = moe.sort_pairs(eid, E, top_k, tile)
+    n_pairs = T * top_k
+    xs = synth.activations_bf16(npad, K, 9202 + T)  # the sorted activations (output of the gate|up GEMM)
+    y = torch.full((n_pairs + 1, N), -3.0, dtype=torch.bfloat16, device=dev())  # one guard row
+    ops.qmm_grouped_down(*d, to_dev(xs, torch.bfloat16), to_dev(tile2e), to_dev(sdst), y_rows=n_pairs, out=y)
+    assert ops.device_status() == 0
+    yh = f32(y)
+    assert np.all(yh[n_pairs] == -3.0)
+    assert np.all(yh[:n_pairs] != -3.0)  # every pair has a slot
+    for e in range(E):
+        slots = np.nonzero((np.repeat(tile2e, tile) == e) & (sdst >= 0))[0]
+        if slots.size == 0:
+            continue
+        codes, s, b = per[e]
+        w_bf16 = oracle_mod.bf16_to_f32(oracle_mod.dequant_bf16(codes, s, b))
+        want = synth.bf16_bits_to_f32(oracle_mod.narrow_f32_bf16(
+            oracle_mod.matmul_f32(np.ascontiguousarray(xs[slots]), w_bf16, "fast")))
+        err = oracle_mod.err_metrics(yh[sdst[slots]], want)
+        assert err["rel_l2"] < TOL and err["max_rel_rms"] < TOL, (e, err)
+
+
+def test_grouped_equals_the_plain_gemm_on_one_expert(vpq, oracle_mod):
+    """One expert, identity routing: the grouped kernel's tiles are the plain GEMM's arithmetic."""
+    ops = vpq.ops
+    tile = ops.qmm_grouped_tile_rows()
+    M, K, N = tile, 256, 512  # M <= 128: the plain entry runs the same single-CTA kernel
+    per, d = _experts(oracle_mod, 1, N, K, 9300)
+    x = to_dev(synth.activations_bf16(M, K, 9301), torch.bfloat16)
+    tile2e = to_dev(np.zeros(M // tile, np.int32))
+    y = ops.qmm_grouped_down(*d, x, tile2e)
+    plain = ops.qmm(d[0][0], d[1][0], d[2][0], x)
+    assert torch.equal(y, plain)
+    # the gated store against the CTA-pair kernel's: the same f32 sums and the same activation
+    g = ops.qmm_grouped_gated(*d, x, tile2e)
+    want = ops.qmm_swiglu(d[0][0], d[1][0], d[2][0], x)
+    assert float((g == want).float().mean()) > 0.99
+    assert oracle_mod.err_metrics(f32(g), f32(want))["max_rel_rms"] < 1e-3
+
+
+def test_grouped_skips_padding_tiles_and_bad_experts(vpq, oracle_mod):
+    ops = vpq.ops
+    tile = ops.qmm_grouped_tile_rows()
+    K, N = 128, 256
+    per, d = _experts(oracle_mod, 2, N, K, 9400)
+    x = to_dev(synth.activations_bf16(3 * tile, K, 9401), torch.bfloat16)
+    tile2e = to_dev(np.array([1, -1, 7], np.int32))  # tile 1: padding; tile 2: no such expert
+    y = torch.full((3 * tile, N), -3.0, dtype=torch.bfloat16, device=dev())
+    ops.qmm_grouped_down(*d, x, tile2e, out=y)
+    assert ops.device_status() == 0
+    assert torch.equal(y[:tile], ops.qmm(d[0][1], d[1][1], d[2][1], x[:tile].contiguous()))
+    assert torch.all(y[tile:] == -3.0)

@@ -27,6 +27,13 @@ SYMBOLS = [
     ("vpq_affine_quant", _i, [_vp, _i, _vp, _vp, _vp, _i64, _i64, _i, _i, C.c_float, _vp]),
     ("vpq_affine_dequant_bf16", _i, [_vp, _vp, _vp, _vp, _i64, _i64, _i, _i, _vp]),
     ("vpq_affine_qmm_swiglu_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    ("vpq_qmm_grouped_tile_rows", _i, []),
+    ("vpq_affine_qmm_grouped_w4g64_bf16", _i,
+     [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _vp]),
+    ("vpq_affine_qmm_grouped_swiglu_w4g64_bf16", _i,
+     [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _vp, _vp]),
+    ("vpq_affine_qmm_grouped_geglu_w4g64_bf16", _i,
+     [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _vp, _vp]),
     ("vpq_affine_qmm_geglu_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     ("vpq_affine_qmm_swiglu_w8g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     ("vpq_affine_qmm_geglu_w8g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),

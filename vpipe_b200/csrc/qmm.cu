@@ -29,6 +29,7 @@
 // reuse between CTAs comes from L2.
 #include "vpq_sm100.cuh"
 
+#include <algorithm>
 #include <cstdlib>
 
 namespace vpq {
@@ -259,12 +260,31 @@ struct ScaleStream {
 
 enum Role : uint32_t { kRoleEpi = 1, kRoleTma = 2, kRoleMma = 3, kRoleDq = 4 };
 
-template <int BN>
+// Grouped (mixture-of-experts) form of the GEMM, the reference's affine_qmm_grouped_w4g64 /
+// affine_qmm_grouped_swiglu_w4g64 (affine_qmm_steel.metal:1026-1176,1371-1440): the rows of x are
+// (token, expert) pairs sorted by expert and padded per expert to whole row tiles; row tile i
+// multiplies expert tile2e[i]'s slab of w ([E, N, K/8], scales [E, N, K/64]); a negative (or out of
+// range) entry is an all-padding tile and is skipped by every role. sdst, when given, scatters
+// row m of the product to row sdst[m] of y (negative or >= y_rows: not stored).
+struct GroupSpec {
+  const int* tile2e;  // null: one weight for all row tiles
+  const int* sdst;    // null: row m of the product is row m of y
+  int experts;
+  int y_rows;
+};
+
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+  const float t = tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x));
+  return 0.5f * x * (1.0f + t);
+}
+
+// kAct 0: y [.., N]; 1 / 2: columns 2j, 2j + 1 are gate j, up j, y [.., N / 2] = silu / gelu(gate) * up.
+template <int BN, int kAct>
 __global__ void __launch_bounds__(32 * (kEpiWarps + 2 + BN / 32), 1)
 affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
                         const __grid_constant__ CUtensorMap tmap_w,
                         const uint16_t* __restrict__ scales, const uint16_t* __restrict__ biases,
-                        __nv_bfloat16* __restrict__ y, int M, int N, int K) {
+                        __nv_bfloat16* __restrict__ y, int M, int N, int K, const GroupSpec G) {
   using L = SmemLayout<BN>;
   constexpr int kDqWarps = BN / 32;
   static_assert(kDqWarps <= kDqWarpsMax, "tile too wide");
@@ -293,6 +313,12 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const int tiles_n = (N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = K / BK;
+  // expert of a tile's row tile; -1: skip the tile (the same answer in every role)
+  auto expert_of = [&](int tile) -> int {
+    if (G.tile2e == nullptr) { return 0; }
+    const int e = __ldg(G.tile2e + tile / tiles_n);
+    return (e >= 0 && e < G.experts) ? e : -1;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -327,15 +353,18 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int e = expert_of(tile);
+        if (e < 0) { continue; }
         const int m0 = (tile / tiles_n) * BM;
         const int n0 = (tile % tiles_n) * BN;
+        const int w_row0 = e * N + n0;  // expert e's slab starts at row e * N of the [E * N, K / 8] map
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
           if (!mbar_wait(bar_empty(s), ph ^ 1u, (1u << 8) | kRoleTma, abort_flag, &g_qmm_status)) { ok = false; break; }
           mbar_expect_tx(bar_full(s), L::kXBytes + L::kCodeBytes);
           tma_load_2d(base + L::kOffX + s * L::kXBytes, &tmap_x, bar_full(s), kb * BK, m0);
-          tma_load_2d(base + L::kOffCode + s * L::kCodeBytes, &tmap_w, bar_full(s), kb * (BK / 8), n0);
+          tma_load_2d(base + L::kOffCode + s * L::kCodeBytes, &tmap_w, bar_full(s), kb * (BK / 8), w_row0);
         }
       }
       // Never leave with a copy still in flight: wait for the last load of every stage.
@@ -354,9 +383,11 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
       constexpr uint32_t idesc = make_idesc<BN>();
       uint32_t it = 0, ti = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++ti) {
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (expert_of(tile) < 0) { continue; }
         const int a = ti & 1;
         const uint32_t aph = (ti >> 1) & 1u;
+        ++ti;
         if (!mbar_wait(bar_accempty(a), aph ^ 1u, (1u << 8) | kRoleMma, abort_flag, &g_qmm_status)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
@@ -390,11 +421,14 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
     uint32_t it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int e = expert_of(tile);
+      if (e < 0) { continue; }
       const int n0 = (tile % tiles_n) * BN;
       int row = n0 + t_row;
       row = row < N ? row : N - 1;  // tail rows: any valid scale; their columns are never stored
-      const uint16_t* srow = scales + (int64_t)row * groups;
-      const uint16_t* brow = biases + (int64_t)row * groups;
+      const int64_t srow_i = (int64_t)e * N + row;
+      const uint16_t* srow = scales + srow_i * groups;
+      const uint16_t* brow = biases + srow_i * groups;
       ScaleStream sst(srow, brow, groups);
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int s = it % kStages;
@@ -438,25 +472,59 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // ------------------------------------------------------------ epilogue
     uint32_t ti = 0;
     bool ok = true;
-    const bool vec_ok = (N % 8) == 0;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++ti) {
+    const int n_out = kAct ? N / 2 : N;  // width of y
+    const bool vec_ok = (n_out % 8) == 0;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      if (expert_of(tile) < 0) { continue; }
       const int m0 = (tile / tiles_n) * BM;
       const int n0 = (tile % tiles_n) * BN;
       const int a = ti & 1;
       const uint32_t aph = (ti >> 1) & 1u;
+      ++ti;
       if (!warp_wait(bar_accfull(a), aph, (1u << 8) | kRoleEpi, abort_flag, &g_qmm_status)) { ok = false; break; }
       tc_fence_after();
       const int m = m0 + warp * 32 + lane;  // warp w reads tensor-memory lanes 32w .. 32w+31
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(a * BN);
-      __nv_bfloat16* yrow = y + (int64_t)m * N + n0;
+      int dr = -1;  // row of y this lane's row goes to
+      if (m < M) {
+        dr = G.sdst ? __ldg(G.sdst + m) : m;
+        if (dr >= G.y_rows) { dr = -1; }
+      }
+      __nv_bfloat16* yrow = y + (int64_t)(dr < 0 ? 0 : dr) * n_out + (kAct ? n0 / 2 : n0);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld32(taddr + (uint32_t)(c * 32), r);
         tmem_ld_wait();
         const int nc = n0 + c * 32;
-        if (m < M && nc < N) {
-          if (vec_ok) {
+        if (dr >= 0 && nc < N) {
+          if (kAct) {
+            float o[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float g = __uint_as_float(r[2 * i]), u = __uint_as_float(r[2 * i + 1]);
+              o[i] = (kAct == 2 ? gelu_tanh_f(g) : __fdividef(g, 1.0f + __expf(-g))) * u;
+            }
+            const int oc = nc / 2;  // first output column of these 16
+            if (vec_ok) {
+#pragma unroll
+              for (int v = 0; v < 2; ++v) {
+                if (oc + v * 8 < n_out) {
+                  uint4 pk;
+                  pk.x = pack_bf16x2(o[8 * v + 0], o[8 * v + 1]);
+                  pk.y = pack_bf16x2(o[8 * v + 2], o[8 * v + 3]);
+                  pk.z = pack_bf16x2(o[8 * v + 4], o[8 * v + 5]);
+                  pk.w = pack_bf16x2(o[8 * v + 6], o[8 * v + 7]);
+                  *reinterpret_cast<uint4*>(yrow + c * 16 + v * 8) = pk;
+                }
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (oc + j < n_out) { yrow[c * 16 + j] = __float2bfloat16_rn(o[j]); }
+              }
+            }
+          } else if (vec_ok) {
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               if (nc + v * 8 < N) {
@@ -494,9 +562,9 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
 #include "qmm_2cta.cuh"
 
 // ------------------------------------------------------------- host side
-template <int BN>
-int launch_qmm(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const void* x,
-               __nv_bfloat16* y, int K, int N, int M, cudaStream_t st) {
+template <int BN, int kAct>
+int launch_qmm_act(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const void* x,
+                   __nv_bfloat16* y, int K, int N, int M, const GroupSpec& G, cudaStream_t st) {
   using L = SmemLayout<BN>;
   CUtensorMap map_x, map_w;
   if (int rc = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)K, (uint64_t)M,
@@ -504,18 +572,37 @@ int launch_qmm(const uint32_t* w, const uint16_t* scales, const uint16_t* biases
     return rc;
   }
   if (int rc = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w, (uint64_t)(K / 8),
-                           (uint64_t)N, BK / 8, BN, CU_TENSOR_MAP_SWIZZLE_NONE, "w")) {
+                           (uint64_t)N * (uint64_t)G.experts, BK / 8, BN, CU_TENSOR_MAP_SWIZZLE_NONE, "w")) {
     return rc;
   }
-  auto kern = affine_qmm_w4g64_kernel<BN>;
+  auto kern = affine_qmm_w4g64_kernel<BN, kAct>;
   VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int sms = num_sms();
   const int grid = tiles < sms ? tiles : sms;
   constexpr int threads = 32 * (kEpiWarps + 2 + BN / 32);
-  kern<<<grid, threads, L::kAlloc, st>>>(map_x, map_w, scales, biases, y, M, N, K);
+  kern<<<grid, threads, L::kAlloc, st>>>(map_x, map_w, scales, biases, y, M, N, K, G);
   VPQ_LAUNCH_OK("affine_qmm_w4g64");
   return VPQ_OK;
+}
+
+template <int BN>
+int launch_qmm(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const void* x,
+               __nv_bfloat16* y, int K, int N, int M, cudaStream_t st) {
+  const GroupSpec G = {nullptr, nullptr, 1, M};
+  return launch_qmm_act<BN, 0>(w, scales, biases, x, y, K, N, M, G, st);
+}
+
+// Rows of a [rows, K] bf16 matrix gathered into sorted order: out[i] = src[srow[i]], zeros where
+// srow[i] is negative or out of range (padding slots). 16-byte copies; K % 8 == 0.
+__global__ void gather_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ srow,
+                                   uint4* __restrict__ out, int n_out, int src_rows, int row_vecs) {
+  const int64_t total = (int64_t)n_out * row_vecs;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / row_vecs), c = (int)(i % row_vecs);
+    const int sr = __ldg(srow + r);
+    out[i] = (sr >= 0 && sr < src_rows) ? __ldg(src + (int64_t)sr * row_vecs + c) : make_uint4(0, 0, 0, 0);
+  }
 }
 
 template <int BITS>
@@ -704,6 +791,81 @@ extern "C" int vpq_affine_qmm_w8g64_bf16(const uint32_t* w, const void* scales, 
   out.ld = N;
   return launch_qmm_2cta_bits<8>(w, static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases), x, out,
                                  (int)K, (int)N, (int)M, static_cast<cudaStream_t>(stream), 0);
+}
+
+namespace {
+int qmm_grouped(const char* who, int act, const uint32_t* w, const void* scales, const void* biases, const void* x,
+                void* y, int64_t K, int64_t N, int64_t M, const int* tile2e, const int* srow, const int* sdst,
+                int64_t experts, int64_t x_rows, int64_t y_rows, void* x_sorted, void* stream) {
+  clear_error();
+  if (!w || !scales || !biases || !x || !y || !tile2e) { return fail(VPQ_ERR_INVALID_ARG, "%s: null pointer", who); }
+  if (K <= 0 || N <= 0 || M <= 0 || (K % 64) != 0 || experts <= 0 || y_rows <= 0 || (act && (N % 2) != 0)) {
+    return fail(VPQ_ERR_INVALID_ARG,
+                "%s: need K>0, N>0 (even for a gated store), M>0, K%%64==0, experts>0, y_rows>0 "
+                "(K=%lld N=%lld M=%lld experts=%lld)",
+                who, (long long)K, (long long)N, (long long)M, (long long)experts);
+  }
+  if (K > (1 << 20) || N > (1 << 24) || M > (1 << 24) || N * experts > (1ll << 30) || y_rows > (1ll << 30)) {
+    return fail(VPQ_ERR_UNSUPPORTED, "%s: shape too large (K=%lld N=%lld M=%lld experts=%lld)", who, (long long)K,
+                (long long)N, (long long)M, (long long)experts);
+  }
+  if (srow && (!x_sorted || x_rows <= 0)) {
+    return fail(VPQ_ERR_INVALID_ARG, "%s: a row gather needs x_rows > 0 and an [M, K] scratch buffer", who);
+  }
+  if (!aligned16(w) || !aligned16(x) || !aligned16(y) || (srow && !aligned16(x_sorted)) ||
+      (reinterpret_cast<uintptr_t>(scales) & 1) || (reinterpret_cast<uintptr_t>(biases) & 1) ||
+      (reinterpret_cast<uintptr_t>(tile2e) & 3) || (reinterpret_cast<uintptr_t>(srow) & 3) ||
+      (reinterpret_cast<uintptr_t>(sdst) & 3)) {
+    return fail(VPQ_ERR_ALIGNMENT, "%s: w, x, y (and the scratch) must be 16-byte aligned, index arrays 4-byte", who);
+  }
+  if (int rc = require_sm100()) { return rc; }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const void* xs = x;
+  if (srow) {  // the gather the reference fuses into its x loader, as one pass over [M, K]
+    const int row_vecs = (int)(K / 8);
+    const int64_t total = M * row_vecs;
+    const int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)num_sms() * 8);
+    gather_rows_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint4*>(x), srow, static_cast<uint4*>(x_sorted),
+                                               (int)M, (int)x_rows, row_vecs);
+    VPQ_LAUNCH_OK("moe row gather");
+    xs = x_sorted;
+  }
+  const GroupSpec G = {tile2e, sdst, (int)experts, (int)y_rows};
+  const uint16_t* s16 = static_cast<const uint16_t*>(scales);
+  const uint16_t* b16 = static_cast<const uint16_t*>(biases);
+  __nv_bfloat16* yb = static_cast<__nv_bfloat16*>(y);
+  switch (act) {
+    case 0: return launch_qmm_act<256, 0>(w, s16, b16, xs, yb, (int)K, (int)N, (int)M, G, st);
+    case 1: return launch_qmm_act<256, 1>(w, s16, b16, xs, yb, (int)K, (int)N, (int)M, G, st);
+    default: return launch_qmm_act<256, 2>(w, s16, b16, xs, yb, (int)K, (int)N, (int)M, G, st);
+  }
+}
+}  // namespace
+
+extern "C" int vpq_qmm_grouped_tile_rows(void) { return BM; }
+
+extern "C" int vpq_affine_qmm_grouped_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
+                                                 const void* x_sorted, void* y, int64_t K, int64_t N, int64_t M,
+                                                 const int* tile2e, const int* sdst, int64_t experts,
+                                                 int64_t y_rows, void* stream) {
+  return qmm_grouped("affine_qmm_grouped_w4g64", 0, w, scales, biases, x_sorted, y, K, N, M, tile2e, nullptr, sdst,
+                     experts, 0, sdst ? y_rows : M, nullptr, stream);
+}
+
+extern "C" int vpq_affine_qmm_grouped_swiglu_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
+                                                        const void* x, void* y, int64_t K, int64_t N, int64_t M,
+                                                        const int* tile2e, const int* srow, int64_t experts,
+                                                        int64_t x_rows, void* x_sorted, void* stream) {
+  return qmm_grouped("affine_qmm_grouped_swiglu_w4g64", 1, w, scales, biases, x, y, K, N, M, tile2e, srow, nullptr,
+                     experts, x_rows, M, x_sorted, stream);
+}
+
+extern "C" int vpq_affine_qmm_grouped_geglu_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
+                                                       const void* x, void* y, int64_t K, int64_t N, int64_t M,
+                                                       const int* tile2e, const int* srow, int64_t experts,
+                                                       int64_t x_rows, void* x_sorted, void* stream) {
+  return qmm_grouped("affine_qmm_grouped_geglu_w4g64", 2, w, scales, biases, x, y, K, N, M, tile2e, srow, nullptr,
+                     experts, x_rows, M, x_sorted, stream);
 }
 
 extern "C" int vpq_device_status(void* stream, uint32_t* detail) {

@@ -290,6 +290,45 @@ def qmm_swiglu(codes, scales, biases, x, out=None, stream=None, act="swiglu", bi
     return out
 
 
+def qmm_grouped_tile_rows() -> int:
+    return int(lib().vpq_qmm_grouped_tile_rows())
+
+
+def qmm_grouped_gated(codes, scales, biases, x, tile2e, srow=None, act="swiglu", out=None, stream=None):
+    """Gate|up GEMM of a mixture of experts over sorted, padded rows: codes [E, N, K/8]; x the hidden
+    [T, K] with srow [M] (gathered), or already sorted [M, K] with srow None. Returns y [M, N/2] in
+    sorted order (vpq_affine_qmm_grouped_{swiglu,geglu}_w4g64_bf16)."""
+    E, N, Kw = codes.shape
+    K = Kw * 8
+    M = int(srow.numel()) if srow is not None else x.numel() // K
+    if out is None:
+        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+    scratch = torch.empty((M, K), dtype=torch.bfloat16, device=x.device) if srow is not None else None
+    fn = getattr(lib(), f"vpq_affine_qmm_grouped_{act}_w4g64_bf16")
+    with torch.cuda.device(x.device):
+        check(fn(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x), _ptr(out), K, N, M, _ptr(tile2e),
+                 _ptr(srow) if srow is not None else None, E, x.numel() // K,
+                 _ptr(scratch) if scratch is not None else None, _stream(stream)))
+    return out
+
+
+def qmm_grouped_down(codes, scales, biases, x_sorted, tile2e, sdst=None, y_rows=0, out=None, stream=None):
+    """Down GEMM of a mixture of experts: x_sorted [M, K]; row m of the product lands in row sdst[m]
+    of y [y_rows, N] (vpq_affine_qmm_grouped_w4g64_bf16). Rows of y no slot points at are not written."""
+    E, N, Kw = codes.shape
+    K = Kw * 8
+    M = x_sorted.numel() // K
+    rows = y_rows if sdst is not None else M
+    if out is None:
+        out = torch.zeros((rows, N), dtype=torch.bfloat16, device=x_sorted.device)
+    with torch.cuda.device(x_sorted.device):
+        check(lib().vpq_affine_qmm_grouped_w4g64_bf16(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x_sorted),
+                                                      _ptr(out), K, N, M, _ptr(tile2e),
+                                                      _ptr(sdst) if sdst is not None else None, E, rows,
+                                                      _stream(stream)))
+    return out
+
+
 def device_status(stream=None) -> int:
     """Raises VpqError(TIMEOUT) if a bounded device-side wait gave up; else 0."""
     detail = C.c_uint32(0)
