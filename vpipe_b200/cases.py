@@ -8,6 +8,7 @@
     python -m vpipe_b200.cases qmm  M K N [reps]       # the GEMM
     python -m vpipe_b200.cases qmm_swiglu M K N [reps] # the GEMM with the fused SwiGLU store (N = 2 ffn)
     python -m vpipe_b200.cases qmm_w8 M K N [reps]     # the GEMM over 8-bit weights
+    python -m vpipe_b200.cases moe T E TOPK HIDDEN FFN [reps]  # grouped gate|up (SwiGLU) + down GEMMs of one MoE layer
 
 Weights are random packed nibbles with bf16 scales / biases (the distribution of the reference's
 kernel tests); each command prints one JSON line with the CUDA-event time. Meant to be wrapped by
@@ -180,6 +181,35 @@ def main(argv):
         t = _time(lambda: fn(codes, s, b, x, out=y), reps)
         print(json.dumps({"case": kind, "M": M, "K": K, "N": N, "ms": t * 1e3,
                           "tflops": synth.qmm_flops(K, N, M) / t / 1e12}))
+    elif kind == "moe":
+        import numpy as np
+        from . import moe
+        T, E, top_k, H, F = (int(a) for a in argv[1:6])
+        reps = int(argv[6]) if len(argv) > 6 else 3
+        tile = ops.qmm_grouped_tile_rows()
+        rng = np.random.default_rng(0)
+        eid = np.stack([rng.choice(E, size=top_k, replace=False) for _ in range(T)]).reshape(-1).astype(np.int32)
+        tile2e, srow, sdst, npad = moe.sort_pairs(eid, E, top_k, tile)
+        tile2e, srow, sdst = (torch.from_numpy(a).to(dev) for a in (tile2e, srow, sdst))
+        hidden = torch.randn((T, H), device=dev).to(torch.bfloat16)
+        gu = [t.view(E, 2 * F, -1) for t in _weight(E * 2 * F, H, dev)]
+        dn = [t.view(E, H, -1) for t in _weight(E * H, F, dev)]
+        act = torch.empty((npad, F), dtype=torch.bfloat16, device=dev)
+        part = torch.empty((T * top_k, H), dtype=torch.bfloat16, device=dev)
+
+        def layer():
+            ops.qmm_grouped_gated(*gu, hidden, tile2e, srow, out=act)
+            ops.qmm_grouped_down(*dn, act, tile2e, sdst, y_rows=T * top_k, out=part)
+
+        for _ in range(2):
+            layer()
+        torch.cuda.synchronize()
+        t = _time(layer, reps)
+        useful = 2.0 * T * top_k * (H * 2 * F + F * H)
+        padded = 2.0 * npad * (H * 2 * F + F * H)
+        print(json.dumps({"case": kind, "tokens": T, "experts": E, "top_k": top_k, "hidden": H, "ffn": F,
+                          "rows_padded": npad, "ms": t * 1e3, "tflops_useful": useful / t / 1e12,
+                          "tflops_padded": padded / t / 1e12}))
     else:
         raise SystemExit(__doc__)
     assert ops.device_status() == 0
