@@ -199,6 +199,12 @@ enum {
 };
 int vpq_affine_qmv_w4g64_bf16_batch(const vpq_linear_desc* descs_host, int count, void* stream);
 
+/* The 8-bit GEMV with a fused store: one descriptor (w u32 [N, K/4]), any VPQ_EPILOGUE_*. Replaces
+ * affine_qmv_w8g64_add, affine_qmv_swiglu_w8g64, affine_qmv_qkv_w8g64 and affine_qmv_gelu_mul_w8g64
+ * (the 8-bit instantiations of the kernels cited above, gpu-kernels/metal/quant/affine_qmv.metal:
+ * 540-560,789-805,3122-3160). */
+int vpq_affine_qmv_w8g64_bf16_fused(const vpq_linear_desc* desc_host, void* stream);
+
 /* A list of independent GEMVs run as ONE launch: the kernel walks the row tiles of all problems
  * back to back, so there is no launch gap and no per-problem ramp-up, and problems that read the
  * same x (q | k | v, gate | up) stage it once. "Encode once, commit many": the analogue of

@@ -63,6 +63,10 @@ def test_function_table_uses_reference_names(vpq):
                            ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w8g64"),
                            ("affine_qmm_steel_bf16", "affine_qmm_geglu_w8g64"),
                            ("affine_qmv_bf16", "affine_qmv_geglu_w4g64"),
+                           ("affine_qmv_bf16", "affine_qmv_w8g64_add"),
+                           ("affine_qmv_bf16", "affine_qmv_swiglu_w8g64"),
+                           ("affine_qmv_bf16", "affine_qmv_qkv_w8g64"),
+                           ("affine_qmv_bf16", "affine_qmv_gelu_mul_w8g64"),
                            ("affine_qmv_bf16", "affine_qmv_gelu_mul_w4g64"),
                            ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64_bm128"),
                            ("affine_dequant_bf16", "affine_dequant_w4g64"),
@@ -112,6 +116,7 @@ def test_argument_validation_happens_before_any_device_work(vpq):
     assert L.vpq_affine_qmm_geglu_w4g64_bf16(p16, p16, p16, p16, p16, 64, 9, 4, None) == INVALID
     assert L.vpq_affine_qmm_swiglu_w8g64_bf16(p16, p16, p16, p16, p16, 96, 8, 4, None) == INVALID
     assert L.vpq_affine_qmm_geglu_w8g64_bf16(None, p16, p16, p16, p16, 64, 8, 4, None) == INVALID
+    assert L.vpq_affine_qmv_w8g64_bf16_fused(None, None) == INVALID
     assert L.vpq_qmm_grouped_tile_rows() == 128
     assert L.vpq_affine_qmm_grouped_w4g64_bf16(p16, p16, p16, p16, p16, 64, 8, 128, None, None, 1, 128, None) == INVALID
     assert L.vpq_affine_qmm_grouped_swiglu_w4g64_bf16(p16, p16, p16, p16, p16, 64, 9, 128, p16, None, 1, 0, None,

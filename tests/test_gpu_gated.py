@@ -135,3 +135,59 @@ def test_qmm_gated_by_reference_names(vpq, oracle_mod):
         ops.dispatch(ops.function("affine_qmm_steel_bf16", entry), {0: d[0], 1: d[1], 2: d[2], 3: d[3], 4: y},
                      K=K, N=N, M=M)
         assert torch.equal(y, want), entry
+
+
+# ------------------------------------------------------- fused stores of the 8-bit GEMV
+
+@pytest.mark.parametrize("K,N,M", [(1024, 512, 1), (2560, 40, 2), (64, 6, 1)])
+def test_qmv_w8_fused_stores_equal_a_separate_pass(vpq, oracle_mod, K, N, M):
+    """affine_qmv_w8g64_add / swiglu_w8g64 / qkv_w8g64 / gelu_mul_w8g64: the sums are the plain 8-bit
+    GEMV's; add and gelu*mul act on its bf16 output (bit-equal), the gated stores on the f32 sums."""
+    ops = vpq.ops
+    (codes, s, b, x), d = _w8_linear(oracle_mod, N, K, M, 8700 + N + K)
+    plain = ops.qmv_w8(*d)
+    aux = to_dev(synth.activations_bf16(M, N, 8701 + N), torch.bfloat16)
+    z = lambda *shape: torch.full(shape, -3.0, dtype=torch.bfloat16, device=dev())
+
+    y = ops.qmv_w8_fused(*d, z(M, N), {"epilogue": "add", "aux": aux})
+    assert torch.equal(y, (plain.float() + aux.float()).to(torch.bfloat16))
+
+    y = ops.qmv_w8_fused(*d, z(M, N), {"epilogue": "gelu_mul", "aux": aux})
+    sep = (_gelu_t(plain.float()) * aux.float()).to(torch.bfloat16)
+    assert float((y == sep).float().mean()) > 0.98
+    assert oracle_mod.err_metrics(f32(y), f32(sep))["max_rel_rms"] < 1e-2
+
+    q_rows, k_rows = (N // 2) & ~1, N // 4
+    yq, yk, yv = z(M, q_rows), z(M, k_rows), z(M, N - q_rows - k_rows)
+    ops.qmv_w8_fused(*d, yq, {"epilogue": "qkv", "aux": yk, "y3": yv, "q_rows": q_rows, "k_rows": k_rows})
+    assert torch.equal(torch.cat([yq, yk, yv], dim=1), plain)
+
+    # fp32 dequantise-then-matmul reference for the gated stores
+    q = codes.view(np.uint8).reshape(N, K).astype(np.float32)
+    wf = (np.repeat(synth.bf16_bits_to_f32(s), 64, axis=1) * q + np.repeat(synth.bf16_bits_to_f32(b), 64, axis=1))
+    ref = oracle_mod.matmul_f32(x, wf.astype(np.float32), "fast")
+    for name, fuse in (("swiglu", oracle_mod.fused_swiglu), ("geglu", oracle_mod.fused_geglu)):
+        y = ops.qmv_w8_fused(*d, z(M, N // 2), {"epilogue": name})
+        e = oracle_mod.err_metrics(f32(y), synth.bf16_bits_to_f32(fuse(ref)))
+        assert e["rel_l2"] < TOL and e["max_rel_rms"] < TOL, (name, e)
+
+
+def test_qmv_w8_fused_by_reference_names(vpq, oracle_mod):
+    ops = vpq.ops
+    K, N = 512, 256
+    _, d = _w8_linear(oracle_mod, N, K, 1, 8800)
+    aux = to_dev(synth.activations_bf16(1, N, 8801), torch.bfloat16)
+    z = lambda n: torch.zeros((1, n), dtype=torch.bfloat16, device=dev())
+    for entry, store, width in (("affine_qmv_w8g64_add", {"epilogue": "add", "aux": aux}, N),
+                                ("affine_qmv_gelu_mul_w8g64", {"epilogue": "gelu_mul", "aux": aux}, N),
+                                ("affine_qmv_swiglu_w8g64", {"epilogue": "swiglu"}, N // 2)):
+        want = ops.qmv_w8_fused(*d, z(width), store)
+        y = z(width)
+        ops.dispatch(ops.function("affine_qmv_bf16", entry), {0: d[0], 1: d[1], 2: d[2], 3: d[3], 4: y, 7: aux},
+                     K=K, N=N)
+        assert torch.equal(y, want), entry
+    plain = ops.qmv_w8(*d)
+    yq, yk, yv = z(128), z(64), z(64)
+    ops.dispatch(ops.function("affine_qmv_bf16", "affine_qmv_qkv_w8g64"),
+                 {0: d[0], 1: d[1], 2: d[2], 3: d[3], 4: yq, 5: yk, 6: yv}, K=K, q_rows=128, k_rows=64, v_rows=64)
+    assert torch.equal(torch.cat([yq, yk, yv], dim=1), plain)

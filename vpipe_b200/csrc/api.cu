@@ -191,7 +191,7 @@ extern "C" size_t vpq_scale_bytes(int N, int K, int group) {
 struct vpq_function_s {
   const char* library;
   const char* entry;
-  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64; 10 + code: quant / dequant twins (see fmt_*)
+  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64, 66..69 qmv w8g64 add / swiglu / qkv / gelu*mul; 10 + code: quant / dequant twins (see fmt_*)
 };
 
 // The reference selects the element type with the library-name suffix and
@@ -206,6 +206,10 @@ static const vpq_function_s g_functions[] = {
     {"affine_qmv_bf16", "affine_qmv_geglu_w4g64", 61},
     {"affine_qmv_bf16", "affine_qmv_gelu_mul_w4g64", 62},
     {"affine_qmv_bf16", "affine_qmv_w8g64", 58},
+    {"affine_qmv_bf16", "affine_qmv_w8g64_add", 66},
+    {"affine_qmv_bf16", "affine_qmv_swiglu_w8g64", 67},
+    {"affine_qmv_bf16", "affine_qmv_qkv_w8g64", 68},
+    {"affine_qmv_bf16", "affine_qmv_gelu_mul_w8g64", 69},
     {"affine_qmv_bf16", "affine_qmv_w4g32", 60},
     {"affine_qmv_bf16", "affine_qmv_batch_w4g64", 9},
     {"affine_qmv_bf16", "affine_qmv_batch4_w4g64", 9},
@@ -292,6 +296,33 @@ extern "C" int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* a, 
     case 9:
       return vpq_affine_qmv_batch_w4g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
                                              const_cast<void*>(b[4]), a->K, a->N, a->M < 1 ? 1 : a->M, stream);
+    case 66:
+    case 67:
+    case 68:
+    case 69: {
+      vpq_linear_desc d;
+      std::memset(&d, 0, sizeof(d));
+      d.w = static_cast<const uint32_t*>(b[0]);
+      d.scales = b[1];
+      d.biases = b[2];
+      d.x = b[3];
+      d.y = const_cast<void*>(b[4]);
+      d.K = a->K;
+      d.M = a->M < 1 ? 1 : a->M;
+      if (fn->kind == 68) {  // slots 4..6 = q, k, v outputs; the row counts give N
+        d.epilogue = VPQ_EPILOGUE_QKV;
+        d.aux = b[5];
+        d.y3 = const_cast<void*>(b[6]);
+        d.q_rows = a->q_rows;
+        d.k_rows = a->k_rows;
+        d.N = a->q_rows + a->k_rows + a->v_rows;
+      } else {
+        d.epilogue = fn->kind == 66 ? VPQ_EPILOGUE_ADD : fn->kind == 67 ? VPQ_EPILOGUE_SWIGLU : VPQ_EPILOGUE_GELU_MUL;
+        d.aux = fn->kind == 67 ? nullptr : b[7];
+        d.N = a->N;
+      }
+      return vpq_affine_qmv_w8g64_bf16_fused(&d, stream);
+    }
     case 61:
       return vpq_affine_qmv_geglu_w4g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
                                              const_cast<void*>(b[4]), a->K, a->N, a->M < 1 ? 1 : a->M, stream);

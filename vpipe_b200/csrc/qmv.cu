@@ -93,7 +93,6 @@ enum : uint32_t { kRoleProducer = 1, kRoleConsumer = 2 };
 
 // Fused stores (the reference's affine_qmv_w4g64_add, affine_qmv_swiglu_w4g64 and
 // affine_qmv_qkv_w4g64, gpu-kernels/metal/quant/affine_qmv.metal:347-363, 806-906, 405-516).
-enum : int { kEpiNone = 0, kEpiAdd = 1, kEpiSwiglu = 2, kEpiQkv = 3, kEpiGeglu = 4, kEpiGeluMul = 5 };
 
 // One GEMV of a launch. Lives in the kernel parameters (single GEMV) or in caller-provided
 // device memory (plan). Tensor maps need 64-byte alignment.
@@ -114,12 +113,6 @@ struct alignas(64) QmvProblem {
 };
 static_assert(sizeof(QmvProblem) % 64 == 0, "problem records are laid out back to back");
 
-// gelu_pytorch_tanh: 0.5 x (1 + tanh(sqrt(2 / pi) (x + 0.044715 x^3))), the activation of the
-// reference's geglu stores (affine_qmv.metal:1421-1429, ops/llm_elementwise.metal:388-407).
-__device__ __forceinline__ float gelu_tanh(float x) {
-  const float t = tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x));
-  return 0.5f * x * (1.0f + t);
-}
 
 __global__ void __launch_bounds__(kThreads, 2)
 affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProblem* __restrict__ list,
@@ -515,39 +508,7 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
         }
         v *= x_unscale;
         const int row = (tile << 4) + lane;
-        const int epi = P->epilogue;
-        if (epi == kEpiNone) {
-          if (row < N) { y[row] = __float2bfloat16_rn(v); }
-        } else if (epi == kEpiAdd) {
-          // the sum is rounded to bf16 first, then added to the residual in bf16, as the reference does
-          if (row < N) {
-            const float r = __uint_as_float((uint32_t)P->aux[row] << 16);
-            y[row] = __float2bfloat16_rn(__bfloat162float(__float2bfloat16_rn(v)) + r);
-          }
-        } else if (epi == kEpiSwiglu) {
-          // rows 2j, 2j+1 are gate j, up j: one output silu(gate) * up from the unrounded sums
-          const float up = __shfl_down_sync(0x0000ffffu, v, 1);
-          if ((lane & 1) == 0 && row + 1 < N) { y[row >> 1] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * up); }
-        } else if (epi == kEpiGeglu) {
-          // as above with the tanh form of gelu on the gate
-          const float up = __shfl_down_sync(0x0000ffffu, v, 1);
-          if ((lane & 1) == 0 && row + 1 < N) { y[row >> 1] = __float2bfloat16_rn(gelu_tanh(v) * up); }
-        } else if (epi == kEpiGeluMul) {
-          // gelu of the bf16-rounded sum, times the multiplier: what a separate pass over y would compute
-          if (row < N) {
-            const float m = __uint_as_float((uint32_t)P->aux[row] << 16);
-            y[row] = __float2bfloat16_rn(gelu_tanh(__bfloat162float(__float2bfloat16_rn(v))) * m);
-          }
-        } else {
-          const int q_rows = P->q_rows, qk = q_rows + P->k_rows;
-          if (row < q_rows) {
-            y[row] = __float2bfloat16_rn(v);
-          } else if (row < qk) {
-            reinterpret_cast<__nv_bfloat16*>(const_cast<uint16_t*>(P->aux))[row - q_rows] = __float2bfloat16_rn(v);
-          } else if (row < N) {
-            P->y3[row - qk] = __float2bfloat16_rn(v);
-          }
-        }
+        fused_store(P->epilogue, v, row, N, lane, y, P->aux, P->y3, P->q_rows, P->k_rows);
       }
       __syncwarp();
       if (lane == 0) { red_cnt[slot] = 0; }
@@ -685,6 +646,11 @@ int check_qmv_args(const char* who, const void* w, const void* scales, const voi
 // Validation of one descriptor, fused store included.
 int check_desc(const char* who, const vpq_linear_desc& d) {
   if (int rc = check_qmv_args(who, d.w, d.scales, d.biases, d.x, d.y, d.K, d.N, d.M)) { return rc; }
+  return qmv_check_store(who, d);
+}
+}  // namespace
+
+int qmv_check_store(const char* who, const vpq_linear_desc& d) {
   switch (d.epilogue) {
     case VPQ_EPILOGUE_NONE:
       return VPQ_OK;
@@ -716,6 +682,8 @@ int check_desc(const char* who, const vpq_linear_desc& d) {
       return fail(VPQ_ERR_INVALID_ARG, "%s: unknown epilogue %d", who, (int)d.epilogue);
   }
 }
+
+namespace {
 
 // Row m of a descriptor as a kernel problem.
 int fill_from_desc(QmvProblem* p, const vpq_linear_desc& d, int64_t m, int tile_begin) {

@@ -67,6 +67,10 @@ struct alignas(64) Problem8 {
   int K, N;
   int row_tiles;
   int scales_tma;
+  int epilogue;                // kEpi*: what the store does with a row's sum (see fused_store)
+  int q_rows, k_rows;
+  const uint16_t* aux;
+  __nv_bfloat16* y3;
 };
 
 __global__ void __launch_bounds__(kThreads, 2)
@@ -335,7 +339,7 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
           v += *reinterpret_cast<volatile float*>(&red[(slot * kConsWarps + ww) * 16 + lane]);
         }
         const int row = (tile << 4) + lane;
-        if (row < N) { P.y[row] = __float2bfloat16_rn(v * x_unscale); }
+        fused_store(P.epilogue, v * x_unscale, row, N, lane, P.y, P.aux, P.y3, P.q_rows, P.k_rows);
       }
       __syncwarp();
       if (lane == 0) { red_cnt[slot] = 0; }
@@ -366,22 +370,26 @@ int qmv8_status_read(cudaStream_t st, uint32_t* out) {
 
 using namespace vpq;
 
-extern "C" int vpq_affine_qmv_w8g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
-                                         void* y, int64_t K, int64_t N, int64_t M, void* stream) {
-  clear_error();
-  if (!w || !scales || !biases || !x || !y) { return fail(VPQ_ERR_INVALID_ARG, "affine_qmv_w8g64: null pointer"); }
+namespace {
+int launch_w8(const char* who, const vpq_linear_desc& d, void* stream) {
+  const uint32_t* w = d.w;
+  const void *scales = d.scales, *biases = d.biases, *x = d.x;
+  void* y = d.y;
+  const int64_t K = d.K, N = d.N, M = d.M;
+  if (!w || !scales || !biases || !x || !y) { return fail(VPQ_ERR_INVALID_ARG, "%s: null pointer", who); }
   if (K <= 0 || N <= 0 || M <= 0 || (K % 64) != 0) {
-    return fail(VPQ_ERR_INVALID_ARG, "affine_qmv_w8g64: need K>0, N>0, M>0, K%%64==0 (K=%lld N=%lld M=%lld)",
+    return fail(VPQ_ERR_INVALID_ARG, "%s: need K>0, N>0, M>0, K%%64==0 (K=%lld N=%lld M=%lld)", who,
                 (long long)K, (long long)N, (long long)M);
   }
   if (K > 16384 || N > (1 << 30) || M > 65535) {
-    return fail(VPQ_ERR_UNSUPPORTED, "affine_qmv_w8g64: K<=16384, M<=65535 supported (K=%lld M=%lld)", (long long)K,
+    return fail(VPQ_ERR_UNSUPPORTED, "%s: K<=16384, M<=65535 supported (K=%lld M=%lld)", who, (long long)K,
                 (long long)M);
   }
   if (!aligned16(w) || !aligned16(x) || (reinterpret_cast<uintptr_t>(scales) & 1) ||
       (reinterpret_cast<uintptr_t>(biases) & 1) || (reinterpret_cast<uintptr_t>(y) & 1)) {
-    return fail(VPQ_ERR_ALIGNMENT, "affine_qmv_w8g64: w and x must be 16-byte aligned");
+    return fail(VPQ_ERR_ALIGNMENT, "%s: w and x must be 16-byte aligned", who);
   }
+  if (int rc = qmv_check_store(who, d)) { return rc; }
   if (int rc = require_sm100()) { return rc; }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Problem8 p;
@@ -406,6 +414,11 @@ extern "C" int vpq_affine_qmv_w8g64_bf16(const uint32_t* w, const void* scales, 
   p.K = (int)K;
   p.N = (int)N;
   p.row_tiles = (int)((N + 15) / 16);
+  p.epilogue = d.epilogue;
+  p.q_rows = (int)d.q_rows;
+  p.k_rows = (int)d.k_rows;
+  const bool gated = d.epilogue == VPQ_EPILOGUE_SWIGLU || d.epilogue == VPQ_EPILOGUE_GEGLU;
+  const int64_t y_pitch = gated ? N / 2 : d.epilogue == VPQ_EPILOGUE_QKV ? d.q_rows : N;
   const int cap_kt = (int)((K + 127) / 128);
   const size_t fixed = fixed_smem(cap_kt);
   const size_t budget = 112 * 1024;  // two CTAs per SM
@@ -418,7 +431,13 @@ extern "C" int vpq_affine_qmv_w8g64_bf16(const uint32_t* w, const void* scales, 
   const int cap = 2 * num_sms();
   for (int64_t m = 0; m < M; ++m) {  // every row streams the weight again, as in the reference
     p.x = static_cast<const uint16_t*>(x) + m * K;
-    p.y = static_cast<__nv_bfloat16*>(y) + m * N;
+    p.y = static_cast<__nv_bfloat16*>(y) + m * y_pitch;
+    if (d.epilogue == VPQ_EPILOGUE_ADD || d.epilogue == VPQ_EPILOGUE_GELU_MUL) {
+      p.aux = static_cast<const uint16_t*>(d.aux) + m * N;
+    } else if (d.epilogue == VPQ_EPILOGUE_QKV) {
+      p.aux = static_cast<const uint16_t*>(d.aux) + m * d.k_rows;
+      p.y3 = static_cast<__nv_bfloat16*>(d.y3) + m * (N - d.q_rows - d.k_rows);
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(p.row_tiles < cap ? p.row_tiles : cap), 1, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
@@ -432,4 +451,27 @@ extern "C" int vpq_affine_qmv_w8g64_bf16(const uint32_t* w, const void* scales, 
     VPQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p, stages, cap_kt));
   }
   return VPQ_OK;
+}
+}  // namespace
+
+extern "C" int vpq_affine_qmv_w8g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                                         void* y, int64_t K, int64_t N, int64_t M, void* stream) {
+  clear_error();
+  vpq_linear_desc d;
+  std::memset(&d, 0, sizeof(d));
+  d.w = w;
+  d.scales = scales;
+  d.biases = biases;
+  d.x = x;
+  d.y = y;
+  d.K = K;
+  d.N = N;
+  d.M = M;
+  return launch_w8("affine_qmv_w8g64", d, stream);
+}
+
+extern "C" int vpq_affine_qmv_w8g64_bf16_fused(const vpq_linear_desc* desc_host, void* stream) {
+  clear_error();
+  if (!desc_host) { return fail(VPQ_ERR_INVALID_ARG, "affine_qmv_w8g64 (fused store): null descriptor"); }
+  return launch_w8("affine_qmv_w8g64 (fused store)", *desc_host, stream);
 }

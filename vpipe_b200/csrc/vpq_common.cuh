@@ -53,6 +53,8 @@ int ensure_dynamic_smem(const void* func, int* granted, size_t bytes);
 int qmv_status_read(cudaStream_t st, uint32_t* out);
 int qmvb_status_read(cudaStream_t st, uint32_t* out);
 int qmv8_status_read(cudaStream_t st, uint32_t* out);
+// The fused-store part of a GEMV descriptor's validation (epilogue code, aux / y3 / row counts).
+int qmv_check_store(const char* who, const vpq_linear_desc& d);
 // Same for the cross-GPU barrier of the fused column-split (nsplit.cu).
 int nsplit_status_read(cudaStream_t st, uint32_t* out);
 
@@ -83,6 +85,54 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
 // to bf16 (gpu-kernels/metal/quant/affine_dequant.metal:49-52).
 __device__ __forceinline__ float dequant_f32(float s, uint32_t q, float b) {
   return __fmaf_rn(s, (float)q, b);
+}
+
+// gelu_pytorch_tanh: 0.5 x (1 + tanh(sqrt(2 / pi) (x + 0.044715 x^3))), the activation of the
+// reference's geglu stores (affine_qmv.metal:1421-1429, ops/llm_elementwise.metal:388-407).
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float t = tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x));
+  return 0.5f * x * (1.0f + t);
+}
+
+// What a GEMV does with a row's f32 sum: the reference's fused decode stores (VPQ_EPILOGUE_*;
+// affine_qmv.metal:265-283,347-363,405-516,806-906,1352-1448). Called by lanes 0..15 of a warp,
+// lane = row within the 16-row tile; the gated stores pair lanes 2j, 2j + 1.
+enum : int { kEpiNone = 0, kEpiAdd = 1, kEpiSwiglu = 2, kEpiQkv = 3, kEpiGeglu = 4, kEpiGeluMul = 5 };
+
+__device__ __forceinline__ void fused_store(int epi, float v, int row, int N, int lane, __nv_bfloat16* y,
+                                            const uint16_t* aux, __nv_bfloat16* y3, int q_rows, int k_rows) {
+  if (epi == kEpiNone) {
+    if (row < N) { y[row] = __float2bfloat16_rn(v); }
+  } else if (epi == kEpiAdd) {
+    // the sum is rounded to bf16 first, then added to the residual in bf16, as the reference does
+    if (row < N) {
+      const float r = __uint_as_float((uint32_t)aux[row] << 16);
+      y[row] = __float2bfloat16_rn(__bfloat162float(__float2bfloat16_rn(v)) + r);
+    }
+  } else if (epi == kEpiSwiglu) {
+    // rows 2j, 2j+1 are gate j, up j: one output silu(gate) * up from the unrounded sums
+    const float up = __shfl_down_sync(0x0000ffffu, v, 1);
+    if ((lane & 1) == 0 && row + 1 < N) { y[row >> 1] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * up); }
+  } else if (epi == kEpiGeglu) {
+    // as above with the tanh form of gelu on the gate
+    const float up = __shfl_down_sync(0x0000ffffu, v, 1);
+    if ((lane & 1) == 0 && row + 1 < N) { y[row >> 1] = __float2bfloat16_rn(gelu_tanh(v) * up); }
+  } else if (epi == kEpiGeluMul) {
+    // gelu of the bf16-rounded sum, times the multiplier: what a separate pass over y would compute
+    if (row < N) {
+      const float m = __uint_as_float((uint32_t)aux[row] << 16);
+      y[row] = __float2bfloat16_rn(gelu_tanh(__bfloat162float(__float2bfloat16_rn(v))) * m);
+    }
+  } else {
+    const int qk = q_rows + k_rows;
+    if (row < q_rows) {
+      y[row] = __float2bfloat16_rn(v);
+    } else if (row < qk) {
+      reinterpret_cast<__nv_bfloat16*>(const_cast<uint16_t*>(aux))[row - q_rows] = __float2bfloat16_rn(v);
+    } else if (row < N) {
+      y3[row - qk] = __float2bfloat16_rn(v);
+    }
+  }
 }
 
 __device__ __forceinline__ uint4 ldg_stream_v4(const void* p) {

@@ -120,6 +120,25 @@ def qmv_w8(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
     return out
 
 
+def qmv_w8_fused(codes, scales, biases, x, y, store, stream=None):
+    """The 8-bit GEMV with a fused store (vpq_affine_qmv_w8g64_bf16_fused); `store` as in qmv_set, `y`
+    the (first) output tensor."""
+    N, Kw = codes.shape
+    K = Kw * 4
+    d = _lib.LinearDesc()
+    d.w, d.scales, d.biases, d.x, d.y = _ptr(codes), _ptr(scales), _ptr(biases), _ptr(x), _ptr(y)
+    d.K, d.N, d.M = K, N, x.numel() // K
+    d.epilogue = EPILOGUES[store["epilogue"]]
+    if store.get("aux") is not None:
+        d.aux = _ptr(store["aux"])
+    if store.get("y3") is not None:
+        d.y3 = _ptr(store["y3"])
+    d.q_rows, d.k_rows = store.get("q_rows", 0), store.get("k_rows", 0)
+    with torch.cuda.device(x.device):
+        check(lib().vpq_affine_qmv_w8g64_bf16_fused(C.byref(d), _stream(stream)))
+    return y
+
+
 def qmv_batch_rows(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
     """x [M, K] with small M: the rows share one stream of the weights (vpq_affine_qmv_batch_w4g64_bf16)."""
     N, Kw = codes.shape
