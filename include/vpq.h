@@ -275,6 +275,16 @@ int vpq_affine_qmm_swiglu_w8g64_bf16(const uint32_t* w, const void* scales, cons
 int vpq_affine_qmm_geglu_w8g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
                                     void* y, int64_t K, int64_t N, int64_t M, void* stream);
 
+/* SwiGLU GEMM writing into a column block of a wider buffer: y[m * out_stride + out_off + j], j in
+ * [0, N/2); out_stride 0 means the contiguous N/2 (then out_off must be 0). Lets a block write its
+ * MLP activations next to other columns with no concat. bits 4 or 8. Replaces
+ * affine_qmm_swiglu_w4g64_bm64_rs / affine_qmm_swiglu_w8g64_bm64_rs (slot 8 = out_stride, 9 = out_off),
+ * gpu-kernels/metal/quant/affine_qmm_steel.metal:657-770,920-947,1815-1837. Stores are 16-byte
+ * vectors when out_stride, out_off and N/2 are multiples of 8, element-wise otherwise. */
+int vpq_affine_qmm_swiglu_bf16_rs(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                                  void* y, int64_t K, int64_t N, int64_t M, int bits, int64_t out_stride,
+                                  int64_t out_off, void* stream);
+
 /* Grouped (mixture-of-experts) GEMMs for prefill. The (token, expert) pairs are sorted by expert
  * and each expert's block is padded to whole row tiles of vpq_qmm_grouped_tile_rows() rows (128;
  * the reference pads to its BM of 32 / 64): M is the padded row count, tile2e [ceil(M / tile)] the
@@ -331,15 +341,21 @@ const char* vpq_function_name(const vpq_function* fn);
  *   QMV add  : as QMV, 7:residual                       affine_qmv.metal:347-363
  *   QMV / QMM swiglu: as QMV / QMM (N = 2 ffn, y is [M, N/2])   affine_qmv.metal:891-906, affine_qmm_steel.metal:801-827
  *   QMV qkv  : 0:w 1:scales 2:biases 3:x 4:q 5:k 6:v; K, q_rows, k_rows, v_rows   affine_qmv.metal:492-511
+ *   QMM swiglu, strided store: as QMM swiglu; out_stride, out_off (the reference's slots 8, 9)   affine_qmm_steel.metal:925-947
+ *   grouped QMM (down): as QMM (x sorted), 8:tile2e 9:sdst; experts, rows = rows of y   affine_qmm_steel.metal:1042-1064
+ *   grouped QMM swiglu / geglu: as QMM (x the hidden), 8:tile2e 9:srow 10:scratch [M, K]; experts, rows = rows of x
+ *                                                       affine_qmm_steel.metal:1266-1336
  *   dequant  : 0:w 1:scales 2:biases 3:ydeq             affine_dequant.metal:14
  *   quant    : 0:x 1:w 2:scales_f16 3:biases_f16        affine_dequant.metal:288-296
  * Replaces ComputeEncoder::set_function/set_buffer/set_constant/dispatch,
  * apple-silicon/metal-compute/compute-encoder.h:80-83,188. */
 typedef struct vpq_dispatch_args {
-  const void* buffers[8];
+  const void* buffers[12];
   int64_t K, N, M;
   float clip;
   int64_t q_rows, k_rows, v_rows; /* QMV qkv only */
+  int64_t out_stride, out_off;    /* QMM swiglu with a strided store only */
+  int64_t experts, rows;          /* grouped QMM only: experts in w; rows of y (down) or of the hidden (gate|up) */
 } vpq_dispatch_args;
 int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* args, void* stream);
 

@@ -132,10 +132,10 @@ class ComputeEncoder {
  public:
   void set_function(const ComputeFunction& fn) { _fn = fn; }
   void set_buffer(int index, const SharedBuffer& buf, std::size_t byte_offset = 0) {
-    if (index >= 0 && index < 8) { _args.buffers[index] = static_cast<const char*>(buf.contents()) + byte_offset; }
+    if (index >= 0 && index < 12) { _args.buffers[index] = static_cast<const char*>(buf.contents()) + byte_offset; }
   }
   void set_buffer(int index, const void* device_ptr) {
-    if (index >= 0 && index < 8) { _args.buffers[index] = device_ptr; }
+    if (index >= 0 && index < 12) { _args.buffers[index] = device_ptr; }
   }
   // The reference numbers the int constants after the buffers: QMV 5:K 6:N (7: residual buffer of
   // _add, total rows of _batch), QMM 5:K 6:N 7:M, dequant 4:K 5:N, quant 4:K 5:N 6:clip.
@@ -145,6 +145,16 @@ class ComputeEncoder {
   void set_m(int64_t M) { _args.M = M; }
   void set_clip(float clip) { _args.clip = clip; }
   // affine_qmv_qkv_w4g64 numbers its constants 7:K 8:q_rows 9:k_rows 10:v_rows (outputs in slots 4..6)
+  // affine_qmm_swiglu_w4g64_bm64_rs: constants 8:out_stride 9:out_off
+  void set_out_block(int64_t out_stride, int64_t out_off) {
+    _args.out_stride = out_stride;
+    _args.out_off = out_off;
+  }
+  // the grouped GEMMs: experts in w; rows of y (down) or of the hidden (gate|up)
+  void set_grouped(int64_t experts, int64_t rows) {
+    _args.experts = experts;
+    _args.rows = rows;
+  }
   void set_qkv_rows(int64_t q_rows, int64_t k_rows, int64_t v_rows) {
     _args.q_rows = q_rows;
     _args.k_rows = k_rows;

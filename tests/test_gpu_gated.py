@@ -191,3 +191,36 @@ def test_qmv_w8_fused_by_reference_names(vpq, oracle_mod):
     ops.dispatch(ops.function("affine_qmv_bf16", "affine_qmv_qkv_w8g64"),
                  {0: d[0], 1: d[1], 2: d[2], 3: d[3], 4: yq, 5: yk, 6: yv}, K=K, q_rows=128, k_rows=64, v_rows=64)
     assert torch.equal(torch.cat([yq, yk, yv], dim=1), plain)
+
+
+# ------------------------------------------------------- SwiGLU GEMM into a column block
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("M,K,N,stride,off", [(256, 512, 512, 1024, 512), (300, 256, 154, 203, 61), (130, 64, 64, 32, 0)])
+def test_qmm_swiglu_into_a_column_block(vpq, oracle_mod, bits, M, K, N, stride, off):
+    """affine_qmm_swiglu_w4g64_bm64_rs / _w8g64_bm64_rs (affine_qmm_steel.metal:657-770,925-947): the
+    values of the contiguous call, at y[m * out_stride + out_off + j]; nothing else is written."""
+    ops = vpq.ops
+    if bits == 4:
+        d, _ = _linear(oracle_mod, N, K, M, 8900 + M + N)
+    else:
+        _, d = _w8_linear(oracle_mod, N, K, M, 8900 + M + N)
+    want = ops.qmm_swiglu(*d, bits=bits)
+    out = torch.full((M, stride), -3.0, dtype=torch.bfloat16, device=dev())
+    ops.qmm_swiglu_into(*d, out, off, bits=bits)
+    assert ops.device_status() == 0
+    assert torch.equal(out[:, off:off + N // 2], want)
+    assert torch.all(out[:, :off] == -3.0) and torch.all(out[:, off + N // 2:] == -3.0)
+    name = f"affine_qmm_swiglu_w{bits}g64_bm64_rs"
+    out2 = torch.full((M, stride), -3.0, dtype=torch.bfloat16, device=dev())
+    ops.dispatch(ops.function("affine_qmm_steel_bf16", name), {0: d[0], 1: d[1], 2: d[2], 3: d[3], 4: out2},
+                 K=K, N=N, M=M, out_stride=stride, out_off=off)
+    assert torch.equal(out2, out)
+
+
+def test_qmm_swiglu_block_must_fit_its_row(vpq, oracle_mod):
+    ops = vpq.ops
+    d, _ = _linear(oracle_mod, 64, 64, 130, 8950)
+    out = torch.zeros((130, 40), dtype=torch.bfloat16, device=dev())
+    with pytest.raises(vpq.VpqError):
+        ops.qmm_swiglu_into(*d, out, 16)

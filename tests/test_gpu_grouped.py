@@ -127,3 +127,28 @@ def test_grouped_skips_padding_tiles_and_bad_experts(vpq, oracle_mod):
     assert ops.device_status() == 0
     assert torch.equal(y[:tile], ops.qmm(d[0][1], d[1][1], d[2][1], x[:tile].contiguous()))
     assert torch.all(y[tile:] == -3.0)
+
+
+def test_grouped_by_reference_names(vpq, oracle_mod):
+    ops = vpq.ops
+    tile = ops.qmm_grouped_tile_rows()
+    T, E, top_k, K, N = 64, 3, 2, 128, 128
+    per, d = _experts(oracle_mod, E, N, K, 9500)
+    x = to_dev(synth.activations_bf16(T, K, 9501), torch.bfloat16)
+    eid = _routing(T, E, top_k, 9502)
+    tile2e, srow, sdst, npad = moe.sort_pairs(eid, E, top_k, tile)
+    t2e, sr, sd = to_dev(tile2e), to_dev(srow), to_dev(sdst)
+    lib = "affine_qmm_steel_bf16"
+    for entry, act in (("affine_qmm_grouped_swiglu_w4g64", "swiglu"), ("affine_qmm_grouped_geglu_w4g64", "geglu")):
+        want = ops.qmm_grouped_gated(*d, x, t2e, sr, act=act)
+        y = torch.zeros_like(want)
+        scratch = torch.empty((npad, K), dtype=torch.bfloat16, device=dev())
+        ops.dispatch(ops.function(lib, entry), {0: d[0], 1: d[1], 2: d[2], 3: x, 4: y, 8: t2e, 9: sr, 10: scratch},
+                     K=K, N=N, M=npad, experts=E, rows=T)
+        assert torch.equal(y, want), entry
+    xs = to_dev(synth.activations_bf16(npad, K, 9503), torch.bfloat16)
+    want = ops.qmm_grouped_down(*d, xs, t2e, sd, y_rows=T * top_k)
+    y = torch.zeros_like(want)
+    ops.dispatch(ops.function(lib, "affine_qmm_grouped_w4g64"), {0: d[0], 1: d[1], 2: d[2], 3: xs, 4: y, 8: t2e, 9: sd},
+                 K=K, N=N, M=npad, experts=E, rows=T * top_k)
+    assert torch.equal(y, want)

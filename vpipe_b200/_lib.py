@@ -27,6 +27,7 @@ SYMBOLS = [
     ("vpq_affine_quant", _i, [_vp, _i, _vp, _vp, _vp, _i64, _i64, _i, _i, C.c_float, _vp]),
     ("vpq_affine_dequant_bf16", _i, [_vp, _vp, _vp, _vp, _i64, _i64, _i, _i, _vp]),
     ("vpq_affine_qmm_swiglu_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    ("vpq_affine_qmm_swiglu_bf16_rs", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i, _i64, _i64, _vp]),
     ("vpq_qmm_grouped_tile_rows", _i, []),
     ("vpq_affine_qmm_grouped_w4g64_bf16", _i,
      [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _vp]),
@@ -73,9 +74,10 @@ SYMBOLS = [
 
 class DispatchArgs(C.Structure):
     """struct vpq_dispatch_args"""
-    _fields_ = [("buffers", C.c_void_p * 8), ("K", C.c_int64), ("N", C.c_int64),
+    _fields_ = [("buffers", C.c_void_p * 12), ("K", C.c_int64), ("N", C.c_int64),
                 ("M", C.c_int64), ("clip", C.c_float), ("q_rows", C.c_int64),
-                ("k_rows", C.c_int64), ("v_rows", C.c_int64)]
+                ("k_rows", C.c_int64), ("v_rows", C.c_int64), ("out_stride", C.c_int64),
+                ("out_off", C.c_int64), ("experts", C.c_int64), ("rows", C.c_int64)]
 
 
 class LinearDesc(C.Structure):

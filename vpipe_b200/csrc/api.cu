@@ -191,7 +191,7 @@ extern "C" size_t vpq_scale_bytes(int N, int K, int group) {
 struct vpq_function_s {
   const char* library;
   const char* entry;
-  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64, 66..69 qmv w8g64 add / swiglu / qkv / gelu*mul; 10 + code: quant / dequant twins (see fmt_*)
+  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64, 66..69 qmv w8g64 add / swiglu / qkv / gelu*mul, 70 / 71 qmm swiglu strided store w4 / w8, 72..74 grouped qmm down / swiglu / geglu; 10 + code: quant / dequant twins (see fmt_*)
 };
 
 // The reference selects the element type with the library-name suffix and
@@ -223,6 +223,11 @@ static const vpq_function_s g_functions[] = {
     {"affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64", 8},
     {"affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64_bm64", 8},
     {"affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64_bm128", 8},
+    {"affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64_bm64_rs", 70},
+    {"affine_qmm_steel_bf16", "affine_qmm_swiglu_w8g64_bm64_rs", 71},
+    {"affine_qmm_steel_bf16", "affine_qmm_grouped_w4g64", 72},
+    {"affine_qmm_steel_bf16", "affine_qmm_grouped_swiglu_w4g64", 73},
+    {"affine_qmm_steel_bf16", "affine_qmm_grouped_geglu_w4g64", 74},
     {"affine_qmm_steel_bf16", "affine_qmm_geglu_w4g64", 63},
     {"affine_qmm_steel_bf16", "affine_qmm_swiglu_w8g64", 64},
     {"affine_qmm_steel_bf16", "affine_qmm_swiglu_w8g64_bm64", 64},
@@ -296,6 +301,24 @@ extern "C" int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* a, 
     case 9:
       return vpq_affine_qmv_batch_w4g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
                                              const_cast<void*>(b[4]), a->K, a->N, a->M < 1 ? 1 : a->M, stream);
+    case 72:
+      return vpq_affine_qmm_grouped_w4g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
+                                               const_cast<void*>(b[4]), a->K, a->N, a->M, static_cast<const int*>(b[8]),
+                                               static_cast<const int*>(b[9]), a->experts, a->rows, stream);
+    case 73:
+      return vpq_affine_qmm_grouped_swiglu_w4g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
+                                                      const_cast<void*>(b[4]), a->K, a->N, a->M,
+                                                      static_cast<const int*>(b[8]), static_cast<const int*>(b[9]),
+                                                      a->experts, a->rows, const_cast<void*>(b[10]), stream);
+    case 74:
+      return vpq_affine_qmm_grouped_geglu_w4g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
+                                                     const_cast<void*>(b[4]), a->K, a->N, a->M,
+                                                     static_cast<const int*>(b[8]), static_cast<const int*>(b[9]),
+                                                     a->experts, a->rows, const_cast<void*>(b[10]), stream);
+    case 70:
+    case 71:
+      return vpq_affine_qmm_swiglu_bf16_rs(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3], const_cast<void*>(b[4]),
+                                           a->K, a->N, a->M, fn->kind == 71 ? 8 : 4, a->out_stride, a->out_off, stream);
     case 66:
     case 67:
     case 68:

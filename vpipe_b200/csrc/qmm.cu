@@ -713,8 +713,13 @@ extern "C" int vpq_affine_qmm_w4g64_bf16(const uint32_t* w, const void* scales, 
 namespace {
 // Gated GEMMs: gate / up rows interleaved in w, y = act(gate) * up, [M, N / 2].
 int qmm_gated(const char* who, int bits, int act, const uint32_t* w, const void* scales, const void* biases,
-              const void* x, void* y, int64_t K, int64_t N, int64_t M, void* stream) {
+              const void* x, void* y, int64_t K, int64_t N, int64_t M, void* stream, int64_t out_stride = 0,
+              int64_t out_off = 0) {
   clear_error();
+  if (out_stride < 0 || out_off < 0 || (out_stride > 0 && out_off + N / 2 > out_stride) ||
+      (out_stride == 0 && out_off != 0) || out_stride > (1ll << 30)) {
+    return fail(VPQ_ERR_INVALID_ARG, "%s: the block [out_off, out_off + N/2) must lie inside a row of out_stride", who);
+  }
   if (!w || !scales || !biases || !x || !y) { return fail(VPQ_ERR_INVALID_ARG, "%s: null pointer", who); }
   if (K <= 0 || N <= 0 || M <= 0 || (K % 64) != 0 || (N % 2) != 0) {
     return fail(VPQ_ERR_INVALID_ARG, "%s: need K>0, M>0, K%%64==0 and an even N>0 (K=%lld N=%lld M=%lld)", who,
@@ -732,8 +737,8 @@ int qmm_gated(const char* who, int bits, int act, const uint32_t* w, const void*
   two_cta::OutSpec out = {};
   out.base[0] = static_cast<__nv_bfloat16*>(y);
   out.count = 1;
-  out.col0 = 0;
-  out.ld = N / 2;
+  out.col0 = (int)out_off;
+  out.ld = out_stride > 0 ? out_stride : N / 2;
   out.swiglu = act;
   const uint16_t* s16 = static_cast<const uint16_t*>(scales);
   const uint16_t* b16 = static_cast<const uint16_t*>(biases);
@@ -747,6 +752,17 @@ extern "C" int vpq_affine_qmm_swiglu_w4g64_bf16(const uint32_t* w, const void* s
                                                 const void* x, void* y, int64_t K, int64_t N, int64_t M,
                                                 void* stream) {
   return qmm_gated("affine_qmm_swiglu_w4g64", 4, 1, w, scales, biases, x, y, K, N, M, stream);
+}
+
+extern "C" int vpq_affine_qmm_swiglu_bf16_rs(const uint32_t* w, const void* scales, const void* biases,
+                                            const void* x, void* y, int64_t K, int64_t N, int64_t M, int bits,
+                                            int64_t out_stride, int64_t out_off, void* stream) {
+  if (bits != 4 && bits != 8) {
+    clear_error();
+    return fail(VPQ_ERR_INVALID_ARG, "affine_qmm_swiglu (strided store): bits must be 4 or 8");
+  }
+  return qmm_gated(bits == 8 ? "affine_qmm_swiglu_w8g64_rs" : "affine_qmm_swiglu_w4g64_rs", bits, 1, w, scales, biases,
+                   x, y, K, N, M, stream, out_stride, out_off);
 }
 
 extern "C" int vpq_affine_qmm_geglu_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,

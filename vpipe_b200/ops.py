@@ -309,6 +309,18 @@ def qmm_swiglu(codes, scales, biases, x, out=None, stream=None, act="swiglu", bi
     return out
 
 
+def qmm_swiglu_into(codes, scales, biases, x, out, out_off, bits=4, stream=None) -> torch.Tensor:
+    """silu(gate) * up written into columns [out_off, out_off + N/2) of the row-major `out` [M, stride]
+    (vpq_affine_qmm_swiglu_bf16_rs)."""
+    N, Kw = codes.shape
+    K = Kw * (32 // bits)
+    M = x.numel() // K
+    with torch.cuda.device(x.device):
+        check(lib().vpq_affine_qmm_swiglu_bf16_rs(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x), _ptr(out), K, N,
+                                                  M, bits, out.shape[-1], out_off, _stream(stream)))
+    return out
+
+
 def qmm_grouped_tile_rows() -> int:
     return int(lib().vpq_qmm_grouped_tile_rows())
 
@@ -360,7 +372,8 @@ def function(library: str, entry: str):
     return lib().vpq_function_lookup(library.encode(), entry.encode())
 
 
-def dispatch(fn, buffers, K=0, N=0, M=0, clip=1.0, q_rows=0, k_rows=0, v_rows=0, stream=None) -> None:
+def dispatch(fn, buffers, K=0, N=0, M=0, clip=1.0, q_rows=0, k_rows=0, v_rows=0, out_stride=0, out_off=0,
+             experts=0, rows=0, stream=None) -> None:
     """One dispatch with the reference's slot numbering (see include/vpq.h). `buffers` is a list
     indexed by slot, or a dict {slot: tensor}."""
     a = _lib.DispatchArgs()
@@ -369,4 +382,5 @@ def dispatch(fn, buffers, K=0, N=0, M=0, clip=1.0, q_rows=0, k_rows=0, v_rows=0,
         a.buffers[i] = _ptr(t) if t is not None else None
     a.K, a.N, a.M, a.clip = K, N, M, clip
     a.q_rows, a.k_rows, a.v_rows = q_rows, k_rows, v_rows
+    a.out_stride, a.out_off, a.experts, a.rows = out_stride, out_off, experts, rows
     check(lib().vpq_dispatch(fn, C.byref(a), _stream(stream)))
