@@ -205,6 +205,13 @@ int vpq_affine_qmv_w4g64_bf16_batch(const vpq_linear_desc* descs_host, int count
  * 540-560,789-805,3122-3160). */
 int vpq_affine_qmv_w8g64_bf16_fused(const vpq_linear_desc* desc_host, void* stream);
 
+/* The small-batch GEMV (w4 g64, rows of x share one stream of the weights) and the group-32 GEMV with
+ * a fused store: one descriptor, any VPQ_EPILOGUE_*. Replace affine_qmv_batch_swiglu_w4g64,
+ * affine_qmv_w4g32_add, affine_qmv_geglu_w4g32, affine_qmv_gelu_mul_w4g32
+ * (gpu-kernels/metal/quant/affine_qmv.metal:367-385,770-787,1451-1470,2871). */
+int vpq_affine_qmv_batch_w4g64_bf16_fused(const vpq_linear_desc* desc_host, void* stream);
+int vpq_affine_qmv_w4g32_bf16_fused(const vpq_linear_desc* desc_host, void* stream);
+
 /* A list of independent GEMVs run as ONE launch: the kernel walks the row tiles of all problems
  * back to back, so there is no launch gap and no per-problem ramp-up, and problems that read the
  * same x (q | k | v, gate | up) stage it once. "Encode once, commit many": the analogue of

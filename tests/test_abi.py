@@ -117,6 +117,8 @@ def test_argument_validation_happens_before_any_device_work(vpq):
     assert L.vpq_affine_qmm_swiglu_w8g64_bf16(p16, p16, p16, p16, p16, 96, 8, 4, None) == INVALID
     assert L.vpq_affine_qmm_geglu_w8g64_bf16(None, p16, p16, p16, p16, 64, 8, 4, None) == INVALID
     assert L.vpq_affine_qmv_w8g64_bf16_fused(None, None) == INVALID
+    assert L.vpq_affine_qmv_batch_w4g64_bf16_fused(None, None) == INVALID
+    assert L.vpq_affine_qmv_w4g32_bf16_fused(None, None) == INVALID
     assert L.vpq_affine_qmm_swiglu_bf16_rs(p16, p16, p16, p16, p16, 64, 64, 4, 4, 40, 16, None) == INVALID
     assert L.vpq_affine_qmm_swiglu_bf16_rs(p16, p16, p16, p16, p16, 64, 64, 4, 5, 64, 0, None) == INVALID
     assert L.vpq_qmm_grouped_tile_rows() == 128

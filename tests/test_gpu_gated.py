@@ -224,3 +224,47 @@ def test_qmm_swiglu_block_must_fit_its_row(vpq, oracle_mod):
     out = torch.zeros((130, 40), dtype=torch.bfloat16, device=dev())
     with pytest.raises(vpq.VpqError):
         ops.qmm_swiglu_into(*d, out, 16)
+
+
+# --------------------------------- fused stores of the small-batch and the group-32 GEMVs
+
+def _stores_against_plain(ops, d, plain, M, N, kind, seed):
+    """Every fused store of a GEMV against the same GEMV's plain output `plain` [M, N]."""
+    aux = to_dev(synth.activations_bf16(M, N, seed), torch.bfloat16)
+    z = lambda *shape: torch.full(shape, 1e30, dtype=torch.bfloat16, device=dev())  # no sum gets near it
+    y = ops.qmv_w8_fused(*d, z(M, N), {"epilogue": "add", "aux": aux}, kind=kind)
+    assert torch.equal(y, (plain.float() + aux.float()).to(torch.bfloat16))
+    y = ops.qmv_w8_fused(*d, z(M, N), {"epilogue": "gelu_mul", "aux": aux}, kind=kind)
+    sep = (_gelu_t(plain.float()) * aux.float()).to(torch.bfloat16)
+    assert float((y == sep).float().mean()) > 0.98
+    q_rows, k_rows = (N // 2) & ~1, N // 4
+    yq, yk, yv = z(M, q_rows), z(M, k_rows), z(M, N - q_rows - k_rows)
+    ops.qmv_w8_fused(*d, yq, {"epilogue": "qkv", "aux": yk, "y3": yv, "q_rows": q_rows, "k_rows": k_rows}, kind=kind)
+    assert torch.equal(torch.cat([yq, yk, yv], dim=1), plain)
+    g, u = plain.float()[:, 0::2], plain.float()[:, 1::2]
+    for name, act in (("swiglu", lambda t: t / (1.0 + torch.exp(-t))), ("geglu", _gelu_t)):
+        y = ops.qmv_w8_fused(*d, z(M, N // 2), {"epilogue": name}, kind=kind)
+        assert torch.all(y.float().abs() < 1e29)  # every output written
+        # the gated stores use the unrounded sums; against the bf16-rounded ones they agree to ~2 ulp
+        e = y.float() - (act(g) * u)
+        assert float(e.abs().max()) <= 2e-2 * float((act(g) * u).abs().max()) + 1e-6, name
+
+
+@pytest.mark.parametrize("K,N,M", [(4096, 1024, 4), (1024, 96, 3), (2048, 40, 2)])
+def test_qmv_batch_fused_stores(vpq, oracle_mod, K, N, M):
+    """affine_qmv_batch_swiglu_w4g64 and the other stores on rows that share one weight stream."""
+    d, _ = _linear(oracle_mod, N, K, M, 9600 + N + K)
+    plain = vpq.ops.qmv_batch_rows(*d)
+    _stores_against_plain(vpq.ops, d, plain, M, N, "batch", 9601 + N)
+
+
+@pytest.mark.parametrize("K,N,M", [(4096, 1024, 2), (96, 34, 1), (1024, 64, 3)])
+def test_qmv_w4g32_fused_stores(vpq, oracle_mod, K, N, M):
+    """affine_qmv_w4g32_add, affine_qmv_geglu_w4g32, affine_qmv_gelu_mul_w4g32."""
+    wb = synth.f32_to_bf16_bits(synth.weight_f32(N, K, 9700 + N + K))
+    codes, s16, b16 = oracle_mod.quant(wb, 4, 32)
+    s, b = oracle_mod.f16_to_bf16(s16), oracle_mod.f16_to_bf16(b16)
+    x = synth.activations_bf16(M, K, 9701 + N)
+    d = (to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16), to_dev(x, torch.bfloat16))
+    plain = vpq.ops.qmv_g32(*d)
+    _stores_against_plain(vpq.ops, d, plain, M, N, "g32", 9702 + N)

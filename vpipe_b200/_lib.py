@@ -49,6 +49,8 @@ SYMBOLS = [
     ("vpq_affine_qmv_qkv_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
     ("vpq_affine_qmv_w4g64_bf16_batch", _i, [_vp, _i, _vp]),
     ("vpq_affine_qmv_w8g64_bf16_fused", _i, [_vp, _vp]),
+    ("vpq_affine_qmv_batch_w4g64_bf16_fused", _i, [_vp, _vp]),
+    ("vpq_affine_qmv_w4g32_bf16_fused", _i, [_vp, _vp]),
     ("vpq_affine_qmv_w4g64_bf16_set_noalloc", _i, [_vp, _i, _vp]),
     ("vpq_qmv_plan_bytes", C.c_size_t, [_vp, _i]),
     ("vpq_qmv_plan_create", _i, [_vp, _i, _vp, C.c_size_t, _vp, C.POINTER(_vp)]),

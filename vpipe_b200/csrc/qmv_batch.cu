@@ -89,6 +89,11 @@ struct alignas(64) BatchProblem {
   int K, N, M;
   int row_tiles;
   int scales_tma;
+  int epilogue;                // kEpi*: what the store does with a row's sums (see fused_store)
+  int q_rows, k_rows;
+  int y_pitch, aux_pitch, y3_pitch;  // elements between consecutive rows of x in y / aux / y3
+  const uint16_t* aux;
+  __nv_bfloat16* y3;
 };
 
 // GROUP = 64: columns = (row of x 0..3, group parity). GROUP = 32 (the reference's affine_qmv_w4g32,
@@ -432,7 +437,9 @@ affine_qmv_batch_w4_kernel(const __grid_constant__ BatchProblem P, int stages, i
           v += *reinterpret_cast<volatile float*>(&red[((size_t)(slot * kConsWarps + ww) * kMaxRows + m) * 16 + r]);
         }
         const int row = (tile << 4) + r;
-        if (m < M && row < N) { P.y[(size_t)m * N + row] = __float2bfloat16_rn(v); }
+        const bool live = m < M;  // every lane takes part in the store's shuffles; idle ones store nothing
+        fused_store(P.epilogue, v, row, live ? N : 0, r, P.y + (size_t)m * P.y_pitch, P.aux + (size_t)m * P.aux_pitch,
+                    P.y3 + (size_t)m * P.y3_pitch, live ? P.q_rows : 0, live ? P.k_rows : 0, 0xffffffffu);
       }
       __syncwarp();
       if (lane == 0) { red_cnt[slot] = 0; }
@@ -462,10 +469,17 @@ int rows_per_pass(int cap_kt) {
 // Passes of `per_pass` rows over one weight stream each. min_rows: the fewest rows this kernel
 // takes itself (group 64 hands single rows to the exact M = 1 kernel through `single`).
 template <int GROUP>
-int launch_batch(const char* who, const uint32_t* w, const void* scales, const void* biases, const void* x, void* y,
-                 int64_t K, int64_t N, int64_t M, int per_pass, cudaStream_t st,
-                 int (*single)(const uint32_t*, const void*, const void*, const void*, void*, int64_t, int64_t, int64_t,
-                               void*)) {
+int launch_batch(const char* who, const vpq_linear_desc& d, int per_pass, cudaStream_t st, bool single_rows_exact) {
+  const uint32_t* w = d.w;
+  const void *scales = d.scales, *biases = d.biases, *x = d.x;
+  void* y = d.y;
+  const int64_t K = d.K, N = d.N, M = d.M;
+  const bool gated = d.epilogue == VPQ_EPILOGUE_SWIGLU || d.epilogue == VPQ_EPILOGUE_GEGLU;
+  const int64_t y_pitch = gated ? N / 2 : d.epilogue == VPQ_EPILOGUE_QKV ? d.q_rows : N;
+  const int64_t aux_pitch = (d.epilogue == VPQ_EPILOGUE_ADD || d.epilogue == VPQ_EPILOGUE_GELU_MUL) ? N
+                            : d.epilogue == VPQ_EPILOGUE_QKV                                         ? d.k_rows
+                                                                                                     : 0;
+  const int64_t y3_pitch = d.epilogue == VPQ_EPILOGUE_QKV ? N - d.q_rows - d.k_rows : 0;
   const int cap_kt = (int)((K + 255) / 256) * 2;
   BatchProblem p;
   std::memset(&p, 0, sizeof(p));
@@ -491,14 +505,28 @@ int launch_batch(const char* who, const uint32_t* w, const void* scales, const v
   p.K = (int)K;
   p.N = (int)N;
   p.row_tiles = (int)((N + 15) / 16);
+  p.epilogue = d.epilogue;
+  p.q_rows = (int)d.q_rows;
+  p.k_rows = (int)d.k_rows;
+  p.y_pitch = (int)y_pitch;
+  p.aux_pitch = (int)aux_pitch;
+  p.y3_pitch = (int)y3_pitch;
   auto kern = affine_qmv_batch_w4_kernel<GROUP>;
   for (int64_t m0 = 0; m0 < M; m0 += per_pass) {
     const int rows = (int)((M - m0) < per_pass ? (M - m0) : per_pass);
     p.x = static_cast<const uint16_t*>(x) + m0 * K;
-    p.y = static_cast<__nv_bfloat16*>(y) + m0 * N;
+    p.y = static_cast<__nv_bfloat16*>(y) + m0 * y_pitch;
+    p.aux = d.aux ? static_cast<const uint16_t*>(d.aux) + m0 * aux_pitch : nullptr;
+    p.y3 = d.y3 ? static_cast<__nv_bfloat16*>(d.y3) + m0 * y3_pitch : nullptr;
     p.M = rows;
-    if (rows == 1 && single) {  // a single row left over: the exact M = 1 kernel
-      if (int rc = single(w, scales, biases, p.x, p.y, K, N, 1, st)) { return rc; }
+    if (rows == 1 && single_rows_exact) {  // a single row left over: the exact M = 1 kernel
+      vpq_linear_desc one = d;
+      one.x = p.x;
+      one.y = p.y;
+      one.aux = p.aux;
+      one.y3 = p.y3;
+      one.M = 1;
+      if (int rc = vpq_affine_qmv_w4g64_bf16_batch(&one, 1, st)) { return rc; }
       continue;
     }
     const size_t fixed = fixed_smem<GROUP>(rows, cap_kt);
@@ -560,26 +588,63 @@ int qmvb_status_read(cudaStream_t st, uint32_t* out) {
 
 using namespace vpq;
 
+namespace {
+vpq_linear_desc plain_desc(const uint32_t* w, const void* scales, const void* biases, const void* x, void* y, int64_t K,
+                           int64_t N, int64_t M) {
+  vpq_linear_desc d;
+  std::memset(&d, 0, sizeof(d));
+  d.w = w;
+  d.scales = scales;
+  d.biases = biases;
+  d.x = x;
+  d.y = y;
+  d.K = K;
+  d.N = N;
+  d.M = M;
+  return d;
+}
+
+int batch_g64(const char* who, const vpq_linear_desc& d, void* stream) {
+  if (int rc = check_batch_args(who, d.w, d.scales, d.biases, d.x, d.y, d.K, d.N, d.M, 64)) { return rc; }
+  if (int rc = qmv_check_store(who, d)) { return rc; }
+  if (int rc = require_sm100()) { return rc; }
+  const int per_pass = rows_per_pass<64>((int)((d.K + 255) / 256) * 2);
+  if (per_pass < 2 || d.M == 1) {  // long rows (K > 8192) do not fit twice in shared memory: one row at a time
+    return vpq_affine_qmv_w4g64_bf16_batch(&d, 1, stream);
+  }
+  return launch_batch<64>(who, d, per_pass, static_cast<cudaStream_t>(stream), true);
+}
+
+int gemv_g32(const char* who, const vpq_linear_desc& d, void* stream) {
+  if (int rc = check_batch_args(who, d.w, d.scales, d.biases, d.x, d.y, d.K, d.N, d.M, 32)) { return rc; }
+  if (int rc = qmv_check_store(who, d)) { return rc; }
+  if (int rc = require_sm100()) { return rc; }
+  const int per_pass = rows_per_pass<32>((int)((d.K + 255) / 256) * 2);  // 2 rows per weight stream where they fit
+  return launch_batch<32>(who, d, per_pass, static_cast<cudaStream_t>(stream), false);
+}
+}  // namespace
+
 extern "C" int vpq_affine_qmv_batch_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases,
                                                const void* x, void* y, int64_t K, int64_t N, int64_t M,
                                                void* stream) {
   clear_error();
-  if (int rc = check_batch_args("affine_qmv_batch_w4g64", w, scales, biases, x, y, K, N, M, 64)) { return rc; }
-  if (int rc = require_sm100()) { return rc; }
-  const int per_pass = rows_per_pass<64>((int)((K + 255) / 256) * 2);
-  if (per_pass < 2 || M == 1) {  // long rows (K > 8192) do not fit twice in shared memory: one row at a time
-    return vpq_affine_qmv_w4g64_bf16(w, scales, biases, x, y, K, N, M, stream);
-  }
-  return launch_batch<64>("affine_qmv_batch_w4g64", w, scales, biases, x, y, K, N, M, per_pass,
-                          static_cast<cudaStream_t>(stream), vpq_affine_qmv_w4g64_bf16);
+  return batch_g64("affine_qmv_batch_w4g64", plain_desc(w, scales, biases, x, y, K, N, M), stream);
+}
+
+extern "C" int vpq_affine_qmv_batch_w4g64_bf16_fused(const vpq_linear_desc* desc_host, void* stream) {
+  clear_error();
+  if (!desc_host) { return fail(VPQ_ERR_INVALID_ARG, "affine_qmv_batch_w4g64 (fused store): null descriptor"); }
+  return batch_g64("affine_qmv_batch_w4g64 (fused store)", *desc_host, stream);
 }
 
 extern "C" int vpq_affine_qmv_w4g32_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
                                          void* y, int64_t K, int64_t N, int64_t M, void* stream) {
   clear_error();
-  if (int rc = check_batch_args("affine_qmv_w4g32", w, scales, biases, x, y, K, N, M, 32)) { return rc; }
-  if (int rc = require_sm100()) { return rc; }
-  const int per_pass = rows_per_pass<32>((int)((K + 255) / 256) * 2);  // 2 rows per weight stream where they fit
-  return launch_batch<32>("affine_qmv_w4g32", w, scales, biases, x, y, K, N, M, per_pass,
-                          static_cast<cudaStream_t>(stream), nullptr);
+  return gemv_g32("affine_qmv_w4g32", plain_desc(w, scales, biases, x, y, K, N, M), stream);
+}
+
+extern "C" int vpq_affine_qmv_w4g32_bf16_fused(const vpq_linear_desc* desc_host, void* stream) {
+  clear_error();
+  if (!desc_host) { return fail(VPQ_ERR_INVALID_ARG, "affine_qmv_w4g32 (fused store): null descriptor"); }
+  return gemv_g32("affine_qmv_w4g32 (fused store)", *desc_host, stream);
 }

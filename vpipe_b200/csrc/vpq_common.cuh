@@ -99,8 +99,10 @@ __device__ __forceinline__ float gelu_tanh(float x) {
 // lane = row within the 16-row tile; the gated stores pair lanes 2j, 2j + 1.
 enum : int { kEpiNone = 0, kEpiAdd = 1, kEpiSwiglu = 2, kEpiQkv = 3, kEpiGeglu = 4, kEpiGeluMul = 5 };
 
+// `mask` names the lanes that make the call together (the gated stores shuffle among them).
 __device__ __forceinline__ void fused_store(int epi, float v, int row, int N, int lane, __nv_bfloat16* y,
-                                            const uint16_t* aux, __nv_bfloat16* y3, int q_rows, int k_rows) {
+                                            const uint16_t* aux, __nv_bfloat16* y3, int q_rows, int k_rows,
+                                            unsigned mask = 0x0000ffffu) {
   if (epi == kEpiNone) {
     if (row < N) { y[row] = __float2bfloat16_rn(v); }
   } else if (epi == kEpiAdd) {
@@ -111,11 +113,11 @@ __device__ __forceinline__ void fused_store(int epi, float v, int row, int N, in
     }
   } else if (epi == kEpiSwiglu) {
     // rows 2j, 2j+1 are gate j, up j: one output silu(gate) * up from the unrounded sums
-    const float up = __shfl_down_sync(0x0000ffffu, v, 1);
+    const float up = __shfl_down_sync(mask, v, 1);
     if ((lane & 1) == 0 && row + 1 < N) { y[row >> 1] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * up); }
   } else if (epi == kEpiGeglu) {
     // as above with the tanh form of gelu on the gate
-    const float up = __shfl_down_sync(0x0000ffffu, v, 1);
+    const float up = __shfl_down_sync(mask, v, 1);
     if ((lane & 1) == 0 && row + 1 < N) { y[row >> 1] = __float2bfloat16_rn(gelu_tanh(v) * up); }
   } else if (epi == kEpiGeluMul) {
     // gelu of the bf16-rounded sum, times the multiplier: what a separate pass over y would compute
