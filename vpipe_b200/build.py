@@ -71,7 +71,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if failed:
         raise RuntimeError("nvcc failed")
     if force or procs or _stale(OUT, objs):
-        cmd = [nvcc, "-shared", "-cudart", "static", "-o", OUT] + objs + ["-ldl", "-lpthread"]
+        cmd = [nvcc, "-shared", "-cudart", "static", "-gencode", "arch=compute_100a,code=sm_100a", "-o", OUT] + objs + ["-ldl", "-lpthread"]
         subprocess.run(cmd, check=True)
     return OUT
 
