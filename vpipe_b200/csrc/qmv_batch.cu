@@ -330,13 +330,22 @@ affine_qmv_batch_w4_kernel(const __grid_constant__ BatchProblem P, int stages, i
         const uint4 rb1 = *reinterpret_cast<const uint4*>(box + off_h1 + 1024);
         uint32_t sa[2], sb2[2], za[2], zb[2];  // per k tile: this lane's two groups' scales / biases, rows rho, rho + 8
         if (sz_tma) {
+          if constexpr (GROUP == 64) {  // the two k tiles' pairs are adjacent: one 8-byte load each
+            const unsigned char* q = sb + sz_off;
+            const uint2 a = *reinterpret_cast<const uint2*>(q), b = *reinterpret_cast<const uint2*>(q + kRow8);
+            const uint2 c = *reinterpret_cast<const uint2*>(q + kStageSZ / 2);
+            const uint2 e = *reinterpret_cast<const uint2*>(q + kStageSZ / 2 + kRow8);
+            sa[0] = a.x, sa[1] = a.y, sb2[0] = b.x, sb2[1] = b.y;
+            za[0] = c.x, za[1] = c.y, zb[0] = e.x, zb[1] = e.y;
+          } else {
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const unsigned char* q = sb + sz_off + h * (2 * GPT);
-            sa[h] = *reinterpret_cast<const uint32_t*>(q);
-            sb2[h] = *reinterpret_cast<const uint32_t*>(q + kRow8);
-            za[h] = *reinterpret_cast<const uint32_t*>(q + kStageSZ / 2);
-            zb[h] = *reinterpret_cast<const uint32_t*>(q + kStageSZ / 2 + kRow8);
+            for (int h = 0; h < 2; ++h) {
+              const unsigned char* q = sb + sz_off + h * (2 * GPT);
+              sa[h] = *reinterpret_cast<const uint32_t*>(q);
+              sb2[h] = *reinterpret_cast<const uint32_t*>(q + kRow8);
+              za[h] = *reinterpret_cast<const uint32_t*>(q + kStageSZ / 2);
+              zb[h] = *reinterpret_cast<const uint32_t*>(q + kStageSZ / 2 + kRow8);
+            }
           }
         } else {
           // clamped onto valid data: a clamped group meets x == 0, a clamped row is never stored
