@@ -25,7 +25,9 @@
  *    without a usable sm_100 device the compute entry points return
  *    VPQ_ERR_CUDA. The reference signals the same conditions with
  *    valid()==false / bool returns (compute-library.h:134, affine-quantizer.cc:57).
- *  - Alignment: w, scales, biases, x, y must be 16-byte aligned; K % 64 == 0.
+ *  - Alignment: w and x must be 16-byte aligned (the GEMMs also want y so); scales, biases and a
+ *    GEMV's y need 2 bytes only, but scales / biases ride on TMA (faster) when 16-byte aligned with
+ *    K % 512 == 0. K % 64 == 0. Violations return VPQ_ERR_ALIGNMENT.
  */
 #ifndef VPQ_H
 #define VPQ_H
@@ -171,10 +173,25 @@ typedef struct vpq_linear_desc {
   int64_t K, N, M;
   /* Fused store, VPQ_EPILOGUE_*; zero-initialised descriptors store y = x W^T as is. */
   int32_t epilogue;
-  int32_t reserved;
+  int32_t depends;      /* plans only: 1 = this GEMV reads (x, residual) what GEMVs earlier in the list write */
   const void* aux;      /* ADD: residual [M, N]; GELU_MUL: multiplier [M, N]; QKV: the k output [M, k_rows] (written) */
   void* y3;             /* QKV: the v output [M, N - q_rows - k_rows] */
   int64_t q_rows, k_rows;
+  /* RMSNorm prologue (w4 g64 GEMV only): with norm_w [K] (bf16, 16-byte aligned) every row of x is
+   * replaced, while it is staged on chip, by bf16(x * rsqrt(mean(x^2) + eps) * norm_w); the normed row
+   * never touches device memory. Replaces affine_qmv_qkv_rms_w4g64 (slot 4 = norm_w, 12 = eps),
+   * gpu-kernels/metal/quant/affine_qmv.metal:570-694; works with every store, not only QKV. */
+  const void* norm_w;
+  /* Expert gather (w4 g64 GEMV only): w / scales / biases are `experts` slabs [experts, N, ..] and row
+   * m (a (token, expert) pair) multiplies slab expert[m], an index the GPU reads when the kernel runs
+   * (the router's output never visits the host). Row m reads x row m / x_div (x_div = top_k for the
+   * gate|up GEMV, whose pairs of one token share its row; 0 or 1: row m) and writes y row m.
+   * Replaces affine_gather_qmv_swiglu_w4g64, affine_gather_qmv_geglu_w4g64 and
+   * affine_gather_down_qmv_w4g64 (slot 7 = pair_eid, 8 = top_k), affine_qmv.metal:908-955,1262-1291,1488-1521. */
+  const int32_t* expert;
+  int64_t experts;
+  int32_t x_div;
+  float eps;
 } vpq_linear_desc;
 
 /* What the GEMV does with each row's f32 sum (the reference's fused decode kernels):
@@ -329,12 +346,26 @@ int vpq_affine_qmm_grouped_geglu_w4g64_bf16(const uint32_t* w, const void* scale
  * apple-silicon/metal-compute/command-stream.h:92-99. */
 int vpq_device_status(void* stream, uint32_t* detail);
 
+/* Two probes of that reporting path, for tests and bring-up: each makes ONE bounded wait run out
+ * on purpose (nothing faults or hangs; the GPU stays usable) so that vpq_device_status can be seen
+ * to return VPQ_ERR_TIMEOUT and then clear. No counterpart in the reference beyond the
+ * Fence::wait_ok contract cited above.
+ * vpq_wait_probe: one thread waits on an mbarrier nobody arrives at, with the kernels' own wait
+ *   and `polls` polls of `hint_ns` each (polls <= 65536, hint_ns <= 100000); detail 0x7f7f.
+ * vpq_peer_barrier_probe: the cross-GPU flag barrier of the fused column split, run on one GPU
+ *   with `workspace` (256 bytes of device memory, 16-byte aligned) standing in for every rank's flag
+ *   table and rank `absent_rank` never publishing; the wait ends after max_polls polls of about
+ *   100 ns (max_polls <= 2^20); detail 0x20000 | 0x7700 | absent_rank. Synchronises `stream` once. */
+int vpq_wait_probe(uint32_t polls, uint32_t hint_ns, void* stream);
+int vpq_peer_barrier_probe(void* workspace, int world, int absent_rank, uint32_t max_polls, void* stream);
+
 /* --- calling by the reference's (library, entry) strings ------------------
  * Replaces MetalCompute::load_library(name).function(entry),
  * apple-silicon/metal-compute/metal-compute.h:301, compute-library.h:134.
  * Returns NULL for an unknown pair (the reference returns an invalid handle).
  * Known libraries: affine_qmv_bf16 (entries affine_qmv_w4g64, affine_qmv_w4g64_add,
- * affine_qmv_swiglu_w4g64, affine_qmv_qkv_w4g64), affine_qmm_steel_bf16, affine_qmm_mma_bf16,
+ * affine_qmv_swiglu_w4g64, affine_qmv_qkv_w4g64, affine_qmv_qkv_rms_w4g64, affine_gather_qmv_swiglu_w4g64,
+ * affine_gather_qmv_geglu_w4g64, affine_gather_down_qmv_w4g64, ...), affine_qmm_steel_bf16, affine_qmm_mma_bf16,
  * affine_dequant_bf16, affine_dequant (quantizer, f16 source). */
 typedef struct vpq_function_s vpq_function;
 const vpq_function* vpq_function_lookup(const char* library, const char* entry);
@@ -348,6 +379,8 @@ const char* vpq_function_name(const vpq_function* fn);
  *   QMV add  : as QMV, 7:residual                       affine_qmv.metal:347-363
  *   QMV / QMM swiglu: as QMV / QMM (N = 2 ffn, y is [M, N/2])   affine_qmv.metal:891-906, affine_qmm_steel.metal:801-827
  *   QMV qkv  : 0:w 1:scales 2:biases 3:x 4:q 5:k 6:v; K, q_rows, k_rows, v_rows   affine_qmv.metal:492-511
+ *   QMV norm + qkv: 0:w 1:scales 2:biases 3:x 4:norm_w 5:q 6:k 7:v; K, q_rows, k_rows, v_rows, eps   affine_qmv.metal:671-694
+ *   gathered expert QMV (gate|up with swiglu / geglu, down): as QMV, 7:pair_eid; experts, top_k (gate|up)   affine_qmv.metal:928-955,1265-1291
  *   QMM swiglu, strided store: as QMM swiglu; out_stride, out_off (the reference's slots 8, 9)   affine_qmm_steel.metal:925-947
  *   grouped QMM (down): as QMM (x sorted), 8:tile2e 9:sdst; experts, rows = rows of y   affine_qmm_steel.metal:1042-1064
  *   grouped QMM swiglu / geglu: as QMM (x the hidden), 8:tile2e 9:srow 10:scratch [M, K]; experts, rows = rows of x
@@ -362,7 +395,9 @@ typedef struct vpq_dispatch_args {
   float clip;
   int64_t q_rows, k_rows, v_rows; /* QMV qkv only */
   int64_t out_stride, out_off;    /* QMM swiglu with a strided store only */
-  int64_t experts, rows;          /* grouped QMM only: experts in w; rows of y (down) or of the hidden (gate|up) */
+  int64_t experts, rows;          /* grouped QMM / gathered QMV: experts in w; grouped QMM: rows of y (down) or of the hidden (gate|up) */
+  int64_t top_k;                  /* gathered gate|up QMV only: pairs per token */
+  float eps;                      /* QMV norm + qkv only */
 } vpq_dispatch_args;
 int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* args, void* stream);
 
@@ -394,11 +429,20 @@ int vpq_affine_qmm_w4g64_bf16_nsplit(vpq_comm* comm,
                                      void* stream);
 
 /* Fused form: no separate collective. y lives in a symmetric buffer that every rank has mapped
- * (CUDA IPC, one process per GPU); each rank's GEMM epilogue stores its column block straight
- * into row-major y[M, N] of EVERY rank with ordinary stores over NVLink, and a small flag
- * barrier over the same mapping follows on the stream. vpq_comm_alloc_symmetric is collective
- * (all ranks, same order) and is the one place this library allocates device memory; it owns
- * the buffer until vpq_comm_free_symmetric / vpq_comm_destroy. Needs M > 128, N % (8*world) == 0. */
+ * (CUDA IPC, one process per GPU). Each rank's GEMM stores its column block into its own row-major
+ * y[M, N]; sender warps of the same kernel copy every finished tile on to the peers' y with
+ * ordinary stores over NVLink while the tensor cores work on the next tiles. Two small flag
+ * barriers over the same mapping bracket the GEMM on the stream:
+ *   entry - no rank starts writing before every rank's stream has reached this call, so work a
+ *           peer enqueued earlier that still reads y (the previous step's result) is finished;
+ *   exit  - when the call's work completes on a rank's stream, every column block has arrived in
+ *           that rank's y.
+ * Ordering is therefore by stream order alone: enqueue the consumers of y after the call and the
+ * next call after them, on the same stream, on every rank; no host synchronisation and no second
+ * buffer are needed. All ranks must make the same sequence of calls on a communicator.
+ * vpq_comm_alloc_symmetric is collective (all ranks, same order) and is the one place this library
+ * allocates device memory; it owns the buffer until vpq_comm_free_symmetric / vpq_comm_destroy.
+ * Needs M > 128, N % (8*world) == 0. */
 int vpq_comm_alloc_symmetric(vpq_comm* comm, size_t bytes, void** local_ptr);
 int vpq_comm_free_symmetric(vpq_comm* comm, void* local_ptr);
 int vpq_affine_qmm_w4g64_bf16_nsplit_fused(vpq_comm* comm, const uint32_t* w_shard,

@@ -155,6 +155,12 @@ class ComputeEncoder {
     _args.experts = experts;
     _args.rows = rows;
   }
+  // the gathered expert GEMVs: experts in w, pairs per token (gate|up); the norm + q|k|v GEMV: epsilon
+  void set_gather(int64_t experts, int64_t top_k) {
+    _args.experts = experts;
+    _args.top_k = top_k;
+  }
+  void set_eps(float eps) { _args.eps = eps; }
   void set_qkv_rows(int64_t q_rows, int64_t k_rows, int64_t v_rows) {
     _args.q_rows = q_rows;
     _args.k_rows = k_rows;

@@ -247,6 +247,22 @@ def linear_f32(codes, s_bf16, b_bf16, x_bf16, mode: str = "fast") -> np.ndarray:
     return matmul_f32(x_bf16, dequant_f32(codes, s_bf16, b_bf16), mode)
 
 
+def rms_norm_bf16(x_bf16: np.ndarray, norm_w_bf16: np.ndarray, eps: float) -> np.ndarray:
+    """RMSNorm prologue of the fused norm + q|k|v GEMV, per row of x: sum of squares in f32,
+    `inv = rsqrt(total / K + eps)`, `tg_x[k] = T(float(x[k]) * inv * float(norm_w[k]))`
+    (gpu-kernels/metal/quant/affine_qmv.metal:601-621). Returns bf16 bit patterns. The f32 sum is
+    taken in double here and rounded once, so a kernel's summation order shows as at most one ulp
+    of `inv`."""
+    x = bf16_to_f32(np.ascontiguousarray(x_bf16, np.uint16))
+    w = bf16_to_f32(np.ascontiguousarray(norm_w_bf16, np.uint16)).reshape(1, -1)
+    x = x.reshape(-1, w.shape[1])
+    total = (x.astype(np.float64) ** 2).sum(axis=1, keepdims=True).astype(np.float32)
+    inv = (np.float32(1.0) / np.sqrt(total / np.float32(x.shape[1]) + np.float32(eps))).astype(np.float32)
+    y = (x * inv).astype(np.float32) * w
+    u = y.astype(np.float32).view(np.uint32).astype(np.uint64)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
 def fused_add(y_f32: np.ndarray, residual_bf16: np.ndarray) -> np.ndarray:
     """Residual store of the fused GEMV: the sum is rounded to bf16, the add happens in bf16
     (`T v = static_cast<T>(result[row]); if (ADD) v += residual[row];`,

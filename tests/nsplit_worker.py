@@ -62,6 +62,32 @@ def main():
         ok = ok and good
         if rank == 0:
             print(f"nsplit-fused world={world} M={M} K={K} N={N}: {'ok' if good else 'MISMATCH'}", flush=True)
+    # Back-to-back fused calls into ONE symmetric buffer with no host synchronisation: each result is
+    # consumed on the stream (copied aside) before the next call; the entry barrier of the next call
+    # must keep a fast rank from overwriting y under a slow rank's copy.
+    M, K, N = 2048, 2048, 4096
+    g = torch.Generator(device=dev).manual_seed(777)
+    w = (torch.randn((N, K), generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    xs = [torch.randn((M, K), generator=g, device=dev).to(torch.bfloat16) for _ in range(2)]
+    codes, s16, b16 = ops.quantize(w)
+    s, b = ops.scales_to_bf16(s16), ops.scales_to_bf16(b16)
+    fulls = [ops.qmm(codes, s, b, x) for x in xs]
+    lo, hi = shard.shard_rows(N, world, rank)
+    cs, ss, bs = codes[lo:hi].contiguous(), s[lo:hi].contiguous(), b[lo:hi].contiguous()
+    y_sym, y_ptr = comm.alloc_symmetric((M, N), torch.bfloat16)
+    keep = [torch.empty_like(y_sym) for _ in range(6)]
+    torch.cuda.synchronize()
+    dist.barrier()
+    for i in range(6):
+        comm.qmm_fused(cs, ss, bs, xs[i % 2], y_ptr)
+        keep[i].copy_(y_sym)
+        if rank == i % world:      # one rank lags behind in every step
+            torch.cuda._sleep(2_000_000)
+    torch.cuda.synchronize()
+    good = all(torch.equal(keep[i], fulls[i % 2]) for i in range(6))
+    ok = ok and good
+    if rank == 0:
+        print(f"nsplit-fused back-to-back world={world}: {'ok' if good else 'MISMATCH'}", flush=True)
     assert ops.device_status() == 0
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)

@@ -264,6 +264,38 @@ def test_qmm_full_size_against_dequant_then_dense(vpq, oracle_mod, tag, M, K, N)
     check_linear(oracle_mod, y, bits32(codes), bits16(s), bits16(b), bits16(x), rows=rows)
 
 
+# Every projection of the prefill / DiT configurations that is not covered above, at full size:
+# C3 v / gate / up (M = 2048), C4 qkv / proj / mlp_up (M = 4096), and the four C5 shapes at the full
+# M = 65280 (y up to 2.0 GB: row offsets near 2^31 bytes, the overflow class the reference guards
+# against in tests/unit-tests/minimax-h3-blocks.cc:1792-1812). The oracle runs on sampled rows that
+# include the first and last rows of the output and of interior row tiles.
+FULL_SHAPES = [("C3.v", 2048, 4096, 1024), ("C3.gate", 2048, 4096, 12288), ("C3.up", 2048, 4096, 12288),
+               ("C4.qkv", 4096, 4096, 12288), ("C4.proj", 4096, 4096, 4096), ("C4.mlp_up", 4096, 4096, 16384),
+               ("C5.qkv", 65280, 5120, 15360), ("C5.out", 65280, 5120, 5120),
+               ("C5.ffn_up", 65280, 5120, 13824), ("C5.ffn_down", 65280, 13824, 5120)]
+
+
+@pytest.mark.parametrize("tag,M,K,N", FULL_SHAPES)
+def test_qmm_full_configs_on_sampled_rows(vpq, oracle_mod, tag, M, K, N):
+    codes, s, b, x = _device_linear(vpq, N, K, M, synth.seed_for("cfg", tag))
+    y = torch.full((M, N), -5.0, dtype=torch.bfloat16, device=dev())
+    vpq.ops.qmm(codes, s, b, x, out=y)
+    assert vpq.ops.device_status() == 0
+    rng = np.random.Generator(np.random.Philox(key=synth.seed_for("rows", tag)))
+    n_rows = 96 if M > 8192 else 64
+    rows = np.unique(np.concatenate([rng.integers(0, M, n_rows), [0, 1, 127, 128, 255, 256, M // 2, M - 257,
+                                                                  M - 256, M - 129, M - 128, M - 2, M - 1]]))
+    idx = torch.from_numpy(rows).to(dev())
+    ys = y.index_select(0, idx)
+    xs = bits16(x.index_select(0, idx))
+    deq = oracle_mod.dequant_f32(bits32(codes), bits16(s), bits16(b))
+    ref = oracle_mod.matmul_f32(xs, deq, "fast")
+    e = oracle_mod.err_metrics(f32(ys), ref)
+    assert e["rel_l2"] < TOL and e["max_rel_rms"] < TOL, (tag, e)
+    # every element was written (none of the fill value left), checked on the device
+    assert int((y == -5.0).sum()) == 0
+
+
 def test_dispatch_by_reference_names(vpq, oracle_mod):
     """load_library(...).function(...) + slot-numbered dispatch gives the same bytes as the direct calls."""
     N, K, M = 256, 1024, 160

@@ -58,6 +58,8 @@ SYMBOLS = [
     ("vpq_qmv_plan_destroy", _i, [_vp]),
     ("vpq_affine_qmm_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     ("vpq_device_status", _i, [_vp, C.POINTER(C.c_uint32)]),
+    ("vpq_wait_probe", _i, [C.c_uint32, C.c_uint32, _vp]),
+    ("vpq_peer_barrier_probe", _i, [_vp, _i, _i, C.c_uint32, _vp]),
     ("vpq_function_lookup", _vp, [C.c_char_p, C.c_char_p]),
     ("vpq_function_name", C.c_char_p, [_vp]),
     ("vpq_dispatch", _i, [_vp, _vp, _vp]),
@@ -79,16 +81,18 @@ class DispatchArgs(C.Structure):
     _fields_ = [("buffers", C.c_void_p * 12), ("K", C.c_int64), ("N", C.c_int64),
                 ("M", C.c_int64), ("clip", C.c_float), ("q_rows", C.c_int64),
                 ("k_rows", C.c_int64), ("v_rows", C.c_int64), ("out_stride", C.c_int64),
-                ("out_off", C.c_int64), ("experts", C.c_int64), ("rows", C.c_int64)]
+                ("out_off", C.c_int64), ("experts", C.c_int64), ("rows", C.c_int64),
+                ("top_k", C.c_int64), ("eps", C.c_float)]
 
 
 class LinearDesc(C.Structure):
     """struct vpq_linear_desc"""
     _fields_ = [("w", C.c_void_p), ("scales", C.c_void_p), ("biases", C.c_void_p),
                 ("x", C.c_void_p), ("y", C.c_void_p), ("K", C.c_int64), ("N", C.c_int64),
-                ("M", C.c_int64), ("epilogue", C.c_int32), ("reserved", C.c_int32),
+                ("M", C.c_int64), ("epilogue", C.c_int32), ("depends", C.c_int32),
                 ("aux", C.c_void_p), ("y3", C.c_void_p), ("q_rows", C.c_int64),
-                ("k_rows", C.c_int64)]
+                ("k_rows", C.c_int64), ("norm_w", C.c_void_p), ("expert", C.c_void_p),
+                ("experts", C.c_int64), ("x_div", C.c_int32), ("eps", C.c_float)]
 
 
 class VpqError(RuntimeError):

@@ -18,7 +18,7 @@ CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libvpq.so")
 OBJ = os.path.join(HERE, "build")
 
-SOURCES = ["api.cu", "quant_dequant.cu", "qmv.cu", "qmv_batch.cu", "qmv_w8.cu", "qmm.cu", "nsplit.cu", "host.cu"]
+SOURCES = ["api.cu", "quant_dequant.cu", "qmv.cu", "qmv_batch.cu", "qmv_w8.cu", "qmm.cu", "nsplit.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -191,7 +191,7 @@ extern "C" size_t vpq_scale_bytes(int N, int K, int group) {
 struct vpq_function_s {
   const char* library;
   const char* entry;
-  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64, 66..69 qmv w8g64 add / swiglu / qkv / gelu*mul, 70 / 71 qmm swiglu strided store w4 / w8, 72..74 grouped qmm down / swiglu / geglu; 10 + code: quant / dequant twins (see fmt_*)
+  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64, 66..69 qmv w8g64 add / swiglu / qkv / gelu*mul, 70 / 71 qmm swiglu strided store w4 / w8, 72..74 grouped qmm down / swiglu / geglu, 75 qmv norm + qkv, 76..78 gathered expert qmv swiglu / geglu / down; 10 + code: quant / dequant twins (see fmt_*)
 };
 
 // The reference selects the element type with the library-name suffix and
@@ -203,6 +203,10 @@ static const vpq_function_s g_functions[] = {
     {"affine_qmv_bf16", "affine_qmv_w4g64_add", 5},
     {"affine_qmv_bf16", "affine_qmv_swiglu_w4g64", 6},
     {"affine_qmv_bf16", "affine_qmv_qkv_w4g64", 7},
+    {"affine_qmv_bf16", "affine_qmv_qkv_rms_w4g64", 75},
+    {"affine_qmv_bf16", "affine_gather_qmv_swiglu_w4g64", 76},
+    {"affine_qmv_bf16", "affine_gather_qmv_geglu_w4g64", 77},
+    {"affine_qmv_bf16", "affine_gather_down_qmv_w4g64", 78},
     {"affine_qmv_bf16", "affine_qmv_geglu_w4g64", 61},
     {"affine_qmv_bf16", "affine_qmv_gelu_mul_w4g64", 62},
     {"affine_qmv_bf16", "affine_qmv_w8g64", 58},
@@ -315,6 +319,38 @@ extern "C" int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* a, 
                                                      const_cast<void*>(b[4]), a->K, a->N, a->M,
                                                      static_cast<const int*>(b[8]), static_cast<const int*>(b[9]),
                                                      a->experts, a->rows, const_cast<void*>(b[10]), stream);
+    case 75:
+    case 76:
+    case 77:
+    case 78: {
+      vpq_linear_desc d;
+      std::memset(&d, 0, sizeof(d));
+      d.w = static_cast<const uint32_t*>(b[0]);
+      d.scales = b[1];
+      d.biases = b[2];
+      d.x = b[3];
+      d.K = a->K;
+      d.M = a->M < 1 ? 1 : a->M;
+      if (fn->kind == 75) {  // slot 4 = norm_w, 5..7 = q, k, v outputs, eps as a constant
+        d.norm_w = b[4];
+        d.eps = a->eps;
+        d.y = const_cast<void*>(b[5]);
+        d.epilogue = VPQ_EPILOGUE_QKV;
+        d.aux = b[6];
+        d.y3 = const_cast<void*>(b[7]);
+        d.q_rows = a->q_rows;
+        d.k_rows = a->k_rows;
+        d.N = a->q_rows + a->k_rows + a->v_rows;
+      } else {               // slot 7 = pair_eid [M]; the gate|up pairs of one token share its x row
+        d.y = const_cast<void*>(b[4]);
+        d.N = a->N;
+        d.expert = static_cast<const int32_t*>(b[7]);
+        d.experts = a->experts;
+        d.x_div = fn->kind == 78 ? 1 : (int32_t)(a->top_k < 1 ? 1 : a->top_k);
+        d.epilogue = fn->kind == 76 ? VPQ_EPILOGUE_SWIGLU : fn->kind == 77 ? VPQ_EPILOGUE_GEGLU : VPQ_EPILOGUE_NONE;
+      }
+      return vpq_affine_qmv_w4g64_bf16_batch(&d, 1, stream);
+    }
     case 70:
     case 71:
       return vpq_affine_qmm_swiglu_bf16_rs(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3], const_cast<void*>(b[4]),

@@ -99,8 +99,11 @@ Nccl& nccl() {
 // Cross-GPU barrier over peer-mapped flags: thread r publishes this rank's epoch into rank r's
 // flag array, then waits (bounded) until rank r's epoch has arrived here. Launched after the
 // GEMM on the same stream, so this GPU's peer stores are complete before its flag is raised.
+// `max_polls` bounds the wait (about 100 ns per poll); a rank that never arrives is recorded in
+// the status word and the kernel returns.
+constexpr uint32_t kBarrierPolls = 1u << 24;
 __global__ void peer_barrier_kernel(uint32_t* const* peer_flags, uint32_t* my_flags, int rank, int world,
-                                    uint32_t epoch, uint32_t* status) {
+                                    uint32_t epoch, uint32_t* status, uint32_t max_polls) {
   const int r = threadIdx.x;
   if (r >= world) { return; }
   __threadfence_system();
@@ -108,7 +111,7 @@ __global__ void peer_barrier_kernel(uint32_t* const* peer_flags, uint32_t* my_fl
   *remote = epoch;
   __threadfence_system();
   volatile uint32_t* mine = my_flags + r;
-  for (uint32_t i = 0; i < (1u << 24); ++i) {
+  for (uint32_t i = 0; i < max_polls; ++i) {
     if ((int32_t)(*mine - epoch) >= 0) { return; }
     __nanosleep(100);
   }
@@ -375,6 +378,20 @@ extern "C" int vpq_affine_qmm_w4g64_bf16_nsplit_fused(vpq_comm* c, const uint32_
   if (!b) { return fail(VPQ_ERR_INVALID_ARG, "qmm_nsplit_fused: y must come from vpq_comm_alloc_symmetric"); }
   if (b->bytes < (size_t)M * (size_t)N * 2) { return fail(VPQ_ERR_INVALID_ARG, "qmm_nsplit_fused: y too small"); }
   const int64_t Ns = N / G;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  char* stage = static_cast<char*>(c->handle_stage) + 64 * 9;  // the peers' flag pointers
+  uint32_t* status = nullptr;
+  if (G > 1) {
+    // Entry barrier: a rank's stores into the peers' y may start only when every peer's stream has
+    // reached this call, i.e. when whatever the peers enqueued earlier to read y (the previous
+    // step's result) is done. Without it a fast rank would overwrite y under a slow rank's reader.
+    VPQ_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_nsplit_status));
+    ++c->epoch;
+    peer_barrier_kernel<<<1, 32, 0, st>>>(reinterpret_cast<uint32_t* const*>(stage),
+                                          static_cast<uint32_t*>(c->flags.local), c->rank, G, c->epoch, status,
+                                          kBarrierPolls);
+    VPQ_LAUNCH_OK("peer_barrier (entry)");
+  }
   // this GPU's copy first, then the peers', so the local stores lead
   void* dests[8];
   int n = 0;
@@ -385,15 +402,47 @@ extern "C" int vpq_affine_qmm_w4g64_bf16_nsplit_fused(vpq_comm* c, const uint32_
     return rc;
   }
   if (G > 1) {
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    char* stage = static_cast<char*>(c->handle_stage) + 64 * 9;  // the peers' flag pointers
-    uint32_t* status = nullptr;
-    VPQ_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_nsplit_status));
+    // Exit barrier: y is complete on this GPU once every peer's kernel (and so its stores into
+    // this GPU's y) has finished.
     ++c->epoch;
     peer_barrier_kernel<<<1, 32, 0, st>>>(reinterpret_cast<uint32_t* const*>(stage),
-                                          static_cast<uint32_t*>(c->flags.local), c->rank, G, c->epoch, status);
+                                          static_cast<uint32_t*>(c->flags.local), c->rank, G, c->epoch, status,
+                                          kBarrierPolls);
     VPQ_LAUNCH_OK("peer_barrier");
   }
+  return VPQ_OK;
+}
+
+// The cross-GPU flag barrier run on ONE GPU against a rank that never arrives: `workspace` (256
+// bytes of device memory) plays every rank's flag table, rank 0 publishes its epoch, and the wait for
+// `absent_rank` runs out after max_polls polls (about 100 ns each). Nothing faults or hangs: the
+// kernel records 0x7700 | absent_rank and returns; vpq_device_status then reports VPQ_ERR_TIMEOUT
+// with detail 0x20000 | 0x7700 | absent_rank and clears the word.
+extern "C" int vpq_peer_barrier_probe(void* workspace, int world, int absent_rank, uint32_t max_polls, void* stream) {
+  clear_error();
+  if (!workspace || world < 2 || world > 8 || absent_rank < 1 || absent_rank >= world) {
+    return fail(VPQ_ERR_INVALID_ARG, "peer_barrier_probe: need a workspace, 2 <= world <= 8, 1 <= absent_rank < world");
+  }
+  if (max_polls == 0 || max_polls > (1u << 20)) {
+    return fail(VPQ_ERR_INVALID_ARG, "peer_barrier_probe: 0 < max_polls <= 2^20 (the probe must end in a fraction of a second)");
+  }
+  if (reinterpret_cast<uintptr_t>(workspace) & 15) { return fail(VPQ_ERR_ALIGNMENT, "peer_barrier_probe: workspace alignment"); }
+  if (int rc = require_sm100()) { return rc; }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  char* ws = static_cast<char*>(workspace);
+  uint32_t* flags = reinterpret_cast<uint32_t*>(ws + 64);
+  // every rank's table is this one; the entries of the ranks that "arrived" carry the epoch already
+  uint32_t host_flags[8] = {};
+  for (int r = 0; r < world; ++r) { host_flags[r] = (r == absent_rank) ? 0u : 1u; }
+  uint32_t* host_ptrs[8];
+  for (int r = 0; r < 8; ++r) { host_ptrs[r] = flags; }
+  VPQ_CUDA_OK(cudaMemcpyAsync(ws, host_ptrs, sizeof(host_ptrs), cudaMemcpyHostToDevice, st));
+  VPQ_CUDA_OK(cudaMemcpyAsync(flags, host_flags, sizeof(host_flags), cudaMemcpyHostToDevice, st));
+  VPQ_CUDA_OK(cudaStreamSynchronize(st));  // the copies read this call's stack
+  uint32_t* status = nullptr;
+  VPQ_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_nsplit_status));
+  peer_barrier_kernel<<<1, 32, 0, st>>>(reinterpret_cast<uint32_t* const*>(ws), flags, 0, world, 1u, status, max_polls);
+  VPQ_LAUNCH_OK("peer_barrier (probe)");
   return VPQ_OK;
 }
 

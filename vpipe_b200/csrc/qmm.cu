@@ -258,7 +258,7 @@ struct ScaleStream {
   }
 };
 
-enum Role : uint32_t { kRoleEpi = 1, kRoleTma = 2, kRoleMma = 3, kRoleDq = 4 };
+enum Role : uint32_t { kRoleEpi = 1, kRoleTma = 2, kRoleMma = 3, kRoleDq = 4, kRoleSend = 5 };
 
 // Grouped (mixture-of-experts) form of the GEMM, the reference's affine_qmm_grouped_w4g64 /
 // affine_qmm_grouped_swiglu_w4g64 (affine_qmm_steel.metal:1026-1176,1371-1440): the rows of x are
@@ -605,28 +605,49 @@ __global__ void gather_rows_kernel(const uint4* __restrict__ src, const int* __r
   }
 }
 
+// Width of the CTA pair's tile. A 256 x 128 tile costs about 0.6 of a 256 x 256 one (it moves
+// more shared-memory bytes per flop), so it pays only where the wide tiles would leave CTA pairs
+// idle: few tiles (small N), or a last round that is mostly empty.
+int pick_tile_width(int M, int N, int pairs) {
+  const int tm = (M + two_cta::TM - 1) / two_cta::TM;
+  const int wide = tm * ((N + 255) / 256), narrow = tm * ((N + 127) / 128);
+  const double t_wide = (double)((wide + pairs - 1) / pairs);
+  const double t_narrow = 0.6 * (double)((narrow + pairs - 1) / pairs);
+  return t_narrow < 0.95 * t_wide ? 128 : 256;
+}
+
 template <int BITS>
 int launch_qmm_2cta_bits(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const void* x,
                          const two_cta::OutSpec& out, int K, int N, int M, cudaStream_t st, int reserve_sms) {
-  using L = two_cta::SmemT<BITS>;
+  int pairs = (num_sms() - reserve_sms) / 2;  // SMs left free run a concurrent collective
+  if (pairs < 1) { pairs = 1; }
+  const int tnt = (BITS == 4 && out.swiglu == 0) ? pick_tile_width(M, N, pairs) : 256;
   CUtensorMap map_x, map_w;
   if (int rc = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)K, (uint64_t)M,
                            BK, 128, CU_TENSOR_MAP_SWIZZLE_128B, "x")) {
     return rc;
   }
   if (int rc = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w, (uint64_t)(K * BITS / 32),
-                           (uint64_t)N, BK * BITS / 32, 128, CU_TENSOR_MAP_SWIZZLE_NONE, "w")) {
+                           (uint64_t)N, BK * BITS / 32, tnt / 2, CU_TENSOR_MAP_SWIZZLE_NONE, "w")) {
     return rc;
   }
-  auto kern = out.swiglu == 2   ? two_cta::affine_qmm_w4g64_2cta_kernel<2, BITS>
-              : out.swiglu == 1 ? two_cta::affine_qmm_w4g64_2cta_kernel<1, BITS>
-                                : two_cta::affine_qmm_w4g64_2cta_kernel<0, BITS>;
-  VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
-  const int tiles = ((M + two_cta::TM - 1) / two_cta::TM) * ((N + two_cta::TN - 1) / two_cta::TN);
-  int pairs = (num_sms() - reserve_sms) / 2;  // SMs left free run a concurrent collective
-  if (pairs < 1) { pairs = 1; }
+  using KernelT = void (*)(const CUtensorMap, const CUtensorMap, const uint16_t*, const uint16_t*, const two_cta::OutSpec,
+                           int, int, int);
+  KernelT kern;
+  int smem;
+  if (tnt == 128) {
+    kern = two_cta::affine_qmm_w4g64_2cta_kernel<0, 4, 128>;
+    smem = two_cta::SmemT<4, 128>::kAlloc;
+  } else {
+    kern = out.swiglu == 2   ? two_cta::affine_qmm_w4g64_2cta_kernel<2, BITS, 256>
+           : out.swiglu == 1 ? two_cta::affine_qmm_w4g64_2cta_kernel<1, BITS, 256>
+                             : two_cta::affine_qmm_w4g64_2cta_kernel<0, BITS, 256>;
+    smem = two_cta::SmemT<BITS, 256>::kAlloc;
+  }
+  VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  const int tiles = ((M + two_cta::TM - 1) / two_cta::TM) * ((N + tnt - 1) / tnt);
   const int grid = 2 * (tiles < pairs ? tiles : pairs);
-  kern<<<grid, two_cta::kThreads2, L::kAlloc, st>>>(map_x, map_w, scales, biases, out, M, N, K);
+  kern<<<grid, two_cta::kThreads2, smem, st>>>(map_x, map_w, scales, biases, out, M, N, K);
   VPQ_LAUNCH_OK("affine_qmm (2-CTA)");
   return VPQ_OK;
 }
@@ -664,8 +685,7 @@ int qmm_launch_reserved(const uint32_t* w, const void* scales, const void* biase
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // 256 x 256 tiles on CTA pairs when there are at least two row tiles' worth of rows; the
   // single-CTA 128 x 256 kernel otherwise.
-  static const bool force_1cta = std::getenv("VPQ_QMM_1CTA") != nullptr;
-  if (M > 128 && !force_1cta) {
+  if (M > 128) {
     two_cta::OutSpec out = {};
     out.base[0] = static_cast<__nv_bfloat16*>(y);
     out.count = 1;
@@ -882,6 +902,35 @@ extern "C" int vpq_affine_qmm_grouped_geglu_w4g64_bf16(const uint32_t* w, const 
                                                        int64_t x_rows, void* x_sorted, void* stream) {
   return qmm_grouped("affine_qmm_grouped_geglu_w4g64", 2, w, scales, biases, x, y, K, N, M, tile2e, srow, nullptr,
                      experts, x_rows, M, x_sorted, stream);
+}
+
+namespace vpq {
+namespace {
+// One thread waits, with the kernels' own bounded wait and a caller-chosen poll limit, on an
+// mbarrier that nobody arrives at. The wait must run out, record (0x7f << 8) | 0x7f in the status
+// word and return: the path every device-side wait takes when its partner never shows up.
+__global__ void wait_probe_kernel(uint32_t polls, uint32_t hint_ns) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0;
+    fence_mbar_init();
+    mbar_wait_limited(smem_u32(&bar), 0u, (0x7fu << 8) | 0x7fu, &abort_flag, &g_qmm_status, polls, hint_ns);
+  }
+}
+}  // namespace
+}  // namespace vpq
+
+extern "C" int vpq_wait_probe(uint32_t polls, uint32_t hint_ns, void* stream) {
+  clear_error();
+  if (polls == 0 || polls > (1u << 16) || hint_ns > 100000u) {
+    return fail(VPQ_ERR_INVALID_ARG, "wait_probe: 0 < polls <= 65536, hint_ns <= 100000 (the probe must end in well under a second)");
+  }
+  if (int rc = require_sm100()) { return rc; }
+  wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(polls, hint_ns);
+  VPQ_LAUNCH_OK("wait_probe");
+  return VPQ_OK;
 }
 
 extern "C" int vpq_device_status(void* stream, uint32_t* detail) {

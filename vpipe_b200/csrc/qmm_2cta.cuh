@@ -6,10 +6,17 @@
 // own 128 x rows (A operand) but only HALF of the W tile (128 rows of B); the tensor cores of
 // both SMs read both halves. Dequant work and shared-memory bytes per flop halve.
 //
-// Per CTA, 448 threads as in the 1-CTA kernel: warps 0-3 epilogue (tensor-memory lanes = this
-// CTA's 128 output rows), warp 4 TMA producer, warp 5 tensor-memory allocation (+ MMA issue in the
-// leader CTA only), warps 6-13 dequantisers: two groups of four warps, one W row (64 values) per
-// thread, the groups taking alternate k blocks so one block's latency hides behind the other's.
+// Per CTA, 512 threads: warps 0-3 epilogue (tensor-memory lanes = this CTA's 128 output rows),
+// warp 4 TMA producer, warp 5 tensor-memory allocation (+ MMA issue in the leader CTA only), warps
+// 6-13 dequantisers: groups of warps with one W row (64 values) per thread, the groups taking
+// k blocks in turn so one block's latency hides behind the others', warps 14-15 senders (column
+// split over several GPUs only): they copy finished tiles from this GPU's y to the peers' y with
+// ordinary stores over NVLink, behind the epilogue, so the link runs beside the tensor cores
+// instead of stalling the accumulator hand-over.
+//
+// Two tile widths: 256 x 256 (TNT = 256: 128 W rows per CTA, two dequant groups of four warps) and
+// 256 x 128 (TNT = 128: 64 W rows per CTA, four groups of two warps), the narrow one for shapes
+// whose 256-wide tiles would leave most CTA pairs idle.
 //
 // Barriers. Local to each CTA: cfull[s] (packed W landed here), empty[s] (x + codes slot free:
 // one multicast tcgen05.commit + the local dequant warps), bempty[t] (dequantised tile free:
@@ -22,14 +29,11 @@
 namespace two_cta {
 
 constexpr int TM = 256;        // tile rows (128 per CTA)
-constexpr int TN = 256;        // tile columns (128 W rows dequantised per CTA)
 constexpr int kXStages4 = 5;   // x + codes ring, 4-bit weights
 constexpr int kXStages8 = 4;   // ... 8-bit weights (the codes of a stage are twice as large)
-constexpr int kBTiles = 5;     // dequantised-B ring
 constexpr int kDqWarps = 8;
-constexpr int kDqGroups = 2;   // warp groups that take alternate k blocks (a group = 4 warps = 128 rows)
-constexpr int kDqGroupWarps = kDqWarps / kDqGroups;
-constexpr int kThreads2 = 32 * (kEpiWarps + 2 + kDqWarps);
+constexpr int kSendWarps = 2;
+constexpr int kThreads2 = 32 * (kEpiWarps + 2 + kDqWarps + kSendWarps);
 
 // Where a CTA pair's output tile goes: `count` row-major destinations (this GPU's y and, in the
 // fused column-split, every peer's y mapped into this address space), leading dimension `ld`,
@@ -44,12 +48,16 @@ struct OutSpec {
                // wide; act = silu (1) or the tanh form of gelu (2). Selects the kernel instantiation.
 };
 
-template <int BITS>
+template <int BITS, int TNT = 256>
 struct SmemT {
-  static constexpr int kXStages = BITS == 8 ? kXStages8 : kXStages4;
+  static constexpr int kWRows = TNT / 2;              // W rows dequantised per CTA
+  static constexpr int kDqGroups = 256 / kWRows;      // warp groups that take k blocks in turn (a group = kWRows threads)
+  static constexpr int kDqGroupWarps = kDqWarps / kDqGroups;
+  static constexpr int kXStages = TNT == 128 ? 6 : (BITS == 8 ? kXStages8 : kXStages4);
+  static constexpr int kBTiles = TNT == 128 ? 8 : 5;  // dequantised-B ring
   static constexpr int kXBytes = 128 * BK * 2;        // 16 KB, 128B-swizzled
-  static constexpr int kCodeBytes = 128 * (BK * BITS / 8);  // 128 rows x 32 B (64 B at 8 bits)
-  static constexpr int kBBytes = 128 * BK * 2;        // 16 KB, 128B-swizzled K-major
+  static constexpr int kCodeBytes = kWRows * (BK * BITS / 8);  // rows x 32 B (64 B at 8 bits)
+  static constexpr int kBBytes = kWRows * BK * 2;     // 128B-swizzled K-major
   static constexpr int kOffX = 0;
   static constexpr int kOffB = kOffX + kXStages * kXBytes;
   static constexpr int kOffCode = kOffB + kBTiles * kBBytes;
@@ -61,8 +69,8 @@ struct SmemT {
   static constexpr int kTotal = kOffTmem + 16;
   static constexpr int kAlloc = kTotal + 1024;
 };
-using Smem = SmemT<4>;
-static_assert(SmemT<4>::kAlloc <= 227 * 1024 && SmemT<8>::kAlloc <= 227 * 1024, "shared memory of the pair kernel");
+static_assert(SmemT<4>::kAlloc <= 227 * 1024 && SmemT<8>::kAlloc <= 227 * 1024 && SmemT<4, 128>::kAlloc <= 227 * 1024,
+              "shared memory of the pair kernel");
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -123,21 +131,33 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
       : "memory");
 }
 
-// Instruction descriptor: D f32, A/B bf16, both K-major, M = 256 (pair), N = 256.
+// Instruction descriptor: D f32, A/B bf16, both K-major, M = 256 (pair), N = TNT.
+template <int TNT>
 __device__ __forceinline__ constexpr uint32_t make_idesc_pair() {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TNT >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
+}
+
+__device__ __forceinline__ uint4 ld_cg_v4(const void* p) {  // from L2: written moments ago by another warp
+  uint4 r;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
+  return r;
 }
 
 
-template <int kAct, int BITS>
+template <int kAct, int BITS, int TNT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
 affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
                              const __grid_constant__ CUtensorMap tmap_w,
                              const uint16_t* __restrict__ scales, const uint16_t* __restrict__ biases,
                              const OutSpec out, int M, int N, int K) {
-  using L = SmemT<BITS>;
+  using L = SmemT<BITS, TNT>;
   constexpr int kXStages = L::kXStages;
-  constexpr uint32_t kTmemCols = 512;  // two 256-column accumulator buffers
+  constexpr int kBTiles = L::kBTiles;
+  constexpr int kDqGroups = L::kDqGroups;
+  constexpr int kDqGroupWarps = L::kDqGroupWarps;
+  constexpr int kWRows = L::kWRows;
+  constexpr int TN = TNT;
+  constexpr uint32_t kTmemCols = 2 * TNT;  // two accumulator buffers
 
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t raw = smem_u32(smem_dyn);
@@ -154,6 +174,7 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
   auto bar_accempty = [&](int a) { return bar0 + 8u * (3 * kXStages + 2 * kBTiles + 2 + a); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L::kOffTmem);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  uint32_t* epi_done = const_cast<uint32_t*>(tmem_slot) + 2;  // epilogue warps that finished a tile's local stores
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -181,6 +202,7 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
       mbar_init(bar_accempty(a), 2 * kEpiWarps);
     }
     *abort_flag = 0;
+    *epi_done = 0;
     fence_mbar_init();
   }
   if (warp == 5) {  // the same warp of both CTAs allocates the pair's tensor memory
@@ -202,7 +224,7 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
       bool ok = true;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         const int m0 = (tile / tiles_n) * TM + (int)rank * 128;
-        const int n0 = (tile % tiles_n) * TN + (int)rank * 128;
+        const int n0 = (tile % tiles_n) * TN + (int)rank * kWRows;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % kXStages;
           const uint32_t ph = (it / kXStages) & 1u;
@@ -230,7 +252,7 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
   } else if (warp == 5) {
     // --------------------------------------------------------- MMA issuer (leader only)
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = make_idesc_pair();
+      constexpr uint32_t idesc = make_idesc_pair<TNT>();
       uint32_t it = 0, ti = 0;
       bool ok = true;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++ti) {
@@ -259,12 +281,70 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
         if (ok) { umma_commit_pair(bar_accfull(a)); }
       }
     }
+  } else if (warp >= 6 + kDqWarps) {
+    // ------------------------------------------------------------ senders (both CTAs)
+    // Column split over several GPUs: a finished tile, already stored to this GPU's y by the
+    // epilogue, is read back (from L2) and stored to every peer's y. A warp moves one 512-byte
+    // row segment per instruction, eight rows in flight. Peer memory is only ever written here.
+    if (out.count > 1 && kAct == 0) {
+      const int sw_id = warp - (6 + kDqWarps);
+      constexpr int kRowsPerWarp = 128 / kSendWarps;
+      constexpr int kLanesPerRow = TN / 8;            // 16-byte chunks of a tile row
+      constexpr int kRowsPerInstr = 32 / kLanesPerRow;  // 1 (256-wide tile) or 2 (128-wide)
+      const int lrow = lane / kLanesPerRow, lcol = (lane % kLanesPerRow) * 8;
+      uint32_t ti = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++ti) {
+        const int m0 = (tile / tiles_n) * TM + (int)rank * 128 + sw_id * kRowsPerWarp;
+        const int n0 = (tile % tiles_n) * TN;
+        // wait (bounded) until the four epilogue warps have stored this tile locally
+        uint32_t seen = 0;
+        if (lane == 0) {
+          for (uint32_t i = 0; i < (1u << 24); ++i) {
+            if (*reinterpret_cast<volatile uint32_t*>(epi_done) >= (uint32_t)kEpiWarps * (ti + 1)) {
+              seen = 1;
+              break;
+            }
+            if (*abort_flag) { break; }
+            __nanosleep(200);
+          }
+          if (!seen) {
+            *abort_flag = 1;
+            atomicCAS(&g_qmm_status, 0u, (1u << 8) | kRoleSend);
+          }
+        }
+        seen = __shfl_sync(0xffffffffu, seen, 0);
+        if (!seen) { ok = false; break; }
+        __threadfence();
+        const bool col_ok = n0 + lcol < N;
+#pragma unroll 1
+        for (int r0 = 0; r0 < kRowsPerWarp; r0 += 8 * kRowsPerInstr) {
+          uint4 v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int mm = m0 + r0 + i * kRowsPerInstr + lrow;
+            v[i] = make_uint4(0, 0, 0, 0);
+            if (mm < M && col_ok) { v[i] = ld_cg_v4(out.base[0] + (int64_t)mm * out.ld + out.col0 + n0 + lcol); }
+          }
+          for (int d = 1; d < out.count; ++d) {
+            __nv_bfloat16* dst = out.base[d];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int mm = m0 + r0 + i * kRowsPerInstr + lrow;
+              if (mm < M && col_ok) {
+                *reinterpret_cast<uint4*>(dst + (int64_t)mm * out.ld + out.col0 + n0 + lcol) = v[i];
+              }
+            }
+          }
+        }
+      }
+    }
   } else if (warp >= 6) {
     // ------------------------------------------------------- dequantisers (both CTAs)
-    // Two groups of four warps take alternate k blocks, one W row (a whole group of 64 values)
-    // per thread: a group has two MMA periods to turn a tile around instead of one.
+    // Groups of kWRows threads take the k blocks in turn, one W row (a whole group of 64 values)
+    // per thread: a group has kDqGroups MMA periods to turn a tile around instead of one.
     const int grp = (warp - 6) / kDqGroupWarps;
-    const int t_row = threadIdx.x - 6 * 32 - grp * (kDqGroupWarps * 32);  // 0 .. 127
+    const int t_row = threadIdx.x - 6 * 32 - grp * (kDqGroupWarps * 32);  // 0 .. kWRows - 1
     const uint32_t row_off = (uint32_t)(t_row >> 3) * 1024u + (uint32_t)(t_row & 7) * 128u;
     const uint32_t sw = (uint32_t)(t_row & 7);
     const int groups = K >> 6;
@@ -272,7 +352,7 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
     uint32_t it = 0;
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-      const int n0 = (tile % tiles_n) * TN + (int)rank * 128;
+      const int n0 = (tile % tiles_n) * TN + (int)rank * kWRows;
       int row = n0 + t_row;
       row = row < N ? row : N - 1;  // tail rows: any valid scale; their columns are never stored
       const uint16_t* srow = scales + (int64_t)row * groups;
@@ -283,7 +363,7 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const uint32_t ph = (it / kXStages) & 1u;
         const int t = it % kBTiles;
         const uint32_t bph = (it / kBTiles) & 1u;
-        if ((kb & (kDqGroups - 1)) != grp) { continue; }  // the other group's k block
+        if ((kb & (kDqGroups - 1)) != grp) { continue; }  // another group's k block
         float sc, bi;
         sst.get(kb, sc, bi);
         if (!warp_wait(bar_cfull(s), ph, (1u << 8) | kRoleDq, abort_flag, &g_qmm_status)) { ok = false; break; }
@@ -424,8 +504,9 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
             const int mm = mrow0 + row;
             if (mm < M && col_ok) {
               const int64_t off = (int64_t)mm * out.ld + out.col0 + nc0 + j * 8;
-              for (int d = 0; d < out.count; ++d) {  // this GPU first, then every peer
-                *reinterpret_cast<uint4*>(out.base[d] + off) = pk;
+              *reinterpret_cast<uint4*>(out.base[0] + off) = pk;  // this GPU's y; the senders feed the peers
+              if (kAct != 0) {
+                for (int d = 1; d < out.count; ++d) { *reinterpret_cast<uint4*>(out.base[d] + off) = pk; }
               }
             }
           }
@@ -455,6 +536,11 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
         } else {
           mbar_arrive_cluster(accempty_leader + 8u * a);
         }
+      }
+      if (out.count > 1 && kAct == 0) {  // hand the tile to the senders: stores first, then the count
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) { atomicAdd(epi_done, 1u); }
       }
     }
   }

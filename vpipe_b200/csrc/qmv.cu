@@ -97,7 +97,7 @@ enum : uint32_t { kRoleProducer = 1, kRoleConsumer = 2 };
 // One GEMV of a launch. Lives in the kernel parameters (single GEMV) or in caller-provided
 // device memory (plan). Tensor maps need 64-byte alignment.
 struct alignas(64) QmvProblem {
-  CUtensorMap mw, ms, mz;      // packed weights [N, K/8] u32; scales, biases [N, K/64] (valid if scales_tma)
+  CUtensorMap mw, ms, mz;      // packed weights [rows, K/8] u32; scales, biases [rows, K/64] (valid if scales_tma)
   const uint16_t* scales;
   const uint16_t* biases;
   const uint16_t* x;           // one row of K bf16
@@ -109,42 +109,304 @@ struct alignas(64) QmvProblem {
   int q_rows, k_rows;          // kEpiQkv: rows [0, q_rows) -> y, [q_rows, q_rows + k_rows) -> aux, the rest -> y3
   const uint16_t* aux;         // kEpiAdd: residual, N values; kEpiGeluMul: the multiplier; kEpiQkv: the second output
   __nv_bfloat16* y3;           // kEpiQkv: the third output
-  int pad[12];
+  const uint16_t* norm_w;      // not null: x is RMS-normalised with these K weights while it is staged
+  const int32_t* eid;          // not null: *eid is the expert whose [N, K] slab of w / scales / biases is used
+  float eps;                   // RMSNorm epsilon
+  int wait_tiles;              // > 0: tiles of the launch that must be complete before x (and aux) may be read
+  int experts;                 // slabs in w (eid is clamped to it)
+  int pad[5];
 };
-static_assert(sizeof(QmvProblem) % 64 == 0, "problem records are laid out back to back");
+static_assert(sizeof(QmvProblem) == 512, "problem records are laid out back to back");
 
+// How a launch's row tiles are dealt to the CTAs.
+//   single: one GEMV in the kernel parameters, tiles split evenly.
+//   ranges: a list of independent GEMVs; the host's table gives every CTA one contiguous run of the
+//           concatenated tiles.
+//   chain:  a list whose GEMVs may read what earlier ones wrote. Every GEMV is spread over the whole
+//           grid (CTA b takes tiles [b * per, (b + 1) * per) of it, per = ceil(tiles / grid)), a
+//           counter in global memory counts finished tiles, and a GEMV with wait_tiles > 0 stages its
+//           x only once that many tiles are complete. The producer warp does not wait: weights are
+//           constants, so the stream of GEMV i + 1 runs while GEMV i drains. The launch must be
+//           cooperative (all CTAs resident), since CTAs wait on one another.
+struct Walk {
+  const QmvProblem* P;  // current problem
+  int tile;             // next tile of P for this CTA
+  int hi;               // end of this CTA's tiles in P
+  int left;             // single / ranges: tiles left in this CTA's run; chain: problems after P
+  __device__ __forceinline__ Walk(const QmvProblem* single, const QmvProblem* list, const int2* ranges,
+                                  int total_tiles, int count, bool chain) {
+    if (chain) {
+      P = list - 1;
+      tile = hi = 0;
+      left = count;
+      return;
+    }
+    int gt, gt_end;
+    P = list ? list : single;
+    if (ranges) {
+      const int2 a = ranges[blockIdx.x], b = ranges[blockIdx.x + 1];
+      gt = a.x;
+      gt_end = b.x;
+      P += a.y;
+    } else {
+      gt = (int)(((int64_t)total_tiles * blockIdx.x) / gridDim.x);
+      gt_end = (int)(((int64_t)total_tiles * (blockIdx.x + 1)) / gridDim.x);
+    }
+    tile = gt - P->tile_begin;
+    hi = P->row_tiles;
+    left = gt_end - gt;
+  }
+  // Advances to the next tile of this CTA; `fresh` is raised when the walk entered another problem.
+  __device__ __forceinline__ bool next(int& out, bool& fresh, bool chain) {
+    if (!chain) {
+      if (left <= 0) { return false; }
+      while (tile >= hi) {
+        ++P;
+        tile = 0;
+        hi = P->row_tiles;
+        fresh = true;
+      }
+      --left;
+    } else {
+      while (tile >= hi) {
+        if (left <= 0) { return false; }
+        --left;
+        ++P;
+        const int rt = P->row_tiles;
+        const int per = (rt + (int)gridDim.x - 1) / (int)gridDim.x;
+        tile = (int)blockIdx.x * per;
+        hi = min(tile + per, rt);
+        fresh = true;
+      }
+    }
+    out = tile++;
+    return true;
+  }
+};
+
+__device__ __forceinline__ uint4 ld_cg_v4(const void* p) {  // L2 only: x may have been written by another SM
+  uint4 r;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
+  return r;
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// A tensor map that lives in global memory may have been rewritten since this SM last used the
+// address (a plan re-created in the same workspace, the fixed array of the no-allocation entry):
+// the acquire fence makes the copy the TMA unit reads current.
+__device__ __forceinline__ void tensormap_acquire(const CUtensorMap* m) {
+  asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(m) : "memory");
+}
+
+// ---- staging of one x vector as signed digit bytes. Warp w converts exactly the 256-k boxes it
+// will multiply (box w of every stage), so no CTA barrier is involved: a half warp takes one
+// box, a lane 16 consecutive values. Every box carries its own power-of-two scale: its largest
+// magnitude lands in [2^21, 2^22) and every value is rounded to an integer X, so a value is
+// exact if it lies within 2^-14 of the largest of its 256 neighbours and is off by at most
+// 2^-22 of that neighbour otherwise (one huge activation costs nothing outside its own box).
+// X = d0 + 256 d1 + 65536 d2 with digits in [-128, 127] (adding 0x808080 turns the balanced
+// digits into plain bytes; an xor takes the offset off again in two's complement). Per digit a
+// lane stores the 16 bytes one lane feeds to an even-nibble MMA (x0,x2,x4,x6 of packed word
+// w0 | of w1) and an odd-nibble MMA (x1,x3,x5,x7 of w0 | of w1). xg[group] = sum of the 64 X of
+// the group (for the bias term), xu[box] = 1 / scale.
+// With norm_w the vector is first RMS-normalised as the reference's fused kernel does
+// (affine_qmv_qkv_rms_w4g64, gpu-kernels/metal/quant/affine_qmv.metal:570-694): sum of squares
+// in f32 over the whole vector (the warps exchange their partial sums through one consumer
+// barrier), x <- bf16(x * rsqrt(mean + eps) * norm_w).
+__device__ __noinline__ bool stage_x(const QmvProblem* P, int K, int warp, int lane, unsigned char* xq, float* xg,
+                                     float* xu, float* sq_part, uint32_t* sq_cnt, int sq_gen,
+                                     volatile uint32_t* abort_flag) {
+  constexpr int kXRegs = 3;  // passes whose loads a lane keeps in registers
+  const int half = lane >> 4, sub = lane & 15;
+  const uint16_t* xr = P->x;
+  const uint16_t* nw = P->norm_w;
+  const int NB = (K + 255) >> 8;
+  const int passes = (((NB + kBoxesPerStage - 1) / kBoxesPerStage) + 1) >> 1;  // two boxes of this warp per pass
+  auto k_of = [&](int j) { return (((2 * j + half) * kBoxesPerStage + warp) << 8) + sub * 16; };
+  auto load_piece = [&](int j, uint4& a, uint4& b) {
+    const int k0 = k_of(j);
+    a = b = make_uint4(0, 0, 0, 0);
+    if (k0 < K) {
+      a = ld_cg_v4(xr + k0);
+      b = ld_cg_v4(xr + k0 + 8);
+    }
+  };
+  uint4 xin[kXRegs][2];
+#pragma unroll
+  for (int r = 0; r < kXRegs; ++r) {
+    if (r < passes) { load_piece(r, xin[r][0], xin[r][1]); }
+  }
+  float inv = 1.0f;
+  if (nw) {
+    float sq = 0.0f;
+    auto add_sq = [&](const uint4& in) {
+      const uint32_t v[4] = {in.x, in.y, in.z, in.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = __uint_as_float(v[j] << 16), hi = __uint_as_float(v[j] & 0xffff0000u);
+        sq = __fmaf_rn(lo, lo, sq);
+        sq = __fmaf_rn(hi, hi, sq);
+      }
+    };
+#pragma unroll
+    for (int r = 0; r < kXRegs; ++r) {
+      if (r < passes) {
+        add_sq(xin[r][0]);
+        add_sq(xin[r][1]);
+      }
+    }
+    for (int j = kXRegs; j < passes; ++j) {
+      uint4 a, b;
+      load_piece(j, a, b);
+      add_sq(a);
+      add_sq(b);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { sq += __shfl_xor_sync(0xffffffffu, sq, o); }
+    // The warps exchange their partial sums through shared memory: post, count, wait (bounded, and
+    // given up at once if a warp of this CTA has aborted) until all eight have posted. Uses alternate
+    // between the two halves of sq_part, so a warp that runs ahead cannot overwrite sums still being read.
+    const int sq_par = sq_gen & 1;
+    const uint32_t target = (uint32_t)kConsWarps * (uint32_t)(sq_gen / 2 + 1);
+    uint32_t all = 1;
+    if (lane == 0) {
+      sq_part[sq_par * kConsWarps + warp] = sq;
+      __threadfence_block();
+      atomicAdd(&sq_cnt[sq_par], 1u);
+      all = 0;
+      for (uint32_t i = 0; i < (1u << 24); ++i) {
+        if (*reinterpret_cast<volatile uint32_t*>(&sq_cnt[sq_par]) >= target) {
+          all = 1;
+          break;
+        }
+        if (*abort_flag) { break; }
+        __nanosleep(20);
+      }
+      if (!all) {
+        *abort_flag = 1;
+        atomicCAS(&g_qmv_status, 0u, (4u << 8) | kRoleConsumer);
+      }
+      __threadfence_block();
+    }
+    all = __shfl_sync(0xffffffffu, all, 0);
+    if (!all) { return false; }
+    float total = 0.0f;
+#pragma unroll
+    for (int ww = 0; ww < kConsWarps; ++ww) {
+      total += *reinterpret_cast<volatile float*>(&sq_part[sq_par * kConsWarps + ww]);
+    }
+    inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)K), P->eps));
+  }
+  auto convert_piece = [&](int j, const uint4& in0, const uint4& in1) {  // whole warps: shuffles inside
+    const int box = (2 * j + half) * kBoxesPerStage + warp;
+    const bool live = box < NB;
+    uint32_t v[8] = {in0.x, in0.y, in0.z, in0.w, in1.x, in1.y, in1.z, in1.w};
+    if (nw) {
+      const int k0 = k_of(j);
+      uint4 n0 = make_uint4(0, 0, 0, 0), n1 = n0;
+      if (k0 < K) {
+        n0 = __ldg(reinterpret_cast<const uint4*>(nw + k0));
+        n1 = __ldg(reinterpret_cast<const uint4*>(nw + k0 + 8));
+      }
+      const uint32_t nv[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float lo = __fmul_rn(__fmul_rn(__uint_as_float(v[q] << 16), inv), __uint_as_float(nv[q] << 16));
+        const float hi = __fmul_rn(__fmul_rn(__uint_as_float(v[q] & 0xffff0000u), inv),
+                                   __uint_as_float(nv[q] & 0xffff0000u));
+        v[q] = pack_bf16x2(lo, hi);
+      }
+    }
+    uint32_t amax = 0;  // largest |x| of the box as bf16 bits (ordering of magnitudes == ordering of bit patterns)
+#pragma unroll
+    for (int q = 0; q < 8; ++q) { amax = max(amax, max(v[q] & 0x7fffu, (v[q] >> 16) & 0x7fffu)); }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) { amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, o)); }
+    int e = (int)(amax >> 7);            // biased exponent of the largest magnitude
+    e = min(max(e, 22), 254);            // all-zero / denormal box: keep both factors normal
+    const float x_scale = __uint_as_float((uint32_t)(275 - e) << 23);   // 2^(148 - e): max |x| -> [2^21, 2^22)
+    // round(x * scale) without the conversion unit: the low bits of fma(x, scale, 1.5 * 2^23)
+    // are 0x4B400000 + X. One add moves that to X + 0x808080 (bytes 0..2: digits + 128; byte 3
+    // is never used); the + 128 is taken off the transposed words below.
+    uint32_t z[16];
+    uint32_t sum = 0;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const uint32_t lo = __float_as_uint(__fmaf_rn(__uint_as_float(v[q] << 16), x_scale, kAccInitF));
+      const uint32_t hi = __float_as_uint(__fmaf_rn(__uint_as_float(v[q] & 0xffff0000u), x_scale, kAccInitF));
+      sum += lo + hi;
+      z[2 * q] = lo + (0x808080u - (uint32_t)kAccInit);
+      z[2 * q + 1] = hi + (0x808080u - (uint32_t)kAccInit);
+    }
+    sum -= 16u * (uint32_t)kAccInit;  // = sum of the 16 X, modulo 2^32
+    // byte d of za, zb, zc, zd -> one word per digit d
+    auto digits_of4 = [](uint32_t za, uint32_t zb, uint32_t zc, uint32_t zd, uint32_t (&out)[3]) {
+      const uint32_t t0 = __byte_perm(za, zb, 0x5140), t1 = __byte_perm(zc, zd, 0x5140);
+      const uint32_t t2 = __byte_perm(za, zb, 0x0062), t3 = __byte_perm(zc, zd, 0x0062);
+      out[0] = __byte_perm(t0, t1, 0x5410) ^ 0x80808080u;
+      out[1] = __byte_perm(t0, t1, 0x7632) ^ 0x80808080u;
+      out[2] = __byte_perm(t2, t3, 0x5410) ^ 0x80808080u;
+    };
+    uint32_t e0[3], o0[3], e1[3], o1[3];
+    digits_of4(z[0], z[2], z[4], z[6], e0);
+    digits_of4(z[1], z[3], z[5], z[7], o0);
+    digits_of4(z[8], z[10], z[12], z[14], e1);
+    digits_of4(z[9], z[11], z[13], z[15], o1);
+    const int i = box * 16 + sub;  // index of this 16-value piece in the padded x
+    if (live) {
+      unsigned char* dst = xq + (size_t)(i >> 3) * kXBytesPerKt + (i & 7) * 16;
+#pragma unroll
+      for (int d = 0; d < 3; ++d) {
+        *reinterpret_cast<uint4*>(dst + d * 128) = make_uint4(e0[d], e1[d], o0[d], o1[d]);
+      }
+    }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if (live && (sub & 3) == 0) { xg[i >> 2] = (float)(int)sum; }
+    if (live && sub == 0) { xu[box] = __uint_as_float((uint32_t)(e - 21) << 23); }  // exact inverse of x_scale
+  };
+#pragma unroll
+  for (int r = 0; r < kXRegs; ++r) {
+    if (r < passes) { convert_piece(r, xin[r][0], xin[r][1]); }
+  }
+  for (int j = kXRegs; j < passes; ++j) {
+    uint4 a, b;
+    load_piece(j, a, b);
+    convert_piece(j, a, b);
+  }
+  __syncwarp();
+  return true;
+}
+
+constexpr uint32_t kDepPolls = 1u << 22;  // polls of the tile counter before a dependent GEMV gives up (seconds)
 
 __global__ void __launch_bounds__(kThreads, 2)
 affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProblem* __restrict__ list,
-                        const int2* __restrict__ ranges, int total_tiles, int stages, int cap_kt) {
+                        const int2* __restrict__ ranges, int total_tiles, int stages, int cap_kt, int count,
+                        uint32_t* sync) {
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t raw = smem_u32(smem_dyn);
   const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled boxes need 1024-byte alignment
   unsigned char* base_ptr = smem_dyn + (base - raw);
   constexpr int kStageBytes = kStageW + kStageSZ;
-  const QmvProblem* probs = list ? list : &single;
-  // Every CTA takes one contiguous run of the launch's row tiles (and so meets few different x):
-  // from the host's table {first tile, its problem} for a list, evenly split for a single GEMV.
-  int gt_begin, gt_end;
-  if (ranges) {
-    const int2 a = ranges[blockIdx.x], b = ranges[blockIdx.x + 1];
-    gt_begin = a.x;
-    gt_end = b.x;
-    probs += a.y;
-  } else {
-    gt_begin = (int)(((int64_t)total_tiles * blockIdx.x) / gridDim.x);
-    gt_end = (int)(((int64_t)total_tiles * (blockIdx.x + 1)) / gridDim.x);
-  }
+  const bool chain = sync != nullptr;
 
   unsigned char* p0 = base_ptr + (size_t)stages * kStageBytes;
   uint4* zero128 = reinterpret_cast<uint4*>(p0);                 // 128 bytes of zeros, 128-byte aligned
   unsigned char* xq = p0 + 128;                                  // [cap_kt][3 digits][4 chunks][32 B]
-  float* xg = reinterpret_cast<float*>(xq + (size_t)cap_kt * kXBytesPerKt);  // [2*cap_kt] sum of x per group
+  float* xg = reinterpret_cast<float*>(xq + (size_t)cap_kt * kXBytesPerKt);  // [2*cap_kt] sum of X per group
   float* zero16 = xg + 2 * cap_kt;                               // 16 bytes of zeros (cap_kt is even)
-  float* red = zero16 + 4;                                       // [kRedSlots][kConsWarps][16]
+  float* xu = zero16 + 4;                                        // [cap_kt/2] 1 / scale of every 256-k box of x
+  float* red = xu + ((cap_kt / 2 + 3) & ~3);                     // [kRedSlots][kConsWarps][16]
   uint32_t* red_cnt = reinterpret_cast<uint32_t*>(red + kRedSlots * kConsWarps * 16);  // [kRedSlots]
-  uint32_t* amax_buf = red_cnt + kRedSlots;                      // [kConsWarps]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(amax_buf + kConsWarps);
+  float* sq_part = reinterpret_cast<float*>(red_cnt + kRedSlots);                      // [2][kConsWarps]
+  uint32_t* sq_cnt = reinterpret_cast<uint32_t*>(sq_part + 2 * kConsWarps);            // [2] warps that posted; [2] = warps that left
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sq_cnt + 4);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * kMaxStages);
   const uint32_t bar0 = smem_u32(bars);
   auto bar_full = [&](int s) { return bar0 + 8u * s; };
@@ -163,6 +425,7 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
     }
     *abort_flag = 0;
     for (int i = 0; i < kRedSlots; ++i) { red_cnt[i] = 0; }
+    for (int i = 0; i < 4; ++i) { sq_cnt[i] = 0; }
     fence_mbar_init();
   }
   if (threadIdx.x < 8) { zero128[threadIdx.x] = make_uint4(0, 0, 0, 0); }
@@ -172,23 +435,36 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
   if (warp == kConsWarps) {
     // ------------------------------------------------------------ producer
     // Weights, scales and biases are constants of the model: streaming them
-    // does not wait for the previous kernel.
+    // does not wait for the previous kernel, nor for an earlier GEMV of a chain.
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      int pi = 0;
-      const QmvProblem* P = probs;
-      int tb = P->tile_begin, rt = P->row_tiles;
-      for (int gt = gt_begin; gt < gt_end && ok; ++gt) {
-        while (gt >= tb + rt) {
-          P = probs + (++pi);
-          tb = P->tile_begin;
-          rt = P->row_tiles;
+      Walk wk(&single, list, ranges, total_tiles, count, chain);
+      int tile = 0;
+      bool fresh = true;
+      int NB = 0, SPT = 0, row0 = 0;
+      bool sz_tma = false;
+      while (ok && wk.next(tile, fresh, chain)) {
+        const QmvProblem* P = wk.P;
+        if (fresh) {
+          fresh = false;
+          NB = (P->K + 255) >> 8;                              // 128-byte boxes per row
+          SPT = (NB + kBoxesPerStage - 1) / kBoxesPerStage;    // stages per row tile
+          sz_tma = P->scales_tma != 0;
+          row0 = 0;
+          if (P->eid) {
+            // the routed expert is an output of an earlier kernel: unlike the weights it must be waited for
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            row0 = min(max(__ldg(P->eid), 0), P->experts - 1) * P->N;
+          }
+          if (list) {
+            tensormap_acquire(&P->mw);
+            if (sz_tma) {
+              tensormap_acquire(&P->ms);
+              tensormap_acquire(&P->mz);
+            }
+          }
         }
-        const int tile = gt - tb;
-        const int NB = (P->K + 255) >> 8;                              // 128-byte boxes per row
-        const int SPT = (NB + kBoxesPerStage - 1) / kBoxesPerStage;    // stages per row tile
-        const bool sz_tma = P->scales_tma != 0;
         for (int st = 0; st < SPT; ++st, ++it) {
           const int s = it % stages;
           const uint32_t ph = (it / stages) & 1u;
@@ -200,11 +476,11 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
           const uint32_t dst = base + (uint32_t)s * kStageBytes;
           mbar_expect_tx(bar_full(s), (uint32_t)nb * kBoxBytes + (sz_tma ? kStageSZ : 0));
           for (int b = 0; b < nb; ++b) {
-            tma_load_2d(dst + b * kBoxBytes, &P->mw, bar_full(s), (st * kBoxesPerStage + b) * 32, tile * 16);
+            tma_load_2d(dst + b * kBoxBytes, &P->mw, bar_full(s), (st * kBoxesPerStage + b) * 32, row0 + tile * 16);
           }
           if (sz_tma) {
-            tma_load_2d(dst + kStageW, &P->ms, bar_full(s), st * 32, tile * 16);
-            tma_load_2d(dst + kStageW + kStageSZ / 2, &P->mz, bar_full(s), st * 32, tile * 16);
+            tma_load_2d(dst + kStageW, &P->ms, bar_full(s), st * 32, row0 + tile * 16);
+            tma_load_2d(dst + kStageW + kStageSZ / 2, &P->mz, bar_full(s), st * 32, row0 + tile * 16);
           }
         }
       }
@@ -225,115 +501,6 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
 
   // x (and y) may be produced / consumed by the previous kernel.
   asm volatile("griddepcontrol.wait;" ::: "memory");
-
-  // ---- staging of one x vector as signed digit bytes (called by all consumer warps together).
-  // x is scaled by a power of two so that its largest magnitude lands in [2^21, 2^22) and rounded
-  // to an integer X: every bf16 value within 2^-14 of the maximum is exact, smaller ones are off
-  // by at most 2^-22 of the maximum. X = d0 + 256 d1 + 65536 d2 with digits in [-128, 127]
-  // (adding 0x808080 turns the balanced digits into plain bytes; an xor takes the offset off
-  // again in two's complement). A thread converts 16 consecutive values (two packed words' worth,
-  // w0 and w1) and stores, per digit, the 16 bytes one lane feeds to an even-nibble MMA
-  // (x0,x2,x4,x6 of w0 | of w1) and an odd-nibble MMA (x1,x3,x5,x7 of w0 | of w1).
-  // xg[group] = sum of the 64 X of the group, for the bias term. Returns 1 / scale.
-  constexpr int kXRegs = 3;  // 16-value pieces a thread keeps in registers between the two passes
-  auto stage_x = [&](const uint16_t* xr, int K, int KT) -> float {
-    const int pieces = KT * 8;  // 32-byte pieces of the padded x
-    uint4 xin[kXRegs][2];
-    uint32_t amax = 0;  // largest |x| as bf16 bits (ordering of magnitudes == ordering of bit patterns)
-    auto fold_amax = [&](const uint4& in) {
-      const uint32_t v[4] = {in.x, in.y, in.z, in.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        amax = max(amax, v[j] & 0x7fffu);
-        amax = max(amax, (v[j] >> 16) & 0x7fffu);
-      }
-    };
-#pragma unroll
-    for (int r = 0; r < kXRegs; ++r) {
-      const int i = threadIdx.x + r * kConsThreads;
-      xin[r][0] = xin[r][1] = make_uint4(0, 0, 0, 0);
-      if (i * 16 < K) {
-        xin[r][0] = *reinterpret_cast<const uint4*>(xr + i * 16);
-        xin[r][1] = *reinterpret_cast<const uint4*>(xr + i * 16 + 8);
-      }
-    }
-#pragma unroll
-    for (int r = 0; r < kXRegs; ++r) {
-      fold_amax(xin[r][0]);
-      fold_amax(xin[r][1]);
-    }
-    for (int i = threadIdx.x + kXRegs * kConsThreads; i * 16 < K; i += kConsThreads) {
-      fold_amax(*reinterpret_cast<const uint4*>(xr + i * 16));
-      fold_amax(*reinterpret_cast<const uint4*>(xr + i * 16 + 8));
-    }
-    amax = __reduce_max_sync(0xffffffffu, amax);
-    // the barrier also orders the previous problem's last reads of xq / xg before the writes below
-    if (lane == 0) { amax_buf[warp] = amax; }
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsThreads) : "memory");  // consumers only
-    amax = 0;
-#pragma unroll
-    for (int ww = 0; ww < kConsWarps; ++ww) { amax = max(amax, amax_buf[ww]); }
-    int e = (int)(amax >> 7);            // biased exponent of the largest magnitude
-    e = min(max(e, 22), 254);            // all-zero / denormal x: keep both factors normal
-    const float x_scale = __uint_as_float((uint32_t)(275 - e) << 23);   // 2^(148 - e): max |x| -> [2^21, 2^22)
-    const float x_unscale = __uint_as_float((uint32_t)(e - 21) << 23);  // its exact inverse
-    auto convert_piece = [&](int i, const uint4& in0, const uint4& in1) {  // whole warps: shuffles inside
-      const bool live = i < pieces;
-      const uint32_t v[8] = {in0.x, in0.y, in0.z, in0.w, in1.x, in1.y, in1.z, in1.w};
-      // round(x * scale) without the conversion unit: the low bits of fma(x, scale, 1.5 * 2^23)
-      // are 0x4B400000 + X. One add moves that to X + 0x808080 (bytes 0..2: digits + 128; byte 3
-      // is never used); the + 128 is taken off the transposed words below.
-      uint32_t z[16];
-      uint32_t sum = 0;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const uint32_t lo = __float_as_uint(__fmaf_rn(__uint_as_float(v[j] << 16), x_scale, kAccInitF));
-        const uint32_t hi = __float_as_uint(__fmaf_rn(__uint_as_float(v[j] & 0xffff0000u), x_scale, kAccInitF));
-        sum += lo + hi;
-        z[2 * j] = lo + (0x808080u - (uint32_t)kAccInit);
-        z[2 * j + 1] = hi + (0x808080u - (uint32_t)kAccInit);
-      }
-      sum -= 16u * (uint32_t)kAccInit;  // = sum of the 16 X, modulo 2^32
-      // byte d of za, zb, zc, zd -> one word per digit d
-      auto digits_of4 = [](uint32_t za, uint32_t zb, uint32_t zc, uint32_t zd, uint32_t (&out)[3]) {
-        const uint32_t t0 = __byte_perm(za, zb, 0x5140), t1 = __byte_perm(zc, zd, 0x5140);
-        const uint32_t t2 = __byte_perm(za, zb, 0x0062), t3 = __byte_perm(zc, zd, 0x0062);
-        out[0] = __byte_perm(t0, t1, 0x5410) ^ 0x80808080u;
-        out[1] = __byte_perm(t0, t1, 0x7632) ^ 0x80808080u;
-        out[2] = __byte_perm(t2, t3, 0x5410) ^ 0x80808080u;
-      };
-      uint32_t e0[3], o0[3], e1[3], o1[3];
-      digits_of4(z[0], z[2], z[4], z[6], e0);
-      digits_of4(z[1], z[3], z[5], z[7], o0);
-      digits_of4(z[8], z[10], z[12], z[14], e1);
-      digits_of4(z[9], z[11], z[13], z[15], o1);
-      if (live) {
-        unsigned char* dst = xq + (size_t)(i >> 3) * kXBytesPerKt + (i & 7) * 16;
-#pragma unroll
-        for (int d = 0; d < 3; ++d) {
-          *reinterpret_cast<uint4*>(dst + d * 128) = make_uint4(e0[d], e1[d], o0[d], o1[d]);
-        }
-      }
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      if (live && (i & 3) == 0) { xg[i >> 2] = (float)(int)sum; }
-    };
-#pragma unroll
-    for (int r = 0; r < kXRegs; ++r) {
-      const int i = threadIdx.x + r * kConsThreads;
-      if (i - lane < pieces) { convert_piece(i, xin[r][0], xin[r][1]); }  // warp-uniform
-    }
-    for (int i = threadIdx.x + kXRegs * kConsThreads; i - lane < pieces; i += kConsThreads) {
-      uint4 in0 = make_uint4(0, 0, 0, 0), in1 = in0;
-      if (i * 16 < K) {
-        in0 = *reinterpret_cast<const uint4*>(xr + i * 16);
-        in1 = *reinterpret_cast<const uint4*>(xr + i * 16 + 8);
-      }
-      convert_piece(i, in0, in1);
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsThreads) : "memory");
-    return x_unscale;
-  };
 
   // Accumulator column c of an MMA is supplied by the lanes with g == c and stands for
   // (digit c >> 1, group parity c & 1): those lanes feed the digit's bytes if their chunk t lies
@@ -360,47 +527,62 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
                           (uint32_t)warp * 8u;
 
   uint32_t tile_seq = 0, ph = 0;
-  int s = 0;
+  int s = 0, sq_gen = 0;
   bool ok = true;
-  int pi = 0;
-  const QmvProblem* P = probs;
-  int tb = P->tile_begin, rt = P->row_tiles;
+  Walk wk(&single, list, ranges, total_tiles, count, chain);
   const uint16_t* staged_x = nullptr;
   int staged_K = -1;
-  float x_unscale = 1.0f;
   // per-problem values, refreshed when the walk enters a new problem
-  int K = 0, N = 0, G = 0, KT = 0, SPT = 0;
+  int N = 0, KT = 0, SPT = 0, row0 = 0;
   bool sz_tma = false;
-  const uint16_t* scales = nullptr;
-  const uint16_t* biases = nullptr;
-  __nv_bfloat16* y = nullptr;
   bool fresh = true;
-  for (int gt = gt_begin; gt < gt_end && ok; ++gt, ++tile_seq) {
-    while (gt >= tb + rt) {
-      P = probs + (++pi);
-      tb = P->tile_begin;
-      rt = P->row_tiles;
-      fresh = true;
-    }
+  int tile = 0;
+  while (ok && wk.next(tile, fresh, chain)) {
+    const QmvProblem* P = wk.P;
     if (fresh) {
       fresh = false;
-      K = P->K;
+      const int K = P->K;
       N = P->N;
-      G = K >> 6;
       KT = ((K + 255) >> 8) * 2;  // k tiles per row, padded to whole 256-k boxes (x is zero there)
       SPT = (((K + 255) >> 8) + kBoxesPerStage - 1) / kBoxesPerStage;
       sz_tma = P->scales_tma != 0;
-      scales = P->scales;
-      biases = P->biases;
-      y = P->y;
+      row0 = 0;
+      if (P->eid) { row0 = min(max(__ldg(P->eid), 0), P->experts - 1) * N; }
       const uint16_t* xr = P->x;
-      if (xr != staged_x || K != staged_K) {  // q|k|v or gate|up of a layer share one staging
-        x_unscale = stage_x(xr, K, KT);
-        staged_x = xr;
+      const int need = chain ? P->wait_tiles : 0;
+      if (need > 0) {
+        // this GEMV reads what earlier GEMVs of the launch wrote: wait (bounded) for their tiles
+        uint32_t seen = 0;
+        if (lane == 0) {
+          for (uint32_t i = 0; i < kDepPolls; ++i) {
+            if (ld_acquire_u32(sync) >= (uint32_t)need) {
+              seen = 1;
+              break;
+            }
+            __nanosleep(64);
+          }
+          if (!seen) {
+            *abort_flag = 1;
+            atomicCAS(&g_qmv_status, 0u, (3u << 8) | kRoleConsumer);
+          }
+        }
+        seen = __shfl_sync(0xffffffffu, seen, 0);
+        if (!seen) {
+          ok = false;
+          break;
+        }
+      }
+      // q|k|v or gate|up of a layer share one staging; a dependent or normalised x is always staged
+      if (need > 0 || P->norm_w != nullptr || xr != staged_x || K != staged_K) {
+        if (!stage_x(P, K, warp, lane, xq, xg, xu, sq_part, sq_cnt, sq_gen, abort_flag)) {
+          ok = false;
+          break;
+        }
+        staged_x = P->norm_w ? nullptr : xr;
         staged_K = K;
+        if (P->norm_w) { ++sq_gen; }
       }
     }
-    const int tile = gt - tb;
     float res_a = 0.0f, res_b = 0.0f;  // rows rho and rho + 8 of the tile: this lane's digit (or bias) share
     for (int st = 0; st < SPT; ++st) {
       if (!warp_wait(bar_full(s), ph, (1u << 8) | kRoleConsumer, abort_flag, &g_qmv_status)) {
@@ -426,8 +608,9 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
           sb2 = *reinterpret_cast<const uint2*>(sb + sz_off + 512);
         } else {
           // clamped onto valid data: a clamped group meets x == 0, a clamped row is never stored
-          const uint16_t* src = bias_lane ? biases : scales;
-          const int64_t r_a = min(tile * 16 + rho, N - 1), r_b = min(tile * 16 + rho + 8, N - 1);
+          const uint16_t* src = bias_lane ? P->biases : P->scales;
+          const int G = P->K >> 6;
+          const int64_t r_a = row0 + min(tile * 16 + rho, N - 1), r_b = row0 + min(tile * 16 + rho + 8, N - 1);
           const int g0 = min(2 * kt0, G - 1), g1 = min(2 * kt0 + 1, G - 1);
           const int g2 = min(2 * kt0 + 2, G - 1), g3 = min(2 * kt0 + 3, G - 1);
           sa.x = ldg_nc_u16(src + r_a * G + g0) | (ldg_nc_u16(src + r_a * G + g1) << 16);
@@ -436,6 +619,7 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
           sb2.y = ldg_nc_u16(src + r_b * G + g2) | (ldg_nc_u16(src + r_b * G + g3) << 16);
         }
         const float4 xs = *reinterpret_cast<const float4*>(xs_base + (kt0 >> 1) * xs_box);
+        const float xu_box = xu[kt0 >> 1];
         // four independent chains: even / odd nibbles of each k tile
         int ce0[4], co0[4], ce1[4], co1[4];
         mma_u8s8_16832_first(ce0, ra0.x & kEvenNibbles, rb0.x & kEvenNibbles, ra0.y & kEvenNibbles,
@@ -456,20 +640,23 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
                        rb1.w & kOddNibbles, x11.z, x11.w);
         // c[0] = (row rho, first group of the k tile) c[1] = (rho, second) c[2] = (rho + 8, first)
         // c[3] = (rho + 8, second); value = even + odd / 16 - surplus (+ sum of x in a bias lane,
-        // whose accumulators hold the bare initial value)
+        // whose accumulators hold the bare initial value). The four groups of the box are folded
+        // with their scales first, then the box's 1 / x-scale brings the sum to true units.
         const float k0 = xs.x - kAccSurplus, k1 = xs.y - kAccSurplus;
         const float k2 = xs.z - kAccSurplus, k3 = xs.w - kAccSurplus;
         auto val = [](int even, int odd, float k) {
           return __int_as_float(even) + __fmaf_rn(__int_as_float(odd), 0.0625f, k);
         };
-        res_a = __fmaf_rn(__uint_as_float(sa.x << 16), val(ce0[0], co0[0], k0), res_a);
-        res_a = __fmaf_rn(__uint_as_float(sa.x & 0xffff0000u), val(ce0[1], co0[1], k1), res_a);
-        res_a = __fmaf_rn(__uint_as_float(sa.y << 16), val(ce1[0], co1[0], k2), res_a);
-        res_a = __fmaf_rn(__uint_as_float(sa.y & 0xffff0000u), val(ce1[1], co1[1], k3), res_a);
-        res_b = __fmaf_rn(__uint_as_float(sb2.x << 16), val(ce0[2], co0[2], k0), res_b);
-        res_b = __fmaf_rn(__uint_as_float(sb2.x & 0xffff0000u), val(ce0[3], co0[3], k1), res_b);
-        res_b = __fmaf_rn(__uint_as_float(sb2.y << 16), val(ce1[2], co1[2], k2), res_b);
-        res_b = __fmaf_rn(__uint_as_float(sb2.y & 0xffff0000u), val(ce1[3], co1[3], k3), res_b);
+        float box_a = __fmul_rn(__uint_as_float(sa.x << 16), val(ce0[0], co0[0], k0));
+        box_a = __fmaf_rn(__uint_as_float(sa.x & 0xffff0000u), val(ce0[1], co0[1], k1), box_a);
+        box_a = __fmaf_rn(__uint_as_float(sa.y << 16), val(ce1[0], co1[0], k2), box_a);
+        box_a = __fmaf_rn(__uint_as_float(sa.y & 0xffff0000u), val(ce1[1], co1[1], k3), box_a);
+        float box_b = __fmul_rn(__uint_as_float(sb2.x << 16), val(ce0[2], co0[2], k0));
+        box_b = __fmaf_rn(__uint_as_float(sb2.x & 0xffff0000u), val(ce0[3], co0[3], k1), box_b);
+        box_b = __fmaf_rn(__uint_as_float(sb2.y << 16), val(ce1[2], co1[2], k2), box_b);
+        box_b = __fmaf_rn(__uint_as_float(sb2.y & 0xffff0000u), val(ce1[3], co1[3], k3), box_b);
+        res_a = __fmaf_rn(xu_box, box_a, res_a);
+        res_b = __fmaf_rn(xu_box, box_b, res_b);
       }
       __syncwarp();
       if (lane == 0) { mbar_arrive(bar_empty(s)); }  // this warp's part of the stage is in registers
@@ -490,6 +677,7 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
     keep += __shfl_xor_sync(0xffffffffu, (t & 1) ? res_a : res_b, 1);
     keep += __shfl_xor_sync(0xffffffffu, keep, 2);
     const int slot = tile_seq % kRedSlots;
+    ++tile_seq;
     if (t < 2) { red[(slot * kConsWarps + warp) * 16 + rho + 8 * t] = keep; }
     __syncwarp();
     uint32_t last = 0;
@@ -506,12 +694,33 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
         for (int ww = 0; ww < kConsWarps; ++ww) {
           v += *reinterpret_cast<volatile float*>(&red[(slot * kConsWarps + ww) * 16 + lane]);
         }
-        v *= x_unscale;
         const int row = (tile << 4) + lane;
-        fused_store(P->epilogue, v, row, N, lane, y, P->aux, P->y3, P->q_rows, P->k_rows);
+        fused_store(P->epilogue, v, row, N, lane, P->y, P->aux, P->y3, P->q_rows, P->k_rows);
       }
       __syncwarp();
-      if (lane == 0) { red_cnt[slot] = 0; }
+      if (lane == 0) {
+        red_cnt[slot] = 0;
+        if (chain) {  // publish the tile: the stores above, then the count
+          __threadfence();
+          atomicAdd(sync, 1u);
+        }
+      }
+    }
+  }
+  if (chain) {
+    // The CTA that leaves last puts both counters back to zero for the next run (every CTA has
+    // passed all of its waits by then, also one that gave up). No barrier: the warp of a CTA that
+    // leaves last reports for the CTA.
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence();
+      if (atomicAdd(&sq_cnt[2], 1u) == (uint32_t)(kConsWarps - 1)) {
+        if (atomicAdd(sync + 1, 1u) == gridDim.x - 1) {
+          sync[0] = 0;
+          sync[1] = 0;
+          __threadfence();
+        }
+      }
     }
   }
 }
@@ -525,8 +734,8 @@ struct LaunchShape {
 LaunchShape shape_for(int cap_kt) {
   const size_t stage_bytes = kStageW + kStageSZ;
   const size_t fixed = 1024 /*alignment slack*/ + 128 + (size_t)cap_kt * kXBytesPerKt + (size_t)2 * cap_kt * 4 + 16 +
-                       kRedSlots * kConsWarps * 16 * 4 + kRedSlots * 4 + kConsWarps * 4 +
-                       2 * kMaxStages * 8 + 16;
+                       (size_t)((cap_kt / 2 + 3) & ~3) * 4 + kRedSlots * kConsWarps * 16 * 4 + kRedSlots * 4 +
+                       2 * kConsWarps * 4 + 16 + 2 * kMaxStages * 8 + 16;
   const size_t budget = 112 * 1024;  // two CTAs per SM
   int stages = fixed + 2 * stage_bytes <= budget ? (int)((budget - fixed) / stage_bytes) : 2;
   if (stages > kMaxStages) { stages = kMaxStages; }
@@ -534,9 +743,10 @@ LaunchShape shape_for(int cap_kt) {
 }
 
 int fill_problem(QmvProblem* p, const uint32_t* w, const uint16_t* scales, const uint16_t* biases,
-                 const uint16_t* x, __nv_bfloat16* y, int K, int N, int tile_begin) {
+                 const uint16_t* x, __nv_bfloat16* y, int K, int N, int tile_begin, int experts = 1) {
   std::memset(p, 0, sizeof(*p));
-  if (int rc = make_map_2d(&p->mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w, (uint64_t)(K / 8), (uint64_t)N, 32,
+  const uint64_t rows = (uint64_t)N * (uint64_t)experts;  // expert slabs are stacked along the rows
+  if (int rc = make_map_2d(&p->mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w, (uint64_t)(K / 8), rows, 32,
                            16, CU_TENSOR_MAP_SWIZZLE_128B, "w")) {
     return rc;
   }
@@ -544,11 +754,11 @@ int fill_problem(QmvProblem* p, const uint32_t* w, const uint16_t* scales, const
   p->scales_tma = ((K % 512) == 0 && aligned16(scales) && aligned16(biases)) ? 1 : 0;
   if (p->scales_tma) {
     const int G = K / 64;
-    if (int rc = make_map_2d(&p->ms, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, (uint64_t)G, (uint64_t)N, 32,
+    if (int rc = make_map_2d(&p->ms, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, (uint64_t)G, rows, 32,
                              16, CU_TENSOR_MAP_SWIZZLE_NONE, "scales")) {
       return rc;
     }
-    if (int rc = make_map_2d(&p->mz, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, biases, (uint64_t)G, (uint64_t)N, 32,
+    if (int rc = make_map_2d(&p->mz, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, biases, (uint64_t)G, rows, 32,
                              16, CU_TENSOR_MAP_SWIZZLE_NONE, "biases")) {
       return rc;
     }
@@ -561,6 +771,7 @@ int fill_problem(QmvProblem* p, const uint32_t* w, const uint16_t* scales, const
   p->N = N;
   p->tile_begin = tile_begin;
   p->row_tiles = (N + 15) / 16;
+  p->experts = experts;
   return VPQ_OK;
 }
 
@@ -604,24 +815,48 @@ void build_ranges(const QmvProblem* p, size_t count, int grid, int2* out) {
   out[grid] = make_int2(last.tile_begin + last.row_tiles, (int)(count - 1));
 }
 
+int g_granted[64] = {};  // dynamic shared memory already granted to the kernel, per device
+
+// `sync` not null: the list is a dependent chain (two counters in device memory, zero between
+// runs); the launch is cooperative because its CTAs wait on one another.
 int launch_list(const QmvProblem& single, const QmvProblem* list, const int2* ranges, int total_tiles, int cap_kt,
-                cudaStream_t st) {
+                cudaStream_t st, int count = 1, uint32_t* sync = nullptr, int chain_grid = 0) {
   const LaunchShape ls = shape_for(cap_kt);
   auto kern = affine_qmv_w4g64_kernel;
-  static int granted[64] = {};
-  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), granted, ls.smem)) { return rc; }
-  const int ctas = grid_for(total_tiles);
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), g_granted, ls.smem)) { return rc; }
+  const int ctas = sync ? chain_grid : grid_for(total_tiles);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)ctas, 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = ls.smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  if (sync) {
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+  } else {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+  }
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  VPQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, single, list, ranges, total_tiles, ls.stages, cap_kt));
+  VPQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, single, list, ranges, total_tiles, ls.stages, cap_kt, count, sync));
+  return VPQ_OK;
+}
+
+// CTAs of a dependent chain: all must be resident at once, so at most what the occupancy
+// calculator grants for this kernel's shared memory, and no more than the largest GEMV has tiles.
+int chain_grid_for(int cap_kt, int max_row_tiles, int* out) {
+  const LaunchShape ls = shape_for(cap_kt);
+  auto kern = affine_qmv_w4g64_kernel;
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), g_granted, ls.smem)) { return rc; }
+  int per_sm = 0;
+  VPQ_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, ls.smem));
+  if (per_sm < 1) { return fail(VPQ_ERR_CUDA, "qmv chain: the kernel does not fit an SM"); }
+  if (per_sm > 2) { per_sm = 2; }
+  int grid = per_sm * num_sms();
+  if (grid > max_row_tiles) { grid = max_row_tiles; }
+  *out = grid;
   return VPQ_OK;
 }
 
@@ -643,12 +878,39 @@ int check_qmv_args(const char* who, const void* w, const void* scales, const voi
   return VPQ_OK;
 }
 
-// Validation of one descriptor, fused store included.
-int check_desc(const char* who, const vpq_linear_desc& d) {
+// Validation of one descriptor: shapes, fused store, RMSNorm prologue, expert gather.
+int check_desc(const char* who, const vpq_linear_desc& d, bool in_plan) {
   if (int rc = check_qmv_args(who, d.w, d.scales, d.biases, d.x, d.y, d.K, d.N, d.M)) { return rc; }
+  if (d.depends != 0 && d.depends != 1) { return fail(VPQ_ERR_INVALID_ARG, "%s: depends must be 0 or 1", who); }
+  if (d.depends && !in_plan) {
+    return fail(VPQ_ERR_UNSUPPORTED, "%s: depends is honoured by vpq_qmv_plan_create only", who);
+  }
+  if (d.norm_w) {
+    if (!aligned16(d.norm_w)) { return fail(VPQ_ERR_ALIGNMENT, "%s: norm_w must be 16-byte aligned", who); }
+    if (!(d.eps >= 0.0f)) { return fail(VPQ_ERR_INVALID_ARG, "%s: eps must be >= 0", who); }
+  }
+  if (d.expert) {
+    if (d.experts <= 0 || d.experts * d.N > (1ll << 30)) {
+      return fail(VPQ_ERR_INVALID_ARG, "%s: an expert gather needs 0 < experts, experts * N <= 2^30", who);
+    }
+    if (reinterpret_cast<uintptr_t>(d.expert) & 3) {
+      return fail(VPQ_ERR_ALIGNMENT, "%s: the expert index array must be 4-byte aligned", who);
+    }
+    if (d.x_div < 0) { return fail(VPQ_ERR_INVALID_ARG, "%s: x_div must be >= 0", who); }
+  } else if (d.experts > 1 || d.x_div > 1) {
+    return fail(VPQ_ERR_INVALID_ARG, "%s: experts / x_div given without an expert index array", who);
+  }
   return qmv_check_store(who, d);
 }
 }  // namespace
+
+// The kernels other than the 4-bit group-64 GEMV take plain descriptors only.
+int qmv_check_plain(const char* who, const vpq_linear_desc& d) {
+  if (d.norm_w || d.expert || d.depends || d.experts > 1 || d.x_div > 1) {
+    return fail(VPQ_ERR_UNSUPPORTED, "%s: norm_w, expert and depends are taken by the w4 g64 GEMV entry points only", who);
+  }
+  return qmv_check_store(who, d);
+}
 
 int qmv_check_store(const char* who, const vpq_linear_desc& d) {
   switch (d.epilogue) {
@@ -691,9 +953,11 @@ int fill_from_desc(QmvProblem* p, const vpq_linear_desc& d, int64_t m, int tile_
   const int64_t y_pitch = gated ? d.N / 2
                           : d.epilogue == VPQ_EPILOGUE_QKV  ? d.q_rows
                                                             : d.N;
+  const int64_t x_row = (d.expert && d.x_div > 1) ? m / d.x_div : m;  // pairs of one token share its row
   if (int rc = fill_problem(p, d.w, static_cast<const uint16_t*>(d.scales), static_cast<const uint16_t*>(d.biases),
-                            static_cast<const uint16_t*>(d.x) + m * d.K,
-                            static_cast<__nv_bfloat16*>(d.y) + m * y_pitch, (int)d.K, (int)d.N, tile_begin)) {
+                            static_cast<const uint16_t*>(d.x) + x_row * d.K,
+                            static_cast<__nv_bfloat16*>(d.y) + m * y_pitch, (int)d.K, (int)d.N, tile_begin,
+                            d.expert ? (int)d.experts : 1)) {
     return rc;
   }
   p->epilogue = d.epilogue;
@@ -705,12 +969,15 @@ int fill_from_desc(QmvProblem* p, const vpq_linear_desc& d, int64_t m, int tile_
     p->aux = static_cast<const uint16_t*>(d.aux) + m * d.k_rows;
     p->y3 = static_cast<__nv_bfloat16*>(d.y3) + m * (d.N - d.q_rows - d.k_rows);
   }
+  p->norm_w = static_cast<const uint16_t*>(d.norm_w);
+  p->eps = d.eps;
+  p->eid = d.expert ? d.expert + m : nullptr;
   return VPQ_OK;
 }
 
 // One launch per row of one descriptor (every row streams the weight again, as in the reference).
 int launch_desc_rows(const char* who, const vpq_linear_desc& d, cudaStream_t st) {
-  if (int rc = check_desc(who, d)) { return rc; }
+  if (int rc = check_desc(who, d, false)) { return rc; }
   if (int rc = require_sm100()) { return rc; }
   const int cap_kt = (int)((d.K + 255) / 256) * 2;
   for (int64_t m = 0; m < d.M; ++m) {
@@ -742,9 +1009,11 @@ using namespace vpq;
 struct vpq_qmv_plan_s {
   const QmvProblem* list_dev;
   const int2* ranges_dev;
-  int count;        // problems (one per GEMV row)
+  uint32_t* sync_dev;  // dependent chain: {finished tiles, CTAs that left}; null for independent GEMVs
+  int count;           // problems (one per GEMV row)
   int total_tiles;
   int cap_kt;
+  int chain_grid;
 };
 
 namespace {
@@ -840,7 +1109,7 @@ extern "C" size_t vpq_qmv_plan_bytes(const vpq_linear_desc* d, int count) {
   if (!d || count <= 0) { return 0; }
   size_t rows = 0;
   for (int i = 0; i < count; ++i) { rows += d[i].M > 0 ? (size_t)d[i].M : 0; }
-  return rows * sizeof(QmvProblem) + 64 + (kMaxGrid + 1) * sizeof(int2);
+  return rows * sizeof(QmvProblem) + 64 + (kMaxGrid + 1) * sizeof(int2) + 64 /* the chain's counters */;
 }
 
 extern "C" int vpq_qmv_plan_create(const vpq_linear_desc* d, int count, void* workspace, size_t bytes,
@@ -853,30 +1122,43 @@ extern "C" int vpq_qmv_plan_create(const vpq_linear_desc* d, int count, void* wo
     return fail(VPQ_ERR_INVALID_ARG, "qmv_plan_create: workspace of %zu bytes, %zu needed", bytes,
                 vpq_qmv_plan_bytes(d, count));
   }
+  bool chain = false;
   for (int i = 0; i < count; ++i) {
-    if (int rc = check_desc("qmv_plan_create", d[i])) { return rc; }
+    if (int rc = check_desc("qmv_plan_create", d[i], true)) { return rc; }
+    chain = chain || d[i].depends != 0;
   }
   if (int rc = require_sm100()) { return rc; }
   size_t rows = 0;
   for (int i = 0; i < count; ++i) { rows += (size_t)d[i].M; }
   QmvProblem* host = static_cast<QmvProblem*>(std::aligned_alloc(64, rows * sizeof(QmvProblem)));
   if (!host) { return fail(VPQ_ERR_INVALID_ARG, "qmv_plan_create: out of host memory"); }
-  int tiles = 0, cap_kt = 0;
+  int tiles = 0, cap_kt = 0, max_rt = 1;
   size_t r = 0;
   for (int i = 0; i < count; ++i) {
+    const int first_tile = tiles;  // a dependent descriptor waits for everything before it in the list
     for (int64_t m = 0; m < d[i].M; ++m, ++r) {
       const int rc = fill_from_desc(&host[r], d[i], m, tiles);
       if (rc) {
         std::free(host);
         return rc;
       }
+      host[r].wait_tiles = d[i].depends ? first_tile : 0;
       tiles += host[r].row_tiles;
+      max_rt = host[r].row_tiles > max_rt ? host[r].row_tiles : max_rt;
       const int kt = (int)((d[i].K + 255) / 256) * 2;
       cap_kt = kt > cap_kt ? kt : cap_kt;
     }
   }
   const uintptr_t dev = (reinterpret_cast<uintptr_t>(workspace) + 63) & ~(uintptr_t)63;
   const uintptr_t dev_ranges = dev + rows * sizeof(QmvProblem);
+  const uintptr_t dev_sync = (dev_ranges + (kMaxGrid + 1) * sizeof(int2) + 15) & ~(uintptr_t)15;
+  int chain_grid = 0;
+  if (chain) {
+    if (int rc = chain_grid_for(cap_kt, max_rt, &chain_grid)) {
+      std::free(host);
+      return rc;
+    }
+  }
   const int grid = grid_for(tiles);
   int2 host_ranges[kMaxGrid + 1];
   build_ranges(host, rows, grid, host_ranges);
@@ -887,15 +1169,18 @@ extern "C" int vpq_qmv_plan_create(const vpq_linear_desc* d, int count, void* wo
     e = cudaMemcpyAsync(reinterpret_cast<void*>(dev_ranges), host_ranges, (size_t)(grid + 1) * sizeof(int2),
                         cudaMemcpyHostToDevice, st);
   }
+  if (e == cudaSuccess) { e = cudaMemsetAsync(reinterpret_cast<void*>(dev_sync), 0, 16, st); }
   if (e == cudaSuccess) { e = cudaStreamSynchronize(st); }
   std::free(host);
   if (e != cudaSuccess) { return fail(VPQ_ERR_CUDA, "qmv_plan_create: copy failed: %s", cudaGetErrorString(e)); }
   vpq_qmv_plan* plan = new vpq_qmv_plan_s();
   plan->list_dev = reinterpret_cast<const QmvProblem*>(dev);
   plan->ranges_dev = reinterpret_cast<const int2*>(dev_ranges);
+  plan->sync_dev = chain ? reinterpret_cast<uint32_t*>(dev_sync) : nullptr;
   plan->count = (int)rows;
   plan->total_tiles = tiles;
   plan->cap_kt = cap_kt;
+  plan->chain_grid = chain_grid;
   *out = plan;
   return VPQ_OK;
 }
@@ -906,14 +1191,18 @@ extern "C" int vpq_qmv_plan_run(const vpq_qmv_plan* plan, void* stream) {
   if (int rc = require_sm100()) { return rc; }
   QmvProblem unused;
   std::memset(&unused, 0, sizeof(unused));
+  if (plan->sync_dev) {
+    return launch_list(unused, plan->list_dev, nullptr, plan->total_tiles, plan->cap_kt,
+                       static_cast<cudaStream_t>(stream), plan->count, plan->sync_dev, plan->chain_grid);
+  }
   return launch_list(unused, plan->list_dev, plan->ranges_dev, plan->total_tiles, plan->cap_kt,
-                     static_cast<cudaStream_t>(stream));
+                     static_cast<cudaStream_t>(stream), plan->count);
 }
 
 // ---------------------------------------------------------------- no-allocation variant
 // The plan kernel needs its list of problem descriptors in device memory. This variant keeps that
 // list in a fixed array that is part of the library image, so the call neither allocates nor needs
-// a caller workspace. Every GPU that loads the library carries the array (28 KB) until exit.
+// a caller workspace. Every GPU that loads the library carries the array (40 KB) until exit.
 constexpr int kNoAllocMaxRows = 64;  // GEMV rows (sum of M over the set) one call can take
 static __device__ __align__(256) unsigned char
     g_noalloc_descs[kNoAllocMaxRows * sizeof(QmvProblem) + (kMaxGrid + 1) * sizeof(int2)];  // records, then the CTA ranges
@@ -923,7 +1212,7 @@ extern "C" int vpq_affine_qmv_w4g64_bf16_set_noalloc(const vpq_linear_desc* d, i
   if (!d || count <= 0) { return fail(VPQ_ERR_INVALID_ARG, "qmv_set_noalloc: null or empty set"); }
   int64_t rows = 0;
   for (int i = 0; i < count; ++i) {
-    if (int rc = check_desc("qmv_set_noalloc", d[i])) { return rc; }
+    if (int rc = check_desc("qmv_set_noalloc", d[i], false)) { return rc; }
     rows += d[i].M;
   }
   if (rows > kNoAllocMaxRows) {
@@ -933,6 +1222,15 @@ extern "C" int vpq_affine_qmv_w4g64_bf16_set_noalloc(const vpq_linear_desc* d, i
                 (long long)rows, kNoAllocMaxRows);
   }
   if (int rc = require_sm100()) { return rc; }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The descriptors travel from this call's stack by stream-ordered copies: a captured copy node
+  // would keep pointers into a dead stack frame and replay them, so the call refuses to be captured.
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  VPQ_CUDA_OK(cudaStreamIsCapturing(st, &capturing));
+  if (capturing != cudaStreamCaptureStatusNone) {
+    return fail(VPQ_ERR_UNSUPPORTED, "qmv_set_noalloc: the stream is being captured; this entry point cannot be "
+                                     "recorded into a CUDA graph (use vpq_qmv_plan_create / vpq_qmv_plan_run)");
+  }
   // Device address of the array, looked up once per device with that device current. In host code
   // the array's name is only a handle for this lookup, never a pointer a kernel could use.
   static void* dev_addr[64] = {};
@@ -954,7 +1252,6 @@ extern "C" int vpq_affine_qmv_w4g64_bf16_set_noalloc(const vpq_linear_desc* d, i
       cap_kt = kt > cap_kt ? kt : cap_kt;
     }
   }
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   // every descriptor the kernel will read is rewritten here, so nothing stale from the previous
   // call is ever used; the copy is ordered before the launch on the same stream
   VPQ_CUDA_OK(cudaMemcpyAsync(dev_addr[dev], host, (size_t)r * sizeof(QmvProblem), cudaMemcpyHostToDevice, st));
@@ -966,7 +1263,7 @@ extern "C" int vpq_affine_qmv_w4g64_bf16_set_noalloc(const vpq_linear_desc* d, i
   QmvProblem unused;
   std::memset(&unused, 0, sizeof(unused));
   return launch_list(unused, static_cast<const QmvProblem*>(dev_addr[dev]), static_cast<const int2*>(dev_ranges), tiles,
-                     cap_kt, st);
+                     cap_kt, st, r);
 }
 
 extern "C" int vpq_qmv_plan_destroy(vpq_qmv_plan* plan) {

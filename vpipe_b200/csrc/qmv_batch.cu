@@ -615,7 +615,7 @@ vpq_linear_desc plain_desc(const uint32_t* w, const void* scales, const void* bi
 
 int batch_g64(const char* who, const vpq_linear_desc& d, void* stream) {
   if (int rc = check_batch_args(who, d.w, d.scales, d.biases, d.x, d.y, d.K, d.N, d.M, 64)) { return rc; }
-  if (int rc = qmv_check_store(who, d)) { return rc; }
+  if (int rc = qmv_check_plain(who, d)) { return rc; }
   if (int rc = require_sm100()) { return rc; }
   const int per_pass = rows_per_pass<64>((int)((d.K + 255) / 256) * 2);
   if (per_pass < 2 || d.M == 1) {  // long rows (K > 8192) do not fit twice in shared memory: one row at a time
@@ -626,7 +626,7 @@ int batch_g64(const char* who, const vpq_linear_desc& d, void* stream) {
 
 int gemv_g32(const char* who, const vpq_linear_desc& d, void* stream) {
   if (int rc = check_batch_args(who, d.w, d.scales, d.biases, d.x, d.y, d.K, d.N, d.M, 32)) { return rc; }
-  if (int rc = qmv_check_store(who, d)) { return rc; }
+  if (int rc = qmv_check_plain(who, d)) { return rc; }
   if (int rc = require_sm100()) { return rc; }
   const int per_pass = rows_per_pass<32>((int)((d.K + 255) / 256) * 2);  // 2 rows per weight stream where they fit
   return launch_batch<32>(who, d, per_pass, static_cast<cudaStream_t>(stream), false);

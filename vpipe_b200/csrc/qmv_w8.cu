@@ -13,7 +13,8 @@
 // column (digit, parity) gets the digit's bytes in the half of B that belongs to its group and
 // zeros in the other, so a lane ends up with digit t's sums for both groups and both of its rows
 // and folds them with the groups' scales (lane 3 of a quad folds the bias term b * sum(x)).
-// x is staged per CTA as digit bytes in natural k order. Every barrier wait is bounded.
+// Every warp stages the part of x it multiplies as digit bytes in natural k order, each 128-k box with
+// its own power-of-two scale. Every barrier wait is bounded.
 #include "vpq_sm100.cuh"
 
 #include <cstring>
@@ -88,8 +89,8 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
   float* zero16 = xg + ((2 * cap_kt + 3) & ~3);                  // 16 bytes of zeros, 16-byte aligned (cap_kt may be odd)
   float* red = zero16 + 4;                                       // [kRedSlots][kConsWarps][16]
   uint32_t* red_cnt = reinterpret_cast<uint32_t*>(red + kRedSlots * kConsWarps * 16);
-  uint32_t* amax_buf = red_cnt + kRedSlots;                      // [kConsWarps]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(amax_buf + kConsWarps);
+  float* xu = reinterpret_cast<float*>(red_cnt + kRedSlots);     // [cap_kt] 1 / scale of every 128-k box of x
+  uint64_t* bars = reinterpret_cast<uint64_t*>(xu + ((cap_kt + 1) & ~1));
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * kMaxStages);
   const uint32_t bar0 = smem_u32(bars);
   auto bar_full = [&](int s) { return bar0 + 8u * s; };
@@ -160,52 +161,44 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
 
   asm volatile("griddepcontrol.wait;" ::: "memory");  // x may come from the previous kernel
 
-  // ---- staging of x as signed digit bytes (all consumer warps together): scaled by a power of two
-  // so that max |x| lands in [2^21, 2^22), rounded to an integer X (exact for every bf16 value
-  // within 2^-14 of the maximum), X = d0 + 256 d1 + 65536 d2 with digits in [-128, 127]; digit
-  // plane d of k tile kt holds the 128 bytes d(X[128 kt .. 128 kt + 127]) in order.
-  float x_unscale;
+  // ---- staging of x as signed digit bytes. Warp w converts exactly the 128-k boxes it will
+  // multiply (box w of every stage), a quarter warp per box, so no CTA barrier is involved. Every
+  // box carries its own power-of-two scale: its largest magnitude lands in [2^21, 2^22) and every
+  // value is rounded to an integer X (exact within 2^-14 of the box's maximum, off by at most
+  // 2^-22 of it otherwise), X = d0 + 256 d1 + 65536 d2 with digits in [-128, 127]; digit plane d
+  // of k tile kt holds the 128 bytes d(X[128 kt .. 128 kt + 127]) in order. xu[kt] = 1 / scale.
   {
-    const int pieces = NB * 8;  // 16-value pieces of the padded x
-    uint32_t amax = 0;
-    for (int i = threadIdx.x; i * 16 < K; i += kConsThreads) {
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const uint4 in = *reinterpret_cast<const uint4*>(P.x + i * 16 + 8 * h);
-        const uint32_t v[4] = {in.x, in.y, in.z, in.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) { amax = max(amax, max(v[j] & 0x7fffu, (v[j] >> 16) & 0x7fffu)); }
-      }
-    }
-    amax = __reduce_max_sync(0xffffffffu, amax);
-    if (lane == 0) { amax_buf[warp] = amax; }
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsThreads) : "memory");  // consumers only
-    amax = 0;
-#pragma unroll
-    for (int ww = 0; ww < kConsWarps; ++ww) { amax = max(amax, amax_buf[ww]); }
-    int e = (int)(amax >> 7);            // biased exponent of the largest magnitude
-    e = min(max(e, 22), 254);            // all-zero / denormal x: keep both factors normal
-    const float x_scale = __uint_as_float((uint32_t)(275 - e) << 23);  // 2^(148 - e)
-    x_unscale = __uint_as_float((uint32_t)(e - 21) << 23);             // its exact inverse
-    for (int i = threadIdx.x; i - lane < pieces; i += kConsThreads) {  // warp-uniform trip count: shuffles inside
-      const bool live = i < pieces;
+    const int quarter = lane >> 3, sub = lane & 7;
+    const int passes = (SPT + 3) >> 2;  // four boxes of this warp per pass
+    for (int j = 0; j < passes; ++j) {
+      const int kt = (4 * j + quarter) * kBoxesPerStage + warp;
+      const bool live = kt < NB;
+      const int k0 = kt * 128 + sub * 16;
       uint4 in0 = make_uint4(0, 0, 0, 0), in1 = in0;
-      if (live && i * 16 < K) {
-        in0 = *reinterpret_cast<const uint4*>(P.x + i * 16);
-        in1 = *reinterpret_cast<const uint4*>(P.x + i * 16 + 8);
+      if (k0 < K) {
+        in0 = *reinterpret_cast<const uint4*>(P.x + k0);
+        in1 = *reinterpret_cast<const uint4*>(P.x + k0 + 8);
       }
       const uint32_t v[8] = {in0.x, in0.y, in0.z, in0.w, in1.x, in1.y, in1.z, in1.w};
+      uint32_t amax = 0;  // largest |x| of the box as bf16 bits
+#pragma unroll
+      for (int q = 0; q < 8; ++q) { amax = max(amax, max(v[q] & 0x7fffu, (v[q] >> 16) & 0x7fffu)); }
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) { amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, o)); }
+      int e = (int)(amax >> 7);            // biased exponent of the largest magnitude
+      e = min(max(e, 22), 254);            // all-zero / denormal box: keep both factors normal
+      const float x_scale = __uint_as_float((uint32_t)(275 - e) << 23);  // 2^(148 - e)
       // round(x * scale) on the FMA pipe: the low bits of fma(x, scale, 1.5 * 2^23) are
       // 0x4B400000 + X; one add turns that into X + 0x808080 (bytes 0..2 = digits + 128).
       uint32_t z[16];
       uint32_t sum = 0;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const uint32_t lo = __float_as_uint(__fmaf_rn(__uint_as_float(v[j] << 16), x_scale, kAccInitF));
-        const uint32_t hi = __float_as_uint(__fmaf_rn(__uint_as_float(v[j] & 0xffff0000u), x_scale, kAccInitF));
+      for (int q = 0; q < 8; ++q) {
+        const uint32_t lo = __float_as_uint(__fmaf_rn(__uint_as_float(v[q] << 16), x_scale, kAccInitF));
+        const uint32_t hi = __float_as_uint(__fmaf_rn(__uint_as_float(v[q] & 0xffff0000u), x_scale, kAccInitF));
         sum += lo + hi;
-        z[2 * j] = lo + (0x808080u - (uint32_t)kAccInit);
-        z[2 * j + 1] = hi + (0x808080u - (uint32_t)kAccInit);
+        z[2 * q] = lo + (0x808080u - (uint32_t)kAccInit);
+        z[2 * q + 1] = hi + (0x808080u - (uint32_t)kAccInit);
       }
       sum -= 16u * (uint32_t)kAccInit;  // = sum of the 16 X, modulo 2^32
       uint32_t plane[3][4];             // digit d of values 4 q .. 4 q + 3 -> plane[d][q]
@@ -219,7 +212,7 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
         plane[2][q] = __byte_perm(t2, t3, 0x5410) ^ 0x80808080u;
       }
       if (live) {
-        unsigned char* dst = xq + (size_t)(i >> 3) * kXBytesPerKt + (i & 7) * 16;
+        unsigned char* dst = xq + (size_t)kt * kXBytesPerKt + sub * 16;
 #pragma unroll
         for (int d = 0; d < 3; ++d) {
           *reinterpret_cast<uint4*>(dst + d * 128) = make_uint4(plane[d][0], plane[d][1], plane[d][2], plane[d][3]);
@@ -227,9 +220,10 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
       }
       sum += __shfl_xor_sync(0xffffffffu, sum, 1);
       sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      if (live && (i & 3) == 0) { xg[i >> 2] = (float)(int)sum; }
+      if (live && (sub & 3) == 0) { xg[kt * 2 + (sub >> 2)] = (float)(int)sum; }
+      if (live && sub == 0) { xu[kt] = __uint_as_float((uint32_t)(e - 21) << 23); }  // exact inverse of x_scale
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsThreads) : "memory");
+    __syncwarp();
   }
 
   // Accumulator column c (fed by the lanes with g == c) = (digit c >> 1, group parity c & 1).
@@ -301,10 +295,14 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
         // whose accumulators hold the bare initial value)
         const float k0 = kAccInitF - xs.x, k1 = kAccInitF - xs.y;
         auto val = [](int a, int b, float k) { return (__int_as_float(a) - kAccInitF) + (__int_as_float(b) - k); };
-        res_a = __fmaf_rn(__uint_as_float(sa << 16), val(ca[0], cb[0], k0), res_a);
-        res_a = __fmaf_rn(__uint_as_float(sa & 0xffff0000u), val(ca[1], cb[1], k1), res_a);
-        res_b = __fmaf_rn(__uint_as_float(sb2 << 16), val(ca[2], cb[2], k0), res_b);
-        res_b = __fmaf_rn(__uint_as_float(sb2 & 0xffff0000u), val(ca[3], cb[3], k1), res_b);
+        // the box's two groups folded with their scales, then its 1 / x-scale brings the sum to true units
+        const float xu_box = xu[kt];
+        float box_a = __fmul_rn(__uint_as_float(sa << 16), val(ca[0], cb[0], k0));
+        box_a = __fmaf_rn(__uint_as_float(sa & 0xffff0000u), val(ca[1], cb[1], k1), box_a);
+        float box_b = __fmul_rn(__uint_as_float(sb2 << 16), val(ca[2], cb[2], k0));
+        box_b = __fmaf_rn(__uint_as_float(sb2 & 0xffff0000u), val(ca[3], cb[3], k1), box_b);
+        res_a = __fmaf_rn(xu_box, box_a, res_a);
+        res_b = __fmaf_rn(xu_box, box_b, res_b);
       }
       __syncwarp();
       if (lane == 0) { mbar_arrive(bar_empty(s)); }
@@ -339,7 +337,7 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
           v += *reinterpret_cast<volatile float*>(&red[(slot * kConsWarps + ww) * 16 + lane]);
         }
         const int row = (tile << 4) + lane;
-        fused_store(P.epilogue, v * x_unscale, row, N, lane, P.y, P.aux, P.y3, P.q_rows, P.k_rows);
+        fused_store(P.epilogue, v, row, N, lane, P.y, P.aux, P.y3, P.q_rows, P.k_rows);
       }
       __syncwarp();
       if (lane == 0) { red_cnt[slot] = 0; }
@@ -349,7 +347,7 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
 
 size_t fixed_smem(int cap_kt) {
   return 1024 /*alignment slack*/ + 128 + (size_t)cap_kt * kXBytesPerKt + (size_t)((2 * cap_kt + 3) & ~3) * 4 + 16 +
-         (size_t)kRedSlots * kConsWarps * 16 * 4 + kRedSlots * 4 + kConsWarps * 4 + 2 * kMaxStages * 8 + 16;
+         (size_t)kRedSlots * kConsWarps * 16 * 4 + kRedSlots * 4 + (size_t)((cap_kt + 1) & ~1) * 4 + 2 * kMaxStages * 8 + 16;
 }
 
 }  // namespace
@@ -389,7 +387,7 @@ int launch_w8(const char* who, const vpq_linear_desc& d, void* stream) {
       (reinterpret_cast<uintptr_t>(biases) & 1) || (reinterpret_cast<uintptr_t>(y) & 1)) {
     return fail(VPQ_ERR_ALIGNMENT, "%s: w and x must be 16-byte aligned", who);
   }
-  if (int rc = qmv_check_store(who, d)) { return rc; }
+  if (int rc = qmv_check_plain(who, d)) { return rc; }
   if (int rc = require_sm100()) { return rc; }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Problem8 p;

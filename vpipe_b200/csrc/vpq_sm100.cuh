@@ -55,8 +55,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 constexpr uint32_t kWaitHintNs = 1000;     // how long one try_wait may sleep
 constexpr uint32_t kWaitPolls = 1u << 21;  // polls before a wait gives up (about 2 s of sleeping)
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t code,
-                                          volatile uint32_t* abort_flag, uint32_t* status_word) {
+__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, uint32_t code,
+                                                  volatile uint32_t* abort_flag, uint32_t* status_word,
+                                                  uint32_t polls, uint32_t hint_ns) {
   uint32_t done;
   asm volatile(
       "{\n\t"
@@ -74,12 +75,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
       "VPQ_WAIT_DONE:\n\t"
       "}"
       : "=r"(done)
-      : "r"(bar), "r"(parity), "r"(kWaitHintNs), "r"(kWaitPolls)
+      : "r"(bar), "r"(parity), "r"(hint_ns), "r"(polls)
       : "memory");
   if (done) { return true; }
   *abort_flag = 1;
   atomicCAS(status_word, 0u, code);
   return false;
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t code,
+                                          volatile uint32_t* abort_flag, uint32_t* status_word) {
+  return mbar_wait_limited(bar, parity, code, abort_flag, status_word, kWaitPolls, kWaitHintNs);
 }
 
 // The same wait for a whole warp: every lane polls, then the lanes agree, so a

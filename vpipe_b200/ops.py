@@ -219,24 +219,35 @@ EPILOGUES = {"none": 0, "add": 1, "swiglu": 2, "qkv": 3, "geglu": 4, "gelu_mul":
 
 def qmv_set(problems):
     """Builds the host descriptor array for qmv_batch / QmvPlan from (codes, scales, biases, x, y)
-    tuples; an optional sixth element is a dict describing a fused store:
+    tuples; an optional sixth element is a dict describing a fused store and the other options:
     {"epilogue": "add", "aux": residual} | {"epilogue": "swiglu"} | {"epilogue": "geglu"} |
     {"epilogue": "gelu_mul", "aux": mul} |
-    {"epilogue": "qkv", "aux": k_out, "y3": v_out, "q_rows": .., "k_rows": ..}."""
+    {"epilogue": "qkv", "aux": k_out, "y3": v_out, "q_rows": .., "k_rows": ..};
+    "norm_w": weights [K] and "eps" (RMSNorm of x while it is staged); "depends": True (plans: this
+    GEMV reads what earlier entries write); "expert": int32 device tensor [M] with "x_div" (codes is
+    then [E, N, K/8]: row m uses slab expert[m] and reads x row m // x_div); "M": rows, when x holds
+    fewer rows than the descriptor has (expert gather)."""
     arr = (_lib.LinearDesc * len(problems))()
     for d, prob in zip(arr, problems):
         codes, scales, biases, x, y = prob[:5]
-        N, Kw = codes.shape
+        e = prob[5] if len(prob) > 5 and prob[5] else {}
+        N, Kw = codes.shape[-2], codes.shape[-1]
         d.w, d.scales, d.biases, d.x, d.y = _ptr(codes), _ptr(scales), _ptr(biases), _ptr(x), _ptr(y)
-        d.K, d.N, d.M = Kw * 8, N, x.numel() // (Kw * 8)
-        if len(prob) > 5 and prob[5]:
-            e = prob[5]
-            d.epilogue = EPILOGUES[e["epilogue"]]
-            if e.get("aux") is not None:
-                d.aux = _ptr(e["aux"])
-            if e.get("y3") is not None:
-                d.y3 = _ptr(e["y3"])
-            d.q_rows, d.k_rows = e.get("q_rows", 0), e.get("k_rows", 0)
+        d.K, d.N, d.M = Kw * 8, N, e.get("M", x.numel() // (Kw * 8))
+        d.epilogue = EPILOGUES[e.get("epilogue", "none")]
+        if e.get("aux") is not None:
+            d.aux = _ptr(e["aux"])
+        if e.get("y3") is not None:
+            d.y3 = _ptr(e["y3"])
+        d.q_rows, d.k_rows = e.get("q_rows", 0), e.get("k_rows", 0)
+        d.depends = 1 if e.get("depends") else 0
+        if e.get("norm_w") is not None:
+            d.norm_w = _ptr(e["norm_w"])
+            d.eps = float(e.get("eps", 1e-6))
+        if e.get("expert") is not None:
+            d.expert = _ptr(e["expert"])
+            d.experts = codes.shape[0]
+            d.x_div = int(e.get("x_div", 1))
     return arr
 
 
@@ -376,7 +387,7 @@ def function(library: str, entry: str):
 
 
 def dispatch(fn, buffers, K=0, N=0, M=0, clip=1.0, q_rows=0, k_rows=0, v_rows=0, out_stride=0, out_off=0,
-             experts=0, rows=0, stream=None) -> None:
+             experts=0, rows=0, top_k=0, eps=0.0, stream=None) -> None:
     """One dispatch with the reference's slot numbering (see include/vpq.h). `buffers` is a list
     indexed by slot, or a dict {slot: tensor}."""
     a = _lib.DispatchArgs()
@@ -386,4 +397,5 @@ def dispatch(fn, buffers, K=0, N=0, M=0, clip=1.0, q_rows=0, k_rows=0, v_rows=0,
     a.K, a.N, a.M, a.clip = K, N, M, clip
     a.q_rows, a.k_rows, a.v_rows = q_rows, k_rows, v_rows
     a.out_stride, a.out_off, a.experts, a.rows = out_stride, out_off, experts, rows
+    a.top_k, a.eps = top_k, eps
     check(lib().vpq_dispatch(fn, C.byref(a), _stream(stream)))
