@@ -1,31 +1,40 @@
 #!/usr/bin/env python
 """Benchmark of the 4-bit affine quantized linear on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5]
-                    [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload c2|c3|c4|c5|c1|plan|decode_chain|qmm|qmm_swiglu|qmm_w8|moe|...] [shape ...]
 
-Default (what the headline metric is quoted on): the decode-layer QMV set of an
-8B Qwen3-style decoder at batch 1 -- q, k, v, gate, up, down at M = 1 -- for all
-36 layers with distinct weights (3.57 GB, larger than L2, so everything
-streams from HBM). One step = one pass over the 36 layers = 216 GEMVs, run as one
-plan launch (vpq_qmv_plan_run); --no-plan replays 216 separate launches as a graph.
-`value` is algorithmic GB/s with everything resident in HBM; `e2e` is the same
-pass driven through the C ABI with the step's activations copied from pinned
-host memory and the result read back, inside the timed region. The same JSON
-line carries `qmm`: the tensor-core GEMM on the prefill / DiT shapes in
-TFLOP/s (column-split with an NCCL all-gather when N > 1).
+Default workload c2 (what the headline metric is quoted on): the decode-layer QMV set of an 8B
+Qwen3-style decoder at batch 1 -- q, k, v, gate, up, down at M = 1 -- for all 36 layers with
+distinct weights (3.57 GB, larger than L2, so everything streams from HBM). One step = one pass
+over the 36 layers = 216 GEMVs, run as one plan launch (vpq_qmv_plan_run); --no-plan replays 216
+separate launches as a graph. `value` is algorithmic GB/s with everything resident in HBM; `e2e`
+is the same pass driven through the C ABI with the step's activations copied from pinned host
+memory and the result read back, inside the timed region. The same JSON line carries
+  c1            the single 4096 x 4096 GEMV of configs[0], cold weights, one launch per GEMV
+  decode_chain  36 decoder layers as a DEPENDENT chain (norm + q|k|v, o + residual, norm + gate|up
+                with SwiGLU, down + residual; each GEMV reads what the one before wrote), as one
+                chained launch and as one launch per GEMV, with a bit-identity check between them
+  qmm, qmm_c3   the tensor-core GEMM on the DiT (C4) and prefill (C3) shapes in TFLOP/s
+  cpu_baseline  the reference's CPU arithmetic for the same op on the host cores (QMV and QMM).
 
-With N > 1 (launched under torchrun) the QMV set runs as N independent replicas
-(decode at batch 1 does not shard; weak scaling); the QMM section is the part
-that is partitioned across GPUs.
+With N > 1 (torchrun) the QMV set runs as N independent replicas (decode at batch 1 does not
+shard: "replicas only"); the `qmm` section is the part that is partitioned across the GPUs
+(column split): per shape the unsharded time on the same box, the fused peer-store form, GEMM +
+NCCL all-gather (whole and in 4 row chunks), the bytes that cross NVLink, and a bit-identity
+check of the gathered result against the unsharded kernel (the run exits non-zero on a mismatch).
 
-Inputs are synthetic: weights N(0, 0.02) quantised with the reference recipe on
-the device, activations N(0, 1) bf16; seeded.
+Inputs are synthetic: weights N(0, 0.02) quantised with the reference recipe on the device,
+activations N(0, 1) bf16; seeded. The small workloads at the end of the list (plan LAYERS,
+decode_chain LAYERS, qmm M K N, qmm_swiglu M K N, qmm_w8 M K N, qmv K N, qmv_w8 K N,
+qmv_batch K N M, moe T E TOPK HIDDEN FFN) run one kernel on a small case and print one JSON line;
+they are what the ncu summaries under profiles/ were taken from.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -41,12 +50,13 @@ if ROOT not in sys.path:
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 LAYERS = 36
+MIN_TIMED_SECONDS = 0.5     # the headline's timed blocks are repeated until this much has been timed
+NVLINK_GBS_MEASURED = 770.0  # peer copy per direction per GPU on this pool; nominal 900
 
-# DRAM traffic per launch measured once with ncu (dram__bytes_read.sum +
-# dram__bytes_write.sum) as a multiple of the algorithmic bytes of that launch, from a 4-layer
-# plan (profiles/qmv_plan_c2_4layers.md: 401.4 MB moved for 396.9 MB algorithmic); traffic grows
-# in proportion to the layers, so the 36-layer launch is scaled by it. The QMM is tensor-bound
-# and its y stays in L2 during a capture, so no DRAM figure is reported for it.
+# DRAM traffic per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) as a
+# multiple of the launch's algorithmic bytes, on small cases whose traffic grows in proportion to
+# the work: a 4-layer plan launch of the C2 set (401.4 MB moved for 396.9 MB algorithmic), and
+# the GEMM at M = K = N = 8192 (x + W + y exceed L2).
 QMV_TRAFFIC_RATIO = 1.011
 QMM_TRAFFIC_RATIO = None
 
@@ -60,6 +70,14 @@ def peaks():
                 "source": "measured"}
     return {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": FALLBACK_BF16_TFLOPS,
             "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def host_cores() -> int:
+    """Cores this process may run on. Not OMP_NUM_THREADS: torchrun sets that to 1."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
 
 
 class ClockSampler:
@@ -173,52 +191,110 @@ def dist_env(args):
     return rank, world, local
 
 
-# ------------------------------------------------------------------ reference arm
+# ------------------------------------------------------------------ CPU arms (oracle port)
+
+def _cpu_qmv_layer(synth, tag):
+    layer = []
+    for p in synth.CONFIGS["C2"].projs:
+        codes, s, b = synth.random_qweight(p.N, p.K, synth.seed_for(tag, p.name))
+        x = synth.activations_bf16(1, p.K, synth.seed_for(tag + "x", p.name))
+        layer.append((codes, s, b, x))
+    return layer, sum(synth.qmv_bytes(p.K, p.N, 1) for p in synth.CONFIGS["C2"].projs)
+
+
+def _cpu_qmm_shapes(synth, key, rows, tag):
+    """One M-slice of `rows` rows of every shape of a QMM config: the CPU cost is linear in M (the
+    dequantisation of the whole weight is part of every step, as it would be of a full-M step)."""
+    shapes = []
+    for p in synth.CONFIGS[key].projs:
+        codes, s, b = synth.random_qweight(p.N, p.K, synth.seed_for(tag, key, p.name))
+        x = synth.activations_bf16(rows, p.K, synth.seed_for(tag + "x", key, p.name))
+        shapes.append((codes, s, b, x, synth.qmm_flops(p.K, p.N, rows)))
+    return shapes
+
+
+def cpu_baseline_qmv(synth, seconds_budget=10.0):
+    """The oracle port (f32 dequantise + blocked fp32 GEMM, all host cores) on a bounded sample of
+    the C2 set: whole decoder layers until the time budget is used."""
+    import oracle
+    oracle.build()
+    layer, bytes_layer = _cpu_qmv_layer(synth, "cpu")
+    threads = host_cores()
+    for codes, s, b, x in layer:   # warm
+        oracle.cpu_linear_seconds(codes, s, b, x, threads)
+    t, n = 0.0, 0
+    while t < seconds_budget and n < LAYERS:
+        for codes, s, b, x in layer:
+            t += oracle.cpu_linear_seconds(codes, s, b, x, threads)[0]
+        n += 1
+    return {"value": bytes_layer * n / t / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"{n} of {LAYERS} decoder layers (6 QMV projections each), "
+                      "f32 dequantise + blocked fp32 GEMM, OpenMP"}
+
+
+def cpu_baseline_qmm(synth, key, rows=256):
+    """The same CPU arithmetic on the GEMM shapes of one config, on an M-slice (linear in M)."""
+    import oracle
+    oracle.build()
+    threads = host_cores()
+    shapes = _cpu_qmm_shapes(synth, key, rows, "cpuqmm")
+    t, flops = 0.0, 0.0
+    for codes, s, b, x, fl in shapes:
+        t += oracle.cpu_linear_seconds(codes, s, b, x, threads)[0]
+        flops += fl
+    return {"value": flops / t / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "sample": f"{key}: every shape on an M-slice of {rows} of {synth.CONFIGS[key].M} rows "
+                      "(cost is linear in M); f32 dequantise of the whole weight + blocked fp32 GEMM, OpenMP"}
+
 
 def run_reference(args, rank, world):
-    """The reference's CPU path for this op, timed on the host cores. The reference has no
-    CPU matmul: this is its f32 dequantise routine plus a plain blocked fp32 GEMM (the
-    oracle port), all host threads. Each step is a bounded sample of the workload."""
+    """The reference's CPU path for this op, timed on the host cores. The reference has no CPU
+    matmul: this is its f32 dequantise routine plus a plain blocked fp32 GEMM (the oracle port), on
+    all host cores. Each step is a bounded sample of the workload."""
     if rank != 0:
         return
-    import numpy as np
-
     import oracle
     from vpipe_b200 import synth
     oracle.build()
-    cfg = synth.CONFIGS["C2"]
-    layer = []
-    for p in cfg.projs:   # one decoder layer = the sample processed per step
-        codes, s, b = synth.random_qweight(p.N, p.K, synth.seed_for("ref", p.name))
-        x = synth.activations_bf16(1, p.K, synth.seed_for("refx", p.name))
-        layer.append((codes, s, b, x, synth.qmv_bytes(p.K, p.N, 1)))
-    bytes_step = sum(t[4] for t in layer)
-    threads = oracle.max_threads()
+    threads = host_cores()
+    wl = args.workload if args.workload in ("c3", "c4", "c5") else "c2"
+    if wl == "c2":
+        layer, per_step = _cpu_qmv_layer(synth, "ref")
+        metric, unit, scale = "int4_qmv_hbm_gbps", "GB/s", 1e9
+        workload = "C2 decode-layer QMV set, 8B Qwen3-style decoder, M=1"
+        sample = "1 of 36 layers per step (6 projections, 99.2 MB of weights)"
 
-    def step():
-        t = 0.0
-        for codes, s, b, x, _ in layer:
-            t += oracle.cpu_linear_seconds(codes, s, b, x, threads)[0]
-        return t
+        def step():
+            return sum(oracle.cpu_linear_seconds(c, s, b, x, threads)[0] for c, s, b, x in layer)
+    else:
+        key = wl.upper()
+        rows = 512 if key != "C5" else 256
+        shapes = _cpu_qmm_shapes(synth, key, rows, "ref")
+        per_step = sum(sh[4] for sh in shapes)
+        metric, unit, scale = "int4_qmm_tflops", "TFLOP/s", 1e12
+        workload = f"{key} {synth.CONFIGS[key].what}"
+        sample = f"every shape on an M-slice of {rows} of {synth.CONFIGS[key].M} rows per step"
 
-    for _ in range(max(args.warmup, 1)):
+        def step():
+            return sum(oracle.cpu_linear_seconds(c, s, b, x, threads)[0] for c, s, b, x, _ in shapes)
+
+    for _ in range(max(min(args.warmup, 3), 1)):
         step()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         step()
     dt = time.perf_counter() - t0
-    val = bytes_step * args.steps / dt / 1e9
+    val = per_step * args.steps / dt / scale
     line = {
-        "impl": "reference", "metric": "int4_qmv_hbm_gbps", "value": val, "unit": "GB/s",
+        "impl": "reference", "metric": metric, "value": val, "unit": unit,
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "int4*bf16->f32", "data": "synthetic",
-        "config": {"workload": "C2 decode-layer QMV set, 8B Qwen3-style decoder, M=1",
-                   "sample": "1 of 36 layers per step (6 projections, 99.2 MB of weights)"},
-        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port",
-                         "sample": "one decoder layer (q,k,v,gate,up,down at M=1) per step; "
-                                   "f32 dequantise + blocked fp32 GEMM, OpenMP"},
-        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak" if wl == "c2" else "strong",
+        "vs_baseline": None, "dtype": "int4 x bf16 -> f32", "data": "synthetic",
+        "config": {"workload": workload, "sample": sample},
+        "cpu_baseline": {"value": val, "unit": unit, "cores": threads, "kind": "port",
+                         "sample": sample + "; f32 dequantise + blocked fp32 GEMM, OpenMP"},
+        "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
@@ -232,6 +308,15 @@ def make_linear(torch, ops, N, K, seed, dev):
     codes, s16, b16 = ops.quantize(w)
     s, b = ops.scales_to_bf16(s16), ops.scales_to_bf16(b16)
     del w, s16, b16
+    return codes, s, b
+
+
+def rand_weight(torch, N, K, dev, bits=4):
+    """Random packed codes with bf16 scales / biases (the distribution of the reference's kernel tests)."""
+    codes = torch.randint(-2**31, 2**31 - 1, (N, K * bits // 32), dtype=torch.int32, device=dev)
+    lo, span = (0.005, 0.015) if bits == 4 else (0.0003, 0.001)
+    s = (torch.rand((N, K // 64), device=dev) * span + lo).to(torch.bfloat16)
+    b = (torch.rand((N, K // 64), device=dev) * 0.2 - 0.1).to(torch.bfloat16)
     return codes, s, b
 
 
@@ -259,9 +344,36 @@ def max_over_ranks(torch, dist, world, t, dev):
     return float(v.item())
 
 
+def timed_blocks(torch, dist, world, dev, fn, steps, warmup, barrier, min_seconds=MIN_TIMED_SECONDS, max_blocks=400):
+    """Blocks of exactly `steps` steps, each bracketed by a barrier + synchronize and timed with CUDA
+    events (max over ranks), repeated until at least `min_seconds` have been timed. Returns the
+    list of block times in seconds (every rank runs the same number of blocks)."""
+    first = max_over_ranks(torch, dist, world, timed(torch, fn, steps, warmup, barrier), dev)
+    blocks = [first]
+    n = min(max_blocks, max(2, int(math.ceil(min_seconds / max(first, 1e-6)))))
+    for _ in range(n - 1):
+        blocks.append(max_over_ranks(torch, dist, world, timed(torch, fn, steps, 0, barrier), dev))
+    return blocks
+
+
+def graph_of(torch, fn):
+    """fn captured into a CUDA graph (after one eager run on a side stream)."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    g.replay()
+    torch.cuda.synchronize()
+    return g
+
+
 def bench_qmv(torch, dist, ops, synth, args, rank, world, dev, pk):
     cfg = synth.CONFIGS["C2"]
-    layers = []
     bytes_step = 0
     # the step's activations live in ONE device buffer (one host->device copy per step), the last
     # layer's outputs in another (one device->host copy per step)
@@ -286,57 +398,30 @@ def bench_qmv(torch, dist, ops, synth, args, rank, world, dev, pk):
                 y = torch.empty((1, p.N), dtype=torch.bfloat16, device=dev)
             problems.append((codes, s, b, xs[p.K], y))
             bytes_step += synth.qmv_bytes(p.K, p.N, 1)
-        layers.append(problems[-len(cfg.projs):])
-    descs = ops.qmv_set(problems)
     launches_step = len(problems)
     torch.cuda.synchronize()
 
-    def direct():
-        ops.qmv_batch(descs)
-
-    # The whole pass as ONE launch (a plan: "encode once, commit many"); failing that, replay the
-    # 216 launches as one CUDA graph.
-    mode = "plan (1 launch per step)"
-    plan = None
+    # The whole pass as ONE launch (a plan: "encode once, commit many"), or, with --no-plan, the
+    # 216 launches replayed as one CUDA graph. Either must work: there is no quieter fallback.
     if not args.no_plan:
-        try:
-            plan = ops.QmvPlan(problems)
-            step = plan.run
-            launches_step = 1
-            step()
-            torch.cuda.synchronize()
-        except Exception as e:
-            plan = None
-            mode = f"cuda-graph (plan unavailable: {type(e).__name__})"
+        plan = ops.QmvPlan(problems)
+        step = plan.run
+        launches_step = 1
+        mode = "plan (1 launch per step)"
     else:
-        mode = "cuda-graph"
-    try:
-        if plan is not None:
-            raise StopIteration
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            direct()
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            direct()
+        descs = ops.qmv_set(problems)
+        graph = graph_of(torch, lambda: ops.qmv_batch(descs))
         step = graph.replay
-        step()
-        torch.cuda.synchronize()
-    except StopIteration:
-        pass
-    except Exception as e:  # fall back to plain launches, and say so
-        mode = f"direct-launches ({type(e).__name__})"
-        step = direct
+        mode = "cuda-graph of 216 launches"
+    step()
+    torch.cuda.synchronize()
 
     barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
     sampler = ClockSampler(dev.index)
     sampler.start()
-    t = timed(torch, step, args.steps, args.warmup, barrier)
+    blocks = timed_blocks(torch, dist, world, dev, step, args.steps, args.warmup, barrier)
     clocks = sampler.stop()
-    t = max_over_ranks(torch, dist, world, t, dev)
+    t = statistics.median(blocks)
     value = bytes_step * args.steps * world / t / 1e9
 
     # e2e: the step's activations come from pinned host memory, the last layer's outputs go back
@@ -351,8 +436,8 @@ def bench_qmv(torch, dist, ops, synth, args, rank, world, dev, pk):
         host_y.copy_(y_last, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
-    te = timed(torch, e2e_step, args.steps, args.warmup, barrier)
-    te = max_over_ranks(torch, dist, world, te, dev)
+    eblocks = timed_blocks(torch, dist, world, dev, e2e_step, args.steps, args.warmup, barrier, min_seconds=0.25)
+    te = statistics.median(eblocks)
     e2e_val = bytes_step * args.steps * world / te / 1e9
     assert ops.device_status() == 0
 
@@ -365,113 +450,351 @@ def bench_qmv(torch, dist, ops, synth, args, rank, world, dev, pk):
     return {
         "value": value, "t": t, "bytes_step": bytes_step, "launches_step": launches_step,
         "clocks": clocks, "roofline": roof, "mode": mode,
+        "timing": {"blocks": len(blocks), "steps_per_block": args.steps, "timed_seconds": sum(blocks),
+                   "ms_per_step_median": t / args.steps * 1e3, "ms_per_step_min": min(blocks) / args.steps * 1e3,
+                   "ms_per_step_max": max(blocks) / args.steps * 1e3},
         "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": te / args.steps * 1e3},
     }
 
 
-def bench_qmm(torch, dist, ops, synth, args, rank, world, dev, pk, key, comm):
-    """QMM on one config's shapes; column-split + all-gather when world > 1."""
+def bench_c1(torch, ops, synth, dev, pk, copies=32, reps=20):
+    """configs[0]: one 4096 x 4096 GEMV. `copies` distinct weights (302 MB > 2 x L2) are cycled so
+    every launch streams from HBM; the launches are replayed from a CUDA graph, one launch per GEMV
+    (the reference's method: tests/unit-tests/metal-lm/quant-gemv-bench.cc:625-632,680)."""
+    K = N = 4096
+    x = torch.randn((1, K), device=dev).to(torch.bfloat16)
+    sets = [rand_weight(torch, N, K, dev) + (x, torch.empty((1, N), dtype=torch.bfloat16, device=dev))
+            for _ in range(copies)]
+    g = graph_of(torch, lambda: [ops.qmv(*p[:4], out=p[4]) for p in sets])
+    t = timed(torch, g.replay, reps, 3, lambda: None) / (reps * copies)
+    gbs = synth.qmv_bytes(K, N) / t / 1e9
+    return {"workload": "C1 single int4 GEMV, M=1, K=N=4096", "us_per_gemv": t * 1e6, "value": gbs, "unit": "GB/s",
+            "frac_of_hbm_peak": gbs / pk["hbm_gbs"], "launches": copies * reps,
+            "method": f"{copies} distinct weight copies (302 MB, cold), graph-replayed single launches"}
+
+
+def decoder_chain(torch, ops, synth, layers, dev, H=4096, KV=1024, F=12288, seed=0):
+    """Weights and buffers of `layers` 8B-style decoder layers and the list of fused GEMVs a decode
+    step issues per layer: RMSNorm + q|k|v (three outputs), o_proj + residual, RMSNorm + gate|up with
+    SwiGLU, down + residual. Every GEMV reads what the one before wrote (attention itself is not
+    part of this path: o_proj reads the q output). Returns (problems, bytes per step)."""
+    h = torch.randn((1, H), device=dev).to(torch.bfloat16)
+    problems, nbytes = [], 0
+    x = h
+    for i in range(layers):
+        ws = [make_linear(torch, ops, n, k, synth.seed_for("chain", seed, i, j), dev)
+              for j, (n, k) in enumerate([(H + 2 * KV, H), (H, H), (2 * F, H), (H, F)])]
+        nw1 = (1.0 + 0.1 * torch.randn((H,), device=dev)).to(torch.bfloat16)
+        nw2 = (1.0 + 0.1 * torch.randn((H,), device=dev)).to(torch.bfloat16)
+        q, k, v, h1, act, h2 = (torch.zeros((1, n), dtype=torch.bfloat16, device=dev) for n in (H, KV, KV, H, F, H))
+        problems += [
+            ws[0] + (x, q, {"epilogue": "qkv", "aux": k, "y3": v, "q_rows": H, "k_rows": KV, "norm_w": nw1,
+                            "eps": 1e-6, "depends": i > 0}),
+            ws[1] + (q, h1, {"epilogue": "add", "aux": x, "depends": True}),
+            ws[2] + (h1, act, {"epilogue": "swiglu", "norm_w": nw2, "eps": 1e-6, "depends": True}),
+            ws[3] + (act, h2, {"epilogue": "add", "aux": h1, "depends": True}),
+        ]
+        nbytes += (synth.qmv_bytes(H, H + 2 * KV) + synth.qmv_bytes(H, H) + synth.qmv_bytes(H, 2 * F) +
+                   synth.qmv_bytes(F, H))
+        x = h2
+    return problems, nbytes
+
+
+def chain_outputs(problems):
+    out = []
+    for p in problems:
+        out.append(p[4])
+        if p[5]["epilogue"] == "qkv":
+            out += [p[5]["aux"], p[5]["y3"]]
+    return out
+
+
+def bench_decode_chain(torch, ops, synth, dev, pk, layers=LAYERS, reps=10):
+    """The decode step as a decoder issues it: a dependent chain. One chained launch (every GEMV
+    waits on-chip for its predecessors while the weight stream runs ahead) against one launch per
+    GEMV replayed from a CUDA graph; the two must produce the same bytes."""
+    problems, nbytes = decoder_chain(torch, ops, synth, layers, dev)
+    plain = [p[:5] + ({k: v for k, v in p[5].items() if k != "depends"},) for p in problems]
+    descs = [ops.qmv_set([p]) for p in plain]
+
+    def per_launch():
+        for d in descs:
+            ops.qmv_batch(d)
+
+    per_launch()
+    torch.cuda.synchronize()
+    want = [t.clone() for t in chain_outputs(problems)]
+    for t in chain_outputs(problems):
+        t.fill_(3.0)
+    plan = ops.QmvPlan(problems)
+    plan.run()
+    torch.cuda.synchronize()
+    same = all(torch.equal(a, b) for a, b in zip(chain_outputs(problems), want))
+    g = graph_of(torch, per_launch)
+    t_launch = timed(torch, g.replay, reps, 3, lambda: None) / reps
+    t_chain = timed(torch, plan.run, reps, 3, lambda: None) / reps
+    assert ops.device_status() == 0
+    plan.close()
+    gbs = nbytes / t_chain / 1e9
+    return {"workload": f"{layers} decoder layers (8B shapes) as a dependent chain of {len(problems)} fused GEMVs",
+            "value": gbs, "unit": "GB/s", "frac_of_hbm_peak": gbs / pk["hbm_gbs"], "ms_per_step": t_chain * 1e3,
+            "launches_per_step": 1, "bytes_per_step": nbytes,
+            "launch_per_gemv": {"value": nbytes / t_launch / 1e9, "unit": "GB/s", "ms_per_step": t_launch * 1e3,
+                                "launches_per_step": len(problems), "mode": "cuda-graph replay"},
+            "bit_identical_to_launch_per_gemv": bool(same)}
+
+
+def bench_qmm(torch, dist, ops, synth, args, dev, pk, key):
+    """QMM on one config's shapes on one GPU."""
     cfg = synth.CONFIGS[key]
     M = cfg.M
     out = {"config": key, "M": M, "shapes": []}
-    barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
     steps = max(3, min(args.steps, 10))
     tot_flops, tot_t = 0.0, 0.0
     e2e_t, e2e_flops, h2d, d2h = 0.0, 0.0, 0, 0
     for p in cfg.projs:
-        if world > 1 and p.N % (8 * world):
-            continue
         flops = synth.qmm_flops(p.K, p.N, M)
-        ns = p.N // world
-        codes, s, b = make_linear(torch, ops, ns, p.K, synth.seed_for("w", key, p.name, rank), dev)
+        codes, s, b = make_linear(torch, ops, p.N, p.K, synth.seed_for("w", key, p.name), dev)
         g = torch.Generator(device=dev).manual_seed(synth.seed_for("x", key, p.name))
         x = torch.randn((M, p.K), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
-        if world == 1:
-            y = torch.empty((M, p.N), dtype=torch.bfloat16, device=dev)
-            fn = lambda: ops.qmm(codes, s, b, x, out=y)  # noqa: E731
-        elif args.nccl_gather or M <= 128:
-            y = torch.empty((world, M, ns), dtype=torch.bfloat16, device=dev)
-            fn = lambda: comm.qmm(codes, s, b, x, y, None, args.m_chunks)  # noqa: E731
-        else:   # fused: the epilogue stores into every rank's row-major y; no collective
-            y, y_ptr = comm.alloc_symmetric((M, p.N), torch.bfloat16)
-            fn = lambda: comm.qmm_fused(codes, s, b, x, y_ptr)  # noqa: E731
-        t = timed(torch, fn, steps, 3, barrier)
-        t = max_over_ranks(torch, dist, world, t, dev) / steps
+        y = torch.empty((M, p.N), dtype=torch.bfloat16, device=dev)
+        t = timed(torch, lambda: ops.qmm(codes, s, b, x, out=y), steps, 3, lambda: None) / steps
         rec = {"name": p.name, "K": p.K, "N": p.N, "ms": t * 1e3, "tflops": flops / t / 1e12}
-        if world > 1:   # compute alone, for the split between GEMM and the exchange
-            ymine = torch.empty((M, ns), dtype=torch.bfloat16, device=dev)
-            tc = timed(torch, lambda: ops.qmm(codes, s, b, x, out=ymine), steps, 2, barrier)
-            rec["gemm_only_ms"] = max_over_ranks(torch, dist, world, tc, dev) / steps * 1e3
-            rec["gather_bytes_per_gpu"] = (world - 1) * M * ns * 2
-        if world == 1:
+        if not args.no_e2e:
             # end to end: the activations come from pinned host memory and the product goes back,
             # inside the timed region (PCIe-bound for the large shapes, and reported as such)
-            try:
-                hx = torch.empty((M, p.K), dtype=torch.bfloat16).pin_memory()
-                hx.copy_(x)
-                hy = torch.empty((M, p.N), dtype=torch.bfloat16).pin_memory()
+            hx = torch.empty((M, p.K), dtype=torch.bfloat16).pin_memory()
+            hx.copy_(x)
+            hy = torch.empty((M, p.N), dtype=torch.bfloat16).pin_memory()
 
-                def e2e_step():
-                    x.copy_(hx, non_blocking=True)
-                    ops.qmm(codes, s, b, x, out=y)
-                    hy.copy_(y, non_blocking=True)
-                    torch.cuda.current_stream().synchronize()
+            def e2e_step():
+                x.copy_(hx, non_blocking=True)
+                ops.qmm(codes, s, b, x, out=y)
+                hy.copy_(y, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
 
-                te = timed(torch, e2e_step, 3, 3, barrier) / 3
-                rec["e2e_ms"] = te * 1e3
-                e2e_t += te
-                e2e_flops += flops
-                h2d += hx.numel() * 2
-                d2h += hy.numel() * 2
-                del hx, hy
-            except Exception as e:   # not enough pinned memory for this shape: say so
-                rec["e2e_ms"] = None
-                rec["e2e_error"] = type(e).__name__
+            te = timed(torch, e2e_step, 3, 3, lambda: None) / 3
+            rec["e2e_ms"] = te * 1e3
+            e2e_t += te
+            e2e_flops += flops
+            h2d += hx.numel() * 2
+            d2h += hy.numel() * 2
+            del hx, hy
         out["shapes"].append(rec)
         tot_flops += flops
         tot_t += t
         del codes, s, b, x, y
         torch.cuda.empty_cache()
     assert ops.device_status() == 0
-    if tot_t > 0:
-        agg = tot_flops / tot_t / 1e12
-        out.update(metric="int4_qmm_tflops", value=agg, unit="TFLOP/s", n_gpus=world,
-                   scaling="strong" if world > 1 else "weak",
-                   roofline={"bound": "tensor", "achieved": agg / world, "peak": pk["bf16_tflops"],
-                             "unit": "TFLOP/s", "frac": agg / world / pk["bf16_tflops"],
-                             "peak_source": pk["source"] + " (burst, cuBLAS bf16)",
-                             "kernel": "affine_qmm_w4g64_kernel",
-                             "traffic": None})
-        if e2e_t > 0:
-            out["e2e"] = {"value": e2e_flops / e2e_t / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
-                          "d2h_bytes_per_step": d2h, "note": "one step = every shape once, x from and y to pinned host memory"}
+    agg = tot_flops / tot_t / 1e12
+    alg_bytes = sum(p.N * p.K // 2 + 4 * p.N * (p.K // 64) + 2 * M * (p.K + p.N) for p in cfg.projs) / len(cfg.projs)
+    out.update(metric="int4_qmm_tflops", value=agg, unit="TFLOP/s", n_gpus=1, scaling="weak",
+               launches=len(cfg.projs) * (steps + 3),
+               roofline={"bound": "tensor", "achieved": agg, "peak": pk["bf16_tflops"],
+                         "unit": "TFLOP/s", "frac": agg / pk["bf16_tflops"],
+                         "frac_of_sustained": agg / pk["bf16_tflops_sustained"],
+                         "peak_source": pk["source"] + " (burst, cuBLAS bf16)",
+                         "kernel": "affine_qmm_w4g64_2cta_kernel",
+                         "traffic": (QMM_TRAFFIC_RATIO * alg_bytes) if QMM_TRAFFIC_RATIO else None})
+    if e2e_t > 0:
+        out["e2e"] = {"value": e2e_flops / e2e_t / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                      "d2h_bytes_per_step": d2h,
+                      "note": "one step = every shape once, x from and y to pinned host memory"}
     return out
 
 
-def cpu_baseline(synth, seconds_budget=12.0):
-    """The oracle port (f32 dequantise + blocked fp32 GEMM, all host threads) on a bounded
-    sample of the C2 set: whole decoder layers until the time budget is used."""
-    import oracle
-    oracle.build()
-    cfg = synth.CONFIGS["C2"]
-    layer = []
-    for p in cfg.projs:
-        codes, s, b = synth.random_qweight(p.N, p.K, synth.seed_for("cpu", p.name))
-        x = synth.activations_bf16(1, p.K, synth.seed_for("cpux", p.name))
-        layer.append((codes, s, b, x))
-    bytes_layer = sum(synth.qmv_bytes(p.K, p.N, 1) for p in cfg.projs)
-    threads = oracle.max_threads()
-    for codes, s, b, x in layer:   # warm
-        oracle.cpu_linear_seconds(codes, s, b, x, threads)
-    t, n = 0.0, 0
-    while t < seconds_budget and n < LAYERS:
-        for codes, s, b, x in layer:
-            t += oracle.cpu_linear_seconds(codes, s, b, x, threads)[0]
-        n += 1
-    return {"value": bytes_layer * n / t / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
-            "sample": f"{n} of {LAYERS} decoder layers (6 QMV projections each), "
-                      "f32 dequantise + blocked fp32 GEMM, OpenMP"}
+def bench_qmm_sharded(torch, dist, ops, shard, synth, args, rank, world, dev, pk, comm, keys):
+    """The column split on `world` GPUs, strong scaling. Per shape: the unsharded GEMM on this box,
+    the fused form (sender warps store finished tiles into every peer's row-major y), GEMM + NCCL
+    all-gather whole and in 4 row chunks, the bytes each GPU must receive and the time that takes at
+    the link rate, and a bit-identity check of the gathered y against the unsharded kernel."""
+    barrier = lambda: dist.barrier()  # noqa: E731
+    steps = max(3, min(args.steps, 10))
+    out = {"n_gpus": world, "scaling": "strong", "configs": {}, "parity": {"bit_identical": True, "checked": []}}
+    for key in keys:
+        cfg = synth.CONFIGS[key]
+        M = cfg.M
+        projs = [p for p in cfg.projs if not (key == "C3" and p.name not in ("gate", "up"))]
+        recs, sums = [], {"flops": 0.0, "one_gpu": 0.0, "fused": 0.0, "nccl_allgather": 0.0, "nccl_chunks4": 0.0}
+        for p in projs:
+            if p.N % (8 * world) or M <= 128:
+                continue
+            flops = synth.qmm_flops(p.K, p.N, M)
+            ns = p.N // world
+            # every rank builds the same full weight (same seed), keeps its row shard
+            codes, s, b = make_linear(torch, ops, p.N, p.K, synth.seed_for("w", key, p.name), dev)
+            g = torch.Generator(device=dev).manual_seed(synth.seed_for("x", key, p.name))
+            x = torch.randn((M, p.K), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+            y_full = torch.empty((M, p.N), dtype=torch.bfloat16, device=dev)
+            t_one = max_over_ranks(torch, dist, world, timed(torch, lambda: ops.qmm(codes, s, b, x, out=y_full),
+                                                             steps, 3, barrier), dev) / steps
+            lo, hi = shard.shard_rows(p.N, world, rank)
+            cs, ss, bs = codes[lo:hi].contiguous(), s[lo:hi].contiguous(), b[lo:hi].contiguous()
+            ymine = torch.empty((M, ns), dtype=torch.bfloat16, device=dev)
+            t_gemm = max_over_ranks(torch, dist, world, timed(torch, lambda: ops.qmm(cs, ss, bs, x, out=ymine),
+                                                              steps, 2, barrier), dev) / steps
+            # fused
+            y_sym, y_ptr = comm.alloc_symmetric((M, p.N), torch.bfloat16)
+            y_sym.zero_()
+            torch.cuda.synchronize()
+            barrier()
+            comm.qmm_fused(cs, ss, bs, x, y_ptr)
+            torch.cuda.synchronize()
+            ok_fused = bool(torch.equal(y_sym, y_full))
+            t_fused = max_over_ranks(torch, dist, world, timed(torch, lambda: comm.qmm_fused(cs, ss, bs, x, y_ptr),
+                                                               steps, 3, barrier), dev) / steps
+            # GEMM + NCCL
+            y_sh = torch.zeros((world, M, ns), dtype=torch.bfloat16, device=dev)
+            y_row = torch.zeros((M, p.N), dtype=torch.bfloat16, device=dev)
+            comm.qmm(cs, ss, bs, x, y_sh, y_row, 1)
+            torch.cuda.synchronize()
+            ok_nccl = bool(torch.equal(y_row, y_full))
+            t_ag = max_over_ranks(torch, dist, world, timed(torch, lambda: comm.qmm(cs, ss, bs, x, y_sh, None, 1),
+                                                            steps, 3, barrier), dev) / steps
+            t_ch = max_over_ranks(torch, dist, world, timed(torch, lambda: comm.qmm(cs, ss, bs, x, y_sh, None, 4),
+                                                            steps, 3, barrier), dev) / steps
+            # a checksum of the gathered result, the same on every rank
+            chk = y_sym.view(torch.int16).to(torch.int64).sum().reshape(1)
+            allchk = [torch.zeros_like(chk) for _ in range(world)]
+            dist.all_gather(allchk, chk)
+            ok_sum = all(int(c.item()) == int(allchk[0].item()) for c in allchk)
+            flag = torch.tensor([int(ok_fused and ok_nccl and ok_sum)], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            good = bool(int(flag.item()))
+            out["parity"]["bit_identical"] = out["parity"]["bit_identical"] and good
+            out["parity"]["checked"].append({"shape": f"{key}.{p.name}", "elements": M * p.N, "fused": ok_fused,
+                                             "nccl_rowmajor": ok_nccl, "checksum_equal_on_all_ranks": ok_sum})
+            recv = (world - 1) * M * ns * 2
+            recs.append({"name": p.name, "K": p.K, "N": p.N, "one_gpu_ms": t_one * 1e3, "shard_gemm_only_ms": t_gemm * 1e3,
+                         "fused_ms": t_fused * 1e3, "nccl_allgather_ms": t_ag * 1e3, "nccl_chunks4_ms": t_ch * 1e3,
+                         "fused_tflops": flops / t_fused / 1e12, "speedup_vs_1gpu": t_one / t_fused,
+                         "exchange_bytes_per_gpu": recv,
+                         "link_floor_ms": recv / (NVLINK_GBS_MEASURED * 1e9) * 1e3,
+                         "link_gbs_over_fused_call": recv / t_fused / 1e9})
+            sums["flops"] += flops
+            sums["one_gpu"] += t_one
+            sums["fused"] += t_fused
+            sums["nccl_allgather"] += t_ag
+            sums["nccl_chunks4"] += t_ch
+            comm.free_symmetric(y_ptr)
+            del codes, s, b, x, y_full, y_sym, y_sh, y_row, ymine, cs, ss, bs
+            torch.cuda.empty_cache()
+        if sums["fused"] > 0:
+            f = sums["flops"] / 1e12
+            out["configs"][key] = {
+                "M": M, "shapes": recs, "one_gpu_tflops": f / sums["one_gpu"],
+                "fused_tflops": f / sums["fused"], "nccl_allgather_tflops": f / sums["nccl_allgather"],
+                "nccl_chunks4_tflops": f / sums["nccl_chunks4"], "speedup_vs_1gpu": sums["one_gpu"] / sums["fused"],
+                "strong_scaling_efficiency": sums["one_gpu"] / sums["fused"] / world}
+    assert ops.device_status() == 0
+    first = out["configs"].get(keys[0])
+    if first:
+        out.update(metric="int4_qmm_tflops", value=first["fused_tflops"], unit="TFLOP/s", config=keys[0],
+                   speedup_vs_1gpu=first["speedup_vs_1gpu"],
+                   roofline={"bound": "tensor", "achieved": first["fused_tflops"] / world, "peak": pk["bf16_tflops"],
+                             "unit": "TFLOP/s", "frac": first["fused_tflops"] / world / pk["bf16_tflops"],
+                             "peak_source": pk["source"] + " (burst, cuBLAS bf16)", "traffic": None})
+    return out
+
+
+# ------------------------------------------------------------- small single-kernel workloads
+
+def small_case(torch, ops, synth, dev, pk, kind, a):
+    def tm(fn, reps):
+        return timed(torch, fn, reps, 0, lambda: None) / reps
+
+    if kind == "plan":
+        layers = int(a[0]) if a else 4
+        xs = {K: torch.randn((1, K), device=dev).to(torch.bfloat16) for K in (4096, 12288)}
+        probs = []
+        for _ in range(layers):
+            for p in synth.CONFIGS["C2"].projs:
+                probs.append(rand_weight(torch, p.N, p.K, dev) +
+                             (xs[p.K], torch.empty((1, p.N), dtype=torch.bfloat16, device=dev)))
+        plan = ops.QmvPlan(probs)
+        for _ in range(3):
+            plan.run()
+        torch.cuda.synchronize()
+        t = tm(plan.run, 1)
+        nbytes = sum(synth.qmv_bytes(p.K, p.N) for p in synth.CONFIGS["C2"].projs) * layers
+        return {"case": "plan", "layers": layers, "us": t * 1e6, "GBs": nbytes / t / 1e9}
+    if kind == "decode_chain":
+        layers = int(a[0]) if a else 4
+        r = bench_decode_chain(torch, ops, synth, dev, pk, layers=layers, reps=3)
+        r["case"] = "decode_chain"
+        return r
+    if kind in ("qmv", "qmv_w8"):
+        K, N = int(a[0]), int(a[1])
+        n = int(a[2]) if len(a) > 2 else 8
+        bits = 8 if kind == "qmv_w8" else 4
+        fn = ops.qmv_w8 if bits == 8 else ops.qmv
+        x = torch.randn((1, K), device=dev).to(torch.bfloat16)
+        sets = [rand_weight(torch, N, K, dev, bits) + (x, torch.empty((1, N), dtype=torch.bfloat16, device=dev))
+                for _ in range(n)]
+        g = graph_of(torch, lambda: [fn(*p[:4], out=p[4]) for p in sets])
+        t = tm(g.replay, 3) / n
+        nbytes = N * K * bits // 8 + 4 * N * (K // 64) + 2 * K + 2 * N
+        return {"case": kind, "K": K, "N": N, "us": t * 1e6, "GBs": nbytes / t / 1e9}
+    if kind == "qmv_batch":
+        K, N, M = int(a[0]), int(a[1]), int(a[2])
+        n = int(a[3]) if len(a) > 3 else 8
+        x = torch.randn((M, K), device=dev).to(torch.bfloat16)
+        sets = [rand_weight(torch, N, K, dev) + (x, torch.empty((M, N), dtype=torch.bfloat16, device=dev))
+                for _ in range(n)]
+        out = {"case": "qmv_batch", "K": K, "N": N, "M": M}
+        for name, fn in (("batch", ops.qmv_batch_rows), ("serial", ops.qmv)):
+            g = graph_of(torch, lambda fn=fn: [fn(*p[:4], out=p[4]) for p in sets])
+            t = tm(g.replay, 3) / n
+            out[name + "_us"] = t * 1e6
+            out[name + "_weight_GBs"] = synth.qmv_bytes(K, N) / t / 1e9
+        out["speedup"] = out["serial_us"] / out["batch_us"]
+        return out
+    if kind in ("qmm", "qmm_swiglu", "qmm_w8"):
+        M, K, N = int(a[0]), int(a[1]), int(a[2])
+        reps = int(a[3]) if len(a) > 3 else 3
+        x = torch.randn((M, K), device=dev).to(torch.bfloat16)
+        codes, s, b = rand_weight(torch, N, K, dev, 8 if kind == "qmm_w8" else 4)
+        fn = {"qmm": ops.qmm, "qmm_swiglu": ops.qmm_swiglu, "qmm_w8": ops.qmm_w8}[kind]
+        y = torch.empty((M, N // 2 if kind == "qmm_swiglu" else N), dtype=torch.bfloat16, device=dev)
+        for _ in range(2):
+            fn(codes, s, b, x, out=y)
+        torch.cuda.synchronize()
+        t = tm(lambda: fn(codes, s, b, x, out=y), reps)
+        return {"case": kind, "M": M, "K": K, "N": N, "ms": t * 1e3, "tflops": synth.qmm_flops(K, N, M) / t / 1e12}
+    if kind == "moe":
+        import numpy as np
+
+        from vpipe_b200 import moe
+        T, E, top_k, H, F = (int(v) for v in a[:5])
+        reps = int(a[5]) if len(a) > 5 else 3
+        tile = ops.qmm_grouped_tile_rows()
+        rng = np.random.default_rng(0)
+        eid = np.stack([rng.choice(E, size=top_k, replace=False) for _ in range(T)]).reshape(-1).astype(np.int32)
+        tile2e, srow, sdst, npad = moe.sort_pairs(eid, E, top_k, tile)
+        tile2e, srow, sdst = (torch.from_numpy(v).to(dev) for v in (tile2e, srow, sdst))
+        hidden = torch.randn((T, H), device=dev).to(torch.bfloat16)
+        gu = [t.view(E, 2 * F, -1) for t in rand_weight(torch, E * 2 * F, H, dev)]
+        dn = [t.view(E, H, -1) for t in rand_weight(torch, E * H, F, dev)]
+        act = torch.empty((npad, F), dtype=torch.bfloat16, device=dev)
+        part = torch.empty((T * top_k, H), dtype=torch.bfloat16, device=dev)
+
+        def layer():
+            ops.qmm_grouped_gated(*gu, hidden, tile2e, srow, out=act)
+            ops.qmm_grouped_down(*dn, act, tile2e, sdst, y_rows=T * top_k, out=part)
+
+        for _ in range(2):
+            layer()
+        torch.cuda.synchronize()
+        t = tm(layer, reps)
+        useful = 2.0 * T * top_k * (H * 2 * F + F * H)
+        padded = 2.0 * npad * (H * 2 * F + F * H)
+        return {"case": kind, "tokens": T, "experts": E, "top_k": top_k, "hidden": H, "ffn": F, "rows_padded": npad,
+                "ms": t * 1e3, "tflops_useful": useful / t / 1e12, "tflops_padded": padded / t / 1e12}
+    raise SystemExit(__doc__)
+
+
+SMALL = ("plan", "decode_chain", "qmv", "qmv_w8", "qmv_batch", "qmm", "qmm_swiglu", "qmm_w8", "moe")
 
 
 def main():
@@ -480,14 +803,13 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5"],
-                    help="c2: the headline line (QMV set + QMM section); c3/c4/c5: QMM only")
-    ap.add_argument("--qmm", default="C4", help="config of the QMM section of the headline line")
-    ap.add_argument("--m-chunks", dest="m_chunks", type=int, default=1)
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5", "c1"] + list(SMALL),
+                    help="c2: the headline line; c3/c4/c5: the GEMM config as the line's metric; the rest: one small case")
+    ap.add_argument("shape", nargs="*", help="sizes of a small workload (see the module docstring)")
+    ap.add_argument("--with-c5", action="store_true", help="add the C5 GEMM config to the headline line (~10 s)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-memory end-to-end pass of the GEMM sections")
     ap.add_argument("--no-plan", action="store_true", help="QMV set as 216 graph-replayed launches")
-    ap.add_argument("--nccl-gather", action="store_true",
-                    help="N > 1: GEMM then NCCL all-gather instead of the fused peer-store epilogue")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, world, local = dist_env(args)
@@ -507,51 +829,85 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (vpipe_b200 has no CPU path)")
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
+    pk = peaks()
+
+    if args.workload in SMALL or args.workload == "c1":
+        r = bench_c1(torch, ops, synth, dev, pk) if args.workload == "c1" else \
+            small_case(torch, ops, synth, dev, pk, args.workload, args.shape)
+        assert ops.device_status() == 0
+        print(json.dumps(r), flush=True)
+        return
+
     comm = None
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
         comm = shard.NsplitComm(rank, world, dev)
-    pk = peaks()
+    parity_ok = True
 
     if args.workload == "c2":
         q = bench_qmv(torch, dist, ops, synth, args, rank, world, dev, pk)
         torch.cuda.empty_cache()
-        qmm = bench_qmm(torch, dist, ops, synth, args, rank, world, dev, pk, args.qmm, comm)
         line = {
             "metric": "int4_qmv_hbm_gbps", "value": q["value"], "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": q["t"] / args.steps * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "int4*bf16->f32", "data": "synthetic",
+            "dtype": "int4 x bf16 -> f32", "data": "synthetic",
             "config": {"workload": "C2 decode-layer QMV set, 8B Qwen3-style decoder, M=1",
                        "layers": LAYERS, "projections": "q,k,v,gate,up,down",
                        "bytes_per_step": q["bytes_step"], "launch_mode": q["mode"],
                        "l2": "36 layers of distinct weights (3.57 GB) exceed L2; no flush needed",
                        "parallelism": "replicas only" if world > 1 else "1 GPU"},
-            "roofline": q["roofline"], "e2e": q["e2e"], "clocks": q["clocks"],
-            "gpu_launches": q["launches_step"] * args.steps,
-            "qmm": qmm,
+            "roofline": q["roofline"], "e2e": q["e2e"], "clocks": q["clocks"], "timing": q["timing"],
+            "gpu_launches": q["launches_step"] * args.steps * q["timing"]["blocks"],
         }
-        if rank == 0 and world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(synth)
+        if world == 1:
+            line["c1"] = bench_c1(torch, ops, synth, dev, pk)
+            torch.cuda.empty_cache()
+            line["decode_chain"] = bench_decode_chain(torch, ops, synth, dev, pk)
+            parity_ok = parity_ok and line["decode_chain"]["bit_identical_to_launch_per_gemv"]
+            torch.cuda.empty_cache()
+            line["qmm"] = bench_qmm(torch, dist, ops, synth, args, dev, pk, "C4")
+            line["qmm_c3"] = bench_qmm(torch, dist, ops, synth, args, dev, pk, "C3")
+            if args.with_c5:
+                line["qmm_c5"] = bench_qmm(torch, dist, ops, synth, args, dev, pk, "C5")
+            if not args.no_cpu_baseline:
+                line["cpu_baseline"] = cpu_baseline_qmv(synth)
+                line["qmm"]["cpu_baseline"] = cpu_baseline_qmm(synth, "C4")
+                line["qmm_c3"]["cpu_baseline"] = cpu_baseline_qmm(synth, "C3")
+        else:
+            line["qmm"] = bench_qmm_sharded(torch, dist, ops, shard, synth, args, rank, world, dev, pk, comm,
+                                            ["C4", "C3"] + (["C5"] if args.with_c5 else []))
+            parity_ok = parity_ok and line["qmm"]["parity"]["bit_identical"]
     else:
         key = args.workload.upper()
         sampler = ClockSampler(dev.index)
         sampler.start()
-        qmm = bench_qmm(torch, dist, ops, synth, args, rank, world, dev, pk, key, comm)
+        if world == 1:
+            qmm = bench_qmm(torch, dist, ops, synth, args, dev, pk, key)
+            ms = sum(s["ms"] for s in qmm["shapes"])
+            extra = {"shapes": qmm["shapes"], "e2e": qmm.get("e2e")}
+            launches = qmm["launches"]
+        else:
+            qmm = bench_qmm_sharded(torch, dist, ops, shard, synth, args, rank, world, dev, pk, comm, [key])
+            parity_ok = qmm["parity"]["bit_identical"]
+            ms = sum(s["fused_ms"] for s in qmm["configs"][key]["shapes"])
+            extra = {"sharded": qmm["configs"][key], "parity": qmm["parity"]}
+            launches = len(qmm["configs"][key]["shapes"]) * 5 * max(3, min(args.steps, 10))
         clocks = sampler.stop()
         line = {
             "metric": "int4_qmm_tflops", "value": qmm.get("value"), "unit": "TFLOP/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": sum(s["ms"] for s in qmm["shapes"]),
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
-            "dtype": "int4*bf16->f32", "data": "synthetic",
+            "dtype": "int4 x bf16 -> f32", "data": "synthetic",
             "config": {"workload": f"{key} {synth.CONFIGS[key].what}", "M": synth.CONFIGS[key].M,
-                       "l2": "x + y of every shape exceed L2", "m_chunks": args.m_chunks,
-                       "parallelism": (f"column-split x{world}, " + ("GEMM + NCCL all-gather" if args.nccl_gather else
-                                        "fused peer-store epilogue over NVLink")) if world > 1 else "1 GPU"},
-            "roofline": qmm.get("roofline"), "e2e": qmm.get("e2e"), "clocks": clocks, "shapes": qmm["shapes"],
-            "gpu_launches": len(qmm["shapes"]) * max(3, min(args.steps, 10)),
+                       "l2": "x + y of every shape exceed L2",
+                       "parallelism": f"column-split x{world}, fused peer-store senders over NVLink"
+                       if world > 1 else "1 GPU"},
+            "roofline": qmm.get("roofline"), "clocks": clocks, "gpu_launches": launches,
         }
+        line.update(extra)
+        if world == 1 and rank == 0 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline_qmm(synth, key)
     if comm is not None:
         comm.close()
     if world > 1:
@@ -559,6 +915,9 @@ def main():
         dist.destroy_process_group()
     if rank == 0:
         print(json.dumps(line), flush=True)
+    if not parity_ok:
+        sys.stderr.write("bench.py: a bit-identity check failed (see the parity fields of the line)\n")
+        sys.exit(3)
 
 
 if __name__ == "__main__":

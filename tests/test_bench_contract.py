@@ -20,3 +20,14 @@ def test_reference_arm_prints_the_contract_line():
     e2e = line["e2e"]
     assert e2e["value"] == line["value"] and e2e["h2d_bytes_per_step"] == 0 and e2e["d2h_bytes_per_step"] == 0
     assert "workload" in line["config"]
+
+
+def test_reference_arm_times_a_gemm_config_with_all_host_cores_even_under_torchrun():
+    """Under torchrun OMP_NUM_THREADS is 1; the arm must still use every core it may run on."""
+    env = dict(os.environ, OMP_NUM_THREADS="1")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--workload", "c3",
+                        "--steps", "1", "--warmup", "1"], capture_output=True, text=True, timeout=900, cwd=ROOT, env=env)
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["metric"] == "int4_qmm_tflops" and line["unit"] == "TFLOP/s"
+    assert line["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0)) and line["value"] > 0

@@ -123,7 +123,7 @@ static_assert(sizeof(QmvProblem) == 512, "problem records are laid out back to b
 //   ranges: a list of independent GEMVs; the host's table gives every CTA one contiguous run of the
 //           concatenated tiles.
 //   chain:  a list whose GEMVs may read what earlier ones wrote. Every GEMV is spread over the whole
-//           grid (CTA b takes tiles [b * per, (b + 1) * per) of it, per = ceil(tiles / grid)), a
+//           grid (as evenly as its tiles go), a
 //           counter in global memory counts finished tiles, and a GEMV with wait_tiles > 0 stages its
 //           x only once that many tiles are complete. The producer warp does not wait: weights are
 //           constants, so the stream of GEMV i + 1 runs while GEMV i drains. The launch must be
@@ -156,31 +156,34 @@ struct Walk {
     hi = P->row_tiles;
     left = gt_end - gt;
   }
-  // Advances to the next tile of this CTA; `fresh` is raised when the walk entered another problem.
-  __device__ __forceinline__ bool next(int& out, bool& fresh, bool chain) {
+  // Advances to this CTA's next run of tiles [lo, hi) inside one problem (P).
+  __device__ __forceinline__ bool next_range(int& lo, int& out_hi, bool chain) {
     if (!chain) {
       if (left <= 0) { return false; }
-      while (tile >= hi) {
+      if (tile >= hi) {
         ++P;
         tile = 0;
         hi = P->row_tiles;
-        fresh = true;
       }
-      --left;
-    } else {
-      while (tile >= hi) {
-        if (left <= 0) { return false; }
-        --left;
-        ++P;
-        const int rt = P->row_tiles;
-        const int per = (rt + (int)gridDim.x - 1) / (int)gridDim.x;
-        tile = (int)blockIdx.x * per;
-        hi = min(tile + per, rt);
-        fresh = true;
-      }
+      lo = tile;
+      out_hi = min(hi, tile + left);
+      left -= out_hi - lo;
+      tile = out_hi;
+      return true;
     }
-    out = tile++;
-    return true;
+    for (;;) {
+      if (left <= 0) { return false; }
+      --left;
+      ++P;
+      // rt tiles over the whole grid as evenly as they go: CTA b takes rt / grid tiles, the first
+      // rt % grid CTAs one more (consecutive CTAs sit on different SMs, so no SM gets two of the extras
+      // while others have none)
+      const int rt = P->row_tiles, grid = (int)gridDim.x, b = (int)blockIdx.x;
+      const int q = rt / grid, r = rt - q * grid;
+      lo = b * q + min(b, r);
+      out_hi = lo + q + (b < r ? 1 : 0);
+      if (lo < out_hi) { return true; }
+    }
   }
 };
 
@@ -203,6 +206,39 @@ __device__ __forceinline__ void tensormap_acquire(const CUtensorMap* m) {
   asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(m) : "memory");
 }
 
+// Shared memory behind the stage ring (p0 = its end), in this order; cap_kt = k tiles of the longest x.
+struct Scratch {
+  uint4* zero128;        // 128 bytes of zeros, 128-byte aligned
+  unsigned char* xq;     // [cap_kt][3 digits][4 chunks][32 B]
+  float* xg;             // [2 * cap_kt] sum of X per group
+  float* zero16;         // 16 bytes of zeros
+  float* xu;             // [cap_kt / 2] 1 / scale of every 256-k box of x
+  float* red;            // [kRedSlots][kConsWarps][16]
+  uint32_t* red_cnt;     // [kRedSlots]
+  float* sq_part;        // [2][kConsWarps]
+  // [0], [1]: warps that posted their sum of squares; [2]: consumer warps that left; [3]: tiles this CTA
+  // finished (chain); [4]: largest dependency a warp of this CTA has claimed the polling of; [5]: largest
+  // dependency known to be satisfied
+  uint32_t* sq_cnt;
+  uint64_t* bars;
+  volatile uint32_t* abort_flag;
+  __device__ __forceinline__ Scratch(unsigned char* p0, int cap_kt) {
+    zero128 = reinterpret_cast<uint4*>(p0);
+    xq = p0 + 128;
+    xg = reinterpret_cast<float*>(xq + (size_t)cap_kt * kXBytesPerKt);
+    zero16 = xg + 2 * cap_kt;  // cap_kt is even
+    xu = zero16 + 4;
+    red = xu + ((cap_kt / 2 + 3) & ~3);
+    red_cnt = reinterpret_cast<uint32_t*>(red + kRedSlots * kConsWarps * 16);
+    sq_part = reinterpret_cast<float*>(red_cnt + kRedSlots);
+    sq_cnt = reinterpret_cast<uint32_t*>(sq_part + 2 * kConsWarps);
+    bars = reinterpret_cast<uint64_t*>(sq_cnt + 8);
+    abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * kMaxStages);
+  }
+};
+
+constexpr uint32_t kDepPolls = 1u << 21;  // polls (an L2 round trip each) of the tile counter before a dependent GEMV gives up: seconds
+
 // ---- staging of one x vector as signed digit bytes. Warp w converts exactly the 256-k boxes it
 // will multiply (box w of every stage), so no CTA barrier is involved: a half warp takes one
 // box, a lane 16 consecutive values. Every box carries its own power-of-two scale: its largest
@@ -218,9 +254,17 @@ __device__ __forceinline__ void tensormap_acquire(const CUtensorMap* m) {
 // (affine_qmv_qkv_rms_w4g64, gpu-kernels/metal/quant/affine_qmv.metal:570-694): sum of squares
 // in f32 over the whole vector (the warps exchange their partial sums through one consumer
 // barrier), x <- bf16(x * rsqrt(mean + eps) * norm_w).
-__device__ __noinline__ bool stage_x(const QmvProblem* P, int K, int warp, int lane, unsigned char* xq, float* xg,
-                                     float* xu, float* sq_part, uint32_t* sq_cnt, int sq_gen,
-                                     volatile uint32_t* abort_flag) {
+__device__ __noinline__ bool stage_x(const QmvProblem* P, unsigned char* p0, int cap_kt, int sq_gen, int need,
+                                     const uint32_t* sync) {
+  const Scratch sc(p0, cap_kt);
+  unsigned char* xq = sc.xq;
+  float* xg = sc.xg;
+  float* xu = sc.xu;
+  float* sq_part = sc.sq_part;
+  uint32_t* sq_cnt = sc.sq_cnt;
+  volatile uint32_t* abort_flag = sc.abort_flag;
+  const int K = P->K;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr int kXRegs = 3;  // passes whose loads a lane keeps in registers
   const int half = lane >> 4, sub = lane & 15;
   const uint16_t* xr = P->x;
@@ -236,6 +280,51 @@ __device__ __noinline__ bool stage_x(const QmvProblem* P, int K, int warp, int l
       b = ld_cg_v4(xr + k0 + 8);
     }
   };
+  if (nw) {  // the norm weights are constants: bring this lane's share into L1 before waiting for x
+    for (int j = 0; j < passes; ++j) {
+      const int k0 = k_of(j);
+      if (k0 < K) { asm volatile("prefetch.global.L1 [%0];" ::"l"(nw + k0)); }
+    }
+  }
+  if (need > 0) {
+    // This GEMV reads what earlier GEMVs of the launch wrote: wait (bounded) until their tiles are
+    // counted. One warp per CTA polls the counter in global memory (the first to get here claims
+    // it), the others watch a flag in shared memory, so a dependency costs the L2 one poller per CTA.
+    uint32_t seen = 0;
+    if (lane == 0) {
+      volatile uint32_t* dep_seen = sq_cnt + 5;
+      if (*dep_seen >= (uint32_t)need) {
+        seen = 1;
+      } else if (atomicMax(sq_cnt + 4, (uint32_t)need) < (uint32_t)need) {  // this warp polls for the CTA
+        for (uint32_t i = 0; i < kDepPolls; ++i) {
+          if (ld_acquire_u32(sync) >= (uint32_t)need) {
+            seen = 1;
+            break;
+          }
+          if (*abort_flag) { break; }
+        }
+        if (seen) {
+          __threadfence_block();
+          *dep_seen = (uint32_t)need;
+        }
+      } else {
+        for (uint32_t i = 0; i < 64u * kDepPolls; ++i) {
+          if (*dep_seen >= (uint32_t)need) {
+            seen = 1;
+            break;
+          }
+          if (*abort_flag) { break; }
+        }
+      }
+      if (!seen) {
+        *abort_flag = 1;
+        atomicCAS(&g_qmv_status, 0u, (3u << 8) | kRoleConsumer);
+      }
+      __threadfence_block();  // the poller's acquire reaches the other warps through the flag in shared memory
+    }
+    seen = __shfl_sync(0xffffffffu, seen, 0);
+    if (!seen) { return false; }
+  }
   uint4 xin[kXRegs][2];
 #pragma unroll
   for (int r = 0; r < kXRegs; ++r) {
@@ -279,13 +368,12 @@ __device__ __noinline__ bool stage_x(const QmvProblem* P, int K, int warp, int l
       __threadfence_block();
       atomicAdd(&sq_cnt[sq_par], 1u);
       all = 0;
-      for (uint32_t i = 0; i < (1u << 24); ++i) {
+      for (uint32_t i = 0; i < (1u << 28); ++i) {
         if (*reinterpret_cast<volatile uint32_t*>(&sq_cnt[sq_par]) >= target) {
           all = 1;
           break;
         }
         if (*abort_flag) { break; }
-        __nanosleep(20);
       }
       if (!all) {
         *abort_flag = 1;
@@ -383,124 +471,103 @@ __device__ __noinline__ bool stage_x(const QmvProblem* P, int K, int warp, int l
   return true;
 }
 
-constexpr uint32_t kDepPolls = 1u << 22;  // polls of the tile counter before a dependent GEMV gives up (seconds)
 
-__global__ void __launch_bounds__(kThreads, 2)
-affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProblem* __restrict__ list,
-                        const int2* __restrict__ ranges, int total_tiles, int stages, int cap_kt, int count,
-                        uint32_t* sync) {
-  extern __shared__ unsigned char smem_dyn[];
-  const uint32_t raw = smem_u32(smem_dyn);
-  const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled boxes need 1024-byte alignment
-  unsigned char* base_ptr = smem_dyn + (base - raw);
+// The producer: one thread streams the weights, scales and biases of this CTA's tiles into the ring.
+// They are constants of the model, so the stream waits neither for the previous kernel nor for an
+// earlier GEMV of a chain.
+__device__ __noinline__ void produce(const QmvProblem* single, const QmvProblem* list, const int2* ranges,
+                                     int total_tiles, int stages, int count, bool chain, uint32_t base, uint32_t bar0,
+                                     volatile uint32_t* abort_flag) {
   constexpr int kStageBytes = kStageW + kStageSZ;
-  const bool chain = sync != nullptr;
-
-  unsigned char* p0 = base_ptr + (size_t)stages * kStageBytes;
-  uint4* zero128 = reinterpret_cast<uint4*>(p0);                 // 128 bytes of zeros, 128-byte aligned
-  unsigned char* xq = p0 + 128;                                  // [cap_kt][3 digits][4 chunks][32 B]
-  float* xg = reinterpret_cast<float*>(xq + (size_t)cap_kt * kXBytesPerKt);  // [2*cap_kt] sum of X per group
-  float* zero16 = xg + 2 * cap_kt;                               // 16 bytes of zeros (cap_kt is even)
-  float* xu = zero16 + 4;                                        // [cap_kt/2] 1 / scale of every 256-k box of x
-  float* red = xu + ((cap_kt / 2 + 3) & ~3);                     // [kRedSlots][kConsWarps][16]
-  uint32_t* red_cnt = reinterpret_cast<uint32_t*>(red + kRedSlots * kConsWarps * 16);  // [kRedSlots]
-  float* sq_part = reinterpret_cast<float*>(red_cnt + kRedSlots);                      // [2][kConsWarps]
-  uint32_t* sq_cnt = reinterpret_cast<uint32_t*>(sq_part + 2 * kConsWarps);            // [2] warps that posted; [2] = warps that left
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sq_cnt + 4);
-  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * kMaxStages);
-  const uint32_t bar0 = smem_u32(bars);
   auto bar_full = [&](int s) { return bar0 + 8u * s; };
   auto bar_empty = [&](int s) { return bar0 + 8u * (kMaxStages + s); };
+  uint32_t it = 0;
+  bool ok = true;
+  Walk wk(single, list, ranges, total_tiles, count, chain);
+  int NB = 0, SPT = 0, row0 = 0;
+  bool sz_tma = false;
+  const QmvProblem* fenced = nullptr;  // the problem whose tensor maps were made current last
+  auto acquire_maps = [&](const QmvProblem* Q) {
+    tensormap_acquire(&Q->mw);
+    if (Q->scales_tma) {
+      tensormap_acquire(&Q->ms);
+      tensormap_acquire(&Q->mz);
+    }
+    fenced = Q;
+  };
+  int lo = 0, hi = 0;
+  while (ok && wk.next_range(lo, hi, chain)) {
+    const QmvProblem* P = wk.P;
+    NB = (P->K + 255) >> 8;                              // 128-byte boxes per row
+    SPT = (NB + kBoxesPerStage - 1) / kBoxesPerStage;    // stages per row tile
+    sz_tma = P->scales_tma != 0;
+    row0 = 0;
+    if (P->eid) {
+      // the routed expert is an output of an earlier kernel: unlike the weights it must be waited for
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      row0 = min(max(__ldg(P->eid), 0), P->experts - 1) * P->N;
+    }
+    if (list && P != fenced) { acquire_maps(P); }
+    for (int tile = lo; tile < hi && ok; ++tile) {
+      for (int st = 0; st < SPT; ++st, ++it) {
+        const int s = it % stages;
+        const uint32_t ph = (it / stages) & 1u;
+        if (!mbar_wait(bar_empty(s), ph ^ 1u, (1u << 8) | kRoleProducer, abort_flag, &g_qmv_status)) {
+          ok = false;
+          break;
+        }
+        const int nb = min(kBoxesPerStage, NB - st * kBoxesPerStage);
+        const uint32_t dst = base + (uint32_t)s * kStageBytes;
+        mbar_expect_tx(bar_full(s), (uint32_t)nb * kBoxBytes + (sz_tma ? kStageSZ : 0));
+        for (int b = 0; b < nb; ++b) {
+          tma_load_2d(dst + b * kBoxBytes, &P->mw, bar_full(s), (st * kBoxesPerStage + b) * 32, row0 + tile * 16);
+        }
+        if (sz_tma) {
+          tma_load_2d(dst + kStageW, &P->ms, bar_full(s), st * 32, row0 + tile * 16);
+          tma_load_2d(dst + kStageW + kStageSZ / 2, &P->mz, bar_full(s), st * 32, row0 + tile * 16);
+        }
+      }
+    }
+    // The walk moves on to the next problem now: make its tensor maps current while this problem's
+    // loads are in flight, instead of in front of its first load.
+    if (list && ok && wk.left > 0 && (chain || wk.tile >= wk.hi)) { acquire_maps(P + 1); }
+  }
+  // Never leave with a copy still in flight: wait for the last load of every stage.
+  for (int s = 0; s < stages; ++s) {
+    if (it > (uint32_t)s) {
+      const uint32_t last = ((it - 1 - s) / stages) * stages + s;
+      mbar_wait(bar_full(s), (last / stages) & 1u, (2u << 8) | kRoleProducer, abort_flag, &g_qmv_status);
+    }
+  }
+}
 
+// The tiles [lo, hi) of one GEMV for this CTA's eight consumer warps: the hot loop, in a function
+// of its own so that it gets its own register allocation. `state` carries the ring position and
+// the tile count between calls: bits 0..2 stage, bit 3 phase, bits 4.. tiles processed; the
+// return value is the new state, or kConsumeFailed if a bounded wait gave up.
+constexpr uint32_t kConsumeFailed = 0xffffffffu;
+
+__device__ __noinline__ uint32_t consume_tiles(const QmvProblem* P, int lo, int hi, uint32_t state, unsigned char* base_ptr,
+                                               int stages, int cap_kt, uint32_t* sync) {
+  constexpr int kStageBytes = kStageW + kStageSZ;
+  const Scratch sc(base_ptr + (size_t)stages * kStageBytes, cap_kt);
+  uint4* zero128 = sc.zero128;
+  unsigned char* xq = sc.xq;
+  float* xg = sc.xg;
+  float* zero16 = sc.zero16;
+  float* xu = sc.xu;
+  float* red = sc.red;
+  uint32_t* red_cnt = sc.red_cnt;
+  uint32_t* sq_cnt = sc.sq_cnt;
+  volatile uint32_t* abort_flag = sc.abort_flag;
+  const uint32_t bar0 = smem_u32(sc.bars);
+  auto bar_full = [&](int s) { return bar0 + 8u * s; };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (kMaxStages + s); };
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-
-  // Let the next kernel in the stream start its own weight stream now.
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) {
-      mbar_init(bar_full(s), 1);
-      mbar_init(bar_empty(s), kConsWarps);
-    }
-    *abort_flag = 0;
-    for (int i = 0; i < kRedSlots; ++i) { red_cnt[i] = 0; }
-    for (int i = 0; i < 4; ++i) { sq_cnt[i] = 0; }
-    fence_mbar_init();
-  }
-  if (threadIdx.x < 8) { zero128[threadIdx.x] = make_uint4(0, 0, 0, 0); }
-  if (threadIdx.x == 8) { *reinterpret_cast<uint4*>(zero16) = make_uint4(0, 0, 0, 0); }
-  __syncthreads();
-
-  if (warp == kConsWarps) {
-    // ------------------------------------------------------------ producer
-    // Weights, scales and biases are constants of the model: streaming them
-    // does not wait for the previous kernel, nor for an earlier GEMV of a chain.
-    if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      Walk wk(&single, list, ranges, total_tiles, count, chain);
-      int tile = 0;
-      bool fresh = true;
-      int NB = 0, SPT = 0, row0 = 0;
-      bool sz_tma = false;
-      while (ok && wk.next(tile, fresh, chain)) {
-        const QmvProblem* P = wk.P;
-        if (fresh) {
-          fresh = false;
-          NB = (P->K + 255) >> 8;                              // 128-byte boxes per row
-          SPT = (NB + kBoxesPerStage - 1) / kBoxesPerStage;    // stages per row tile
-          sz_tma = P->scales_tma != 0;
-          row0 = 0;
-          if (P->eid) {
-            // the routed expert is an output of an earlier kernel: unlike the weights it must be waited for
-            asm volatile("griddepcontrol.wait;" ::: "memory");
-            row0 = min(max(__ldg(P->eid), 0), P->experts - 1) * P->N;
-          }
-          if (list) {
-            tensormap_acquire(&P->mw);
-            if (sz_tma) {
-              tensormap_acquire(&P->ms);
-              tensormap_acquire(&P->mz);
-            }
-          }
-        }
-        for (int st = 0; st < SPT; ++st, ++it) {
-          const int s = it % stages;
-          const uint32_t ph = (it / stages) & 1u;
-          if (!mbar_wait(bar_empty(s), ph ^ 1u, (1u << 8) | kRoleProducer, abort_flag, &g_qmv_status)) {
-            ok = false;
-            break;
-          }
-          const int nb = min(kBoxesPerStage, NB - st * kBoxesPerStage);
-          const uint32_t dst = base + (uint32_t)s * kStageBytes;
-          mbar_expect_tx(bar_full(s), (uint32_t)nb * kBoxBytes + (sz_tma ? kStageSZ : 0));
-          for (int b = 0; b < nb; ++b) {
-            tma_load_2d(dst + b * kBoxBytes, &P->mw, bar_full(s), (st * kBoxesPerStage + b) * 32, row0 + tile * 16);
-          }
-          if (sz_tma) {
-            tma_load_2d(dst + kStageW, &P->ms, bar_full(s), st * 32, row0 + tile * 16);
-            tma_load_2d(dst + kStageW + kStageSZ / 2, &P->mz, bar_full(s), st * 32, row0 + tile * 16);
-          }
-        }
-      }
-      // Never leave with a copy still in flight: wait for the last load of every stage.
-      for (int s = 0; s < stages; ++s) {
-        if (it > (uint32_t)s) {
-          const uint32_t last = ((it - 1 - s) / stages) * stages + s;
-          mbar_wait(bar_full(s), (last / stages) & 1u, (2u << 8) | kRoleProducer, abort_flag, &g_qmv_status);
-        }
-      }
-    }
-    return;
-  }
-
-  // ---------------------------------------------------------------- consumers
   const int g = lane >> 2, t = lane & 3;
   const int rho = (g >> 1) | ((g & 1) << 2);  // stage row of MMA row g (g+8 -> rho+8): bank-conflict-free
-
-  // x (and y) may be produced / consumed by the previous kernel.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const bool chain = sync != nullptr;
 
   // Accumulator column c of an MMA is supplied by the lanes with g == c and stands for
   // (digit c >> 1, group parity c & 1): those lanes feed the digit's bytes if their chunk t lies
@@ -526,63 +593,14 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
   const uint32_t sz_off = (uint32_t)kStageW + (bias_lane ? (uint32_t)kStageSZ / 2 : 0u) + (uint32_t)rho * 64u +
                           (uint32_t)warp * 8u;
 
-  uint32_t tile_seq = 0, ph = 0;
-  int s = 0, sq_gen = 0;
+  int s = (int)(state & 7u);
+  uint32_t ph = (state >> 3) & 1u;
+  uint32_t tile_seq = state >> 4;
   bool ok = true;
-  Walk wk(&single, list, ranges, total_tiles, count, chain);
-  const uint16_t* staged_x = nullptr;
-  int staged_K = -1;
-  // per-problem values, refreshed when the walk enters a new problem
-  int N = 0, KT = 0, SPT = 0, row0 = 0;
-  bool sz_tma = false;
-  bool fresh = true;
-  int tile = 0;
-  while (ok && wk.next(tile, fresh, chain)) {
-    const QmvProblem* P = wk.P;
-    if (fresh) {
-      fresh = false;
-      const int K = P->K;
-      N = P->N;
-      KT = ((K + 255) >> 8) * 2;  // k tiles per row, padded to whole 256-k boxes (x is zero there)
-      SPT = (((K + 255) >> 8) + kBoxesPerStage - 1) / kBoxesPerStage;
-      sz_tma = P->scales_tma != 0;
-      row0 = 0;
-      if (P->eid) { row0 = min(max(__ldg(P->eid), 0), P->experts - 1) * N; }
-      const uint16_t* xr = P->x;
-      const int need = chain ? P->wait_tiles : 0;
-      if (need > 0) {
-        // this GEMV reads what earlier GEMVs of the launch wrote: wait (bounded) for their tiles
-        uint32_t seen = 0;
-        if (lane == 0) {
-          for (uint32_t i = 0; i < kDepPolls; ++i) {
-            if (ld_acquire_u32(sync) >= (uint32_t)need) {
-              seen = 1;
-              break;
-            }
-            __nanosleep(64);
-          }
-          if (!seen) {
-            *abort_flag = 1;
-            atomicCAS(&g_qmv_status, 0u, (3u << 8) | kRoleConsumer);
-          }
-        }
-        seen = __shfl_sync(0xffffffffu, seen, 0);
-        if (!seen) {
-          ok = false;
-          break;
-        }
-      }
-      // q|k|v or gate|up of a layer share one staging; a dependent or normalised x is always staged
-      if (need > 0 || P->norm_w != nullptr || xr != staged_x || K != staged_K) {
-        if (!stage_x(P, K, warp, lane, xq, xg, xu, sq_part, sq_cnt, sq_gen, abort_flag)) {
-          ok = false;
-          break;
-        }
-        staged_x = P->norm_w ? nullptr : xr;
-        staged_K = K;
-        if (P->norm_w) { ++sq_gen; }
-      }
-    }
+  const int KT = ((P->K + 255) >> 8) * 2;  // k tiles per row, padded to whole 256-k boxes (x is zero there)
+  const int SPT = ((KT >> 1) + kBoxesPerStage - 1) / kBoxesPerStage;
+  const bool sz_tma = P->scales_tma != 0;
+  for (int tile = lo; tile < hi; ++tile) {
     float res_a = 0.0f, res_b = 0.0f;  // rows rho and rho + 8 of the tile: this lane's digit (or bias) share
     for (int st = 0; st < SPT; ++st) {
       if (!warp_wait(bar_full(s), ph, (1u << 8) | kRoleConsumer, abort_flag, &g_qmv_status)) {
@@ -609,7 +627,8 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
         } else {
           // clamped onto valid data: a clamped group meets x == 0, a clamped row is never stored
           const uint16_t* src = bias_lane ? P->biases : P->scales;
-          const int G = P->K >> 6;
+          const int G = P->K >> 6, N = P->N;
+          const int64_t row0 = P->eid ? (int64_t)min(max(__ldg(P->eid), 0), P->experts - 1) * N : 0;
           const int64_t r_a = row0 + min(tile * 16 + rho, N - 1), r_b = row0 + min(tile * 16 + rho + 8, N - 1);
           const int g0 = min(2 * kt0, G - 1), g1 = min(2 * kt0 + 1, G - 1);
           const int g2 = min(2 * kt0 + 2, G - 1), g3 = min(2 * kt0 + 3, G - 1);
@@ -695,17 +714,92 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
           v += *reinterpret_cast<volatile float*>(&red[(slot * kConsWarps + ww) * 16 + lane]);
         }
         const int row = (tile << 4) + lane;
-        fused_store(P->epilogue, v, row, N, lane, P->y, P->aux, P->y3, P->q_rows, P->k_rows);
+        fused_store(P->epilogue, v, row, P->N, lane, P->y, P->aux, P->y3, P->q_rows, P->k_rows);
       }
       __syncwarp();
       if (lane == 0) {
         red_cnt[slot] = 0;
-        if (chain) {  // publish the tile: the stores above, then the count
-          __threadfence();
-          atomicAdd(sync, 1u);
+        if (chain) {
+          // Publish: the stores above, then the count. Tiles of a CTA finish in order, so the warp that
+          // finishes the CTA's last tile of this GEMV reports all of them with one release-add.
+          // (the finishers of a CTA are chained at block scope through a counter in shared memory, so the
+          // one release below also covers the stores of the tiles that other warps finished)
+          __threadfence_block();
+          atomicAdd(sq_cnt + 3, 1u);
+          if (tile == hi - 1) {
+            const uint32_t mine = (uint32_t)(hi - lo);
+            __threadfence_block();
+            asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(sync), "r"(mine) : "memory");
+          }
         }
       }
     }
+  }
+  if (!ok) { return kConsumeFailed; }
+  return (uint32_t)s | (ph << 3) | (tile_seq << 4);
+}
+
+__global__ void __launch_bounds__(kThreads, 2)
+affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProblem* __restrict__ list,
+                        const int2* __restrict__ ranges, int total_tiles, int stages, int cap_kt, int count,
+                        uint32_t* sync) {
+  extern __shared__ unsigned char smem_dyn[];
+  const uint32_t raw = smem_u32(smem_dyn);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled boxes need 1024-byte alignment
+  unsigned char* base_ptr = smem_dyn + (base - raw);
+  constexpr int kStageBytes = kStageW + kStageSZ;
+  const bool chain = sync != nullptr;
+  unsigned char* p0 = base_ptr + (size_t)stages * kStageBytes;
+  const Scratch sc(p0, cap_kt);
+  const uint32_t bar0 = smem_u32(sc.bars);
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+
+  // Let the next kernel in the stream start its own weight stream now.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(bar0 + 8u * s, 1);
+      mbar_init(bar0 + 8u * (kMaxStages + s), kConsWarps);
+    }
+    *sc.abort_flag = 0;
+    for (int i = 0; i < kRedSlots; ++i) { sc.red_cnt[i] = 0; }
+    for (int i = 0; i < 8; ++i) { sc.sq_cnt[i] = 0; }
+    fence_mbar_init();
+  }
+  if (threadIdx.x < 8) { sc.zero128[threadIdx.x] = make_uint4(0, 0, 0, 0); }
+  if (threadIdx.x == 8) { *reinterpret_cast<uint4*>(sc.zero16) = make_uint4(0, 0, 0, 0); }
+  __syncthreads();
+
+  if (warp == kConsWarps) {
+    if (lane == 0) { produce(&single, list, ranges, total_tiles, stages, count, chain, base, bar0, sc.abort_flag); }
+    return;
+  }
+
+  // ---------------------------------------------------------------- consumers
+  // x (and y) may be produced / consumed by the previous kernel.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  Walk wk(&single, list, ranges, total_tiles, count, chain);
+  const uint16_t* staged_x = nullptr;
+  int staged_K = -1, sq_gen = 0;
+  uint32_t state = 0;
+  int lo = 0, hi = 0;
+  while (wk.next_range(lo, hi, chain)) {
+    const QmvProblem* P = wk.P;
+    const int K = P->K;
+    const uint16_t* xr = P->x;
+    const int need = chain ? P->wait_tiles : 0;
+    // q|k|v or gate|up of a layer share one staging; a dependent or normalised x is always staged
+    if (need > 0 || P->norm_w != nullptr || xr != staged_x || K != staged_K) {
+      if (!stage_x(P, p0, cap_kt, sq_gen, need, sync)) { break; }
+      staged_x = P->norm_w ? nullptr : xr;
+      staged_K = K;
+      if (P->norm_w) { ++sq_gen; }
+    }
+    state = consume_tiles(P, lo, hi, state, base_ptr, stages, cap_kt, sync);
+    if (state == kConsumeFailed) { break; }
   }
   if (chain) {
     // The CTA that leaves last puts both counters back to zero for the next run (every CTA has
@@ -714,7 +808,7 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
     __syncwarp();
     if (lane == 0) {
       __threadfence();
-      if (atomicAdd(&sq_cnt[2], 1u) == (uint32_t)(kConsWarps - 1)) {
+      if (atomicAdd(&sc.sq_cnt[2], 1u) == (uint32_t)(kConsWarps - 1)) {
         if (atomicAdd(sync + 1, 1u) == gridDim.x - 1) {
           sync[0] = 0;
           sync[1] = 0;
@@ -735,7 +829,7 @@ LaunchShape shape_for(int cap_kt) {
   const size_t stage_bytes = kStageW + kStageSZ;
   const size_t fixed = 1024 /*alignment slack*/ + 128 + (size_t)cap_kt * kXBytesPerKt + (size_t)2 * cap_kt * 4 + 16 +
                        (size_t)((cap_kt / 2 + 3) & ~3) * 4 + kRedSlots * kConsWarps * 16 * 4 + kRedSlots * 4 +
-                       2 * kConsWarps * 4 + 16 + 2 * kMaxStages * 8 + 16;
+                       2 * kConsWarps * 4 + 32 + 2 * kMaxStages * 8 + 16;
   const size_t budget = 112 * 1024;  // two CTAs per SM
   int stages = fixed + 2 * stage_bytes <= budget ? (int)((budget - fixed) / stage_bytes) : 2;
   if (stages > kMaxStages) { stages = kMaxStages; }

@@ -108,6 +108,11 @@ class NsplitComm:
         t = torch.as_tensor(raw, device=torch.device("cuda", torch.cuda.current_device()))
         return t.view(dtype).view(*shape), ptr.value
 
+    def free_symmetric(self, ptr) -> None:
+        """Releases a buffer of alloc_symmetric (collective: every rank, same order)."""
+        from ._lib import check, lib
+        check(lib().vpq_comm_free_symmetric(self.handle, ptr))
+
     def qmm_fused(self, codes_shard, scales_shard, biases_shard, x, y_sym_ptr, stream=None):
         """Column-split QMM whose epilogue writes every rank's row-major y directly (no collective)."""
         import torch
