@@ -288,6 +288,14 @@ int vpq_affine_qmm_swiglu_w4g64_bf16(const uint32_t* w, const void* scales, cons
 int vpq_affine_qmm_w8g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
                               void* y, int64_t K, int64_t N, int64_t M, void* stream);
 
+/* The GEMM over any of the format twins: bits 4 | 8, group 64 | 32 (scales / biases [N, K/group]), act 0
+ * (y [M, N]) or 2 (GeGLU over interleaved gate | up rows, y [M, N/2]; 4-bit only at group 32). The
+ * group-32 forms are the same CTA-pair kernel with two scales per 64-wide k block. Replaces
+ * affine_qmm_steel_w4g32, affine_qmm_geglu_w4g32 and affine_qmm_steel_w8g32 (slots as the GEMM),
+ * gpu-kernels/metal/quant/affine_qmm_steel.metal:618-639,1573-1593,1677-1697. */
+int vpq_affine_qmm_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x, void* y,
+                        int64_t K, int64_t N, int64_t M, int bits, int group, int act, void* stream);
+
 /* The other gated GEMMs, same slots and layout as the SwiGLU one: gelu_pytorch_tanh on the gate
  * (affine_qmm_geglu_w4g64, gpu-kernels/metal/quant/affine_qmm_steel.metal:1451-1569), and both
  * activations over 8-bit weights (affine_qmm_swiglu_w8g64, :1700-1790; affine_qmm_geglu_w8g64,

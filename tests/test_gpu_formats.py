@@ -222,3 +222,32 @@ def test_qmv_w4g32_f32_accuracy_and_name(vpq, oracle_mod):
     y2 = torch.empty_like(y)
     vpq.ops.dispatch(vpq.ops.function("affine_qmv_bf16", "affine_qmv_w4g32"), list(d) + [y2], K=K, N=N, M=2)
     assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("bits,act,M,K,N", [(4, "none", 300, 1024, 520), (4, "none", 2048, 4096, 1024),
+                                            (8, "none", 512, 2048, 768), (4, "geglu", 260, 1024, 512)])
+def test_qmm_group32_twins(vpq, oracle_mod, bits, act, M, K, N):
+    """affine_qmm_steel_w4g32 / affine_qmm_steel_w8g32 / affine_qmm_geglu_w4g32
+    (affine_qmm_steel.metal:618-639,1573-1593,1677-1697): the GEMM with two scales per 64-wide k block.
+    Against a dense f32 product of the bit-exact dequantised W (rounded to bf16 as the kernel does)."""
+    wb = synth.f32_to_bf16_bits(synth.weight_f32(N, K, synth.seed_for("g32", bits, M, K, N)))
+    codes, s16, b16 = oracle_mod.quant(wb, bits, 32)
+    s, b = oracle_mod.f16_to_bf16(s16), oracle_mod.f16_to_bf16(b16)
+    x = synth.activations_bf16(M, K, synth.seed_for("g32x", bits, M, K, N))
+    d = (to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16), to_dev(x, torch.bfloat16))
+    y = vpq.ops.qmm_any(d[0], d[1], d[2], d[3], bits, 32, act)
+    assert vpq.ops.device_status() == 0
+    wd = vpq.ops.dequantize_any(d[0], d[1], d[2], bits, 32)
+    assert np.array_equal(bits16(wd), oracle_mod.dequant_bf16_any(codes, s, b, bits, 32))
+    ref = d[3].float() @ wd.float().t()
+    if act == "geglu":
+        ref = torch.from_numpy(synth.bf16_bits_to_f32(oracle_mod.fused_geglu(ref.cpu().numpy()))).to(ref.device)
+        assert y.shape == (M, N // 2)
+    assert float((y.float() - ref).abs().max()) <= 1e-2 * float(ref.abs().max())
+    assert float((y.float() - ref).norm() / ref.norm()) < 3e-3
+    # by the reference's name
+    name = {(4, "none"): "affine_qmm_steel_w4g32", (8, "none"): "affine_qmm_steel_w8g32",
+            (4, "geglu"): "affine_qmm_geglu_w4g32"}[(bits, act)]
+    y2 = torch.zeros_like(y)
+    vpq.ops.dispatch(vpq.ops.function("affine_qmm_steel_bf16", name), [d[0], d[1], d[2], d[3], y2], K=K, N=N, M=M)
+    assert torch.equal(y, y2)

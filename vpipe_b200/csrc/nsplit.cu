@@ -32,7 +32,7 @@ struct vpq_comm_s {
   // fused column-split: symmetric buffers, and a flag array per rank for the cross-GPU barrier
   vpq_sym_buf bufs[8];
   int nbufs = 0;
-  vpq_sym_buf flags;       // uint32 [8] per rank
+  vpq_sym_buf flags;       // uint32 [16] per rank: [r] rank r started call `epoch`, [8 + r] rank r finished it; [16] sender-warp count
   uint32_t epoch = 0;
   void* handle_stage = nullptr;  // device staging for the IPC-handle exchange
   cudaStream_t comm_stream = nullptr;
@@ -116,6 +116,22 @@ __global__ void peer_barrier_kernel(uint32_t* const* peer_flags, uint32_t* my_fl
     __nanosleep(100);
   }
   atomicCAS(status, 0u, 0x7700u | (uint32_t)r);  // rank r never arrived
+}
+
+// The waiting half alone: thread r waits (bounded) until flags[r] has reached `epoch`.
+__global__ void peer_wait_kernel(uint32_t* flags, int rank, int world, uint32_t epoch, uint32_t* status,
+                                 uint32_t max_polls) {
+  const int r = threadIdx.x;
+  if (r >= world || r == rank) { return; }
+  volatile uint32_t* f = flags + r;
+  for (uint32_t i = 0; i < max_polls; ++i) {
+    if ((int32_t)(*f - epoch) >= 0) {
+      __threadfence_system();
+      return;
+    }
+    __nanosleep(100);
+  }
+  atomicCAS(status, 0u, 0x7700u | (uint32_t)r);  // rank r never finished
 }
 
 __device__ uint32_t g_nsplit_status;
@@ -326,10 +342,10 @@ extern "C" int vpq_comm_alloc_symmetric(vpq_comm* c, size_t bytes, void** local_
   if (c->world > 8) { return fail(VPQ_ERR_UNSUPPORTED, "comm_alloc_symmetric: at most 8 ranks"); }
   if (c->nbufs >= 8) { return fail(VPQ_ERR_UNSUPPORTED, "comm_alloc_symmetric: at most 8 live buffers"); }
   if (!c->flags.local) {  // first use: the barrier flags
-    VPQ_CUDA_OK(cudaMalloc(&c->flags.local, 8 * sizeof(uint32_t)));
-    VPQ_CUDA_OK(cudaMemset(c->flags.local, 0, 8 * sizeof(uint32_t)));
+    VPQ_CUDA_OK(cudaMalloc(&c->flags.local, 32 * sizeof(uint32_t)));
+    VPQ_CUDA_OK(cudaMemset(c->flags.local, 0, 32 * sizeof(uint32_t)));
     VPQ_CUDA_OK(cudaDeviceSynchronize());
-    c->flags.bytes = 8 * sizeof(uint32_t);
+    c->flags.bytes = 32 * sizeof(uint32_t);
     if (int rc = map_peers(c, &c->flags)) { return rc; }
     // the peers' flag arrays as a device table for the barrier kernel
     uint32_t* hp[8] = {};
@@ -379,36 +395,36 @@ extern "C" int vpq_affine_qmm_w4g64_bf16_nsplit_fused(vpq_comm* c, const uint32_
   if (b->bytes < (size_t)M * (size_t)N * 2) { return fail(VPQ_ERR_INVALID_ARG, "qmm_nsplit_fused: y too small"); }
   const int64_t Ns = N / G;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  char* stage = static_cast<char*>(c->handle_stage) + 64 * 9;  // the peers' flag pointers
-  uint32_t* status = nullptr;
-  if (G > 1) {
-    // Entry barrier: a rank's stores into the peers' y may start only when every peer's stream has
-    // reached this call, i.e. when whatever the peers enqueued earlier to read y (the previous
-    // step's result) is done. Without it a fast rank would overwrite y under a slow rank's reader.
-    VPQ_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_nsplit_status));
-    ++c->epoch;
-    peer_barrier_kernel<<<1, 32, 0, st>>>(reinterpret_cast<uint32_t* const*>(stage),
-                                          static_cast<uint32_t*>(c->flags.local), c->rank, G, c->epoch, status,
-                                          kBarrierPolls);
-    VPQ_LAUNCH_OK("peer_barrier (entry)");
-  }
-  // this GPU's copy first, then the peers', so the local stores lead
+  // this GPU's copy first, then the peers' (rotated, so that the ranks do not all start on the same peer)
   void* dests[8];
+  PeerSync ps = {};
   int n = 0;
   dests[n++] = b->local;
-  for (int r = 1; r < G; ++r) { dests[n++] = b->peer[(c->rank + r) % G]; }
+  for (int r = 1; r < G; ++r) {
+    const int peer = (c->rank + r) % G;
+    ps.flag_of[n] = static_cast<uint32_t*>(c->flags.peer[peer]);
+    ps.src_rank[n] = peer;
+    dests[n++] = b->peer[peer];
+  }
+  ps.my_flags = static_cast<uint32_t*>(c->flags.local);
+  ps.warps_done = ps.my_flags + 16;
+  ps.epoch = ++c->epoch;
+  ps.rank = c->rank;
+  // The handshake with the peers runs inside the GEMM kernel: it announces "started" when it starts,
+  // its sender warps hold their stores into a peer's y until that peer has started too (whatever the
+  // peer enqueued earlier to read y is then done), and the sender warp that finishes last announces
+  // "finished" to every peer.
   if (int rc = qmm_launch_multi_dest(w_shard, scales_shard, biases_shard, x, dests, n, N, (int64_t)c->rank * Ns,
-                                     K, Ns, M, stream)) {
+                                     K, Ns, M, stream, G > 1 ? &ps : nullptr)) {
     return rc;
   }
   if (G > 1) {
-    // Exit barrier: y is complete on this GPU once every peer's kernel (and so its stores into
-    // this GPU's y) has finished.
-    ++c->epoch;
-    peer_barrier_kernel<<<1, 32, 0, st>>>(reinterpret_cast<uint32_t* const*>(stage),
-                                          static_cast<uint32_t*>(c->flags.local), c->rank, G, c->epoch, status,
-                                          kBarrierPolls);
-    VPQ_LAUNCH_OK("peer_barrier");
+    // y is complete on this GPU once every peer has announced "finished": a small kernel behind the
+    // GEMM waits for that (bounded), so that later work on the stream sees all column blocks.
+    uint32_t* status = nullptr;
+    VPQ_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_nsplit_status));
+    peer_wait_kernel<<<1, 32, 0, st>>>(ps.my_flags + 8, c->rank, G, ps.epoch, status, kBarrierPolls);
+    VPQ_LAUNCH_OK("peer_wait");
   }
   return VPQ_OK;
 }

@@ -560,6 +560,7 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
 }
 
 #include "qmm_2cta.cuh"
+#include "qmm_ta.cuh"
 
 // ------------------------------------------------------------- host side
 template <int BN, int kAct>
@@ -618,10 +619,11 @@ int pick_tile_width(int M, int N, int pairs) {
 
 template <int BITS>
 int launch_qmm_2cta_bits(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const void* x,
-                         const two_cta::OutSpec& out, int K, int N, int M, cudaStream_t st, int reserve_sms) {
+                         const two_cta::OutSpec& out, int K, int N, int M, cudaStream_t st, int reserve_sms,
+                         int group = 64) {
   int pairs = (num_sms() - reserve_sms) / 2;  // SMs left free run a concurrent collective
   if (pairs < 1) { pairs = 1; }
-  const int tnt = (BITS == 4 && out.swiglu == 0) ? pick_tile_width(M, N, pairs) : 256;
+  const int tnt = (BITS == 4 && out.swiglu == 0 && group == 64) ? pick_tile_width(M, N, pairs) : 256;
   CUtensorMap map_x, map_w;
   if (int rc = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)K, (uint64_t)M,
                            BK, 128, CU_TENSOR_MAP_SWIZZLE_128B, "x")) {
@@ -636,12 +638,19 @@ int launch_qmm_2cta_bits(const uint32_t* w, const uint16_t* scales, const uint16
   KernelT kern;
   int smem;
   if (tnt == 128) {
-    kern = two_cta::affine_qmm_w4g64_2cta_kernel<0, 4, 128>;
+    kern = two_cta::affine_qmm_w4g64_2cta_kernel<0, 4, 128, 64>;
     smem = two_cta::SmemT<4, 128>::kAlloc;
+  } else if (group == 32) {  // the group-32 twins the reference has: plain (4 and 8 bits) and GeGLU (4 bits)
+    if (out.swiglu == 1 || (out.swiglu == 2 && BITS == 8)) {
+      return fail(VPQ_ERR_UNSUPPORTED, "affine_qmm (group 32): gated stores exist for 4-bit GeGLU only");
+    }
+    kern = out.swiglu == 2 ? two_cta::affine_qmm_w4g64_2cta_kernel<2, 4, 256, 32>
+                           : two_cta::affine_qmm_w4g64_2cta_kernel<0, BITS, 256, 32>;
+    smem = two_cta::SmemT<BITS, 256>::kAlloc;
   } else {
-    kern = out.swiglu == 2   ? two_cta::affine_qmm_w4g64_2cta_kernel<2, BITS, 256>
-           : out.swiglu == 1 ? two_cta::affine_qmm_w4g64_2cta_kernel<1, BITS, 256>
-                             : two_cta::affine_qmm_w4g64_2cta_kernel<0, BITS, 256>;
+    kern = out.swiglu == 2   ? two_cta::affine_qmm_w4g64_2cta_kernel<2, BITS, 256, 64>
+           : out.swiglu == 1 ? two_cta::affine_qmm_w4g64_2cta_kernel<1, BITS, 256, 64>
+                             : two_cta::affine_qmm_w4g64_2cta_kernel<0, BITS, 256, 64>;
     smem = two_cta::SmemT<BITS, 256>::kAlloc;
   }
   VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -652,8 +661,41 @@ int launch_qmm_2cta_bits(const uint32_t* w, const uint16_t* scales, const uint16
   return VPQ_OK;
 }
 
+// The kernel with the dequantised W tile in tensor memory (qmm_ta.cuh): plain 4-bit group-64 GEMM into
+// one row-major output. It moves half the shared-memory bytes per flop of the kernel above, but its
+// 256 x 192 tiles want enough of them to fill the CTA pairs.
+bool prefer_ta(int M, int N, int pairs) {
+  const int tiles = ((M + ta::TX - 1) / ta::TX) * ((N + ta::TW - 1) / ta::TW);
+  return tiles >= 2 * pairs;
+}
+
+int launch_qmm_ta(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const void* x, __nv_bfloat16* y,
+                  int64_t ld, int K, int N, int M, cudaStream_t st) {
+  using L = ta::SmemTa;
+  CUtensorMap map_x, map_w;
+  if (int rc = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)K, (uint64_t)M, BK, ta::TX / 2,
+                           CU_TENSOR_MAP_SWIZZLE_128B, "x")) {
+    return rc;
+  }
+  if (int rc = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w, (uint64_t)(K / 8), (uint64_t)N, BK / 8, 128,
+                           CU_TENSOR_MAP_SWIZZLE_NONE, "w")) {
+    return rc;
+  }
+  auto kern = ta::affine_qmm_w4g64_ta_kernel;
+  VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
+  const int tiles = ((M + ta::TX - 1) / ta::TX) * ((N + ta::TW - 1) / ta::TW);
+  const int pairs = num_sms() / 2;
+  const int grid = 2 * (tiles < pairs ? tiles : pairs);
+  kern<<<grid, ta::kThreadsTa, L::kAlloc, st>>>(map_x, map_w, scales, biases, y, ld, M, N, K);
+  VPQ_LAUNCH_OK("affine_qmm (tensor-memory A)");
+  return VPQ_OK;
+}
+
 int launch_qmm_2cta(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const void* x,
                     const two_cta::OutSpec& out, int K, int N, int M, cudaStream_t st, int reserve_sms) {
+  if (out.count == 1 && out.swiglu == 0 && reserve_sms == 0 && prefer_ta(M, N, num_sms() / 2)) {
+    return launch_qmm_ta(w, scales, biases, x, out.base[0] + out.col0, out.ld, K, N, M, st);
+  }
   return launch_qmm_2cta_bits<4>(w, scales, biases, x, out, K, N, M, st, reserve_sms);
 }
 
@@ -702,7 +744,7 @@ int qmm_launch_reserved(const uint32_t* w, const void* scales, const void* biase
 // and its peers' copies of y): the fused epilogue of the column-split. Needs M > 128.
 int qmm_launch_multi_dest(const uint32_t* w, const void* scales, const void* biases, const void* x,
                           void* const* dests, int count, int64_t ld, int64_t col0, int64_t K, int64_t N,
-                          int64_t M, void* stream) {
+                          int64_t M, void* stream, const PeerSync* sync) {
   if (!w || !scales || !biases || !x || !dests || count < 1 || count > 8) {
     return fail(VPQ_ERR_INVALID_ARG, "qmm (fused split): null pointer or more than 8 destinations");
   }
@@ -719,6 +761,10 @@ int qmm_launch_multi_dest(const uint32_t* w, const void* scales, const void* bia
   out.count = count;
   out.col0 = (int)col0;
   out.ld = ld;
+  if (sync && count > 1) {
+    out.handshake = 1;
+    out.sync = *sync;
+  }
   return launch_qmm_2cta(w, static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases), x, out,
                          (int)K, (int)N, (int)M, static_cast<cudaStream_t>(stream), 0);
 }
@@ -801,6 +847,41 @@ extern "C" int vpq_affine_qmm_geglu_w8g64_bf16(const uint32_t* w, const void* sc
                                                const void* x, void* y, int64_t K, int64_t N, int64_t M,
                                                void* stream) {
   return qmm_gated("affine_qmm_geglu_w8g64", 8, 2, w, scales, biases, x, y, K, N, M, stream);
+}
+
+// The GEMM for any of the format twins: bits 4 | 8, group 64 | 32; act 0 plain, 2 GeGLU (4 bits).
+extern "C" int vpq_affine_qmm_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x, void* y,
+                                   int64_t K, int64_t N, int64_t M, int bits, int group, int act, void* stream) {
+  clear_error();
+  if ((bits != 4 && bits != 8) || (group != 64 && group != 32) || (act != 0 && act != 2)) {
+    return fail(VPQ_ERR_INVALID_ARG, "affine_qmm: bits must be 4 or 8, group 64 or 32, act 0 or 2 (got %d, %d, %d)", bits,
+                group, act);
+  }
+  if (!w || !scales || !biases || !x || !y) { return fail(VPQ_ERR_INVALID_ARG, "affine_qmm: null pointer"); }
+  if (K <= 0 || N <= 0 || M <= 0 || (K % 64) != 0 || (act && (N % 2))) {
+    return fail(VPQ_ERR_INVALID_ARG, "affine_qmm: need K>0, N>0 (even for a gated store), M>0, K%%64==0 (K=%lld N=%lld M=%lld)",
+                (long long)K, (long long)N, (long long)M);
+  }
+  if (K > (1 << 20) || N > (1 << 24) || M > (1 << 24)) {
+    return fail(VPQ_ERR_UNSUPPORTED, "affine_qmm: shape too large (K=%lld N=%lld M=%lld)", (long long)K, (long long)N,
+                (long long)M);
+  }
+  if (!aligned16(w) || !aligned16(x) || !aligned16(y) || (reinterpret_cast<uintptr_t>(scales) & 1) ||
+      (reinterpret_cast<uintptr_t>(biases) & 1)) {
+    return fail(VPQ_ERR_ALIGNMENT, "affine_qmm: w, x and y must be 16-byte aligned");
+  }
+  if (int rc = require_sm100()) { return rc; }
+  two_cta::OutSpec out = {};
+  out.base[0] = static_cast<__nv_bfloat16*>(y);
+  out.count = 1;
+  out.col0 = 0;
+  out.ld = act ? N / 2 : N;
+  out.swiglu = act;
+  const uint16_t* s16 = static_cast<const uint16_t*>(scales);
+  const uint16_t* b16 = static_cast<const uint16_t*>(biases);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (bits == 8) { return launch_qmm_2cta_bits<8>(w, s16, b16, x, out, (int)K, (int)N, (int)M, st, 0, group); }
+  return launch_qmm_2cta_bits<4>(w, s16, b16, x, out, (int)K, (int)N, (int)M, st, 0, group);
 }
 
 extern "C" int vpq_affine_qmm_w8g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,

@@ -46,6 +46,8 @@ struct OutSpec {
   int64_t ld;
   int swiglu;  // 1, 2: columns 2j, 2j+1 of the product are gate j, up j: store act(gate) * up, half as
                // wide; act = silu (1) or the tanh form of gelu (2). Selects the kernel instantiation.
+  int handshake;      // 1: `sync` is valid (column split with the cross-GPU handshake inside the kernel)
+  vpq::PeerSync sync;
 };
 
 template <int BITS, int TNT = 256>
@@ -144,7 +146,8 @@ __device__ __forceinline__ uint4 ld_cg_v4(const void* p) {  // from L2: written 
 }
 
 
-template <int kAct, int BITS, int TNT>
+// GS: quantization group along K, 64 (one group per k block) or 32 (two).
+template <int kAct, int BITS, int TNT, int GS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
 affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
                              const __grid_constant__ CUtensorMap tmap_w,
@@ -216,6 +219,12 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
   cluster_sync_all();  // both CTAs' barriers exist before anybody signals across
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+
+  if (out.handshake && blockIdx.x == 0 && threadIdx.x < (unsigned)out.count && threadIdx.x >= 1) {
+    // this rank's stream has reached the call: tell every peer (its senders wait for this before they
+    // write into our y, which an earlier kernel of ours may have been reading until now)
+    *reinterpret_cast<volatile uint32_t*>(out.sync.flag_of[threadIdx.x] + out.sync.rank) = out.sync.epoch;
+  }
 
   if (warp == 4) {
     // ------------------------------------------------------- TMA producer (both CTAs)
@@ -294,6 +303,28 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const int lrow = lane / kLanesPerRow, lcol = (lane % kLanesPerRow) * 8;
       uint32_t ti = 0;
       bool ok = true;
+      if (out.handshake) {
+        // No store into a peer's y before that peer's stream has reached this call (bounded wait).
+        uint32_t seen = 1;
+        if (lane >= 1 && lane < out.count) {
+          seen = 0;
+          volatile uint32_t* f = out.sync.my_flags + out.sync.src_rank[lane];
+          for (uint32_t i = 0; i < (1u << 24); ++i) {
+            if ((int32_t)(*f - out.sync.epoch) >= 0) {
+              seen = 1;
+              break;
+            }
+            if (*abort_flag) { break; }
+            __nanosleep(100);
+          }
+          if (!seen) {
+            *abort_flag = 1;
+            atomicCAS(&g_qmm_status, 0u, (2u << 8) | kRoleSend);
+          }
+        }
+        ok = __all_sync(0xffffffffu, seen != 0);
+        __threadfence_system();
+      }
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++ti) {
         const int m0 = (tile / tiles_n) * TM + (int)rank * 128 + sw_id * kRowsPerWarp;
         const int n0 = (tile % tiles_n) * TN;
@@ -338,6 +369,23 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
           }
         }
       }
+      if (out.handshake) {
+        // All of this warp's stores are out: the sender warp that finishes last on this GPU tells every
+        // peer that this rank's column block is complete in the peer's y.
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const uint32_t total = gridDim.x * (uint32_t)kSendWarps;
+          if (atomicAdd(out.sync.warps_done, 1u) == total - 1u) {
+            __threadfence_system();
+            for (int d = 1; d < out.count; ++d) {
+              *reinterpret_cast<volatile uint32_t*>(out.sync.flag_of[d] + 8 + out.sync.rank) = out.sync.epoch;
+            }
+            *out.sync.warps_done = 0;
+            __threadfence_system();
+          }
+        }
+      }
     }
   } else if (warp >= 6) {
     // ------------------------------------------------------- dequantisers (both CTAs)
@@ -347,7 +395,7 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
     const int t_row = threadIdx.x - 6 * 32 - grp * (kDqGroupWarps * 32);  // 0 .. kWRows - 1
     const uint32_t row_off = (uint32_t)(t_row >> 3) * 1024u + (uint32_t)(t_row & 7) * 128u;
     const uint32_t sw = (uint32_t)(t_row & 7);
-    const int groups = K >> 6;
+    const int groups = K / GS;
     const uint32_t bfull_leader = map_to_cta(bar0, 0);  // cluster address of the leader's barrier block
     uint32_t it = 0;
     bool ok = true;
@@ -364,8 +412,15 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const int t = it % kBTiles;
         const uint32_t bph = (it / kBTiles) & 1u;
         if ((kb & (kDqGroups - 1)) != grp) { continue; }  // another group's k block
-        float sc, bi;
-        sst.get(kb, sc, bi);
+        float sc, bi, sc_hi, bi_hi;  // group 32: the scales of the two halves of the k block
+        if (GS == 64) {
+          sst.get(kb, sc, bi);
+          sc_hi = sc;
+          bi_hi = bi;
+        } else {
+          sst.get(2 * kb, sc, bi);
+          sst.get(2 * kb + 1, sc_hi, bi_hi);
+        }
         if (!warp_wait(bar_cfull(s), ph, (1u << 8) | kRoleDq, abort_flag, &g_qmm_status)) { ok = false; break; }
         const uint4* cp = reinterpret_cast<const uint4*>(base_ptr + L::kOffCode + s * L::kCodeBytes +
                                                          t_row * (BK * BITS / 8));
@@ -376,14 +431,19 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
           if (lane == 0) { mbar_arrive(bar_empty(s)); }  // codes are in registers
 
           const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-          float s_133, s_129;
-          if (dequant_scale_up(sc, s_133, s_129)) {
-            const uint64_t s2 = pack_f32x2(s_133, s_129), b2 = pack_f32x2(bi, bi);
 #pragma unroll
-            for (int wd = 0; wd < 8; ++wd) { dequant_word_fast(cw[wd], s2, b2, o + 4 * wd); }
-          } else {  // a zero, subnormal or large scale: the plain way
+          for (int hf = 0; hf < (GS == 64 ? 1 : 2); ++hf) {  // per scale: the whole k block, or each half of it
+            constexpr int kWords = GS == 64 ? 8 : 4;
+            const float sh = hf ? sc_hi : sc, bh = hf ? bi_hi : bi;
+            float s_133, s_129;
+            if (dequant_scale_up(sh, s_133, s_129)) {
+              const uint64_t s2 = pack_f32x2(s_133, s_129), b2 = pack_f32x2(bh, bh);
 #pragma unroll
-            for (int wd = 0; wd < 8; ++wd) { dequant_word_exact(cw[wd], sc, bi, o + 4 * wd); }
+              for (int wd = 0; wd < kWords; ++wd) { dequant_word_fast(cw[hf * kWords + wd], s2, b2, o + 4 * (hf * kWords + wd)); }
+            } else {  // a zero, subnormal or large scale: the plain way
+#pragma unroll
+              for (int wd = 0; wd < kWords; ++wd) { dequant_word_exact(cw[hf * kWords + wd], sh, bh, o + 4 * (hf * kWords + wd)); }
+            }
           }
         } else {
           const uint4 c0 = cp[0], c1 = cp[1], c2 = cp[2], c3 = cp[3];
@@ -395,14 +455,19 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
           // (subnormals and the first binade are linear in their bit pattern), so
           // fma(that, s * 2^133, b) rounds the same real number as fma(s, q, b): bit-exact,
           // as long as s * 2^133 is a normal float (2^-126 <= |s| < 2^-5; else the plain way).
-          float s_133, s_129;
-          if (dequant_scale_up(sc, s_133, s_129)) {
-            const uint64_t s2 = pack_f32x2(s_133, s_133), b2 = pack_f32x2(bi, bi);
 #pragma unroll
-            for (int wd = 0; wd < 16; ++wd) { dequant_word8_fast(cw[wd], s2, b2, o + 2 * wd); }
-          } else {
+          for (int hf = 0; hf < (GS == 64 ? 1 : 2); ++hf) {
+            constexpr int kWords = GS == 64 ? 16 : 8;
+            const float sh = hf ? sc_hi : sc, bh = hf ? bi_hi : bi;
+            float s_133, s_129;
+            if (dequant_scale_up(sh, s_133, s_129)) {
+              const uint64_t s2 = pack_f32x2(s_133, s_133), b2 = pack_f32x2(bh, bh);
 #pragma unroll
-            for (int wd = 0; wd < 16; ++wd) { dequant_word8_exact(cw[wd], sc, bi, o + 2 * wd); }
+              for (int wd = 0; wd < kWords; ++wd) { dequant_word8_fast(cw[hf * kWords + wd], s2, b2, o + 2 * (hf * kWords + wd)); }
+            } else {
+#pragma unroll
+              for (int wd = 0; wd < kWords; ++wd) { dequant_word8_exact(cw[hf * kWords + wd], sh, bh, o + 2 * (hf * kWords + wd)); }
+            }
           }
         }
 

@@ -42,11 +42,26 @@ int num_sms();
 int qmm_launch_reserved(const uint32_t* w, const void* scales, const void* biases, const void* x, void* y,
                         int64_t K, int64_t N, int64_t M, void* stream, int reserve_sms);
 
-// The QMM whose epilogue stores its [M, N] column block into several row-major outputs of leading
-// dimension ld at column col0 (this GPU's y and its peers' y); qmm.cu.
+// Cross-GPU handshake of the fused column split, carried out inside the GEMM kernel itself.
+// Every rank has a flag table (uint32 [16], mapped by all peers): slot r = "rank r has started call
+// number `epoch`" (so whatever it enqueued earlier to read y is done), slot 8 + r = "rank r has
+// finished storing its column block of call `epoch` everywhere". flag_of[d] is the table of the
+// peer behind destination d (d >= 1; the order of `dests`), src_rank[d] that peer's rank.
+struct PeerSync {
+  uint32_t* flag_of[8];
+  int src_rank[8];
+  uint32_t* my_flags;   // this rank's own table
+  uint32_t* warps_done; // this GPU's count of sender warps that finished (zero between calls)
+  uint32_t epoch;
+  int rank;
+};
+
+// The QMM that stores its [M, N] column block into this GPU's row-major output dests[0] (leading
+// dimension ld, first column col0) and whose sender warps copy every finished tile on to the peers'
+// outputs dests[1..count); qmm.cu. `sync` (null: no handshake) as above.
 int qmm_launch_multi_dest(const uint32_t* w, const void* scales, const void* biases, const void* x,
                           void* const* dests, int count, int64_t ld, int64_t col0, int64_t K, int64_t N,
-                          int64_t M, void* stream);
+                          int64_t M, void* stream, const PeerSync* sync);
 
 // Reads and clears the GEMV kernel's device status word (qmv.cu).
 int ensure_dynamic_smem(const void* func, int* granted, size_t bytes);

@@ -296,6 +296,20 @@ def qmm(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
     return out
 
 
+def qmm_any(codes, scales, biases, x, bits: int, group: int, act: str = "none", out=None, stream=None) -> torch.Tensor:
+    """GEMM over any format twin (vpq_affine_qmm_bf16): bits 4 | 8, group 64 | 32, act "none" | "geglu"."""
+    N, Kw = codes.shape
+    K = Kw * (32 // bits)
+    M = x.numel() // K
+    a = {"none": 0, "geglu": 2}[act]
+    if out is None:
+        out = torch.empty((M, N // 2 if a else N), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().vpq_affine_qmm_bf16(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x), _ptr(out), K, N, M, bits,
+                                        group, a, _stream(stream)))
+    return out
+
+
 def qmm_w8(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
     """GEMM over 8-bit group-64 weights, codes int32 [N, K/4] (vpq_affine_qmm_w8g64_bf16)."""
     N, Kw = codes.shape
