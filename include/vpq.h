@@ -288,6 +288,17 @@ int vpq_affine_qmm_swiglu_w4g64_bf16(const uint32_t* w, const void* scales, cons
 int vpq_affine_qmm_w8g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
                               void* y, int64_t K, int64_t N, int64_t M, void* stream);
 
+/* q | k | v as ONE GEMM over the row-concatenated weight (the way the reference keeps these three
+ * projections, generative-models/qwen3/metal-qwen-model.cc:214-250), with three outputs q [M, q_rows],
+ * k [M, k_rows], v [M, v_rows]: narrow k / v projections (N = 1024 in an 8B decoder) alone fill a
+ * quarter of the GPU's tiles, together with q they fill it. q_rows and k_rows must be multiples of
+ * 128, v_rows of 8 (otherwise run three GEMMs on row slices of w). The prefill counterpart of
+ * affine_qmv_qkv_w4g64 (gpu-kernels/metal/quant/affine_qmv.metal:405-516); in the reference prefill
+ * runs affine_qmm_steel_w4g64 on the concatenated weight and slices the output afterwards. */
+int vpq_affine_qmm_qkv_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                                  void* q_out, void* k_out, void* v_out, int64_t K, int64_t q_rows,
+                                  int64_t k_rows, int64_t v_rows, int64_t M, void* stream);
+
 /* The GEMM over any of the format twins: bits 4 | 8, group 64 | 32 (scales / biases [N, K/group]), act 0
  * (y [M, N]) or 2 (GeGLU over interleaved gate | up rows, y [M, N/2]; 4-bit only at group 32). The
  * group-32 forms are the same CTA-pair kernel with two scales per 64-wide k block. Replaces

@@ -296,6 +296,24 @@ def test_qmm_full_configs_on_sampled_rows(vpq, oracle_mod, tag, M, K, N):
     assert int(torch.isnan(y).sum()) == 0
 
 
+@pytest.mark.parametrize("M,K,q_rows,k_rows,v_rows", [(2048, 4096, 4096, 1024, 1024), (300, 1024, 256, 128, 72)])
+def test_qmm_qkv_in_one_gemm_equals_three(vpq, oracle_mod, M, K, q_rows, k_rows, v_rows):
+    """q | k | v as one GEMM over the row-concatenated weight: each output carries exactly the bytes of
+    the plain GEMM on that projection's row slice, and the whole matches the fp32 oracle."""
+    N = q_rows + k_rows + v_rows
+    codes, s, b, x = _device_linear(vpq, N, K, M, synth.seed_for("qkvmm", M, K))
+    q, k, v = vpq.ops.qmm_qkv(codes, s, b, x, q_rows, k_rows, v_rows)
+    assert vpq.ops.device_status() == 0
+    lo = 0
+    for out, rows in ((q, q_rows), (k, k_rows), (v, v_rows)):
+        want = vpq.ops.qmm(codes[lo:lo + rows].contiguous(), s[lo:lo + rows].contiguous(),
+                           b[lo:lo + rows].contiguous(), x)
+        assert torch.equal(out, want)
+        lo += rows
+    rows_s = np.arange(0, M, max(M // 16, 1))
+    check_linear(oracle_mod, torch.cat([q, k, v], dim=1), bits32(codes), bits16(s), bits16(b), bits16(x), rows=rows_s)
+
+
 def test_dispatch_by_reference_names(vpq, oracle_mod):
     """load_library(...).function(...) + slot-numbered dispatch gives the same bytes as the direct calls."""
     N, K, M = 256, 1024, 160

@@ -560,7 +560,6 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
 }
 
 #include "qmm_2cta.cuh"
-#include "qmm_ta.cuh"
 
 // ------------------------------------------------------------- host side
 template <int BN, int kAct>
@@ -623,7 +622,7 @@ int launch_qmm_2cta_bits(const uint32_t* w, const uint16_t* scales, const uint16
                          int group = 64) {
   int pairs = (num_sms() - reserve_sms) / 2;  // SMs left free run a concurrent collective
   if (pairs < 1) { pairs = 1; }
-  const int tnt = (BITS == 4 && out.swiglu == 0 && group == 64) ? pick_tile_width(M, N, pairs) : 256;
+  const int tnt = (BITS == 4 && out.swiglu == 0 && group == 64 && out.split0 == 0) ? pick_tile_width(M, N, pairs) : 256;
   CUtensorMap map_x, map_w;
   if (int rc = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)K, (uint64_t)M,
                            BK, 128, CU_TENSOR_MAP_SWIZZLE_128B, "x")) {
@@ -661,41 +660,8 @@ int launch_qmm_2cta_bits(const uint32_t* w, const uint16_t* scales, const uint16
   return VPQ_OK;
 }
 
-// The kernel with the dequantised W tile in tensor memory (qmm_ta.cuh): plain 4-bit group-64 GEMM into
-// one row-major output. It moves half the shared-memory bytes per flop of the kernel above, but its
-// 256 x 192 tiles want enough of them to fill the CTA pairs.
-bool prefer_ta(int M, int N, int pairs) {
-  const int tiles = ((M + ta::TX - 1) / ta::TX) * ((N + ta::TW - 1) / ta::TW);
-  return tiles >= 2 * pairs;
-}
-
-int launch_qmm_ta(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const void* x, __nv_bfloat16* y,
-                  int64_t ld, int K, int N, int M, cudaStream_t st) {
-  using L = ta::SmemTa;
-  CUtensorMap map_x, map_w;
-  if (int rc = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)K, (uint64_t)M, BK, ta::TX / 2,
-                           CU_TENSOR_MAP_SWIZZLE_128B, "x")) {
-    return rc;
-  }
-  if (int rc = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w, (uint64_t)(K / 8), (uint64_t)N, BK / 8, 128,
-                           CU_TENSOR_MAP_SWIZZLE_NONE, "w")) {
-    return rc;
-  }
-  auto kern = ta::affine_qmm_w4g64_ta_kernel;
-  VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
-  const int tiles = ((M + ta::TX - 1) / ta::TX) * ((N + ta::TW - 1) / ta::TW);
-  const int pairs = num_sms() / 2;
-  const int grid = 2 * (tiles < pairs ? tiles : pairs);
-  kern<<<grid, ta::kThreadsTa, L::kAlloc, st>>>(map_x, map_w, scales, biases, y, ld, M, N, K);
-  VPQ_LAUNCH_OK("affine_qmm (tensor-memory A)");
-  return VPQ_OK;
-}
-
 int launch_qmm_2cta(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const void* x,
                     const two_cta::OutSpec& out, int K, int N, int M, cudaStream_t st, int reserve_sms) {
-  if (out.count == 1 && out.swiglu == 0 && reserve_sms == 0 && prefer_ta(M, N, num_sms() / 2)) {
-    return launch_qmm_ta(w, scales, biases, x, out.base[0] + out.col0, out.ld, K, N, M, st);
-  }
   return launch_qmm_2cta_bits<4>(w, scales, biases, x, out, K, N, M, st, reserve_sms);
 }
 
@@ -847,6 +813,46 @@ extern "C" int vpq_affine_qmm_geglu_w8g64_bf16(const uint32_t* w, const void* sc
                                                const void* x, void* y, int64_t K, int64_t N, int64_t M,
                                                void* stream) {
   return qmm_gated("affine_qmm_geglu_w8g64", 8, 2, w, scales, biases, x, y, K, N, M, stream);
+}
+
+// q | k | v in one GEMM over the row-concatenated weight, three outputs.
+extern "C" int vpq_affine_qmm_qkv_w4g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                                             void* q_out, void* k_out, void* v_out, int64_t K, int64_t q_rows,
+                                             int64_t k_rows, int64_t v_rows, int64_t M, void* stream) {
+  clear_error();
+  if (!w || !scales || !biases || !x || !q_out || !k_out || !v_out) {
+    return fail(VPQ_ERR_INVALID_ARG, "affine_qmm_qkv_w4g64: null pointer");
+  }
+  if (K <= 0 || M <= 0 || (K % 64) != 0 || q_rows <= 0 || k_rows <= 0 || v_rows <= 0) {
+    return fail(VPQ_ERR_INVALID_ARG, "affine_qmm_qkv_w4g64: need K>0, M>0, K%%64==0 and positive q / k / v row counts");
+  }
+  if ((q_rows % 128) != 0 || (k_rows % 128) != 0 || (v_rows % 8) != 0) {
+    return fail(VPQ_ERR_UNSUPPORTED,
+                "affine_qmm_qkv_w4g64: q_rows and k_rows must be multiples of 128 and v_rows of 8 (got %lld, %lld, %lld); "
+                "run three GEMMs on the row slices of w instead",
+                (long long)q_rows, (long long)k_rows, (long long)v_rows);
+  }
+  const int64_t N = q_rows + k_rows + v_rows;
+  if (K > (1 << 20) || N > (1 << 24) || M > (1 << 24)) {
+    return fail(VPQ_ERR_UNSUPPORTED, "affine_qmm_qkv_w4g64: shape too large (K=%lld N=%lld M=%lld)", (long long)K,
+                (long long)N, (long long)M);
+  }
+  if (!aligned16(w) || !aligned16(x) || !aligned16(q_out) || !aligned16(k_out) || !aligned16(v_out) ||
+      (reinterpret_cast<uintptr_t>(scales) & 1) || (reinterpret_cast<uintptr_t>(biases) & 1)) {
+    return fail(VPQ_ERR_ALIGNMENT, "affine_qmm_qkv_w4g64: w, x and the outputs must be 16-byte aligned");
+  }
+  if (int rc = require_sm100()) { return rc; }
+  two_cta::OutSpec out = {};
+  out.base[0] = static_cast<__nv_bfloat16*>(q_out);
+  out.base[1] = static_cast<__nv_bfloat16*>(k_out);
+  out.base[2] = static_cast<__nv_bfloat16*>(v_out);
+  out.count = 1;
+  out.col0 = 0;
+  out.ld = N;
+  out.split0 = (int)q_rows;
+  out.split1 = (int)(q_rows + k_rows);
+  return launch_qmm_2cta_bits<4>(w, static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases), x, out,
+                                 (int)K, (int)N, (int)M, static_cast<cudaStream_t>(stream), 0);
 }
 
 // The GEMM for any of the format twins: bits 4 | 8, group 64 | 32; act 0 plain, 2 GeGLU (4 bits).

@@ -46,6 +46,10 @@ struct OutSpec {
   int64_t ld;
   int swiglu;  // 1, 2: columns 2j, 2j+1 of the product are gate j, up j: store act(gate) * up, half as
                // wide; act = silu (1) or the tanh form of gelu (2). Selects the kernel instantiation.
+  // q | k | v GEMM: split0 > 0 routes output columns [0, split0) to base[0] (row pitch split0),
+  // [split0, split1) to base[1] (pitch split1 - split0) and the rest to base[2] (pitch N - split1);
+  // both splits are multiples of 128, so a 128-column pass never straddles two outputs.
+  int split0, split1;
   int handshake;      // 1: `sync` is valid (column split with the cross-GPU handshake inside the kernel)
   vpq::PeerSync sync;
 };
@@ -558,10 +562,23 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
           }
         }
         __syncwarp();
-        const int nc0 = swiglu ? n0 / 2 : n0 + h * 128;  // first stored column of this pass (within the block)
+        int nc0 = swiglu ? n0 / 2 : n0 + h * 128;  // first stored column of this pass (within the block)
         const int j = lane & 15;               // this lane's 16-byte chunk = 8 columns
         const bool col_ok = nc0 + j * 8 < n_out;
-        if (vec_ok) {
+        if (out.split0 > 0) {
+          // three outputs (q | k | v): this pass's 128 columns belong to exactly one of them
+          const int seg = nc0 < out.split0 ? 0 : nc0 < out.split1 ? 1 : 2;
+          const int seg0 = seg == 0 ? 0 : seg == 1 ? out.split0 : out.split1;
+          const int seg_w = (seg == 0 ? out.split0 : seg == 1 ? out.split1 : N) - seg0;
+          __nv_bfloat16* dst = out.base[seg];
+#pragma unroll 4
+          for (int i = 0; i < 16; ++i) {
+            const int row = 2 * i + (lane >> 4);
+            const uint4 pk = *reinterpret_cast<const uint4*>(stg + row * 256 + ((j ^ (row & 15)) << 4));
+            const int mm = mrow0 + row;
+            if (mm < M && col_ok) { *reinterpret_cast<uint4*>(dst + (int64_t)mm * seg_w + (nc0 - seg0) + j * 8) = pk; }
+          }
+        } else if (vec_ok) {
 #pragma unroll 4
           for (int i = 0; i < 16; ++i) {
             const int row = 2 * i + (lane >> 4);

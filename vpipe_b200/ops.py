@@ -296,6 +296,21 @@ def qmm(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
     return out
 
 
+def qmm_qkv(codes, scales, biases, x, q_rows, k_rows, v_rows, outs=None, stream=None):
+    """W = q | k | v row-concatenated, one GEMM, three outputs (vpq_affine_qmm_qkv_w4g64_bf16)."""
+    N, Kw = codes.shape
+    K = Kw * 8
+    M = x.numel() // K
+    assert q_rows + k_rows + v_rows == N
+    if outs is None:
+        outs = [torch.empty((M, r), dtype=torch.bfloat16, device=x.device) for r in (q_rows, k_rows, v_rows)]
+    with torch.cuda.device(x.device):
+        check(lib().vpq_affine_qmm_qkv_w4g64_bf16(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x), _ptr(outs[0]),
+                                                  _ptr(outs[1]), _ptr(outs[2]), K, q_rows, k_rows, v_rows, M,
+                                                  _stream(stream)))
+    return tuple(outs)
+
+
 def qmm_any(codes, scales, biases, x, bits: int, group: int, act: str = "none", out=None, stream=None) -> torch.Tensor:
     """GEMM over any format twin (vpq_affine_qmm_bf16): bits 4 | 8, group 64 | 32, act "none" | "geglu"."""
     N, Kw = codes.shape
