@@ -54,11 +54,12 @@ MIN_TIMED_SECONDS = 0.5     # the headline's timed blocks are repeated until thi
 NVLINK_GBS_MEASURED = 770.0  # peer copy per direction per GPU on this pool; nominal 900
 
 # DRAM traffic per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) as a
-# multiple of the launch's algorithmic bytes, on small cases whose traffic grows in proportion to
-# the work: a 4-layer plan launch of the C2 set (401.4 MB moved for 396.9 MB algorithmic), and
-# the GEMM at M = K = N = 8192 (x + W + y exceed L2).
-QMV_TRAFFIC_RATIO = 1.011
-QMM_TRAFFIC_RATIO = None
+# multiple of the launch's algorithmic bytes: a 4-layer plan launch of the C2 set (405.7 MB moved for
+# 396.9 MB algorithmic; it grows in proportion to the layers), and the GEMM at M = K = N = 8192
+# (402.8 MB moved for 306 MB: x tiles that have left L2 are read again; an upper estimate for the
+# smaller C3 / C4 shapes, whose x stays in L2).
+QMV_TRAFFIC_RATIO = 1.022
+QMM_TRAFFIC_RATIO = 1.32
 
 
 def peaks():

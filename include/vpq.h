@@ -234,8 +234,15 @@ int vpq_affine_qmv_w4g32_bf16_fused(const vpq_linear_desc* desc_host, void* stre
  * same x (q | k | v, gate | up) stage it once. "Encode once, commit many": the analogue of
  * encoding a decode step's dispatches into one command buffer and re-committing it,
  * apple-silicon/metal-compute/command-stream.h:144, generative-models/qwen3/metal-qwen-model.cc:3004-3074.
- * The GEMVs must be independent of each other (none reads another's y); pointers are captured
- * at creation, their contents may change between runs. `workspace` is caller-owned device memory
+ * Descriptors with depends == 0 must be independent of each other (none reads another's y). A
+ * descriptor with depends == 1 may read (x, residual) what ANY earlier descriptor of the list
+ * writes: the list then runs as a dependent chain inside one cooperative launch -- every GEMV is
+ * spread over the whole grid, a counter in the workspace counts finished tiles, and a dependent
+ * GEMV stages its x only when everything before it is complete, while its weights are already
+ * streaming. That is a whole decode step between two attention calls as one launch: o_proj +
+ * residual -> norm + gate|up (SwiGLU) -> down + residual -> norm + q|k|v; bit-identical to one
+ * launch per GEMV. An expert index array (`expert`) must be complete before the launch. Pointers
+ * are captured at creation, their contents may change between runs. `workspace` is caller-owned device memory
  * of vpq_qmv_plan_bytes() bytes holding the per-problem descriptors; it must outlive the plan.
  * vpq_qmv_plan_create copies into it and synchronises `stream`; vpq_qmv_plan_run only launches. */
 typedef struct vpq_qmv_plan_s vpq_qmv_plan;
@@ -256,8 +263,10 @@ int vpq_qmv_plan_destroy(vpq_qmv_plan* plan);
  * and uses no allocating library routine. The first call on each device looks up the array's
  * device address; make that first call outside any stream capture. All calls share the one
  * array: a call rewrites every descriptor it uses (nothing is read from a previous call), but
- * two calls that overlap on the GPU (different streams, or graphs replayed concurrently) race on
- * it -- keep calls to this entry point ordered on one stream per device. */
+ * two calls that overlap on the GPU (different streams) race on it -- keep calls to this entry
+ * point ordered on one stream per device. The call cannot be recorded into a CUDA graph: its
+ * descriptors are copied from the call's stack, so a stream that is being captured is refused with
+ * VPQ_ERR_UNSUPPORTED (use vpq_qmv_plan_create / vpq_qmv_plan_run there). */
 int vpq_affine_qmv_w4g64_bf16_set_noalloc(const vpq_linear_desc* descs_host, int count, void* stream);
 
 /* Prefill / DiT GEMM: y[M,N] = x[M,K] @ dequant(W)[N,K]^T. W is dequantised
@@ -450,15 +459,18 @@ int vpq_affine_qmm_w4g64_bf16_nsplit(vpq_comm* comm,
 /* Fused form: no separate collective. y lives in a symmetric buffer that every rank has mapped
  * (CUDA IPC, one process per GPU). Each rank's GEMM stores its column block into its own row-major
  * y[M, N]; sender warps of the same kernel copy every finished tile on to the peers' y with
- * ordinary stores over NVLink while the tensor cores work on the next tiles. Two small flag
- * barriers over the same mapping bracket the GEMM on the stream:
- *   entry - no rank starts writing before every rank's stream has reached this call, so work a
- *           peer enqueued earlier that still reads y (the previous step's result) is finished;
- *   exit  - when the call's work completes on a rank's stream, every column block has arrived in
- *           that rank's y.
+ * ordinary stores over NVLink while the tensor cores work on the next tiles. The handshake between
+ * the ranks runs inside the kernel as well:
+ *   started  - the kernel announces its start to every peer, and its sender warps hold their first
+ *              store into a peer's y until that peer has announced its own start, i.e. until
+ *              whatever the peer enqueued earlier to read y (the previous step's result) is done;
+ *   finished - the sender warp that finishes last on a GPU announces it to every peer, and a small
+ *              kernel behind the GEMM on the stream waits for all peers' announcements, so that
+ *              later work on the stream finds every column block in y.
  * Ordering is therefore by stream order alone: enqueue the consumers of y after the call and the
  * next call after them, on the same stream, on every rank; no host synchronisation and no second
- * buffer are needed. All ranks must make the same sequence of calls on a communicator.
+ * buffer are needed. All ranks must make the same sequence of calls on a communicator. Every wait
+ * is bounded; a rank that never shows up ends in VPQ_ERR_TIMEOUT from vpq_device_status.
  * vpq_comm_alloc_symmetric is collective (all ranks, same order) and is the one place this library
  * allocates device memory; it owns the buffer until vpq_comm_free_symmetric / vpq_comm_destroy.
  * Needs M > 128, N % (8*world) == 0. */
