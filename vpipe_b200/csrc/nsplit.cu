@@ -32,7 +32,8 @@ struct vpq_comm_s {
   // fused column-split: symmetric buffers, and a flag array per rank for the cross-GPU barrier
   vpq_sym_buf bufs[8];
   int nbufs = 0;
-  vpq_sym_buf flags;       // uint32 [16] per rank: [r] rank r started call `epoch`, [8 + r] rank r finished it; [16] sender-warp count
+  vpq_sym_buf flags;       // uint32 per rank: [r] rank r started call `epoch`, [8 + r] rank r finished it; [16] sender-CTA
+                           // count; [32 ..) one counter per GEMM tile
   uint32_t epoch = 0;
   void* handle_stage = nullptr;  // device staging for the IPC-handle exchange
   cudaStream_t comm_stream = nullptr;
@@ -43,6 +44,7 @@ struct vpq_comm_s {
 namespace vpq {
 namespace {
 
+constexpr int kTileFlags = 1 << 18;  // GEMM tiles the fused column split can count (1 MB of flags per GPU)
 constexpr int kCollectiveSms = 16;  // SMs the GEMM leaves to NCCL when the exchange overlaps it
 
 struct Nccl {
@@ -342,10 +344,10 @@ extern "C" int vpq_comm_alloc_symmetric(vpq_comm* c, size_t bytes, void** local_
   if (c->world > 8) { return fail(VPQ_ERR_UNSUPPORTED, "comm_alloc_symmetric: at most 8 ranks"); }
   if (c->nbufs >= 8) { return fail(VPQ_ERR_UNSUPPORTED, "comm_alloc_symmetric: at most 8 live buffers"); }
   if (!c->flags.local) {  // first use: the barrier flags
-    VPQ_CUDA_OK(cudaMalloc(&c->flags.local, 32 * sizeof(uint32_t)));
-    VPQ_CUDA_OK(cudaMemset(c->flags.local, 0, 32 * sizeof(uint32_t)));
+    VPQ_CUDA_OK(cudaMalloc(&c->flags.local, (32 + kTileFlags) * sizeof(uint32_t)));
+    VPQ_CUDA_OK(cudaMemset(c->flags.local, 0, (32 + kTileFlags) * sizeof(uint32_t)));
     VPQ_CUDA_OK(cudaDeviceSynchronize());
-    c->flags.bytes = 32 * sizeof(uint32_t);
+    c->flags.bytes = (32 + kTileFlags) * sizeof(uint32_t);
     if (int rc = map_peers(c, &c->flags)) { return rc; }
     // the peers' flag arrays as a device table for the barrier kernel
     uint32_t* hp[8] = {};
@@ -408,6 +410,8 @@ extern "C" int vpq_affine_qmm_w4g64_bf16_nsplit_fused(vpq_comm* c, const uint32_
   }
   ps.my_flags = static_cast<uint32_t*>(c->flags.local);
   ps.warps_done = ps.my_flags + 16;
+  ps.tile_flags = ps.my_flags + 32;
+  ps.tile_flag_count = kTileFlags;
   ps.epoch = ++c->epoch;
   ps.rank = c->rank;
   // The handshake with the peers runs inside the GEMM kernel: it announces "started" when it starts,

@@ -622,7 +622,9 @@ int launch_qmm_2cta_bits(const uint32_t* w, const uint16_t* scales, const uint16
                          int group = 64) {
   int pairs = (num_sms() - reserve_sms) / 2;  // SMs left free run a concurrent collective
   if (pairs < 1) { pairs = 1; }
-  const int tnt = (BITS == 4 && out.swiglu == 0 && group == 64 && out.split0 == 0) ? pick_tile_width(M, N, pairs) : 256;
+  const int tnt = (BITS == 4 && out.swiglu == 0 && group == 64 && out.split0 == 0)
+                      ? pick_tile_width(M, N, pairs - (out.comm_pairs > 0 ? out.comm_pairs : 0))
+                      : 256;
   CUtensorMap map_x, map_w;
   if (int rc = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)K, (uint64_t)M,
                            BK, 128, CU_TENSOR_MAP_SWIZZLE_128B, "x")) {
@@ -654,8 +656,14 @@ int launch_qmm_2cta_bits(const uint32_t* w, const uint16_t* scales, const uint16
   }
   VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   const int tiles = ((M + two_cta::TM - 1) / two_cta::TM) * ((N + tnt - 1) / tnt);
-  const int grid = 2 * (tiles < pairs ? tiles : pairs);
-  kern<<<grid, two_cta::kThreads2, smem, st>>>(map_x, map_w, scales, biases, out, M, N, K);
+  two_cta::OutSpec spec = out;
+  int compute = pairs;
+  if (spec.comm_pairs > 0) {  // column split: the last pairs of the grid only send
+    if (spec.comm_pairs > pairs / 2) { spec.comm_pairs = pairs / 2; }
+    compute = pairs - spec.comm_pairs;
+  }
+  const int grid = 2 * ((tiles < compute ? tiles : compute) + spec.comm_pairs);
+  kern<<<grid, two_cta::kThreads2, smem, st>>>(map_x, map_w, scales, biases, spec, M, N, K);
   VPQ_LAUNCH_OK("affine_qmm (2-CTA)");
   return VPQ_OK;
 }
@@ -727,8 +735,16 @@ int qmm_launch_multi_dest(const uint32_t* w, const void* scales, const void* bia
   out.count = count;
   out.col0 = (int)col0;
   out.ld = ld;
-  if (sync && count > 1) {
-    out.handshake = 1;
+  if (count > 1) {
+    if (!sync || !sync->tile_flags) { return fail(VPQ_ERR_INVALID_ARG, "qmm (fused split): the tile flags are missing"); }
+    const int64_t tiles = ((M + 255) / 256) * ((N + 127) / 128);
+    if (tiles > sync->tile_flag_count) {
+      return fail(VPQ_ERR_UNSUPPORTED, "qmm (fused split): %lld tiles, the communicator's flag array holds %d", (long long)tiles,
+                  sync->tile_flag_count);
+    }
+    out.comm_pairs = count <= 2 ? 4 : count <= 4 ? 6 : 8;  // sender pairs: enough SMs to keep the links busy
+    out.tile_flags = sync->tile_flags;
+    out.handshake = sync->my_flags != nullptr;
     out.sync = *sync;
   }
   return launch_qmm_2cta(w, static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases), x, out,

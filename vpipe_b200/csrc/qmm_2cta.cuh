@@ -6,13 +6,18 @@
 // own 128 x rows (A operand) but only HALF of the W tile (128 rows of B); the tensor cores of
 // both SMs read both halves. Dequant work and shared-memory bytes per flop halve.
 //
-// Per CTA, 512 threads: warps 0-3 epilogue (tensor-memory lanes = this CTA's 128 output rows),
+// Per CTA, 448 threads: warps 0-3 epilogue (tensor-memory lanes = this CTA's 128 output rows),
 // warp 4 TMA producer, warp 5 tensor-memory allocation (+ MMA issue in the leader CTA only), warps
 // 6-13 dequantisers: groups of warps with one W row (64 values) per thread, the groups taking
-// k blocks in turn so one block's latency hides behind the others', warps 14-15 senders (column
-// split over several GPUs only): they copy finished tiles from this GPU's y to the peers' y with
-// ordinary stores over NVLink, behind the epilogue, so the link runs beside the tensor cores
-// instead of stalling the accumulator hand-over.
+// k blocks in turn so one block's latency hides behind the others'.
+//
+// Column split over several GPUs: the last `comm_pairs` CTA pairs of the grid compute nothing. They
+// are SENDER CTAs: the computing pairs store every tile into this GPU's y and count it in a flag
+// array; a sender CTA waits for its next tile's count, reads the tile back (from L2) and stores it
+// into every peer's y with ordinary stores over NVLink. Keeping the peer stores on SMs of their
+// own matters: a store that waits for link credit holds up everything behind it on its SM's way to
+// the memory system. Issued from the computing SMs (first from the epilogue warps, then from two
+// extra warps per CTA) the exchange did not overlap the GEMM, it added to it.
 //
 // Two tile widths: 256 x 256 (TNT = 256: 128 W rows per CTA, two dequant groups of four warps) and
 // 256 x 128 (TNT = 128: 64 W rows per CTA, four groups of two warps), the narrow one for shapes
@@ -32,8 +37,7 @@ constexpr int TM = 256;        // tile rows (128 per CTA)
 constexpr int kXStages4 = 5;   // x + codes ring, 4-bit weights
 constexpr int kXStages8 = 4;   // ... 8-bit weights (the codes of a stage are twice as large)
 constexpr int kDqWarps = 8;
-constexpr int kSendWarps = 2;
-constexpr int kThreads2 = 32 * (kEpiWarps + 2 + kDqWarps + kSendWarps);
+constexpr int kThreads2 = 32 * (kEpiWarps + 2 + kDqWarps);
 
 // Where a CTA pair's output tile goes: `count` row-major destinations (this GPU's y and, in the
 // fused column-split, every peer's y mapped into this address space), leading dimension `ld`,
@@ -51,6 +55,8 @@ struct OutSpec {
   // both splits are multiples of 128, so a 128-column pass never straddles two outputs.
   int split0, split1;
   int handshake;      // 1: `sync` is valid (column split with the cross-GPU handshake inside the kernel)
+  int comm_pairs;     // column split: CTA pairs at the end of the grid that only send (0: nothing is sent)
+  uint32_t* tile_flags;  // column split: per tile, epilogue warps that have stored it locally (zero between calls)
   vpq::PeerSync sync;
 };
 
@@ -181,18 +187,109 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
   auto bar_accempty = [&](int a) { return bar0 + 8u * (3 * kXStages + 2 * kBTiles + 2 + a); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L::kOffTmem);
   volatile uint32_t* abort_flag = tmem_slot + 1;
-  uint32_t* epi_done = const_cast<uint32_t*>(tmem_slot) + 2;  // epilogue warps that finished a tile's local stores
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = leader (issues the MMAs)
   const int cluster_id = blockIdx.x >> 1;
-  const int num_clusters = gridDim.x >> 1;
+  const int num_clusters = (gridDim.x >> 1) - out.comm_pairs;  // the pairs that compute
 
   const int tiles_m = (M + TM - 1) / TM;
   const int tiles_n = (N + TN - 1) / TN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = K / BK;
+
+  if (out.comm_pairs > 0 && cluster_id >= num_clusters) {
+    // -------------------------------------------------- sender CTAs (column split only)
+    // Both CTAs of a sender pair work alone: sender CTA c of C takes tiles c, c + C, ... in the
+    // order the computing pairs finish them. No barriers of the pipeline, no tensor memory.
+    const int C = 2 * out.comm_pairs;
+    const int c = (cluster_id - num_clusters) * 2 + (int)rank;
+    __shared__ uint32_t comm_ok;
+    if (threadIdx.x == 0) { comm_ok = 1; }
+    __syncthreads();
+    if (out.handshake && threadIdx.x >= 1 && threadIdx.x < (unsigned)out.count) {
+      // No store into a peer's y before that peer's stream has reached this call (bounded wait).
+      bool seen = false;
+      volatile uint32_t* f = out.sync.my_flags + out.sync.src_rank[threadIdx.x];
+      for (uint32_t i = 0; i < (1u << 24); ++i) {
+        if ((int32_t)(*f - out.sync.epoch) >= 0) {
+          seen = true;
+          break;
+        }
+        __nanosleep(100);
+      }
+      if (!seen) {
+        comm_ok = 0;
+        atomicCAS(&g_qmm_status, 0u, (2u << 8) | kRoleSend);
+      }
+    }
+    __threadfence_system();
+    __syncthreads();
+    constexpr int kLanesPerRow = TN / 8;              // 16-byte chunks of a tile row
+    constexpr int kRowsPerInstr = 32 / kLanesPerRow;  // 1 (256-wide tile) or 2 (128-wide)
+    constexpr int kWarps = kThreads2 / 32;
+    const int lrow = lane / kLanesPerRow, lcol = (lane % kLanesPerRow) * 8;
+    for (int tile = c; tile < num_tiles && comm_ok; tile += C) {
+      if (threadIdx.x == 0) {  // wait (bounded) until the eight epilogue warps of the tile's pair have stored it
+        bool seen = false;
+        volatile uint32_t* f = out.tile_flags + tile;
+        for (uint32_t i = 0; i < (1u << 24); ++i) {
+          if (*f >= 2u * kEpiWarps) {
+            seen = true;
+            break;
+          }
+          __nanosleep(100);
+        }
+        if (!seen) {
+          comm_ok = 0;
+          atomicCAS(&g_qmm_status, 0u, (1u << 8) | kRoleSend);
+        }
+        __threadfence();
+      }
+      __syncthreads();
+      if (!comm_ok) { break; }
+      const int m0 = (tile / tiles_n) * TM;
+      const int n0 = (tile % tiles_n) * TN;
+      const bool col_ok = n0 + lcol < N;
+      // 256 rows of the tile, kRowsPerInstr per warp instruction, eight instructions in flight
+      constexpr int kStep = kWarps * 8 * kRowsPerInstr;
+      for (int r0 = warp * 8 * kRowsPerInstr; r0 < TM; r0 += kStep) {
+        uint4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int mm = m0 + r0 + i * kRowsPerInstr + lrow;
+          v[i] = make_uint4(0, 0, 0, 0);
+          if (mm < M && col_ok) { v[i] = ld_cg_v4(out.base[0] + (int64_t)mm * out.ld + out.col0 + n0 + lcol); }
+        }
+        for (int d = 1; d < out.count; ++d) {
+          __nv_bfloat16* dst = out.base[d];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int mm = m0 + r0 + i * kRowsPerInstr + lrow;
+            if (mm < M && col_ok) { *reinterpret_cast<uint4*>(dst + (int64_t)mm * out.ld + out.col0 + n0 + lcol) = v[i]; }
+          }
+        }
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) { out.tile_flags[tile] = 0; }  // ready for the next call
+    }
+    // All stores of this CTA are out: the sender CTA that finishes last on this GPU tells every peer
+    // that this rank's column block is complete in the peer's y.
+    __threadfence_system();
+    __syncthreads();
+    if (out.handshake && threadIdx.x == 0) {
+      if (atomicAdd(out.sync.warps_done, 1u) == (uint32_t)C - 1u) {
+        __threadfence_system();
+        for (int d = 1; d < out.count; ++d) {
+          *reinterpret_cast<volatile uint32_t*>(out.sync.flag_of[d] + 8 + out.sync.rank) = out.sync.epoch;
+        }
+        *out.sync.warps_done = 0;
+        __threadfence_system();
+      }
+    }
+    return;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kXStages; ++s) {
@@ -209,7 +306,6 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
       mbar_init(bar_accempty(a), 2 * kEpiWarps);
     }
     *abort_flag = 0;
-    *epi_done = 0;
     fence_mbar_init();
   }
   if (warp == 5) {  // the same warp of both CTAs allocates the pair's tensor memory
@@ -292,103 +388,6 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
           umma_commit_pair(bar_bempty(t));  // dequantised tiles free in both CTAs
         }
         if (ok) { umma_commit_pair(bar_accfull(a)); }
-      }
-    }
-  } else if (warp >= 6 + kDqWarps) {
-    // ------------------------------------------------------------ senders (both CTAs)
-    // Column split over several GPUs: a finished tile, already stored to this GPU's y by the
-    // epilogue, is read back (from L2) and stored to every peer's y. A warp moves one 512-byte
-    // row segment per instruction, eight rows in flight. Peer memory is only ever written here.
-    if (out.count > 1 && kAct == 0) {
-      const int sw_id = warp - (6 + kDqWarps);
-      constexpr int kRowsPerWarp = 128 / kSendWarps;
-      constexpr int kLanesPerRow = TN / 8;            // 16-byte chunks of a tile row
-      constexpr int kRowsPerInstr = 32 / kLanesPerRow;  // 1 (256-wide tile) or 2 (128-wide)
-      const int lrow = lane / kLanesPerRow, lcol = (lane % kLanesPerRow) * 8;
-      uint32_t ti = 0;
-      bool ok = true;
-      if (out.handshake) {
-        // No store into a peer's y before that peer's stream has reached this call (bounded wait).
-        uint32_t seen = 1;
-        if (lane >= 1 && lane < out.count) {
-          seen = 0;
-          volatile uint32_t* f = out.sync.my_flags + out.sync.src_rank[lane];
-          for (uint32_t i = 0; i < (1u << 24); ++i) {
-            if ((int32_t)(*f - out.sync.epoch) >= 0) {
-              seen = 1;
-              break;
-            }
-            if (*abort_flag) { break; }
-            __nanosleep(100);
-          }
-          if (!seen) {
-            *abort_flag = 1;
-            atomicCAS(&g_qmm_status, 0u, (2u << 8) | kRoleSend);
-          }
-        }
-        ok = __all_sync(0xffffffffu, seen != 0);
-        __threadfence_system();
-      }
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++ti) {
-        const int m0 = (tile / tiles_n) * TM + (int)rank * 128 + sw_id * kRowsPerWarp;
-        const int n0 = (tile % tiles_n) * TN;
-        // wait (bounded) until the four epilogue warps have stored this tile locally
-        uint32_t seen = 0;
-        if (lane == 0) {
-          for (uint32_t i = 0; i < (1u << 24); ++i) {
-            if (*reinterpret_cast<volatile uint32_t*>(epi_done) >= (uint32_t)kEpiWarps * (ti + 1)) {
-              seen = 1;
-              break;
-            }
-            if (*abort_flag) { break; }
-            __nanosleep(200);
-          }
-          if (!seen) {
-            *abort_flag = 1;
-            atomicCAS(&g_qmm_status, 0u, (1u << 8) | kRoleSend);
-          }
-        }
-        seen = __shfl_sync(0xffffffffu, seen, 0);
-        if (!seen) { ok = false; break; }
-        __threadfence();
-        const bool col_ok = n0 + lcol < N;
-#pragma unroll 1
-        for (int r0 = 0; r0 < kRowsPerWarp; r0 += 8 * kRowsPerInstr) {
-          uint4 v[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int mm = m0 + r0 + i * kRowsPerInstr + lrow;
-            v[i] = make_uint4(0, 0, 0, 0);
-            if (mm < M && col_ok) { v[i] = ld_cg_v4(out.base[0] + (int64_t)mm * out.ld + out.col0 + n0 + lcol); }
-          }
-          for (int d = 1; d < out.count; ++d) {
-            __nv_bfloat16* dst = out.base[d];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int mm = m0 + r0 + i * kRowsPerInstr + lrow;
-              if (mm < M && col_ok) {
-                *reinterpret_cast<uint4*>(dst + (int64_t)mm * out.ld + out.col0 + n0 + lcol) = v[i];
-              }
-            }
-          }
-        }
-      }
-      if (out.handshake) {
-        // All of this warp's stores are out: the sender warp that finishes last on this GPU tells every
-        // peer that this rank's column block is complete in the peer's y.
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0) {
-          const uint32_t total = gridDim.x * (uint32_t)kSendWarps;
-          if (atomicAdd(out.sync.warps_done, 1u) == total - 1u) {
-            __threadfence_system();
-            for (int d = 1; d < out.count; ++d) {
-              *reinterpret_cast<volatile uint32_t*>(out.sync.flag_of[d] + 8 + out.sync.rank) = out.sync.epoch;
-            }
-            *out.sync.warps_done = 0;
-            __threadfence_system();
-          }
-        }
       }
     }
   } else if (warp >= 6) {
@@ -619,10 +618,10 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
           mbar_arrive_cluster(accempty_leader + 8u * a);
         }
       }
-      if (out.count > 1 && kAct == 0) {  // hand the tile to the senders: stores first, then the count
+      if (out.comm_pairs > 0) {  // hand the tile to the sender CTAs: stores first, then the count
         __threadfence();
         __syncwarp();
-        if (lane == 0) { atomicAdd(epi_done, 1u); }
+        if (lane == 0) { atomicAdd(out.tile_flags + tile, 1u); }
       }
     }
   }

@@ -68,14 +68,28 @@ __device__ __forceinline__ void mma_u8s8_16832(int (&c)[4], uint32_t a0, uint32_
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// D = A * B + init: starts an accumulator chain from a constant held in one register.
+// D = A * B + init: starts an accumulator chain from a constant. The constant sits in four
+// registers of its own that only these instructions read, so the hardware's accumulator-input quad
+// is there already and no moves are needed to seed the four chains of every stage (16 of ~240
+// instructions per stage otherwise).
+struct AccInit {
+  int c0, c1, c2, c3;
+};
+__device__ __forceinline__ AccInit make_acc_init(int v) {
+  AccInit a;
+  // opaque to the compiler on purpose: four equal constants would be merged into one register again
+  asm volatile("mov.b32 %0, %4;\n\tmov.b32 %1, %4;\n\tmov.b32 %2, %4;\n\tmov.b32 %3, %4;"
+               : "=r"(a.c0), "=r"(a.c1), "=r"(a.c2), "=r"(a.c3)
+               : "r"(v));
+  return a;
+}
 __device__ __forceinline__ void mma_u8s8_16832_first(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                                     uint32_t a3, uint32_t b0, uint32_t b1, int init) {
+                                                     uint32_t a3, uint32_t b0, uint32_t b1, const AccInit& init) {
   asm volatile(
       "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 "
-      "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
       : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(init));
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(init.c0), "r"(init.c1), "r"(init.c2), "r"(init.c3));
 }
 
 // Accumulators start at the bits of 12582912.0f (1.5 * 2^23): while |sum| < 2^22 the integer
@@ -211,7 +225,7 @@ struct Scratch {
   uint4* zero128;        // 128 bytes of zeros, 128-byte aligned
   unsigned char* xq;     // [cap_kt][3 digits][4 chunks][32 B]
   float* xg;             // [2 * cap_kt] sum of X per group
-  float* zero16;         // 16 bytes of zeros
+  float* zero16;         // four times -kAccSurplus: "no bias term" in the form the fold wants
   float* xu;             // [cap_kt / 2] 1 / scale of every 256-k box of x
   float* red;            // [kRedSlots][kConsWarps][16]
   uint32_t* red_cnt;     // [kRedSlots]
@@ -455,7 +469,8 @@ __device__ __noinline__ bool stage_x(const QmvProblem* P, unsigned char* p0, int
     }
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    if (live && (sub & 3) == 0) { xg[i >> 2] = (float)(int)sum; }
+    // (stored with the accumulators' surplus already taken off: the fold then needs no subtraction)
+    if (live && (sub & 3) == 0) { xg[i >> 2] = (float)(int)sum - kAccSurplus; }
     if (live && sub == 0) { xu[box] = __uint_as_float((uint32_t)(e - 21) << 23); }  // exact inverse of x_scale
   };
 #pragma unroll
@@ -593,6 +608,7 @@ __device__ __noinline__ uint32_t consume_tiles(const QmvProblem* P, int lo, int 
   const uint32_t sz_off = (uint32_t)kStageW + (bias_lane ? (uint32_t)kStageSZ / 2 : 0u) + (uint32_t)rho * 64u +
                           (uint32_t)warp * 8u;
 
+  const AccInit acc_init = make_acc_init(kAccInit);
   int s = (int)(state & 7u);
   uint32_t ph = (state >> 3) & 1u;
   uint32_t tile_seq = state >> 4;
@@ -642,13 +658,13 @@ __device__ __noinline__ uint32_t consume_tiles(const QmvProblem* P, int lo, int 
         // four independent chains: even / odd nibbles of each k tile
         int ce0[4], co0[4], ce1[4], co1[4];
         mma_u8s8_16832_first(ce0, ra0.x & kEvenNibbles, rb0.x & kEvenNibbles, ra0.y & kEvenNibbles,
-                             rb0.y & kEvenNibbles, x00.x, x00.y, kAccInit);
+                             rb0.y & kEvenNibbles, x00.x, x00.y, acc_init);
         mma_u8s8_16832_first(ce1, ra1.x & kEvenNibbles, rb1.x & kEvenNibbles, ra1.y & kEvenNibbles,
-                             rb1.y & kEvenNibbles, x10.x, x10.y, kAccInit);
+                             rb1.y & kEvenNibbles, x10.x, x10.y, acc_init);
         mma_u8s8_16832_first(co0, ra0.x & kOddNibbles, rb0.x & kOddNibbles, ra0.y & kOddNibbles,
-                             rb0.y & kOddNibbles, x00.z, x00.w, kAccInit);
+                             rb0.y & kOddNibbles, x00.z, x00.w, acc_init);
         mma_u8s8_16832_first(co1, ra1.x & kOddNibbles, rb1.x & kOddNibbles, ra1.y & kOddNibbles,
-                             rb1.y & kOddNibbles, x10.z, x10.w, kAccInit);
+                             rb1.y & kOddNibbles, x10.z, x10.w, acc_init);
         mma_u8s8_16832(ce0, ra0.z & kEvenNibbles, rb0.z & kEvenNibbles, ra0.w & kEvenNibbles,
                        rb0.w & kEvenNibbles, x01.x, x01.y);
         mma_u8s8_16832(ce1, ra1.z & kEvenNibbles, rb1.z & kEvenNibbles, ra1.w & kEvenNibbles,
@@ -661,8 +677,7 @@ __device__ __noinline__ uint32_t consume_tiles(const QmvProblem* P, int lo, int 
         // c[3] = (rho + 8, second); value = even + odd / 16 - surplus (+ sum of x in a bias lane,
         // whose accumulators hold the bare initial value). The four groups of the box are folded
         // with their scales first, then the box's 1 / x-scale brings the sum to true units.
-        const float k0 = xs.x - kAccSurplus, k1 = xs.y - kAccSurplus;
-        const float k2 = xs.z - kAccSurplus, k3 = xs.w - kAccSurplus;
+        const float k0 = xs.x, k1 = xs.y, k2 = xs.z, k3 = xs.w;  // sum of x (bias lanes) or 0, minus the surplus
         auto val = [](int even, int odd, float k) {
           return __int_as_float(even) + __fmaf_rn(__int_as_float(odd), 0.0625f, k);
         };
@@ -769,7 +784,9 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
     fence_mbar_init();
   }
   if (threadIdx.x < 8) { sc.zero128[threadIdx.x] = make_uint4(0, 0, 0, 0); }
-  if (threadIdx.x == 8) { *reinterpret_cast<uint4*>(sc.zero16) = make_uint4(0, 0, 0, 0); }
+  if (threadIdx.x == 8) {  // what the lanes without a bias term read in place of a group sum of x
+    sc.zero16[0] = sc.zero16[1] = sc.zero16[2] = sc.zero16[3] = -kAccSurplus;
+  }
   __syncthreads();
 
   if (warp == kConsWarps) {

@@ -51,14 +51,17 @@ struct PeerSync {
   uint32_t* flag_of[8];
   int src_rank[8];
   uint32_t* my_flags;   // this rank's own table
-  uint32_t* warps_done; // this GPU's count of sender warps that finished (zero between calls)
+  uint32_t* warps_done; // this GPU's count of sender CTAs that finished (zero between calls)
+  uint32_t* tile_flags; // per tile of the GEMM: epilogue warps that stored it locally (zero between calls)
+  int tile_flag_count;  // entries of tile_flags
   uint32_t epoch;
   int rank;
 };
 
 // The QMM that stores its [M, N] column block into this GPU's row-major output dests[0] (leading
-// dimension ld, first column col0) and whose sender warps copy every finished tile on to the peers'
-// outputs dests[1..count); qmm.cu. `sync` (null: no handshake) as above.
+// dimension ld, first column col0) and whose sender CTAs copy every finished tile on to the peers'
+// outputs dests[1..count); qmm.cu. `sync` carries the tile flags; its handshake part is used when
+// sync->my_flags is not null.
 int qmm_launch_multi_dest(const uint32_t* w, const void* scales, const void* biases, const void* x,
                           void* const* dests, int count, int64_t ld, int64_t col0, int64_t K, int64_t N,
                           int64_t M, void* stream, const PeerSync* sync);
