@@ -96,11 +96,11 @@ static EncodeTiledFn encode_tiled_fn() {
 namespace {
 struct MapKey {
   const void* ptr;
-  uint64_t inner, outer;
+  uint64_t inner, outer, pitch;
   uint32_t box_inner, box_outer;
   int dt, elt_bytes, swz;
   bool operator==(const MapKey& o) const {
-    return ptr == o.ptr && inner == o.inner && outer == o.outer && box_inner == o.box_inner &&
+    return ptr == o.ptr && inner == o.inner && outer == o.outer && pitch == o.pitch && box_inner == o.box_inner &&
            box_outer == o.box_outer && dt == o.dt && elt_bytes == o.elt_bytes && swz == o.swz;
   }
 };
@@ -116,8 +116,9 @@ std::mutex g_maps_mutex;
 
 int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elt_bytes, const void* ptr,
                 uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer,
-                CUtensorMapSwizzle swz, const char* what) {
-  const MapKey key = {ptr, inner, outer, box_inner, box_outer, (int)dt, elt_bytes, (int)swz};
+                CUtensorMapSwizzle swz, const char* what, uint64_t row_pitch_bytes) {
+  if (row_pitch_bytes == 0) { row_pitch_bytes = inner * (uint64_t)elt_bytes; }
+  const MapKey key = {ptr, inner, outer, row_pitch_bytes, box_inner, box_outer, (int)dt, elt_bytes, (int)swz};
   const uint64_t h = (reinterpret_cast<uintptr_t>(ptr) >> 4) * 0x9E3779B97F4A7C15ull + box_outer * 31u + (uint64_t)dt;
   MapSlot& slot = g_maps[(h >> 32) % kMapSlots];
   {
@@ -130,7 +131,7 @@ int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elt_bytes, const v
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) { return fail(VPQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver"); }
   const cuuint64_t dims[2] = {inner, outer};
-  const cuuint64_t strides[1] = {inner * (uint64_t)elt_bytes};
+  const cuuint64_t strides[1] = {row_pitch_bytes};
   const cuuint32_t box[2] = {box_inner, box_outer};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,

@@ -635,7 +635,7 @@ int launch_qmm_2cta_bits(const uint32_t* w, const uint16_t* scales, const uint16
     return rc;
   }
   using KernelT = void (*)(const CUtensorMap, const CUtensorMap, const uint16_t*, const uint16_t*, const two_cta::OutSpec,
-                           int, int, int);
+                           const two_cta::DestMaps, int, int, int);
   KernelT kern;
   int smem;
   if (tnt == 128) {
@@ -663,7 +663,16 @@ int launch_qmm_2cta_bits(const uint32_t* w, const uint16_t* scales, const uint16
     compute = pairs - spec.comm_pairs;
   }
   const int grid = 2 * ((tiles < compute ? tiles : compute) + spec.comm_pairs);
-  kern<<<grid, two_cta::kThreads2, smem, st>>>(map_x, map_w, scales, biases, spec, M, N, K);
+  two_cta::DestMaps maps = {};
+  for (int d = 0; spec.comm_pairs > 0 && d < spec.count; ++d) {
+    // this rank's column block of destination d: [M rows x N columns] at column col0 of a row-major [M, ld]
+    if (int rc = make_map_2d(&maps.m[d], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, spec.base[d] + spec.col0, (uint64_t)N,
+                             (uint64_t)M, (uint32_t)tnt, 64, CU_TENSOR_MAP_SWIZZLE_NONE, "y (column split)",
+                             (uint64_t)spec.ld * 2)) {
+      return rc;
+    }
+  }
+  kern<<<grid, two_cta::kThreads2, smem, st>>>(map_x, map_w, scales, biases, spec, maps, M, N, K);
   VPQ_LAUNCH_OK("affine_qmm (2-CTA)");
   return VPQ_OK;
 }
@@ -742,7 +751,7 @@ int qmm_launch_multi_dest(const uint32_t* w, const void* scales, const void* bia
       return fail(VPQ_ERR_UNSUPPORTED, "qmm (fused split): %lld tiles, the communicator's flag array holds %d", (long long)tiles,
                   sync->tile_flag_count);
     }
-    out.comm_pairs = count <= 2 ? 4 : count <= 4 ? 6 : 8;  // sender pairs: enough SMs to keep the links busy
+    out.comm_pairs = count <= 2 ? 6 : 8;  // sender pairs: enough SMs (12 / 16) to keep the links busy
     out.tile_flags = sync->tile_flags;
     out.handshake = sync->my_flags != nullptr;
     out.sync = *sync;

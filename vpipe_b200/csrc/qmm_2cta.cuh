@@ -60,6 +60,12 @@ struct OutSpec {
   vpq::PeerSync sync;
 };
 
+// Column split: tensor maps over this rank's column block of every destination's y (m[0] = this
+// GPU's copy, the source of the senders; m[1..] = the peers'), boxes of [tile width x 64 rows].
+struct DestMaps {
+  CUtensorMap m[8];
+};
+
 template <int BITS, int TNT = 256>
 struct SmemT {
   static constexpr int kWRows = TNT / 2;              // W rows dequantised per CTA
@@ -162,7 +168,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
 affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
                              const __grid_constant__ CUtensorMap tmap_w,
                              const uint16_t* __restrict__ scales, const uint16_t* __restrict__ biases,
-                             const OutSpec out, int M, int N, int K) {
+                             const OutSpec out, const __grid_constant__ DestMaps maps, int M, int N, int K) {
   using L = SmemT<BITS, TNT>;
   constexpr int kXStages = L::kXStages;
   constexpr int kBTiles = L::kBTiles;
@@ -226,53 +232,85 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
     }
     __threadfence_system();
     __syncthreads();
-    constexpr int kLanesPerRow = TN / 8;              // 16-byte chunks of a tile row
-    constexpr int kRowsPerInstr = 32 / kLanesPerRow;  // 1 (256-wide tile) or 2 (128-wide)
-    constexpr int kWarps = kThreads2 / 32;
-    const int lrow = lane / kLanesPerRow, lcol = (lane % kLanesPerRow) * 8;
-    for (int tile = c; tile < num_tiles && comm_ok; tile += C) {
-      if (threadIdx.x == 0) {  // wait (bounded) until the eight epilogue warps of the tile's pair have stored it
-        bool seen = false;
-        volatile uint32_t* f = out.tile_flags + tile;
-        for (uint32_t i = 0; i < (1u << 24); ++i) {
-          if (*f >= 2u * kEpiWarps) {
-            seen = true;
+    // One thread drives the copy with the TMA unit, nothing passes through registers: a tile travels
+    // as chunks of kChunkRows rows; a chunk is loaded from this GPU's y into a ring slot of shared
+    // memory (tensor-map load, completion on the slot's mbarrier) and stored from there into every
+    // peer's y (tensor-map stores, one bulk group per chunk). Loads run kSlots - 1 chunks ahead of
+    // the stores. The maps cover exactly this rank's column block, so a tile that overhangs the block
+    // is clipped by the hardware on both sides.
+    constexpr int kChunkRows = 64;
+    constexpr int kChunkBytes = kChunkRows * TN * 2;   // 32 KB (16 KB for the 128-wide tile)
+    constexpr int kSlots = 6;
+    constexpr int kChunksPerTile = TM / kChunkRows;
+    static_assert(kSlots * kChunkBytes + kSlots * 8 <= L::kTotal, "sender ring fits the kernel's shared memory");
+    const uint32_t ring = base;                         // the pipeline's shared memory is free in a sender CTA
+    const uint32_t sbar = base + kSlots * kChunkBytes;  // one mbarrier per slot
+    __shared__ uint32_t comm_abort;
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < kSlots; ++i) { mbar_init(sbar + 8u * i, 1); }
+      fence_mbar_init();
+      int my_tiles = 0;
+      for (int tile = c; tile < num_tiles; tile += C) { ++my_tiles; }
+      const int total = my_tiles * kChunksPerTile;
+      int loaded = 0, ready_tiles = 0;   // chunks whose load was issued; tiles of this CTA's list known to be complete
+      bool ok = comm_ok != 0;
+      // Is tile number ti of this CTA's list stored locally by all eight epilogue warps of its pair?
+      // block: wait for it (bounded; false = gave up); otherwise just look.
+      auto tile_ready = [&](int ti, bool block) -> bool {
+        if (ti < ready_tiles) { return true; }
+        volatile uint32_t* f = out.tile_flags + (c + ti * C);
+        bool seen = *f >= 2u * kEpiWarps;
+        for (uint32_t i = 0; block && !seen && i < (1u << 24); ++i) {
+          __nanosleep(64);
+          seen = *f >= 2u * kEpiWarps;
+        }
+        if (seen) {
+          __threadfence();
+          asm volatile("fence.proxy.async.global;" ::: "memory");  // generic-proxy stores -> the TMA unit's reads
+          ready_tiles = ti + 1;
+        }
+        return seen;
+      };
+      auto issue_load = [&](int q) {   // chunk q of this CTA's list
+        const int ti = q / kChunksPerTile, ch = q % kChunksPerTile;
+        const int tile = c + ti * C;
+        const int slot = q % kSlots;
+        mbar_expect_tx(sbar + 8u * slot, kChunkBytes);
+        tma_load_2d(ring + slot * kChunkBytes, &maps.m[0], sbar + 8u * slot, (tile % tiles_n) * TN,
+                    (tile / tiles_n) * TM + ch * kChunkRows);
+      };
+      for (int q = 0; q < total && ok; ++q) {
+        // loads run up to kSlots chunks ahead, as far as finished tiles allow; the chunk that is due
+        // now is waited for
+        while (loaded < total && loaded < q + kSlots) {
+          const bool must = loaded == q;
+          if (!tile_ready(loaded / kChunksPerTile, must)) {
+            if (must) {
+              atomicCAS(&g_qmm_status, 0u, (1u << 8) | kRoleSend);
+              ok = false;
+            }
             break;
           }
-          __nanosleep(100);
+          issue_load(loaded);
+          ++loaded;
         }
-        if (!seen) {
-          comm_ok = 0;
-          atomicCAS(&g_qmm_status, 0u, (1u << 8) | kRoleSend);
+        if (!ok) { break; }
+        const int slot = q % kSlots;
+        if (!mbar_wait(sbar + 8u * slot, (uint32_t)(q / kSlots) & 1u, (3u << 8) | kRoleSend, &comm_abort, &g_qmm_status)) {
+          ok = false;
+          break;
         }
-        __threadfence();
-      }
-      __syncthreads();
-      if (!comm_ok) { break; }
-      const int m0 = (tile / tiles_n) * TM;
-      const int n0 = (tile % tiles_n) * TN;
-      const bool col_ok = n0 + lcol < N;
-      // 256 rows of the tile, kRowsPerInstr per warp instruction, eight instructions in flight
-      constexpr int kStep = kWarps * 8 * kRowsPerInstr;
-      for (int r0 = warp * 8 * kRowsPerInstr; r0 < TM; r0 += kStep) {
-        uint4 v[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int mm = m0 + r0 + i * kRowsPerInstr + lrow;
-          v[i] = make_uint4(0, 0, 0, 0);
-          if (mm < M && col_ok) { v[i] = ld_cg_v4(out.base[0] + (int64_t)mm * out.ld + out.col0 + n0 + lcol); }
-        }
+        const int ti = q / kChunksPerTile, ch = q % kChunksPerTile;
+        const int tile = c + ti * C;
         for (int d = 1; d < out.count; ++d) {
-          __nv_bfloat16* dst = out.base[d];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int mm = m0 + r0 + i * kRowsPerInstr + lrow;
-            if (mm < M && col_ok) { *reinterpret_cast<uint4*>(dst + (int64_t)mm * out.ld + out.col0 + n0 + lcol) = v[i]; }
-          }
+          tma_store_2d(&maps.m[d], ring + slot * kChunkBytes, (tile % tiles_n) * TN, (tile / tiles_n) * TM + ch * kChunkRows);
         }
+        bulk_commit();
+        if (ch == kChunksPerTile - 1) { out.tile_flags[tile] = 0; }  // all of the tile's loads have landed: ready for the next call
+        bulk_wait_read<0>();  // the slot may be loaded again (the stores themselves drain behind)
       }
-      __syncthreads();
-      if (threadIdx.x == 0) { out.tile_flags[tile] = 0; }  // ready for the next call
+      bulk_wait_all();  // every store of this CTA has been performed
+      if (!ok) { comm_ok = 0; }
     }
     // All stores of this CTA are out: the sender CTA that finishes last on this GPU tells every peer
     // that this rank's column block is complete in the peer's y.

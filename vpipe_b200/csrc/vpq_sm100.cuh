@@ -8,10 +8,11 @@
 
 namespace vpq {
 
-// Encodes a row-major 2-D tensor map (inner extent first). Host side, api.cu.
+// Encodes a row-major 2-D tensor map (inner extent first); row_pitch_bytes 0 = rows back to back.
+// Host side, api.cu.
 int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elt_bytes, const void* ptr,
                 uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer,
-                CUtensorMapSwizzle swz, const char* what);
+                CUtensorMapSwizzle swz, const char* what, uint64_t row_pitch_bytes = 0);
 
 #ifdef __CUDACC__
 
@@ -105,6 +106,21 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
       : "memory");
 }
+
+// 2-D TMA store of a shared-memory tile (no swizzle) into global memory -- this GPU's or, in the
+// column split, a peer's; elements outside the tensor are not written. Completion is tracked with
+// bulk groups: commit, then wait for the group's READS of shared memory before reusing the tile.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(src), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
