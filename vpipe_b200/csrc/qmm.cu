@@ -667,7 +667,7 @@ int launch_qmm_2cta_bits(const uint32_t* w, const uint16_t* scales, const uint16
   for (int d = 0; spec.comm_pairs > 0 && d < spec.count; ++d) {
     // this rank's column block of destination d: [M rows x N columns] at column col0 of a row-major [M, ld]
     if (int rc = make_map_2d(&maps.m[d], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, spec.base[d] + spec.col0, (uint64_t)N,
-                             (uint64_t)M, (uint32_t)tnt, 64, CU_TENSOR_MAP_SWIZZLE_NONE, "y (column split)",
+                             (uint64_t)M, (uint32_t)tnt, 16, CU_TENSOR_MAP_SWIZZLE_NONE, "y (column split)",
                              (uint64_t)spec.ld * 2)) {
       return rc;
     }

@@ -61,7 +61,7 @@ struct OutSpec {
 };
 
 // Column split: tensor maps over this rank's column block of every destination's y (m[0] = this
-// GPU's copy, the source of the senders; m[1..] = the peers'), boxes of [tile width x 64 rows].
+// GPU's copy, the source of the senders; m[1..] = the peers'), boxes of [tile width x 16 rows].
 struct DestMaps {
   CUtensorMap m[8];
 };
@@ -238,15 +238,21 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // peer's y (tensor-map stores, one bulk group per chunk). Loads run kSlots - 1 chunks ahead of
     // the stores. The maps cover exactly this rank's column block, so a tile that overhangs the block
     // is clipped by the hardware on both sides.
-    constexpr int kChunkRows = 64;
-    constexpr int kChunkBytes = kChunkRows * TN * 2;   // 32 KB (16 KB for the 128-wide tile)
+    // kDrivers threads of a sender CTA (lane 0 of the first warps) each run such a pipeline of their
+    // own on their own share of the tiles: one thread's load -> store -> wait chain keeps the TMA unit
+    // busy only part of the time.
+    constexpr int kDrivers = 4;
+    constexpr int kChunkRows = 16;
+    constexpr int kChunkBytes = kChunkRows * TN * 2;   // 8 KB (4 KB for the 128-wide tile)
     constexpr int kSlots = 6;
     constexpr int kChunksPerTile = TM / kChunkRows;
-    static_assert(kSlots * kChunkBytes + kSlots * 8 <= L::kTotal, "sender ring fits the kernel's shared memory");
-    const uint32_t ring = base;                         // the pipeline's shared memory is free in a sender CTA
-    const uint32_t sbar = base + kSlots * kChunkBytes;  // one mbarrier per slot
+    static_assert(kDrivers * (kSlots * kChunkBytes + kSlots * 8) <= L::kTotal, "sender rings fit the kernel's shared memory");
     __shared__ uint32_t comm_abort;
-    if (threadIdx.x == 0) {
+    if (lane == 0 && warp < kDrivers) {
+      const uint32_t ring = base + (uint32_t)warp * (kSlots * kChunkBytes);              // the pipeline's shared memory is free here
+      const uint32_t sbar = base + kDrivers * kSlots * kChunkBytes + (uint32_t)warp * kSlots * 8u;  // one mbarrier per slot
+      const int C = kDrivers * 2 * out.comm_pairs;   // (shadows: tiles are dealt over all drivers of all sender CTAs)
+      const int c = ((cluster_id - num_clusters) * 2 + (int)rank) * kDrivers + warp;
       for (int i = 0; i < kSlots; ++i) { mbar_init(sbar + 8u * i, 1); }
       fence_mbar_init();
       int my_tiles = 0;
@@ -309,7 +315,7 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
         if (ch == kChunksPerTile - 1) { out.tile_flags[tile] = 0; }  // all of the tile's loads have landed: ready for the next call
         bulk_wait_read<0>();  // the slot may be loaded again (the stores themselves drain behind)
       }
-      bulk_wait_all();  // every store of this CTA has been performed
+      bulk_wait_all();  // every store of this driver has been performed
       if (!ok) { comm_ok = 0; }
     }
     // All stores of this CTA are out: the sender CTA that finishes last on this GPU tells every peer
