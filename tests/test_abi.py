@@ -75,7 +75,14 @@ def test_function_table_uses_reference_names(vpq):
                            ("affine_dequant_bf16", "affine_dequant_w8g64"),
                            ("affine_dequant_bf16", "affine_dequant_w8g32"),
                            ("affine_dequant_bf16", "affine_quant_w8_g64"),
-                           ("affine_dequant", "affine_quant_w4_g32")]:
+                           ("affine_dequant", "affine_quant_w4_g32"),
+                           ("affine_qmv_bf16", "affine_qmv_qkv_rms_w4g64"),
+                           ("affine_qmv_bf16", "affine_gather_qmv_swiglu_w4g64"),
+                           ("affine_qmv_bf16", "affine_gather_qmv_geglu_w4g64"),
+                           ("affine_qmv_bf16", "affine_gather_down_qmv_w4g64"),
+                           ("affine_qmm_steel_bf16", "affine_qmm_steel_w4g32"),
+                           ("affine_qmm_steel_bf16", "affine_qmm_geglu_w4g32"),
+                           ("affine_qmm_steel_bf16", "affine_qmm_steel_w8g32")]:
         fn = ops.function(libname, entry)
         assert fn, (libname, entry)
         assert vpq.lib().vpq_function_name(fn).decode() == entry
@@ -161,3 +168,38 @@ def test_no_cpu_fallback_without_a_gpu(vpq):
 def test_python_front_end_refuses_cpu_tensors(vpq):
     with pytest.raises(Exception):
         vpq.ops.dequantize(torch.zeros(8, 8, dtype=torch.int32), torch.zeros(8, 1), torch.zeros(8, 1))
+
+
+def test_descriptor_extensions_are_validated_on_the_host(vpq):
+    """The plan dependency, the RMSNorm prologue and the expert gather of a GEMV descriptor are
+    checked before any device work; the other GEMV kernels refuse them."""
+    from vpipe_b200 import _lib
+    L = vpq.lib()
+    d = _lib.LinearDesc()
+    d.w, d.scales, d.biases, d.x, d.y = 0x1000, 0x2000, 0x3000, 0x4000, 0x5000
+    d.K, d.N, d.M = 128, 32, 1
+    d.depends = 1                       # honoured by plans only
+    assert L.vpq_affine_qmv_w4g64_bf16_batch(C.byref(d), 1, None) == 3
+    assert b"depends" in L.vpq_last_error()
+    d.depends = 0
+    d.norm_w = 0x6008                   # not 16-byte aligned
+    assert L.vpq_affine_qmv_w4g64_bf16_batch(C.byref(d), 1, None) == 2
+    d.norm_w = 0
+    d.expert, d.experts = 0x7000, 0    # an expert gather needs the number of slabs
+    assert L.vpq_affine_qmv_w4g64_bf16_batch(C.byref(d), 1, None) == 1
+    d.experts = 4
+    assert L.vpq_affine_qmv_w8g64_bf16_fused(C.byref(d), None) == 3     # the 8-bit kernel takes plain descriptors only
+    assert L.vpq_affine_qmv_batch_w4g64_bf16_fused(C.byref(d), None) == 3
+
+
+def test_qkv_gemm_and_format_gemm_validate_their_arguments(vpq):
+    L = vpq.lib()
+    p = 0x10000
+    # q and k row counts must be multiples of 128
+    assert L.vpq_affine_qmm_qkv_w4g64_bf16(p, p, p, p, p, p, p, 1024, 100, 128, 128, 256, None) == 3
+    assert L.vpq_affine_qmm_qkv_w4g64_bf16(p, p, p, p, None, p, p, 1024, 128, 128, 128, 256, None) == 1
+    assert L.vpq_affine_qmm_bf16(p, p, p, p, p, 1024, 64, 256, 5, 64, 0, None) == 1      # bits
+    assert L.vpq_affine_qmm_bf16(p, p, p, p, p, 1024, 64, 256, 4, 48, 0, None) == 1      # group
+    assert L.vpq_affine_qmm_bf16(p, p, p, p, p, 1024, 63, 256, 4, 32, 2, None) == 1      # a gated store needs an even N
+    assert L.vpq_wait_probe(0, 1000, None) == 1
+    assert L.vpq_peer_barrier_probe(None, 2, 1, 100, None) == 1
