@@ -229,6 +229,13 @@ int vpq_affine_qmv_w8g64_bf16_fused(const vpq_linear_desc* desc_host, void* stre
 int vpq_affine_qmv_batch_w4g64_bf16_fused(const vpq_linear_desc* desc_host, void* stream);
 int vpq_affine_qmv_w4g32_bf16_fused(const vpq_linear_desc* desc_host, void* stream);
 
+/* The scale-only group-32 GEMV for GGUF Q4_0 repacks: every group's bias is -8 * its scale (exact in
+ * bf16), so the biases are neither passed nor read (desc->biases is ignored and may be null): one
+ * ninth less weight traffic. Results are bit-identical to vpq_affine_qmv_w4g32_bf16_fused given
+ * biases = -8 * scales. Any VPQ_EPILOGUE_*. Replaces affine_qmv_w4g32_q40, affine_qmv_w4g32_add_q40
+ * and affine_qmv_geglu_w4g32_q40 (gpu-kernels/metal/quant/affine_qmv.metal:322-341,384-403,1472-1487). */
+int vpq_affine_qmv_w4g32_q40_bf16_fused(const vpq_linear_desc* desc_host, void* stream);
+
 /* A list of independent GEMVs run as ONE launch: the kernel walks the row tiles of all problems
  * back to back, so there is no launch gap and no per-problem ramp-up, and problems that read the
  * same x (q | k | v, gate | up) stage it once. "Encode once, commit many": the analogue of

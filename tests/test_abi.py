@@ -51,6 +51,13 @@ def test_function_table_uses_reference_names(vpq):
                            ("affine_qmv_bf16", "affine_qmv_qkv_w4g64"),
                            ("affine_qmv_bf16", "affine_qmv_w8g64"),
                            ("affine_qmv_bf16", "affine_qmv_w4g32"),
+                           ("affine_qmv_bf16", "affine_qmv_w4g32_add"),
+                           ("affine_qmv_bf16", "affine_qmv_geglu_w4g32"),
+                           ("affine_qmv_bf16", "affine_qmv_gelu_mul_w4g32"),
+                           ("affine_qmv_bf16", "affine_qmv_qkv_w4g32"),
+                           ("affine_qmv_bf16", "affine_qmv_w4g32_q40"),
+                           ("affine_qmv_bf16", "affine_qmv_w4g32_add_q40"),
+                           ("affine_qmv_bf16", "affine_qmv_geglu_w4g32_q40"),
                            ("affine_qmm_steel_bf16", "affine_qmm_steel_w8g64"),
                            ("affine_qmv_bf16", "affine_qmv_batch_w4g64"),
                            ("affine_qmv_bf16", "affine_qmv_batch4_w4g64"),
@@ -126,6 +133,7 @@ def test_argument_validation_happens_before_any_device_work(vpq):
     assert L.vpq_affine_qmv_w8g64_bf16_fused(None, None) == INVALID
     assert L.vpq_affine_qmv_batch_w4g64_bf16_fused(None, None) == INVALID
     assert L.vpq_affine_qmv_w4g32_bf16_fused(None, None) == INVALID
+    assert L.vpq_affine_qmv_w4g32_q40_bf16_fused(None, None) == INVALID
     assert L.vpq_affine_qmm_swiglu_bf16_rs(p16, p16, p16, p16, p16, 64, 64, 4, 4, 40, 16, None) == INVALID
     assert L.vpq_affine_qmm_swiglu_bf16_rs(p16, p16, p16, p16, p16, 64, 64, 4, 5, 64, 0, None) == INVALID
     assert L.vpq_qmm_grouped_tile_rows() == 128

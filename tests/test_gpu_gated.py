@@ -268,3 +268,80 @@ def test_qmv_w4g32_fused_stores(vpq, oracle_mod, K, N, M):
     d = (to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16), to_dev(x, torch.bfloat16))
     plain = vpq.ops.qmv_g32(*d)
     _stores_against_plain(vpq.ops, d, plain, M, N, "g32", 9702 + N)
+
+
+def _q40_linear(N, K, M, seed):
+    """A GGUF Q4_0 repack as the reference's converter leaves it: nibbles 0..15, one scale per group of
+    32 (either sign), bias = -8 * scale."""
+    rng = np.random.default_rng(seed)
+    codes = rng.integers(0, 2**32, size=(N, K // 8), dtype=np.uint64).astype(np.uint32)
+    sf = (rng.standard_normal((N, K // 32)) * 0.02).astype(np.float32)
+    s = synth.f32_to_bf16_bits(sf)
+    b = synth.f32_to_bf16_bits(-8.0 * synth.bf16_bits_to_f32(s))   # exact
+    x = synth.activations_bf16(M, K, seed + 1)
+    return codes, s, b, x
+
+
+@pytest.mark.parametrize("K,N,M", [(4096, 2048, 1), (4096, 1024, 2), (96, 34, 1), (1056, 66, 3), (11008, 256, 2)])
+def test_qmv_w4g32_q40_scale_only(vpq, oracle_mod, K, N, M):
+    """affine_qmv_w4g32_q40, _add_q40, geglu_w4g32_q40 (affine_qmv.metal:322-341,384-403,1472-1487): the
+    bias buffer is not read; bit-identical to the group-32 GEMV given biases = -8 * scales, and within
+    tolerance of the fp32 oracle."""
+    from test_gpu_formats import _g32_reference
+    ops = vpq.ops
+    codes, s, b, x = _q40_linear(N, K, M, 9800 + N + K)
+    d = (to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16), to_dev(x, torch.bfloat16))
+    q = (d[0], d[1], None, d[3])
+    z = lambda *shape: torch.full(shape, float("nan"), dtype=torch.bfloat16, device=dev())
+    plain = ops.qmv_g32(*d)
+    y = ops.qmv_w8_fused(*q, z(M, N), {"epilogue": "none"}, kind="q40")
+    assert torch.equal(y, plain)
+    e = oracle_mod.err_metrics(f32(y), _g32_reference(oracle_mod, codes, s, b, x))
+    assert e["rel_l2"] < TOL and e["max_rel_rms"] < TOL, e
+    aux = to_dev(synth.activations_bf16(M, N, 9801 + N), torch.bfloat16)
+    for store in ({"epilogue": "add", "aux": aux}, {"epilogue": "geglu"}):
+        width = N // 2 if store["epilogue"] == "geglu" else N
+        want = ops.qmv_w8_fused(*d, z(M, width), store, kind="g32")
+        got = ops.qmv_w8_fused(*q, z(M, width), store, kind="q40")
+        assert not torch.isnan(got.float()).any()
+        assert torch.equal(got, want), store["epilogue"]
+    # by the reference's names; slot 2 (biases) is left empty
+    lib_name = "affine_qmv_bf16"
+    y2 = z(M, N)
+    ops.dispatch(ops.function(lib_name, "affine_qmv_w4g32_q40"), {0: d[0], 1: d[1], 3: d[3], 4: y2}, K=K, N=N, M=M)
+    assert torch.equal(y2, plain)
+    y2 = z(M, N)
+    ops.dispatch(ops.function(lib_name, "affine_qmv_w4g32_add_q40"), {0: d[0], 1: d[1], 3: d[3], 4: y2, 7: aux},
+                 K=K, N=N, M=M)
+    assert torch.equal(y2, (plain.float() + aux.float()).to(torch.bfloat16))
+    y2 = z(M, N // 2)
+    ops.dispatch(ops.function(lib_name, "affine_qmv_geglu_w4g32_q40"), {0: d[0], 1: d[1], 3: d[3], 4: y2}, K=K, N=N, M=M)
+    assert torch.equal(y2, ops.qmv_w8_fused(*d, z(M, N // 2), {"epilogue": "geglu"}, kind="g32"))
+
+
+def test_qmv_w4g32_fused_names(vpq, oracle_mod):
+    """affine_qmv_w4g32_add, affine_qmv_geglu_w4g32, affine_qmv_gelu_mul_w4g32, affine_qmv_qkv_w4g32 by name."""
+    ops = vpq.ops
+    K, N, M = 2048, 768, 2
+    codes, s, b, x = _q40_linear(N, K, M, 9900)
+    b = synth.f32_to_bf16_bits(synth.bf16_bits_to_f32(b) * 0.75)  # a general affine bias
+    d = (to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16), to_dev(x, torch.bfloat16))
+    aux = to_dev(synth.activations_bf16(M, N, 9901), torch.bfloat16)
+    z = lambda *shape: torch.full(shape, float("nan"), dtype=torch.bfloat16, device=dev())
+    lib_name = "affine_qmv_bf16"
+    for name, store, width in (("affine_qmv_w4g32_add", {"epilogue": "add", "aux": aux}, N),
+                               ("affine_qmv_geglu_w4g32", {"epilogue": "geglu"}, N // 2),
+                               ("affine_qmv_gelu_mul_w4g32", {"epilogue": "gelu_mul", "aux": aux}, N)):
+        want = ops.qmv_w8_fused(*d, z(M, width), store, kind="g32")
+        got = z(M, width)
+        bufs = {0: d[0], 1: d[1], 2: d[2], 3: d[3], 4: got}
+        if "aux" in store:
+            bufs[7] = aux
+        ops.dispatch(ops.function(lib_name, name), bufs, K=K, N=N, M=M)
+        assert torch.equal(got, want), name
+    q_rows, k_rows = 512, 128
+    yq, yk, yv = z(M, q_rows), z(M, k_rows), z(M, N - q_rows - k_rows)
+    ops.dispatch(ops.function(lib_name, "affine_qmv_qkv_w4g32"),
+                 {0: d[0], 1: d[1], 2: d[2], 3: d[3], 4: yq, 5: yk, 6: yv},
+                 K=K, M=M, q_rows=q_rows, k_rows=k_rows, v_rows=N - q_rows - k_rows)
+    assert torch.equal(torch.cat([yq, yk, yv], dim=1), ops.qmv_g32(*d))

@@ -53,6 +53,7 @@ SYMBOLS = [
     ("vpq_affine_qmv_w8g64_bf16_fused", _i, [_vp, _vp]),
     ("vpq_affine_qmv_batch_w4g64_bf16_fused", _i, [_vp, _vp]),
     ("vpq_affine_qmv_w4g32_bf16_fused", _i, [_vp, _vp]),
+    ("vpq_affine_qmv_w4g32_q40_bf16_fused", _i, [_vp, _vp]),
     ("vpq_affine_qmv_w4g64_bf16_set_noalloc", _i, [_vp, _i, _vp]),
     ("vpq_qmv_plan_bytes", C.c_size_t, [_vp, _i]),
     ("vpq_qmv_plan_create", _i, [_vp, _i, _vp, C.c_size_t, _vp, C.POINTER(_vp)]),

@@ -192,7 +192,7 @@ extern "C" size_t vpq_scale_bytes(int N, int K, int group) {
 struct vpq_function_s {
   const char* library;
   const char* entry;
-  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64, 66..69 qmv w8g64 add / swiglu / qkv / gelu*mul, 70 / 71 qmm swiglu strided store w4 / w8, 72..74 grouped qmm down / swiglu / geglu, 75 qmv norm + qkv, 76..78 gathered expert qmv swiglu / geglu / down, 79..81 qmm w4g32 / geglu w4g32 / w8g32; 10 + code: quant / dequant twins (see fmt_*)
+  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64, 66..69 qmv w8g64 add / swiglu / qkv / gelu*mul, 70 / 71 qmm swiglu strided store w4 / w8, 72..74 grouped qmm down / swiglu / geglu, 75 qmv norm + qkv, 76..78 gathered expert qmv swiglu / geglu / down, 79..81 qmm w4g32 / geglu w4g32 / w8g32, 82..85 qmv w4g32 add / geglu / gelu*mul / qkv, 86..88 scale-only (Q4_0) qmv w4g32 plain / add / geglu; 10 + code: quant / dequant twins (see fmt_*)
 };
 
 // The reference selects the element type with the library-name suffix and
@@ -216,6 +216,13 @@ static const vpq_function_s g_functions[] = {
     {"affine_qmv_bf16", "affine_qmv_qkv_w8g64", 68},
     {"affine_qmv_bf16", "affine_qmv_gelu_mul_w8g64", 69},
     {"affine_qmv_bf16", "affine_qmv_w4g32", 60},
+    {"affine_qmv_bf16", "affine_qmv_w4g32_add", 82},
+    {"affine_qmv_bf16", "affine_qmv_geglu_w4g32", 83},
+    {"affine_qmv_bf16", "affine_qmv_gelu_mul_w4g32", 84},
+    {"affine_qmv_bf16", "affine_qmv_qkv_w4g32", 85},
+    {"affine_qmv_bf16", "affine_qmv_w4g32_q40", 86},
+    {"affine_qmv_bf16", "affine_qmv_w4g32_add_q40", 87},
+    {"affine_qmv_bf16", "affine_qmv_geglu_w4g32_q40", 88},
     {"affine_qmv_bf16", "affine_qmv_batch_w4g64", 9},
     {"affine_qmv_bf16", "affine_qmv_batch4_w4g64", 9},
     {"affine_qmm_steel_bf16", "affine_qmm_steel_w4g64", 1},
@@ -364,6 +371,42 @@ extern "C" int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* a, 
     case 71:
       return vpq_affine_qmm_swiglu_bf16_rs(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3], const_cast<void*>(b[4]),
                                            a->K, a->N, a->M, fn->kind == 71 ? 8 : 4, a->out_stride, a->out_off, stream);
+    case 82:
+    case 83:
+    case 84:
+    case 85:
+    case 86:
+    case 87:
+    case 88: {  // group-32 GEMVs with a fused store; 86..88 ignore slot 2 (bias = -8 * scale)
+      vpq_linear_desc d;
+      std::memset(&d, 0, sizeof(d));
+      d.w = static_cast<const uint32_t*>(b[0]);
+      d.scales = b[1];
+      d.biases = b[2];
+      d.x = b[3];
+      d.y = const_cast<void*>(b[4]);
+      d.K = a->K;
+      d.M = a->M < 1 ? 1 : a->M;
+      d.N = a->N;
+      const int k = fn->kind;
+      if (k == 85) {
+        d.epilogue = VPQ_EPILOGUE_QKV;
+        d.aux = b[5];
+        d.y3 = const_cast<void*>(b[6]);
+        d.q_rows = a->q_rows;
+        d.k_rows = a->k_rows;
+        d.N = a->q_rows + a->k_rows + a->v_rows;
+      } else if (k == 82 || k == 87) {
+        d.epilogue = VPQ_EPILOGUE_ADD;
+        d.aux = b[7];
+      } else if (k == 83 || k == 88) {
+        d.epilogue = VPQ_EPILOGUE_GEGLU;
+      } else if (k == 84) {
+        d.epilogue = VPQ_EPILOGUE_GELU_MUL;
+        d.aux = b[7];
+      }
+      return k >= 86 ? vpq_affine_qmv_w4g32_q40_bf16_fused(&d, stream) : vpq_affine_qmv_w4g32_bf16_fused(&d, stream);
+    }
     case 66:
     case 67:
     case 68:

@@ -751,7 +751,10 @@ int qmm_launch_multi_dest(const uint32_t* w, const void* scales, const void* bia
       return fail(VPQ_ERR_UNSUPPORTED, "qmm (fused split): %lld tiles, the communicator's flag array holds %d", (long long)tiles,
                   sync->tile_flag_count);
     }
-    out.comm_pairs = count <= 2 ? 6 : 8;  // sender pairs: enough SMs (12 / 16) to keep the links busy
+    // Sender pairs: with one peer 12 sender SMs keep up with the GEMM; from three peers on the exchange
+    // is the longer part and more SMs move more (peer stores from 8 / 16 / 24 / 32 SMs: 470 / 537 / 604 /
+    // 613 GB/s measured), so 24.
+    out.comm_pairs = count <= 2 ? 6 : 12;
     out.tile_flags = sync->tile_flags;
     out.handshake = sync->my_flags != nullptr;
     out.sync = *sync;

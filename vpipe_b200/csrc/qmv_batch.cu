@@ -89,6 +89,7 @@ struct alignas(64) BatchProblem {
   int K, N, M;
   int row_tiles;
   int scales_tma;
+  int scale_only;              // 1: no biases are read, every group's bias is -8 * its scale (GGUF Q4_0 repacks)
   int epilogue;                // kEpi*: what the store does with a row's sums (see fused_store)
   int q_rows, k_rows;
   int y_pitch, aux_pitch, y3_pitch;  // elements between consecutive rows of x in y / aux / y3
@@ -156,6 +157,7 @@ affine_qmv_batch_w4_kernel(const __grid_constant__ BatchProblem P, int stages, i
       uint32_t it = 0;
       bool ok = true;
       const bool sz_tma = P.scales_tma != 0;
+      const uint32_t sz_bytes = sz_tma ? (P.scale_only ? kStageSZ / 2 : kStageSZ) : 0;
       for (int tile = gt_begin; tile < gt_end && ok; ++tile) {
         for (int st = 0; st < SPT; ++st, ++it) {
           const int s = it % stages;
@@ -166,13 +168,13 @@ affine_qmv_batch_w4_kernel(const __grid_constant__ BatchProblem P, int stages, i
           }
           const int nb = min(kBoxesPerStage, NB - st * kBoxesPerStage);
           const uint32_t dst = base + (uint32_t)s * kStageBytes;
-          mbar_expect_tx(bar_full(s), (uint32_t)nb * kBoxBytes + (sz_tma ? kStageSZ : 0));
+          mbar_expect_tx(bar_full(s), (uint32_t)nb * kBoxBytes + sz_bytes);
           for (int b = 0; b < nb; ++b) {
             tma_load_2d(dst + b * kBoxBytes, &P.mw, bar_full(s), (st * kBoxesPerStage + b) * 32, tile * 16);
           }
           if (sz_tma) {
             tma_load_2d(dst + kStageW, &P.ms, bar_full(s), st * GPS, tile * 16);
-            tma_load_2d(dst + kStageW + kStageSZ / 2, &P.mz, bar_full(s), st * GPS, tile * 16);
+            if (!P.scale_only) { tma_load_2d(dst + kStageW + kStageSZ / 2, &P.mz, bar_full(s), st * GPS, tile * 16); }
           }
         }
       }
@@ -308,7 +310,13 @@ affine_qmv_batch_w4_kernel(const __grid_constant__ BatchProblem P, int stages, i
   const uint32_t sz_off = (uint32_t)kStageW + (uint32_t)rho * (GPS * 2) + (uint32_t)(warp * 2 * GPT + gbase) * 2u;
   constexpr uint32_t kRow8 = 8u * GPS * 2u;
   const bool sz_tma = P.scales_tma != 0;
+  const bool scale_only = P.scale_only != 0;
   const int G = K / GROUP;
+  // a pair of bf16 scales -> the pair of biases -8 * scale (exact: a power of two times a bf16 value)
+  auto neg8 = [](uint32_t s2) {
+    const float a = -8.0f * __uint_as_float(s2 << 16), b = -8.0f * __uint_as_float(s2 & 0xffff0000u);
+    return (__float_as_uint(a) >> 16) | (__float_as_uint(b) & 0xffff0000u);
+  };
 
   uint32_t tile_seq = 0, ph = 0;
   int s = 0;
@@ -333,18 +341,22 @@ affine_qmv_batch_w4_kernel(const __grid_constant__ BatchProblem P, int stages, i
           if constexpr (GROUP == 64) {  // the two k tiles' pairs are adjacent: one 8-byte load each
             const unsigned char* q = sb + sz_off;
             const uint2 a = *reinterpret_cast<const uint2*>(q), b = *reinterpret_cast<const uint2*>(q + kRow8);
-            const uint2 c = *reinterpret_cast<const uint2*>(q + kStageSZ / 2);
-            const uint2 e = *reinterpret_cast<const uint2*>(q + kStageSZ / 2 + kRow8);
             sa[0] = a.x, sa[1] = a.y, sb2[0] = b.x, sb2[1] = b.y;
-            za[0] = c.x, za[1] = c.y, zb[0] = e.x, zb[1] = e.y;
+            if (!scale_only) {
+              const uint2 c = *reinterpret_cast<const uint2*>(q + kStageSZ / 2);
+              const uint2 e = *reinterpret_cast<const uint2*>(q + kStageSZ / 2 + kRow8);
+              za[0] = c.x, za[1] = c.y, zb[0] = e.x, zb[1] = e.y;
+            }
           } else {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               const unsigned char* q = sb + sz_off + h * (2 * GPT);
               sa[h] = *reinterpret_cast<const uint32_t*>(q);
               sb2[h] = *reinterpret_cast<const uint32_t*>(q + kRow8);
-              za[h] = *reinterpret_cast<const uint32_t*>(q + kStageSZ / 2);
-              zb[h] = *reinterpret_cast<const uint32_t*>(q + kStageSZ / 2 + kRow8);
+              if (!scale_only) {
+                za[h] = *reinterpret_cast<const uint32_t*>(q + kStageSZ / 2);
+                zb[h] = *reinterpret_cast<const uint32_t*>(q + kStageSZ / 2 + kRow8);
+              }
             }
           }
         } else {
@@ -356,9 +368,15 @@ affine_qmv_batch_w4_kernel(const __grid_constant__ BatchProblem P, int stages, i
             const int g0 = min((kt0 + h) * GPT + gbase, G - 1), g1 = min((kt0 + h) * GPT + gbase + 1, G - 1);
             sa[h] = pair(P.scales, r_a * G + g0, r_a * G + g1);
             sb2[h] = pair(P.scales, r_b * G + g0, r_b * G + g1);
-            za[h] = pair(P.biases, r_a * G + g0, r_a * G + g1);
-            zb[h] = pair(P.biases, r_b * G + g0, r_b * G + g1);
+            if (!scale_only) {
+              za[h] = pair(P.biases, r_a * G + g0, r_a * G + g1);
+              zb[h] = pair(P.biases, r_b * G + g0, r_b * G + g1);
+            }
           }
+        }
+        if (scale_only) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) { za[h] = neg8(sa[h]), zb[h] = neg8(sb2[h]); }
         }
         const int kt1 = kt0 + 1;
         float c0[4], d0[4], c1[4], d1[4];  // four independent accumulator chains
@@ -478,9 +496,10 @@ int rows_per_pass(int cap_kt) {
 // Passes of `per_pass` rows over one weight stream each. min_rows: the fewest rows this kernel
 // takes itself (group 64 hands single rows to the exact M = 1 kernel through `single`).
 template <int GROUP>
-int launch_batch(const char* who, const vpq_linear_desc& d, int per_pass, cudaStream_t st, bool single_rows_exact) {
+int launch_batch(const char* who, const vpq_linear_desc& d, int per_pass, cudaStream_t st, bool single_rows_exact,
+                 bool scale_only = false) {
   const uint32_t* w = d.w;
-  const void *scales = d.scales, *biases = d.biases, *x = d.x;
+  const void *scales = d.scales, *biases = scale_only ? d.scales : d.biases, *x = d.x;
   void* y = d.y;
   const int64_t K = d.K, N = d.N, M = d.M;
   const bool gated = d.epilogue == VPQ_EPILOGUE_SWIGLU || d.epilogue == VPQ_EPILOGUE_GEGLU;
@@ -499,6 +518,7 @@ int launch_batch(const char* who, const vpq_linear_desc& d, int per_pass, cudaSt
   constexpr int GPS = 2048 / GROUP;
   // scale / bias rows as TMA boxes: pitch and base multiples of 16 bytes
   p.scales_tma = ((K / GROUP) % 8 == 0 && aligned16(scales) && aligned16(biases)) ? 1 : 0;
+  p.scale_only = scale_only ? 1 : 0;
   if (p.scales_tma) {
     if (int rc = make_map_2d(&p.ms, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, (uint64_t)(K / GROUP), (uint64_t)N, GPS,
                              16, CU_TENSOR_MAP_SWIZZLE_NONE, "scales")) {
@@ -624,12 +644,15 @@ int batch_g64(const char* who, const vpq_linear_desc& d, void* stream) {
   return launch_batch<64>(who, d, per_pass, static_cast<cudaStream_t>(stream), true);
 }
 
-int gemv_g32(const char* who, const vpq_linear_desc& d, void* stream) {
-  if (int rc = check_batch_args(who, d.w, d.scales, d.biases, d.x, d.y, d.K, d.N, d.M, 32)) { return rc; }
+// scale_only: the descriptor's biases are ignored (may be null)
+int gemv_g32(const char* who, const vpq_linear_desc& d, void* stream, bool scale_only = false) {
+  if (int rc = check_batch_args(who, d.w, d.scales, scale_only ? d.scales : d.biases, d.x, d.y, d.K, d.N, d.M, 32)) {
+    return rc;
+  }
   if (int rc = qmv_check_plain(who, d)) { return rc; }
   if (int rc = require_sm100()) { return rc; }
   const int per_pass = rows_per_pass<32>((int)((d.K + 255) / 256) * 2);  // 2 rows per weight stream where they fit
-  return launch_batch<32>(who, d, per_pass, static_cast<cudaStream_t>(stream), false);
+  return launch_batch<32>(who, d, per_pass, static_cast<cudaStream_t>(stream), false, scale_only);
 }
 }  // namespace
 
@@ -656,4 +679,10 @@ extern "C" int vpq_affine_qmv_w4g32_bf16_fused(const vpq_linear_desc* desc_host,
   clear_error();
   if (!desc_host) { return fail(VPQ_ERR_INVALID_ARG, "affine_qmv_w4g32 (fused store): null descriptor"); }
   return gemv_g32("affine_qmv_w4g32 (fused store)", *desc_host, stream);
+}
+
+extern "C" int vpq_affine_qmv_w4g32_q40_bf16_fused(const vpq_linear_desc* desc_host, void* stream) {
+  clear_error();
+  if (!desc_host) { return fail(VPQ_ERR_INVALID_ARG, "affine_qmv_w4g32_q40: null descriptor"); }
+  return gemv_g32("affine_qmv_w4g32_q40", *desc_host, stream, true);
 }

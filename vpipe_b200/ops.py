@@ -123,11 +123,13 @@ def qmv_w8(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
 def qmv_w8_fused(codes, scales, biases, x, y, store, stream=None, kind="w8"):
     """A GEMV with a fused store through one descriptor; `store` as in qmv_set, `y` the (first) output
     tensor. kind "w8": 8-bit weights (vpq_affine_qmv_w8g64_bf16_fused); "batch": w4 g64 rows sharing one
-    weight stream (vpq_affine_qmv_batch_w4g64_bf16_fused); "g32": w4 g32 (vpq_affine_qmv_w4g32_bf16_fused)."""
+    weight stream (vpq_affine_qmv_batch_w4g64_bf16_fused); "g32": w4 g32 (vpq_affine_qmv_w4g32_bf16_fused);
+    "q40": w4 g32 scale-only, `biases` may be None (vpq_affine_qmv_w4g32_q40_bf16_fused)."""
     N, Kw = codes.shape
     K = Kw * (4 if kind == "w8" else 8)
     d = _lib.LinearDesc()
-    d.w, d.scales, d.biases, d.x, d.y = _ptr(codes), _ptr(scales), _ptr(biases), _ptr(x), _ptr(y)
+    d.w, d.scales, d.x, d.y = _ptr(codes), _ptr(scales), _ptr(x), _ptr(y)
+    d.biases = _ptr(biases) if biases is not None else None
     d.K, d.N, d.M = K, N, x.numel() // K
     d.epilogue = EPILOGUES[store["epilogue"]]
     if store.get("aux") is not None:
@@ -136,7 +138,7 @@ def qmv_w8_fused(codes, scales, biases, x, y, store, stream=None, kind="w8"):
         d.y3 = _ptr(store["y3"])
     d.q_rows, d.k_rows = store.get("q_rows", 0), store.get("k_rows", 0)
     fn = {"w8": lib().vpq_affine_qmv_w8g64_bf16_fused, "batch": lib().vpq_affine_qmv_batch_w4g64_bf16_fused,
-          "g32": lib().vpq_affine_qmv_w4g32_bf16_fused}[kind]
+          "g32": lib().vpq_affine_qmv_w4g32_bf16_fused, "q40": lib().vpq_affine_qmv_w4g32_q40_bf16_fused}[kind]
     with torch.cuda.device(x.device):
         check(fn(C.byref(d), _stream(stream)))
     return y
