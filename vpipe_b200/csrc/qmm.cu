@@ -622,9 +622,14 @@ int launch_qmm_2cta_bits(const uint32_t* w, const uint16_t* scales, const uint16
                          int group = 64) {
   int pairs = (num_sms() - reserve_sms) / 2;  // SMs left free run a concurrent collective
   if (pairs < 1) { pairs = 1; }
-  const int tnt = (BITS == 4 && out.swiglu == 0 && group == 64 && out.split0 == 0)
-                      ? pick_tile_width(M, N, pairs - (out.comm_pairs > 0 ? out.comm_pairs : 0))
-                      : 256;
+  const bool two_widths = BITS == 4 && out.swiglu == 0 && group == 64 && out.split0 == 0;
+  int comm_pairs = out.comm_pairs > 0 ? out.comm_pairs : 0;
+  if (comm_pairs > 0 && out.direct_last) {
+    // Column split with at most one tile per pair: every pair sends its own tile, no SM is set aside.
+    const int w = two_widths ? pick_tile_width(M, N, pairs) : 256;
+    if (((M + two_cta::TM - 1) / two_cta::TM) * ((N + w - 1) / w) <= pairs) { comm_pairs = 0; }
+  }
+  const int tnt = two_widths ? pick_tile_width(M, N, pairs - comm_pairs) : 256;
   CUtensorMap map_x, map_w;
   if (int rc = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)K, (uint64_t)M,
                            BK, 128, CU_TENSOR_MAP_SWIZZLE_128B, "x")) {
@@ -657,6 +662,7 @@ int launch_qmm_2cta_bits(const uint32_t* w, const uint16_t* scales, const uint16
   VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   const int tiles = ((M + two_cta::TM - 1) / two_cta::TM) * ((N + tnt - 1) / tnt);
   two_cta::OutSpec spec = out;
+  spec.comm_pairs = comm_pairs;
   int compute = pairs;
   if (spec.comm_pairs > 0) {  // column split: the last pairs of the grid only send
     if (spec.comm_pairs > pairs / 2) { spec.comm_pairs = pairs / 2; }
@@ -751,10 +757,10 @@ int qmm_launch_multi_dest(const uint32_t* w, const void* scales, const void* bia
       return fail(VPQ_ERR_UNSUPPORTED, "qmm (fused split): %lld tiles, the communicator's flag array holds %d", (long long)tiles,
                   sync->tile_flag_count);
     }
-    // Sender pairs: with one peer 12 sender SMs keep up with the GEMM; from three peers on the exchange
-    // is the longer part and more SMs move more (peer stores from 8 / 16 / 24 / 32 SMs: 470 / 537 / 604 /
-    // 613 GB/s measured), so 24.
-    out.comm_pairs = count <= 2 ? 6 : 12;
+    // Sender pairs: 12 SMs with one peer, 16 with more. More do not help (24 or 32 sender SMs gave the
+    // same times for the exchange-bound shapes at 4 GPUs, and cost the others a round of tiles).
+    out.comm_pairs = count <= 2 ? 6 : 8;
+    out.direct_last = 1;
     out.tile_flags = sync->tile_flags;
     out.handshake = sync->my_flags != nullptr;
     out.sync = *sync;

@@ -56,6 +56,8 @@ struct OutSpec {
   int split0, split1;
   int handshake;      // 1: `sync` is valid (column split with the cross-GPU handshake inside the kernel)
   int comm_pairs;     // column split: CTA pairs at the end of the grid that only send (0: nothing is sent)
+  int direct_last;    // column split: a computing pair stores its LAST tile into the peers itself (nothing
+                      // is queued behind that tile on its SMs, and the tail of the exchange runs on all SMs)
   uint32_t* tile_flags;  // column split: per tile, epilogue warps that have stored it locally (zero between calls)
   vpq::PeerSync sync;
 };
@@ -210,7 +212,8 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // Both CTAs of a sender pair work alone: sender CTA c of C takes tiles c, c + C, ... in the
     // order the computing pairs finish them. No barriers of the pipeline, no tensor memory.
     const int C = 2 * out.comm_pairs;
-    const int c = (cluster_id - num_clusters) * 2 + (int)rank;
+    // tiles the senders move: all, or all but the last tile of every computing pair (the last num_clusters)
+    const int send_tiles = out.direct_last ? max(0, num_tiles - num_clusters) : num_tiles;
     __shared__ uint32_t comm_ok;
     if (threadIdx.x == 0) { comm_ok = 1; }
     __syncthreads();
@@ -256,7 +259,7 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
       for (int i = 0; i < kSlots; ++i) { mbar_init(sbar + 8u * i, 1); }
       fence_mbar_init();
       int my_tiles = 0;
-      for (int tile = c; tile < num_tiles; tile += C) { ++my_tiles; }
+      for (int tile = c; tile < send_tiles; tile += C) { ++my_tiles; }
       const int total = my_tiles * kChunksPerTile;
       int loaded = 0, ready_tiles = 0;   // chunks whose load was issued; tiles of this CTA's list known to be complete
       bool ok = comm_ok != 0;
@@ -318,12 +321,14 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
       bulk_wait_all();  // every store of this driver has been performed
       if (!ok) { comm_ok = 0; }
     }
-    // All stores of this CTA are out: the sender CTA that finishes last on this GPU tells every peer
-    // that this rank's column block is complete in the peer's y.
+    // All stores of this CTA are out: the CTA that finishes last on this GPU (of the senders, or of the
+    // whole grid when the computing pairs store their last tiles themselves) tells every peer that this
+    // rank's column block is complete in the peer's y.
     __threadfence_system();
     __syncthreads();
     if (out.handshake && threadIdx.x == 0) {
-      if (atomicAdd(out.sync.warps_done, 1u) == (uint32_t)C - 1u) {
+      const uint32_t parties = out.direct_last ? gridDim.x : (uint32_t)C;
+      if (atomicAdd(out.sync.warps_done, 1u) == parties - 1u) {
         __threadfence_system();
         for (int d = 1; d < out.count; ++d) {
           *reinterpret_cast<volatile uint32_t*>(out.sync.flag_of[d] + 8 + out.sync.rank) = out.sync.epoch;
@@ -554,6 +559,29 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const int n0 = (tile % tiles_n) * TN;
       const int a = ti & 1;
       const uint32_t aph = (ti >> 1) & 1u;
+      // this pair's last tile goes to the peers from here (column split)
+      bool direct = kAct == 0 && out.direct_last != 0 && out.count > 1 && tile + num_clusters >= num_tiles;
+      if (direct && out.handshake) {
+        // no store into a peer's y before that peer's stream has reached this call (bounded wait; by the
+        // last tile the flags have long arrived)
+        bool seen = true;
+        if (lane >= 1 && lane < out.count) {
+          volatile uint32_t* f = out.sync.my_flags + out.sync.src_rank[lane];
+          seen = false;
+          for (uint32_t i = 0; i < (1u << 24); ++i) {
+            if ((int32_t)(*f - out.sync.epoch) >= 0) {
+              seen = true;
+              break;
+            }
+            __nanosleep(100);
+          }
+        }
+        if (!__all_sync(0xffffffffu, seen)) {
+          if (lane == 0) { atomicCAS(&g_qmm_status, 0u, (4u << 8) | kRoleSend); }
+          direct = false;  // this GPU's y is still written; the peers' stay untouched
+        }
+        __threadfence_system();
+      }
       if (!warp_wait(bar_accfull(a), aph, (1u << 8) | kRoleEpi, abort_flag, &g_qmm_status)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(a * TN);
@@ -630,7 +658,7 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
             if (mm < M && col_ok) {
               const int64_t off = (int64_t)mm * out.ld + out.col0 + nc0 + j * 8;
               *reinterpret_cast<uint4*>(out.base[0] + off) = pk;  // this GPU's y; the senders feed the peers
-              if (kAct != 0) {
+              if (kAct != 0 || direct) {
                 for (int d = 1; d < out.count; ++d) { *reinterpret_cast<uint4*>(out.base[d] + off) = pk; }
               }
             }
@@ -662,16 +690,30 @@ affine_qmm_w4g64_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x,
           mbar_arrive_cluster(accempty_leader + 8u * a);
         }
       }
-      if (out.comm_pairs > 0) {  // hand the tile to the sender CTAs: stores first, then the count
+      if (out.comm_pairs > 0 && !direct) {  // hand the tile to the sender CTAs: stores first, then the count
         __threadfence();
         __syncwarp();
         if (lane == 0) { atomicAdd(out.tile_flags + tile, 1u); }
       }
+      if (direct) { __threadfence_system(); }  // this warp's peer stores, before the CTA reports below
     }
   }
 
   tc_fence_before();
   __syncthreads();
+  if (kAct == 0 && out.direct_last != 0 && out.handshake && threadIdx.x == 0) {
+    // this CTA's peer stores are out (fenced by their warps, ordered before this thread by the barrier):
+    // the CTA of the grid that reports last tells every peer that the column block is complete
+    __threadfence_system();
+    if (atomicAdd(out.sync.warps_done, 1u) == gridDim.x - 1u) {
+      __threadfence_system();
+      for (int d = 1; d < out.count; ++d) {
+        *reinterpret_cast<volatile uint32_t*>(out.sync.flag_of[d] + 8 + out.sync.rank) = out.sync.epoch;
+      }
+      *out.sync.warps_done = 0;
+      __threadfence_system();
+    }
+  }
   cluster_sync_all();  // nobody leaves while its partner may still read its shared memory or signal it
   if (warp == 5) {
     tc_fence_after();
