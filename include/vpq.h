@@ -86,7 +86,7 @@ int vpq_scales_f16_to_bf16(const void* src_f16, void* dst_bf16, int64_t n, void*
  * GGUF-repacked checkpoints use: bits 4 or 8, group 64 or 32 (codes u32 [N, K*bits/32], 8-bit
  * codes one byte per value, little-endian in the word; scales / biases [N, K/group]). Bit-exact
  * with kernels affine_quant_w8_g64 / _w4_g64 / _w8_g32 / _w4_g32 and affine_dequant_w4g64 / _w8g64
- * / _w8g32, gpu-kernels/metal/quant/affine_dequant.metal:25-135,243-301; validated as
+ * / _w8g32 / _w4g32, gpu-kernels/metal/quant/affine_dequant.metal:25-135,191-225,243-301; validated as
  * AffineQuantizer::quantize_linear does, generative-models/quantize/affine-quantizer.cc:55-57.
  * Besides w4 g64 the library has a fused GEMV and GEMM for w8 g64 (vpq_affine_qmv_w8g64_bf16,
  * vpq_affine_qmm_w8g64_bf16) and a fused GEMV for w4 g32 (vpq_affine_qmv_w4g32_bf16); the remaining
@@ -96,6 +96,16 @@ int vpq_affine_quant(const void* w_elt, int src_is_bf16, uint32_t* codes, void* 
                      int64_t K, int64_t N, int bits, int group, float clip, void* stream);
 int vpq_affine_dequant_bf16(const uint32_t* w, const void* scales, const void* biases, void* ydeq, int64_t K,
                             int64_t N, int bits, int group, void* stream);
+
+/* 8-bit group-64 weights requantised to 4 bits (the draft copy of a vocabulary matrix that a
+ * speculative head reads at half the bandwidth): per group of 64, v = s8 * q8 + b8 in f32,
+ * s4 = (max v - min v) / 15, b4 = min v, q4 = clamp(round((v - min v) / s4), 0, 15) computed with the
+ * f32 scale, scales and biases then narrowed to bf16. w8 u32 [N, K/4] -> w4 u32 [N, K/8]; s8, b8, s4, b4
+ * bf16 [N, K/64]; slots 0..5 in this order, K and N as constants. Replaces affine_requant_w8_to_w4_g64
+ * (gpu-kernels/metal/quant/affine_dequant.metal:135-189). Division and reciprocal are IEEE-rounded;
+ * the reference's are Metal's, which no test of the reference pins. */
+int vpq_affine_requant_w8_to_w4_g64_bf16(const uint32_t* w8, const void* s8, const void* b8, uint32_t* w4, void* s4,
+                                         void* b4, int64_t K, int64_t N, void* stream);
 
 /* Dequantize to dense bf16 [N,K]: bf16_rne(float(s)*q + float(b)). Bit-exact.
  * Replaces kernel affine_dequant_w4g64 (slots 0:w 1:scales 2:biases 3:ydeq 4:K 5:N),

@@ -111,6 +111,9 @@ def ref():
             d = getattr(R, f"ref_affine_dequant_{sfx}")
             d.restype = C.c_int
             d.argtypes = [C.c_void_p] * 4 + [C.c_int] * 4
+            r = getattr(R, f"ref_affine_requant_w8_to_w4_g64_{sfx}")
+            r.restype = C.c_int
+            r.argtypes = [C.c_void_p] * 6 + [C.c_int] * 2
         _ref = R
     return _ref
 
@@ -192,7 +195,8 @@ def quant(w_elt: np.ndarray, bits: int, group: int, src_is_bf16: bool = True, cl
 
 
 def dequant_bf16_any(codes, s_bf16, b_bf16, bits: int, group: int, use_ref: bool = False) -> np.ndarray:
-    """Dequantizer for any (bits, group); the reference ships w4g64, w8g64 and w8g32 kernels."""
+    """Dequantizer for any (bits, group): affine_dequant_w4g64 / _w8g64 / _w8g32 / _w4g32
+    (gpu-kernels/metal/quant/affine_dequant.metal:25-135,191-225)."""
     codes = _c(codes, np.uint32)
     N, Kw = codes.shape
     K = Kw * 32 // bits
@@ -202,6 +206,42 @@ def dequant_bf16_any(codes, s_bf16, b_bf16, bits: int, group: int, use_ref: bool
     if rc != 0:
         raise ValueError("dequant_bf16_any: bad arguments")
     return out
+
+
+def requant_w8_to_w4_g64(codes8, s8_bf16, b8_bf16, use_ref: bool = False):
+    """affine_requant_w8_to_w4_g64 (gpu-kernels/metal/quant/affine_dequant.metal:135-189), bf16 build:
+    per group of 64, v = s8 * q8 + b8 in f32 (the product of an 8-bit significand and an 8-bit code is
+    exact, so fused or not is the same value), scale = (max - min) / 15, inv = scale > 0 ? 1 / scale : 0,
+    q4 = clamp(round((v - min) * inv), 0, 15) with round() halves away from zero; the stored scale and
+    bias are scale and min narrowed to bf16. Returns (codes4 u32 [N, K/8], s4, b4 bf16 bits [N, K/64])."""
+    codes8 = _c(codes8, np.uint32)
+    N, Kw = codes8.shape
+    K = Kw * 4
+    G = K // 64
+    if use_ref:
+        w4 = np.zeros((N, K // 8), np.uint32)
+        s4 = np.zeros((N, G), np.uint16)
+        b4 = np.zeros((N, G), np.uint16)
+        rc = ref().ref_affine_requant_w8_to_w4_g64_bf16(_p(codes8), _p(_c(s8_bf16, np.uint16)), _p(_c(b8_bf16, np.uint16)),
+                                                        _p(w4), _p(s4), _p(b4), K, N)
+        if rc != 0:
+            raise ValueError("requant_w8_to_w4_g64: bad arguments")
+        return w4, s4, b4
+    q8 = ((codes8[:, :, None] >> (np.arange(4, dtype=np.uint32) * 8)) & np.uint32(0xFF)).reshape(N, G, 64).astype(np.float32)
+    s = bf16_to_f32(s8_bf16).reshape(N, G, 1)
+    b = bf16_to_f32(b8_bf16).reshape(N, G, 1)
+    v = (s * q8 + b).astype(np.float32)           # s * q8 is exact in f32: one rounding, on the add
+    mn = v.min(axis=2, keepdims=True)
+    mx = v.max(axis=2, keepdims=True)
+    scale = ((mx - mn).astype(np.float32) / np.float32(15.0)).astype(np.float32)
+    with np.errstate(divide="ignore"):
+        inv = np.where(scale > 0, np.float32(1.0) / scale, np.float32(0.0)).astype(np.float32)
+    t = ((v - mn).astype(np.float32) * inv).astype(np.float32)
+    q4 = np.clip(np.floor(t.astype(np.float64) + 0.5), 0, 15).astype(np.uint32).reshape(N, K // 8, 8)
+    w4 = np.zeros((N, K // 8), np.uint32)
+    for i in range(8):
+        w4 |= q4[:, :, i] << np.uint32(4 * i)
+    return w4, narrow_f32_bf16(scale.reshape(N, G)), narrow_f32_bf16(mn.reshape(N, G))
 
 
 def dequant_f16_ref(codes, s_f16, b_f16) -> np.ndarray:

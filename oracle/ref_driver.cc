@@ -86,7 +86,7 @@ int REF_FN(ref_affine_quant)(const void* x, uint32_t* w, void* s, void* b, int K
   return 0;
 }
 
-// The reference ships dequantizers for w4g64, w8g64 and w8g32 (no w4g32 one).
+// The reference's dequantizers: w4g64, w8g64, w8g32, w4g32.
 int REF_FN(ref_affine_dequant)(const uint32_t* w, const void* s, const void* b, void* out, int K, int N,
                                int bits, int group) {
   if (N <= 0 || K <= 0 || (K % group) != 0) { return -1; }
@@ -103,9 +103,25 @@ int REF_FN(ref_affine_dequant)(const uint32_t* w, const void* s, const void* b, 
         affine_dequant_w8g64(w, sp, bp, op, K, N, gid);
       } else if (bits == 8 && group == 32) {
         affine_dequant_w8g32(w, sp, bp, op, K, N, gid);
+      } else if (bits == 4 && group == 32) {
+        affine_dequant_w4g32(w, sp, bp, op, K, N, gid);
       } else {
         return -1;
       }
+    }
+  }
+  return 0;
+}
+
+// 8-bit group-64 weights requantised to 4 bits: grid {K/64, N, 1}
+// (gpu-kernels/metal/quant/affine_dequant.metal:143).
+int REF_FN(ref_affine_requant_w8_to_w4_g64)(const uint32_t* w8, const void* s8, const void* b8, uint32_t* w4,
+                                            void* s4, void* b4, int K, int N) {
+  if (N <= 0 || K <= 0 || (K % 64) != 0) { return -1; }
+  for (unsigned n = 0; n < (unsigned)N; ++n) {
+    for (unsigned g = 0; g < (unsigned)(K / 64); ++g) {
+      affine_requant_w8_to_w4_g64(w8, static_cast<const VPIPE_ELT*>(s8), static_cast<const VPIPE_ELT*>(b8), w4,
+                                  static_cast<VPIPE_ELT*>(s4), static_cast<VPIPE_ELT*>(b4), K, N, metal::uint2(g, n));
     }
   }
   return 0;

@@ -69,7 +69,7 @@ def dequant_case(name, N, K, seed):
 
 def twin_case(name, N, K, bits, group, bf16, clip, seed):
     """The other (bits, group) instantiations of the quantizer template and their dequantizers
-    (affine_dequant.metal:60-135, 303-306); the reference has no w4g32 dequant kernel."""
+    (affine_dequant.metal:60-135, 191-225, 303-306)."""
     w = synth.weight_f32(N, K, seed)
     wb = synth.f32_to_bf16_bits(w) if bf16 else w.astype(np.float16).view(np.uint16)
     wb[0, :group] = 0x8000                     # all -0
@@ -78,10 +78,24 @@ def twin_case(name, N, K, bits, group, bf16, clip, seed):
     codes, s, b = oracle.quant(wb, bits, group, bf16, clip, use_ref=True)
     out = {"w_bits": wb, "src_is_bf16": np.array(int(bf16)), "clip": np.array(clip, np.float32),
            "bits": np.array(bits), "group": np.array(group), "codes": codes, "scales_f16": s, "biases_f16": b}
-    if bf16 and (bits, group) != (4, 32):
+    if bf16:
         sb, bb = oracle.f16_to_bf16(s), oracle.f16_to_bf16(b)
         out["scales_bf16"], out["biases_bf16"] = sb, bb
         out["deq_bf16"] = oracle.dequant_bf16_any(codes, sb, bb, bits, group, use_ref=True)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **out)
+    print(name, {k: v.shape for k, v in out.items()})
+
+
+def requant_case(name, N, K, seed):
+    """affine_requant_w8_to_w4_g64 (affine_dequant.metal:135-189) on 8-bit weights the reference's own
+    quantizer produced, with a constant group (scale 0) and an evenly spread one."""
+    w = synth.weight_f32(N, K, seed)
+    w[0, :64] = 0.25
+    w[1, :64] = np.linspace(-1.0, 1.0, 64, dtype=np.float32)
+    codes8, s, b = oracle.quant(synth.f32_to_bf16_bits(w), 8, 64, True, 1.0, use_ref=True)
+    s8, b8 = oracle.f16_to_bf16(s), oracle.f16_to_bf16(b)
+    w4, s4, b4 = oracle.requant_w8_to_w4_g64(codes8, s8, b8, use_ref=True)
+    out = {"codes8": codes8, "scales8_bf16": s8, "biases8_bf16": b8, "codes4": w4, "scales4_bf16": s4, "biases4_bf16": b4}
     np.savez_compressed(os.path.join(HERE, name + ".npz"), **out)
     print(name, {k: v.shape for k, v in out.items()})
 
@@ -99,3 +113,4 @@ if __name__ == "__main__":
     twin_case("twin_w8g32_bf16_n12_k160", 12, 160, 8, 32, True, 0.9, 17)
     twin_case("twin_w4g32_bf16_n12_k160", 12, 160, 4, 32, True, 1.0, 18)
     twin_case("twin_w8g64_f16_n12_k128", 12, 128, 8, 64, False, 1.0, 19)
+    requant_case("requant_w8g64_bf16_n10_k320", 10, 320, 20)

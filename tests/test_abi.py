@@ -52,6 +52,11 @@ def test_function_table_uses_reference_names(vpq):
                            ("affine_qmv_bf16", "affine_qmv_w8g64"),
                            ("affine_qmv_bf16", "affine_qmv_w4g32"),
                            ("affine_qmv_bf16", "affine_qmv_w4g32_add"),
+                           ("affine_qmv_bf16", "affine_qmv_geglu_w8g64"),
+                           ("affine_dequant_bf16", "affine_dequant_w4g32"),
+                           ("affine_dequant_bf16", "affine_requant_w8_to_w4_g64"),
+                           ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64_bm64_rs_acc16"),
+                           ("affine_qmm_steel_bf16", "affine_qmm_steel_w8g64_bm64_acc16"),
                            ("affine_qmv_bf16", "affine_qmv_geglu_w4g32"),
                            ("affine_qmv_bf16", "affine_qmv_gelu_mul_w4g32"),
                            ("affine_qmv_bf16", "affine_qmv_qkv_w4g32"),

@@ -282,3 +282,73 @@ def test_chain_first_layer_against_oracle(vpq, oracle_mod):
     r_dn = oracle_mod.fused_add(
         oracle_mod.linear_f32(host(dn[0]), host(dn[1]), host(dn[2]), host(gu[4]), "f64").astype(np.float32), host(o[4]))
     assert oracle_mod.err_metrics(f32(dn[4]), synth.bf16_bits_to_f32(r_dn))["max_rel_rms"] < TOL
+
+
+def _chain_outputs(problems):
+    return [t for p in problems for t in ([p[4]] + ([p[5]["aux"], p[5]["y3"]] if p[5]["epilogue"] == "qkv" else []))]
+
+
+def _per_launch(ops, problems):
+    for p in problems:
+        plain = dict(p[5])
+        plain.pop("depends", None)
+        ops.qmv_batch(ops.qmv_set([p[:5] + (plain,)]))
+
+
+def test_chain_with_an_input_that_is_no_first_output_and_replayed_from_a_graph(vpq, oracle_mod):
+    """A chained plan in which one GEMV reads the k output of a q|k|v GEMV (not a first output: it
+    waits on the plan's tile counter while the others poll tagged words), run directly, re-created in
+    the same workspace, and replayed from a CUDA graph with the layer input changed between replays.
+    Every run must give the bytes of the same GEMVs launched one by one on that input."""
+    ops = vpq.ops
+    H, KV, F = 1024, 256, 1536
+    L, out = _decoder_layers(vpq, oracle_mod, 2, H, KV, F, 6100)
+    problems = [p for layer in L for p in layer]
+    c, s, b = quantized_linear(oracle_mod, 528, KV, 6177)
+    side_y = torch.zeros((1, 528), dtype=torch.bfloat16, device=dev())
+    side = (to_dev(c), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16), L[0][0][5]["aux"], side_y,
+            {"epilogue": "none", "depends": True})
+    problems.insert(2, side)
+    h0 = L[0][0][3]
+    inputs = [to_dev(synth.activations_bf16(1, H, 6200 + i), torch.bfloat16) for i in range(3)]
+
+    def reference(x):
+        h0.copy_(x)
+        _per_launch(ops, problems)
+        torch.cuda.synchronize()
+        return [t.clone() for t in _chain_outputs(problems)]
+
+    def check(x, run_it, what):
+        want = reference(x)
+        for t in _chain_outputs(problems):
+            t.fill_(7.0)
+        run_it()
+        torch.cuda.synchronize()
+        for i, (g, w) in enumerate(zip(_chain_outputs(problems), want)):
+            assert torch.equal(g, w), f"{what}: output {i} differs"
+
+    plan = ops.QmvPlan(problems)
+    for i in (0, 1, 0):
+        check(inputs[i], plan.run, f"direct run, input {i}")
+    # the same workspace, a plan over a different list first, then this one again
+    ws = plan.workspace
+    plan.close()
+    other = ops.QmvPlan(problems[:5], workspace=ws)
+    other.run()
+    torch.cuda.synchronize()
+    other.close()
+    plan = ops.QmvPlan(problems, workspace=ws)
+    check(inputs[2], plan.run, "plan re-created in its old workspace")
+    side_stream = torch.cuda.Stream()
+    side_stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side_stream):
+        plan.run()
+    torch.cuda.current_stream().wait_stream(side_stream)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        plan.run()
+    for i in (1, 2, 0, 1):
+        check(inputs[i], g.replay, f"graph replay, input {i}")
+    plan.close()
+    assert ops.device_status() == 0

@@ -251,3 +251,52 @@ def test_qmm_group32_twins(vpq, oracle_mod, bits, act, M, K, N):
     y2 = torch.zeros_like(y)
     vpq.ops.dispatch(vpq.ops.function("affine_qmm_steel_bf16", name), [d[0], d[1], d[2], d[3], y2], K=K, N=N, M=M)
     assert torch.equal(y, y2)
+
+
+def test_requant_w8_to_w4_bit_exact(vpq, oracle_mod, golden_dir):
+    """affine_requant_w8_to_w4_g64 (affine_dequant.metal:135-189): the reference-built fixture, then
+    larger random weights against the oracle; codes, scales and biases bit for bit; also by name."""
+    g = dict(np.load(os.path.join(golden_dir, "requant_w8g64_bf16_n10_k320.npz")))
+    cases = [(g["codes8"], g["scales8_bf16"], g["biases8_bf16"], (g["codes4"], g["scales4_bf16"], g["biases4_bf16"]))]
+    for seed, (N, K) in enumerate([(257, 4096), (33, 64), (1000, 1024)]):
+        rng = np.random.default_rng(700 + seed)
+        w = (rng.standard_normal((N, K)) * 0.03).astype(np.float32)
+        w[0, :64] = -0.5
+        codes8, s, b = oracle_mod.quant(synth.f32_to_bf16_bits(w), 8, 64)
+        s8, b8 = oracle_mod.f16_to_bf16(s), oracle_mod.f16_to_bf16(b)
+        if seed == 1:
+            s8[2, 0] ^= 0x8000          # a negative scale: min and max swap roles
+        cases.append((codes8, s8, b8, oracle_mod.requant_w8_to_w4_g64(codes8, s8, b8)))
+    for codes8, s8, b8, want in cases:
+        d = (to_dev(codes8), to_dev(s8, torch.bfloat16), to_dev(b8, torch.bfloat16))
+        c4, s4, b4 = vpq.ops.requant_w8_to_w4(*d)
+        assert np.array_equal(c4.cpu().numpy().view(np.uint32), want[0])
+        assert np.array_equal(bits16(s4), want[1])
+        assert np.array_equal(bits16(b4), want[2])
+        N, K = codes8.shape[0], codes8.shape[1] * 4
+        c4b, s4b, b4b = torch.zeros_like(c4), torch.zeros_like(s4), torch.zeros_like(b4)
+        vpq.ops.dispatch(vpq.ops.function("affine_dequant_bf16", "affine_requant_w8_to_w4_g64"),
+                         [d[0], d[1], d[2], c4b, s4b, b4b], K=K, N=N)
+        assert torch.equal(c4b, c4) and torch.equal(s4b, s4) and torch.equal(b4b, b4)
+
+
+def test_dequant_w4g32_and_geglu_w8_by_name(vpq, oracle_mod, golden_dir):
+    """affine_dequant_w4g32 (affine_dequant.metal:191-225) on the reference-built fixture; and
+    affine_qmv_geglu_w8g64 by name against the descriptor call."""
+    g = dict(np.load(os.path.join(golden_dir, "twin_w4g32_bf16_n12_k160.npz")))
+    d = (to_dev(g["codes"]), to_dev(g["scales_bf16"], torch.bfloat16), to_dev(g["biases_bf16"], torch.bfloat16))
+    N, K = g["codes"].shape[0], g["codes"].shape[1] * 8
+    out = torch.zeros((N, K), dtype=torch.bfloat16, device=dev())
+    vpq.ops.dispatch(vpq.ops.function("affine_dequant_bf16", "affine_dequant_w4g32"), [d[0], d[1], d[2], out], K=K, N=N)
+    assert np.array_equal(bits16(out), g["deq_bf16"])
+    K, N, M = 1024, 96, 2
+    wb = synth.f32_to_bf16_bits(synth.weight_f32(N, K, 7301))
+    codes, s16, b16 = oracle_mod.quant(wb, 8, 64)
+    x = synth.activations_bf16(M, K, 7302)
+    d = (to_dev(codes), to_dev(oracle_mod.f16_to_bf16(s16), torch.bfloat16),
+         to_dev(oracle_mod.f16_to_bf16(b16), torch.bfloat16), to_dev(x, torch.bfloat16))
+    want = vpq.ops.qmv_w8_fused(*d, torch.zeros((M, N // 2), dtype=torch.bfloat16, device=dev()), {"epilogue": "geglu"})
+    got = torch.zeros_like(want)
+    vpq.ops.dispatch(vpq.ops.function("affine_qmv_bf16", "affine_qmv_geglu_w8g64"), {0: d[0], 1: d[1], 2: d[2], 3: d[3], 4: got},
+                     K=K, N=N, M=M)
+    assert torch.equal(got, want) and float(got.float().abs().max()) > 0

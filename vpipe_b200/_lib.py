@@ -26,6 +26,7 @@ SYMBOLS = [
     ("vpq_affine_qmv_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     ("vpq_affine_quant", _i, [_vp, _i, _vp, _vp, _vp, _i64, _i64, _i, _i, C.c_float, _vp]),
     ("vpq_affine_dequant_bf16", _i, [_vp, _vp, _vp, _vp, _i64, _i64, _i, _i, _vp]),
+    ("vpq_affine_requant_w8_to_w4_g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp]),
     ("vpq_affine_qmm_swiglu_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     ("vpq_affine_qmm_swiglu_bf16_rs", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i, _i64, _i64, _vp]),
     ("vpq_qmm_grouped_tile_rows", _i, []),

@@ -192,7 +192,7 @@ extern "C" size_t vpq_scale_bytes(int N, int K, int group) {
 struct vpq_function_s {
   const char* library;
   const char* entry;
-  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64, 66..69 qmv w8g64 add / swiglu / qkv / gelu*mul, 70 / 71 qmm swiglu strided store w4 / w8, 72..74 grouped qmm down / swiglu / geglu, 75 qmv norm + qkv, 76..78 gathered expert qmv swiglu / geglu / down, 79..81 qmm w4g32 / geglu w4g32 / w8g32, 82..85 qmv w4g32 add / geglu / gelu*mul / qkv, 86..88 scale-only (Q4_0) qmv w4g32 plain / add / geglu; 10 + code: quant / dequant twins (see fmt_*)
+  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64, 66..69 qmv w8g64 add / swiglu / qkv / gelu*mul, 70 / 71 qmm swiglu strided store w4 / w8, 72..74 grouped qmm down / swiglu / geglu, 75 qmv norm + qkv, 76..78 gathered expert qmv swiglu / geglu / down, 79..81 qmm w4g32 / geglu w4g32 / w8g32, 82..85 qmv w4g32 add / geglu / gelu*mul / qkv, 86..88 scale-only (Q4_0) qmv w4g32 plain / add / geglu, 89 requant w8 -> w4, 90 qmv geglu w8g64; 10 + code: quant / dequant twins (see fmt_*)
 };
 
 // The reference selects the element type with the library-name suffix and
@@ -215,6 +215,7 @@ static const vpq_function_s g_functions[] = {
     {"affine_qmv_bf16", "affine_qmv_swiglu_w8g64", 67},
     {"affine_qmv_bf16", "affine_qmv_qkv_w8g64", 68},
     {"affine_qmv_bf16", "affine_qmv_gelu_mul_w8g64", 69},
+    {"affine_qmv_bf16", "affine_qmv_geglu_w8g64", 90},
     {"affine_qmv_bf16", "affine_qmv_w4g32", 60},
     {"affine_qmv_bf16", "affine_qmv_w4g32_add", 82},
     {"affine_qmv_bf16", "affine_qmv_geglu_w4g32", 83},
@@ -228,6 +229,15 @@ static const vpq_function_s g_functions[] = {
     {"affine_qmm_steel_bf16", "affine_qmm_steel_w4g64", 1},
     {"affine_qmm_steel_bf16", "affine_qmm_steel_w4g64_bm64", 1},
     {"affine_qmm_steel_bf16", "affine_qmm_steel_w4g64_bm128", 1},
+    // the reference's half-precision-accumulate tuning twins: served by the same kernels, which accumulate in f32
+    {"affine_qmm_steel_bf16", "affine_qmm_steel_w4g64_bm64_acc16", 1},
+    {"affine_qmm_steel_bf16", "affine_qmm_steel_w8g64_bm64_acc16", 59},
+    {"affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64_acc16", 8},
+    {"affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64_bm64_acc16", 8},
+    {"affine_qmm_steel_bf16", "affine_qmm_swiglu_w8g64_acc16", 64},
+    {"affine_qmm_steel_bf16", "affine_qmm_swiglu_w8g64_bm64_acc16", 64},
+    {"affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64_bm64_rs_acc16", 70},
+    {"affine_qmm_steel_bf16", "affine_qmm_swiglu_w8g64_bm64_rs_acc16", 71},
     {"affine_qmm_mma_bf16", "affine_qmm_mma_w4g64", 1},
     {"affine_qmm_steel_bf16", "affine_qmm_steel_w8g64", 59},
     {"affine_qmm_steel_bf16", "affine_qmm_steel_w8g64_bm64", 59},
@@ -254,6 +264,8 @@ static const vpq_function_s g_functions[] = {
     // the format twins: kind = 10 + 16 * (quant ? 1 + bf16 source : 0) + 4 * (bits == 8) + (group == 32)
     {"affine_dequant_bf16", "affine_dequant_w8g64", 10 + 4},
     {"affine_dequant_bf16", "affine_dequant_w8g32", 10 + 4 + 1},
+    {"affine_dequant_bf16", "affine_dequant_w4g32", 10 + 1},
+    {"affine_dequant_bf16", "affine_requant_w8_to_w4_g64", 89},
     {"affine_dequant_bf16", "affine_quant_w8_g64", 10 + 32 + 4},
     {"affine_dequant_bf16", "affine_quant_w8_g32", 10 + 32 + 4 + 1},
     {"affine_dequant_bf16", "affine_quant_w4_g32", 10 + 32 + 1},
@@ -407,10 +419,15 @@ extern "C" int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* a, 
       }
       return k >= 86 ? vpq_affine_qmv_w4g32_q40_bf16_fused(&d, stream) : vpq_affine_qmv_w4g32_bf16_fused(&d, stream);
     }
+    case 89:
+      return vpq_affine_requant_w8_to_w4_g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2],
+                                                  static_cast<uint32_t*>(const_cast<void*>(b[3])), const_cast<void*>(b[4]),
+                                                  const_cast<void*>(b[5]), a->K, a->N, stream);
     case 66:
     case 67:
     case 68:
-    case 69: {
+    case 69:
+    case 90: {
       vpq_linear_desc d;
       std::memset(&d, 0, sizeof(d));
       d.w = static_cast<const uint32_t*>(b[0]);
@@ -428,8 +445,11 @@ extern "C" int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* a, 
         d.k_rows = a->k_rows;
         d.N = a->q_rows + a->k_rows + a->v_rows;
       } else {
-        d.epilogue = fn->kind == 66 ? VPQ_EPILOGUE_ADD : fn->kind == 67 ? VPQ_EPILOGUE_SWIGLU : VPQ_EPILOGUE_GELU_MUL;
-        d.aux = fn->kind == 67 ? nullptr : b[7];
+        d.epilogue = fn->kind == 66   ? VPQ_EPILOGUE_ADD
+                     : fn->kind == 67 ? VPQ_EPILOGUE_SWIGLU
+                     : fn->kind == 90 ? VPQ_EPILOGUE_GEGLU
+                                      : VPQ_EPILOGUE_GELU_MUL;
+        d.aux = (fn->kind == 67 || fn->kind == 90) ? nullptr : b[7];
         d.N = a->N;
       }
       return vpq_affine_qmv_w8g64_bf16_fused(&d, stream);

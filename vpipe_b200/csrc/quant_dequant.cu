@@ -96,9 +96,8 @@ affine_quant_kernel(const uint16_t* __restrict__ x, uint32_t* __restrict__ w,
 // -------------------------------------------------------------- dequantize
 // One thread expands 8 values (one packed word at 4 bits, two at 8) into 8 bf16 (one 16-byte
 // store): fully coalesced reads and writes. Replaces affine_dequant_w4g64, _w8g64 and _w8g32
-// (gpu-kernels/metal/quant/affine_dequant.metal:25-58, 69-98, 107-135); the w4g32 form has no
-// kernel in the reference (its group-32 models dequantise inside the GEMV) but follows from the
-// same expression.
+// and affine_dequant_w4g32 (gpu-kernels/metal/quant/affine_dequant.metal:25-58, 69-98, 107-135,
+// 191-225).
 template <int BITS, int GROUP>
 __global__ void __launch_bounds__(256)
 affine_dequant_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ scales,
@@ -130,6 +129,66 @@ affine_dequant_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict
       o[i] = lo | (hi << 16);
     }
     ydeq[oct] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// ---------------------------------------------------------------- requantize 8 -> 4 bits
+// Replaces affine_requant_w8_to_w4_g64 (gpu-kernels/metal/quant/affine_dequant.metal:135-189): per
+// group of 64, v = s8 * q8 + b8 in f32, scale4 = (max v - min v) / 15, bias4 = min v,
+// q4 = clamp(round((v - min) * (1 / scale4)), 0, 15) with the UNROUNDED f32 scale (the stored scale and
+// bias are narrowed to the element type afterwards) and round() to nearest, halves away from zero.
+// The reference runs one thread per group; here eight lanes share a group (8 values = one 8-byte
+// load and one packed output word each, min / max by shuffles), so a warp reads 256 and writes 128
+// contiguous bytes. Division and reciprocal are IEEE-rounded here; Metal does not promise that for
+// its own, and the reference has no test that pins them.
+__global__ void __launch_bounds__(256)
+affine_requant_w8_to_w4_g64_kernel(const uint2* __restrict__ w8, const uint16_t* __restrict__ s8,
+                                   const uint16_t* __restrict__ b8, uint32_t* __restrict__ w4,
+                                   uint16_t* __restrict__ s4, uint16_t* __restrict__ b4, int64_t total_octets) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t first = (int64_t)blockIdx.x * blockDim.x + (threadIdx.x & ~31);  // the warp's first octet
+  for (int64_t base = first; base < total_octets; base += stride) {
+    const int64_t oct = base + (threadIdx.x & 31);
+    const bool live = oct < total_octets;   // whole groups of 8 lanes are live or not
+    const int64_t g = oct >> 3;
+    float v[8];
+    float mn = INFINITY, mx = -INFINITY;
+    if (live) {
+      const float s = bf16_bits_to_f32(__ldg(s8 + g));
+      const float b = bf16_bits_to_f32(__ldg(b8 + g));
+      const uint2 packed = __ldg(w8 + oct);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        v[i] = dequant_f32(s, (packed.x >> (8 * i)) & 0xffu, b);
+        v[4 + i] = dequant_f32(s, (packed.y >> (8 * i)) & 0xffu, b);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        mn = fminf(mn, v[i]);
+        mx = fmaxf(mx, v[i]);
+      }
+    }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+      mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    if (live) {
+      const float scale = __fdiv_rn(__fsub_rn(mx, mn), 15.0f);
+      const float inv = scale > 0.0f ? __fdiv_rn(1.0f, scale) : 0.0f;
+      uint32_t out = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        int q = (int)roundf(__fmul_rn(__fsub_rn(v[i], mn), inv));
+        q = min(max(q, 0), 15);
+        out |= (uint32_t)q << (4 * i);
+      }
+      w4[oct] = out;
+      if ((oct & 7) == 0) {
+        s4[g] = (uint16_t)f32_to_bf16_bits(scale);
+        b4[g] = (uint16_t)f32_to_bf16_bits(mn);
+      }
+    }
   }
 }
 
@@ -257,6 +316,25 @@ extern "C" int vpq_affine_dequant_w4g64_bf16(const uint32_t* w, const void* scal
                                              const void* biases, void* ydeq, int64_t K, int64_t N,
                                              void* stream) {
   return vpq_affine_dequant_bf16(w, scales, biases, ydeq, K, N, 4, 64, stream);
+}
+
+extern "C" int vpq_affine_requant_w8_to_w4_g64_bf16(const uint32_t* w8, const void* s8, const void* b8, uint32_t* w4,
+                                                    void* s4, void* b4, int64_t K, int64_t N, void* stream) {
+  clear_error();
+  if (!w8 || !s8 || !b8 || !w4 || !s4 || !b4) { return fail(VPQ_ERR_INVALID_ARG, "affine_requant_w8_to_w4_g64: null pointer"); }
+  if (N <= 0 || K <= 0 || (K % 64) != 0) { return fail(VPQ_ERR_INVALID_ARG, "affine_requant_w8_to_w4_g64: need N>0, K>0, K%%64==0"); }
+  if ((reinterpret_cast<uintptr_t>(w8) & 7) || (reinterpret_cast<uintptr_t>(w4) & 3) ||
+      (reinterpret_cast<uintptr_t>(s8) & 1) || (reinterpret_cast<uintptr_t>(b8) & 1) ||
+      (reinterpret_cast<uintptr_t>(s4) & 1) || (reinterpret_cast<uintptr_t>(b4) & 1)) {
+    return fail(VPQ_ERR_ALIGNMENT, "affine_requant_w8_to_w4_g64: w8 must be 8-byte aligned, w4 4-byte, scales and biases 2-byte");
+  }
+  if (int rc = require_sm100()) { return rc; }
+  const int64_t octets = N * (K / 8);
+  affine_requant_w8_to_w4_g64_kernel<<<stream_grid(octets, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint2*>(w8), static_cast<const uint16_t*>(s8), static_cast<const uint16_t*>(b8), w4,
+      static_cast<uint16_t*>(s4), static_cast<uint16_t*>(b4), octets);
+  VPQ_LAUNCH_OK("affine_requant_w8_to_w4_g64");
+  return VPQ_OK;
 }
 
 extern "C" int vpq_scales_f16_to_bf16(const void* src_f16, void* dst_bf16, int64_t n, void* stream) {

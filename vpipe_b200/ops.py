@@ -57,6 +57,21 @@ def dequantize_any(codes, scales, biases, bits: int, group: int, out=None, strea
     return out
 
 
+def requant_w8_to_w4(codes8, scales8, biases8, stream=None):
+    """8-bit group-64 weights -> (codes int32 [N, K/8], scales bf16, biases bf16 [N, K/64]) at 4 bits
+    (vpq_affine_requant_w8_to_w4_g64_bf16)."""
+    N, Kw = codes8.shape
+    K = Kw * 4
+    dev = codes8.device
+    codes4 = torch.empty((N, K // 8), dtype=torch.int32, device=dev)
+    s4 = torch.empty((N, K // 64), dtype=torch.bfloat16, device=dev)
+    b4 = torch.empty((N, K // 64), dtype=torch.bfloat16, device=dev)
+    with torch.cuda.device(dev):
+        check(lib().vpq_affine_requant_w8_to_w4_g64_bf16(_ptr(codes8), _ptr(scales8), _ptr(biases8), _ptr(codes4),
+                                                         _ptr(s4), _ptr(b4), K, N, _stream(stream)))
+    return codes4, s4, b4
+
+
 def narrow_f32_bf16(w: torch.Tensor, stream=None) -> torch.Tensor:
     out = torch.empty(w.shape, dtype=torch.bfloat16, device=w.device)
     with torch.cuda.device(w.device):
@@ -266,15 +281,17 @@ def qmv_set_noalloc(descs, stream=None) -> None:
 class QmvPlan:
     """A list of independent GEMVs run as one launch (vpq_qmv_plan_*). Holds the device workspace."""
 
-    def __init__(self, problems, stream=None):
+    def __init__(self, problems, stream=None, workspace=None):
         self.descs = qmv_set(problems)
         self._keep = problems            # the plan captures pointers: keep the tensors alive
         dev = problems[0][0].device
         n = lib().vpq_qmv_plan_bytes(self.descs, len(self.descs))
-        self.workspace = torch.empty(n, dtype=torch.uint8, device=dev)
+        if workspace is not None and workspace.numel() < n:
+            raise ValueError(f"QmvPlan: workspace of {workspace.numel()} bytes, {n} needed")
+        self.workspace = workspace if workspace is not None else torch.empty(n, dtype=torch.uint8, device=dev)
         self.handle = C.c_void_p()
         with torch.cuda.device(dev):
-            check(lib().vpq_qmv_plan_create(self.descs, len(self.descs), self.workspace.data_ptr(), n,
+            check(lib().vpq_qmv_plan_create(self.descs, len(self.descs), self.workspace.data_ptr(), self.workspace.numel(),
                                             _stream(stream), C.byref(self.handle)))
 
     def run(self, stream=None) -> None:
