@@ -477,12 +477,12 @@ int vpq_affine_qmm_w4g64_bf16_nsplit(vpq_comm* comm,
  * (CUDA IPC, one process per GPU). Each rank's GEMM stores its column block into its own row-major
  * y[M, N]; a few CTAs of the same kernel compute nothing and instead copy every finished tile on to
  * the peers' y over NVLink (TMA load from the local y, TMA stores to the peers) while the tensor
- * cores of the other SMs work on the next tiles. The handshake between the ranks runs inside the
- * kernel as well:
- *   started  - the kernel announces its start to every peer, and its sender CTAs hold their first
- *              store into a peer's y until that peer has announced its own start, i.e. until
+ * cores of the other SMs work on the next tiles; the last tile of every computing CTA pair goes to
+ * the peers straight from its epilogue. The handshake between the ranks runs inside the kernel as well:
+ *   started  - the kernel announces its start to every peer, and nothing is stored into a peer's y
+ *              until that peer has announced its own start, i.e. until
  *              whatever the peer enqueued earlier to read y (the previous step's result) is done;
- *   finished - the sender CTA that finishes last on a GPU announces it to every peer, and a small
+ *   finished - the CTA whose peer stores complete last on a GPU announces it to every peer, and a small
  *              kernel behind the GEMM on the stream waits for all peers' announcements, so that
  *              later work on the stream finds every column block in y.
  * Ordering is therefore by stream order alone: enqueue the consumers of y after the call and the

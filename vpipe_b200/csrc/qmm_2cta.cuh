@@ -14,10 +14,12 @@
 // Column split over several GPUs: the last `comm_pairs` CTA pairs of the grid compute nothing. They
 // are SENDER CTAs: the computing pairs store every tile into this GPU's y and count it in a flag
 // array; a sender CTA waits for its next tile's count, reads the tile back (from L2) and stores it
-// into every peer's y with ordinary stores over NVLink. Keeping the peer stores on SMs of their
+// into every peer's y with the TMA unit over NVLink. Keeping the peer stores on SMs of their
 // own matters: a store that waits for link credit holds up everything behind it on its SM's way to
 // the memory system. Issued from the computing SMs (first from the epilogue warps, then from two
-// extra warps per CTA) the exchange did not overlap the GEMM, it added to it.
+// extra warps per CTA) the exchange did not overlap the GEMM, it added to it. The exception is a
+// pair's LAST tile (direct_last): nothing follows it on those SMs, so its epilogue warps store it
+// into the peers themselves, and the end of the exchange runs on every SM instead of the senders'.
 //
 // Two tile widths: 256 x 256 (TNT = 256: 128 W rows per CTA, two dequant groups of four warps) and
 // 256 x 128 (TNT = 128: 64 W rows per CTA, four groups of two warps), the narrow one for shapes
