@@ -27,7 +27,7 @@ check of the gathered result against the unsharded kernel (the run exits non-zer
 Inputs are synthetic: weights N(0, 0.02) quantised with the reference recipe on the device,
 activations N(0, 1) bf16; seeded. The small workloads at the end of the list (plan LAYERS,
 decode_chain LAYERS, qmm M K N, qmm_swiglu M K N, qmm_w8 M K N, qmv K N, qmv_w8 K N,
-qmv_batch K N M, moe T E TOPK HIDDEN FFN) run one kernel on a small case and print one JSON line;
+qmv_batch K N M, moe T E TOPK HIDDEN FFN, streams [N K COPIES]) run one kernel on a small case and print one JSON line;
 they are what the ncu summaries under profiles/ were taken from.
 """
 from __future__ import annotations
@@ -809,10 +809,45 @@ def small_case(torch, ops, synth, dev, pk, kind, a):
         padded = 2.0 * npad * (H * 2 * F + F * H)
         return {"case": kind, "tokens": T, "experts": E, "top_k": top_k, "hidden": H, "ffn": F, "rows_padded": npad,
                 "ms": t * 1e3, "tflops_useful": useful / t / 1e12, "tflops_padded": padded / t / 1e12}
+    if kind == "streams":
+        # the HBM-bound streams of the path: quantizer, dequantizer, requantizer, conversions, on an
+        # [N, K] weight (default 12288 x 4096 x 8 copies: every pass moves more than L2 holds)
+        N, K = (int(a[0]), int(a[1])) if len(a) >= 2 else (12288, 4096)
+        copies = int(a[2]) if len(a) > 2 else 8
+        reps = 5
+        w = [(torch.randn((N, K), device=dev) * 0.02).to(torch.bfloat16) for _ in range(copies)]
+        out = {"case": "streams", "N": N, "K": K, "copies": copies, "hbm_peak_GBs": pk["hbm_gbs"]}
+
+        def rate(name, fn, nbytes):
+            g = graph_of(torch, fn)   # the calls allocate their outputs: replayed from a graph, the timing is the kernels'
+            t = tm(g.replay, reps)
+            out[name] = {"us": t * 1e6 / copies, "GBs": nbytes * copies / t / 1e9,
+                         "frac_of_hbm_peak": nbytes * copies / t / 1e9 / pk["hbm_gbs"]}
+
+        q4 = [ops.quantize(t) for t in w]
+        q8 = [ops.quantize(t, bits=8) for t in w]
+        G = K // 64
+        rate("quant_w4_g64", lambda: [ops.quantize(t) for t in w], N * K * 2 + N * K // 2 + 4 * N * G)
+        rate("quant_w8_g64", lambda: [ops.quantize(t, bits=8) for t in w], N * K * 2 + N * K + 4 * N * G)
+        sb4 = [(c, ops.scales_to_bf16(s_), ops.scales_to_bf16(b_)) for c, s_, b_ in q4]
+        sb8 = [(c, ops.scales_to_bf16(s_), ops.scales_to_bf16(b_)) for c, s_, b_ in q8]
+        dense = torch.empty((N, K), dtype=torch.bfloat16, device=dev)
+        rate("dequant_w4g64", lambda: [ops.dequantize(*t, out=dense) for t in sb4], N * K // 2 + 4 * N * G + N * K * 2)
+        rate("dequant_w8g64", lambda: [ops.dequantize_any(*t, 8, 64, out=dense) for t in sb8],
+             N * K + 4 * N * G + N * K * 2)
+        rate("requant_w8_to_w4_g64", lambda: [ops.requant_w8_to_w4(*t) for t in sb8],
+             N * K + 4 * N * G + N * K // 2 + 4 * N * G)
+        # what the memory system gives torch's own fill and copy kernels on the same sizes (a write-only and a
+        # read + write stream), for scale next to the copy rate in MEASURED_PEAKS.json
+        rate("torch_fill_bf16", lambda: [dense.fill_(1.0) for _ in range(copies)], N * K * 2)
+        rate("torch_copy_bf16", lambda: [dense.copy_(t) for t in w], N * K * 4)
+        f32 = [t.float() for t in w[:max(1, copies // 2)]]
+        rate("narrow_f32_bf16", lambda: [ops.narrow_f32_bf16(t) for _ in range(copies // len(f32)) for t in f32], N * K * 6)
+        return out
     raise SystemExit(__doc__)
 
 
-SMALL = ("plan", "decode_chain", "qmv", "qmv_w8", "qmv_batch", "qmm", "qmm_swiglu", "qmm_w8", "moe")
+SMALL = ("plan", "decode_chain", "qmv", "qmv_w8", "qmv_batch", "qmm", "qmm_swiglu", "qmm_w8", "moe", "streams")
 
 
 def main():

@@ -104,7 +104,9 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
 // in f32 (8-bit x 4-bit significands), one f32 rounding on the add, then RNE
 // to bf16 (gpu-kernels/metal/quant/affine_dequant.metal:49-52).
 __device__ __forceinline__ float dequant_f32(float s, uint32_t q, float b) {
-  return __fmaf_rn(s, (float)q, b);
+  // (float)q without the conversion unit: q < 2^23 sits in the mantissa of 2^23 + q, exactly
+  const float qf = __fsub_rn(__uint_as_float(0x4B000000u | q), 8388608.0f);
+  return __fmaf_rn(s, qf, b);
 }
 
 // gelu_pytorch_tanh: 0.5 x (1 + tanh(sqrt(2 / pi) (x + 0.044715 x^3))), the activation of the
