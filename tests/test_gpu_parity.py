@@ -90,6 +90,11 @@ def test_narrow_and_scale_conversion_bit_exact(vpq, oracle_mod):
          10.0 ** np.random.default_rng(4).integers(-8, 8, 1 << 20)).astype(np.float32)
     got = vpq.ops.narrow_f32_bf16(torch.from_numpy(f).to(dev()))
     assert np.array_equal(bits16(got), oracle_mod.narrow_f32_bf16(f))
+    # lengths that are no multiple of the kernel's 8-value step, and a source that is not 16-byte aligned
+    fd = torch.from_numpy(f).to(dev())
+    for n, off in ((1, 0), (7, 0), (8, 0), (4099, 0), (4099, 1), (65537, 3)):
+        got = vpq.ops.narrow_f32_bf16(fd[off:off + n])
+        assert np.array_equal(bits16(got), oracle_mod.narrow_f32_bf16(f[off:off + n])), (n, off)
     h = np.arange(65536, dtype=np.uint16)
     h = h[np.isfinite(h.view(np.float16))]
     got = vpq.ops.scales_to_bf16(to_dev(h, torch.float16))

@@ -50,7 +50,6 @@ namespace {
 constexpr int kConsWarps = 8;
 constexpr int kConsThreads = kConsWarps * 32;
 constexpr int kThreads = kConsThreads + 32;  // + producer warp
-constexpr int kTileK = 128;                  // k per MMA unit: 64 bytes of a row, two groups
 constexpr int kBoxBytes = 16 * 128;          // one TMA box: 16 rows x 128 bytes (256 k)
 constexpr int kBoxesPerStage = 8;            // a stage spans 2048 k
 constexpr int kStageW = kBoxesPerStage * kBoxBytes;  // 16 KB of nibbles
