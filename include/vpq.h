@@ -229,7 +229,10 @@ int vpq_affine_qmv_w4g64_bf16_batch(const vpq_linear_desc* descs_host, int count
 /* The 8-bit GEMV with a fused store: one descriptor (w u32 [N, K/4]), any VPQ_EPILOGUE_*. Replaces
  * affine_qmv_w8g64_add, affine_qmv_swiglu_w8g64, affine_qmv_qkv_w8g64 and affine_qmv_gelu_mul_w8g64
  * (the 8-bit instantiations of the kernels cited above, gpu-kernels/metal/quant/affine_qmv.metal:
- * 540-560,789-805,3122-3160). */
+ * 540-560,789-805,3122-3160), affine_qmv_geglu_w8g64, and, with expert / experts / x_div set as for the
+ * 4-bit GEMV (w then holds the experts' slabs, u32 [experts * N, K/4]), the 8-bit expert-gather GEMVs
+ * affine_gather_qmv_swiglu_w8g64, affine_gather_qmv_geglu_w8g64 and affine_gather_down_qmv_w8g64
+ * (affine_qmv.metal:957-994,1290-1322,1519-1548). norm_w and depends are not taken. */
 int vpq_affine_qmv_w8g64_bf16_fused(const vpq_linear_desc* desc_host, void* stream);
 
 /* The small-batch GEMV (w4 g64, rows of x share one stream of the weights) and the group-32 GEMV with

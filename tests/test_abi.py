@@ -53,6 +53,9 @@ def test_function_table_uses_reference_names(vpq):
                            ("affine_qmv_bf16", "affine_qmv_w4g32"),
                            ("affine_qmv_bf16", "affine_qmv_w4g32_add"),
                            ("affine_qmv_bf16", "affine_qmv_geglu_w8g64"),
+                           ("affine_qmv_bf16", "affine_gather_qmv_swiglu_w8g64"),
+                           ("affine_qmv_bf16", "affine_gather_qmv_geglu_w8g64"),
+                           ("affine_qmv_bf16", "affine_gather_down_qmv_w8g64"),
                            ("affine_dequant_bf16", "affine_dequant_w4g32"),
                            ("affine_dequant_bf16", "affine_requant_w8_to_w4_g64"),
                            ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64_bm64_rs_acc16"),
@@ -200,9 +203,12 @@ def test_descriptor_extensions_are_validated_on_the_host(vpq):
     d.norm_w = 0
     d.expert, d.experts = 0x7000, 0    # an expert gather needs the number of slabs
     assert L.vpq_affine_qmv_w4g64_bf16_batch(C.byref(d), 1, None) == 1
+    assert L.vpq_affine_qmv_w8g64_bf16_fused(C.byref(d), None) == 1     # the 8-bit kernel takes the gather too
     d.experts = 4
-    assert L.vpq_affine_qmv_w8g64_bf16_fused(C.byref(d), None) == 3     # the 8-bit kernel takes plain descriptors only
-    assert L.vpq_affine_qmv_batch_w4g64_bf16_fused(C.byref(d), None) == 3
+    assert L.vpq_affine_qmv_batch_w4g64_bf16_fused(C.byref(d), None) == 3   # the small-batch kernel does not
+    d.expert, d.experts = 0, 0
+    d.norm_w = 0x6000
+    assert L.vpq_affine_qmv_w8g64_bf16_fused(C.byref(d), None) == 3     # ... but not the RMSNorm prologue
 
 
 def test_qkv_gemm_and_format_gemm_validate_their_arguments(vpq):

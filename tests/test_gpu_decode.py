@@ -352,3 +352,50 @@ def test_chain_with_an_input_that_is_no_first_output_and_replayed_from_a_graph(v
         check(inputs[i], g.replay, f"graph replay, input {i}")
     plan.close()
     assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("act", ["swiglu", "geglu"])
+def test_moe_gather_gemvs_over_8_bit_experts(vpq, oracle_mod, act):
+    """affine_gather_qmv_swiglu_w8g64 / _geglu_w8g64 / affine_gather_down_qmv_w8g64
+    (affine_qmv.metal:957-994,1290-1322,1519-1548), by the reference's names and slots: every pair
+    bit-identical to this library's plain 8-bit GEMV on the routed expert's slab (the reference's
+    gathered kernels are token-exact with its plain ones) and within tolerance of the fp32 oracle."""
+    from test_gpu_formats import _w8_reference
+    ops = vpq.ops
+    E, H, F, T, top_k = 5, 1024, 320, 2, 2
+    def experts(N, K, seed):
+        cs, ss, bs = [], [], []
+        for e in range(E):
+            wb = synth.f32_to_bf16_bits(synth.weight_f32(N, K, seed + e))
+            c, s16, b16 = oracle_mod.quant(wb, 8, 64)
+            cs.append(c), ss.append(oracle_mod.f16_to_bf16(s16)), bs.append(oracle_mod.f16_to_bf16(b16))
+        return np.stack(cs), np.stack(ss), np.stack(bs)
+    gu, dn = experts(2 * F, H, 3500), experts(H, F, 3600)
+    xb = synth.activations_bf16(T, H, 3700)
+    eid = np.array([3, 0, 4, 4], np.int32)
+    npair = T * top_k
+    d_gu = [to_dev(gu[0]), to_dev(gu[1], torch.bfloat16), to_dev(gu[2], torch.bfloat16)]
+    d_dn = [to_dev(dn[0]), to_dev(dn[1], torch.bfloat16), to_dev(dn[2], torch.bfloat16)]
+    dx, deid = to_dev(xb, torch.bfloat16), torch.from_numpy(eid).to(dev())
+    a = torch.full((npair, F), float("nan"), dtype=torch.bfloat16, device=dev())
+    part = torch.full((npair, H), float("nan"), dtype=torch.bfloat16, device=dev())
+    ops.dispatch(ops.function("affine_qmv_bf16", f"affine_gather_qmv_{act}_w8g64"),
+                 {0: d_gu[0], 1: d_gu[1], 2: d_gu[2], 3: dx, 4: a, 7: deid}, K=H, N=2 * F, M=npair, experts=E, top_k=top_k)
+    ops.dispatch(ops.function("affine_qmv_bf16", "affine_gather_down_qmv_w8g64"),
+                 {0: d_dn[0], 1: d_dn[1], 2: d_dn[2], 3: a, 4: part, 7: deid}, K=F, N=H, M=npair, experts=E)
+    torch.cuda.synchronize()
+    assert not torch.isnan(a.float()).any() and not torch.isnan(part.float()).any()
+    fuse = oracle_mod.fused_swiglu if act == "swiglu" else oracle_mod.fused_geglu
+    for p in range(npair):
+        e, t = int(eid[p]), p // top_k
+        plain_a = ops.qmv_w8_fused(d_gu[0][e], d_gu[1][e], d_gu[2][e], dx[t:t + 1],
+                                   torch.zeros((1, F), dtype=torch.bfloat16, device=dev()), {"epilogue": act})
+        assert torch.equal(plain_a, a[p:p + 1]), p
+        ref_a = fuse(_w8_reference(oracle_mod, gu[0][e], gu[1][e], gu[2][e], xb[t:t + 1], "f64").astype(np.float32))
+        ea = oracle_mod.err_metrics(f32(a[p:p + 1]), synth.bf16_bits_to_f32(ref_a))
+        assert ea["rel_l2"] < TOL and ea["max_rel_rms"] < TOL, (p, ea)
+        assert torch.equal(ops.qmv_w8(d_dn[0][e], d_dn[1][e], d_dn[2][e], a[p:p + 1]), part[p:p + 1]), p
+        ref_d = _w8_reference(oracle_mod, dn[0][e], dn[1][e], dn[2][e], bits16(a[p:p + 1]), "f64")
+        ed = oracle_mod.err_metrics(f32(part[p:p + 1]), ref_d.astype(np.float32))
+        assert ed["rel_l2"] < TOL and ed["max_rel_rms"] < TOL, (p, ed)
+    assert ops.device_status() == 0

@@ -192,7 +192,7 @@ extern "C" size_t vpq_scale_bytes(int N, int K, int group) {
 struct vpq_function_s {
   const char* library;
   const char* entry;
-  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64, 66..69 qmv w8g64 add / swiglu / qkv / gelu*mul, 70 / 71 qmm swiglu strided store w4 / w8, 72..74 grouped qmm down / swiglu / geglu, 75 qmv norm + qkv, 76..78 gathered expert qmv swiglu / geglu / down, 79..81 qmm w4g32 / geglu w4g32 / w8g32, 82..85 qmv w4g32 add / geglu / gelu*mul / qkv, 86..88 scale-only (Q4_0) qmv w4g32 plain / add / geglu, 89 requant w8 -> w4, 90 qmv geglu w8g64; 10 + code: quant / dequant twins (see fmt_*)
+  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64, 66..69 qmv w8g64 add / swiglu / qkv / gelu*mul, 70 / 71 qmm swiglu strided store w4 / w8, 72..74 grouped qmm down / swiglu / geglu, 75 qmv norm + qkv, 76..78 gathered expert qmv swiglu / geglu / down, 79..81 qmm w4g32 / geglu w4g32 / w8g32, 82..85 qmv w4g32 add / geglu / gelu*mul / qkv, 86..88 scale-only (Q4_0) qmv w4g32 plain / add / geglu, 89 requant w8 -> w4, 90 qmv geglu w8g64, 91..93 gathered expert qmv w8g64 swiglu / geglu / down; 10 + code: quant / dequant twins (see fmt_*)
 };
 
 // The reference selects the element type with the library-name suffix and
@@ -208,6 +208,9 @@ static const vpq_function_s g_functions[] = {
     {"affine_qmv_bf16", "affine_gather_qmv_swiglu_w4g64", 76},
     {"affine_qmv_bf16", "affine_gather_qmv_geglu_w4g64", 77},
     {"affine_qmv_bf16", "affine_gather_down_qmv_w4g64", 78},
+    {"affine_qmv_bf16", "affine_gather_qmv_swiglu_w8g64", 91},
+    {"affine_qmv_bf16", "affine_gather_qmv_geglu_w8g64", 92},
+    {"affine_qmv_bf16", "affine_gather_down_qmv_w8g64", 93},
     {"affine_qmv_bf16", "affine_qmv_geglu_w4g64", 61},
     {"affine_qmv_bf16", "affine_qmv_gelu_mul_w4g64", 62},
     {"affine_qmv_bf16", "affine_qmv_w8g64", 58},
@@ -350,7 +353,10 @@ extern "C" int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* a, 
     case 75:
     case 76:
     case 77:
-    case 78: {
+    case 78:
+    case 91:
+    case 92:
+    case 93: {
       vpq_linear_desc d;
       std::memset(&d, 0, sizeof(d));
       d.w = static_cast<const uint32_t*>(b[0]);
@@ -374,9 +380,13 @@ extern "C" int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* a, 
         d.N = a->N;
         d.expert = static_cast<const int32_t*>(b[7]);
         d.experts = a->experts;
-        d.x_div = fn->kind == 78 ? 1 : (int32_t)(a->top_k < 1 ? 1 : a->top_k);
-        d.epilogue = fn->kind == 76 ? VPQ_EPILOGUE_SWIGLU : fn->kind == 77 ? VPQ_EPILOGUE_GEGLU : VPQ_EPILOGUE_NONE;
+        const int k = fn->kind;
+        d.x_div = (k == 78 || k == 93) ? 1 : (int32_t)(a->top_k < 1 ? 1 : a->top_k);
+        d.epilogue = (k == 76 || k == 91)   ? VPQ_EPILOGUE_SWIGLU
+                     : (k == 77 || k == 92) ? VPQ_EPILOGUE_GEGLU
+                                            : VPQ_EPILOGUE_NONE;
       }
+      if (fn->kind >= 91) { return vpq_affine_qmv_w8g64_bf16_fused(&d, stream); }
       return vpq_affine_qmv_w4g64_bf16_batch(&d, 1, stream);
     }
     case 70:

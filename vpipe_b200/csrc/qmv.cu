@@ -1022,6 +1022,24 @@ int qmv_check_plain(const char* who, const vpq_linear_desc& d) {
   return qmv_check_store(who, d);
 }
 
+int qmv_check_gather(const char* who, const vpq_linear_desc& d) {
+  if (d.norm_w || d.depends) {
+    return fail(VPQ_ERR_UNSUPPORTED, "%s: norm_w and depends are taken by the w4 g64 GEMV entry points only", who);
+  }
+  if (d.expert) {
+    if (d.experts <= 0 || d.experts * d.N > (1ll << 30)) {
+      return fail(VPQ_ERR_INVALID_ARG, "%s: an expert gather needs 0 < experts, experts * N <= 2^30", who);
+    }
+    if (reinterpret_cast<uintptr_t>(d.expert) & 3) {
+      return fail(VPQ_ERR_ALIGNMENT, "%s: the expert index array must be 4-byte aligned", who);
+    }
+    if (d.x_div < 0) { return fail(VPQ_ERR_INVALID_ARG, "%s: x_div must be >= 0", who); }
+  } else if (d.experts > 1 || d.x_div > 1) {
+    return fail(VPQ_ERR_INVALID_ARG, "%s: experts / x_div given without an expert index array", who);
+  }
+  return qmv_check_store(who, d);
+}
+
 int qmv_check_store(const char* who, const vpq_linear_desc& d) {
   switch (d.epilogue) {
     case VPQ_EPILOGUE_NONE:

@@ -72,6 +72,8 @@ struct alignas(64) Problem8 {
   int q_rows, k_rows;
   const uint16_t* aux;
   __nv_bfloat16* y3;
+  const int32_t* eid;          // not null: *eid is the expert whose [N, K] slab of w / scales / biases is used
+  int experts;                 // slabs in w (eid is clamped to it)
 };
 
 __global__ void __launch_bounds__(kThreads, 2)
@@ -124,6 +126,14 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
       uint32_t it = 0;
       bool ok = true;
       const bool sz_tma = P.scales_tma != 0;
+      int row0 = 0;
+      if (P.eid) {
+        // the routed expert is an output of an earlier kernel: unlike the weights it must be waited for
+        // (the reference's affine_gather_qmv_swiglu_w8g64 / _geglu_ / affine_gather_down_qmv_w8g64 read it
+        // the same way, gpu-kernels/metal/quant/affine_qmv.metal:957-994,1290-1322,1519-1548)
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        row0 = min(max(__ldg(P.eid), 0), P.experts - 1) * N;
+      }
       for (int tile = gt_begin; tile < gt_end && ok; ++tile) {
         for (int st = 0; st < SPT; ++st, ++it) {
           const int s = it % stages;
@@ -136,11 +146,11 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
           const uint32_t dst = base + (uint32_t)s * kStageBytes;
           mbar_expect_tx(bar_full(s), (uint32_t)nb * kBoxBytes + (sz_tma ? kStageSZ : 0));
           for (int b = 0; b < nb; ++b) {
-            tma_load_2d(dst + b * kBoxBytes, &P.mw, bar_full(s), (st * kBoxesPerStage + b) * 32, tile * 16);
+            tma_load_2d(dst + b * kBoxBytes, &P.mw, bar_full(s), (st * kBoxesPerStage + b) * 32, row0 + tile * 16);
           }
           if (sz_tma) {
-            tma_load_2d(dst + kStageW, &P.ms, bar_full(s), st * 16, tile * 16);
-            tma_load_2d(dst + kStageW + kStageSZ / 2, &P.mz, bar_full(s), st * 16, tile * 16);
+            tma_load_2d(dst + kStageW, &P.ms, bar_full(s), st * 16, row0 + tile * 16);
+            tma_load_2d(dst + kStageW + kStageSZ / 2, &P.mz, bar_full(s), st * 16, row0 + tile * 16);
           }
         }
       }
@@ -279,7 +289,8 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
         } else {
           // clamped onto valid data: a clamped group meets x == 0, a clamped row is never stored
           const uint16_t* src = bias_lane ? P.biases : P.scales;
-          const int64_t r_a = min(tile * 16 + rho, N - 1), r_b = min(tile * 16 + rho + 8, N - 1);
+          const int64_t slab = P.eid ? (int64_t)min(max(__ldg(P.eid), 0), P.experts - 1) * N : 0;
+          const int64_t r_a = slab + min(tile * 16 + rho, N - 1), r_b = slab + min(tile * 16 + rho + 8, N - 1);
           const int g0 = min(2 * kt, G - 1), g1 = min(2 * kt + 1, G - 1);
           sa = ldg_nc_u16(src + r_a * G + g0) | (ldg_nc_u16(src + r_a * G + g1) << 16);
           sb2 = ldg_nc_u16(src + r_b * G + g0) | (ldg_nc_u16(src + r_b * G + g1) << 16);
@@ -387,22 +398,23 @@ int launch_w8(const char* who, const vpq_linear_desc& d, void* stream) {
       (reinterpret_cast<uintptr_t>(biases) & 1) || (reinterpret_cast<uintptr_t>(y) & 1)) {
     return fail(VPQ_ERR_ALIGNMENT, "%s: w and x must be 16-byte aligned", who);
   }
-  if (int rc = qmv_check_plain(who, d)) { return rc; }
+  if (int rc = qmv_check_gather(who, d)) { return rc; }
   if (int rc = require_sm100()) { return rc; }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Problem8 p;
   std::memset(&p, 0, sizeof(p));
-  if (int rc = make_map_2d(&p.mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w, (uint64_t)(K / 4), (uint64_t)N, 32, 16,
+  const uint64_t rows = (uint64_t)N * (uint64_t)(d.expert ? d.experts : 1);  // expert slabs are stacked along the rows
+  if (int rc = make_map_2d(&p.mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w, (uint64_t)(K / 4), rows, 32, 16,
                            CU_TENSOR_MAP_SWIZZLE_128B, "w")) {
     return rc;
   }
   p.scales_tma = ((K % 512) == 0 && aligned16(scales) && aligned16(biases)) ? 1 : 0;
   if (p.scales_tma) {
-    if (int rc = make_map_2d(&p.ms, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, (uint64_t)(K / 64), (uint64_t)N, 16, 16,
+    if (int rc = make_map_2d(&p.ms, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, (uint64_t)(K / 64), rows, 16, 16,
                              CU_TENSOR_MAP_SWIZZLE_NONE, "scales")) {
       return rc;
     }
-    if (int rc = make_map_2d(&p.mz, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, biases, (uint64_t)(K / 64), (uint64_t)N, 16, 16,
+    if (int rc = make_map_2d(&p.mz, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, biases, (uint64_t)(K / 64), rows, 16, 16,
                              CU_TENSOR_MAP_SWIZZLE_NONE, "biases")) {
       return rc;
     }
@@ -427,8 +439,12 @@ int launch_w8(const char* who, const vpq_linear_desc& d, void* stream) {
   static int granted[64] = {};
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), granted, smem)) { return rc; }
   const int cap = 2 * num_sms();
+  p.experts = d.expert ? (int)d.experts : 1;
   for (int64_t m = 0; m < M; ++m) {  // every row streams the weight again, as in the reference
-    p.x = static_cast<const uint16_t*>(x) + m * K;
+    // expert gather: row m is a (token, expert) pair; the pairs of one token share its x row
+    const int64_t x_row = (d.expert && d.x_div > 1) ? m / d.x_div : m;
+    p.x = static_cast<const uint16_t*>(x) + x_row * K;
+    p.eid = d.expert ? d.expert + m : nullptr;
     p.y = static_cast<__nv_bfloat16*>(y) + m * y_pitch;
     if (d.epilogue == VPQ_EPILOGUE_ADD || d.epilogue == VPQ_EPILOGUE_GELU_MUL) {
       p.aux = static_cast<const uint16_t*>(d.aux) + m * N;
