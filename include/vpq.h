@@ -235,6 +235,13 @@ int vpq_affine_qmv_w4g64_bf16_batch(const vpq_linear_desc* descs_host, int count
  * (affine_qmv.metal:957-994,1290-1322,1519-1548). norm_w and depends are not taken. */
 int vpq_affine_qmv_w8g64_bf16_fused(const vpq_linear_desc* desc_host, void* stream);
 
+/* The shared-expert gate of a mixture-of-experts block: out[m] = sigmoid(dequant(w) . x[m]) for ONE
+ * 8-bit group-64 weight row (w u32 [K/4], scales / biases [K/64]) and M rows of x; out bf16 [M].
+ * Slots 0..4 = w, scales, biases, x, out; K as a constant. Replaces affine_moe_gate_w8g64
+ * (gpu-kernels/metal/quant/affine_qmv.metal:1323-1347). x must be 8-byte aligned. */
+int vpq_affine_moe_gate_w8g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                                   void* out, int64_t K, int64_t M, void* stream);
+
 /* The small-batch GEMV (w4 g64, rows of x share one stream of the weights) and the group-32 GEMV with
  * a fused store: one descriptor, any VPQ_EPILOGUE_*. Replace affine_qmv_batch_swiglu_w4g64,
  * affine_qmv_w4g32_add, affine_qmv_geglu_w4g32, affine_qmv_gelu_mul_w4g32

@@ -399,3 +399,23 @@ def test_moe_gather_gemvs_over_8_bit_experts(vpq, oracle_mod, act):
         ed = oracle_mod.err_metrics(f32(part[p:p + 1]), ref_d.astype(np.float32))
         assert ed["rel_l2"] < TOL and ed["max_rel_rms"] < TOL, (p, ed)
     assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("K,M", [(2048, 1), (4096, 5), (64, 3), (3136, 2)])
+def test_moe_shared_expert_gate(vpq, oracle_mod, K, M):
+    """affine_moe_gate_w8g64 (affine_qmv.metal:1323-1347): sigmoid of one 8-bit row's dot product with
+    every row of x, against the fp32 oracle (f64 accumulation), and by the reference's name."""
+    from test_gpu_formats import _w8_reference
+    wb = synth.f32_to_bf16_bits(synth.weight_f32(1, K, 3900 + K) * 3.0)
+    codes, s16, b16 = oracle_mod.quant(wb, 8, 64)
+    s, b = oracle_mod.f16_to_bf16(s16), oracle_mod.f16_to_bf16(b16)
+    x = synth.activations_bf16(M, K, 3901 + K)
+    d = (to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16), to_dev(x, torch.bfloat16))
+    got = vpq.ops.moe_gate_w8(*d)
+    logit = _w8_reference(oracle_mod, codes, s, b, x, "f64").astype(np.float64).reshape(M)
+    want = 1.0 / (1.0 + np.exp(-logit))
+    assert float(np.abs(want - 0.5).max()) > 0.05           # the logits are not all near zero
+    assert np.abs(got.float().cpu().numpy().astype(np.float64) - want).max() < 1e-2 * 0.5 + 2.0 ** -8
+    out = torch.full((M,), float("nan"), dtype=torch.bfloat16, device=dev())
+    vpq.ops.dispatch(vpq.ops.function("affine_qmv_bf16", "affine_moe_gate_w8g64"), [d[0], d[1], d[2], d[3], out], K=K, M=M)
+    assert torch.equal(out, got)

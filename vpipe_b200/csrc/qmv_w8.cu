@@ -468,6 +468,65 @@ int launch_w8(const char* who, const vpq_linear_desc& d, void* stream) {
 }
 }  // namespace
 
+// The shared-expert gate of a mixture-of-experts block: g[m] = sigmoid(dequant(w[1, K]) . x[m]), w one
+// 8-bit group-64 row. Replaces affine_moe_gate_w8g64 (gpu-kernels/metal/quant/affine_qmv.metal:1323-1347),
+// which has the same decomposition: one warp per row of x, lanes striding over k (here four consecutive k
+// = one packed word per step), a warp sum, lane 0 writes. Latency-bound by construction (K bytes of
+// weight): a dozen microseconds of HBM time saved by nothing cleverer.
+namespace vpq {
+__global__ void __launch_bounds__(128)
+affine_moe_gate_w8g64_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ scales,
+                             const uint16_t* __restrict__ biases, const uint16_t* __restrict__ x,
+                             __nv_bfloat16* __restrict__ out, int K, int M) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // x may come from the previous kernel
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= M) { return; }
+  const uint2* xr = reinterpret_cast<const uint2*>(x + (size_t)row * K);
+  float acc = 0.0f;
+  for (int wd = lane; wd < (K >> 2); wd += 32) {   // word wd = k 4 wd .. 4 wd + 3, all in group wd / 16
+    const float s = __uint_as_float((uint32_t)__ldg(scales + (wd >> 4)) << 16);
+    const float b = __uint_as_float((uint32_t)__ldg(biases + (wd >> 4)) << 16);
+    const uint32_t q = __ldg(w + wd);
+    const uint2 xv = xr[wd];
+    acc = __fmaf_rn(dequant_f32(s, q & 0xffu, b), __uint_as_float(xv.x << 16), acc);
+    acc = __fmaf_rn(dequant_f32(s, (q >> 8) & 0xffu, b), __uint_as_float(xv.x & 0xffff0000u), acc);
+    acc = __fmaf_rn(dequant_f32(s, (q >> 16) & 0xffu, b), __uint_as_float(xv.y << 16), acc);
+    acc = __fmaf_rn(dequant_f32(s, q >> 24, b), __uint_as_float(xv.y & 0xffff0000u), acc);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { acc += __shfl_xor_sync(0xffffffffu, acc, o); }
+  if (lane == 0) { out[row] = __float2bfloat16_rn(1.0f / (1.0f + expf(-acc))); }
+}
+}  // namespace vpq
+
+extern "C" int vpq_affine_moe_gate_w8g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
+                                              void* out, int64_t K, int64_t M, void* stream) {
+  clear_error();
+  if (!w || !scales || !biases || !x || !out) { return fail(VPQ_ERR_INVALID_ARG, "affine_moe_gate_w8g64: null pointer"); }
+  if (K <= 0 || M <= 0 || (K % 64) != 0 || K > (1 << 24) || M > (1 << 24)) {
+    return fail(VPQ_ERR_INVALID_ARG, "affine_moe_gate_w8g64: need K>0, M>0, K%%64==0 (K=%lld M=%lld)", (long long)K, (long long)M);
+  }
+  if ((reinterpret_cast<uintptr_t>(w) & 3) || (reinterpret_cast<uintptr_t>(x) & 7) || (reinterpret_cast<uintptr_t>(scales) & 1) ||
+      (reinterpret_cast<uintptr_t>(biases) & 1) || (reinterpret_cast<uintptr_t>(out) & 1)) {
+    return fail(VPQ_ERR_ALIGNMENT, "affine_moe_gate_w8g64: w must be 4-byte aligned, x 8-byte");
+  }
+  if (int rc = require_sm100()) { return rc; }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((M + 3) / 4), 1, 1);
+  cfg.blockDim = dim3(128, 1, 1);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  VPQ_CUDA_OK(cudaLaunchKernelEx(&cfg, affine_moe_gate_w8g64_kernel, w, static_cast<const uint16_t*>(scales),
+                                 static_cast<const uint16_t*>(biases), static_cast<const uint16_t*>(x),
+                                 static_cast<__nv_bfloat16*>(out), (int)K, (int)M));
+  return VPQ_OK;
+}
+
 extern "C" int vpq_affine_qmv_w8g64_bf16(const uint32_t* w, const void* scales, const void* biases, const void* x,
                                          void* y, int64_t K, int64_t N, int64_t M, void* stream) {
   clear_error();

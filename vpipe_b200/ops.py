@@ -135,6 +135,18 @@ def qmv_w8(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
     return out
 
 
+def moe_gate_w8(codes, scales, biases, x, out=None, stream=None) -> torch.Tensor:
+    """out[m] = sigmoid(dequant(w[1, K]) . x[m]) for one 8-bit row (vpq_affine_moe_gate_w8g64_bf16)."""
+    K = codes.numel() * 4
+    M = x.numel() // K
+    if out is None:
+        out = torch.empty((M,), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().vpq_affine_moe_gate_w8g64_bf16(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x), _ptr(out), K, M,
+                                                   _stream(stream)))
+    return out
+
+
 def qmv_w8_fused(codes, scales, biases, x, y, store, stream=None, kind="w8"):
     """A GEMV with a fused store through one descriptor; `store` as in qmv_set, `y` the (first) output
     tensor. kind "w8": 8-bit weights (vpq_affine_qmv_w8g64_bf16_fused); "batch": w4 g64 rows sharing one
