@@ -184,7 +184,7 @@ typedef struct vpq_linear_desc {
   /* Fused store, VPQ_EPILOGUE_*; zero-initialised descriptors store y = x W^T as is. */
   int32_t epilogue;
   int32_t depends;      /* plans only: 1 = this GEMV reads (x, residual) what GEMVs earlier in the list write */
-  const void* aux;      /* ADD: residual [M, N]; GELU_MUL: multiplier [M, N]; QKV: the k output [M, k_rows] (written) */
+  const void* aux;      /* ADD: residual [M, N]; GELU_MUL, SILU_MUL: multiplier [M, N]; QKV: the k output [M, k_rows] (written) */
   void* y3;             /* QKV: the v output [M, N - q_rows - k_rows] */
   int64_t q_rows, k_rows;
   /* RMSNorm prologue (w4 g64 GEMV only): with norm_w [K] (bf16, 16-byte aligned) every row of x is
@@ -215,14 +215,20 @@ typedef struct vpq_linear_desc {
  * GEGLU   as SWIGLU with gelu(g) = 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) on the gate
  *         affine_qmv_geglu_w4g64, affine_qmv.metal:1352-1448
  * GELU_MUL y[n] = bf16(gelu(bf16(sum)) * mul[n])                 affine_qmv_gelu_mul_w4g64,
- *         affine_qmv.metal:265-283,745-765 (Gemma per-layer-input gate) */
+ *         affine_qmv.metal:265-283,745-765 (Gemma per-layer-input gate)
+ * SILU_MUL y[n] = bf16(silu(sum) * mul[n]), mul [M, N] in aux (may be y itself: each element is read, then
+ *         written, by one thread). The second half of a SwiGLU whose gate and up matrices are separate and of
+ *         different widths: run the up GEMV into y, then the gate GEMV with this store and aux = y
+ *         (affine_gather_qmv_swiglu_w4w8g64 / _w8w4g64, affine_qmv.metal:1153-1259; up reaches the product
+ *         rounded to bf16 here, unrounded there) */
 enum {
   VPQ_EPILOGUE_NONE = 0,
   VPQ_EPILOGUE_ADD = 1,
   VPQ_EPILOGUE_SWIGLU = 2,
   VPQ_EPILOGUE_QKV = 3,
   VPQ_EPILOGUE_GEGLU = 4,
-  VPQ_EPILOGUE_GELU_MUL = 5
+  VPQ_EPILOGUE_GELU_MUL = 5,
+  VPQ_EPILOGUE_SILU_MUL = 6
 };
 int vpq_affine_qmv_w4g64_bf16_batch(const vpq_linear_desc* descs_host, int count, void* stream);
 

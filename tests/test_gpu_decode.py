@@ -419,3 +419,48 @@ def test_moe_shared_expert_gate(vpq, oracle_mod, K, M):
     out = torch.full((M,), float("nan"), dtype=torch.bfloat16, device=dev())
     vpq.ops.dispatch(vpq.ops.function("affine_qmv_bf16", "affine_moe_gate_w8g64"), [d[0], d[1], d[2], d[3], out], K=K, M=M)
     assert torch.equal(out, got)
+
+
+@pytest.mark.parametrize("gate_bits", [4, 8])
+def test_moe_gather_swiglu_with_gate_and_up_of_different_widths(vpq, oracle_mod, gate_bits):
+    """affine_gather_qmv_swiglu_w4w8g64 / _w8w4g64 (affine_qmv.metal:1153-1259): separate gate and up
+    matrices, one at 4 and one at 8 bits, per routed pair; against the fp32 oracle of silu(gate) * up."""
+    from test_gpu_formats import _w8_reference
+    ops = vpq.ops
+    E, H, F, T, top_k = 4, 1024, 256, 2, 2
+    up_bits = 12 - gate_bits
+
+    def experts(bits, seed):
+        cs, ss, bs = [], [], []
+        for e in range(E):
+            wb = synth.f32_to_bf16_bits(synth.weight_f32(F, H, seed + e))
+            c, s16, b16 = oracle_mod.quant(wb, bits, 64)
+            cs.append(c), ss.append(oracle_mod.f16_to_bf16(s16)), bs.append(oracle_mod.f16_to_bf16(b16))
+        return np.stack(cs), np.stack(ss), np.stack(bs)
+
+    def linear(w, bits, e, xrow):
+        if bits == 8:
+            return _w8_reference(oracle_mod, w[0][e], w[1][e], w[2][e], xrow, "f64").astype(np.float64)
+        return oracle_mod.linear_f32(w[0][e], w[1][e], w[2][e], xrow, "f64").astype(np.float64)
+
+    g, u = experts(gate_bits, 4100), experts(up_bits, 4200)
+    xb = synth.activations_bf16(T, H, 4300)
+    eid = np.array([2, 0, 3, 1], np.int32)
+    npair = T * top_k
+    dg = [to_dev(g[0]), to_dev(g[1], torch.bfloat16), to_dev(g[2], torch.bfloat16)]
+    du = [to_dev(u[0]), to_dev(u[1], torch.bfloat16), to_dev(u[2], torch.bfloat16)]
+    dx, deid = to_dev(xb, torch.bfloat16), torch.from_numpy(eid).to(dev())
+    y = torch.full((npair, F), float("nan"), dtype=torch.bfloat16, device=dev())
+    name = "affine_gather_qmv_swiglu_w4w8g64" if gate_bits == 4 else "affine_gather_qmv_swiglu_w8w4g64"
+    ops.dispatch(ops.function("affine_qmv_bf16", name),
+                 {0: dg[0], 1: dg[1], 2: dg[2], 3: du[0], 4: du[1], 5: du[2], 6: dx, 7: y, 10: deid},
+                 K=H, N=F, M=npair, experts=E, top_k=top_k)
+    torch.cuda.synchronize()
+    assert not torch.isnan(y.float()).any()
+    for p in range(npair):
+        e, t = int(eid[p]), p // top_k
+        gv, uv = linear(g, gate_bits, e, xb[t:t + 1]), linear(u, up_bits, e, xb[t:t + 1])
+        want = (gv / (1.0 + np.exp(-gv)) * uv).astype(np.float32)
+        err = oracle_mod.err_metrics(f32(y[p:p + 1]), want)
+        assert err["rel_l2"] < TOL and err["max_rel_rms"] < TOL, (p, err)
+    assert ops.device_status() == 0

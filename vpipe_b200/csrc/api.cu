@@ -192,7 +192,7 @@ extern "C" size_t vpq_scale_bytes(int N, int K, int group) {
 struct vpq_function_s {
   const char* library;
   const char* entry;
-  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64, 66..69 qmv w8g64 add / swiglu / qkv / gelu*mul, 70 / 71 qmm swiglu strided store w4 / w8, 72..74 grouped qmm down / swiglu / geglu, 75 qmv norm + qkv, 76..78 gathered expert qmv swiglu / geglu / down, 79..81 qmm w4g32 / geglu w4g32 / w8g32, 82..85 qmv w4g32 add / geglu / gelu*mul / qkv, 86..88 scale-only (Q4_0) qmv w4g32 plain / add / geglu, 89 requant w8 -> w4, 90 qmv geglu w8g64, 91..93 gathered expert qmv w8g64 swiglu / geglu / down, 94 moe gate w8g64; 10 + code: quant / dequant twins (see fmt_*)
+  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64, 66..69 qmv w8g64 add / swiglu / qkv / gelu*mul, 70 / 71 qmm swiglu strided store w4 / w8, 72..74 grouped qmm down / swiglu / geglu, 75 qmv norm + qkv, 76..78 gathered expert qmv swiglu / geglu / down, 79..81 qmm w4g32 / geglu w4g32 / w8g32, 82..85 qmv w4g32 add / geglu / gelu*mul / qkv, 86..88 scale-only (Q4_0) qmv w4g32 plain / add / geglu, 89 requant w8 -> w4, 90 qmv geglu w8g64, 91..93 gathered expert qmv w8g64 swiglu / geglu / down, 94 moe gate w8g64, 95 / 96 gathered split-width swiglu (gate w4 + up w8 / gate w8 + up w4); 10 + code: quant / dequant twins (see fmt_*)
 };
 
 // The reference selects the element type with the library-name suffix and
@@ -212,6 +212,8 @@ static const vpq_function_s g_functions[] = {
     {"affine_qmv_bf16", "affine_gather_qmv_geglu_w8g64", 92},
     {"affine_qmv_bf16", "affine_gather_down_qmv_w8g64", 93},
     {"affine_qmv_bf16", "affine_moe_gate_w8g64", 94},
+    {"affine_qmv_bf16", "affine_gather_qmv_swiglu_w4w8g64", 95},
+    {"affine_qmv_bf16", "affine_gather_qmv_swiglu_w8w4g64", 96},
     {"affine_qmv_bf16", "affine_qmv_geglu_w4g64", 61},
     {"affine_qmv_bf16", "affine_qmv_gelu_mul_w4g64", 62},
     {"affine_qmv_bf16", "affine_qmv_w8g64", 58},
@@ -429,6 +431,35 @@ extern "C" int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* a, 
         d.aux = b[7];
       }
       return k >= 86 ? vpq_affine_qmv_w4g32_q40_bf16_fused(&d, stream) : vpq_affine_qmv_w4g32_bf16_fused(&d, stream);
+    }
+    case 95:
+    case 96: {
+      // Separate gate and up matrices of different widths (slots: gate 0..2, up 3..5, x 6, y 7, pair_eid 10;
+      // N = ffn): the up GEMV writes y, the gate GEMV multiplies silu(gate) into it.
+      vpq_linear_desc up, gate;
+      std::memset(&up, 0, sizeof(up));
+      up.w = static_cast<const uint32_t*>(b[3]);
+      up.scales = b[4];
+      up.biases = b[5];
+      up.x = b[6];
+      up.y = const_cast<void*>(b[7]);
+      up.K = a->K;
+      up.N = a->N;
+      up.M = a->M < 1 ? 1 : a->M;
+      up.expert = static_cast<const int32_t*>(b[10]);
+      up.experts = a->experts;
+      up.x_div = (int32_t)(a->top_k < 1 ? 1 : a->top_k);
+      gate = up;
+      gate.w = static_cast<const uint32_t*>(b[0]);
+      gate.scales = b[1];
+      gate.biases = b[2];
+      gate.epilogue = VPQ_EPILOGUE_SILU_MUL;
+      gate.aux = b[7];
+      const bool gate_w4 = fn->kind == 95;
+      if (int rc = gate_w4 ? vpq_affine_qmv_w8g64_bf16_fused(&up, stream) : vpq_affine_qmv_w4g64_bf16_batch(&up, 1, stream)) {
+        return rc;
+      }
+      return gate_w4 ? vpq_affine_qmv_w4g64_bf16_batch(&gate, 1, stream) : vpq_affine_qmv_w8g64_bf16_fused(&gate, stream);
     }
     case 94:
       return vpq_affine_moe_gate_w8g64_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3], const_cast<void*>(b[4]),

@@ -1050,6 +1050,7 @@ int qmv_check_store(const char* who, const vpq_linear_desc& d) {
       }
       return VPQ_OK;
     case VPQ_EPILOGUE_GELU_MUL:
+    case VPQ_EPILOGUE_SILU_MUL:
       if (!d.aux || (reinterpret_cast<uintptr_t>(d.aux) & 1)) {
         return fail(VPQ_ERR_INVALID_ARG, "%s: the multiplier is null or not 2-byte aligned", who);
       }
@@ -1089,7 +1090,7 @@ int fill_from_desc(QmvProblem* p, const vpq_linear_desc& d, int64_t m, int tile_
     return rc;
   }
   p->epilogue = d.epilogue;
-  if (d.epilogue == VPQ_EPILOGUE_ADD || d.epilogue == VPQ_EPILOGUE_GELU_MUL) {
+  if (d.epilogue == VPQ_EPILOGUE_ADD || d.epilogue == VPQ_EPILOGUE_GELU_MUL || d.epilogue == VPQ_EPILOGUE_SILU_MUL) {
     p->aux = static_cast<const uint16_t*>(d.aux) + m * d.N;
   } else if (d.epilogue == VPQ_EPILOGUE_QKV) {
     p->q_rows = (int)d.q_rows;

@@ -504,7 +504,7 @@ int launch_batch(const char* who, const vpq_linear_desc& d, int per_pass, cudaSt
   const int64_t K = d.K, N = d.N, M = d.M;
   const bool gated = d.epilogue == VPQ_EPILOGUE_SWIGLU || d.epilogue == VPQ_EPILOGUE_GEGLU;
   const int64_t y_pitch = gated ? N / 2 : d.epilogue == VPQ_EPILOGUE_QKV ? d.q_rows : N;
-  const int64_t aux_pitch = (d.epilogue == VPQ_EPILOGUE_ADD || d.epilogue == VPQ_EPILOGUE_GELU_MUL) ? N
+  const int64_t aux_pitch = (d.epilogue == VPQ_EPILOGUE_ADD || d.epilogue == VPQ_EPILOGUE_GELU_MUL || d.epilogue == VPQ_EPILOGUE_SILU_MUL) ? N
                             : d.epilogue == VPQ_EPILOGUE_QKV                                         ? d.k_rows
                                                                                                      : 0;
   const int64_t y3_pitch = d.epilogue == VPQ_EPILOGUE_QKV ? N - d.q_rows - d.k_rows : 0;

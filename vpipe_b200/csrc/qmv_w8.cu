@@ -446,7 +446,7 @@ int launch_w8(const char* who, const vpq_linear_desc& d, void* stream) {
     p.x = static_cast<const uint16_t*>(x) + x_row * K;
     p.eid = d.expert ? d.expert + m : nullptr;
     p.y = static_cast<__nv_bfloat16*>(y) + m * y_pitch;
-    if (d.epilogue == VPQ_EPILOGUE_ADD || d.epilogue == VPQ_EPILOGUE_GELU_MUL) {
+    if (d.epilogue == VPQ_EPILOGUE_ADD || d.epilogue == VPQ_EPILOGUE_GELU_MUL || d.epilogue == VPQ_EPILOGUE_SILU_MUL) {
       p.aux = static_cast<const uint16_t*>(d.aux) + m * N;
     } else if (d.epilogue == VPQ_EPILOGUE_QKV) {
       p.aux = static_cast<const uint16_t*>(d.aux) + m * d.k_rows;

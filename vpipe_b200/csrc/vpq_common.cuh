@@ -121,7 +121,7 @@ __device__ __forceinline__ float gelu_tanh(float x) {
 // What a GEMV does with a row's f32 sum: the reference's fused decode stores (VPQ_EPILOGUE_*;
 // affine_qmv.metal:265-283,347-363,405-516,806-906,1352-1448). Called by lanes 0..15 of a warp,
 // lane = row within the 16-row tile; the gated stores pair lanes 2j, 2j + 1.
-enum : int { kEpiNone = 0, kEpiAdd = 1, kEpiSwiglu = 2, kEpiQkv = 3, kEpiGeglu = 4, kEpiGeluMul = 5 };
+enum : int { kEpiNone = 0, kEpiAdd = 1, kEpiSwiglu = 2, kEpiQkv = 3, kEpiGeglu = 4, kEpiGeluMul = 5, kEpiSiluMul = 6 };
 
 // `mask` names the lanes that make the call together (the gated stores shuffle among them).
 __device__ __forceinline__ void fused_store(int epi, float v, int row, int N, int lane, __nv_bfloat16* y,
@@ -148,6 +148,12 @@ __device__ __forceinline__ void fused_store(int epi, float v, int row, int N, in
     if (row < N) {
       const float m = __uint_as_float((uint32_t)aux[row] << 16);
       y[row] = __float2bfloat16_rn(gelu_tanh(__bfloat162float(__float2bfloat16_rn(v))) * m);
+    }
+  } else if (epi == kEpiSiluMul) {
+    // silu of the unrounded sum, times the multiplier (the up projection of a split-width SwiGLU)
+    if (row < N) {
+      const float m = __uint_as_float((uint32_t)aux[row] << 16);
+      y[row] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * m);
     }
   } else {
     const int qk = q_rows + k_rows;

@@ -243,14 +243,14 @@ def qmv_qkv(codes, scales, biases, x, q_rows, k_rows, v_rows, stream=None):
     return tuple(outs)
 
 
-EPILOGUES = {"none": 0, "add": 1, "swiglu": 2, "qkv": 3, "geglu": 4, "gelu_mul": 5}
+EPILOGUES = {"none": 0, "add": 1, "swiglu": 2, "qkv": 3, "geglu": 4, "gelu_mul": 5, "silu_mul": 6}
 
 
 def qmv_set(problems):
     """Builds the host descriptor array for qmv_batch / QmvPlan from (codes, scales, biases, x, y)
     tuples; an optional sixth element is a dict describing a fused store and the other options:
     {"epilogue": "add", "aux": residual} | {"epilogue": "swiglu"} | {"epilogue": "geglu"} |
-    {"epilogue": "gelu_mul", "aux": mul} |
+    {"epilogue": "gelu_mul", "aux": mul} | {"epilogue": "silu_mul", "aux": mul} |
     {"epilogue": "qkv", "aux": k_out, "y3": v_out, "q_rows": .., "k_rows": ..};
     "norm_w": weights [K] and "eps" (RMSNorm of x while it is staged); "depends": True (plans: this
     GEMV reads what earlier entries write); "expert": int32 device tensor [M] with "x_div" (codes is
