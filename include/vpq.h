@@ -399,6 +399,16 @@ int vpq_affine_qmm_grouped_geglu_w4g64_bf16(const uint32_t* w, const void* scale
                                             const int* tile2e, const int* srow, int64_t experts,
                                             int64_t x_rows, void* x_sorted, void* stream);
 
+/* The grouped GEMMs over 8-bit experts (w u32 [experts * N, K/4]). act 0: the down GEMM (rows_map = sdst,
+ * rows = y_rows, x_sorted unused); act 1 / 2: gate|up with the SwiGLU / GeGLU store (rows_map = srow,
+ * rows = x_rows, x_sorted the [M, K] scratch), arguments otherwise as for the 4-bit entries above.
+ * Replace affine_qmm_grouped_w8g64, affine_qmm_grouped_swiglu_w8g64, affine_qmm_grouped_geglu_w8g64
+ * (gpu-kernels/metal/quant/affine_qmm_steel.metal:1069-1094,1341-1367,1290-1312). */
+int vpq_affine_qmm_grouped_w8g64_bf16(int act, const uint32_t* w, const void* scales, const void* biases,
+                                      const void* x, void* y, int64_t K, int64_t N, int64_t M, const int* tile2e,
+                                      const int* rows_map, int64_t experts, int64_t rows, void* x_sorted,
+                                      void* stream);
+
 /* Device-side status of the tensor-core kernels: every wait inside them is
  * bounded; one that gives up records where and the kernel returns. Reads the
  * status word of the current device back to the host (synchronises `stream`),

@@ -152,3 +152,69 @@ def test_grouped_by_reference_names(vpq, oracle_mod):
     ops.dispatch(ops.function(lib, "affine_qmm_grouped_w4g64"), {0: d[0], 1: d[1], 2: d[2], 3: xs, 4: y, 8: t2e, 9: sd},
                  K=K, N=N, M=npad, experts=E, rows=T * top_k)
     assert torch.equal(y, want)
+
+
+def _experts8(oracle_mod, E, N, K, seed):
+    per = []
+    for e in range(E):
+        wb = synth.f32_to_bf16_bits(synth.weight_f32(N, K, seed + 17 * e))
+        c, s16, b16 = oracle_mod.quant(wb, 8, 64)
+        per.append((c, oracle_mod.f16_to_bf16(s16), oracle_mod.f16_to_bf16(b16)))
+    d = (to_dev(np.stack([p[0] for p in per])), to_dev(np.stack([p[1] for p in per]), torch.bfloat16),
+         to_dev(np.stack([p[2] for p in per]), torch.bfloat16))
+    return per, d
+
+
+@pytest.mark.parametrize("act", ["swiglu", "geglu"])
+def test_grouped_gemms_over_8_bit_experts(vpq, oracle_mod, act):
+    """affine_qmm_grouped_swiglu_w8g64 / _geglu_w8g64 / affine_qmm_grouped_w8g64
+    (affine_qmm_steel.metal:1069-1094,1290-1312,1341-1367): gate|up with the row gather, then down with
+    the scatter, per expert against the oracle (dequantise to bf16, fp32 matmul); also by name."""
+    ops = vpq.ops
+    tile = ops.qmm_grouped_tile_rows()
+    T, E, top_k, H, F = 200, 5, 2, 512, 320
+    per_gu, d_gu = _experts8(oracle_mod, E, 2 * F, H, 9500)
+    per_dn, d_dn = _experts8(oracle_mod, E, H, F, 9600)
+    x = synth.activations_bf16(T, H, 9700)
+    dx = to_dev(x, torch.bfloat16)
+    eid = _routing(T, E, top_k, 9701, idle=(3,))
+    tile2e, srow, sdst, npad = moe.sort_pairs(eid, E, top_k, tile)
+    dt, dsrow, dsdst = to_dev(tile2e), to_dev(srow), to_dev(sdst)
+    act_out = torch.full((npad, F), -3.0, dtype=torch.bfloat16, device=dev())
+    ops.qmm_grouped_gated(*d_gu, dx, dt, dsrow, act=act, out=act_out, bits=8)
+    n_pairs = T * top_k
+    y = torch.full((n_pairs + 1, H), -3.0, dtype=torch.bfloat16, device=dev())
+    ops.qmm_grouped_down(*d_dn, act_out, dt, dsdst, y_rows=n_pairs, out=y, bits=8)
+    assert ops.device_status() == 0
+    ah, yh = f32(act_out), f32(y)
+    assert np.all(yh[n_pairs] == -3.0) and np.all(yh[:n_pairs] != -3.0)
+    fuse = oracle_mod.fused_geglu if act == "geglu" else oracle_mod.fused_swiglu
+    from test_gpu_parity import bits16
+    a_bits = bits16(act_out)
+    for e in range(E):
+        slots = np.nonzero((np.repeat(tile2e, tile) == e) & (srow >= 0))[0]
+        if slots.size == 0:
+            continue
+        c, s, b = per_gu[e]
+        w = oracle_mod.bf16_to_f32(oracle_mod.dequant_bf16_any(c, s, b, 8, 64))
+        want = synth.bf16_bits_to_f32(fuse(oracle_mod.matmul_f32(np.ascontiguousarray(x[srow[slots]]), w, "fast")))
+        err = oracle_mod.err_metrics(ah[slots], want)
+        assert err["rel_l2"] < TOL and err["max_rel_rms"] < TOL, ("gate|up", e, err)
+        c, s, b = per_dn[e]
+        w = oracle_mod.bf16_to_f32(oracle_mod.dequant_bf16_any(c, s, b, 8, 64))
+        want = synth.bf16_bits_to_f32(oracle_mod.narrow_f32_bf16(
+            oracle_mod.matmul_f32(np.ascontiguousarray(a_bits[slots]), w, "fast")))
+        err = oracle_mod.err_metrics(yh[sdst[slots]], want)
+        assert err["rel_l2"] < TOL and err["max_rel_rms"] < TOL, ("down", e, err)
+    # by the reference's names (slots as for the 4-bit kernels: 8 = tile2e, 9 = srow / sdst, 10 = scratch)
+    act2 = torch.full_like(act_out, -3.0)
+    scratch = torch.empty((npad, H), dtype=torch.bfloat16, device=dev())
+    ops.dispatch(ops.function("affine_qmm_steel_bf16", f"affine_qmm_grouped_{act}_w8g64"),
+                 {0: d_gu[0], 1: d_gu[1], 2: d_gu[2], 3: dx, 4: act2, 8: dt, 9: dsrow, 10: scratch},
+                 K=H, N=2 * F, M=npad, experts=E, rows=T)
+    assert torch.equal(act2, act_out)
+    y2 = torch.full_like(y, -3.0)
+    ops.dispatch(ops.function("affine_qmm_steel_bf16", "affine_qmm_grouped_w8g64"),
+                 {0: d_dn[0], 1: d_dn[1], 2: d_dn[2], 3: act_out, 4: y2, 8: dt, 9: dsdst},
+                 K=F, N=H, M=npad, experts=E, rows=n_pairs)
+    assert torch.equal(y2, y)

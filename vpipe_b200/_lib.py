@@ -36,6 +36,8 @@ SYMBOLS = [
      [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _vp, _vp]),
     ("vpq_affine_qmm_grouped_geglu_w4g64_bf16", _i,
      [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _vp, _vp]),
+    ("vpq_affine_qmm_grouped_w8g64_bf16", _i,
+     [_i, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _vp, _vp]),
     ("vpq_affine_qmm_geglu_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     ("vpq_affine_qmm_swiglu_w8g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     ("vpq_affine_qmm_geglu_w8g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),

@@ -192,7 +192,7 @@ extern "C" size_t vpq_scale_bytes(int N, int K, int group) {
 struct vpq_function_s {
   const char* library;
   const char* entry;
-  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64, 66..69 qmv w8g64 add / swiglu / qkv / gelu*mul, 70 / 71 qmm swiglu strided store w4 / w8, 72..74 grouped qmm down / swiglu / geglu, 75 qmv norm + qkv, 76..78 gathered expert qmv swiglu / geglu / down, 79..81 qmm w4g32 / geglu w4g32 / w8g32, 82..85 qmv w4g32 add / geglu / gelu*mul / qkv, 86..88 scale-only (Q4_0) qmv w4g32 plain / add / geglu, 89 requant w8 -> w4, 90 qmv geglu w8g64, 91..93 gathered expert qmv w8g64 swiglu / geglu / down, 94 moe gate w8g64, 95 / 96 gathered split-width swiglu (gate w4 + up w8 / gate w8 + up w4); 10 + code: quant / dequant twins (see fmt_*)
+  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64, 66..69 qmv w8g64 add / swiglu / qkv / gelu*mul, 70 / 71 qmm swiglu strided store w4 / w8, 72..74 grouped qmm down / swiglu / geglu, 75 qmv norm + qkv, 76..78 gathered expert qmv swiglu / geglu / down, 79..81 qmm w4g32 / geglu w4g32 / w8g32, 82..85 qmv w4g32 add / geglu / gelu*mul / qkv, 86..88 scale-only (Q4_0) qmv w4g32 plain / add / geglu, 89 requant w8 -> w4, 90 qmv geglu w8g64, 91..93 gathered expert qmv w8g64 swiglu / geglu / down, 94 moe gate w8g64, 95 / 96 gathered split-width swiglu (gate w4 + up w8 / gate w8 + up w4), 97..99 grouped qmm w8g64 down / swiglu / geglu; 10 + code: quant / dequant twins (see fmt_*)
 };
 
 // The reference selects the element type with the library-name suffix and
@@ -256,6 +256,9 @@ static const vpq_function_s g_functions[] = {
     {"affine_qmm_steel_bf16", "affine_qmm_grouped_w4g64", 72},
     {"affine_qmm_steel_bf16", "affine_qmm_grouped_swiglu_w4g64", 73},
     {"affine_qmm_steel_bf16", "affine_qmm_grouped_geglu_w4g64", 74},
+    {"affine_qmm_steel_bf16", "affine_qmm_grouped_w8g64", 97},
+    {"affine_qmm_steel_bf16", "affine_qmm_grouped_swiglu_w8g64", 98},
+    {"affine_qmm_steel_bf16", "affine_qmm_grouped_geglu_w8g64", 99},
     {"affine_qmm_steel_bf16", "affine_qmm_geglu_w4g64", 63},
     {"affine_qmm_steel_bf16", "affine_qmm_steel_w4g32", 79},
     {"affine_qmm_steel_bf16", "affine_qmm_geglu_w4g32", 80},
@@ -348,6 +351,16 @@ extern "C" int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* a, 
                                                      const_cast<void*>(b[4]), a->K, a->N, a->M,
                                                      static_cast<const int*>(b[8]), static_cast<const int*>(b[9]),
                                                      a->experts, a->rows, const_cast<void*>(b[10]), stream);
+    case 97:
+      return vpq_affine_qmm_grouped_w8g64_bf16(0, static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
+                                               const_cast<void*>(b[4]), a->K, a->N, a->M, static_cast<const int*>(b[8]),
+                                               static_cast<const int*>(b[9]), a->experts, a->rows, nullptr, stream);
+    case 98:
+    case 99:
+      return vpq_affine_qmm_grouped_w8g64_bf16(fn->kind == 98 ? 1 : 2, static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3],
+                                               const_cast<void*>(b[4]), a->K, a->N, a->M, static_cast<const int*>(b[8]),
+                                               static_cast<const int*>(b[9]), a->experts, a->rows,
+                                               const_cast<void*>(b[10]), stream);
     case 79:
     case 80:
     case 81:

@@ -47,10 +47,10 @@ constexpr int kBStages = 3;   // dequantised B ring
 constexpr int kEpiWarps = 4;
 constexpr int kDqWarpsMax = 8;
 
-template <int BN>
+template <int BN, int BITS = 4>
 struct SmemLayout {
   static constexpr int kXBytes = BM * BK * 2;       // 16 KB, 128B-swizzled
-  static constexpr int kCodeBytes = BN * (BK / 2);  // BN rows x 32 B
+  static constexpr int kCodeBytes = BN * (BK * BITS / 8);  // BN rows x 32 B (64 B at 8 bits)
   static constexpr int kBBytes = BN * BK * 2;       // 128B-swizzled K-major
   static constexpr int kOffX = 0;
   static constexpr int kOffB = kOffX + kStages * kXBytes;
@@ -279,13 +279,14 @@ __device__ __forceinline__ float gelu_tanh_f(float x) {
 }
 
 // kAct 0: y [.., N]; 1 / 2: columns 2j, 2j + 1 are gate j, up j, y [.., N / 2] = silu / gelu(gate) * up.
-template <int BN, int kAct>
+template <int BN, int kAct, int BITS>
 __global__ void __launch_bounds__(32 * (kEpiWarps + 2 + BN / 32), 1)
 affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
                         const __grid_constant__ CUtensorMap tmap_w,
                         const uint16_t* __restrict__ scales, const uint16_t* __restrict__ biases,
                         __nv_bfloat16* __restrict__ y, int M, int N, int K, const GroupSpec G) {
-  using L = SmemLayout<BN>;
+  using L = SmemLayout<BN, BITS>;
+  static_assert(L::kAlloc <= 227 * 1024, "shared memory of the single-CTA kernel");
   constexpr int kDqWarps = BN / 32;
   static_assert(kDqWarps <= kDqWarpsMax, "tile too wide");
   constexpr uint32_t kTmemCols = 2 * BN;  // two accumulator buffers (power of two >= 32)
@@ -364,7 +365,7 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
           if (!mbar_wait(bar_empty(s), ph ^ 1u, (1u << 8) | kRoleTma, abort_flag, &g_qmm_status)) { ok = false; break; }
           mbar_expect_tx(bar_full(s), L::kXBytes + L::kCodeBytes);
           tma_load_2d(base + L::kOffX + s * L::kXBytes, &tmap_x, bar_full(s), kb * BK, m0);
-          tma_load_2d(base + L::kOffCode + s * L::kCodeBytes, &tmap_w, bar_full(s), kb * (BK / 8), w_row0);
+          tma_load_2d(base + L::kOffCode + s * L::kCodeBytes, &tmap_w, bar_full(s), kb * (BK * BITS / 32), w_row0);
         }
       }
       // Never leave with a copy still in flight: wait for the last load of every stage.
@@ -439,21 +440,36 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
         sst.get(kb, sc, bi);
         if (!warp_wait(bar_full(s), ph, (1u << 8) | kRoleDq, abort_flag, &g_qmm_status)) { ok = false; break; }
         const uint4* cp = reinterpret_cast<const uint4*>(base_ptr + L::kOffCode + s * L::kCodeBytes +
-                                                         t_row * (BK / 2));
-        const uint4 c0 = cp[0], c1 = cp[1];
-        __syncwarp();
-        if (lane == 0) { mbar_arrive(bar_empty(s)); }  // codes are in registers
-
+                                                         t_row * (BK * BITS / 8));
         uint32_t o[32];
-        const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
         float s_133, s_129;
-        if (dequant_scale_up(sc, s_133, s_129)) {
-          const uint64_t s2 = pack_f32x2(s_133, s_129), b2 = pack_f32x2(bi, bi);
+        if (BITS == 4) {
+          const uint4 c0 = cp[0], c1 = cp[1];
+          __syncwarp();
+          if (lane == 0) { mbar_arrive(bar_empty(s)); }  // codes are in registers
+          const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+          if (dequant_scale_up(sc, s_133, s_129)) {
+            const uint64_t s2 = pack_f32x2(s_133, s_129), b2 = pack_f32x2(bi, bi);
 #pragma unroll
-          for (int wd = 0; wd < 8; ++wd) { dequant_word_fast(cw[wd], s2, b2, o + 4 * wd); }
-        } else {
+            for (int wd = 0; wd < 8; ++wd) { dequant_word_fast(cw[wd], s2, b2, o + 4 * wd); }
+          } else {
 #pragma unroll
-          for (int wd = 0; wd < 8; ++wd) { dequant_word_exact(cw[wd], sc, bi, o + 4 * wd); }
+            for (int wd = 0; wd < 8; ++wd) { dequant_word_exact(cw[wd], sc, bi, o + 4 * wd); }
+          }
+        } else {  // a byte per value: 16 words (see dequant_word8_fast)
+          const uint4 c0 = cp[0], c1 = cp[1], c2 = cp[2], c3 = cp[3];
+          __syncwarp();
+          if (lane == 0) { mbar_arrive(bar_empty(s)); }
+          const uint32_t cw[16] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w,
+                                   c2.x, c2.y, c2.z, c2.w, c3.x, c3.y, c3.z, c3.w};
+          if (dequant_scale_up(sc, s_133, s_129)) {
+            const uint64_t s2 = pack_f32x2(s_133, s_133), b2 = pack_f32x2(bi, bi);
+#pragma unroll
+            for (int wd = 0; wd < 16; ++wd) { dequant_word8_fast(cw[wd], s2, b2, o + 2 * wd); }
+          } else {
+#pragma unroll
+            for (int wd = 0; wd < 16; ++wd) { dequant_word8_exact(cw[wd], sc, bi, o + 2 * wd); }
+          }
         }
 
         if (!warp_wait(bar_bempty(t), bph ^ 1u, (2u << 8) | kRoleDq, abort_flag, &g_qmm_status)) { ok = false; break; }
@@ -562,20 +578,20 @@ affine_qmm_w4g64_kernel(const __grid_constant__ CUtensorMap tmap_x,
 #include "qmm_2cta.cuh"
 
 // ------------------------------------------------------------- host side
-template <int BN, int kAct>
+template <int BN, int kAct, int BITS = 4>
 int launch_qmm_act(const uint32_t* w, const uint16_t* scales, const uint16_t* biases, const void* x,
                    __nv_bfloat16* y, int K, int N, int M, const GroupSpec& G, cudaStream_t st) {
-  using L = SmemLayout<BN>;
+  using L = SmemLayout<BN, BITS>;
   CUtensorMap map_x, map_w;
   if (int rc = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)K, (uint64_t)M,
                            BK, BM, CU_TENSOR_MAP_SWIZZLE_128B, "x")) {
     return rc;
   }
-  if (int rc = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w, (uint64_t)(K / 8),
-                           (uint64_t)N * (uint64_t)G.experts, BK / 8, BN, CU_TENSOR_MAP_SWIZZLE_NONE, "w")) {
+  if (int rc = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w, (uint64_t)(K * BITS / 32),
+                           (uint64_t)N * (uint64_t)G.experts, BK * BITS / 32, BN, CU_TENSOR_MAP_SWIZZLE_NONE, "w")) {
     return rc;
   }
-  auto kern = affine_qmm_w4g64_kernel<BN, kAct>;
+  auto kern = affine_qmm_w4g64_kernel<BN, kAct, BITS>;
   VPQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int sms = num_sms();
@@ -953,7 +969,7 @@ extern "C" int vpq_affine_qmm_w8g64_bf16(const uint32_t* w, const void* scales, 
 namespace {
 int qmm_grouped(const char* who, int act, const uint32_t* w, const void* scales, const void* biases, const void* x,
                 void* y, int64_t K, int64_t N, int64_t M, const int* tile2e, const int* srow, const int* sdst,
-                int64_t experts, int64_t x_rows, int64_t y_rows, void* x_sorted, void* stream) {
+                int64_t experts, int64_t x_rows, int64_t y_rows, void* x_sorted, void* stream, int bits = 4) {
   clear_error();
   if (!w || !scales || !biases || !x || !y || !tile2e) { return fail(VPQ_ERR_INVALID_ARG, "%s: null pointer", who); }
   if (K <= 0 || N <= 0 || M <= 0 || (K % 64) != 0 || experts <= 0 || y_rows <= 0 || (act && (N % 2) != 0)) {
@@ -991,6 +1007,13 @@ int qmm_grouped(const char* who, int act, const uint32_t* w, const void* scales,
   const uint16_t* s16 = static_cast<const uint16_t*>(scales);
   const uint16_t* b16 = static_cast<const uint16_t*>(biases);
   __nv_bfloat16* yb = static_cast<__nv_bfloat16*>(y);
+  if (bits == 8) {
+    switch (act) {
+      case 0: return launch_qmm_act<256, 0, 8>(w, s16, b16, xs, yb, (int)K, (int)N, (int)M, G, st);
+      case 1: return launch_qmm_act<256, 1, 8>(w, s16, b16, xs, yb, (int)K, (int)N, (int)M, G, st);
+      default: return launch_qmm_act<256, 2, 8>(w, s16, b16, xs, yb, (int)K, (int)N, (int)M, G, st);
+    }
+  }
   switch (act) {
     case 0: return launch_qmm_act<256, 0>(w, s16, b16, xs, yb, (int)K, (int)N, (int)M, G, st);
     case 1: return launch_qmm_act<256, 1>(w, s16, b16, xs, yb, (int)K, (int)N, (int)M, G, st);
@@ -998,6 +1021,26 @@ int qmm_grouped(const char* who, int act, const uint32_t* w, const void* scales,
   }
 }
 }  // namespace
+
+// The grouped GEMMs over 8-bit experts (w u32 [experts * N, K/4]): act 0 down (scatter through sdst),
+// 1 SwiGLU, 2 GeGLU (row gather through srow). Replace affine_qmm_grouped_w8g64, _grouped_swiglu_w8g64,
+// _grouped_geglu_w8g64 (the 8-bit instantiations, gpu-kernels/metal/quant/affine_qmm_steel.metal:1069-1094,
+// 1290-1312,1341-1367).
+extern "C" int vpq_affine_qmm_grouped_w8g64_bf16(int act, const uint32_t* w, const void* scales, const void* biases,
+                                                 const void* x, void* y, int64_t K, int64_t N, int64_t M,
+                                                 const int* tile2e, const int* rows_map, int64_t experts,
+                                                 int64_t rows, void* x_sorted, void* stream) {
+  if (act < 0 || act > 2) {
+    clear_error();
+    return fail(VPQ_ERR_INVALID_ARG, "affine_qmm_grouped_w8g64: act must be 0 (down), 1 (swiglu) or 2 (geglu)");
+  }
+  if (act == 0) {
+    return qmm_grouped("affine_qmm_grouped_w8g64", 0, w, scales, biases, x, y, K, N, M, tile2e, nullptr, rows_map, experts, 0,
+                       rows_map ? rows : M, nullptr, stream, 8);
+  }
+  return qmm_grouped(act == 1 ? "affine_qmm_grouped_swiglu_w8g64" : "affine_qmm_grouped_geglu_w8g64", act, w, scales, biases,
+                     x, y, K, N, M, tile2e, rows_map, nullptr, experts, rows, M, x_sorted, stream, 8);
+}
 
 extern "C" int vpq_qmm_grouped_tile_rows(void) { return BM; }
 

@@ -399,38 +399,48 @@ def qmm_grouped_tile_rows() -> int:
     return int(lib().vpq_qmm_grouped_tile_rows())
 
 
-def qmm_grouped_gated(codes, scales, biases, x, tile2e, srow=None, act="swiglu", out=None, stream=None):
-    """Gate|up GEMM of a mixture of experts over sorted, padded rows: codes [E, N, K/8]; x the hidden
+def qmm_grouped_gated(codes, scales, biases, x, tile2e, srow=None, act="swiglu", out=None, stream=None, bits=4):
+    """Gate|up GEMM of a mixture of experts over sorted, padded rows: codes [E, N, K*bits/32]; x the hidden
     [T, K] with srow [M] (gathered), or already sorted [M, K] with srow None. Returns y [M, N/2] in
-    sorted order (vpq_affine_qmm_grouped_{swiglu,geglu}_w4g64_bf16)."""
+    sorted order (vpq_affine_qmm_grouped_{swiglu,geglu}_w4g64_bf16; bits=8: vpq_affine_qmm_grouped_w8g64_bf16)."""
     E, N, Kw = codes.shape
-    K = Kw * 8
+    K = Kw * 32 // bits
     M = int(srow.numel()) if srow is not None else x.numel() // K
     if out is None:
         out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
     scratch = torch.empty((M, K), dtype=torch.bfloat16, device=x.device) if srow is not None else None
-    fn = getattr(lib(), f"vpq_affine_qmm_grouped_{act}_w4g64_bf16")
+    args = (_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x), _ptr(out), K, N, M, _ptr(tile2e),
+            _ptr(srow) if srow is not None else None, E, x.numel() // K,
+            _ptr(scratch) if scratch is not None else None, _stream(stream))
     with torch.cuda.device(x.device):
-        check(fn(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x), _ptr(out), K, N, M, _ptr(tile2e),
-                 _ptr(srow) if srow is not None else None, E, x.numel() // K,
-                 _ptr(scratch) if scratch is not None else None, _stream(stream)))
+        if bits == 8:
+            check(lib().vpq_affine_qmm_grouped_w8g64_bf16({"swiglu": 1, "geglu": 2}[act], *args))
+        else:
+            check(getattr(lib(), f"vpq_affine_qmm_grouped_{act}_w4g64_bf16")(*args))
     return out
 
 
-def qmm_grouped_down(codes, scales, biases, x_sorted, tile2e, sdst=None, y_rows=0, out=None, stream=None):
+def qmm_grouped_down(codes, scales, biases, x_sorted, tile2e, sdst=None, y_rows=0, out=None, stream=None, bits=4):
     """Down GEMM of a mixture of experts: x_sorted [M, K]; row m of the product lands in row sdst[m]
-    of y [y_rows, N] (vpq_affine_qmm_grouped_w4g64_bf16). Rows of y no slot points at are not written."""
+    of y [y_rows, N] (vpq_affine_qmm_grouped_w4g64_bf16; bits=8: vpq_affine_qmm_grouped_w8g64_bf16). Rows of y
+    no slot points at are not written."""
     E, N, Kw = codes.shape
-    K = Kw * 8
+    K = Kw * 32 // bits
     M = x_sorted.numel() // K
     rows = y_rows if sdst is not None else M
     if out is None:
         out = torch.zeros((rows, N), dtype=torch.bfloat16, device=x_sorted.device)
     with torch.cuda.device(x_sorted.device):
-        check(lib().vpq_affine_qmm_grouped_w4g64_bf16(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x_sorted),
-                                                      _ptr(out), K, N, M, _ptr(tile2e),
-                                                      _ptr(sdst) if sdst is not None else None, E, rows,
-                                                      _stream(stream)))
+        if bits == 8:
+            check(lib().vpq_affine_qmm_grouped_w8g64_bf16(0, _ptr(codes), _ptr(scales), _ptr(biases), _ptr(x_sorted),
+                                                          _ptr(out), K, N, M, _ptr(tile2e),
+                                                          _ptr(sdst) if sdst is not None else None, E, rows, None,
+                                                          _stream(stream)))
+        else:
+            check(lib().vpq_affine_qmm_grouped_w4g64_bf16(_ptr(codes), _ptr(scales), _ptr(biases), _ptr(x_sorted),
+                                                          _ptr(out), K, N, M, _ptr(tile2e),
+                                                          _ptr(sdst) if sdst is not None else None, E, rows,
+                                                          _stream(stream)))
     return out
 
 
