@@ -57,6 +57,8 @@ def test_function_table_uses_reference_names(vpq):
                            ("affine_qmv_bf16", "affine_gather_qmv_geglu_w8g64"),
                            ("affine_qmv_bf16", "affine_gather_down_qmv_w8g64"),
                            ("affine_qmv_bf16", "affine_moe_gate_w8g64"),
+                           ("affine_qmv_bf16", "affine_qmv_w4g64_r8p2"),
+                           ("affine_qmv_bf16", "affine_qmv_w8g64_r8p2"),
                            ("affine_qmm_steel_bf16", "affine_qmm_grouped_w8g64"),
                            ("affine_qmm_steel_bf16", "affine_qmm_grouped_swiglu_w8g64"),
                            ("affine_qmm_steel_bf16", "affine_qmm_grouped_geglu_w8g64"),

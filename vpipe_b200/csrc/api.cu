@@ -201,6 +201,8 @@ struct vpq_function_s {
 // the shape), so their names all resolve to it.
 static const vpq_function_s g_functions[] = {
     {"affine_qmv_bf16", "affine_qmv_w4g64", 0},
+    {"affine_qmv_bf16", "affine_qmv_w4g64_r8p2", 0},   // the reference's rows-per-simdgroup tuning twins: same contract
+    {"affine_qmv_bf16", "affine_qmv_w8g64_r8p2", 58},
     {"affine_qmv_bf16", "affine_qmv_w4g64_add", 5},
     {"affine_qmv_bf16", "affine_qmv_swiglu_w4g64", 6},
     {"affine_qmv_bf16", "affine_qmv_qkv_w4g64", 7},
