@@ -57,6 +57,8 @@ def test_function_table_uses_reference_names(vpq):
                            ("affine_qmv_bf16", "affine_gather_qmv_geglu_w8g64"),
                            ("affine_qmv_bf16", "affine_gather_down_qmv_w8g64"),
                            ("affine_qmv_bf16", "affine_moe_gate_w8g64"),
+                           ("affine_qmv_bf16", "affine_qmv_qkv_rms_w8g64"),
+                           ("affine_qmv_bf16", "affine_qmv_qkv_rms_w4g32"),
                            ("affine_qmv_bf16", "affine_qmv_w4g64_r8p2"),
                            ("affine_qmv_bf16", "affine_qmv_w8g64_r8p2"),
                            ("affine_qmm_steel_bf16", "affine_qmm_grouped_w8g64"),
@@ -216,8 +218,10 @@ def test_descriptor_extensions_are_validated_on_the_host(vpq):
     d.experts = 4
     assert L.vpq_affine_qmv_batch_w4g64_bf16_fused(C.byref(d), None) == 3   # the small-batch kernel does not
     d.expert, d.experts = 0, 0
+    d.norm_w = 0x6008
+    assert L.vpq_affine_qmv_w8g64_bf16_fused(C.byref(d), None) == 2     # ... and the RMSNorm prologue (aligned weights)
+    assert L.vpq_affine_qmv_batch_w4g64_bf16_fused(C.byref(d), None) == 2   # the small-batch kernel likewise
     d.norm_w = 0x6000
-    assert L.vpq_affine_qmv_w8g64_bf16_fused(C.byref(d), None) == 3     # ... but not the RMSNorm prologue
 
 
 def test_qkv_gemm_and_format_gemm_validate_their_arguments(vpq):

@@ -464,3 +464,75 @@ def test_moe_gather_swiglu_with_gate_and_up_of_different_widths(vpq, oracle_mod,
         err = oracle_mod.err_metrics(f32(y[p:p + 1]), want)
         assert err["rel_l2"] < TOL and err["max_rel_rms"] < TOL, (p, err)
     assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("K,q_rows,k_rows,v_rows", [(4096, 2048, 512, 512), (1024, 128, 32, 40), (3136, 48, 16, 16)])
+def test_qkv_with_rmsnorm_prologue_over_8_bit_weights(vpq, oracle_mod, K, q_rows, k_rows, v_rows):
+    """affine_qmv_qkv_rms_w8g64 (the 8-bit instantiation of affine_qmv.metal:570-694) by the reference's
+    name and slots: the oracle's RMSNorm followed by the 8-bit GEMV oracle; and the library's own 8-bit
+    q|k|v GEMV on the oracle's normed x, equal except where 1/rms rounds differently (one bf16 ulp of x)."""
+    from test_gpu_formats import _w8_reference
+    ops = vpq.ops
+    N = q_rows + k_rows + v_rows
+    wb = synth.f32_to_bf16_bits(synth.weight_f32(N, K, 2500 + K))
+    codes, s16, b16 = oracle_mod.quant(wb, 8, 64)
+    s, b = oracle_mod.f16_to_bf16(s16), oracle_mod.f16_to_bf16(b16)
+    xb = synth.f32_to_bf16_bits(3.0 * synth.bf16_bits_to_f32(synth.activations_bf16(1, K, 2600 + K)))
+    nw = _norm_weights(K, 2700 + K)
+    eps = 1e-6
+    xn = oracle_mod.rms_norm_bf16(xb, nw, eps)
+    ref = _w8_reference(oracle_mod, codes, s, b, xn, "f64")
+    dc, ds, db = to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16)
+    dx, dnw = to_dev(xb, torch.bfloat16), to_dev(nw, torch.bfloat16)
+    z = lambda n: torch.full((1, n), float("nan"), dtype=torch.bfloat16, device=dev())  # noqa: E731
+    q, k, v = z(q_rows), z(k_rows), z(v_rows)
+    ops.dispatch(ops.function("affine_qmv_bf16", "affine_qmv_qkv_rms_w8g64"), [dc, ds, db, dx, dnw, q, k, v],
+                 K=K, q_rows=q_rows, k_rows=k_rows, v_rows=v_rows, eps=eps)
+    torch.cuda.synchronize()
+    got = np.concatenate([f32(q), f32(k), f32(v)], axis=1)
+    assert not np.isnan(got).any()
+    e = oracle_mod.err_metrics(got, ref.astype(np.float32))
+    assert e["rel_l2"] < TOL and e["max_rel_rms"] < TOL and e["max_rel_1e2"] < 2 * TOL, e
+    pq, pk, pv = z(q_rows), z(k_rows), z(v_rows)
+    ops.qmv_w8_fused(dc, ds, db, to_dev(xn, torch.bfloat16), pq,
+                     {"epilogue": "qkv", "aux": pk, "y3": pv, "q_rows": q_rows, "k_rows": k_rows})
+    same = np.mean(np.concatenate([bits16(t) for t in (pq, pk, pv)], axis=1) == np.concatenate(
+        [bits16(q), bits16(k), bits16(v)], axis=1))
+    assert same > 0.98
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("K,q_rows,k_rows,v_rows,M", [(4096, 2048, 512, 512, 1), (1024, 128, 32, 40, 2), (2080, 48, 16, 16, 1)])
+def test_qkv_with_rmsnorm_prologue_over_group_32_weights(vpq, oracle_mod, K, q_rows, k_rows, v_rows, M):
+    """affine_qmv_qkv_rms_w4g32 (the group-32 instantiation of affine_qmv.metal:570-694) by the
+    reference's name and slots, and the same prologue on rows that share one weight stream: the oracle's
+    RMSNorm followed by the group-32 GEMV oracle."""
+    from test_gpu_formats import _g32_reference
+    ops = vpq.ops
+    N = q_rows + k_rows + v_rows
+    wb = synth.f32_to_bf16_bits(synth.weight_f32(N, K, 2800 + K))
+    codes, s16, b16 = oracle_mod.quant(wb, 4, 32)
+    s, b = oracle_mod.f16_to_bf16(s16), oracle_mod.f16_to_bf16(b16)
+    xb = synth.f32_to_bf16_bits(3.0 * synth.bf16_bits_to_f32(synth.activations_bf16(M, K, 2900 + K)))
+    nw = _norm_weights(K, 3000 + K)
+    eps = 1e-6
+    xn = np.concatenate([oracle_mod.rms_norm_bf16(xb[m:m + 1], nw, eps) for m in range(M)])
+    ref = _g32_reference(oracle_mod, codes, s, b, xn, "f64")
+    dc, ds, db = to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16)
+    dx, dnw = to_dev(xb, torch.bfloat16), to_dev(nw, torch.bfloat16)
+    z = lambda n: torch.full((M, n), float("nan"), dtype=torch.bfloat16, device=dev())  # noqa: E731
+    q, k, v = z(q_rows), z(k_rows), z(v_rows)
+    ops.dispatch(ops.function("affine_qmv_bf16", "affine_qmv_qkv_rms_w4g32"), [dc, ds, db, dx, dnw, q, k, v],
+                 K=K, M=M, q_rows=q_rows, k_rows=k_rows, v_rows=v_rows, eps=eps)
+    torch.cuda.synchronize()
+    got = np.concatenate([f32(q), f32(k), f32(v)], axis=1)
+    assert not np.isnan(got).any()
+    e = oracle_mod.err_metrics(got, ref.astype(np.float32))
+    assert e["rel_l2"] < TOL and e["max_rel_rms"] < TOL and e["max_rel_1e2"] < 2 * TOL, e
+    pq, pk, pv = z(q_rows), z(k_rows), z(v_rows)
+    ops.qmv_w8_fused(dc, ds, db, to_dev(xn, torch.bfloat16), pq,
+                     {"epilogue": "qkv", "aux": pk, "y3": pv, "q_rows": q_rows, "k_rows": k_rows}, kind="g32")
+    same = np.mean(np.concatenate([bits16(t) for t in (pq, pk, pv)], axis=1) == np.concatenate(
+        [bits16(q), bits16(k), bits16(v)], axis=1))
+    assert same > 0.98
+    assert ops.device_status() == 0

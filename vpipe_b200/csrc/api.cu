@@ -192,7 +192,7 @@ extern "C" size_t vpq_scale_bytes(int N, int K, int group) {
 struct vpq_function_s {
   const char* library;
   const char* entry;
-  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64, 66..69 qmv w8g64 add / swiglu / qkv / gelu*mul, 70 / 71 qmm swiglu strided store w4 / w8, 72..74 grouped qmm down / swiglu / geglu, 75 qmv norm + qkv, 76..78 gathered expert qmv swiglu / geglu / down, 79..81 qmm w4g32 / geglu w4g32 / w8g32, 82..85 qmv w4g32 add / geglu / gelu*mul / qkv, 86..88 scale-only (Q4_0) qmv w4g32 plain / add / geglu, 89 requant w8 -> w4, 90 qmv geglu w8g64, 91..93 gathered expert qmv w8g64 swiglu / geglu / down, 94 moe gate w8g64, 95 / 96 gathered split-width swiglu (gate w4 + up w8 / gate w8 + up w4), 97..99 grouped qmm w8g64 down / swiglu / geglu; 10 + code: quant / dequant twins (see fmt_*)
+  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64, 66..69 qmv w8g64 add / swiglu / qkv / gelu*mul, 70 / 71 qmm swiglu strided store w4 / w8, 72..74 grouped qmm down / swiglu / geglu, 75 qmv norm + qkv, 76..78 gathered expert qmv swiglu / geglu / down, 79..81 qmm w4g32 / geglu w4g32 / w8g32, 82..85 qmv w4g32 add / geglu / gelu*mul / qkv, 86..88 scale-only (Q4_0) qmv w4g32 plain / add / geglu, 89 requant w8 -> w4, 90 qmv geglu w8g64, 91..93 gathered expert qmv w8g64 swiglu / geglu / down, 94 moe gate w8g64, 95 / 96 gathered split-width swiglu (gate w4 + up w8 / gate w8 + up w4), 97..99 grouped qmm w8g64 down / swiglu / geglu, 100 / 101 qmv norm + qkv w8g64 / w4g32; 10 + code: quant / dequant twins (see fmt_*)
 };
 
 // The reference selects the element type with the library-name suffix and
@@ -207,6 +207,8 @@ static const vpq_function_s g_functions[] = {
     {"affine_qmv_bf16", "affine_qmv_swiglu_w4g64", 6},
     {"affine_qmv_bf16", "affine_qmv_qkv_w4g64", 7},
     {"affine_qmv_bf16", "affine_qmv_qkv_rms_w4g64", 75},
+    {"affine_qmv_bf16", "affine_qmv_qkv_rms_w8g64", 100},
+    {"affine_qmv_bf16", "affine_qmv_qkv_rms_w4g32", 101},
     {"affine_qmv_bf16", "affine_gather_qmv_swiglu_w4g64", 76},
     {"affine_qmv_bf16", "affine_gather_qmv_geglu_w4g64", 77},
     {"affine_qmv_bf16", "affine_gather_down_qmv_w4g64", 78},
@@ -369,6 +371,8 @@ extern "C" int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* a, 
       return vpq_affine_qmm_bf16(static_cast<const uint32_t*>(b[0]), b[1], b[2], b[3], const_cast<void*>(b[4]), a->K,
                                  a->N, a->M, fn->kind == 81 ? 8 : 4, 32, fn->kind == 80 ? 2 : 0, stream);
     case 75:
+    case 100:
+    case 101:
     case 76:
     case 77:
     case 78:
@@ -383,7 +387,7 @@ extern "C" int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* a, 
       d.x = b[3];
       d.K = a->K;
       d.M = a->M < 1 ? 1 : a->M;
-      if (fn->kind == 75) {  // slot 4 = norm_w, 5..7 = q, k, v outputs, eps as a constant
+      if (fn->kind == 75 || fn->kind == 100 || fn->kind == 101) {  // slot 4 = norm_w, 5..7 = q, k, v outputs, eps as a constant
         d.norm_w = b[4];
         d.eps = a->eps;
         d.y = const_cast<void*>(b[5]);
@@ -404,7 +408,8 @@ extern "C" int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* a, 
                      : (k == 77 || k == 92) ? VPQ_EPILOGUE_GEGLU
                                             : VPQ_EPILOGUE_NONE;
       }
-      if (fn->kind >= 91) { return vpq_affine_qmv_w8g64_bf16_fused(&d, stream); }
+      if (fn->kind == 101) { return vpq_affine_qmv_w4g32_bf16_fused(&d, stream); }
+      if (fn->kind >= 91) { return vpq_affine_qmv_w8g64_bf16_fused(&d, stream); }  // 91..93, 100: 8-bit
       return vpq_affine_qmv_w4g64_bf16_batch(&d, 1, stream);
     }
     case 70:

@@ -1015,16 +1015,26 @@ int check_desc(const char* who, const vpq_linear_desc& d, bool in_plan) {
 }  // namespace
 
 // The kernels other than the 4-bit group-64 GEMV take plain descriptors only.
-int qmv_check_plain(const char* who, const vpq_linear_desc& d) {
-  if (d.norm_w || d.expert || d.depends || d.experts > 1 || d.x_div > 1) {
-    return fail(VPQ_ERR_UNSUPPORTED, "%s: norm_w, expert and depends are taken by the w4 g64 GEMV entry points only", who);
+int qmv_check_plain(const char* who, const vpq_linear_desc& d, bool allow_norm) {
+  if ((d.norm_w && !allow_norm) || d.expert || d.depends || d.experts > 1 || d.x_div > 1) {
+    return fail(VPQ_ERR_UNSUPPORTED, "%s: %sexpert and depends are taken by the w4 g64 GEMV entry points only", who,
+                allow_norm ? "" : "norm_w, ");
+  }
+  if (d.norm_w) {
+    if (!aligned16(d.norm_w)) { return fail(VPQ_ERR_ALIGNMENT, "%s: norm_w must be 16-byte aligned", who); }
+    if (!(d.eps >= 0.0f)) { return fail(VPQ_ERR_INVALID_ARG, "%s: eps must be >= 0", who); }
   }
   return qmv_check_store(who, d);
 }
 
-int qmv_check_gather(const char* who, const vpq_linear_desc& d) {
-  if (d.norm_w || d.depends) {
-    return fail(VPQ_ERR_UNSUPPORTED, "%s: norm_w and depends are taken by the w4 g64 GEMV entry points only", who);
+int qmv_check_gather(const char* who, const vpq_linear_desc& d, bool allow_norm) {
+  if ((d.norm_w && !allow_norm) || d.depends) {
+    return fail(VPQ_ERR_UNSUPPORTED, "%s: %s taken by the w4 g64 GEMV entry points only", who,
+                allow_norm ? "depends is" : "norm_w and depends are");
+  }
+  if (d.norm_w) {
+    if (!aligned16(d.norm_w)) { return fail(VPQ_ERR_ALIGNMENT, "%s: norm_w must be 16-byte aligned", who); }
+    if (!(d.eps >= 0.0f)) { return fail(VPQ_ERR_INVALID_ARG, "%s: eps must be >= 0", who); }
   }
   if (d.expert) {
     if (d.experts <= 0 || d.experts * d.N > (1ll << 30)) {

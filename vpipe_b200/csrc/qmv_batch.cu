@@ -95,6 +95,8 @@ struct alignas(64) BatchProblem {
   int y_pitch, aux_pitch, y3_pitch;  // elements between consecutive rows of x in y / aux / y3
   const uint16_t* aux;
   __nv_bfloat16* y3;
+  const uint16_t* norm_w;      // not null: every row of x is RMS-normalised with these K weights while it is staged
+  float eps;                   // RMSNorm epsilon
 };
 
 // GROUP = 64: columns = (row of x 0..3, group parity). GROUP = 32 (the reference's affine_qmv_w4g32,
@@ -206,12 +208,34 @@ affine_qmv_batch_w4_kernel(const __grid_constant__ BatchProblem P, int stages, i
     uint32_t amax[kMaxRows] = {0, 0, 0, 0};
     constexpr int kXRegs = 8;  // chunks a thread keeps in registers between the two passes
     uint4 xin[kXRegs];
-    auto load_chunk = [&](int i) {
+    auto load_raw = [&](int i) {
       const int m = i / chunks, ci = i - m * chunks;
       uint4 in = make_uint4(0, 0, 0, 0);
       if (i < total && ci * 8 < K) { in = *reinterpret_cast<const uint4*>(P.x + (size_t)m * K + ci * 8); }
       return in;
     };
+    // With norm_w every row is first RMS-normalised as the reference's fused kernel does
+    // (affine_qmv_qkv_rms_w4g32 / _w4g64, gpu-kernels/metal/quant/affine_qmv.metal:570-694): sum of
+    // squares in f32 over the row (partial sums of the warps through shared memory, the consumers'
+    // barrier), x <- bf16(x * rsqrt(mean + eps) * norm_w); scales and digits are taken from that.
+    const uint16_t* nw = P.norm_w;
+    float inv[kMaxRows] = {1.0f, 1.0f, 1.0f, 1.0f};
+    auto normalise = [&](int i, uint4 in) {
+      const int m = i / chunks, ci = i - m * chunks;
+      if (!(i < total && ci * 8 < K)) { return in; }
+      const float r = m == 0 ? inv[0] : m == 1 ? inv[1] : m == 2 ? inv[2] : inv[3];
+      const uint4 n = __ldg(reinterpret_cast<const uint4*>(nw + ci * 8));
+      const uint32_t v[4] = {in.x, in.y, in.z, in.w}, w4[4] = {n.x, n.y, n.z, n.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = __fmul_rn(__fmul_rn(__uint_as_float(v[j] << 16), r), __uint_as_float(w4[j] << 16));
+        const float hi = __fmul_rn(__fmul_rn(__uint_as_float(v[j] & 0xffff0000u), r), __uint_as_float(w4[j] & 0xffff0000u));
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[j]) : "f"(hi), "f"(lo));
+      }
+      return make_uint4(o[0], o[1], o[2], o[3]);
+    };
+    auto load_chunk = [&](int i) { return nw ? normalise(i, load_raw(i)) : load_raw(i); };
     auto fold_amax = [&](int i, const uint4& in) {
       const int m = i / chunks;
       const uint32_t v[4] = {in.x, in.y, in.z, in.w};
@@ -222,7 +246,45 @@ affine_qmv_batch_w4_kernel(const __grid_constant__ BatchProblem P, int stages, i
       for (int r = 0; r < kMaxRows; ++r) { amax[r] = (r == m) ? max(amax[r], a) : amax[r]; }
     };
 #pragma unroll
-    for (int r = 0; r < kXRegs; ++r) { xin[r] = load_chunk(threadIdx.x + r * kConsThreads); }
+    for (int r = 0; r < kXRegs; ++r) { xin[r] = load_raw(threadIdx.x + r * kConsThreads); }
+    if (nw) {
+      float sq[kMaxRows] = {0.0f, 0.0f, 0.0f, 0.0f};
+      auto fold_sq = [&](int i, const uint4& in) {
+        const int m = i / chunks;
+        const uint32_t v[4] = {in.x, in.y, in.z, in.w};
+        float a = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float lo = __uint_as_float(v[j] << 16), hi = __uint_as_float(v[j] & 0xffff0000u);
+          a = __fmaf_rn(lo, lo, a);
+          a = __fmaf_rn(hi, hi, a);
+        }
+#pragma unroll
+        for (int r = 0; r < kMaxRows; ++r) { sq[r] += (r == m) ? a : 0.0f; }
+      };
+#pragma unroll
+      for (int r = 0; r < kXRegs; ++r) { fold_sq(threadIdx.x + r * kConsThreads, xin[r]); }
+      for (int i = threadIdx.x + kXRegs * kConsThreads; i < total; i += kConsThreads) { fold_sq(i, load_raw(i)); }
+      float* sq_buf = reinterpret_cast<float*>(amax_buf);   // [kConsWarps][kMaxRows], free until the amax pass
+#pragma unroll
+      for (int r = 0; r < kMaxRows; ++r) {
+        float a = sq[r];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) { a += __shfl_xor_sync(0xffffffffu, a, o); }
+        if (lane == 0) { sq_buf[warp * kMaxRows + r] = a; }
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kConsThreads) : "memory");
+#pragma unroll
+      for (int r = 0; r < kMaxRows; ++r) {
+        float tot = 0.0f;
+#pragma unroll
+        for (int ww = 0; ww < kConsWarps; ++ww) { tot += sq_buf[ww * kMaxRows + r]; }
+        inv[r] = __frsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)K), P.eps));
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kConsThreads) : "memory");  // sq_buf is read: the amax pass may reuse it
+#pragma unroll
+      for (int r = 0; r < kXRegs; ++r) { xin[r] = normalise(threadIdx.x + r * kConsThreads, xin[r]); }
+    }
 #pragma unroll
     for (int r = 0; r < kXRegs; ++r) { fold_amax(threadIdx.x + r * kConsThreads, xin[r]); }
     for (int i = threadIdx.x + kXRegs * kConsThreads; i < total; i += kConsThreads) { fold_amax(i, load_chunk(i)); }
@@ -519,6 +581,8 @@ int launch_batch(const char* who, const vpq_linear_desc& d, int per_pass, cudaSt
   // scale / bias rows as TMA boxes: pitch and base multiples of 16 bytes
   p.scales_tma = ((K / GROUP) % 8 == 0 && aligned16(scales) && aligned16(biases)) ? 1 : 0;
   p.scale_only = scale_only ? 1 : 0;
+  p.norm_w = static_cast<const uint16_t*>(d.norm_w);
+  p.eps = d.eps;
   if (p.scales_tma) {
     if (int rc = make_map_2d(&p.ms, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, (uint64_t)(K / GROUP), (uint64_t)N, GPS,
                              16, CU_TENSOR_MAP_SWIZZLE_NONE, "scales")) {
@@ -635,7 +699,7 @@ vpq_linear_desc plain_desc(const uint32_t* w, const void* scales, const void* bi
 
 int batch_g64(const char* who, const vpq_linear_desc& d, void* stream) {
   if (int rc = check_batch_args(who, d.w, d.scales, d.biases, d.x, d.y, d.K, d.N, d.M, 64)) { return rc; }
-  if (int rc = qmv_check_plain(who, d)) { return rc; }
+  if (int rc = qmv_check_plain(who, d, /*allow_norm=*/true)) { return rc; }
   if (int rc = require_sm100()) { return rc; }
   const int per_pass = rows_per_pass<64>((int)((d.K + 255) / 256) * 2);
   if (per_pass < 2 || d.M == 1) {  // long rows (K > 8192) do not fit twice in shared memory: one row at a time
@@ -649,7 +713,7 @@ int gemv_g32(const char* who, const vpq_linear_desc& d, void* stream, bool scale
   if (int rc = check_batch_args(who, d.w, d.scales, scale_only ? d.scales : d.biases, d.x, d.y, d.K, d.N, d.M, 32)) {
     return rc;
   }
-  if (int rc = qmv_check_plain(who, d)) { return rc; }
+  if (int rc = qmv_check_plain(who, d, /*allow_norm=*/true)) { return rc; }
   if (int rc = require_sm100()) { return rc; }
   const int per_pass = rows_per_pass<32>((int)((d.K + 255) / 256) * 2);  // 2 rows per weight stream where they fit
   return launch_batch<32>(who, d, per_pass, static_cast<cudaStream_t>(stream), false, scale_only);

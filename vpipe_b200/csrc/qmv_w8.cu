@@ -74,6 +74,8 @@ struct alignas(64) Problem8 {
   __nv_bfloat16* y3;
   const int32_t* eid;          // not null: *eid is the expert whose [N, K] slab of w / scales / biases is used
   int experts;                 // slabs in w (eid is clamped to it)
+  float eps;                   // RMSNorm epsilon
+  const uint16_t* norm_w;      // not null: x is RMS-normalised with these K weights while it is staged
 };
 
 __global__ void __launch_bounds__(kThreads, 2)
@@ -94,6 +96,8 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
   float* xu = reinterpret_cast<float*>(red_cnt + kRedSlots);     // [cap_kt] 1 / scale of every 128-k box of x
   uint64_t* bars = reinterpret_cast<uint64_t*>(xu + ((cap_kt + 1) & ~1));
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * kMaxStages);
+  uint32_t* sq_cnt = const_cast<uint32_t*>(abort_flag) + 1;      // consumer warps that posted their sum of squares
+  float* sq_part = reinterpret_cast<float*>(sq_cnt + 3);         // [kConsWarps]
   const uint32_t bar0 = smem_u32(bars);
   auto bar_full = [&](int s) { return bar0 + 8u * s; };
   auto bar_empty = [&](int s) { return bar0 + 8u * (kMaxStages + s); };
@@ -113,6 +117,7 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
       mbar_init(bar_empty(s), kConsWarps);
     }
     *abort_flag = 0;
+    *sq_cnt = 0;
     for (int i = 0; i < kRedSlots; ++i) { red_cnt[i] = 0; }
     fence_mbar_init();
   }
@@ -177,6 +182,51 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
   // value is rounded to an integer X (exact within 2^-14 of the box's maximum, off by at most
   // 2^-22 of it otherwise), X = d0 + 256 d1 + 65536 d2 with digits in [-128, 127]; digit plane d
   // of k tile kt holds the 128 bytes d(X[128 kt .. 128 kt + 127]) in order. xu[kt] = 1 / scale.
+  // With norm_w the vector is first RMS-normalised as the reference's fused kernel does
+  // (affine_qmv_qkv_rms_w8g64, the 8-bit instantiation of gpu-kernels/metal/quant/affine_qmv.metal:570-694):
+  // sum of squares in f32 over the whole vector (the eight consumer warps exchange partial sums through
+  // shared memory: post, count, bounded wait), x <- bf16(x * rsqrt(mean + eps) * norm_w).
+  float inv = 1.0f;
+  if (P.norm_w) {
+    float sq = 0.0f;
+    for (int k0 = (warp * 32 + lane) * 8; k0 < K; k0 += kConsThreads * 8) {
+      const uint4 in = *reinterpret_cast<const uint4*>(P.x + k0);
+      const uint32_t v[4] = {in.x, in.y, in.z, in.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float lo = __uint_as_float(v[q] << 16), hi = __uint_as_float(v[q] & 0xffff0000u);
+        sq = __fmaf_rn(lo, lo, sq);
+        sq = __fmaf_rn(hi, hi, sq);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { sq += __shfl_xor_sync(0xffffffffu, sq, o); }
+    uint32_t all = 1;
+    if (lane == 0) {
+      sq_part[warp] = sq;
+      __threadfence_block();
+      atomicAdd(sq_cnt, 1u);
+      all = 0;
+      for (uint32_t i = 0; i < (1u << 28); ++i) {
+        if (*reinterpret_cast<volatile uint32_t*>(sq_cnt) >= (uint32_t)kConsWarps) {
+          all = 1;
+          break;
+        }
+        if (*abort_flag) { break; }
+      }
+      if (!all) {
+        *abort_flag = 1;
+        atomicCAS(&g_qmv8_status, 0u, (4u << 8) | kRoleConsumer);
+      }
+      __threadfence_block();
+    }
+    all = __shfl_sync(0xffffffffu, all, 0);
+    if (!all) { return; }
+    float total = 0.0f;
+#pragma unroll
+    for (int ww = 0; ww < kConsWarps; ++ww) { total += *reinterpret_cast<volatile float*>(&sq_part[ww]); }
+    inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)K), P.eps));
+  }
   {
     const int quarter = lane >> 3, sub = lane & 7;
     const int passes = (SPT + 3) >> 2;  // four boxes of this warp per pass
@@ -189,7 +239,22 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
         in0 = *reinterpret_cast<const uint4*>(P.x + k0);
         in1 = *reinterpret_cast<const uint4*>(P.x + k0 + 8);
       }
-      const uint32_t v[8] = {in0.x, in0.y, in0.z, in0.w, in1.x, in1.y, in1.z, in1.w};
+      uint32_t v[8] = {in0.x, in0.y, in0.z, in0.w, in1.x, in1.y, in1.z, in1.w};
+      if (P.norm_w) {
+        uint4 n0 = make_uint4(0, 0, 0, 0), n1 = n0;
+        if (k0 < K) {
+          n0 = __ldg(reinterpret_cast<const uint4*>(P.norm_w + k0));
+          n1 = __ldg(reinterpret_cast<const uint4*>(P.norm_w + k0 + 8));
+        }
+        const uint32_t nv[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float lo = __fmul_rn(__fmul_rn(__uint_as_float(v[q] << 16), inv), __uint_as_float(nv[q] << 16));
+          const float hi = __fmul_rn(__fmul_rn(__uint_as_float(v[q] & 0xffff0000u), inv),
+                                     __uint_as_float(nv[q] & 0xffff0000u));
+          v[q] = pack_bf16x2(lo, hi);
+        }
+      }
       uint32_t amax = 0;  // largest |x| of the box as bf16 bits
 #pragma unroll
       for (int q = 0; q < 8; ++q) { amax = max(amax, max(v[q] & 0x7fffu, (v[q] >> 16) & 0x7fffu)); }
@@ -358,7 +423,8 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
 
 size_t fixed_smem(int cap_kt) {
   return 1024 /*alignment slack*/ + 128 + (size_t)cap_kt * kXBytesPerKt + (size_t)((2 * cap_kt + 3) & ~3) * 4 + 16 +
-         (size_t)kRedSlots * kConsWarps * 16 * 4 + kRedSlots * 4 + (size_t)((cap_kt + 1) & ~1) * 4 + 2 * kMaxStages * 8 + 16;
+         (size_t)kRedSlots * kConsWarps * 16 * 4 + kRedSlots * 4 + (size_t)((cap_kt + 1) & ~1) * 4 + 2 * kMaxStages * 8 + 16 +
+         kConsWarps * 4 /* partial sums of squares */;
 }
 
 }  // namespace
@@ -398,7 +464,7 @@ int launch_w8(const char* who, const vpq_linear_desc& d, void* stream) {
       (reinterpret_cast<uintptr_t>(biases) & 1) || (reinterpret_cast<uintptr_t>(y) & 1)) {
     return fail(VPQ_ERR_ALIGNMENT, "%s: w and x must be 16-byte aligned", who);
   }
-  if (int rc = qmv_check_gather(who, d)) { return rc; }
+  if (int rc = qmv_check_gather(who, d, /*allow_norm=*/true)) { return rc; }
   if (int rc = require_sm100()) { return rc; }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Problem8 p;
@@ -440,6 +506,8 @@ int launch_w8(const char* who, const vpq_linear_desc& d, void* stream) {
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), granted, smem)) { return rc; }
   const int cap = 2 * num_sms();
   p.experts = d.expert ? (int)d.experts : 1;
+  p.norm_w = static_cast<const uint16_t*>(d.norm_w);
+  p.eps = d.eps;
   for (int64_t m = 0; m < M; ++m) {  // every row streams the weight again, as in the reference
     // expert gather: row m is a (token, expert) pair; the pairs of one token share its x row
     const int64_t x_row = (d.expert && d.x_div > 1) ? m / d.x_div : m;

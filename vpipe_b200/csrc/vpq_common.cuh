@@ -74,9 +74,9 @@ int qmv8_status_read(cudaStream_t st, uint32_t* out);
 // The fused-store part of a GEMV descriptor's validation (epilogue code, aux / y3 / row counts).
 int qmv_check_store(const char* who, const vpq_linear_desc& d);
 // Same, and rejects the RMSNorm prologue, expert gather and plan dependency of the w4 g64 GEMV.
-int qmv_check_plain(const char* who, const vpq_linear_desc& d);
-// Same, but the expert gather (expert, experts, x_div) is allowed and validated.
-int qmv_check_gather(const char* who, const vpq_linear_desc& d);
+int qmv_check_plain(const char* who, const vpq_linear_desc& d, bool allow_norm = false);
+// Same, but the expert gather (expert, experts, x_div) is allowed and validated; allow_norm: norm_w too.
+int qmv_check_gather(const char* who, const vpq_linear_desc& d, bool allow_norm = false);
 // Same for the cross-GPU barrier of the fused column-split (nsplit.cu).
 int nsplit_status_read(cudaStream_t st, uint32_t* out);
 
