@@ -241,6 +241,11 @@ int vpq_affine_qmv_w4g64_bf16_batch(const vpq_linear_desc* descs_host, int count
  * (affine_qmv.metal:957-994,1290-1322,1519-1548). norm_w and depends are not taken. */
 int vpq_affine_qmv_w8g64_bf16_fused(const vpq_linear_desc* desc_host, void* stream);
 
+/* The same GEMV over 8-bit weights in groups of 32 (scales / biases [N, K/32], K % 32 == 0): the 8-bit
+ * layers of GGUF repacks. One descriptor, any VPQ_EPILOGUE_*, norm_w and the expert gather as above.
+ * Replaces affine_qmv_w8g32 (gpu-kernels/metal/quant/affine_qmv.metal:3050-3066). */
+int vpq_affine_qmv_w8g32_bf16_fused(const vpq_linear_desc* desc_host, void* stream);
+
 /* The shared-expert gate of a mixture-of-experts block: out[m] = sigmoid(dequant(w) . x[m]) for ONE
  * 8-bit group-64 weight row (w u32 [K/4], scales / biases [K/64]) and M rows of x; out bf16 [M].
  * Slots 0..4 = w, scales, biases, x, out; K as a constant. Replaces affine_moe_gate_w8g64

@@ -59,6 +59,7 @@ def test_function_table_uses_reference_names(vpq):
                            ("affine_qmv_bf16", "affine_moe_gate_w8g64"),
                            ("affine_qmv_bf16", "affine_qmv_qkv_rms_w8g64"),
                            ("affine_qmv_bf16", "affine_qmv_qkv_rms_w4g32"),
+                           ("affine_qmv_bf16", "affine_qmv_w8g32"),
                            ("affine_qmv_bf16", "affine_qmv_w4g64_r8p2"),
                            ("affine_qmv_bf16", "affine_qmv_w8g64_r8p2"),
                            ("affine_qmm_steel_bf16", "affine_qmm_grouped_w8g64"),
@@ -149,6 +150,7 @@ def test_argument_validation_happens_before_any_device_work(vpq):
     assert L.vpq_affine_qmm_swiglu_w8g64_bf16(p16, p16, p16, p16, p16, 96, 8, 4, None) == INVALID
     assert L.vpq_affine_qmm_geglu_w8g64_bf16(None, p16, p16, p16, p16, 64, 8, 4, None) == INVALID
     assert L.vpq_affine_qmv_w8g64_bf16_fused(None, None) == INVALID
+    assert L.vpq_affine_qmv_w8g32_bf16_fused(None, None) == INVALID
     assert L.vpq_affine_moe_gate_w8g64_bf16(p16, p16, p16, p16, p16, 96, 1, None) == INVALID   # K % 64
     assert L.vpq_affine_qmv_batch_w4g64_bf16_fused(None, None) == INVALID
     assert L.vpq_affine_qmv_w4g32_bf16_fused(None, None) == INVALID

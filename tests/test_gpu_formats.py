@@ -300,3 +300,35 @@ def test_dequant_w4g32_and_geglu_w8_by_name(vpq, oracle_mod, golden_dir):
     vpq.ops.dispatch(vpq.ops.function("affine_qmv_bf16", "affine_qmv_geglu_w8g64"), {0: d[0], 1: d[1], 2: d[2], 3: d[3], 4: got},
                      K=K, N=N, M=M)
     assert torch.equal(got, want) and float(got.float().abs().max()) > 0
+
+
+def _w8g32_reference(oracle_mod, codes, s_bf16, b_bf16, x_bits, mode="f64"):
+    N, Kw = codes.shape
+    q = codes.view(np.uint8).reshape(N, Kw * 4).astype(np.float32)
+    s = np.repeat(synth.bf16_bits_to_f32(s_bf16), 32, axis=1)
+    b = np.repeat(synth.bf16_bits_to_f32(b_bf16), 32, axis=1)
+    return oracle_mod.matmul_f32(x_bits, (s * q + b).astype(np.float32), mode)
+
+
+@pytest.mark.parametrize("K,N,M", [(4096, 4096, 1), (12288, 512, 1), (1024, 1024, 2), (2080, 40, 1), (32, 8, 1),
+                                   (352, 33, 2), (1280, 4099, 1)])
+def test_qmv_w8g32_matches_fp32_oracle(vpq, oracle_mod, K, N, M):
+    """affine_qmv_w8g32 (affine_qmv.metal:3050-3066): the quantizer's 8-bit group-32 output through the
+    GEMV, against the fp32 dequantise-then-matmul oracle; K values with and without whole 256-k spans
+    (scale rows as TMA boxes or as plain loads), ragged N; by the reference's name; a fused store."""
+    wb = synth.f32_to_bf16_bits(synth.weight_f32(N, K, synth.seed_for("w8g32", K, N)))
+    codes, s16, b16 = oracle_mod.quant(wb, 8, 32)
+    s, b = oracle_mod.f16_to_bf16(s16), oracle_mod.f16_to_bf16(b16)
+    x = synth.activations_bf16(M, K, synth.seed_for("w8g32x", K, N))
+    d = (to_dev(codes), to_dev(s, torch.bfloat16), to_dev(b, torch.bfloat16), to_dev(x, torch.bfloat16))
+    y = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+    vpq.ops.qmv_w8_fused(*d, y, {"epilogue": "none"}, kind="w8g32")
+    assert not torch.isnan(y.float()).any()
+    e = oracle_mod.err_metrics(y.float().cpu().numpy(), _w8g32_reference(oracle_mod, codes, s, b, x).astype(np.float32))
+    assert e["rel_l2"] < 1e-2 and e["max_rel_rms"] < 1e-2, e
+    y2 = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+    vpq.ops.dispatch(vpq.ops.function("affine_qmv_bf16", "affine_qmv_w8g32"), list(d) + [y2], K=K, N=N, M=M)
+    assert torch.equal(y2, y)
+    aux = to_dev(synth.activations_bf16(M, N, 7400 + N), torch.bfloat16)
+    y3 = vpq.ops.qmv_w8_fused(*d, torch.zeros_like(y), {"epilogue": "add", "aux": aux}, kind="w8g32")
+    assert torch.equal(y3, (y.float() + aux.float()).to(torch.bfloat16))

@@ -54,6 +54,7 @@ SYMBOLS = [
     ("vpq_affine_qmv_qkv_w4g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
     ("vpq_affine_qmv_w4g64_bf16_batch", _i, [_vp, _i, _vp]),
     ("vpq_affine_qmv_w8g64_bf16_fused", _i, [_vp, _vp]),
+    ("vpq_affine_qmv_w8g32_bf16_fused", _i, [_vp, _vp]),
     ("vpq_affine_moe_gate_w8g64_bf16", _i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp]),
     ("vpq_affine_qmv_batch_w4g64_bf16_fused", _i, [_vp, _vp]),
     ("vpq_affine_qmv_w4g32_bf16_fused", _i, [_vp, _vp]),

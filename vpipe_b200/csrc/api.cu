@@ -192,7 +192,7 @@ extern "C" size_t vpq_scale_bytes(int N, int K, int group) {
 struct vpq_function_s {
   const char* library;
   const char* entry;
-  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64, 66..69 qmv w8g64 add / swiglu / qkv / gelu*mul, 70 / 71 qmm swiglu strided store w4 / w8, 72..74 grouped qmm down / swiglu / geglu, 75 qmv norm + qkv, 76..78 gathered expert qmv swiglu / geglu / down, 79..81 qmm w4g32 / geglu w4g32 / w8g32, 82..85 qmv w4g32 add / geglu / gelu*mul / qkv, 86..88 scale-only (Q4_0) qmv w4g32 plain / add / geglu, 89 requant w8 -> w4, 90 qmv geglu w8g64, 91..93 gathered expert qmv w8g64 swiglu / geglu / down, 94 moe gate w8g64, 95 / 96 gathered split-width swiglu (gate w4 + up w8 / gate w8 + up w4), 97..99 grouped qmm w8g64 down / swiglu / geglu, 100 / 101 qmv norm + qkv w8g64 / w4g32; 10 + code: quant / dequant twins (see fmt_*)
+  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64, 66..69 qmv w8g64 add / swiglu / qkv / gelu*mul, 70 / 71 qmm swiglu strided store w4 / w8, 72..74 grouped qmm down / swiglu / geglu, 75 qmv norm + qkv, 76..78 gathered expert qmv swiglu / geglu / down, 79..81 qmm w4g32 / geglu w4g32 / w8g32, 82..85 qmv w4g32 add / geglu / gelu*mul / qkv, 86..88 scale-only (Q4_0) qmv w4g32 plain / add / geglu, 89 requant w8 -> w4, 90 qmv geglu w8g64, 91..93 gathered expert qmv w8g64 swiglu / geglu / down, 94 moe gate w8g64, 95 / 96 gathered split-width swiglu (gate w4 + up w8 / gate w8 + up w4), 97..99 grouped qmm w8g64 down / swiglu / geglu, 100 / 101 qmv norm + qkv w8g64 / w4g32, 102 qmv w8g32; 10 + code: quant / dequant twins (see fmt_*)
 };
 
 // The reference selects the element type with the library-name suffix and
@@ -221,6 +221,7 @@ static const vpq_function_s g_functions[] = {
     {"affine_qmv_bf16", "affine_qmv_geglu_w4g64", 61},
     {"affine_qmv_bf16", "affine_qmv_gelu_mul_w4g64", 62},
     {"affine_qmv_bf16", "affine_qmv_w8g64", 58},
+    {"affine_qmv_bf16", "affine_qmv_w8g32", 102},
     {"affine_qmv_bf16", "affine_qmv_w8g64_add", 66},
     {"affine_qmv_bf16", "affine_qmv_swiglu_w8g64", 67},
     {"affine_qmv_bf16", "affine_qmv_qkv_w8g64", 68},
@@ -492,7 +493,8 @@ extern "C" int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* a, 
     case 67:
     case 68:
     case 69:
-    case 90: {
+    case 90:
+    case 102: {
       vpq_linear_desc d;
       std::memset(&d, 0, sizeof(d));
       d.w = static_cast<const uint32_t*>(b[0]);
@@ -509,6 +511,9 @@ extern "C" int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* a, 
         d.q_rows = a->q_rows;
         d.k_rows = a->k_rows;
         d.N = a->q_rows + a->k_rows + a->v_rows;
+      } else if (fn->kind == 102) {
+        d.N = a->N;
+        return vpq_affine_qmv_w8g32_bf16_fused(&d, stream);
       } else {
         d.epilogue = fn->kind == 66   ? VPQ_EPILOGUE_ADD
                      : fn->kind == 67 ? VPQ_EPILOGUE_SWIGLU

@@ -31,8 +31,15 @@ constexpr int kThreads = kConsThreads + 32;  // + producer warp
 constexpr int kBoxBytes = 16 * 128;          // one TMA box: 16 rows x 128 bytes (128 k, two groups)
 constexpr int kBoxesPerStage = 8;            // a stage spans 1024 k
 constexpr int kStageW = kBoxesPerStage * kBoxBytes;
-constexpr int kStageSZ = 2 * 16 * 32;        // scales + biases of the span: 2 x [16 rows x 16 groups]
-constexpr int kStageBytes = kStageW + kStageSZ;
+// GS: quantization group, 64 or 32 (the reference's affine_qmv_w8g32, affine_qmv.metal:3050-3066). A 128-k
+// box holds 128 / GS groups.
+template <int GS>
+struct Cfg {
+  static constexpr int kGroupsPerKt = 128 / GS;
+  static constexpr int kStageGroups = kBoxesPerStage * kGroupsPerKt;   // groups a stage spans
+  static constexpr int kStageSZ = 2 * 16 * kStageGroups * 2;           // scales + biases: 2 x [16 rows x groups] bf16
+  static constexpr int kStageBytes = kStageW + kStageSZ;
+};
 constexpr int kMaxStages = 6;
 constexpr int kRedSlots = 8;
 constexpr int kXBytesPerKt = 3 * 128;        // staged x per 128-k tile: 3 digit planes of 128 bytes
@@ -78,8 +85,12 @@ struct alignas(64) Problem8 {
   const uint16_t* norm_w;      // not null: x is RMS-normalised with these K weights while it is staged
 };
 
+template <int GS>
 __global__ void __launch_bounds__(kThreads, 2)
 affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_kt) {
+  constexpr int kStageSZ = Cfg<GS>::kStageSZ;
+  constexpr int kStageBytes = Cfg<GS>::kStageBytes;
+  constexpr int GPK = Cfg<GS>::kGroupsPerKt;    // groups per 128-k tile: 2 or 4
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t raw = smem_u32(smem_dyn);
   const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled boxes need 1024-byte alignment
@@ -89,8 +100,8 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
   unsigned char* p0 = base_ptr + (size_t)stages * kStageBytes;
   uint4* zero128 = reinterpret_cast<uint4*>(p0);                 // 128 bytes of zeros, 128-byte aligned
   unsigned char* xq = p0 + 128;                                  // [cap_kt][3 digits][128 B]: digit bytes in k order
-  float* xg = reinterpret_cast<float*>(xq + (size_t)cap_kt * kXBytesPerKt);  // [2*cap_kt] sum of X per group
-  float* zero16 = xg + ((2 * cap_kt + 3) & ~3);                  // 16 bytes of zeros, 16-byte aligned (cap_kt may be odd)
+  float* xg = reinterpret_cast<float*>(xq + (size_t)cap_kt * kXBytesPerKt);  // [GPK * cap_kt] sum of X per group
+  float* zero16 = xg + ((GPK * cap_kt + 3) & ~3);                // 16 bytes of zeros, 16-byte aligned (cap_kt may be odd)
   float* red = zero16 + 4;                                       // [kRedSlots][kConsWarps][16]
   uint32_t* red_cnt = reinterpret_cast<uint32_t*>(red + kRedSlots * kConsWarps * 16);
   float* xu = reinterpret_cast<float*>(red_cnt + kRedSlots);     // [cap_kt] 1 / scale of every 128-k box of x
@@ -154,8 +165,8 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
             tma_load_2d(dst + b * kBoxBytes, &P.mw, bar_full(s), (st * kBoxesPerStage + b) * 32, row0 + tile * 16);
           }
           if (sz_tma) {
-            tma_load_2d(dst + kStageW, &P.ms, bar_full(s), st * 16, row0 + tile * 16);
-            tma_load_2d(dst + kStageW + kStageSZ / 2, &P.mz, bar_full(s), st * 16, row0 + tile * 16);
+            tma_load_2d(dst + kStageW, &P.ms, bar_full(s), st * Cfg<GS>::kStageGroups, row0 + tile * 16);
+            tma_load_2d(dst + kStageW + kStageSZ / 2, &P.mz, bar_full(s), st * Cfg<GS>::kStageGroups, row0 + tile * 16);
           }
         }
       }
@@ -294,8 +305,12 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
         }
       }
       sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      if (live && (sub & 3) == 0) { xg[kt * 2 + (sub >> 2)] = (float)(int)sum; }
+      if (GS == 64) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if (live && (sub & 3) == 0) { xg[kt * 2 + (sub >> 2)] = (float)(int)sum; }
+      } else {  // a group is 32 values = two lanes' pieces
+        if (live && (sub & 1) == 0) { xg[kt * 4 + (sub >> 1)] = (float)(int)sum; }
+      }
       if (live && sub == 0) { xu[kt] = __uint_as_float((uint32_t)(e - 21) << 23); }  // exact inverse of x_scale
     }
     __syncwarp();
@@ -306,26 +321,32 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
   // B register 0 of a lane carries its digit's bytes if the column's parity is 0, register 1 if
   // it is 1; the other register reads zeros (from a zero line, at the chunks the real reads of
   // the same quarter warp do not use).
+  // Group 32: a box has four groups, two in each 64-byte half (chunks t = 0, 1 / t = 2, 3 of a half), so
+  // every A fragment meets two B operands: one with this lane's digit bytes in the first half only (and
+  // only if its chunk lies in the column's group of that half), one likewise for the second half; the
+  // accumulator columns (digit, parity) then hold groups 0 | 1 after the first MMA, 2 | 3 after the second.
   const int digit = g >> 1, parity = g & 1;
   const bool has_digit = digit < 3;
   const unsigned char* zline = reinterpret_cast<const unsigned char*>(zero128);
-  const unsigned char* real_ptr = xq + digit * 128 + parity * 64 + t * 16;
-  const unsigned char* b0_ptr = (has_digit && parity == 0) ? real_ptr : zline + (4 + t) * 16;
-  const unsigned char* b1_ptr = (has_digit && parity == 1) ? real_ptr : zline + t * 16;
-  const int b0_kt = (has_digit && parity == 0) ? kXBytesPerKt : 0;
-  const int b1_kt = (has_digit && parity == 1) ? kXBytesPerKt : 0;
+  const bool b0_real = has_digit && (GS == 64 ? parity == 0 : (t >> 1) == parity);
+  const bool b1_real = has_digit && (GS == 64 ? parity == 1 : (t >> 1) == parity);
+  const unsigned char* b0_ptr = b0_real ? xq + digit * 128 + t * 16 : zline + (4 + t) * 16;
+  const unsigned char* b1_ptr = b1_real ? xq + digit * 128 + 64 + t * 16 : zline + t * 16;
+  const int b0_kt = b0_real ? kXBytesPerKt : 0;
+  const int b1_kt = b1_real ? kXBytesPerKt : 0;
   const bool bias_lane = t == 3;  // folds b * sum(x) where the others fold s * (digit sum)
   const float* xs_base = bias_lane ? xg : zero16;
-  const int xs_kt = bias_lane ? 2 : 0;
+  const int xs_kt = bias_lane ? GPK : 0;
   const float digit_weight = t == 1 ? 256.0f : t == 2 ? 65536.0f : 1.0f;
 
   const uint32_t off_lo = (uint32_t)rho * 128u + (uint32_t)(((0 + t) ^ rho) << 4);  // k 16 t .. of the first group
   const uint32_t off_hi = (uint32_t)rho * 128u + (uint32_t)(((4 + t) ^ rho) << 4);  // k 64 + 16 t .. of the second
-  // 4 bytes = the 2 groups of this warp's box, row rho, in the stage's scales or biases
-  const uint32_t sz_off = (uint32_t)kStageW + (bias_lane ? (uint32_t)kStageSZ / 2 : 0u) + (uint32_t)rho * 32u +
-                          (uint32_t)warp * 4u;
+  // 4 (8) bytes = the 2 (4) groups of this warp's box, row rho, in the stage's scales or biases
+  constexpr uint32_t kSzRow = (uint32_t)Cfg<GS>::kStageGroups * 2u;   // bytes of one row of the stage's scales
+  const uint32_t sz_off = (uint32_t)kStageW + (bias_lane ? (uint32_t)kStageSZ / 2 : 0u) + (uint32_t)rho * kSzRow +
+                          (uint32_t)warp * (2u * GPK);
   const bool sz_tma = P.scales_tma != 0;
-  const int G = K >> 6;
+  const int G = K / GS;
 
   uint32_t tile_seq = 0, ph = 0;
   int s = 0;
@@ -347,36 +368,71 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
         const uint4 rb_hi = *reinterpret_cast<const uint4*>(box + off_hi + 1024);
         const uint4 x0 = *reinterpret_cast<const uint4*>(b0_ptr + (size_t)kt * b0_kt);
         const uint4 x1 = *reinterpret_cast<const uint4*>(b1_ptr + (size_t)kt * b1_kt);
-        uint32_t sa, sb2;  // the two groups' scales (or biases) of rows rho, rho + 8
+        uint2 sa, sb2;  // the groups' scales (or biases) of rows rho, rho + 8: 2 in .x (group 64), 4 in .x .y (group 32)
+        sa.y = sb2.y = 0;
         if (sz_tma) {
-          sa = *reinterpret_cast<const uint32_t*>(sb + sz_off);
-          sb2 = *reinterpret_cast<const uint32_t*>(sb + sz_off + 256);
+          if (GS == 64) {
+            sa.x = *reinterpret_cast<const uint32_t*>(sb + sz_off);
+            sb2.x = *reinterpret_cast<const uint32_t*>(sb + sz_off + 8 * kSzRow);
+          } else {
+            sa = *reinterpret_cast<const uint2*>(sb + sz_off);
+            sb2 = *reinterpret_cast<const uint2*>(sb + sz_off + 8 * kSzRow);
+          }
         } else {
           // clamped onto valid data: a clamped group meets x == 0, a clamped row is never stored
           const uint16_t* src = bias_lane ? P.biases : P.scales;
           const int64_t slab = P.eid ? (int64_t)min(max(__ldg(P.eid), 0), P.experts - 1) * N : 0;
           const int64_t r_a = slab + min(tile * 16 + rho, N - 1), r_b = slab + min(tile * 16 + rho + 8, N - 1);
-          const int g0 = min(2 * kt, G - 1), g1 = min(2 * kt + 1, G - 1);
-          sa = ldg_nc_u16(src + r_a * G + g0) | (ldg_nc_u16(src + r_a * G + g1) << 16);
-          sb2 = ldg_nc_u16(src + r_b * G + g0) | (ldg_nc_u16(src + r_b * G + g1) << 16);
+          const int g0 = min(GPK * kt, G - 1), g1 = min(GPK * kt + 1, G - 1);
+          sa.x = ldg_nc_u16(src + r_a * G + g0) | (ldg_nc_u16(src + r_a * G + g1) << 16);
+          sb2.x = ldg_nc_u16(src + r_b * G + g0) | (ldg_nc_u16(src + r_b * G + g1) << 16);
+          if (GS == 32) {
+            const int g2 = min(4 * kt + 2, G - 1), g3 = min(4 * kt + 3, G - 1);
+            sa.y = ldg_nc_u16(src + r_a * G + g2) | (ldg_nc_u16(src + r_a * G + g3) << 16);
+            sb2.y = ldg_nc_u16(src + r_b * G + g2) | (ldg_nc_u16(src + r_b * G + g3) << 16);
+          }
         }
-        const float2 xs = *reinterpret_cast<const float2*>(xs_base + kt * xs_kt);
-        int ca[4], cb[4];  // two independent chains
-        mma_u8s8_first(ca, ra_lo.x, rb_lo.x, ra_hi.x, rb_hi.x, x0.x, x1.x, kAccInit);
-        mma_u8s8_first(cb, ra_lo.y, rb_lo.y, ra_hi.y, rb_hi.y, x0.y, x1.y, kAccInit);
-        mma_u8s8(ca, ra_lo.z, rb_lo.z, ra_hi.z, rb_hi.z, x0.z, x1.z);
-        mma_u8s8(cb, ra_lo.w, rb_lo.w, ra_hi.w, rb_hi.w, x0.w, x1.w);
-        // c[0] = (row rho, first group) c[1] = (rho, second) c[2] = (rho + 8, first) c[3] = (rho + 8, second);
-        // value = chain a + chain b without the two initial values (+ sum of x in a bias lane,
-        // whose accumulators hold the bare initial value)
-        const float k0 = kAccInitF - xs.x, k1 = kAccInitF - xs.y;
         auto val = [](int a, int b, float k) { return (__int_as_float(a) - kAccInitF) + (__int_as_float(b) - k); };
-        // the box's two groups folded with their scales, then its 1 / x-scale brings the sum to true units
         const float xu_box = xu[kt];
-        float box_a = __fmul_rn(__uint_as_float(sa << 16), val(ca[0], cb[0], k0));
-        box_a = __fmaf_rn(__uint_as_float(sa & 0xffff0000u), val(ca[1], cb[1], k1), box_a);
-        float box_b = __fmul_rn(__uint_as_float(sb2 << 16), val(ca[2], cb[2], k0));
-        box_b = __fmaf_rn(__uint_as_float(sb2 & 0xffff0000u), val(ca[3], cb[3], k1), box_b);
+        float box_a, box_b;
+        if (GS == 64) {
+          const float2 xs = *reinterpret_cast<const float2*>(xs_base + kt * xs_kt);
+          int ca[4], cb[4];  // two independent chains
+          mma_u8s8_first(ca, ra_lo.x, rb_lo.x, ra_hi.x, rb_hi.x, x0.x, x1.x, kAccInit);
+          mma_u8s8_first(cb, ra_lo.y, rb_lo.y, ra_hi.y, rb_hi.y, x0.y, x1.y, kAccInit);
+          mma_u8s8(ca, ra_lo.z, rb_lo.z, ra_hi.z, rb_hi.z, x0.z, x1.z);
+          mma_u8s8(cb, ra_lo.w, rb_lo.w, ra_hi.w, rb_hi.w, x0.w, x1.w);
+          // c[0] = (row rho, first group) c[1] = (rho, second) c[2] = (rho + 8, first) c[3] = (rho + 8, second);
+          // value = chain a + chain b without the two initial values (+ sum of x in a bias lane,
+          // whose accumulators hold the bare initial value)
+          const float k0 = kAccInitF - xs.x, k1 = kAccInitF - xs.y;
+          // the box's two groups folded with their scales, then its 1 / x-scale brings the sum to true units
+          box_a = __fmul_rn(__uint_as_float(sa.x << 16), val(ca[0], cb[0], k0));
+          box_a = __fmaf_rn(__uint_as_float(sa.x & 0xffff0000u), val(ca[1], cb[1], k1), box_a);
+          box_b = __fmul_rn(__uint_as_float(sb2.x << 16), val(ca[2], cb[2], k0));
+          box_b = __fmaf_rn(__uint_as_float(sb2.x & 0xffff0000u), val(ca[3], cb[3], k1), box_b);
+        } else {
+          const float4 xs = *reinterpret_cast<const float4*>(xs_base + kt * xs_kt);
+          int la[4], lb[4], ha[4], hb[4];  // first / second half of the box, two chains each
+          mma_u8s8_first(la, ra_lo.x, rb_lo.x, ra_hi.x, rb_hi.x, x0.x, 0u, kAccInit);
+          mma_u8s8_first(lb, ra_lo.y, rb_lo.y, ra_hi.y, rb_hi.y, x0.y, 0u, kAccInit);
+          mma_u8s8_first(ha, ra_lo.x, rb_lo.x, ra_hi.x, rb_hi.x, 0u, x1.x, kAccInit);
+          mma_u8s8_first(hb, ra_lo.y, rb_lo.y, ra_hi.y, rb_hi.y, 0u, x1.y, kAccInit);
+          mma_u8s8(la, ra_lo.z, rb_lo.z, ra_hi.z, rb_hi.z, x0.z, 0u);
+          mma_u8s8(lb, ra_lo.w, rb_lo.w, ra_hi.w, rb_hi.w, x0.w, 0u);
+          mma_u8s8(ha, ra_lo.z, rb_lo.z, ra_hi.z, rb_hi.z, 0u, x1.z);
+          mma_u8s8(hb, ra_lo.w, rb_lo.w, ra_hi.w, rb_hi.w, 0u, x1.w);
+          // c[0] / c[1] = row rho, groups 0 | 1 (first half) or 2 | 3 (second half); c[2] / c[3] = row rho + 8
+          const float k0 = kAccInitF - xs.x, k1 = kAccInitF - xs.y, k2 = kAccInitF - xs.z, k3 = kAccInitF - xs.w;
+          box_a = __fmul_rn(__uint_as_float(sa.x << 16), val(la[0], lb[0], k0));
+          box_a = __fmaf_rn(__uint_as_float(sa.x & 0xffff0000u), val(la[1], lb[1], k1), box_a);
+          box_a = __fmaf_rn(__uint_as_float(sa.y << 16), val(ha[0], hb[0], k2), box_a);
+          box_a = __fmaf_rn(__uint_as_float(sa.y & 0xffff0000u), val(ha[1], hb[1], k3), box_a);
+          box_b = __fmul_rn(__uint_as_float(sb2.x << 16), val(la[2], lb[2], k0));
+          box_b = __fmaf_rn(__uint_as_float(sb2.x & 0xffff0000u), val(la[3], lb[3], k1), box_b);
+          box_b = __fmaf_rn(__uint_as_float(sb2.y << 16), val(ha[2], hb[2], k2), box_b);
+          box_b = __fmaf_rn(__uint_as_float(sb2.y & 0xffff0000u), val(ha[3], hb[3], k3), box_b);
+        }
         res_a = __fmaf_rn(xu_box, box_a, res_a);
         res_b = __fmaf_rn(xu_box, box_b, res_b);
       }
@@ -421,8 +477,8 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
   }
 }
 
-size_t fixed_smem(int cap_kt) {
-  return 1024 /*alignment slack*/ + 128 + (size_t)cap_kt * kXBytesPerKt + (size_t)((2 * cap_kt + 3) & ~3) * 4 + 16 +
+size_t fixed_smem(int cap_kt, int groups_per_kt) {
+  return 1024 /*alignment slack*/ + 128 + (size_t)cap_kt * kXBytesPerKt + (size_t)((groups_per_kt * cap_kt + 3) & ~3) * 4 + 16 +
          (size_t)kRedSlots * kConsWarps * 16 * 4 + kRedSlots * 4 + (size_t)((cap_kt + 1) & ~1) * 4 + 2 * kMaxStages * 8 + 16 +
          kConsWarps * 4 /* partial sums of squares */;
 }
@@ -446,14 +502,16 @@ int qmv8_status_read(cudaStream_t st, uint32_t* out) {
 using namespace vpq;
 
 namespace {
+template <int GS>
 int launch_w8(const char* who, const vpq_linear_desc& d, void* stream) {
+  constexpr int kStageBytes = Cfg<GS>::kStageBytes;
   const uint32_t* w = d.w;
   const void *scales = d.scales, *biases = d.biases, *x = d.x;
   void* y = d.y;
   const int64_t K = d.K, N = d.N, M = d.M;
   if (!w || !scales || !biases || !x || !y) { return fail(VPQ_ERR_INVALID_ARG, "%s: null pointer", who); }
-  if (K <= 0 || N <= 0 || M <= 0 || (K % 64) != 0) {
-    return fail(VPQ_ERR_INVALID_ARG, "%s: need K>0, N>0, M>0, K%%64==0 (K=%lld N=%lld M=%lld)", who,
+  if (K <= 0 || N <= 0 || M <= 0 || (K % GS) != 0) {
+    return fail(VPQ_ERR_INVALID_ARG, "%s: need K>0, N>0, M>0, K%%%d==0 (K=%lld N=%lld M=%lld)", who, GS,
                 (long long)K, (long long)N, (long long)M);
   }
   if (K > 16384 || N > (1 << 30) || M > 65535) {
@@ -474,14 +532,15 @@ int launch_w8(const char* who, const vpq_linear_desc& d, void* stream) {
                            CU_TENSOR_MAP_SWIZZLE_128B, "w")) {
     return rc;
   }
-  p.scales_tma = ((K % 512) == 0 && aligned16(scales) && aligned16(biases)) ? 1 : 0;
+  // scale / bias rows as TMA boxes: their pitch (K / GS values of 2 bytes) and base multiples of 16 bytes
+  p.scales_tma = ((K % (8 * GS)) == 0 && aligned16(scales) && aligned16(biases)) ? 1 : 0;
   if (p.scales_tma) {
-    if (int rc = make_map_2d(&p.ms, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, (uint64_t)(K / 64), rows, 16, 16,
-                             CU_TENSOR_MAP_SWIZZLE_NONE, "scales")) {
+    if (int rc = make_map_2d(&p.ms, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, (uint64_t)(K / GS), rows,
+                             Cfg<GS>::kStageGroups, 16, CU_TENSOR_MAP_SWIZZLE_NONE, "scales")) {
       return rc;
     }
-    if (int rc = make_map_2d(&p.mz, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, biases, (uint64_t)(K / 64), rows, 16, 16,
-                             CU_TENSOR_MAP_SWIZZLE_NONE, "biases")) {
+    if (int rc = make_map_2d(&p.mz, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, biases, (uint64_t)(K / GS), rows,
+                             Cfg<GS>::kStageGroups, 16, CU_TENSOR_MAP_SWIZZLE_NONE, "biases")) {
       return rc;
     }
   }
@@ -496,12 +555,12 @@ int launch_w8(const char* who, const vpq_linear_desc& d, void* stream) {
   const bool gated = d.epilogue == VPQ_EPILOGUE_SWIGLU || d.epilogue == VPQ_EPILOGUE_GEGLU;
   const int64_t y_pitch = gated ? N / 2 : d.epilogue == VPQ_EPILOGUE_QKV ? d.q_rows : N;
   const int cap_kt = (int)((K + 127) / 128);
-  const size_t fixed = fixed_smem(cap_kt);
+  const size_t fixed = fixed_smem(cap_kt, Cfg<GS>::kGroupsPerKt);
   const size_t budget = 112 * 1024;  // two CTAs per SM
   int stages = fixed + 2 * (size_t)kStageBytes <= budget ? (int)((budget - fixed) / kStageBytes) : 2;
   if (stages > kMaxStages) { stages = kMaxStages; }
   const size_t smem = fixed + (size_t)stages * kStageBytes;
-  auto kern = affine_qmv_w8g64_kernel;
+  auto kern = affine_qmv_w8g64_kernel<GS>;
   static int granted[64] = {};
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), granted, smem)) { return rc; }
   const int cap = 2 * num_sms();
@@ -608,11 +667,18 @@ extern "C" int vpq_affine_qmv_w8g64_bf16(const uint32_t* w, const void* scales, 
   d.K = K;
   d.N = N;
   d.M = M;
-  return launch_w8("affine_qmv_w8g64", d, stream);
+  return launch_w8<64>("affine_qmv_w8g64", d, stream);
 }
 
 extern "C" int vpq_affine_qmv_w8g64_bf16_fused(const vpq_linear_desc* desc_host, void* stream) {
   clear_error();
   if (!desc_host) { return fail(VPQ_ERR_INVALID_ARG, "affine_qmv_w8g64 (fused store): null descriptor"); }
-  return launch_w8("affine_qmv_w8g64 (fused store)", *desc_host, stream);
+  return launch_w8<64>("affine_qmv_w8g64 (fused store)", *desc_host, stream);
+}
+
+// 8-bit weights in groups of 32 (scales / biases [N, K/32]): one descriptor, any VPQ_EPILOGUE_*.
+extern "C" int vpq_affine_qmv_w8g32_bf16_fused(const vpq_linear_desc* desc_host, void* stream) {
+  clear_error();
+  if (!desc_host) { return fail(VPQ_ERR_INVALID_ARG, "affine_qmv_w8g32: null descriptor"); }
+  return launch_w8<32>("affine_qmv_w8g32", *desc_host, stream);
 }

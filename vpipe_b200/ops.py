@@ -151,9 +151,10 @@ def qmv_w8_fused(codes, scales, biases, x, y, store, stream=None, kind="w8"):
     """A GEMV with a fused store through one descriptor; `store` as in qmv_set, `y` the (first) output
     tensor. kind "w8": 8-bit weights (vpq_affine_qmv_w8g64_bf16_fused); "batch": w4 g64 rows sharing one
     weight stream (vpq_affine_qmv_batch_w4g64_bf16_fused); "g32": w4 g32 (vpq_affine_qmv_w4g32_bf16_fused);
-    "q40": w4 g32 scale-only, `biases` may be None (vpq_affine_qmv_w4g32_q40_bf16_fused)."""
+    "q40": w4 g32 scale-only, `biases` may be None (vpq_affine_qmv_w4g32_q40_bf16_fused); "w8g32": 8-bit weights
+    in groups of 32 (vpq_affine_qmv_w8g32_bf16_fused)."""
     N, Kw = codes.shape
-    K = Kw * (4 if kind == "w8" else 8)
+    K = Kw * (4 if kind in ("w8", "w8g32") else 8)
     d = _lib.LinearDesc()
     d.w, d.scales, d.x, d.y = _ptr(codes), _ptr(scales), _ptr(x), _ptr(y)
     d.biases = _ptr(biases) if biases is not None else None
@@ -164,7 +165,8 @@ def qmv_w8_fused(codes, scales, biases, x, y, store, stream=None, kind="w8"):
     if store.get("y3") is not None:
         d.y3 = _ptr(store["y3"])
     d.q_rows, d.k_rows = store.get("q_rows", 0), store.get("k_rows", 0)
-    fn = {"w8": lib().vpq_affine_qmv_w8g64_bf16_fused, "batch": lib().vpq_affine_qmv_batch_w4g64_bf16_fused,
+    fn = {"w8": lib().vpq_affine_qmv_w8g64_bf16_fused, "w8g32": lib().vpq_affine_qmv_w8g32_bf16_fused,
+          "batch": lib().vpq_affine_qmv_batch_w4g64_bf16_fused,
           "g32": lib().vpq_affine_qmv_w4g32_bf16_fused, "q40": lib().vpq_affine_qmv_w4g32_q40_bf16_fused}[kind]
     with torch.cuda.device(x.device):
         check(fn(C.byref(d), _stream(stream)))
