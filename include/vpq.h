@@ -202,6 +202,19 @@ typedef struct vpq_linear_desc {
   int64_t experts;
   int32_t x_div;
   float eps;
+  /* Sorted-slot form of the expert gather (the 4- and 8-bit GEMVs): the M rows are slots of (token,
+   * expert) pairs sorted by expert and padded per expert to tiles of expert_div slots. row_map [M]
+   * (device int32) is the reference's srow: slot m is live iff row_map[m] >= 0, and also only if its
+   * tile's expert is >= 0; a dead slot's y row is not written. With row_gather = 1 slot m reads x row
+   * row_map[m] (the gate|up GEMV, which gathers from the hidden states), with 0 it reads x row m (the
+   * down GEMV over the sorted activations). Slot m multiplies slab expert[m / expert_div] (expert is then
+   * the reference's tile2e; 0 or 1: expert[m]). Replaces affine_grouped_swiglu_w4g64, affine_grouped_down_w4g64
+   * and their _w8g64 twins (slot 7 = srow, 8 = tile2e; tiles of 2 slots), gpu-kernels/metal/quant/
+   * affine_qmv.metal:2551-2719. Every live slot is one GEMV over its expert's slab here (the reference
+   * shares one weight read between the two slots of a tile). */
+  const int32_t* row_map;
+  int32_t row_gather;
+  int32_t expert_div;
 } vpq_linear_desc;
 
 /* What the GEMV does with each row's f32 sum (the reference's fused decode kernels):

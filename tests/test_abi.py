@@ -57,6 +57,10 @@ def test_function_table_uses_reference_names(vpq):
                            ("affine_qmv_bf16", "affine_gather_qmv_geglu_w8g64"),
                            ("affine_qmv_bf16", "affine_gather_down_qmv_w8g64"),
                            ("affine_qmv_bf16", "affine_moe_gate_w8g64"),
+                           ("affine_qmv_bf16", "affine_grouped_swiglu_w4g64"),
+                           ("affine_qmv_bf16", "affine_grouped_down_w4g64"),
+                           ("affine_qmv_bf16", "affine_grouped_swiglu_w8g64"),
+                           ("affine_qmv_bf16", "affine_grouped_down_w8g64"),
                            ("affine_qmv_bf16", "affine_qmv_qkv_rms_w8g64"),
                            ("affine_qmv_bf16", "affine_qmv_qkv_rms_w4g32"),
                            ("affine_qmv_bf16", "affine_qmv_w8g32"),
@@ -237,3 +241,120 @@ def test_qkv_gemm_and_format_gemm_validate_their_arguments(vpq):
     assert L.vpq_affine_qmm_bf16(p, p, p, p, p, 1024, 63, 256, 4, 32, 2, None) == 1      # a gated store needs an even N
     assert L.vpq_wait_probe(0, 1000, None) == 1
     assert L.vpq_peer_barrier_probe(None, 2, 1, 100, None) == 1
+
+
+# Every kernel entry point of the reference's quant shaders (gpu-kernels/metal/quant/*.metal, plain
+# `kernel void` definitions and the names its instantiation macros produce), bf16 libraries. The legacy
+# f16-only affine_qmm_w4g64 (library affine_qmm, which has no bf16 build) is the one name left out.
+REFERENCE_QUANT_KERNELS = [
+    ("affine_dequant_bf16", "affine_dequant_w4g32"),
+    ("affine_dequant_bf16", "affine_dequant_w4g64"),
+    ("affine_dequant_bf16", "affine_dequant_w8g32"),
+    ("affine_dequant_bf16", "affine_dequant_w8g64"),
+    ("affine_qmv_bf16", "affine_gather_down_qmv_w4g64"),
+    ("affine_qmv_bf16", "affine_gather_down_qmv_w8g64"),
+    ("affine_qmv_bf16", "affine_gather_qmv_geglu_w4g64"),
+    ("affine_qmv_bf16", "affine_gather_qmv_geglu_w8g64"),
+    ("affine_qmv_bf16", "affine_gather_qmv_swiglu_w4g64"),
+    ("affine_qmv_bf16", "affine_gather_qmv_swiglu_w4w8g64"),
+    ("affine_qmv_bf16", "affine_gather_qmv_swiglu_w8g64"),
+    ("affine_qmv_bf16", "affine_gather_qmv_swiglu_w8w4g64"),
+    ("affine_qmv_bf16", "affine_grouped_down_w4g64"),
+    ("affine_qmv_bf16", "affine_grouped_down_w8g64"),
+    ("affine_qmv_bf16", "affine_grouped_swiglu_w4g64"),
+    ("affine_qmv_bf16", "affine_grouped_swiglu_w8g64"),
+    ("affine_qmv_bf16", "affine_moe_gate_w8g64"),
+    ("affine_qmm_steel_bf16", "affine_qmm_geglu_w4g32"),
+    ("affine_qmm_steel_bf16", "affine_qmm_geglu_w4g64"),
+    ("affine_qmm_steel_bf16", "affine_qmm_geglu_w8g64"),
+    ("affine_qmm_steel_bf16", "affine_qmm_grouped_geglu_w4g64"),
+    ("affine_qmm_steel_bf16", "affine_qmm_grouped_geglu_w8g64"),
+    ("affine_qmm_steel_bf16", "affine_qmm_grouped_swiglu_w4g64"),
+    ("affine_qmm_steel_bf16", "affine_qmm_grouped_swiglu_w8g64"),
+    ("affine_qmm_steel_bf16", "affine_qmm_grouped_w4g64"),
+    ("affine_qmm_steel_bf16", "affine_qmm_grouped_w8g64"),
+    ("affine_qmm_mma_bf16", "affine_qmm_mma_w4g64"),
+    ("affine_qmm_steel_bf16", "affine_qmm_steel_w4g32"),
+    ("affine_qmm_steel_bf16", "affine_qmm_steel_w4g64"),
+    ("affine_qmm_steel_bf16", "affine_qmm_steel_w4g64_bm128"),
+    ("affine_qmm_steel_bf16", "affine_qmm_steel_w4g64_bm64"),
+    ("affine_qmm_steel_bf16", "affine_qmm_steel_w4g64_bm64_acc16"),
+    ("affine_qmm_steel_bf16", "affine_qmm_steel_w8g32"),
+    ("affine_qmm_steel_bf16", "affine_qmm_steel_w8g64"),
+    ("affine_qmm_steel_bf16", "affine_qmm_steel_w8g64_bm128"),
+    ("affine_qmm_steel_bf16", "affine_qmm_steel_w8g64_bm64"),
+    ("affine_qmm_steel_bf16", "affine_qmm_steel_w8g64_bm64_acc16"),
+    ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64"),
+    ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64_acc16"),
+    ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64_bm128"),
+    ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64_bm64"),
+    ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64_bm64_acc16"),
+    ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64_bm64_rs"),
+    ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w4g64_bm64_rs_acc16"),
+    ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w8g64"),
+    ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w8g64_acc16"),
+    ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w8g64_bm128"),
+    ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w8g64_bm64"),
+    ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w8g64_bm64_acc16"),
+    ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w8g64_bm64_rs"),
+    ("affine_qmm_steel_bf16", "affine_qmm_swiglu_w8g64_bm64_rs_acc16"),
+    ("affine_qmv_bf16", "affine_qmv_batch4_swiglu_w4g64"),
+    ("affine_qmv_bf16", "affine_qmv_batch4_w4g64"),
+    ("affine_qmv_bf16", "affine_qmv_batch4_w8g64"),
+    ("affine_qmv_bf16", "affine_qmv_batch4_xp_swiglu_w4g64"),
+    ("affine_qmv_bf16", "affine_qmv_batch4_xp_w4g64"),
+    ("affine_qmv_bf16", "affine_qmv_batch4_xp_w8g64"),
+    ("affine_qmv_bf16", "affine_qmv_batch8_tg4_w4g64"),
+    ("affine_qmv_bf16", "affine_qmv_batch8_tg4_w8g64"),
+    ("affine_qmv_bf16", "affine_qmv_batch8_tg_w4g64"),
+    ("affine_qmv_bf16", "affine_qmv_batch8_xd_w4g64"),
+    ("affine_qmv_bf16", "affine_qmv_batch8_xd_w8g64"),
+    ("affine_qmv_bf16", "affine_qmv_batch8_xh16_w4g64"),
+    ("affine_qmv_bf16", "affine_qmv_batch8_xh_w4g64"),
+    ("affine_qmv_bf16", "affine_qmv_batch8_xp1_w4g64"),
+    ("affine_qmv_bf16", "affine_qmv_batch8_xp2_swiglu_w4g64"),
+    ("affine_qmv_bf16", "affine_qmv_batch8_xp2_w4g64"),
+    ("affine_qmv_bf16", "affine_qmv_batch8_xp2_w8g64"),
+    ("affine_qmv_bf16", "affine_qmv_batch_geglu_w4g32"),
+    ("affine_qmv_bf16", "affine_qmv_batch_geglu_w4g64"),
+    ("affine_qmv_bf16", "affine_qmv_batch_swiglu_w4g64"),
+    ("affine_qmv_bf16", "affine_qmv_batch_w4g32"),
+    ("affine_qmv_bf16", "affine_qmv_batch_w4g64"),
+    ("affine_qmv_bf16", "affine_qmv_batch_w8g64"),
+    ("affine_qmv_bf16", "affine_qmv_geglu_w4g32"),
+    ("affine_qmv_bf16", "affine_qmv_geglu_w4g32_q40"),
+    ("affine_qmv_bf16", "affine_qmv_geglu_w4g64"),
+    ("affine_qmv_bf16", "affine_qmv_geglu_w8g64"),
+    ("affine_qmv_bf16", "affine_qmv_gelu_mul_w4g32"),
+    ("affine_qmv_bf16", "affine_qmv_gelu_mul_w4g64"),
+    ("affine_qmv_bf16", "affine_qmv_gelu_mul_w8g64"),
+    ("affine_qmv_bf16", "affine_qmv_qkv_rms_w4g32"),
+    ("affine_qmv_bf16", "affine_qmv_qkv_rms_w4g64"),
+    ("affine_qmv_bf16", "affine_qmv_qkv_rms_w8g64"),
+    ("affine_qmv_bf16", "affine_qmv_qkv_w4g32"),
+    ("affine_qmv_bf16", "affine_qmv_qkv_w4g64"),
+    ("affine_qmv_bf16", "affine_qmv_qkv_w8g64"),
+    ("affine_qmv_bf16", "affine_qmv_swiglu_w4g64"),
+    ("affine_qmv_bf16", "affine_qmv_swiglu_w8g64"),
+    ("affine_qmv_bf16", "affine_qmv_w4g32"),
+    ("affine_qmv_bf16", "affine_qmv_w4g32_add"),
+    ("affine_qmv_bf16", "affine_qmv_w4g32_add_q40"),
+    ("affine_qmv_bf16", "affine_qmv_w4g32_q40"),
+    ("affine_qmv_bf16", "affine_qmv_w4g64"),
+    ("affine_qmv_bf16", "affine_qmv_w4g64_add"),
+    ("affine_qmv_bf16", "affine_qmv_w8g32"),
+    ("affine_qmv_bf16", "affine_qmv_w8g64"),
+    ("affine_qmv_bf16", "affine_qmv_w8g64_add"),
+    ("affine_dequant_bf16", "affine_quant_w4_g32"),
+    ("affine_dequant_bf16", "affine_quant_w4_g64"),
+    ("affine_dequant_bf16", "affine_quant_w8_g32"),
+    ("affine_dequant_bf16", "affine_quant_w8_g64"),
+    ("affine_dequant_bf16", "affine_requant_w8_to_w4_g64"),
+]
+
+
+def test_every_reference_quant_kernel_name_resolves(vpq):
+    ops = vpq.ops
+    assert len(REFERENCE_QUANT_KERNELS) == 103
+    for libname, entry in REFERENCE_QUANT_KERNELS:
+        assert ops.function(libname, entry), (libname, entry)

@@ -536,3 +536,62 @@ def test_qkv_with_rmsnorm_prologue_over_group_32_weights(vpq, oracle_mod, K, q_r
         [bits16(q), bits16(k), bits16(v)], axis=1))
     assert same > 0.98
     assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_moe_sorted_slot_gemvs(vpq, oracle_mod, bits):
+    """affine_grouped_swiglu_w4g64 / affine_grouped_down_w4g64 and their _w8g64 twins
+    (affine_qmv.metal:2551-2719): (token, expert) pairs sorted by expert into tiles of two slots; the
+    gate|up GEMV gathers its x rows through srow, the down GEMV reads the sorted activations by slot;
+    padding slots and tiles without an expert are not written. Every live slot bit-identical to the
+    plain GEMV on its expert's slab."""
+    from vpipe_b200 import moe
+    ops = vpq.ops
+    E, H, F, T, top_k = 5, 1024, 320, 3, 2
+
+    def experts(N, K, seed):
+        cs, ss, bs = [], [], []
+        for e in range(E):
+            if bits == 4:
+                c, s, b = quantized_linear(oracle_mod, N, K, seed + e)
+            else:
+                c, s16, b16 = oracle_mod.quant(synth.f32_to_bf16_bits(synth.weight_f32(N, K, seed + e)), 8, 64)
+                s, b = oracle_mod.f16_to_bf16(s16), oracle_mod.f16_to_bf16(b16)
+            cs.append(c), ss.append(s), bs.append(b)
+        return [to_dev(np.stack(cs)), to_dev(np.stack(ss), torch.bfloat16), to_dev(np.stack(bs), torch.bfloat16)]
+
+    gu, dn = experts(2 * F, H, 4500), experts(H, F, 4600)
+    xb = to_dev(synth.activations_bf16(T, H, 4700), torch.bfloat16)
+    eid = np.array([4, 0, 4, 2, 4, 1], np.int32)                  # expert 4 gets three pairs: one padding slot
+    tile2e, srow, sdst, npad = moe.sort_pairs(eid, E, top_k, 2)
+    tile2e = np.concatenate([tile2e, np.array([-1], np.int32)])    # plus a tile without an expert
+    srow = np.concatenate([srow, np.array([0, 1], np.int32)])
+    npad += 2
+    dt, ds = to_dev(tile2e), to_dev(srow)
+    sfx = "w4g64" if bits == 4 else "w8g64"
+    act = torch.full((npad, F), float("nan"), dtype=torch.bfloat16, device=dev())
+    ops.dispatch(ops.function("affine_qmv_bf16", f"affine_grouped_swiglu_{sfx}"),
+                 {0: gu[0], 1: gu[1], 2: gu[2], 3: xb, 4: act, 7: ds, 8: dt}, K=H, N=2 * F, M=npad, experts=E)
+    y = torch.full((npad, H), float("nan"), dtype=torch.bfloat16, device=dev())
+    act_in = torch.nan_to_num(act, nan=0.0)                       # the dead slots' rows are read but never used
+    ops.dispatch(ops.function("affine_qmv_bf16", f"affine_grouped_down_{sfx}"),
+                 {0: dn[0], 1: dn[1], 2: dn[2], 3: act_in, 4: y, 7: ds, 8: dt}, K=F, N=H, M=npad, experts=E)
+    torch.cuda.synchronize()
+    live = 0
+    for slot in range(npad):
+        e, r = int(tile2e[slot // 2]), int(srow[slot])
+        if e < 0 or r < 0:
+            assert torch.isnan(act[slot].float()).all() and torch.isnan(y[slot].float()).all(), slot
+            continue
+        live += 1
+        zf = torch.zeros((1, F), dtype=torch.bfloat16, device=dev())
+        if bits == 4:
+            want_a = ops.qmv_swiglu(gu[0][e], gu[1][e], gu[2][e], xb[r:r + 1])
+            want_y = ops.qmv(dn[0][e], dn[1][e], dn[2][e], act[slot:slot + 1])
+        else:
+            want_a = ops.qmv_w8_fused(gu[0][e], gu[1][e], gu[2][e], xb[r:r + 1], zf, {"epilogue": "swiglu"})
+            want_y = ops.qmv_w8(dn[0][e], dn[1][e], dn[2][e], act[slot:slot + 1])
+        assert torch.equal(act[slot:slot + 1], want_a), slot
+        assert torch.equal(y[slot:slot + 1], want_y), slot
+    assert live == eid.size
+    assert ops.device_status() == 0

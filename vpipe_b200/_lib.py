@@ -100,7 +100,8 @@ class LinearDesc(C.Structure):
                 ("M", C.c_int64), ("epilogue", C.c_int32), ("depends", C.c_int32),
                 ("aux", C.c_void_p), ("y3", C.c_void_p), ("q_rows", C.c_int64),
                 ("k_rows", C.c_int64), ("norm_w", C.c_void_p), ("expert", C.c_void_p),
-                ("experts", C.c_int64), ("x_div", C.c_int32), ("eps", C.c_float)]
+                ("experts", C.c_int64), ("x_div", C.c_int32), ("eps", C.c_float),
+                ("row_map", C.c_void_p), ("row_gather", C.c_int32), ("expert_div", C.c_int32)]
 
 
 class VpqError(RuntimeError):

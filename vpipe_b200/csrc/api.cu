@@ -192,7 +192,7 @@ extern "C" size_t vpq_scale_bytes(int N, int K, int group) {
 struct vpq_function_s {
   const char* library;
   const char* entry;
-  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64, 66..69 qmv w8g64 add / swiglu / qkv / gelu*mul, 70 / 71 qmm swiglu strided store w4 / w8, 72..74 grouped qmm down / swiglu / geglu, 75 qmv norm + qkv, 76..78 gathered expert qmv swiglu / geglu / down, 79..81 qmm w4g32 / geglu w4g32 / w8g32, 82..85 qmv w4g32 add / geglu / gelu*mul / qkv, 86..88 scale-only (Q4_0) qmv w4g32 plain / add / geglu, 89 requant w8 -> w4, 90 qmv geglu w8g64, 91..93 gathered expert qmv w8g64 swiglu / geglu / down, 94 moe gate w8g64, 95 / 96 gathered split-width swiglu (gate w4 + up w8 / gate w8 + up w4), 97..99 grouped qmm w8g64 down / swiglu / geglu, 100 / 101 qmv norm + qkv w8g64 / w4g32, 102 qmv w8g32; 10 + code: quant / dequant twins (see fmt_*)
+  int kind;  // 0 qmv, 1 qmm, 2 dequant, 3 quant(bf16 src), 4 quant(f16 src), 5 qmv+add, 6 qmv swiglu, 7 qmv qkv, 8 qmm swiglu, 9 qmv batch, 58 qmv w8g64, 59 qmm w8g64, 60 qmv w4g32, 61 qmv geglu, 62 qmv gelu*mul, 63 qmm geglu, 64 / 65 qmm swiglu / geglu w8g64, 66..69 qmv w8g64 add / swiglu / qkv / gelu*mul, 70 / 71 qmm swiglu strided store w4 / w8, 72..74 grouped qmm down / swiglu / geglu, 75 qmv norm + qkv, 76..78 gathered expert qmv swiglu / geglu / down, 79..81 qmm w4g32 / geglu w4g32 / w8g32, 82..85 qmv w4g32 add / geglu / gelu*mul / qkv, 86..88 scale-only (Q4_0) qmv w4g32 plain / add / geglu, 89 requant w8 -> w4, 90 qmv geglu w8g64, 91..93 gathered expert qmv w8g64 swiglu / geglu / down, 94 moe gate w8g64, 95 / 96 gathered split-width swiglu (gate w4 + up w8 / gate w8 + up w4), 97..99 grouped qmm w8g64 down / swiglu / geglu, 100 / 101 qmv norm + qkv w8g64 / w4g32, 102 qmv w8g32, 103..106 sorted-slot expert qmv swiglu / down, w4g64 / w8g64, 107 / 108 qmv batch swiglu / geglu; 10 + code: quant / dequant twins (see fmt_*)
 };
 
 // The reference selects the element type with the library-name suffix and
@@ -216,6 +216,10 @@ static const vpq_function_s g_functions[] = {
     {"affine_qmv_bf16", "affine_gather_qmv_geglu_w8g64", 92},
     {"affine_qmv_bf16", "affine_gather_down_qmv_w8g64", 93},
     {"affine_qmv_bf16", "affine_moe_gate_w8g64", 94},
+    {"affine_qmv_bf16", "affine_grouped_swiglu_w4g64", 103},
+    {"affine_qmv_bf16", "affine_grouped_down_w4g64", 104},
+    {"affine_qmv_bf16", "affine_grouped_swiglu_w8g64", 105},
+    {"affine_qmv_bf16", "affine_grouped_down_w8g64", 106},
     {"affine_qmv_bf16", "affine_gather_qmv_swiglu_w4w8g64", 95},
     {"affine_qmv_bf16", "affine_gather_qmv_swiglu_w8w4g64", 96},
     {"affine_qmv_bf16", "affine_qmv_geglu_w4g64", 61},
@@ -237,6 +241,28 @@ static const vpq_function_s g_functions[] = {
     {"affine_qmv_bf16", "affine_qmv_geglu_w4g32_q40", 88},
     {"affine_qmv_bf16", "affine_qmv_batch_w4g64", 9},
     {"affine_qmv_bf16", "affine_qmv_batch4_w4g64", 9},
+    // the reference's batch ladder (row-count and tiling twins of one contract: slot 7 = total rows)
+    {"affine_qmv_bf16", "affine_qmv_batch4_xp_w4g64", 9},
+    {"affine_qmv_bf16", "affine_qmv_batch8_tg_w4g64", 9},
+    {"affine_qmv_bf16", "affine_qmv_batch8_tg4_w4g64", 9},
+    {"affine_qmv_bf16", "affine_qmv_batch8_xd_w4g64", 9},
+    {"affine_qmv_bf16", "affine_qmv_batch8_xh_w4g64", 9},
+    {"affine_qmv_bf16", "affine_qmv_batch8_xh16_w4g64", 9},
+    {"affine_qmv_bf16", "affine_qmv_batch8_xp1_w4g64", 9},
+    {"affine_qmv_bf16", "affine_qmv_batch8_xp2_w4g64", 9},
+    {"affine_qmv_bf16", "affine_qmv_batch_swiglu_w4g64", 107},
+    {"affine_qmv_bf16", "affine_qmv_batch4_swiglu_w4g64", 107},
+    {"affine_qmv_bf16", "affine_qmv_batch4_xp_swiglu_w4g64", 107},
+    {"affine_qmv_bf16", "affine_qmv_batch8_xp2_swiglu_w4g64", 107},
+    {"affine_qmv_bf16", "affine_qmv_batch_geglu_w4g64", 108},
+    {"affine_qmv_bf16", "affine_qmv_batch_w8g64", 58},
+    {"affine_qmv_bf16", "affine_qmv_batch4_w8g64", 58},
+    {"affine_qmv_bf16", "affine_qmv_batch4_xp_w8g64", 58},
+    {"affine_qmv_bf16", "affine_qmv_batch8_tg4_w8g64", 58},
+    {"affine_qmv_bf16", "affine_qmv_batch8_xd_w8g64", 58},
+    {"affine_qmv_bf16", "affine_qmv_batch8_xp2_w8g64", 58},
+    {"affine_qmv_bf16", "affine_qmv_batch_w4g32", 60},
+    {"affine_qmv_bf16", "affine_qmv_batch_geglu_w4g32", 83},
     {"affine_qmm_steel_bf16", "affine_qmm_steel_w4g64", 1},
     {"affine_qmm_steel_bf16", "affine_qmm_steel_w4g64_bm64", 1},
     {"affine_qmm_steel_bf16", "affine_qmm_steel_w4g64_bm128", 1},
@@ -452,6 +478,46 @@ extern "C" int vpq_dispatch(const vpq_function* fn, const vpq_dispatch_args* a, 
         d.aux = b[7];
       }
       return k >= 86 ? vpq_affine_qmv_w4g32_q40_bf16_fused(&d, stream) : vpq_affine_qmv_w4g32_bf16_fused(&d, stream);
+    }
+    case 107:
+    case 108: {
+      vpq_linear_desc d;
+      std::memset(&d, 0, sizeof(d));
+      d.w = static_cast<const uint32_t*>(b[0]);
+      d.scales = b[1];
+      d.biases = b[2];
+      d.x = b[3];
+      d.y = const_cast<void*>(b[4]);
+      d.K = a->K;
+      d.N = a->N;
+      d.M = a->M < 1 ? 1 : a->M;
+      d.epilogue = fn->kind == 107 ? VPQ_EPILOGUE_SWIGLU : VPQ_EPILOGUE_GEGLU;
+      return vpq_affine_qmv_batch_w4g64_bf16_fused(&d, stream);
+    }
+    case 103:
+    case 104:
+    case 105:
+    case 106: {
+      // sorted slots in tiles of two (slot 7 = srow [M], 8 = tile2e [M / 2]); gate|up gathers its x rows
+      // through srow, down reads the sorted activations by slot; dead slots are not written
+      vpq_linear_desc d;
+      std::memset(&d, 0, sizeof(d));
+      d.w = static_cast<const uint32_t*>(b[0]);
+      d.scales = b[1];
+      d.biases = b[2];
+      d.x = b[3];
+      d.y = const_cast<void*>(b[4]);
+      d.K = a->K;
+      d.N = a->N;
+      d.M = a->M < 1 ? 1 : a->M;
+      d.row_map = static_cast<const int32_t*>(b[7]);
+      d.expert = static_cast<const int32_t*>(b[8]);
+      d.experts = a->experts;
+      d.expert_div = 2;
+      const bool gate_up = fn->kind == 103 || fn->kind == 105;
+      d.row_gather = gate_up ? 1 : 0;
+      d.epilogue = gate_up ? VPQ_EPILOGUE_SWIGLU : VPQ_EPILOGUE_NONE;
+      return fn->kind >= 105 ? vpq_affine_qmv_w8g64_bf16_fused(&d, stream) : vpq_affine_qmv_w4g64_bf16_batch(&d, 1, stream);
     }
     case 95:
     case 96: {

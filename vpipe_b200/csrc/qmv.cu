@@ -127,7 +127,9 @@ struct alignas(64) QmvProblem {
   float eps;                   // RMSNorm epsilon
   int wait_tiles;              // > 0: tiles of the launch that must be complete before x (and aux) may be read
   int experts;                 // slabs in w (eid is clamped to it)
-  int pad[5];
+  int pad0;
+  const int32_t* xrow;         // not null: x is row max(*xrow, 0) of the matrix P.x points at (sorted-slot gather)
+  const int32_t* vrow;         // not null: the slot is live, and its outputs are stored, only if *vrow >= 0 (and *eid >= 0)
 };
 static_assert(sizeof(QmvProblem) == 512, "problem records are laid out back to back");
 
@@ -281,6 +283,7 @@ __device__ __noinline__ bool stage_x(const QmvProblem* P, unsigned char* p0, int
   constexpr int kXRegs = 3;  // passes whose loads a lane keeps in registers
   const int half = lane >> 4, sub = lane & 15;
   const uint16_t* xr = P->x;
+  if (P->xrow) { xr += (size_t)max(__ldg(P->xrow), 0) * (size_t)K; }   // a dead slot reads row 0 and stores nothing
   const uint16_t* nw = P->norm_w;
   const int NB = (K + 255) >> 8;
   const int passes = (((NB + kBoxesPerStage - 1) / kBoxesPerStage) + 1) >> 1;  // two boxes of this warp per pass
@@ -728,7 +731,9 @@ __device__ __noinline__ uint32_t consume_tiles(const QmvProblem* P, int lo, int 
           v += *reinterpret_cast<volatile float*>(&red[(slot * kConsWarps + ww) * 16 + lane]);
         }
         const int row = (tile << 4) + lane;
-        fused_store(P->epilogue, v, row, P->N, lane, P->y, P->aux, P->y3, P->q_rows, P->k_rows);
+        // a dead slot of the sorted form (padding row, or a tile without an expert) stores nothing
+        const bool live = !P->vrow || (__ldg(P->vrow) >= 0 && (!P->eid || __ldg(P->eid) >= 0));
+        if (live) { fused_store(P->epilogue, v, row, P->N, lane, P->y, P->aux, P->y3, P->q_rows, P->k_rows); }
       }
       __syncwarp();
       if (lane == 0) {
@@ -808,7 +813,7 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
     const uint16_t* xr = P->x;
     const int need = chain ? P->wait_tiles : 0;
     // q|k|v or gate|up of a layer share one staging; a dependent or normalised x is always staged
-    if (need > 0 || P->norm_w != nullptr || xr != staged_x || K != staged_K) {
+    if (need > 0 || P->norm_w != nullptr || P->xrow != nullptr || xr != staged_x || K != staged_K) {
       if (!stage_x(P, p0, cap_kt, sq_gen, need, sync)) { break; }
       staged_x = P->norm_w ? nullptr : xr;
       staged_K = K;
@@ -989,6 +994,8 @@ int check_qmv_args(const char* who, const void* w, const void* scales, const voi
 }
 
 // Validation of one descriptor: shapes, fused store, RMSNorm prologue, expert gather.
+int check_row_map(const char* who, const vpq_linear_desc& d);
+
 int check_desc(const char* who, const vpq_linear_desc& d, bool in_plan) {
   if (int rc = check_qmv_args(who, d.w, d.scales, d.biases, d.x, d.y, d.K, d.N, d.M)) { return rc; }
   if (d.depends != 0 && d.depends != 1) { return fail(VPQ_ERR_INVALID_ARG, "%s: depends must be 0 or 1", who); }
@@ -1010,13 +1017,15 @@ int check_desc(const char* who, const vpq_linear_desc& d, bool in_plan) {
   } else if (d.experts > 1 || d.x_div > 1) {
     return fail(VPQ_ERR_INVALID_ARG, "%s: experts / x_div given without an expert index array", who);
   }
+  if (int rc = check_row_map(who, d)) { return rc; }
   return qmv_check_store(who, d);
 }
 }  // namespace
 
 // The kernels other than the 4-bit group-64 GEMV take plain descriptors only.
 int qmv_check_plain(const char* who, const vpq_linear_desc& d, bool allow_norm) {
-  if ((d.norm_w && !allow_norm) || d.expert || d.depends || d.experts > 1 || d.x_div > 1) {
+  if ((d.norm_w && !allow_norm) || d.expert || d.depends || d.experts > 1 || d.x_div > 1 || d.row_map || d.row_gather ||
+      d.expert_div > 1) {
     return fail(VPQ_ERR_UNSUPPORTED, "%s: %sexpert and depends are taken by the w4 g64 GEMV entry points only", who,
                 allow_norm ? "" : "norm_w, ");
   }
@@ -1027,7 +1036,25 @@ int qmv_check_plain(const char* who, const vpq_linear_desc& d, bool allow_norm) 
   return qmv_check_store(who, d);
 }
 
+namespace {
+int check_row_map(const char* who, const vpq_linear_desc& d) {
+  if (d.row_map) {
+    if (reinterpret_cast<uintptr_t>(d.row_map) & 3) {
+      return fail(VPQ_ERR_ALIGNMENT, "%s: row_map must be 4-byte aligned", who);
+    }
+    if (d.row_gather != 0 && d.row_gather != 1) { return fail(VPQ_ERR_INVALID_ARG, "%s: row_gather must be 0 or 1", who); }
+  } else if (d.row_gather != 0) {
+    return fail(VPQ_ERR_INVALID_ARG, "%s: row_gather given without row_map", who);
+  }
+  if (d.expert_div < 0 || (d.expert_div > 1 && !d.expert)) {
+    return fail(VPQ_ERR_INVALID_ARG, "%s: expert_div must be >= 0 and needs an expert index array", who);
+  }
+  return VPQ_OK;
+}
+}  // namespace
+
 int qmv_check_gather(const char* who, const vpq_linear_desc& d, bool allow_norm) {
+  if (int rc = check_row_map(who, d)) { return rc; }
   if ((d.norm_w && !allow_norm) || d.depends) {
     return fail(VPQ_ERR_UNSUPPORTED, "%s: %s taken by the w4 g64 GEMV entry points only", who,
                 allow_norm ? "depends is" : "norm_w and depends are");
@@ -1092,7 +1119,8 @@ int fill_from_desc(QmvProblem* p, const vpq_linear_desc& d, int64_t m, int tile_
   const int64_t y_pitch = gated ? d.N / 2
                           : d.epilogue == VPQ_EPILOGUE_QKV  ? d.q_rows
                                                             : d.N;
-  const int64_t x_row = (d.expert && d.x_div > 1) ? m / d.x_div : m;  // pairs of one token share its row
+  const bool row_gather = d.row_map && d.row_gather;   // the x row is read on the GPU (row_map[m])
+  const int64_t x_row = row_gather ? 0 : (d.expert && d.x_div > 1) ? m / d.x_div : m;  // pairs of one token share its row
   if (int rc = fill_problem(p, d.w, static_cast<const uint16_t*>(d.scales), static_cast<const uint16_t*>(d.biases),
                             static_cast<const uint16_t*>(d.x) + x_row * d.K,
                             static_cast<__nv_bfloat16*>(d.y) + m * y_pitch, (int)d.K, (int)d.N, tile_begin,
@@ -1110,7 +1138,9 @@ int fill_from_desc(QmvProblem* p, const vpq_linear_desc& d, int64_t m, int tile_
   }
   p->norm_w = static_cast<const uint16_t*>(d.norm_w);
   p->eps = d.eps;
-  p->eid = d.expert ? d.expert + m : nullptr;
+  p->eid = d.expert ? d.expert + (d.expert_div > 1 ? m / d.expert_div : m) : nullptr;
+  p->vrow = d.row_map ? d.row_map + m : nullptr;
+  p->xrow = row_gather ? d.row_map + m : nullptr;
   return VPQ_OK;
 }
 

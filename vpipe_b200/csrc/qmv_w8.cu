@@ -83,6 +83,8 @@ struct alignas(64) Problem8 {
   int experts;                 // slabs in w (eid is clamped to it)
   float eps;                   // RMSNorm epsilon
   const uint16_t* norm_w;      // not null: x is RMS-normalised with these K weights while it is staged
+  const int32_t* xrow;         // not null: x is row max(*xrow, 0) of the matrix x points at (sorted-slot gather)
+  const int32_t* vrow;         // not null: the slot's outputs are stored only if *vrow >= 0 (and *eid >= 0)
 };
 
 template <int GS>
@@ -197,11 +199,12 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
   // (affine_qmv_qkv_rms_w8g64, the 8-bit instantiation of gpu-kernels/metal/quant/affine_qmv.metal:570-694):
   // sum of squares in f32 over the whole vector (the eight consumer warps exchange partial sums through
   // shared memory: post, count, bounded wait), x <- bf16(x * rsqrt(mean + eps) * norm_w).
+  const uint16_t* xrow_ptr = P.x + (P.xrow ? (size_t)max(__ldg(P.xrow), 0) * (size_t)K : 0);  // a dead slot reads row 0
   float inv = 1.0f;
   if (P.norm_w) {
     float sq = 0.0f;
     for (int k0 = (warp * 32 + lane) * 8; k0 < K; k0 += kConsThreads * 8) {
-      const uint4 in = *reinterpret_cast<const uint4*>(P.x + k0);
+      const uint4 in = *reinterpret_cast<const uint4*>(xrow_ptr + k0);
       const uint32_t v[4] = {in.x, in.y, in.z, in.w};
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
@@ -247,8 +250,8 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
       const int k0 = kt * 128 + sub * 16;
       uint4 in0 = make_uint4(0, 0, 0, 0), in1 = in0;
       if (k0 < K) {
-        in0 = *reinterpret_cast<const uint4*>(P.x + k0);
-        in1 = *reinterpret_cast<const uint4*>(P.x + k0 + 8);
+        in0 = *reinterpret_cast<const uint4*>(xrow_ptr + k0);
+        in1 = *reinterpret_cast<const uint4*>(xrow_ptr + k0 + 8);
       }
       uint32_t v[8] = {in0.x, in0.y, in0.z, in0.w, in1.x, in1.y, in1.z, in1.w};
       if (P.norm_w) {
@@ -469,7 +472,8 @@ affine_qmv_w8g64_kernel(const __grid_constant__ Problem8 P, int stages, int cap_
           v += *reinterpret_cast<volatile float*>(&red[(slot * kConsWarps + ww) * 16 + lane]);
         }
         const int row = (tile << 4) + lane;
-        fused_store(P.epilogue, v, row, N, lane, P.y, P.aux, P.y3, P.q_rows, P.k_rows);
+        const bool live = !P.vrow || (__ldg(P.vrow) >= 0 && (!P.eid || __ldg(P.eid) >= 0));
+        if (live) { fused_store(P.epilogue, v, row, N, lane, P.y, P.aux, P.y3, P.q_rows, P.k_rows); }
       }
       __syncwarp();
       if (lane == 0) { red_cnt[slot] = 0; }
@@ -569,9 +573,12 @@ int launch_w8(const char* who, const vpq_linear_desc& d, void* stream) {
   p.eps = d.eps;
   for (int64_t m = 0; m < M; ++m) {  // every row streams the weight again, as in the reference
     // expert gather: row m is a (token, expert) pair; the pairs of one token share its x row
-    const int64_t x_row = (d.expert && d.x_div > 1) ? m / d.x_div : m;
+    const bool row_gather = d.row_map && d.row_gather;   // the x row is read on the GPU (row_map[m])
+    const int64_t x_row = row_gather ? 0 : (d.expert && d.x_div > 1) ? m / d.x_div : m;
     p.x = static_cast<const uint16_t*>(x) + x_row * K;
-    p.eid = d.expert ? d.expert + m : nullptr;
+    p.eid = d.expert ? d.expert + (d.expert_div > 1 ? m / d.expert_div : m) : nullptr;
+    p.vrow = d.row_map ? d.row_map + m : nullptr;
+    p.xrow = row_gather ? d.row_map + m : nullptr;
     p.y = static_cast<__nv_bfloat16*>(y) + m * y_pitch;
     if (d.epilogue == VPQ_EPILOGUE_ADD || d.epilogue == VPQ_EPILOGUE_GELU_MUL || d.epilogue == VPQ_EPILOGUE_SILU_MUL) {
       p.aux = static_cast<const uint16_t*>(d.aux) + m * N;

@@ -279,6 +279,10 @@ def qmv_set(problems):
             d.expert = _ptr(e["expert"])
             d.experts = codes.shape[0]
             d.x_div = int(e.get("x_div", 1))
+            d.expert_div = int(e.get("expert_div", 1))
+        if e.get("row_map") is not None:      # sorted slots: live iff row_map[m] >= 0; "row_gather": x row = row_map[m]
+            d.row_map = _ptr(e["row_map"])
+            d.row_gather = 1 if e.get("row_gather") else 0
     return arr
 
 
