@@ -859,7 +859,8 @@ def main():
     ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5", "c1"] + list(SMALL),
                     help="c2: the headline line; c3/c4/c5: the GEMM config as the line's metric; the rest: one small case")
     ap.add_argument("shape", nargs="*", help="sizes of a small workload (see the module docstring)")
-    ap.add_argument("--with-c5", action="store_true", help="add the C5 GEMM config to the headline line (~10 s)")
+    ap.add_argument("--with-c5", action="store_true",
+                    help="add the C5 GEMM config to the 1-GPU headline line (~10 s; with more GPUs it is always there)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-memory end-to-end pass of the GEMM sections")
     ap.add_argument("--no-plan", action="store_true", help="QMV set as 216 graph-replayed launches")
@@ -928,8 +929,9 @@ def main():
                 line["qmm"]["cpu_baseline"] = cpu_baseline_qmm(synth, "C4")
                 line["qmm_c3"]["cpu_baseline"] = cpu_baseline_qmm(synth, "C3")
         else:
+            # every config BASELINE.json shards: C4, C3 gate / up, C5
             line["qmm"] = bench_qmm_sharded(torch, dist, ops, shard, synth, args, rank, world, dev, pk, comm,
-                                            ["C4", "C3"] + (["C5"] if args.with_c5 else []))
+                                            ["C4", "C3", "C5"])
             parity_ok = parity_ok and line["qmm"]["parity"]["bit_identical"]
     else:
         key = args.workload.upper()
