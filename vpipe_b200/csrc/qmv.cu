@@ -202,12 +202,6 @@ struct Walk {
   }
 };
 
-__device__ __forceinline__ uint4 ld_cg_v4(const void* p) {  // L2 only: x may have been written by another SM
-  uint4 r;
-  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
-  return r;
-}
-
 __device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -269,7 +263,7 @@ constexpr uint32_t kDepPolls = 1u << 21;  // polls (an L2 round trip each) of th
 // (affine_qmv_qkv_rms_w4g64, gpu-kernels/metal/quant/affine_qmv.metal:570-694): sum of squares
 // in f32 over the whole vector (the warps exchange their partial sums through one consumer
 // barrier), x <- bf16(x * rsqrt(mean + eps) * norm_w).
-__device__ __noinline__ bool stage_x(const QmvProblem* P, unsigned char* p0, int cap_kt, int sq_gen, int need,
+__device__ __forceinline__ bool stage_x(const QmvProblem* P, unsigned char* p0, int cap_kt, int sq_gen, int need,
                                      const uint32_t* sync) {
   const Scratch sc(p0, cap_kt);
   unsigned char* xq = sc.xq;
@@ -280,20 +274,22 @@ __device__ __noinline__ bool stage_x(const QmvProblem* P, unsigned char* p0, int
   volatile uint32_t* abort_flag = sc.abort_flag;
   const int K = P->K;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  constexpr int kXRegs = 3;  // passes whose loads a lane keeps in registers
   const int half = lane >> 4, sub = lane & 15;
   const uint16_t* xr = P->x;
   if (P->xrow) { xr += (size_t)max(__ldg(P->xrow), 0) * (size_t)K; }   // a dead slot reads row 0 and stores nothing
   const uint16_t* nw = P->norm_w;
   const int NB = (K + 255) >> 8;
   const int passes = (((NB + kBoxesPerStage - 1) / kBoxesPerStage) + 1) >> 1;  // two boxes of this warp per pass
-  auto k_of = [&](int j) { return (((2 * j + half) * kBoxesPerStage + warp) << 8) + sub * 16; };
+  auto box_of = [&](int j) { return (2 * j + half) * kBoxesPerStage + warp; };
+  auto k_of = [&](int j) { return (box_of(j) << 8) + sub * 16; };
+  // This lane's 32 raw bytes of box `box` wait inside the box's own 768 bytes of xq until they are converted.
+  auto raw_of = [&](int box) { return xq + (size_t)box * (2 * kXBytesPerKt) + sub * 32; };
   auto load_piece = [&](int j, uint4& a, uint4& b) {
-    const int k0 = k_of(j);
     a = b = make_uint4(0, 0, 0, 0);
-    if (k0 < K) {
-      a = ld_cg_v4(xr + k0);
-      b = ld_cg_v4(xr + k0 + 8);
+    if (box_of(j) < NB) {
+      const unsigned char* raw = raw_of(box_of(j));
+      a = *reinterpret_cast<const uint4*>(raw);
+      b = *reinterpret_cast<const uint4*>(raw + 16);
     }
   };
   if (nw) {  // the norm weights are constants: bring this lane's share into L1 before waiting for x
@@ -341,11 +337,20 @@ __device__ __noinline__ bool stage_x(const QmvProblem* P, unsigned char* p0, int
     seen = __shfl_sync(0xffffffffu, seen, 0);
     if (!seen) { return false; }
   }
-  uint4 xin[kXRegs][2];
-#pragma unroll
-  for (int r = 0; r < kXRegs; ++r) {
-    if (r < passes) { load_piece(r, xin[r][0], xin[r][1]); }
+  // All of this warp's boxes are fetched at once, asynchronously and past L1 (x may have been written
+  // by another SM a moment ago), so a long vector costs one trip to L2 and no registers; past K the
+  // copy fills zeros.
+  for (int j = 0; j < passes; ++j) {
+    if (box_of(j) < NB) {
+      const int k0 = k_of(j);
+      const uint32_t dst = smem_u32(raw_of(box_of(j)));
+      const uint32_t n = k0 < K ? 16u : 0u;
+      const uint16_t* src = xr + (k0 < K ? k0 : 0);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + 16u), "l"(src + 8), "r"(n) : "memory");
+    }
   }
+  asm volatile("cp.async.wait_all;" ::: "memory");
   float inv = 1.0f;
   if (nw) {
     float sq = 0.0f;
@@ -358,14 +363,7 @@ __device__ __noinline__ bool stage_x(const QmvProblem* P, unsigned char* p0, int
         sq = __fmaf_rn(hi, hi, sq);
       }
     };
-#pragma unroll
-    for (int r = 0; r < kXRegs; ++r) {
-      if (r < passes) {
-        add_sq(xin[r][0]);
-        add_sq(xin[r][1]);
-      }
-    }
-    for (int j = kXRegs; j < passes; ++j) {
+    for (int j = 0; j < passes; ++j) {
       uint4 a, b;
       load_piece(j, a, b);
       add_sq(a);
@@ -475,13 +473,10 @@ __device__ __noinline__ bool stage_x(const QmvProblem* P, unsigned char* p0, int
     if (live && (sub & 3) == 0) { xg[i >> 2] = (float)(int)sum - kAccSurplus; }
     if (live && sub == 0) { xu[box] = __uint_as_float((uint32_t)(e - 21) << 23); }  // exact inverse of x_scale
   };
-#pragma unroll
-  for (int r = 0; r < kXRegs; ++r) {
-    if (r < passes) { convert_piece(r, xin[r][0], xin[r][1]); }
-  }
-  for (int j = kXRegs; j < passes; ++j) {
+  for (int j = 0; j < passes; ++j) {
     uint4 a, b;
     load_piece(j, a, b);
+    __syncwarp();  // every lane holds its raw piece before the digits of the box overwrite it
     convert_piece(j, a, b);
   }
   __syncwarp();
@@ -564,7 +559,7 @@ __device__ __noinline__ void produce(const QmvProblem* single, const QmvProblem*
 // return value is the new state, or kConsumeFailed if a bounded wait gave up.
 constexpr uint32_t kConsumeFailed = 0xffffffffu;
 
-__device__ __noinline__ uint32_t consume_tiles(const QmvProblem* P, int lo, int hi, uint32_t state, unsigned char* base_ptr,
+__device__ __forceinline__ uint32_t consume_tiles(const QmvProblem* P, int lo, int hi, uint32_t state, unsigned char* base_ptr,
                                                int stages, int cap_kt, uint32_t* sync) {
   constexpr int kStageBytes = kStageW + kStageSZ;
   const Scratch sc(base_ptr + (size_t)stages * kStageBytes, cap_kt);
