@@ -276,7 +276,7 @@ __device__ __forceinline__ bool stage_x(const QmvProblem* P, unsigned char* p0, 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int half = lane >> 4, sub = lane & 15;
   const uint16_t* xr = P->x;
-  if (P->xrow) { xr += (size_t)max(__ldg(P->xrow), 0) * (size_t)K; }   // a dead slot reads row 0 and stores nothing
+  const int32_t* xrow = P->xrow;
   const uint16_t* nw = P->norm_w;
   const int NB = (K + 255) >> 8;
   const int passes = (((NB + kBoxesPerStage - 1) / kBoxesPerStage) + 1) >> 1;  // two boxes of this warp per pass
@@ -298,6 +298,12 @@ __device__ __forceinline__ bool stage_x(const QmvProblem* P, unsigned char* p0, 
       if (k0 < K) { asm volatile("prefetch.global.L1 [%0];" ::"l"(nw + k0)); }
     }
   }
+  // Everything above reads the problem record and constants of the model; from here on the kernel
+  // touches what the previous kernel in the stream may still be writing (x, the routed rows, and
+  // later the residual and y), so this is where it waits for it. The record's fields are in flight
+  // during the wait instead of after it.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (xrow) { xr += (size_t)max(__ldg(xrow), 0) * (size_t)K; }   // a dead slot reads row 0 and stores nothing
   if (need > 0) {
     // This GEMV reads what earlier GEMVs of the launch wrote: wait (bounded) until their tiles are
     // counted. One warp per CTA polls the counter in global memory (the first to get here claims
@@ -794,9 +800,8 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
   }
 
   // ---------------------------------------------------------------- consumers
-  // x (and y) may be produced / consumed by the previous kernel.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-
+  // x (and y) may be produced / consumed by the previous kernel: stage_x waits for it before it
+  // touches x, and every range of a CTA starts with a staging or follows one.
   Walk wk(&single, list, ranges, total_tiles, count, chain);
   const uint16_t* staged_x = nullptr;
   int staged_K = -1, sq_gen = 0;
