@@ -284,6 +284,44 @@ def test_chain_first_layer_against_oracle(vpq, oracle_mod):
     assert oracle_mod.err_metrics(f32(dn[4]), synth.bf16_bits_to_f32(r_dn))["max_rel_rms"] < TOL
 
 
+def test_chain_over_buffers_that_the_layers_reuse(vpq, oracle_mod):
+    """A decoder keeps one set of activation buffers for all layers: the residual stream ping-pongs
+    between two vectors and q | k | v | act are overwritten by every layer. Inside one chained launch
+    an SM then reads addresses it has read before with other contents (x, the residual); the bytes
+    must still equal those of one launch per GEMV."""
+    ops = vpq.ops
+    H, KV, F, layers = 1024, 256, 1536, 6
+    L, _ = _decoder_layers(vpq, oracle_mod, layers, H, KV, F, 4700)
+    h0 = L[0][0][3].clone()
+    a, b = torch.zeros_like(h0), torch.zeros_like(h0)
+    q, k, v, act = (torch.zeros((1, n), dtype=torch.bfloat16, device=dev()) for n in (H, KV, KV, F))
+    problems = []
+    for i, (qkv, o, gu, dn) in enumerate(L):
+        problems += [
+            qkv[:3] + (a, q, dict(qkv[5], aux=k, y3=v, depends=i > 0)),
+            o[:3] + (q, b, dict(o[5], aux=a)),
+            gu[:3] + (b, act, dict(gu[5])),
+            dn[:3] + (act, a, dict(dn[5], aux=b)),
+        ]
+    outs = [a, b, q, k, v, act]
+    a.copy_(h0)
+    _per_launch(ops, problems)
+    torch.cuda.synchronize()
+    want = [t.clone() for t in outs]
+    assert float(want[0].float().abs().max()) > 0
+    plan = ops.QmvPlan(problems)
+    for run in range(4):
+        for t in outs:
+            t.fill_(5.0)
+        a.copy_(h0)
+        plan.run()
+        torch.cuda.synchronize()
+        for i, (g, w) in enumerate(zip(outs, want)):
+            assert torch.equal(g, w), f"run {run}: buffer {i} differs"
+    plan.close()
+    assert ops.device_status() == 0
+
+
 def _chain_outputs(problems):
     return [t for p in problems for t in ([p[4]] + ([p[5]["aux"], p[5]["y3"]] if p[5]["epilogue"] == "qkv" else []))]
 

@@ -123,6 +123,14 @@ __device__ __forceinline__ float gelu_tanh(float x) {
 // lane = row within the 16-row tile; the gated stores pair lanes 2j, 2j + 1.
 enum : int { kEpiNone = 0, kEpiAdd = 1, kEpiSwiglu = 2, kEpiQkv = 3, kEpiGeglu = 4, kEpiGeluMul = 5, kEpiSiluMul = 6 };
 
+// A residual or multiplier may have been written by another SM earlier in the same launch (a chain of
+// dependent GEMVs over buffers that the layers reuse), so it is read past L1.
+__device__ __forceinline__ uint32_t ld_cg_u16(const uint16_t* p) {
+  uint16_t r;
+  asm volatile("ld.global.cg.u16 %0, [%1];" : "=h"(r) : "l"(p) : "memory");
+  return r;
+}
+
 // `mask` names the lanes that make the call together (the gated stores shuffle among them).
 __device__ __forceinline__ void fused_store(int epi, float v, int row, int N, int lane, __nv_bfloat16* y,
                                             const uint16_t* aux, __nv_bfloat16* y3, int q_rows, int k_rows,
@@ -132,7 +140,7 @@ __device__ __forceinline__ void fused_store(int epi, float v, int row, int N, in
   } else if (epi == kEpiAdd) {
     // the sum is rounded to bf16 first, then added to the residual in bf16, as the reference does
     if (row < N) {
-      const float r = __uint_as_float((uint32_t)aux[row] << 16);
+      const float r = __uint_as_float(ld_cg_u16(aux + row) << 16);
       y[row] = __float2bfloat16_rn(__bfloat162float(__float2bfloat16_rn(v)) + r);
     }
   } else if (epi == kEpiSwiglu) {
@@ -146,13 +154,13 @@ __device__ __forceinline__ void fused_store(int epi, float v, int row, int N, in
   } else if (epi == kEpiGeluMul) {
     // gelu of the bf16-rounded sum, times the multiplier: what a separate pass over y would compute
     if (row < N) {
-      const float m = __uint_as_float((uint32_t)aux[row] << 16);
+      const float m = __uint_as_float(ld_cg_u16(aux + row) << 16);
       y[row] = __float2bfloat16_rn(gelu_tanh(__bfloat162float(__float2bfloat16_rn(v))) * m);
     }
   } else if (epi == kEpiSiluMul) {
     // silu of the unrounded sum, times the multiplier (the up projection of a split-width SwiGLU)
     if (row < N) {
-      const float m = __uint_as_float((uint32_t)aux[row] << 16);
+      const float m = __uint_as_float(ld_cg_u16(aux + row) << 16);
       y[row] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * m);
     }
   } else {
