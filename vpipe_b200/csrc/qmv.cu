@@ -164,8 +164,12 @@ struct Walk {
       gt_end = b.x;
       P += a.y;
     } else {
-      gt = (int)(((int64_t)total_tiles * blockIdx.x) / gridDim.x);
-      gt_end = (int)(((int64_t)total_tiles * (blockIdx.x + 1)) / gridDim.x);
+      // as evenly as the tiles go, the extras to the lowest CTAs: those are placed first, one per SM,
+      // so no SM gets two of the extras while another has none
+      const int grid = (int)gridDim.x, b = (int)blockIdx.x;
+      const int q = total_tiles / grid, r = total_tiles - q * grid;
+      gt = b * q + min(b, r);
+      gt_end = gt + q + (b < r ? 1 : 0);
     }
     tile = gt - P->tile_begin;
     hi = P->row_tiles;
@@ -892,15 +896,14 @@ int fill_problem(QmvProblem* p, const uint32_t* w, const uint16_t* scales, const
 
 constexpr int kMaxGrid = 1023;  // CTAs a range table has room for
 
-// CTAs of a launch: at most two per SM, and no more than give every CTA the same number of row
-// tiles: 384 tiles run as 192 CTAs x 2 rather than 296 CTAs of which 88 take a second tile while
-// the rest of the machine idles (measured: +1 % on a chain of dependent decode launches).
+// CTAs of a launch: two per SM, or one per row tile if there are fewer. With the extra tiles on the
+// lowest CTAs an SM's two CTAs differ by at most one tile from any other SM's (384 tiles: 3 or 2 per
+// SM; as 192 CTAs x 2 some SMs would hold 4 and others 2). Measured on a chain of dependent decode
+// launches: 8.55 us per launch against 8.82 with equal tiles per CTA.
 int grid_for(int total_tiles) {
   int cap = 2 * num_sms();
   if (cap > kMaxGrid) { cap = kMaxGrid; }
-  if (total_tiles <= cap) { return total_tiles; }
-  const int per = (total_tiles + cap - 1) / cap;
-  return (total_tiles + per - 1) / per;
+  return total_tiles <= cap ? total_tiles : cap;
 }
 
 // Splits the concatenated row tiles of `count` problems into `grid` contiguous runs of about equal
