@@ -103,7 +103,11 @@ struct alignas(64) BatchProblem {
 // gpu-kernels/metal/quant/affine_qmv.metal:303-320: GGUF Q4_0 repacks): a k tile of 128 has four
 // groups and a lane's 32-nibble chunk is exactly one of them, so columns = (row of x 0..1, group
 // 0..3); lanes t and t ^ 1 of a quad then hold the two halves of a row's sum.
-template <int GROUP>
+// XREGS: 16-byte chunks of x a thread keeps in registers between the staging passes. 8 covers four
+// rows of K = 4096 but spills 140 bytes per thread; 4 does not spill and covers one or two rows of
+// K = 4096 (the group-32 GEMVs and the two-row batch), whose launches are short enough for the
+// spill traffic to show (an SM running two of these CTAs has less L1 than the spills need).
+template <int GROUP, int XREGS>
 __global__ void __launch_bounds__(kThreads, 2)
 affine_qmv_batch_w4_kernel(const __grid_constant__ BatchProblem P, int stages, int cap_kt) {
   constexpr int GPT = 128 / GROUP;            // groups per k tile
@@ -206,7 +210,7 @@ affine_qmv_batch_w4_kernel(const __grid_constant__ BatchProblem P, int stages, i
     const int chunks = KT * 16;          // 16-byte chunks of one padded row
     const int total = M * chunks;
     uint32_t amax[kMaxRows] = {0, 0, 0, 0};
-    constexpr int kXRegs = 8;  // chunks a thread keeps in registers between the two passes
+    constexpr int kXRegs = XREGS;
     uint4 xin[kXRegs];
     auto load_raw = [&](int i) {
       const int m = i / chunks, ci = i - m * chunks;
@@ -604,9 +608,10 @@ int launch_batch(const char* who, const vpq_linear_desc& d, int per_pass, cudaSt
   p.y_pitch = (int)y_pitch;
   p.aux_pitch = (int)aux_pitch;
   p.y3_pitch = (int)y3_pitch;
-  auto kern = affine_qmv_batch_w4_kernel<GROUP>;
   for (int64_t m0 = 0; m0 < M; m0 += per_pass) {
     const int rows = (int)((M - m0) < per_pass ? (M - m0) : per_pass);
+    const bool few = (int64_t)rows * cap_kt * 16 <= 4 * kConsThreads;  // chunks of the pass fit four per thread
+    auto kern = few ? affine_qmv_batch_w4_kernel<GROUP, 4> : affine_qmv_batch_w4_kernel<GROUP, 8>;
     p.x = static_cast<const uint16_t*>(x) + m0 * K;
     p.y = static_cast<__nv_bfloat16*>(y) + m0 * y_pitch;
     p.aux = d.aux ? static_cast<const uint16_t*>(d.aux) + m0 * aux_pitch : nullptr;
@@ -627,8 +632,8 @@ int launch_batch(const char* who, const vpq_linear_desc& d, int per_pass, cudaSt
     if (stages > kMaxStages) { stages = kMaxStages; }
     if (stages < 2) { return fail(VPQ_ERR_UNSUPPORTED, "%s: K=%lld does not fit in shared memory", who, (long long)K); }
     const size_t smem = fixed + (size_t)stages * stage_bytes<GROUP>();
-    static int granted[64] = {};
-    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), granted, smem)) { return rc; }
+    static int granted[2][64] = {};
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), granted[few ? 0 : 1], smem)) { return rc; }
     const int cap = 2 * num_sms();
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(p.row_tiles < cap ? p.row_tiles : cap), 1, 1);
