@@ -26,7 +26,11 @@
 //    lane folds four (row, group) sums per k tile with that group's scale -- and lane 3, whose
 //    digit does not exist, folds the bias term b * sum(x) instead. Accumulators start from the
 //    bit pattern of 12582912.0f, so the integer sum reads back as a float with no conversion;
-//  * x is staged once per CTA in shared memory, already as digit bytes in B-fragment order;
+//  * x is staged once per CTA in shared memory, already as digit bytes in B-fragment order; the raw
+//    values get there by asynchronous copies, so the staging holds nothing in registers across its
+//    passes. The kernel must not have a stack frame: two CTAs of 112 KB shared memory leave an SM
+//    less L1 than sixteen warps' spill slots, and a spilled value then costs a trip to L2 (measured:
+//    2 us per dependent launch with 176 bytes of frame per thread);
 //  * per row tile: two shuffles, one shared-memory reduction over the 8 warps.
 // One launch can run a whole list of GEMVs (a "plan"): the CTAs walk the concatenated row tiles
 // of all problems, the producer keeps streaming across problem boundaries, and the consumers
@@ -34,7 +38,8 @@
 // passed in the kernel parameters.
 // The launch opts into programmatic dependent launch: the producer starts
 // streaming weights before griddepcontrol.wait, so the next launch's stream is
-// already running while this one drains. Every barrier wait is bounded.
+// already running while this one drains, and the consumers wait only in front of
+// their first read of x, with the problem record already fetched. Every barrier wait is bounded.
 #include "vpq_sm100.cuh"
 
 #include <cstdlib>
