@@ -616,9 +616,11 @@ __device__ __forceinline__ uint32_t consume_tiles(const QmvProblem* P, int lo, i
   // byte offsets of this lane's two 16-byte reads inside its box, per half (k tile) of the box
   const uint32_t off_h0 = (uint32_t)rho * 128u + (uint32_t)(((0 + t) ^ rho) << 4);
   const uint32_t off_h1 = (uint32_t)rho * 128u + (uint32_t)(((4 + t) ^ rho) << 4);
-  // this lane's 8 bytes (4 groups of the warp's box) of row rho in the stage's scales or biases
+  // this lane's 8 bytes (4 groups of the warp's box) of row rho in the stage's scales or biases. The
+  // 64-byte rows arrive with the 64-byte swizzle (16-byte chunk ^= (row >> 1) & 3), so the eight
+  // rows a warp reads lie in eight different banks instead of two.
   const uint32_t sz_off = (uint32_t)kStageW + (bias_lane ? (uint32_t)kStageSZ / 2 : 0u) + (uint32_t)rho * 64u +
-                          (uint32_t)warp * 8u;
+                          (uint32_t)((((warp >> 1) ^ (rho >> 1)) & 3) << 4) + (uint32_t)(warp & 1) * 8u;
 
   const AccInit acc_init = make_acc_init(kAccInit);
   int s = (int)(state & 7u);
@@ -879,11 +881,11 @@ int fill_problem(QmvProblem* p, const uint32_t* w, const uint16_t* scales, const
   if (p->scales_tma) {
     const int G = K / 64;
     if (int rc = make_map_2d(&p->ms, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, (uint64_t)G, rows, 32,
-                             16, CU_TENSOR_MAP_SWIZZLE_NONE, "scales")) {
+                             16, CU_TENSOR_MAP_SWIZZLE_64B, "scales")) {
       return rc;
     }
     if (int rc = make_map_2d(&p->mz, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, biases, (uint64_t)G, rows, 32,
-                             16, CU_TENSOR_MAP_SWIZZLE_NONE, "biases")) {
+                             16, CU_TENSOR_MAP_SWIZZLE_64B, "biases")) {
       return rc;
     }
   }
