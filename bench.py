@@ -14,7 +14,8 @@ memory and the result read back, inside the timed region. The same JSON line car
   c1            the single 4096 x 4096 GEMV of configs[0], cold weights, one launch per GEMV
   decode_chain  36 decoder layers as a DEPENDENT chain (norm + q|k|v, o + residual, norm + gate|up
                 with SwiGLU, down + residual; each GEMV reads what the one before wrote), as one
-                chained launch and as one launch per GEMV, with a bit-identity check between them
+                chained launch and as one launch per GEMV (graph replay), with a bit-identity check
+                between them; `value` is the faster form, named in `form`
   qmm, qmm_c3   the tensor-core GEMM on the DiT (C4) and prefill (C3) shapes in TFLOP/s
   cpu_baseline  the reference's CPU arithmetic for the same op on the host cores (QMV and QMM).
 
@@ -537,13 +538,21 @@ def bench_decode_chain(torch, ops, synth, dev, pk, layers=LAYERS, reps=10):
     t_chain = timed(torch, plan.run, reps, 3, lambda: None) / reps
     assert ops.device_status() == 0
     plan.close()
-    gbs = nbytes / t_chain / 1e9
+    forms = {
+        "launch_per_gemv": {"value": nbytes / t_launch / 1e9, "unit": "GB/s", "ms_per_step": t_launch * 1e3,
+                            "launches_per_step": len(problems),
+                            "mode": "one launch per GEMV, programmatic dependent launch, cuda-graph replay"},
+        "chained_launch": {"value": nbytes / t_chain / 1e9, "unit": "GB/s", "ms_per_step": t_chain * 1e3,
+                           "launches_per_step": 1, "mode": "one cooperative launch, dependencies waited for on chip"},
+    }
+    best = max(forms, key=lambda k: forms[k]["value"])
+    gbs = forms[best]["value"]
+    # `value` is the faster of the two ways this library runs a dependent chain; both are listed.
     return {"workload": f"{layers} decoder layers (8B shapes) as a dependent chain of {len(problems)} fused GEMVs",
-            "value": gbs, "unit": "GB/s", "frac_of_hbm_peak": gbs / pk["hbm_gbs"], "ms_per_step": t_chain * 1e3,
-            "launches_per_step": 1, "bytes_per_step": nbytes,
-            "launch_per_gemv": {"value": nbytes / t_launch / 1e9, "unit": "GB/s", "ms_per_step": t_launch * 1e3,
-                                "launches_per_step": len(problems), "mode": "cuda-graph replay"},
-            "bit_identical_to_launch_per_gemv": bool(same)}
+            "value": gbs, "unit": "GB/s", "frac_of_hbm_peak": gbs / pk["hbm_gbs"], "form": best,
+            "ms_per_step": forms[best]["ms_per_step"], "launches_per_step": forms[best]["launches_per_step"],
+            "bytes_per_step": nbytes, "launch_per_gemv": forms["launch_per_gemv"],
+            "chained_launch": forms["chained_launch"], "bit_identical_to_launch_per_gemv": bool(same)}
 
 
 def bench_qmm(torch, dist, ops, synth, args, dev, pk, key):
