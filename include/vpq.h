@@ -295,7 +295,12 @@ int vpq_affine_qmv_w4g32_q40_bf16_fused(const vpq_linear_desc* desc_host, void* 
  * launch per GEMV. An expert index array (`expert`) must be complete before the launch. Pointers
  * are captured at creation, their contents may change between runs. `workspace` is caller-owned device memory
  * of vpq_qmv_plan_bytes() bytes holding the per-problem descriptors; it must outlive the plan.
- * vpq_qmv_plan_create copies into it and synchronises `stream`; vpq_qmv_plan_run only launches. */
+ * vpq_qmv_plan_create copies into it and synchronises `stream`; vpq_qmv_plan_run only launches.
+ * A large list of independent GEMVs keeps the last tenth of its row tiles as a pool that the CTAs
+ * draw from as they finish (the SMs of a GPU do not stream at one rate); whoever computes a tile,
+ * its bytes are the same. The pool's counter and the chain's counters live in the workspace and go
+ * back to zero at the end of every run, so runs of one plan must follow one another on the GPU:
+ * one stream, or streams ordered by events -- never two runs of the same plan at once. */
 typedef struct vpq_qmv_plan_s vpq_qmv_plan;
 size_t vpq_qmv_plan_bytes(const vpq_linear_desc* descs_host, int count);
 int vpq_qmv_plan_create(const vpq_linear_desc* descs_host, int count, void* workspace, size_t bytes,

@@ -345,6 +345,40 @@ def test_dispatch_by_reference_names(vpq, oracle_mod):
     assert torch.equal(c2, c3) and torch.equal(s2, s3) and torch.equal(b2, b3)
 
 
+def test_large_plan_with_a_pool_of_chunks_equals_single_launches(vpq, oracle_mod):
+    """A plan with enough row tiles hands its last tenth out at run time (chunks claimed by the CTAs
+    that finish first). Whoever computes a tile, the bytes must be those of the per-GEMV launches, on
+    every run, also back to back without a host synchronise (the next run's claims wait for the
+    previous run to put the counter back)."""
+    torch.manual_seed(5)
+    shapes = [(512, 4096)] * 30 + [(1024, 2064), (3840, 1000), (256, 4096), (512, 4096), (1536, 2048)] * 3
+    xs = {}
+    problems, singles = [], []
+    for i, (K, N) in enumerate(shapes):
+        codes = torch.randint(-2**31, 2**31 - 1, (N, K // 8), dtype=torch.int32, device=dev())
+        s = (torch.rand((N, K // 64), device=dev()) * 0.015 + 0.005).to(torch.bfloat16)
+        b = (torch.rand((N, K // 64), device=dev()) * 0.2 - 0.1).to(torch.bfloat16)
+        if (K, i % 3) not in xs:
+            xs[(K, i % 3)] = torch.randn((1, K), device=dev()).to(torch.bfloat16)
+        x = xs[(K, i % 3)]
+        y = torch.zeros((1, N), dtype=torch.bfloat16, device=dev())
+        problems.append((codes, s, b, x, y))
+        singles.append(vpq.ops.qmv(codes, s, b, x))
+    assert sum((N + 15) // 16 for _, N in shapes) >= 32 * 2 * torch.cuda.get_device_properties(dev()).multi_processor_count
+    plan = vpq.ops.QmvPlan(problems)
+    for run in range(3):
+        for p in problems:
+            p[4].zero_()
+        plan.run()
+        plan.run()
+        plan.run()
+        torch.cuda.synchronize()
+        for i, (p, want) in enumerate(zip(problems, singles)):
+            assert torch.equal(p[4], want), f"run {run}: GEMV {i} differs"
+    plan.close()
+    assert vpq.ops.device_status() == 0
+
+
 def test_qmv_and_qmm_agree_on_small_m(vpq, oracle_mod):
     """Both kernels on the same rows: QMM rounds W to bf16 first, so agreement is to tolerance."""
     N, K, M = 1024, 4096, 4

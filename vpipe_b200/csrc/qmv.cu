@@ -44,6 +44,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <vector>
 
 namespace vpq {
 
@@ -61,6 +62,7 @@ constexpr int kStageW = kBoxesPerStage * kBoxBytes;  // 16 KB of nibbles
 constexpr int kStageSZ = 2 * 16 * 64;        // scales + biases of the span: 2 x [16 rows x 32 groups]
 constexpr int kMaxStages = 6;
 constexpr int kRedSlots = 8;                 // row tiles whose cross-warp sums may be pending
+constexpr int kDynSlots = 8;                 // chunks the producer may have posted ahead of the slowest consumer warp (> ring depth)
 
 // D = A * B + C: A unsigned bytes [16 x 32], B signed bytes [32 x 8], s32 accumulate.
 __device__ __forceinline__ void mma_u8s8_16832(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -141,7 +143,11 @@ static_assert(sizeof(QmvProblem) == 512, "problem records are laid out back to b
 // How a launch's row tiles are dealt to the CTAs.
 //   single: one GEMV in the kernel parameters, tiles split evenly.
 //   ranges: a list of independent GEMVs; the host's table gives every CTA one contiguous run of the
-//           concatenated tiles.
+//           concatenated tiles. A plan may keep the last tenth of its tiles out of the table, as a
+//           pool of chunks (a few tiles of one GEMV each): a CTA that has finished its run takes
+//           chunks from the pool until it is empty, so the CTAs of slower SMs end up with less. The
+//           producer thread claims a chunk (one atomic add on a counter in the plan's workspace) and
+//           posts it to its consumers through a small queue in shared memory.
 //   chain:  a list whose GEMVs may read what earlier ones wrote. Every GEMV is spread over the whole
 //           grid (as evenly as its tiles go), a
 //           counter in global memory counts finished tiles, and a GEMV with wait_tiles > 0 stages its
@@ -180,7 +186,68 @@ struct Walk {
     hi = P->row_tiles;
     left = gt_end - gt;
   }
-  // Advances to this CTA's next run of tiles [lo, hi) inside one problem (P).
+  // The producer thread's way into the pool: claims the next chunk and posts it (or the end mark,
+  // a chunk of no tiles) to the consumer warps. False when the pool is empty.
+  // `dyn_n`: chunks taken so far.
+  __device__ __forceinline__ bool claim_chunk(const QmvProblem* list, uint32_t* dq, uint32_t* dyn, const int4* chunks,
+                                              int num_chunks, volatile uint32_t* abort_flag, uint32_t& dyn_n) {
+    // The counter belongs to the previous launch of the plan until that launch has ended.
+    if (dyn_n == 0) { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+    // (after a wait of this CTA has given up its consumers may be gone: claim nothing more)
+    const uint32_t c = *abort_flag ? (uint32_t)num_chunks : atomicAdd(dyn, 1u);
+    const int4 ch = c < (uint32_t)num_chunks ? __ldg(chunks + c) : make_int4(0, 0, 0, 0);
+    volatile uint32_t* e = dq + (dyn_n & (kDynSlots - 1)) * 4;
+    e[0] = (uint32_t)ch.x;
+    e[1] = (uint32_t)ch.y;
+    e[2] = (uint32_t)ch.z;
+    __threadfence_block();
+    ++dyn_n;
+    *reinterpret_cast<volatile uint32_t*>(dq + kDynSlots * 4) = dyn_n;
+    if (ch.z == 0) { return false; }
+    P = list + ch.y;
+    tile = ch.x - P->tile_begin;
+    hi = P->row_tiles;
+    left = ch.z;
+    return true;
+  }
+  // A consumer warp's way: waits (bounded) for the producer's next post. False at the end mark.
+  __device__ __forceinline__ bool receive_chunk(const QmvProblem* list, const uint32_t* dq, volatile uint32_t* abort_flag,
+                                                uint32_t& dyn_n) {
+    uint32_t gt = 0, prob = 0, cnt = 0;
+    if ((threadIdx.x & 31) == 0) {
+      const volatile uint32_t* posted = dq + kDynSlots * 4;
+      bool got = false;
+      for (uint32_t i = 0; i < (1u << 28); ++i) {
+        if (*posted > dyn_n) {
+          got = true;
+          break;
+        }
+        if (*abort_flag) { break; }
+      }
+      if (got) {
+        __threadfence_block();
+        const volatile uint32_t* e = dq + (dyn_n & (kDynSlots - 1)) * 4;
+        gt = e[0];
+        prob = e[1];
+        cnt = e[2];
+      } else if (!*abort_flag) {
+        *abort_flag = 1;
+        atomicCAS(&g_qmv_status, 0u, (5u << 8) | kRoleConsumer);
+      }
+    }
+    gt = __shfl_sync(0xffffffffu, gt, 0);
+    prob = __shfl_sync(0xffffffffu, prob, 0);
+    cnt = __shfl_sync(0xffffffffu, cnt, 0);
+    ++dyn_n;
+    if (cnt == 0) { return false; }
+    P = list + prob;
+    tile = (int)gt - P->tile_begin;
+    hi = P->row_tiles;
+    left = (int)cnt;
+    return true;
+  }
+  // Advances to this CTA's next run of tiles [lo, hi) inside one problem (P). When it returns false
+  // in a launch with a pool, claim_chunk / receive_chunk refill the walk and the caller asks again.
   __device__ __forceinline__ bool next_range(int& lo, int& out_hi, bool chain) {
     if (!chain) {
       if (left <= 0) { return false; }
@@ -240,6 +307,9 @@ struct Scratch {
   uint32_t* sq_cnt;
   uint64_t* bars;
   volatile uint32_t* abort_flag;
+  // chunks of the launch's shared pool the producer has claimed for this CTA: kDynSlots entries of
+  // {first tile, problem, tiles, -}, then the number of entries posted so far
+  uint32_t* dq;
   __device__ __forceinline__ Scratch(unsigned char* p0, int cap_kt) {
     zero128 = reinterpret_cast<uint4*>(p0);
     xq = p0 + 128;
@@ -252,6 +322,7 @@ struct Scratch {
     sq_cnt = reinterpret_cast<uint32_t*>(sq_part + 2 * kConsWarps);
     bars = reinterpret_cast<uint64_t*>(sq_cnt + 8);
     abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * kMaxStages);
+    dq = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages) + 4;
   }
 };
 
@@ -504,7 +575,8 @@ __device__ __forceinline__ bool stage_x(const QmvProblem* P, unsigned char* p0, 
 // earlier GEMV of a chain.
 __device__ __noinline__ void produce(const QmvProblem* single, const QmvProblem* list, const int2* ranges,
                                      int total_tiles, int stages, int count, bool chain, uint32_t base, uint32_t bar0,
-                                     volatile uint32_t* abort_flag) {
+                                     volatile uint32_t* abort_flag, uint32_t* dq, uint32_t* dyn, const int4* chunks,
+                                     int num_chunks) {
   constexpr int kStageBytes = kStageW + kStageSZ;
   auto bar_full = [&](int s) { return bar0 + 8u * s; };
   auto bar_empty = [&](int s) { return bar0 + 8u * (kMaxStages + s); };
@@ -523,7 +595,10 @@ __device__ __noinline__ void produce(const QmvProblem* single, const QmvProblem*
     fenced = Q;
   };
   int lo = 0, hi = 0;
-  while (ok && wk.next_range(lo, hi, chain)) {
+  uint32_t dyn_n = 0;
+  while (ok && (wk.next_range(lo, hi, chain) ||
+                (dyn && wk.claim_chunk(list, dq, dyn, chunks, num_chunks, abort_flag, dyn_n) &&
+                 wk.next_range(lo, hi, chain)))) {
     const QmvProblem* P = wk.P;
     NB = (P->K + 255) >> 8;                              // 128-byte boxes per row
     SPT = (NB + kBoxesPerStage - 1) / kBoxesPerStage;    // stages per row tile
@@ -770,10 +845,13 @@ __device__ __forceinline__ uint32_t consume_tiles(const QmvProblem* P, int lo, i
   return (uint32_t)s | (ph << 3) | (tile_seq << 4);
 }
 
+// kPool: the launch has a pool of chunks (a plan of independent GEMVs). Its own instantiation, and
+// the pool's loop after the table's, so that the launches without a pool keep their code.
+template <bool kPool>
 __global__ void __launch_bounds__(kThreads, 2)
 affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProblem* __restrict__ list,
                         const int2* __restrict__ ranges, int total_tiles, int stages, int cap_kt, int count,
-                        uint32_t* sync) {
+                        uint32_t* sync, uint32_t* dyn, const int4* __restrict__ chunks, int num_chunks) {
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t raw = smem_u32(smem_dyn);
   const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled boxes need 1024-byte alignment
@@ -797,6 +875,7 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
     *sc.abort_flag = 0;
     for (int i = 0; i < kRedSlots; ++i) { sc.red_cnt[i] = 0; }
     for (int i = 0; i < 8; ++i) { sc.sq_cnt[i] = 0; }
+    sc.dq[kDynSlots * 4] = 0;
     fence_mbar_init();
   }
   if (threadIdx.x < 8) { sc.zero128[threadIdx.x] = make_uint4(0, 0, 0, 0); }
@@ -806,7 +885,10 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
   __syncthreads();
 
   if (warp == kConsWarps) {
-    if (lane == 0) { produce(&single, list, ranges, total_tiles, stages, count, chain, base, bar0, sc.abort_flag); }
+    if (lane == 0) {
+      produce(&single, list, ranges, total_tiles, stages, count, chain, base, bar0, sc.abort_flag, sc.dq,
+              kPool ? dyn : nullptr, chunks, num_chunks);
+    }
     return;
   }
 
@@ -833,17 +915,39 @@ affine_qmv_w4g64_kernel(const __grid_constant__ QmvProblem single, const QmvProb
     state = consume_tiles(P, lo, hi, state, base_ptr, stages, cap_kt, sync);
     if (state == kConsumeFailed) { break; }
   }
-  if (chain) {
+  if constexpr (kPool) {
+    // The pool: chunks the producer claims once the table's run is used up. The loop body is the one
+    // above, written out a second time: as one loop over both sources the launches without a pool
+    // lost 1 - 2 % (the hot loop's register allocation moved).
+    uint32_t dyn_n = 0;
+    while (state != kConsumeFailed && !*sc.abort_flag && wk.receive_chunk(list, sc.dq, sc.abort_flag, dyn_n) &&
+           wk.next_range(lo, hi, chain)) {
+      const QmvProblem* P = wk.P;
+      const int K = P->K;
+      const uint16_t* xr = P->x;
+      if (P->norm_w != nullptr || P->xrow != nullptr || xr != staged_x || K != staged_K) {
+        if (!stage_x(P, p0, cap_kt, sq_gen, 0, sync)) { break; }
+        staged_x = P->norm_w ? nullptr : xr;
+        staged_K = K;
+        if (P->norm_w) { ++sq_gen; }
+      }
+      state = consume_tiles(P, lo, hi, state, base_ptr, stages, cap_kt, sync);
+      if (state == kConsumeFailed) { break; }
+    }
+  }
+  if (chain || kPool) {
     // The CTA that leaves last puts both counters back to zero for the next run (every CTA has
-    // passed all of its waits by then, also one that gave up). No barrier: the warp of a CTA that
-    // leaves last reports for the CTA.
+    // passed all of its waits by then, also one that gave up, and every producer has made its last
+    // claim, since its consumers leave only after the end mark it posts). No barrier: the warp of a
+    // CTA that leaves last reports for the CTA.
+    uint32_t* ctr = chain ? sync : dyn;
     __syncwarp();
     if (lane == 0) {
       __threadfence();
       if (atomicAdd(&sc.sq_cnt[2], 1u) == (uint32_t)(kConsWarps - 1)) {
-        if (atomicAdd(sync + 1, 1u) == gridDim.x - 1) {
-          sync[0] = 0;
-          sync[1] = 0;
+        if (atomicAdd(ctr + 1, 1u) == gridDim.x - 1) {
+          ctr[0] = 0;
+          ctr[1] = 0;
           __threadfence();
         }
       }
@@ -861,7 +965,7 @@ LaunchShape shape_for(int cap_kt) {
   const size_t stage_bytes = kStageW + kStageSZ;
   const size_t fixed = 1024 /*alignment slack*/ + 128 + (size_t)cap_kt * kXBytesPerKt + (size_t)2 * cap_kt * 4 + 16 +
                        (size_t)((cap_kt / 2 + 3) & ~3) * 4 + kRedSlots * kConsWarps * 16 * 4 + kRedSlots * 4 +
-                       2 * kConsWarps * 4 + 32 + 2 * kMaxStages * 8 + 16;
+                       2 * kConsWarps * 4 + 32 + 2 * kMaxStages * 8 + 16 + (kDynSlots * 4 + 4) * 4;
   const size_t budget = 112 * 1024;  // two CTAs per SM
   int stages = fixed + 2 * stage_bytes <= budget ? (int)((budget - fixed) / stage_bytes) : 2;
   if (stages > kMaxStages) { stages = kMaxStages; }
@@ -917,11 +1021,12 @@ int grid_for(int total_tiles) {
 // cost (a tile costs its stages -- the kernel is bound by the bytes it streams -- plus a small
 // fixed share for the reduction and the store).
 // out[b] = {first tile of CTA b, index of the problem it belongs to}, out[grid] closes the list.
+int64_t tile_cost(const QmvProblem& q) {
+  const int nb = (q.K + 255) >> 8;
+  return (int64_t)(16 * ((nb + kBoxesPerStage - 1) / kBoxesPerStage) + 3);  // measured: the fixed share is ~0.2 stage
+}
+
 void build_ranges(const QmvProblem* p, size_t count, int grid, int2* out) {
-  auto tile_cost = [](const QmvProblem& q) {
-    const int nb = (q.K + 255) >> 8;
-    return (int64_t)(16 * ((nb + kBoxesPerStage - 1) / kBoxesPerStage) + 3);  // measured: the fixed share is ~0.2 stage
-  };
   int64_t total = 0;
   for (size_t r = 0; r < count; ++r) { total += tile_cost(p[r]) * p[r].row_tiles; }
   size_t r = 0;
@@ -941,14 +1046,18 @@ void build_ranges(const QmvProblem* p, size_t count, int grid, int2* out) {
 }
 
 int g_granted[64] = {};  // dynamic shared memory already granted to the kernel, per device
+int g_granted_pool[64] = {};
 
 // `sync` not null: the list is a dependent chain (two counters in device memory, zero between
 // runs); the launch is cooperative because its CTAs wait on one another.
 int launch_list(const QmvProblem& single, const QmvProblem* list, const int2* ranges, int total_tiles, int cap_kt,
-                cudaStream_t st, int count = 1, uint32_t* sync = nullptr, int chain_grid = 0) {
+                cudaStream_t st, int count = 1, uint32_t* sync = nullptr, int chain_grid = 0, uint32_t* dyn = nullptr,
+                const int4* chunks = nullptr, int num_chunks = 0) {
   const LaunchShape ls = shape_for(cap_kt);
-  auto kern = affine_qmv_w4g64_kernel;
-  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), g_granted, ls.smem)) { return rc; }
+  auto kern = dyn ? affine_qmv_w4g64_kernel<true> : affine_qmv_w4g64_kernel<false>;
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), dyn ? g_granted_pool : g_granted, ls.smem)) {
+    return rc;
+  }
   const int ctas = sync ? chain_grid : grid_for(total_tiles);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)ctas, 1, 1);
@@ -965,7 +1074,8 @@ int launch_list(const QmvProblem& single, const QmvProblem* list, const int2* ra
   }
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  VPQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, single, list, ranges, total_tiles, ls.stages, cap_kt, count, sync));
+  VPQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, single, list, ranges, total_tiles, ls.stages, cap_kt, count, sync, dyn,
+                                 chunks, num_chunks));
   return VPQ_OK;
 }
 
@@ -973,7 +1083,7 @@ int launch_list(const QmvProblem& single, const QmvProblem* list, const int2* ra
 // calculator grants for this kernel's shared memory, and no more than the largest GEMV has tiles.
 int chain_grid_for(int cap_kt, int max_row_tiles, int* out) {
   const LaunchShape ls = shape_for(cap_kt);
-  auto kern = affine_qmv_w4g64_kernel;
+  auto kern = affine_qmv_w4g64_kernel<false>;
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), g_granted, ls.smem)) { return rc; }
   int per_sm = 0;
   VPQ_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, ls.smem));
@@ -1189,6 +1299,9 @@ struct vpq_qmv_plan_s {
   const QmvProblem* list_dev;
   const int2* ranges_dev;
   uint32_t* sync_dev;  // dependent chain: {finished tiles, CTAs that left}; null for independent GEMVs
+  uint32_t* dyn_dev;   // pool of chunks: {chunks claimed, CTAs that left}; null without a pool
+  const int4* chunks_dev;  // the pool: {first tile, problem, tiles, 0} per chunk
+  int num_chunks;
   int count;           // problems (one per GEMV row)
   int total_tiles;
   int cap_kt;
@@ -1284,11 +1397,29 @@ extern "C" int vpq_affine_qmv_w4g64_bf16_batch(const vpq_linear_desc* d, int cou
   return VPQ_OK;
 }
 
+namespace {
+// The pool of a plan of independent GEMVs: the share of the launch's cost that is handed out in
+// chunks at run time, the cost of one chunk in units of tile_cost (about eight 4096-k tiles: long
+// enough to pay for a staging of x, short next to the spread of the CTAs' finishing times, which it
+// bounds), and the least work per CTA for a pool to be worth having.
+constexpr int kPoolPercent = 10;
+constexpr int64_t kChunkCost = 8 * 35;
+constexpr int kPoolMinTilesPerCta = 32;
+
+size_t pool_chunks_bound(size_t tiles, size_t rows) { return tiles * (kPoolPercent + 2) / 100 + rows + 8; }
+}  // namespace
+
 extern "C" size_t vpq_qmv_plan_bytes(const vpq_linear_desc* d, int count) {
   if (!d || count <= 0) { return 0; }
-  size_t rows = 0;
-  for (int i = 0; i < count; ++i) { rows += d[i].M > 0 ? (size_t)d[i].M : 0; }
-  return rows * sizeof(QmvProblem) + 64 + (kMaxGrid + 1) * sizeof(int2) + 64 /* the chain's counters */;
+  size_t rows = 0, tiles = 0;
+  for (int i = 0; i < count; ++i) {
+    if (d[i].M > 0 && d[i].N > 0) {
+      rows += (size_t)d[i].M;
+      tiles += (size_t)d[i].M * (size_t)((d[i].N + 15) / 16);
+    }
+  }
+  return rows * sizeof(QmvProblem) + 64 + (kMaxGrid + 1) * sizeof(int2) + 64 /* the chain's counters */ +
+         128 /* the pool's counters, alignment */ + pool_chunks_bound(tiles, rows) * sizeof(int4);
 }
 
 extern "C" int vpq_qmv_plan_create(const vpq_linear_desc* d, int count, void* workspace, size_t bytes,
@@ -1340,7 +1471,43 @@ extern "C" int vpq_qmv_plan_create(const vpq_linear_desc* d, int count, void* wo
   }
   const int grid = grid_for(tiles);
   int2 host_ranges[kMaxGrid + 1];
-  build_ranges(host, rows, grid, host_ranges);
+  const uintptr_t dev_dyn = dev_sync + 64;
+  const uintptr_t dev_chunks = dev_dyn + 64;
+  std::vector<int4> pool;
+  if (!chain && tiles >= kPoolMinTilesPerCta * grid) {
+    // The tail of the list, worth kPoolPercent of the launch's cost, leaves the CTAs' table and
+    // becomes the pool: chunks of about kChunkCost, none across two GEMVs, in list order.
+    int64_t total = 0;
+    for (size_t q = 0; q < rows; ++q) { total += tile_cost(host[q]) * host[q].row_tiles; }
+    int64_t want = total * kPoolPercent / 100;
+    size_t split = rows;      // first problem with tiles in the pool
+    int split_tiles = 0;      // tiles of it that stay in the table
+    while (split > 0 && want > 0) {
+      --split;
+      const int64_t c = tile_cost(host[split]);
+      const int64_t take = want / c < host[split].row_tiles ? want / c : host[split].row_tiles;
+      split_tiles = host[split].row_tiles - (int)take;
+      want -= take * c;
+      if (take < host[split].row_tiles) { break; }
+    }
+    for (size_t q = split; q < rows; ++q) {
+      const int per = (int)(kChunkCost / tile_cost(host[q]) > 0 ? kChunkCost / tile_cost(host[q]) : 1);
+      for (int t = q == split ? split_tiles : 0; t < host[q].row_tiles; t += per) {
+        const int n = host[q].row_tiles - t < per ? host[q].row_tiles - t : per;
+        pool.push_back(make_int4(host[q].tile_begin + t, (int)q, n, 0));
+      }
+    }
+    if (pool.empty() || pool.size() > pool_chunks_bound((size_t)tiles, rows) || (split == 0 && split_tiles == 0)) {
+      pool.clear();
+    } else {
+      // the table over what stays: the list up to the split, the split problem cut short
+      const int kept = host[split].row_tiles;
+      host[split].row_tiles = split_tiles;
+      build_ranges(host, split_tiles > 0 ? split + 1 : split, grid, host_ranges);
+      host[split].row_tiles = kept;
+    }
+  }
+  if (pool.empty()) { build_ranges(host, rows, grid, host_ranges); }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e = cudaMemcpyAsync(reinterpret_cast<void*>(dev), host, rows * sizeof(QmvProblem),
                                   cudaMemcpyHostToDevice, st);
@@ -1348,7 +1515,11 @@ extern "C" int vpq_qmv_plan_create(const vpq_linear_desc* d, int count, void* wo
     e = cudaMemcpyAsync(reinterpret_cast<void*>(dev_ranges), host_ranges, (size_t)(grid + 1) * sizeof(int2),
                         cudaMemcpyHostToDevice, st);
   }
-  if (e == cudaSuccess) { e = cudaMemsetAsync(reinterpret_cast<void*>(dev_sync), 0, 16, st); }
+  if (e == cudaSuccess && !pool.empty()) {
+    e = cudaMemcpyAsync(reinterpret_cast<void*>(dev_chunks), pool.data(), pool.size() * sizeof(int4),
+                        cudaMemcpyHostToDevice, st);
+  }
+  if (e == cudaSuccess) { e = cudaMemsetAsync(reinterpret_cast<void*>(dev_sync), 0, 128, st); }
   if (e == cudaSuccess) { e = cudaStreamSynchronize(st); }
   std::free(host);
   if (e != cudaSuccess) { return fail(VPQ_ERR_CUDA, "qmv_plan_create: copy failed: %s", cudaGetErrorString(e)); }
@@ -1356,6 +1527,9 @@ extern "C" int vpq_qmv_plan_create(const vpq_linear_desc* d, int count, void* wo
   plan->list_dev = reinterpret_cast<const QmvProblem*>(dev);
   plan->ranges_dev = reinterpret_cast<const int2*>(dev_ranges);
   plan->sync_dev = chain ? reinterpret_cast<uint32_t*>(dev_sync) : nullptr;
+  plan->dyn_dev = pool.empty() ? nullptr : reinterpret_cast<uint32_t*>(dev_dyn);
+  plan->chunks_dev = pool.empty() ? nullptr : reinterpret_cast<const int4*>(dev_chunks);
+  plan->num_chunks = (int)pool.size();
   plan->count = (int)rows;
   plan->total_tiles = tiles;
   plan->cap_kt = cap_kt;
@@ -1375,7 +1549,8 @@ extern "C" int vpq_qmv_plan_run(const vpq_qmv_plan* plan, void* stream) {
                        static_cast<cudaStream_t>(stream), plan->count, plan->sync_dev, plan->chain_grid);
   }
   return launch_list(unused, plan->list_dev, plan->ranges_dev, plan->total_tiles, plan->cap_kt,
-                     static_cast<cudaStream_t>(stream), plan->count);
+                     static_cast<cudaStream_t>(stream), plan->count, nullptr, 0, plan->dyn_dev, plan->chunks_dev,
+                     plan->num_chunks);
 }
 
 // ---------------------------------------------------------------- no-allocation variant
