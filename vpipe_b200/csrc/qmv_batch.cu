@@ -104,9 +104,10 @@ struct alignas(64) BatchProblem {
 // groups and a lane's 32-nibble chunk is exactly one of them, so columns = (row of x 0..1, group
 // 0..3); lanes t and t ^ 1 of a quad then hold the two halves of a row's sum.
 // XREGS: 16-byte chunks of x a thread keeps in registers between the staging passes. 8 covers four
-// rows of K = 4096 but spills 140 bytes per thread; 4 does not spill and covers one or two rows of
-// K = 4096 (the group-32 GEMVs and the two-row batch), whose launches are short enough for the
-// spill traffic to show (an SM running two of these CTAs has less L1 than the spills need).
+// rows of K = 4096 but spills 140 bytes per thread, 6 (three rows) spills 48, 4 does not spill and
+// covers one or two rows of K = 4096 (the group-32 GEMVs and the two-row batch), whose launches are
+// short enough for the spill traffic to show (an SM running two of these CTAs has less L1 than the
+// spills need).
 template <int GROUP, int XREGS>
 __global__ void __launch_bounds__(kThreads, 2)
 affine_qmv_batch_w4_kernel(const __grid_constant__ BatchProblem P, int stages, int cap_kt) {
@@ -610,8 +611,13 @@ int launch_batch(const char* who, const vpq_linear_desc& d, int per_pass, cudaSt
   p.y3_pitch = (int)y3_pitch;
   for (int64_t m0 = 0; m0 < M; m0 += per_pass) {
     const int rows = (int)((M - m0) < per_pass ? (M - m0) : per_pass);
-    const bool few = (int64_t)rows * cap_kt * 16 <= 4 * kConsThreads;  // chunks of the pass fit four per thread
-    auto kern = few ? affine_qmv_batch_w4_kernel<GROUP, 4> : affine_qmv_batch_w4_kernel<GROUP, 8>;
+    // chunks of x per thread in this pass: the instantiation that holds just that many (4: no stack
+    // frame, 6: 48 bytes, 8: 140 bytes)
+    const int64_t per_thread = ((int64_t)rows * cap_kt * 16 + kConsThreads - 1) / kConsThreads;
+    const int held = per_thread <= 4 ? 0 : per_thread <= 6 ? 1 : 2;
+    auto kern = held == 0   ? affine_qmv_batch_w4_kernel<GROUP, 4>
+                : held == 1 ? affine_qmv_batch_w4_kernel<GROUP, 6>
+                            : affine_qmv_batch_w4_kernel<GROUP, 8>;
     p.x = static_cast<const uint16_t*>(x) + m0 * K;
     p.y = static_cast<__nv_bfloat16*>(y) + m0 * y_pitch;
     p.aux = d.aux ? static_cast<const uint16_t*>(d.aux) + m0 * aux_pitch : nullptr;
@@ -632,8 +638,8 @@ int launch_batch(const char* who, const vpq_linear_desc& d, int per_pass, cudaSt
     if (stages > kMaxStages) { stages = kMaxStages; }
     if (stages < 2) { return fail(VPQ_ERR_UNSUPPORTED, "%s: K=%lld does not fit in shared memory", who, (long long)K); }
     const size_t smem = fixed + (size_t)stages * stage_bytes<GROUP>();
-    static int granted[2][64] = {};
-    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), granted[few ? 0 : 1], smem)) { return rc; }
+    static int granted[3][64] = {};
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), granted[held], smem)) { return rc; }
     const int cap = 2 * num_sms();
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(p.row_tiles < cap ? p.row_tiles : cap), 1, 1);
