@@ -512,7 +512,8 @@ __device__ __forceinline__ bool stage_x(const QmvProblem* P, unsigned char* p0, 
     }
     uint32_t amax = 0;  // largest |x| of the box as bf16 bits (ordering of magnitudes == ordering of bit patterns)
 #pragma unroll
-    for (int q = 0; q < 8; ++q) { amax = max(amax, max(v[q] & 0x7fffu, (v[q] >> 16) & 0x7fffu)); }
+    for (int q = 0; q < 8; ++q) { amax = __vmaxu2(amax, v[q] & 0x7fff7fffu); }  // both halves at once
+    amax = max(amax & 0xffffu, amax >> 16);
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) { amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, o)); }
     int e = (int)(amax >> 7);            // biased exponent of the largest magnitude
